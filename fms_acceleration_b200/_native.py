@@ -1,0 +1,145 @@
+"""ctypes binding to the in-tree native library ``lib/libfmsb200.so``.
+
+Every native entry point is an ``extern "C"`` launcher taking raw device pointers, sizes and a
+``cudaStream_t``; the Python wrappers in :mod:`fms_acceleration_b200.ops` own allocation and autograd.
+The library is built in-tree (see :mod:`fms_acceleration_b200.build`); on a machine with a GPU a
+missing library is an error, never a silent fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+_LIB = None
+_LOCK = threading.Lock()
+
+P = c_void_p
+I = c_int
+L = c_longlong
+F = c_float
+
+# name -> argtypes (all return int)
+_SIGNATURES = {
+    "fmsb_gemm": [P, L, P, L, I, P, L, P, L, I, I, I, P, L, I, P, L, F, F, I, I, I, I, I, P, P],
+    "fmsb_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, I, I, P],
+    "fmsb_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, I, I, I, P],
+    "fmsb_rope": [P, P, P, P, I, I, I, L, F, I, P],
+    "fmsb_glu_fwd": [P, P, P, I, I, L, L, L, I, I, P],
+    "fmsb_glu_bwd": [P, P, P, P, P, P, I, I, L, L, L, L, L, L, I, I, P],
+    "fmsb_add": [P, P, P, L, I, P],
+    "fmsb_ce": [P, L, P, P, P, P, P, I, I, I, F, I, I, P],
+    "fmsb_ce_bwd": [P, L, P, P, P, L, I, I, I, I, P],
+    "fmsb_count_valid": [P, L, I, P, P],
+    "fmsb_quant4": [P, L, P, I, P, P, I, P],
+    "fmsb_quant8_blockwise": [P, L, F, P, P, P, P],
+    "fmsb_dequant4": [P, P, P, P, P, F, P, I, L, P, I, P],
+    "fmsb_gptq_dequant": [P, P, P, P, I, I, I, I, I, P, I, P],
+}
+
+
+def library_path() -> str:
+    return os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libfmsb200.so")
+
+
+def available() -> bool:
+    return os.path.exists(library_path())
+
+
+def lib():
+    """Load (once) and return the native library."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    with _LOCK:
+        if _LIB is not None:
+            return _LIB
+        path = library_path()
+        if not os.path.exists(path):
+            raise RuntimeError(
+                f"native library {path} is missing: run `python -m fms_acceleration_b200.build` "
+                "(the CUDA kernels of this package have no PyTorch fallback on a GPU)"
+            )
+        handle = ctypes.CDLL(path)
+        for name, argtypes in _SIGNATURES.items():
+            try:
+                fn = getattr(handle, name)
+            except AttributeError:
+                continue
+            fn.argtypes = argtypes
+            fn.restype = c_int
+        _LIB = handle
+    return _LIB
+
+
+def declare(name: str, argtypes) -> None:
+    """Register the signature of an entry point defined outside this table."""
+    _SIGNATURES[name] = argtypes
+    if _LIB is not None and hasattr(_LIB, name):
+        fn = getattr(_LIB, name)
+        fn.argtypes = argtypes
+        fn.restype = c_int
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float16:
+        return 0
+    if dt == torch.bfloat16:
+        return 1
+    if dt == torch.float32:
+        return 2
+    raise TypeError(f"unsupported dtype {dt}")
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise NativeError(f"{what} failed with code {rc}")
+
+
+_STATUS_NAMES = {
+    1: "TMA producer timed out waiting for a free stage",
+    2: "MMA issuer timed out",
+    3: "epilogue timed out waiting for an accumulator",
+    4: "wait on a peer flag timed out",
+    5: "bad argument detected on device",
+    6: "dequant warps timed out",
+    7: "receive-buffer capacity overflow",
+}
+
+_status_words: dict[int, torch.Tensor] = {}
+
+
+def status_word(device=None) -> torch.Tensor:
+    """Per-device int32 status word shared by all kernels with bounded waits."""
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    if dev is None:
+        dev = torch.cuda.current_device()
+    w = _status_words.get(dev)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32, device=f"cuda:{dev}")
+        _status_words[dev] = w
+    return w
+
+
+def check_status(device=None) -> None:
+    """Synchronising check of the status word; raises if any kernel reported a time-out."""
+    w = status_word(device)
+    v = int(w.item())
+    if v != 0:
+        w.zero_()
+        raise NativeError(f"device status {v}: {_STATUS_NAMES.get(v, 'unknown')}")

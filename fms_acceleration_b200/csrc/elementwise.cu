@@ -1,0 +1,503 @@
+// Bandwidth-bound fused ops for sm_100a: RMSNorm (+residual add) forward/backward, rotary
+// embedding with explicit position ids, SwiGLU / GEGLU forward/backward.
+//
+// Reference semantics (file paths inside the reference project):
+//   RMSNorm   fms_acceleration_foak/kernels/unsloth/rms_layernorm.py:21-128  (fp32 accumulate,
+//             inv_rms saved; gemma variant uses W+1; the reference has no dW, here it is optional)
+//   RoPE      fms_acceleration_foak/kernels/unsloth/rope_embedding.py:20-72   (rotate halves; the
+//             reference derives the position from row % seqlen, which is wrong for packed
+//             batches; this kernel takes position ids)
+//   SwiGLU    fms_acceleration_foak/fused_ops/unsloth_lora/swiglu.py:20-98
+//   GEGLU     fms_acceleration_foak/fused_ops/unsloth_lora/geglu.py:20-202
+//
+// All kernels use 16-byte vector accesses; rows must be multiples of 8 elements and 16-byte
+// aligned.  dtype code: 0 = fp16, 1 = bf16.
+#include "common.cuh"
+
+namespace fmsb {
+
+template <typename T>
+struct Vec8 {
+  uint4 u;
+  __device__ __forceinline__ void load(const T* p) { u = *reinterpret_cast<const uint4*>(p); }
+  __device__ __forceinline__ void store(T* p) const { *reinterpret_cast<uint4*>(p) = u; }
+  __device__ __forceinline__ void to_float(float (&f)[8]) const;
+  __device__ __forceinline__ void from_float(const float (&f)[8]);
+};
+template <>
+__device__ __forceinline__ void Vec8<__nv_bfloat16>::to_float(float (&f)[8]) const {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 v = __bfloat1622float2(h[i]);
+    f[2 * i] = v.x;
+    f[2 * i + 1] = v.y;
+  }
+}
+template <>
+__device__ __forceinline__ void Vec8<__half>::to_float(float (&f)[8]) const {
+  const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 v = __half22float2(h[i]);
+    f[2 * i] = v.x;
+    f[2 * i + 1] = v.y;
+  }
+}
+template <>
+__device__ __forceinline__ void Vec8<__nv_bfloat16>::from_float(const float (&f)[8]) {
+  u.x = pack_bf16x2(f[0], f[1]);
+  u.y = pack_bf16x2(f[2], f[3]);
+  u.z = pack_bf16x2(f[4], f[5]);
+  u.w = pack_bf16x2(f[6], f[7]);
+}
+template <>
+__device__ __forceinline__ void Vec8<__half>::from_float(const float (&f)[8]) {
+  u.x = pack_f16x2(f[0], f[1]);
+  u.y = pack_f16x2(f[2], f[3]);
+  u.z = pack_f16x2(f[4], f[5]);
+  u.w = pack_f16x2(f[6], f[7]);
+}
+
+template <typename T>
+__device__ __forceinline__ float round_to(float v);
+template <>
+__device__ __forceinline__ float round_to<__nv_bfloat16>(float v) {
+  return __bfloat162float(__float2bfloat16_rn(v));
+}
+template <>
+__device__ __forceinline__ float round_to<__half>(float v) {
+  return __half2float(__float2half_rn(v));
+}
+
+constexpr int NORM_THREADS = 256;
+constexpr int NORM_MAXV = 4;  // vectors of 8 cached per thread -> fast path up to H = 8192
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int i = 0; i < NORM_THREADS / 32; ++i) t += red[i];
+  return t;
+}
+
+// y = rms_norm(x [+ residual]) * (w [+1]);  optional h_out = x + residual (the new residual stream)
+template <typename T>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ residual, const T* __restrict__ w,
+                   T* __restrict__ y, T* __restrict__ h_out, float* __restrict__ inv_rms, int rows, int H,
+                   float eps, int gemma) {
+  __shared__ float red[NORM_THREADS / 32];
+  const int nvec = H / 8;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* xr = x + (long long)row * H;
+    float cache[NORM_MAXV][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < NORM_MAXV; ++j) {
+      const int v = threadIdx.x + j * NORM_THREADS;
+      if (v < nvec) {
+        Vec8<T> a;
+        a.load(xr + v * 8);
+        a.to_float(cache[j]);
+        if (residual != nullptr) {
+          Vec8<T> b;
+          float rb[8];
+          b.load(residual + (long long)row * H + v * 8);
+          b.to_float(rb);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) cache[j][i] = round_to<T>(cache[j][i] + rb[i]);
+          if (h_out != nullptr) {
+            Vec8<T> o;
+            o.from_float(cache[j]);
+            o.store(h_out + (long long)row * H + v * 8);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += cache[j][i] * cache[j][i];
+      }
+    }
+    const float tot = block_sum(ss, red);
+    const float inv = rsqrtf(tot / (float)H + eps);
+    if (threadIdx.x == 0 && inv_rms != nullptr) inv_rms[row] = inv;
+#pragma unroll
+    for (int j = 0; j < NORM_MAXV; ++j) {
+      const int v = threadIdx.x + j * NORM_THREADS;
+      if (v < nvec) {
+        Vec8<T> wv;
+        float wf[8], out[8];
+        wv.load(w + v * 8);
+        wv.to_float(wf);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          if (gemma) {
+            out[i] = cache[j][i] * inv * (wf[i] + 1.f);
+          } else {
+            out[i] = round_to<T>(cache[j][i] * inv) * wf[i];
+          }
+        }
+        Vec8<T> o;
+        o.from_float(out);
+        o.store(y + (long long)row * H + v * 8);
+      }
+    }
+  }
+}
+
+// dx = inv/H * (H * dy*w - xhat * sum(dy*w*xhat)) [+ dres_in];   dw_partial[block] += dy * xhat
+template <typename T>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
+                   const float* __restrict__ inv_rms, const T* __restrict__ dres_in, T* __restrict__ dx,
+                   float* __restrict__ dw_partial, int rows, int H, int gemma) {
+  __shared__ float red[NORM_THREADS / 32];
+  const int nvec = H / 8;
+  float dwacc[NORM_MAXV][8];
+#pragma unroll
+  for (int j = 0; j < NORM_MAXV; ++j)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dwacc[j][i] = 0.f;
+  float wf[NORM_MAXV][8];
+#pragma unroll
+  for (int j = 0; j < NORM_MAXV; ++j) {
+    const int v = threadIdx.x + j * NORM_THREADS;
+    if (v < nvec) {
+      Vec8<T> wv;
+      wv.load(w + v * 8);
+      wv.to_float(wf[j]);
+      if (gemma) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) wf[j][i] += 1.f;
+      }
+    }
+  }
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float inv = inv_rms[row];
+    float xh[NORM_MAXV][8], g[NORM_MAXV][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < NORM_MAXV; ++j) {
+      const int v = threadIdx.x + j * NORM_THREADS;
+      if (v < nvec) {
+        Vec8<T> a, b;
+        float dyf[8];
+        a.load(x + (long long)row * H + v * 8);
+        a.to_float(xh[j]);
+        b.load(dy + (long long)row * H + v * 8);
+        b.to_float(dyf);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          xh[j][i] *= inv;
+          g[j][i] = dyf[i] * wf[j][i];
+          dot += g[j][i] * xh[j][i];
+          dwacc[j][i] += dyf[i] * xh[j][i];
+        }
+      }
+    }
+    const float tot = block_sum(dot, red);
+    const float c = tot / (float)H;
+#pragma unroll
+    for (int j = 0; j < NORM_MAXV; ++j) {
+      const int v = threadIdx.x + j * NORM_THREADS;
+      if (v < nvec) {
+        float out[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) out[i] = inv * (g[j][i] - xh[j][i] * c);
+        if (dres_in != nullptr) {
+          Vec8<T> r;
+          float rf[8];
+          r.load(dres_in + (long long)row * H + v * 8);
+          r.to_float(rf);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) out[i] += rf[i];
+        }
+        Vec8<T> o;
+        o.from_float(out);
+        o.store(dx + (long long)row * H + v * 8);
+      }
+    }
+  }
+  if (dw_partial != nullptr) {
+#pragma unroll
+    for (int j = 0; j < NORM_MAXV; ++j) {
+      const int v = threadIdx.x + j * NORM_THREADS;
+      if (v < nvec) {
+        float* dst = dw_partial + (long long)blockIdx.x * H + v * 8;
+        *reinterpret_cast<float4*>(dst) = make_float4(dwacc[j][0], dwacc[j][1], dwacc[j][2], dwacc[j][3]);
+        *reinterpret_cast<float4*>(dst + 4) = make_float4(dwacc[j][4], dwacc[j][5], dwacc[j][6], dwacc[j][7]);
+      }
+    }
+  }
+}
+
+// out[c] = sum_b partial[b, c]
+__global__ void colsum_kernel(const float* __restrict__ partial, float* __restrict__ out, int nblocks, int H) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= H) return;
+  float s = 0.f;
+  for (int b = 0; b < nblocks; ++b) s += partial[(long long)b * H + c];
+  out[c] = s;
+}
+
+// Rotary embedding on a packed [T, row_stride] buffer holding n_heads heads of size d starting
+// at column 0 (e.g. the q|k part of a fused qkv projection).  cos/sin: [max_pos, d/2] fp32.
+// sign = +1 forward, -1 backward.  In place.
+template <typename T>
+__global__ void rope_kernel(T* __restrict__ qk, const int* __restrict__ pos, const float* __restrict__ cos_t,
+                            const float* __restrict__ sin_t, int T_tokens, int n_heads, int d,
+                            long long row_stride, float sign) {
+  const int half = d / 2;
+  const int vec_per_head = half / 8;
+  const long long total = (long long)T_tokens * n_heads * vec_per_head;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int v = (int)(idx % vec_per_head);
+    const long long th = idx / vec_per_head;
+    const int h = (int)(th % n_heads);
+    const long long t = th / n_heads;
+    const int p = pos[t];
+    T* base = qk + t * row_stride + (long long)h * d + v * 8;
+    Vec8<T> a, b;
+    float x1[8], x2[8], o1[8], o2[8];
+    a.load(base);
+    b.load(base + half);
+    a.to_float(x1);
+    b.to_float(x2);
+    const float4* cp = reinterpret_cast<const float4*>(cos_t + (long long)p * half + v * 8);
+    const float4* sp = reinterpret_cast<const float4*>(sin_t + (long long)p * half + v * 8);
+    float c[8], s[8];
+    *reinterpret_cast<float4*>(c) = cp[0];
+    *reinterpret_cast<float4*>(c + 4) = cp[1];
+    *reinterpret_cast<float4*>(s) = sp[0];
+    *reinterpret_cast<float4*>(s + 4) = sp[1];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float sn = s[i] * sign;
+      o1[i] = x1[i] * c[i] - x2[i] * sn;
+      o2[i] = x2[i] * c[i] + x1[i] * sn;
+    }
+    a.from_float(o1);
+    b.from_float(o2);
+    a.store(base);
+    b.store(base + half);
+  }
+}
+
+// activation codes: 0 = SwiGLU (silu), 1 = GEGLU exact (erf), 2 = GEGLU tanh approximation
+__device__ __forceinline__ float act_fwd(float e, int act) {
+  if (act == 0) return e / (1.f + __expf(-e));
+  if (act == 1) return 0.5f * e * (1.f + erff(e * 0.70710678118654752f));
+  const float k = 0.7978845608028654f;
+  return 0.5f * e * (1.f + tanhf(k * e * (1.f + 0.044715f * e * e)));
+}
+__device__ __forceinline__ float act_grad(float e, int act) {
+  if (act == 0) {
+    const float s = 1.f / (1.f + __expf(-e));
+    return s * (1.f + e * (1.f - s));
+  }
+  if (act == 1) {
+    return 0.5f * (1.f + erff(e * 0.70710678118654752f)) + e * 0.3989422804014327f * __expf(-0.5f * e * e);
+  }
+  const float k = 0.7978845608028654f;
+  const float u = k * e * (1.f + 0.044715f * e * e);
+  const float th = tanhf(u);
+  return 0.5f * (1.f + th) + 0.5f * e * (1.f - th * th) * k * (1.f + 3.f * 0.044715f * e * e);
+}
+
+// h[t, i] = act(e[t, i]) * g[t, i]    e, g, h: row strides in elements
+template <typename T>
+__global__ void glu_fwd_kernel(const T* __restrict__ e, const T* __restrict__ g, T* __restrict__ h, int rows,
+                               int I, long long se, long long sg, long long sh, int act) {
+  const int vec_per_row = I / 8;
+  const long long total = (long long)rows * vec_per_row;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long r = idx / vec_per_row;
+    const int c = (int)(idx % vec_per_row) * 8;
+    Vec8<T> a, b;
+    float ef[8], gf[8], out[8];
+    a.load(e + r * se + c);
+    b.load(g + r * sg + c);
+    a.to_float(ef);
+    b.to_float(gf);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out[i] = round_to<T>(act_fwd(ef[i], act)) * gf[i];
+    Vec8<T> o;
+    o.from_float(out);
+    o.store(h + r * sh + c);
+  }
+}
+
+// Given dh, e, g:  de = dh * g * act'(e),  dg = dh * act(e); optionally also h = act(e) * g.
+// de/dg may alias e/g (the in-place scheme of the reference).
+template <typename T>
+__global__ void glu_bwd_kernel(const T* __restrict__ dh, const T* e, const T* g, T* de, T* dg,
+                               T* __restrict__ h_out, int rows, int I, long long sdh, long long se, long long sg,
+                               long long sde, long long sdg, long long sh, int act) {
+  const int vec_per_row = I / 8;
+  const long long total = (long long)rows * vec_per_row;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long r = idx / vec_per_row;
+    const int c = (int)(idx % vec_per_row) * 8;
+    Vec8<T> a, b, d;
+    float ef[8], gf[8], df[8], o1[8], o2[8], o3[8];
+    a.load(e + r * se + c);
+    b.load(g + r * sg + c);
+    d.load(dh + r * sdh + c);
+    a.to_float(ef);
+    b.to_float(gf);
+    d.to_float(df);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float f = act_fwd(ef[i], act);
+      o1[i] = df[i] * gf[i] * act_grad(ef[i], act);
+      o2[i] = df[i] * f;
+      o3[i] = f * gf[i];
+    }
+    Vec8<T> w1, w2;
+    w1.from_float(o1);
+    w2.from_float(o2);
+    w1.store(de + r * sde + c);
+    w2.store(dg + r * sdg + c);
+    if (h_out != nullptr) {
+      Vec8<T> w3;
+      w3.from_float(o3);
+      w3.store(h_out + r * sh + c);
+    }
+  }
+}
+
+// y = a + b (residual add), 16-bit
+template <typename T>
+__global__ void add_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ y, long long n8) {
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < n8;
+       idx += (long long)gridDim.x * blockDim.x) {
+    Vec8<T> va, vb;
+    float fa[8], fb[8];
+    va.load(a + idx * 8);
+    vb.load(b + idx * 8);
+    va.to_float(fa);
+    vb.to_float(fb);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) fa[i] += fb[i];
+    va.from_float(fa);
+    va.store(y + idx * 8);
+  }
+}
+
+static inline int grid_for(long long work_items, int threads, int cap_blocks) {
+  long long b = (work_items + threads - 1) / threads;
+  if (b > cap_blocks) b = cap_blocks;
+  if (b < 1) b = 1;
+  return (int)b;
+}
+
+}  // namespace fmsb
+
+using namespace fmsb;
+
+extern "C" int fmsb_rmsnorm_fwd(const void* x, const void* residual, const void* w, void* y, void* h_out,
+                                float* inv_rms, int rows, int H, float eps, int gemma, int dtype,
+                                cudaStream_t stream) {
+  if (H % 8 != 0 || H > 8 * NORM_THREADS * NORM_MAXV) return -2;
+  if (rows <= 0) return 0;
+  const int grid = rows < 148 * 8 ? rows : 148 * 8;
+  if (dtype == 1)
+    rmsnorm_fwd_kernel<__nv_bfloat16><<<grid, NORM_THREADS, 0, stream>>>(
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)w, (__nv_bfloat16*)y,
+        (__nv_bfloat16*)h_out, inv_rms, rows, H, eps, gemma);
+  else
+    rmsnorm_fwd_kernel<__half><<<grid, NORM_THREADS, 0, stream>>>((const __half*)x, (const __half*)residual,
+                                                                  (const __half*)w, (__half*)y, (__half*)h_out,
+                                                                  inv_rms, rows, H, eps, gemma);
+  return (int)cudaGetLastError();
+}
+
+// dw_partial: [n_partial_blocks, H] fp32 scratch (may be null: no weight gradient);
+// the launch uses exactly n_partial_blocks CTAs when dw_partial is given.
+extern "C" int fmsb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* inv_rms,
+                                const void* dres_in, void* dx, float* dw_partial, float* dw, int n_partial_blocks,
+                                int rows, int H, int gemma, int dtype, cudaStream_t stream) {
+  if (H % 8 != 0 || H > 8 * NORM_THREADS * NORM_MAXV) return -2;
+  if (rows <= 0) return 0;
+  int grid = rows < 148 * 4 ? rows : 148 * 4;
+  if (dw_partial != nullptr) {
+    if (n_partial_blocks <= 0) return -2;
+    grid = n_partial_blocks;
+  }
+  if (dtype == 1)
+    rmsnorm_bwd_kernel<__nv_bfloat16><<<grid, NORM_THREADS, 0, stream>>>(
+        (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, inv_rms,
+        (const __nv_bfloat16*)dres_in, (__nv_bfloat16*)dx, dw_partial, rows, H, gemma);
+  else
+    rmsnorm_bwd_kernel<__half><<<grid, NORM_THREADS, 0, stream>>>((const __half*)dy, (const __half*)x,
+                                                                  (const __half*)w, inv_rms, (const __half*)dres_in,
+                                                                  (__half*)dx, dw_partial, rows, H, gemma);
+  if (dw_partial != nullptr && dw != nullptr) {
+    colsum_kernel<<<(H + 255) / 256, 256, 0, stream>>>(dw_partial, dw, grid, H);
+  }
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fmsb_rope(void* qk, const int* pos, const float* cos_t, const float* sin_t, int T_tokens,
+                         int n_heads, int d, long long row_stride, float sign, int dtype, cudaStream_t stream) {
+  if (d % 16 != 0 || row_stride % 8 != 0) return -2;
+  if (T_tokens <= 0 || n_heads <= 0) return 0;
+  const long long total = (long long)T_tokens * n_heads * (d / 16);
+  const int grid = grid_for(total, 256, 148 * 16);
+  if (dtype == 1)
+    rope_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((__nv_bfloat16*)qk, pos, cos_t, sin_t, T_tokens, n_heads, d,
+                                                         row_stride, sign);
+  else
+    rope_kernel<__half><<<grid, 256, 0, stream>>>((__half*)qk, pos, cos_t, sin_t, T_tokens, n_heads, d, row_stride,
+                                                  sign);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fmsb_glu_fwd(const void* e, const void* g, void* h, int rows, int I, long long se, long long sg,
+                            long long sh, int act, int dtype, cudaStream_t stream) {
+  if (I % 8 != 0 || se % 8 || sg % 8 || sh % 8) return -2;
+  if (rows <= 0) return 0;
+  const int grid = grid_for((long long)rows * (I / 8), 256, 148 * 16);
+  if (dtype == 1)
+    glu_fwd_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)e, (const __nv_bfloat16*)g,
+                                                            (__nv_bfloat16*)h, rows, I, se, sg, sh, act);
+  else
+    glu_fwd_kernel<__half><<<grid, 256, 0, stream>>>((const __half*)e, (const __half*)g, (__half*)h, rows, I, se, sg,
+                                                     sh, act);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fmsb_glu_bwd(const void* dh, const void* e, const void* g, void* de, void* dg, void* h_out, int rows,
+                            int I, long long sdh, long long se, long long sg, long long sde, long long sdg,
+                            long long sh, int act, int dtype, cudaStream_t stream) {
+  if (I % 8 != 0 || sdh % 8 || se % 8 || sg % 8 || sde % 8 || sdg % 8 || sh % 8) return -2;
+  if (rows <= 0) return 0;
+  const int grid = grid_for((long long)rows * (I / 8), 256, 148 * 16);
+  if (dtype == 1)
+    glu_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
+        (const __nv_bfloat16*)dh, (const __nv_bfloat16*)e, (const __nv_bfloat16*)g, (__nv_bfloat16*)de,
+        (__nv_bfloat16*)dg, (__nv_bfloat16*)h_out, rows, I, sdh, se, sg, sde, sdg, sh, act);
+  else
+    glu_bwd_kernel<__half><<<grid, 256, 0, stream>>>((const __half*)dh, (const __half*)e, (const __half*)g,
+                                                     (__half*)de, (__half*)dg, (__half*)h_out, rows, I, sdh, se, sg,
+                                                     sde, sdg, sh, act);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fmsb_add(const void* a, const void* b, void* y, long long n, int dtype, cudaStream_t stream) {
+  if (n % 8 != 0) return -2;
+  if (n <= 0) return 0;
+  const int grid = grid_for(n / 8, 256, 148 * 16);
+  if (dtype == 1)
+    add_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b,
+                                                        (__nv_bfloat16*)y, n / 8);
+  else
+    add_kernel<__half><<<grid, 256, 0, stream>>>((const __half*)a, (const __half*)b, (__half*)y, n / 8);
+  return (int)cudaGetLastError();
+}

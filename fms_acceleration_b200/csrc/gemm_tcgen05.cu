@@ -1,0 +1,458 @@
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a.
+//
+//   D[M,N] = alpha * (A1 . B1^T  +  A2 . B2^T) + beta * C
+//
+// Two operand pairs are accumulated into the SAME tensor-memory accumulator, i.e. the
+// contraction runs over the concatenation [A1 | A2] x [B1 | B2].  Pair 2 is how a LoRA update
+// is fused into the base projection (A2 = s * X.A^T of shape [M, r], B2 = lora_B of shape
+// [N, r]) without a second pass over D; it is optional (K2 = 0).
+//
+// Operand layouts ("K-major": the contraction index is contiguous in memory,
+// "MN-major": the M (or N) index is contiguous):
+//   a_mn = 0 : A stored [M, K] row-major          a_mn = 1 : A stored [K, M] row-major
+//   b_mn = 0 : B stored [N, K] row-major          b_mn = 1 : B stored [K, N] row-major
+// so y = x W^T, dx = dy W and dW = dy^T x are all served without a transposed copy.
+//
+// Structure of one CTA (192 threads, one CTA per SM, persistent over output tiles):
+//   warp 0      : TMA producer  (cp.async.bulk.tensor, 128-byte swizzle, no multicast)
+//   warp 1      : MMA issuer    (one lane issues tcgen05.mma, 128 x BN x 16 per instruction)
+//   warps 2..5  : epilogue      (tcgen05.ld of the fp32 accumulator, scale/add, 16-byte stores)
+// The accumulator is double buffered in tensor memory (2 x BN columns) so the epilogue of
+// tile i overlaps the main loop of tile i+1.  All mbarrier waits are bounded (common.cuh).
+//
+// The role of this kernel in the reference design: it replaces the cuBLAS calls behind
+// torch.matmul in fms_acceleration_foak/fused_ops/unsloth_lora/utils.py:250-283 (matmul_lora)
+// and the "dequant then matmul" of fms_acceleration_peft/gptqmodel/nn_modules/triton_utils/dequant.py:132-161.
+#include "common.cuh"
+#include <mutex>
+
+namespace fmsb {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int GROUP_M = 16;
+
+struct GemmParams {
+  int M, N;
+  int kblocks1, kblocks2;
+  void* D;
+  long long ldd;
+  int d_fp32;
+  const void* C;
+  long long ldc;
+  float alpha, beta;
+  int fmt;  // 0 = fp16, 1 = bf16
+  int* status;
+};
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStagesRaw = (200 * 1024) / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kTmemCols = (2 * BN) < 32 ? 32 : (2 * BN);
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int group_size = GROUP_M * tiles_n;
+  const int group = t / group_size;
+  const int first_m = group * GROUP_M;
+  const int gm = min(tiles_m - first_m, GROUP_M);
+  const int in_group = t - group * group_size;
+  tm = first_m + in_group % gm;
+  tn = in_group / gm;
+}
+
+template <int BN, int A_MN, int B_MN>
+__global__ void __launch_bounds__(192, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
+                    const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
+                    const GemmParams p) {
+  using Cfg = GemmCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte swizzled tiles need 1024-byte alignment
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + Cfg::kStages * Cfg::kStageBytes;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::kStages + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * Cfg::kStages + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * Cfg::kStages + 2 + a); };
+  const uint32_t holder = bar_base + 8u * (2 * Cfg::kStages + 4);
+  auto sA = [&](int s) { return smem_base + s * Cfg::kStageBytes; };
+  auto sB = [&](int s) { return smem_base + s * Cfg::kStageBytes + Cfg::kABytes; };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (warp == 1 && lane == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 128);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    if (lane == 0) {
+      prefetch_tmap(&tmA1);
+      prefetch_tmap(&tmB1);
+      if (p.kblocks2 > 0) {
+        prefetch_tmap(&tmA2);
+        prefetch_tmap(&tmB2);
+      }
+    }
+    __syncwarp();
+    tmem_alloc(holder, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(holder));
+
+  const int tiles_m = (p.M + BM - 1) / BM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int kblocks = p.kblocks1 + p.kblocks2;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int tm, tn;
+        tile_coords(t, tiles_m, tiles_n, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, p.status, kTimeoutProducer)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(full_bar(stage), Cfg::kStageBytes);
+          const bool second = kb >= p.kblocks1;
+          const CUtensorMap* ta = second ? &tmA2 : &tmA1;
+          const CUtensorMap* tb = second ? &tmB2 : &tmB1;
+          const int k0 = (second ? kb - p.kblocks1 : kb) * BK;
+          if (A_MN == 0) {
+            tma_load_2d(sA(stage), ta, full_bar(stage), k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_2d(sA(stage) + j * 8192, ta, full_bar(stage), m0 + 64 * j, k0);
+          }
+          if (B_MN == 0) {
+            tma_load_2d(sB(stage), tb, full_bar(stage), k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(sB(stage) + j * 8192, tb, full_bar(stage), n0 + 64 * j, k0);
+          }
+          if (++stage == Cfg::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_f16(BM, BN, p.fmt, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, p.status, kTimeoutMma)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, p.status, kTimeoutMma)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t adesc = A_MN ? make_smem_desc(sA(stage) + k * 2048, 8192, 1024)
+                                        : make_smem_desc(sA(stage) + k * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? make_smem_desc(sB(stage) + k * 2048, 8192, 1024)
+                                        : make_smem_desc(sB(stage) + k * 32, 16, 1024);
+            tc_mma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(empty_bar(stage));
+          if (++stage == Cfg::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        tc_commit(tfull_bar(acc));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (4 warps)
+    const int q = warp & 3;  // tensor-memory lane quarter this warp may read
+    const int row = q * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    constexpr int CH = BN >= 32 ? 32 : 16;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      int tm, tn;
+      tile_coords(t, tiles_m, tiles_n, tm, tn);
+      const int gm = tm * BM + row;
+      const int n0 = tn * BN;
+      if (!mbar_wait(tfull_bar(acc), acc_phase, p.status, kTimeoutEpilogue)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN / CH; ++c) {
+        float v[CH];
+        if constexpr (CH == 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * CH, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+        } else {
+          uint32_t r[16];
+          tmem_ld_32x16(taddr + c * CH, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+        }
+        const int gn = n0 + c * CH;
+        if (gm < p.M && gn < p.N) {
+          const bool full = (gn + CH <= p.N);
+#pragma unroll
+          for (int i = 0; i < CH; ++i) v[i] *= p.alpha;
+          if (p.C != nullptr && p.beta != 0.f) {
+            if (p.fmt == 1) {
+              const __nv_bfloat16* crow = reinterpret_cast<const __nv_bfloat16*>(p.C) + (long long)gm * p.ldc + gn;
+              if (full && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
+#pragma unroll
+                for (int i = 0; i < CH; i += 8) {
+                  uint4 u = *reinterpret_cast<const uint4*>(crow + i);
+                  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    float2 f = __bfloat1622float2(h[j]);
+                    v[i + 2 * j] += p.beta * f.x;
+                    v[i + 2 * j + 1] += p.beta * f.y;
+                  }
+                }
+              } else {
+                for (int i = 0; i < CH; ++i)
+                  if (gn + i < p.N) v[i] += p.beta * __bfloat162float(crow[i]);
+              }
+            } else {
+              const __half* crow = reinterpret_cast<const __half*>(p.C) + (long long)gm * p.ldc + gn;
+              for (int i = 0; i < CH; ++i)
+                if (gn + i < p.N) v[i] += p.beta * __half2float(crow[i]);
+            }
+          }
+          if (p.d_fp32) {
+            float* drow = reinterpret_cast<float*>(p.D) + (long long)gm * p.ldd + gn;
+            if (full && ((reinterpret_cast<uintptr_t>(drow) & 15) == 0)) {
+#pragma unroll
+              for (int i = 0; i < CH; i += 4)
+                *reinterpret_cast<float4*>(drow + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+            } else {
+              for (int i = 0; i < CH; ++i)
+                if (gn + i < p.N) drow[i] = v[i];
+            }
+          } else {
+            uint16_t* drow = reinterpret_cast<uint16_t*>(p.D) + (long long)gm * p.ldd + gn;
+            if (full && ((reinterpret_cast<uintptr_t>(drow) & 15) == 0)) {
+#pragma unroll
+              for (int i = 0; i < CH; i += 8) {
+                uint4 u;
+                if (p.fmt == 1) {
+                  u.x = pack_bf16x2(v[i], v[i + 1]);
+                  u.y = pack_bf16x2(v[i + 2], v[i + 3]);
+                  u.z = pack_bf16x2(v[i + 4], v[i + 5]);
+                  u.w = pack_bf16x2(v[i + 6], v[i + 7]);
+                } else {
+                  u.x = pack_f16x2(v[i], v[i + 1]);
+                  u.y = pack_f16x2(v[i + 2], v[i + 3]);
+                  u.z = pack_f16x2(v[i + 4], v[i + 5]);
+                  u.w = pack_f16x2(v[i + 6], v[i + 7]);
+                }
+                *reinterpret_cast<uint4*>(drow + i) = u;
+              }
+            } else {
+              for (int i = 0; i < CH; ++i) {
+                if (gn + i < p.N) {
+                  if (p.fmt == 1) {
+                    __nv_bfloat16 b = __float2bfloat16_rn(v[i]);
+                    drow[i] = *reinterpret_cast<uint16_t*>(&b);
+                  } else {
+                    __half b = __float2half_rn(v[i]);
+                    drow[i] = *reinterpret_cast<uint16_t*>(&b);
+                  }
+                }
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(tempty_bar(acc));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+}  // namespace fmsb
+
+// ========================================================================================
+// host side
+// ========================================================================================
+namespace fmsb_host {
+
+EncodeTiledFn get_encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, []() {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+  });
+  return fn;
+}
+
+int make_tmap_2d_16b(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride_elems,
+                     uint32_t box_rows, uint32_t box_cols) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (enc == nullptr) return -1;
+  cuuint64_t gdim[2] = {cols, rows};
+  cuuint64_t gstr[1] = {row_stride_elems * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstr, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r) - 100;
+}
+
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+template <int BN, int A_MN, int B_MN>
+int launch_gemm(const CUtensorMap& a1, const CUtensorMap& b1, const CUtensorMap& a2, const CUtensorMap& b2,
+                const fmsb::GemmParams& p, int max_ctas, cudaStream_t stream) {
+  using Cfg = fmsb::GemmCfg<BN>;
+  auto kern = fmsb::gemm_tcgen05_kernel<BN, A_MN, B_MN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  const int tiles = ((p.M + fmsb::BM - 1) / fmsb::BM) * ((p.N + BN - 1) / BN);
+  int ctas = sm_count();
+  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
+  if (tiles < ctas) ctas = tiles;
+  if (ctas <= 0) return 0;
+  kern<<<ctas, 192, Cfg::kSmemBytes, stream>>>(a1, b1, a2, b2, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace fmsb_host
+
+// D[M,N] = alpha * (A1.B1^T + A2.B2^T) + beta * C.   16-bit inputs (fmt 0 = fp16, 1 = bf16).
+// Constraints: K1, K2 multiples of 8; leading dimensions multiples of 8 elements; base pointers
+// 16-byte aligned.  bn selects the N tile (16/32/64/128/256); MN-major B needs bn >= 64.
+// max_ctas > 0 limits the grid (used to leave SMs to a concurrent communication kernel).
+// Returns 0 or a CUDA / encode error code.  Time-outs are reported through *status.
+extern "C" int fmsb_gemm(const void* A1, long long lda1, const void* B1, long long ldb1, int K1,  //
+                         const void* A2, long long lda2, const void* B2, long long ldb2, int K2,  //
+                         int a_mn, int b_mn,                                                       //
+                         void* D, long long ldd, int d_fp32, const void* C, long long ldc,        //
+                         float alpha, float beta, int M, int N, int fmt, int bn, int max_ctas, int* status,
+                         cudaStream_t stream) {
+  using namespace fmsb_host;
+  if (M <= 0 || N <= 0) return 0;
+  if ((K1 % 8) || (K2 % 8) || K1 <= 0) return -2;
+  if (b_mn && bn < 64) return -3;
+  CUtensorMap ta1, tb1, ta2, tb2;
+  int rc;
+  auto mk_a = [&](CUtensorMap* t, const void* A, long long lda, int K) {
+    return a_mn ? make_tmap_2d_16b(t, A, K, M, lda, 64, 64) : make_tmap_2d_16b(t, A, M, K, lda, fmsb::BM, 64);
+  };
+  auto mk_b = [&](CUtensorMap* t, const void* B, long long ldb, int K) {
+    return b_mn ? make_tmap_2d_16b(t, B, K, N, ldb, 64, 64) : make_tmap_2d_16b(t, B, N, K, ldb, bn, 64);
+  };
+  if ((rc = mk_a(&ta1, A1, lda1, K1))) return rc;
+  if ((rc = mk_b(&tb1, B1, ldb1, K1))) return rc;
+  if (K2 > 0) {
+    if ((rc = mk_a(&ta2, A2, lda2, K2))) return rc;
+    if ((rc = mk_b(&tb2, B2, ldb2, K2))) return rc;
+  } else {
+    ta2 = ta1;
+    tb2 = tb1;
+  }
+  fmsb::GemmParams p;
+  p.M = M;
+  p.N = N;
+  p.kblocks1 = (K1 + fmsb::BK - 1) / fmsb::BK;
+  p.kblocks2 = K2 > 0 ? (K2 + fmsb::BK - 1) / fmsb::BK : 0;
+  p.D = D;
+  p.ldd = ldd;
+  p.d_fp32 = d_fp32;
+  p.C = C;
+  p.ldc = ldc;
+  p.alpha = alpha;
+  p.beta = beta;
+  p.fmt = fmt;
+  p.status = status;
+
+#define FMSB_DISPATCH(BNV)                                                                          \
+  if (bn == BNV) {                                                                                  \
+    if (!a_mn && !b_mn) return launch_gemm<BNV, 0, 0>(ta1, tb1, ta2, tb2, p, max_ctas, stream);     \
+    if (a_mn && !b_mn) return launch_gemm<BNV, 1, 0>(ta1, tb1, ta2, tb2, p, max_ctas, stream);      \
+    if constexpr (BNV >= 64) {                                                                      \
+      if (!a_mn && b_mn) return launch_gemm<BNV, 0, 1>(ta1, tb1, ta2, tb2, p, max_ctas, stream);    \
+      if (a_mn && b_mn) return launch_gemm<BNV, 1, 1>(ta1, tb1, ta2, tb2, p, max_ctas, stream);     \
+    }                                                                                               \
+  }
+  FMSB_DISPATCH(256)
+  FMSB_DISPATCH(128)
+  FMSB_DISPATCH(64)
+  FMSB_DISPATCH(32)
+  FMSB_DISPATCH(16)
+#undef FMSB_DISPATCH
+  return -4;
+}

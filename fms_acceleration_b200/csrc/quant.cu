@@ -1,0 +1,254 @@
+// 4-bit blockwise (NF4 / FP4, optional double quantisation of the block scales) and GPTQ
+// 2/4/8-bit weight formats: quantise, dequantise.
+//
+// What these replace in the reference project:
+//   the bitsandbytes C library calls in fms_acceleration_foak/fused_ops/unsloth_lora/utils.py:86-141
+//     (cdequantize_blockwise_fp32 on the 8-bit block scales, `+ offset`, then
+//      cdequantize_blockwise_{fp16,bf16}_nf4 on the packed weights) and the quantise-at-load
+//      done by bitsandbytes for fms_acceleration_peft/framework_plugin_bnb.py:143-158;
+//   the Triton dequant_kernel_248 in
+//     fms_acceleration_foak/fused_ops/unsloth_lora/gptq/triton/kernels.py:53-122 and
+//     fms_acceleration_peft/gptqmodel/nn_modules/triton_utils/dequant.py:36-100.
+//
+// 4-bit blockwise layout: the tensor is flattened; each run of `blocksize` (a multiple of 32)
+// values shares one scale absmax = max|w|; value i is stored as the index of the code-book entry
+// nearest to w/absmax; two indices per byte, the earlier element in the high nibble.  With
+// double quantisation the fp32 scales have their mean (`offset`) removed and are themselves
+// stored as 8-bit indices into a 256-entry code book with one fp32 scale per 256 block scales.
+#include "common.cuh"
+
+namespace fmsb {
+
+// ---------------------------------------------------------------------------- quantise 4-bit
+template <typename T>
+__device__ __forceinline__ float to_f(T v);
+template <>
+__device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <>
+__device__ __forceinline__ float to_f<__half>(__half v) { return __half2float(v); }
+
+// one warp per block of `blocksize` values
+template <typename T>
+__global__ void quant4_kernel(const T* __restrict__ w, long long n, const float* __restrict__ code16, int blocksize,
+                              uint8_t* __restrict__ packed, float* __restrict__ absmax) {
+  __shared__ float code[16];
+  if (threadIdx.x < 16) code[threadIdx.x] = code16[threadIdx.x];
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const long long warp_global = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const long long nblocks = (n + blocksize - 1) / blocksize;
+  for (long long b = warp_global; b < nblocks; b += nwarps) {
+    const long long base = b * blocksize;
+    float mx = 0.f;
+    for (int i = lane; i < blocksize; i += 32) {
+      const long long idx = base + i;
+      if (idx < n) mx = fmaxf(mx, fabsf(to_f<T>(w[idx])));
+    }
+    mx = warp_max(mx);
+    if (lane == 0) absmax[b] = mx;
+    const float inv = mx > 0.f ? 1.f / mx : 0.f;
+    // each lane packs pairs (2 values -> 1 byte)
+    for (int pair = lane; pair < blocksize / 2; pair += 32) {
+      uint32_t byte = 0;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const long long idx = base + 2 * pair + h;
+        const float v = idx < n ? to_f<T>(w[idx]) * inv : 0.f;
+        int best = 0;
+        float bd = fabsf(v - code[0]);
+#pragma unroll
+        for (int c = 1; c < 16; ++c) {
+          const float d = fabsf(v - code[c]);
+          if (d < bd) {
+            bd = d;
+            best = c;
+          }
+        }
+        byte |= (uint32_t)best << (h == 0 ? 4 : 0);
+      }
+      const long long pidx = (base >> 1) + pair;
+      if (2 * pidx < n) packed[pidx] = (uint8_t)byte;
+    }
+  }
+}
+
+// 8-bit blockwise quantisation of (v - offset) against a sorted 256-entry code book; one CTA of
+// 256 threads per block of 256 values.
+__global__ void quant8_kernel(const float* __restrict__ v, long long n, float offset, const float* __restrict__ code256,
+                              uint8_t* __restrict__ q, float* __restrict__ absmax2) {
+  __shared__ float code[256];
+  __shared__ float red[8];
+  code[threadIdx.x] = code256[threadIdx.x];
+  const long long idx = blockIdx.x * 256LL + threadIdx.x;
+  const float x = idx < n ? v[idx] - offset : 0.f;
+  float mx = warp_max(fabsf(x));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  mx = red[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) mx = fmaxf(mx, red[i]);
+  if (threadIdx.x == 0) absmax2[blockIdx.x] = mx;
+  if (idx >= n) return;
+  const float t = mx > 0.f ? x / mx : 0.f;
+  // binary search for the nearest entry of the sorted code book
+  int lo = 0, hi = 255;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (code[mid] <= t) lo = mid; else hi = mid;
+  }
+  q[idx] = (uint8_t)((fabsf(code[hi] - t) < fabsf(t - code[lo])) ? hi : lo);
+}
+
+// ---------------------------------------------------------------------------- dequantise 4-bit
+// Each thread expands 16 packed bytes (32 values, never straddling a block since blocksize % 32 == 0).
+template <typename T>
+__global__ void dequant4_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ absmax,
+                                const uint8_t* __restrict__ absmax_q, const float* __restrict__ code256,
+                                const float* __restrict__ absmax2, float offset, const float* __restrict__ code16,
+                                int blocksize, long long n, T* __restrict__ out) {
+  __shared__ float code[16];
+  if (threadIdx.x < 16) code[threadIdx.x] = code16[threadIdx.x];
+  __syncthreads();
+  const long long nchunks = n / 32;
+  for (long long c = blockIdx.x * (long long)blockDim.x + threadIdx.x; c < nchunks;
+       c += (long long)gridDim.x * blockDim.x) {
+    const long long e0 = c * 32;
+    const long long b = e0 / blocksize;
+    float s;
+    if (absmax_q != nullptr) {
+      s = code256[absmax_q[b]] * absmax2[b >> 8] + offset;
+    } else {
+      s = absmax[b];
+    }
+    const uint4 u = *reinterpret_cast<const uint4*>(packed + (e0 >> 1));
+    const uint32_t words[4] = {u.x, u.y, u.z, u.w};
+    uint4 o[4];
+    uint32_t* ow = reinterpret_cast<uint32_t*>(o);
+#pragma unroll
+    for (int wi = 0; wi < 4; ++wi) {
+#pragma unroll
+      for (int bi = 0; bi < 4; ++bi) {
+        const uint32_t byte = (words[wi] >> (8 * bi)) & 0xff;
+        const float hi = code[byte >> 4] * s;
+        const float lo = code[byte & 15] * s;
+        if (sizeof(T) == 2) {
+          ow[wi * 4 + bi] = std::is_same<T, __nv_bfloat16>::value ? pack_bf16x2(hi, lo) : pack_f16x2(hi, lo);
+        }
+      }
+    }
+    uint4* dst = reinterpret_cast<uint4*>(out + e0);
+    dst[0] = o[0];
+    dst[1] = o[1];
+    dst[2] = o[2];
+    dst[3] = o[3];
+  }
+}
+
+// ---------------------------------------------------------------------------- GPTQ dequantise
+// qweight int32 [in*bits/32, out] packs consecutive input rows along the bit positions;
+// qzeros int32 [groups, out*bits/32] packs along the output columns; scales [groups, out];
+// g_idx int32 [in] (may be null: group = row / group_size).  Output W[in, out]:
+//   W[r, c] = scales[g, c] * (field(qweight[r / per, c], r % per) - (field(qzeros[g, c / per], c % per) + zero_offset))
+template <typename T>
+__global__ void gptq_dequant_kernel(const int* __restrict__ qweight, const T* __restrict__ scales,
+                                    const int* __restrict__ qzeros, const int* __restrict__ g_idx, int in_features,
+                                    int out_features, int bits, int group_size, int zero_offset,
+                                    T* __restrict__ out) {
+  const int per = 32 / bits;
+  const uint32_t mask = (1u << bits) - 1u;
+  const long long total = (long long)in_features * out_features;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(idx / out_features);
+    const int c = (int)(idx % out_features);
+    const int g = g_idx != nullptr ? g_idx[r] : r / group_size;
+    const uint32_t qw = (uint32_t)qweight[(long long)(r / per) * out_features + c];
+    const uint32_t qz = (uint32_t)qzeros[(long long)g * (out_features / per) + c / per];
+    const int wv = (int)((qw >> ((r % per) * bits)) & mask);
+    const int zv = (int)((qz >> ((c % per) * bits)) & mask) + zero_offset;
+    const float s = to_f<T>(scales[(long long)g * out_features + c]);
+    const float v = s * (float)(wv - zv);
+    if (std::is_same<T, __nv_bfloat16>::value)
+      reinterpret_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(v);
+    else
+      reinterpret_cast<__half*>(out)[idx] = __float2half_rn(v);
+  }
+}
+
+}  // namespace fmsb
+
+using namespace fmsb;
+
+extern "C" int fmsb_quant4(const void* w, long long n, const float* code16, int blocksize, void* packed,
+                           float* absmax, int dtype, cudaStream_t stream) {
+  if (blocksize % 32 != 0 || n % 2 != 0) return -2;
+  if (n <= 0) return 0;
+  const long long nblocks = (n + blocksize - 1) / blocksize;
+  long long ctas = (nblocks + 7) / 8;
+  if (ctas > 148 * 32) ctas = 148 * 32;
+  if (dtype == 0)
+    quant4_kernel<__half><<<(int)ctas, 256, 0, stream>>>((const __half*)w, n, code16, blocksize, (uint8_t*)packed,
+                                                         absmax);
+  else if (dtype == 1)
+    quant4_kernel<__nv_bfloat16><<<(int)ctas, 256, 0, stream>>>((const __nv_bfloat16*)w, n, code16, blocksize,
+                                                                (uint8_t*)packed, absmax);
+  else if (dtype == 2)
+    quant4_kernel<float><<<(int)ctas, 256, 0, stream>>>((const float*)w, n, code16, blocksize, (uint8_t*)packed,
+                                                        absmax);
+  else
+    return -2;
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fmsb_quant8_blockwise(const float* v, long long n, float offset, const float* code256, void* q,
+                                     float* absmax2, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  quant8_kernel<<<(int)((n + 255) / 256), 256, 0, stream>>>(v, n, offset, code256, (uint8_t*)q, absmax2);
+  return (int)cudaGetLastError();
+}
+
+// absmax_q == nullptr: plain fp32 block scales in `absmax`; otherwise double-quantised scales.
+extern "C" int fmsb_dequant4(const void* packed, const float* absmax, const void* absmax_q, const float* code256,
+                             const float* absmax2, float offset, const float* code16, int blocksize, long long n,
+                             void* out, int dtype, cudaStream_t stream) {
+  if (blocksize % 32 != 0 || n % 32 != 0) return -2;
+  if (n <= 0) return 0;
+  long long ctas = (n / 32 + 255) / 256;
+  if (ctas > 148 * 16) ctas = 148 * 16;
+  if (dtype == 1)
+    dequant4_kernel<__nv_bfloat16><<<(int)ctas, 256, 0, stream>>>((const uint8_t*)packed, absmax,
+                                                                  (const uint8_t*)absmax_q, code256, absmax2, offset,
+                                                                  code16, blocksize, n, (__nv_bfloat16*)out);
+  else if (dtype == 0)
+    dequant4_kernel<__half><<<(int)ctas, 256, 0, stream>>>((const uint8_t*)packed, absmax, (const uint8_t*)absmax_q,
+                                                           code256, absmax2, offset, code16, blocksize, n,
+                                                           (__half*)out);
+  else
+    return -2;
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fmsb_gptq_dequant(const int* qweight, const void* scales, const int* qzeros, const int* g_idx,
+                                 int in_features, int out_features, int bits, int group_size, int zero_offset,
+                                 void* out, int dtype, cudaStream_t stream) {
+  if (!(bits == 2 || bits == 4 || bits == 8)) return -2;
+  if (out_features % (32 / bits) != 0 || in_features % (32 / bits) != 0) return -2;
+  const long long total = (long long)in_features * out_features;
+  if (total <= 0) return 0;
+  long long ctas = (total + 255) / 256;
+  if (ctas > 148 * 32) ctas = 148 * 32;
+  if (dtype == 1)
+    gptq_dequant_kernel<__nv_bfloat16><<<(int)ctas, 256, 0, stream>>>(qweight, (const __nv_bfloat16*)scales, qzeros,
+                                                                      g_idx, in_features, out_features, bits,
+                                                                      group_size, zero_offset, (__nv_bfloat16*)out);
+  else if (dtype == 0)
+    gptq_dequant_kernel<__half><<<(int)ctas, 256, 0, stream>>>(qweight, (const __half*)scales, qzeros, g_idx,
+                                                               in_features, out_features, bits, group_size,
+                                                               zero_offset, (__half*)out);
+  else
+    return -2;
+  return (int)cudaGetLastError();
+}

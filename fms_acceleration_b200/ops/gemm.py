@@ -1,0 +1,107 @@
+"""Python front-end of the tcgen05 GEMM (``csrc/gemm_tcgen05.cu``).
+
+``gemm(a, b)`` computes ``alpha * (op(a) @ op(b)^T + op(a2) @ op(b2)^T) + beta * c`` with fp32
+accumulation in tensor memory.  Operand orientation is described by two flags instead of
+transposed copies:
+
+* ``a_mn=False``: ``a`` is ``[M, K]`` (contraction contiguous); ``a_mn=True``: ``a`` is ``[K, M]``.
+* ``b_mn=False``: ``b`` is ``[N, K]`` (an ``nn.Linear`` weight); ``b_mn=True``: ``b`` is ``[K, N]``.
+
+So ``y = x W^T`` is ``gemm(x, W)``, ``dx = dy W`` is ``gemm(dy, W, b_mn=True)`` and
+``dW = dy^T x`` is ``gemm(dy, x, a_mn=True, b_mn=True)``.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import _native as N
+
+
+def _pick_bn(n: int, b_mn: bool) -> int:
+    if n >= 192:
+        bn = 256
+    elif n > 64:
+        bn = 128
+    elif n > 32:
+        bn = 64
+    elif n > 16:
+        bn = 32
+    else:
+        bn = 16
+    if b_mn and bn < 64:
+        bn = 64
+    return bn
+
+
+def _check_operand(t: torch.Tensor, name: str) -> None:
+    if t.dim() != 2:
+        raise ValueError(f"{name} must be 2-D")
+    if t.stride(1) != 1:
+        raise ValueError(f"{name} must have unit stride in its last dimension")
+    if t.stride(0) % 8 != 0 or t.data_ptr() % 16 != 0:
+        raise ValueError(f"{name}: leading dimension must be a multiple of 8 elements and 16-byte aligned")
+
+
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    *,
+    a_mn: bool = False,
+    b_mn: bool = False,
+    a2: torch.Tensor | None = None,
+    b2: torch.Tensor | None = None,
+    c: torch.Tensor | None = None,
+    alpha: float = 1.0,
+    beta: float = 0.0,
+    out: torch.Tensor | None = None,
+    out_dtype: torch.dtype | None = None,
+    bn: int | None = None,
+    max_ctas: int = 0,
+) -> torch.Tensor:
+    if a.dtype not in (torch.bfloat16, torch.float16) or b.dtype != a.dtype:
+        raise TypeError("gemm operands must both be bf16 or both fp16")
+    _check_operand(a, "a")
+    _check_operand(b, "b")
+    M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
+    Nn, Kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
+    if K != Kb:
+        raise ValueError(f"contraction mismatch: {K} vs {Kb}")
+    K2 = 0
+    if a2 is not None:
+        _check_operand(a2, "a2")
+        _check_operand(b2, "b2")
+        M2, K2 = (a2.shape[1], a2.shape[0]) if a_mn else (a2.shape[0], a2.shape[1])
+        N2, K2b = (b2.shape[1], b2.shape[0]) if b_mn else (b2.shape[0], b2.shape[1])
+        if (M2, N2) != (M, Nn) or K2 != K2b:
+            raise ValueError("second operand pair has mismatching shape")
+    if out is None:
+        out = torch.empty(M, Nn, dtype=out_dtype or a.dtype, device=a.device)
+    else:
+        if out.shape != (M, Nn) or out.stride(1) != 1:
+            raise ValueError("bad `out`")
+    if out.dtype not in (a.dtype, torch.float32):
+        raise TypeError("output must have the operand dtype or fp32")
+    if c is not None:
+        if c.shape != (M, Nn) or c.stride(1) != 1 or c.dtype != a.dtype:
+            raise ValueError("bad `c`")
+    if bn is None:
+        bn = _pick_bn(Nn, b_mn)
+    status = N.status_word(a.device)
+    rc = N.lib().fmsb_gemm(
+        a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), K,
+        N.ptr(a2), a2.stride(0) if a2 is not None else 0, N.ptr(b2), b2.stride(0) if b2 is not None else 0, K2,
+        int(a_mn), int(b_mn),
+        out.data_ptr(), out.stride(0), int(out.dtype == torch.float32),
+        N.ptr(c), c.stride(0) if c is not None else 0,
+        float(alpha), float(beta), M, Nn, N.dtype_code(a.dtype), bn, int(max_ctas),
+        status.data_ptr(), N.stream_ptr(),
+    )
+    N.check(rc, "fmsb_gemm")
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``x @ w.T`` for ``x [..., K]`` and ``w [N, K]``."""
+    lead = x.shape[:-1]
+    y = gemm(x.reshape(-1, x.shape[-1]), w)
+    return y.reshape(*lead, w.shape[0])

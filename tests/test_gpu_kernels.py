@@ -1,0 +1,228 @@
+"""Numerics of the hand-written sm_100a kernels against plain PyTorch fp32 references."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from fms_acceleration_b200 import _native as NV
+from fms_acceleration_b200.ops import activation as A
+from fms_acceleration_b200.ops import cross_entropy as CE
+from fms_acceleration_b200.ops import quant as Q
+from fms_acceleration_b200.ops import rmsnorm as RN
+from fms_acceleration_b200.ops import rope as RP
+from fms_acceleration_b200.ops.gemm import gemm
+
+DEV = "cuda"
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm().clamp(min=1e-12)).item()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (200, 72, 136), (1000, 1032, 520)])
+def test_gemm_layouts(dtype, a_mn, b_mn, M, N, K):
+    torch.manual_seed(0)
+    a = torch.randn((K, M) if a_mn else (M, K), device=DEV, dtype=dtype)
+    b = torch.randn((K, N) if b_mn else (N, K), device=DEV, dtype=dtype)
+    ref = (a.float().t() if a_mn else a.float()) @ (b.float() if b_mn else b.float().t())
+    out = gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    NV.check_status()
+    assert out.shape == (M, N)
+    assert _rel(out, ref) < 1e-2
+    out32 = gemm(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+    NV.check_status()
+    assert _rel(out32, ref) < 2e-3 if dtype == torch.float16 else _rel(out32, ref) < 2e-3
+
+
+@pytest.mark.parametrize("bn", [16, 32, 64, 128, 256])
+def test_gemm_tile_widths(bn):
+    torch.manual_seed(1)
+    M, N_, K = 384, 272, 320
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N_, K, device=DEV, dtype=torch.bfloat16)
+    out = gemm(a, b, bn=bn, out_dtype=torch.float32)
+    NV.check_status()
+    assert _rel(out, a.float() @ b.float().t()) < 2e-3
+
+
+def test_gemm_dual_pair_and_epilogue():
+    torch.manual_seed(2)
+    M, N_, K, r = 512, 768, 1024, 16
+    x = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(N_, K, device=DEV, dtype=torch.bfloat16) * 0.05
+    xa = torch.randn(M, r, device=DEV, dtype=torch.bfloat16)
+    lb = torch.randn(N_, r, device=DEV, dtype=torch.bfloat16)
+    c = torch.randn(M, N_, device=DEV, dtype=torch.bfloat16)
+    ref = 0.5 * (x.float() @ w.float().t() + xa.float() @ lb.float().t()) + 2.0 * c.float()
+    out = gemm(x, w, a2=xa, b2=lb, c=c, alpha=0.5, beta=2.0, out_dtype=torch.float32)
+    NV.check_status()
+    assert _rel(out, ref) < 2e-3
+    # in-place accumulate into a bf16 output
+    d = c.clone()
+    gemm(x, w, c=d, beta=1.0, out=d)
+    NV.check_status()
+    assert _rel(d, x.float() @ w.float().t() + c.float()) < 1e-2
+
+
+def test_gemm_large_persistent():
+    torch.manual_seed(3)
+    M, N_, K = 4096, 4096, 2048
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N_, K, device=DEV, dtype=torch.bfloat16)
+    out = gemm(a, b)
+    NV.check_status()
+    ref = a @ b.t()
+    assert _rel(out, ref) < 1e-2
+    out2 = gemm(a, b)
+    assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,H", [(7, 256), (300, 4096), (33, 1536)])
+def test_rmsnorm(dtype, rows, H):
+    torch.manual_seed(0)
+    x = torch.randn(rows, H, device=DEV, dtype=dtype, requires_grad=True)
+    r = torch.randn(rows, H, device=DEV, dtype=dtype, requires_grad=True)
+    w = (torch.randn(H, device=DEV, dtype=dtype) * 0.1 + 1).requires_grad_()
+    y, h = RN.rmsnorm(x, w, 1e-6, False, r)
+    gy = torch.randn_like(y)
+    gh = torch.randn_like(h)
+    (y.float() * gy.float()).sum().backward(retain_graph=True)
+    # fp32 oracle
+    xf, rf, wf = (t.detach().float().requires_grad_() for t in (x, r, w))
+    hf = xf + rf
+    yf = hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + 1e-6) * wf
+    (yf * gy.float()).sum().backward()
+    tol = 2e-2
+    assert _rel(y, yf) < tol
+    assert _rel(h, hf) < tol
+    assert _rel(x.grad, xf.grad) < tol
+    assert _rel(r.grad, rf.grad) < tol
+    assert _rel(w.grad, wf.grad) < tol
+    # no residual, gemma flavour
+    x2 = torch.randn(rows, H, device=DEV, dtype=dtype)
+    y2 = RN.rmsnorm(x2, w.detach(), 1e-5, True)
+    ref2, _ = RN.rmsnorm_ref(x2.cpu(), w.detach().cpu(), 1e-5, True)
+    assert _rel(y2.cpu(), ref2) < tol
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_rope(dtype):
+    torch.manual_seed(0)
+    T, nh, d = 257, 6, 128
+    x = torch.randn(T, nh, d, device=DEV, dtype=dtype, requires_grad=True)
+    pos = torch.randint(0, 500, (T,), device=DEV, dtype=torch.int32)
+    cos_t, sin_t = RP.rope_tables(d, 512, 10000.0, DEV)
+    y = RP.apply_rope(x, pos, cos_t, sin_t)
+    ref = RP.rope_ref(x.detach().float(), pos, cos_t, sin_t)
+    assert _rel(y, ref) < 1e-2
+    g = torch.randn_like(y)
+    y.backward(g)
+    gref = RP.rope_ref(g.float(), pos, cos_t, sin_t, -1.0)
+    assert _rel(x.grad, gref) < 1e-2
+
+
+@pytest.mark.parametrize("act", ["silu", "gelu", "gelu_pytorch_tanh"])
+def test_glu(act):
+    torch.manual_seed(0)
+    rows, I = 130, 1024
+    eg = torch.randn(rows, 2 * I, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    e, g = eg[:, :I], eg[:, I:]
+    h = A.glu(e, g, act)
+    ef = eg.detach().float().requires_grad_()
+    fn = {"silu": torch.nn.functional.silu, "gelu": torch.nn.functional.gelu,
+          "gelu_pytorch_tanh": lambda t: torch.nn.functional.gelu(t, approximate="tanh")}[act]
+    hf = fn(ef[:, :I]) * ef[:, I:]
+    assert _rel(h, hf) < 1e-2
+    gh = torch.randn_like(h)
+    h.backward(gh)
+    hf.backward(gh.float())
+    assert _rel(eg.grad, ef.grad) < 1.5e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("V", [1000, 32000, 70001])
+def test_cross_entropy(dtype, V):
+    torch.manual_seed(0)
+    rows = 37
+    logits = (torch.randn(rows, V, device=DEV) * 3).to(dtype).requires_grad_()
+    labels = torch.randint(0, V, (rows,), device=DEV)
+    labels[::5] = -100
+    ref_in = logits.detach().float().requires_grad_()
+    ref = torch.nn.functional.cross_entropy(ref_in, labels, ignore_index=-100, reduction="none")
+    w = torch.randn(rows, device=DEV)
+    (ref * w).sum().backward()
+    keep = logits.detach().clone()
+    loss = CE.fast_cross_entropy_loss(logits, labels)
+    assert torch.allclose(loss, ref, rtol=1e-4, atol=1e-4)
+    (loss * w).sum().backward()
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert _rel(logits.grad, ref_in.grad) < max(tol, 1e-5)
+    # the backward reuses the logits storage for the gradient
+    assert not torch.equal(keep, logits.detach()) or V == 0
+
+
+def test_fused_linear_ce():
+    torch.manual_seed(0)
+    T, H, V = 700, 512, 4096
+    x = (torch.randn(T, H, device=DEV) * 0.5).bfloat16().requires_grad_()
+    w = (torch.randn(V, H, device=DEV) * 0.05).bfloat16().requires_grad_()
+    labels = torch.randint(0, V, (T,), device=DEV)
+    labels[:17] = -100
+    loss = CE.fused_linear_cross_entropy(x, w, labels)
+    NV.check_status()
+    (loss * 2.0).backward()
+    xf = x.detach().float().requires_grad_()
+    wf = w.detach().float().requires_grad_()
+    ref = torch.nn.functional.cross_entropy(xf @ wf.t(), labels, ignore_index=-100)
+    (ref * 2.0).backward()
+    assert abs(loss.item() - ref.item()) < 2e-2
+    assert _rel(x.grad, xf.grad) < 3e-2
+    assert _rel(w.grad, wf.grad) < 3e-2
+
+
+@pytest.mark.parametrize("quant_type", ["nf4", "fp4"])
+@pytest.mark.parametrize("double_quant", [True, False])
+def test_quant4_roundtrip(quant_type, double_quant):
+    torch.manual_seed(0)
+    w = (torch.randn(512, 1024, device=DEV) * 0.02).bfloat16()
+    qs = Q.quantize_4bit(w, quant_type, 64, double_quant)
+    qs_ref = Q.quantize_4bit(w.cpu(), quant_type, 64, double_quant)
+    # identical codes and scales as the CPU oracle
+    assert (qs.packed.cpu() != qs_ref.packed).float().mean().item() < 1e-4
+    if double_quant:
+        assert (qs.absmax_q.cpu() != qs_ref.absmax_q).float().mean().item() < 1e-3
+        assert torch.allclose(qs.absmax2.cpu(), qs_ref.absmax2)
+    else:
+        assert torch.allclose(qs.absmax.cpu(), qs_ref.absmax)
+    for dt in (torch.bfloat16, torch.float16):
+        d = Q.dequantize_4bit(qs, dt)
+        d_ref = Q.dequantize_4bit_ref(qs.to("cpu"), dt)
+        assert _rel(d.cpu(), d_ref) < 5e-3
+    err = _rel(Q.dequantize_4bit(qs), w)
+    assert err < (0.12 if quant_type == "nf4" else 0.2)
+
+
+@pytest.mark.parametrize("bits", [2, 4, 8])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_gptq_dequant(bits, dtype):
+    torch.manual_seed(0)
+    i, o, gs = 512, 256, 128
+    wi = torch.randint(0, 2 ** bits, (i, o), device=DEV)
+    zi = torch.randint(0, 2 ** bits - 1, (i // gs, o), device=DEV)
+    sc = (torch.rand(i // gs, o, device=DEV) * 0.01).to(dtype)
+    qw, qz = Q.gptq_pack(wi, bits), Q.gptq_pack_zeros(zi, bits)
+    g_idx = (torch.arange(i, device=DEV) // gs).int()
+    for gi in (g_idx, None):
+        for zoff in (0, 1):
+            W = Q.gptq_dequant(qw, sc, qz, gi, bits, gs, zoff)
+            ref = sc[g_idx.long()].float() * (wi - (zi[g_idx.long()] + zoff)).float()
+            assert _rel(W, ref) < 5e-3
+    # act-order style permuted groups
+    perm = torch.randperm(i, device=DEV)
+    g2 = g_idx[perm].contiguous()
+    W = Q.gptq_dequant(qw, sc, qz, g2, bits, gs, 0)
+    ref = sc[g2.long()].float() * (wi - zi[g2.long()]).float()
+    assert _rel(W, ref) < 5e-3
