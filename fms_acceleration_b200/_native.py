@@ -143,3 +143,8 @@ def check_status(device=None) -> None:
     if v != 0:
         w.zero_()
         raise NativeError(f"device status {v}: {_STATUS_NAMES.get(v, 'unknown')}")
+
+declare("fmsb_attn_fwd", [P, L, P, L, P, L, P, L, P, P, P, I, I, I, I, F, I, P, P])
+declare("fmsb_attn_delta", [P, P, L, L, P, I, I, I, I, P])
+declare("fmsb_attn_bwd_dq", [P, L, P, L, P, L, P, L, P, L, P, P, P, P, I, I, I, I, F, I, P, P])
+declare("fmsb_attn_bwd_dkv", [P, L, P, L, P, L, P, L, P, L, P, L, P, P, P, P, I, I, I, I, F, I, P, P])

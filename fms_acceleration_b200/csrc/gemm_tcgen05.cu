@@ -393,8 +393,7 @@ int launch_gemm(const CUtensorMap& a1, const CUtensorMap& b1, const CUtensorMap&
 }  // namespace fmsb_host
 
 // D[M,N] = alpha * (A1.B1^T + A2.B2^T) + beta * C.   16-bit inputs (fmt 0 = fp16, 1 = bf16).
-// Constraints: K1, K2 multiples of 8; leading dimensions multiples of 8 elements; base pointers
-// 16-byte aligned.  bn selects the N tile (16/32/64/128/256); MN-major B needs bn >= 64.
+// Constraints: leading dimensions multiples of 8 elements; base pointers 16-byte aligned.  bn selects the N tile (16/32/64/128/256); MN-major B needs bn >= 64.
 // max_ctas > 0 limits the grid (used to leave SMs to a concurrent communication kernel).
 // Returns 0 or a CUDA / encode error code.  Time-outs are reported through *status.
 extern "C" int fmsb_gemm(const void* A1, long long lda1, const void* B1, long long ldb1, int K1,  //
@@ -405,7 +404,8 @@ extern "C" int fmsb_gemm(const void* A1, long long lda1, const void* B1, long lo
                          cudaStream_t stream) {
   using namespace fmsb_host;
   if (M <= 0 || N <= 0) return 0;
-  if ((K1 % 8) || (K2 % 8) || K1 <= 0) return -2;
+  if (K1 <= 0 || K2 < 0) return -2;
+  if ((lda1 % 8) || (ldb1 % 8) || (K2 > 0 && ((lda2 % 8) || (ldb2 % 8)))) return -2;
   if (b_mn && bn < 64) return -3;
   CUtensorMap ta1, tb1, ta2, tb2;
   int rc;
