@@ -71,15 +71,41 @@ def lib():
                 continue
             fn.argtypes = argtypes
             fn.restype = c_int
-        _LIB = handle
+        _LIB = _CountingLib(handle)
     return _LIB
+
+
+class _CountingLib:
+    """Thin proxy over the CDLL handle that counts calls into the native launchers."""
+
+    def __init__(self, handle):
+        self._handle = handle
+        self._cache = {}
+        self.calls = 0
+
+    def __getattr__(self, name):
+        fn = self._cache.get(name)
+        if fn is None:
+            raw = getattr(self._handle, name)
+
+            def fn(*args, _raw=raw):
+                self.calls += 1
+                return _raw(*args)
+
+            self._cache[name] = fn
+        return fn
+
+
+def launch_count() -> int:
+    """Number of native launcher calls made by this process so far."""
+    return 0 if _LIB is None else _LIB.calls
 
 
 def declare(name: str, argtypes) -> None:
     """Register the signature of an entry point defined outside this table."""
     _SIGNATURES[name] = argtypes
-    if _LIB is not None and hasattr(_LIB, name):
-        fn = getattr(_LIB, name)
+    if _LIB is not None and hasattr(_LIB._handle, name):
+        fn = getattr(_LIB._handle, name)
         fn.argtypes = argtypes
         fn.restype = c_int
 

@@ -1,0 +1,118 @@
+"""Architecture descriptions for the in-tree model zoo and the presets used by the benchmarks."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field, asdict
+from typing import List, Optional
+
+
+@dataclass
+class DecoderConfig:
+    vocab_size: int = 32000
+    hidden_size: int = 4096
+    intermediate_size: int = 11008
+    num_hidden_layers: int = 32
+    num_attention_heads: int = 32
+    num_key_value_heads: Optional[int] = None
+    head_dim: Optional[int] = None
+    hidden_act: str = "silu"
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 10000.0
+    max_position_embeddings: int = 4096
+    tie_word_embeddings: bool = False
+    initializer_range: float = 0.02
+    model_type: str = "llama"
+    architectures: List[str] = field(default_factory=lambda: ["LlamaForCausalLM"])
+    # granite-style scalars
+    embedding_multiplier: float = 1.0
+    attention_multiplier: Optional[float] = None
+    residual_multiplier: float = 1.0
+    logits_scaling: float = 1.0
+    # mixture of experts
+    num_local_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    shared_intermediate_size: int = 0
+    router_aux_loss_coef: float = 0.0
+    # mamba2
+    mamba_d_state: int = 128
+    mamba_d_conv: int = 4
+    mamba_expand: int = 2
+    mamba_d_head: int = 64
+    mamba_n_groups: int = 1
+    mamba_chunk_size: int = 256
+    mamba_conv_bias: bool = True
+    mamba_proj_bias: bool = False
+    name_or_path: str = ""
+    torch_dtype: str = "bfloat16"
+
+    def __post_init__(self):
+        if self.num_key_value_heads is None:
+            self.num_key_value_heads = self.num_attention_heads
+        if self.head_dim is None:
+            self.head_dim = self.hidden_size // self.num_attention_heads
+
+    def to_dict(self):
+        return asdict(self)
+
+
+def tiny_llama() -> DecoderConfig:
+    """2-layer Llama used for CPU plumbing tests."""
+    return DecoderConfig(vocab_size=32000, hidden_size=256, intermediate_size=688, num_hidden_layers=2,
+                         num_attention_heads=4, num_key_value_heads=4, rms_norm_eps=1e-6, rope_theta=10000.0,
+                         max_position_embeddings=2048)
+
+
+def mistral_7b() -> DecoderConfig:
+    return DecoderConfig(vocab_size=32000, hidden_size=4096, intermediate_size=14336, num_hidden_layers=32,
+                         num_attention_heads=32, num_key_value_heads=8, rms_norm_eps=1e-5, rope_theta=1e6,
+                         max_position_embeddings=32768, model_type="mistral", architectures=["MistralForCausalLM"])
+
+
+def llama2_70b() -> DecoderConfig:
+    return DecoderConfig(vocab_size=32000, hidden_size=8192, intermediate_size=28672, num_hidden_layers=80,
+                         num_attention_heads=64, num_key_value_heads=8, rms_norm_eps=1e-5, rope_theta=10000.0,
+                         max_position_embeddings=4096, model_type="llama", architectures=["LlamaForCausalLM"])
+
+
+def granite_3b_a800m() -> DecoderConfig:
+    return DecoderConfig(vocab_size=49155, hidden_size=1536, intermediate_size=512, num_hidden_layers=32,
+                         num_attention_heads=24, num_key_value_heads=8, rms_norm_eps=1e-6, rope_theta=10000.0,
+                         max_position_embeddings=4096, tie_word_embeddings=True, model_type="granitemoe",
+                         architectures=["GraniteMoeForCausalLM"], num_local_experts=40, num_experts_per_tok=8,
+                         moe_intermediate_size=512)
+
+
+def tiny_granitemoe() -> DecoderConfig:
+    return DecoderConfig(vocab_size=1024, hidden_size=256, intermediate_size=128, num_hidden_layers=2,
+                         num_attention_heads=4, num_key_value_heads=2, tie_word_embeddings=True,
+                         model_type="granitemoe", architectures=["GraniteMoeForCausalLM"], num_local_experts=8,
+                         num_experts_per_tok=2, moe_intermediate_size=128)
+
+
+def mamba2_2p7b() -> DecoderConfig:
+    return DecoderConfig(vocab_size=50288, hidden_size=2560, num_hidden_layers=64, num_attention_heads=80,
+                         model_type="mamba2", architectures=["Mamba2ForCausalLM"], mamba_d_state=128,
+                         mamba_d_head=64, mamba_expand=2, mamba_d_conv=4, mamba_chunk_size=256, rms_norm_eps=1e-5,
+                         tie_word_embeddings=True)
+
+
+def tiny_mamba2() -> DecoderConfig:
+    return DecoderConfig(vocab_size=512, hidden_size=128, num_hidden_layers=2, num_attention_heads=4,
+                         model_type="mamba2", architectures=["Mamba2ForCausalLM"], mamba_d_state=32, mamba_d_head=64,
+                         mamba_expand=2, mamba_d_conv=4, mamba_chunk_size=32, rms_norm_eps=1e-5,
+                         tie_word_embeddings=True)
+
+
+PRESETS = {
+    "tiny-llama": tiny_llama,
+    "mistral-7b": mistral_7b,
+    "llama2-70b": llama2_70b,
+    "granite-3b-a800m": granite_3b_a800m,
+    "tiny-granitemoe": tiny_granitemoe,
+    "mamba2-2.7b": mamba2_2p7b,
+    "tiny-mamba2": tiny_mamba2,
+}
+
+
+def preset(name: str) -> DecoderConfig:
+    return PRESETS[name]()

@@ -1,0 +1,82 @@
+"""GPTQ-LoRA plugin - configuration path ``peft.quantization.auto_gptq``.
+
+Lifecycle as in fms_acceleration_peft/framework_plugin_autogptq.py:44-395 of the reference: the loader builds
+a model whose linears are GPTQ ``QuantLinear`` modules from a quantised checkpoint (``from_quantized: True`` is
+the only supported mode, ``kernel`` must be ``triton_v2`` for configuration compatibility - the kernel that
+actually runs is this package's CUDA dequant + tcgen05 GEMM), marks it ``is_loaded_in_4bit`` /
+``quantization_method = "gptq"``, and the augmentation installs LoRA adapters and returns ``peft_config=None``.
+Unlike the reference, bf16 compute is allowed in addition to fp16.
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, Tuple
+
+import torch
+
+from ...framework.framework_plugin import AccelerationPlugin
+from ...nn.lora import get_peft_model
+from .framework_plugin_bnb import _prepare_model_for_kbit_training
+
+
+class AutoGPTQAccelerationPlugin(AccelerationPlugin):
+    require_packages = None
+
+    def __init__(self, configurations: Dict[str, Dict]):
+        super().__init__(configurations)
+        self._check_config_equal(key="peft.quantization.auto_gptq.kernel", value="triton_v2")
+        self._check_config_equal(key="peft.quantization.auto_gptq.from_quantized", value=True)
+        self.use_external_lib = self._check_config_and_maybe_check_values(
+            key="peft.quantization.auto_gptq.use_external_lib", values=[True, False], default=False)
+
+    @property
+    def requires_custom_loading(self):
+        return True
+
+    @property
+    def requires_augmentation(self):
+        return True
+
+    def model_loader(self, model_name, **kwargs):
+        from .gptqmodel import GPTQModel, QuantizeConfig
+
+        torch_dtype = kwargs.get("torch_dtype", torch.float16)
+        device = kwargs.get("device")
+        if device is None:
+            device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else "cpu"
+        quantize_config = kwargs.get("quantize_config")
+        model = GPTQModel.from_quantized(model_name, quantize_config=quantize_config, torch_dtype=torch_dtype,
+                                         device=device, low_cpu_mem_usage=kwargs.get("low_cpu_mem_usage", False))
+        inner = getattr(model, "model", model)
+        inner.is_loaded_in_4bit = True
+        inner.quantization_method = "gptq"
+        return inner
+
+    def augmentation(self, model, train_args, modifiable_args: Tuple):
+        from .gptqmodel.utils.peft import get_gptq_peft_model
+
+        (peft_config,) = modifiable_args
+        assert peft_config is not None, "need peft_config to install PEFT adapters"
+        assert train_args.fp16 is True or train_args.bf16 is True, (
+            f"{self.__class__} requires mixed precision argument `--fp16` or `--bf16`")
+        model = _prepare_model_for_kbit_training(
+            model, use_gradient_checkpointing=train_args.gradient_checkpointing,
+            gradient_checkpointing_kwargs=train_args.gradient_checkpointing_kwargs)
+        qm = getattr(model, "quantization_method", "gptq")
+        model = get_gptq_peft_model(model, peft_config=peft_config,
+                                    auto_find_all_linears=requires_installation_on_all_linears(peft_config),
+                                    train_mode=True)
+        model.quantization_method = qm
+        return model, (None,)
+
+    def get_callbacks_and_ready_for_train(self, model=None, accelerator=None):
+        return []
+
+
+def requires_installation_on_all_linears(peft_config) -> bool:
+    """True when ``target_modules`` asks for every linear layer (``all-linear``)."""
+    tm = getattr(peft_config, "target_modules", None)
+    return isinstance(tm, str) and tm in ("all-linear", "all_linear")
+
+
+AccelerationPlugin.register_plugin(AutoGPTQAccelerationPlugin, configuration_and_paths=["peft.quantization.auto_gptq"])

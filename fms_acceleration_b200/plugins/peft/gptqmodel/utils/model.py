@@ -1,0 +1,170 @@
+"""Model surgery helpers for GPTQ: locate linears, swap them for ``QuantLinear``, pack, convert between the
+v1 and v2 zero-point layouts, find and shard checkpoint files.  Role of
+fms_acceleration_peft/gptqmodel/utils/model.py:103-717 in the reference."""
+from __future__ import annotations
+
+import json
+import os
+import re
+from typing import Dict, List, Optional, Tuple
+
+import torch
+from torch import nn
+
+from fms_acceleration_b200.nn.gptq import QuantLinear
+
+SAFE_WEIGHTS_NAME = "model.safetensors"
+SAFE_WEIGHTS_INDEX_NAME = "model.safetensors.index.json"
+
+
+def recurse_getattr(obj, attr: str):
+    for part in attr.split("."):
+        obj = getattr(obj, part)
+    return obj
+
+
+def recurse_setattr(module, name: str, value) -> None:
+    head, _, leaf = name.rpartition(".")
+    target = recurse_getattr(module, head) if head else module
+    setattr(target, leaf, value)
+
+
+def find_layers(module: nn.Module, layers=None, name: str = "") -> Dict[str, nn.Module]:
+    """All (dotted name -> module) below ``module`` whose type is one of ``layers`` (default: linear-like)."""
+    if layers is None:
+        layers = (nn.Linear, nn.Conv2d)
+    found = {}
+    for n, m in module.named_modules():
+        if isinstance(m, tuple(layers)) or (m.__class__.__name__ == "Conv1D" and nn.Linear in layers):
+            found[(name + "." + n) if name and n else (n or name)] = m
+    return found
+
+
+def get_module_by_name_prefix(model: nn.Module, prefix: str):
+    for n, m in model.named_modules():
+        if n.startswith(prefix):
+            return m
+    return None
+
+
+def get_module_by_name_suffix(model: nn.Module, suffix: str):
+    for n, m in model.named_modules():
+        if n.endswith(suffix):
+            return m
+    return None
+
+
+def make_quant(module: nn.Module, names, bits: int, group_size: int, dtype=torch.float16, zero_offset: int = 0,
+               device=None) -> None:
+    """Replace the linears listed in ``names`` (dotted, relative to ``module``) by empty ``QuantLinear``s."""
+    for n in list(names):
+        sub = recurse_getattr(module, n)
+        if isinstance(sub, QuantLinear):
+            continue
+        if isinstance(sub, nn.Linear):
+            in_f, out_f = sub.in_features, sub.out_features
+        elif sub.__class__.__name__ == "Conv1D":
+            in_f, out_f = sub.weight.shape[0], sub.weight.shape[1]
+        else:
+            in_f, out_f = sub.in_channels, sub.out_channels
+        dev = device if device is not None else (sub.weight.device if not sub.weight.is_meta else "cpu")
+        ql = QuantLinear(bits, group_size, in_f, out_f, getattr(sub, "bias", None) is not None, dtype, zero_offset, dev)
+        recurse_setattr(module, n, ql)
+
+
+def pack_model(model: nn.Module, quantizers: Dict[str, Tuple], bits: int, group_size: int, dtype=torch.float16) -> None:
+    """``quantizers[name] = (quantizer, scale [out,G], zero [out,G], g_idx)`` -> packed ``QuantLinear`` modules."""
+    floats = {n: m for n, m in find_layers(model).items() if n in quantizers}
+    make_quant(model, floats.keys(), bits, group_size, dtype)
+    for name, lin in floats.items():
+        _, scale, zero, g_idx = quantizers[name]
+        ql: QuantLinear = recurse_getattr(model, name)
+        ql.pack(lin.to("cpu"), scale.to("cpu"), zero.to("cpu"), g_idx.to("cpu") if g_idx is not None else None)
+
+
+def convert_gptq_v1_to_v2_format(model: nn.Module, bits: int) -> nn.Module:
+    """v1 checkpoints store ``zero - 1``; add one to every packed zero field (an integer add of a repeated
+    ``1`` pattern, e.g. 0x11111111 for 4 bits, carries exactly like the reference's conversion)."""
+    pattern = {2: 0b01010101010101010101010101010101, 4: 0x11111111, 8: 0x01010101}
+    for m in model.modules():
+        if isinstance(m, QuantLinear):
+            if bits == 3:
+                raise NotImplementedError("3-bit zero-point conversion is not supported")
+            add = pattern[bits]
+            z = (m.qzeros.long() & 0xFFFFFFFF) + add
+            z = z & 0xFFFFFFFF
+            m.qzeros = torch.where(z >= 2 ** 31, z - 2 ** 32, z).to(torch.int32)
+            m.zero_offset = 0
+    return model
+
+
+def convert_gptq_v2_to_v1_format(model: nn.Module, bits: int) -> nn.Module:
+    pattern = {2: 0b01010101010101010101010101010101, 4: 0x11111111, 8: 0x01010101}
+    for m in model.modules():
+        if isinstance(m, QuantLinear):
+            sub = pattern[bits]
+            z = ((m.qzeros.long() & 0xFFFFFFFF) - sub) & 0xFFFFFFFF
+            m.qzeros = torch.where(z >= 2 ** 31, z - 2 ** 32, z).to(torch.int32)
+            m.zero_offset = 1
+    return model
+
+
+def get_checkpoints(model_dir: str, extensions=(".safetensors",), possible_basenames=("model", "gptq_model"),
+                    **kwargs) -> Tuple[bool, List[str], Optional[str]]:
+    """(is_sharded, files, found_basename) for a local checkpoint directory."""
+    index = os.path.join(model_dir, SAFE_WEIGHTS_INDEX_NAME)
+    if os.path.exists(index):
+        with open(index, encoding="utf-8") as fh:
+            files = sorted(set(json.load(fh)["weight_map"].values()))
+        return True, [os.path.join(model_dir, f) for f in files], "model"
+    for base in possible_basenames:
+        for ext in extensions:
+            p = os.path.join(model_dir, base + ext)
+            if os.path.exists(p):
+                return False, [p], base
+    return False, [], None
+
+
+def shard_checkpoint(state_dict: Dict[str, torch.Tensor], max_shard_size: int = 5 * 2 ** 30,
+                     weights_name: str = SAFE_WEIGHTS_NAME):
+    """Split a state dict into shards of at most ``max_shard_size`` bytes.  Returns (shards, index or None)."""
+    shards: List[Dict[str, torch.Tensor]] = [{}]
+    sizes = [0]
+    total = 0
+    for k, v in state_dict.items():
+        nbytes = v.numel() * v.element_size()
+        if sizes[-1] + nbytes > max_shard_size and shards[-1]:
+            shards.append({})
+            sizes.append(0)
+        shards[-1][k] = v
+        sizes[-1] += nbytes
+        total += nbytes
+    if len(shards) == 1:
+        return {weights_name: shards[0]}, None
+    stem, ext = os.path.splitext(weights_name)
+    named, weight_map = {}, {}
+    for i, sh in enumerate(shards):
+        fname = f"{stem}-{i + 1:05d}-of-{len(shards):05d}{ext}"
+        named[fname] = sh
+        for k in sh:
+            weight_map[k] = fname
+    return named, {"metadata": {"total_size": total}, "weight_map": weight_map}
+
+
+def parse_size(size) -> int:
+    if isinstance(size, int):
+        return size
+    m = re.fullmatch(r"\s*(\d+(?:\.\d+)?)\s*([KMGT]?)I?B\s*", str(size).upper())
+    if not m:
+        raise ValueError(f"cannot parse size {size!r}")
+    mult = {"": 1, "K": 2 ** 10, "M": 2 ** 20, "G": 2 ** 30, "T": 2 ** 40}[m.group(2)]
+    return int(float(m.group(1)) * mult)
+
+
+def auto_dtype_from_config(config, quant_inference: bool = False) -> torch.dtype:
+    dt = getattr(config, "torch_dtype", None)
+    if isinstance(dt, str):
+        dt = getattr(torch, dt, None)
+    if dt in (torch.float16, torch.bfloat16):
+        return dt
+    return torch.float16
