@@ -304,6 +304,281 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
+// ----------------------------------------------------------------------------------------
+// Forward, two query tiles per CTA ("ping-pong"): while the softmax warpgroup of one tile
+// works, the tensor core runs the other tile's S and P.V products.  P never touches shared
+// memory: each softmax thread overwrites the first 64 columns of its own S row in tensor
+// memory with the 128 probabilities as packed 16-bit pairs and the P.V product reads its A
+// operand from tensor memory.  The running maximum is only advanced (and O rescaled) when the
+// block maximum exceeds it by more than 2^8, so most blocks skip the O round trip.
+// ----------------------------------------------------------------------------------------
+template <int D>
+struct AttnFwd2Cfg {
+  static constexpr int kTileBytes = 128 * D * 2;
+  static constexpr int kHalfBytes = 128 * 64 * 2;
+  static constexpr int kSmemBytes = 2 * kTileBytes /*Qa,Qb*/ + 2 * 2 * kTileBytes /*K,V x2 stages*/ + 1024 + 256;
+};
+
+template <int D>
+__global__ void __launch_bounds__(320, 1)
+attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+  using Cfg = AttnFwd2Cfg<D>;
+  constexpr int NH = D / 64;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  auto sQ = [&](int x) { return base + Cfg::kTileBytes * x; };
+  auto sK = [&](int s) { return base + Cfg::kTileBytes * (2 + 2 * s); };
+  auto sV = [&](int s) { return base + Cfg::kTileBytes * (3 + 2 * s); };
+  const uint32_t bars = base + Cfg::kTileBytes * 6;
+  const uint32_t bar_q = bars;
+  auto bar_kv_full = [&](int s) { return bars + 8u * (1 + s); };
+  auto bar_kv_empty = [&](int s) { return bars + 8u * (3 + s); };
+  auto bar_s_full = [&](int x) { return bars + 8u * (5 + x); };
+  auto bar_p_full = [&](int x) { return bars + 8u * (7 + x); };
+  auto bar_pv_done = [&](int x) { return bars + 8u * (9 + x); };
+  const uint32_t holder = bars + 8u * 11;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = gridDim.x - 1 - blockIdx.x;
+  const int head = blockIdx.y;
+  const int hk = head / (p.nh / p.nkv);
+  const int q0 = qt * 256;
+  // per-tile key-block ranges (tile 1 may lie completely beyond T)
+  int blk_lo[2], blk_hi[2], ds_last_t[2];
+  bool exists[2];
+#pragma unroll
+  for (int x = 0; x < 2; ++x) {
+    const int qs = q0 + 128 * x;
+    exists[x] = qs < p.T;
+    const int ql = min(qs + 127, p.T - 1);
+    blk_lo[x] = exists[x] ? p.doc_start[qs] / ATT_BK : 0;
+    blk_hi[x] = exists[x] ? ql / ATT_BK : -1;
+    ds_last_t[x] = exists[x] ? p.doc_start[ql] : 0;
+  }
+  const int kb_lo = blk_lo[0];
+  const int kb_hi = exists[1] ? blk_hi[1] : blk_hi[0];
+  const int nblk = kb_hi - kb_lo + 1;
+  auto active = [&](int x, int j) { const int kb = kb_lo + j; return exists[x] && kb >= blk_lo[x] && kb <= blk_hi[x]; };
+
+  if (warp == 1 && lane == 0) {
+    mbar_init(bar_q, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_kv_full(s), 1);
+      mbar_init(bar_kv_empty(s), 1);
+      mbar_init(bar_s_full(s), 1);
+      mbar_init(bar_p_full(s), 128);
+      mbar_init(bar_pv_done(s), 1);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(holder, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  uint32_t tmem;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem) : "r"(holder));
+  auto tS = [&](int x) { return tmem + 128u * x; };
+  auto tO = [&](int x) { return tmem + 256u + 128u * x; };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(bar_q, (exists[1] ? 2 : 1) * Cfg::kTileBytes);
+      for (int x = 0; x < 2; ++x) {
+        if (!exists[x]) continue;
+#pragma unroll
+        for (int h = 0; h < NH; ++h)
+          tma_load_2d(sQ(x) + h * Cfg::kHalfBytes, &tmQ, bar_q, head * D + 64 * h, q0 + 128 * x);
+      }
+      for (int j = 0; j < nblk; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(bar_kv_empty(s), ((j >> 1) & 1) ^ 1u, p.status, kTimeoutProducer)) break;
+        mbar_expect_tx(bar_kv_full(s), 2 * Cfg::kTileBytes);
+        const int k0 = (kb_lo + j) * ATT_BK;
+#pragma unroll
+        for (int h = 0; h < NH; ++h) {
+          tma_load_2d(sK(s) + h * Cfg::kHalfBytes, &tmK, bar_kv_full(s), hk * D + 64 * h, k0);
+          tma_load_2d(sV(s) + h * Cfg::kHalfBytes, &tmV, bar_kv_full(s), hk * D + 64 * h, k0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_f16(128, 128, p.fmt, 0, 0);
+      const uint32_t idesc_o = make_idesc_f16(128, D, p.fmt, 0, 1);
+      auto issue_s = [&](int x, int j) {
+        const int s = j & 1;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (ks / 4) * Cfg::kHalfBytes + (ks % 4) * 32;
+          tc_mma_f16(tS(x), make_smem_desc(sQ(x) + off, 16, 1024), make_smem_desc(sK(s) + off, 16, 1024), idesc_s,
+                     ks != 0);
+        }
+        tc_commit(bar_s_full(x));
+      };
+      int cnt[2] = {0, 0};  // active blocks issued so far per tile
+      bool ok = mbar_wait(bar_q, 0, p.status, kTimeoutMma);
+      if (ok) ok = mbar_wait(bar_kv_full(0), 0, p.status, kTimeoutMma);
+      if (ok) {
+        tc_fence_after();
+        for (int x = 0; x < 2; ++x)
+          if (active(x, 0)) issue_s(x, 0);
+      }
+      for (int j = 0; j < nblk && ok; ++j) {
+        const int s = j & 1;
+        bool next_ready = false;
+        for (int x = 0; x < 2 && ok; ++x) {
+          if (active(x, j)) {
+            if (!mbar_wait(bar_p_full(x), cnt[x] & 1, p.status, kTimeoutMma)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll
+            for (int ks = 0; ks < ATT_BK / 16; ++ks) {
+              const uint64_t bdesc = make_smem_desc(sV(s) + ks * 2048, Cfg::kHalfBytes, 1024);
+              tc_mma_f16_ts(tO(x), tS(x) + ks * 8, bdesc, idesc_o, (cnt[x] | ks) != 0);
+            }
+            tc_commit(bar_pv_done(x));
+            cnt[x] += 1;
+          }
+          if (j + 1 < nblk && active(x, j + 1)) {
+            if (!next_ready) {
+              const int jn = j + 1;
+              if (!mbar_wait(bar_kv_full(jn & 1), (jn >> 1) & 1, p.status, kTimeoutMma)) { ok = false; break; }
+              tc_fence_after();
+              next_ready = true;
+            }
+            issue_s(x, j + 1);
+          }
+        }
+        if (ok) tc_commit(bar_kv_empty(s));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax warpgroups
+    const int x = (warp - 2) >> 2;  // tile handled by this warpgroup
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    const int t = q0 + 128 * x + row;
+    const bool row_ok = t < p.T;
+    const int ds = row_ok ? p.doc_start[t] : 0;
+    const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+    const float sl2 = p.scale * 1.4426950408889634f;
+    const int qs = q0 + 128 * x;
+    float m_used = -1e30f, l_run = 0.f;
+    int cnt = 0;
+    bool ok = true;
+    if (exists[x]) {
+      for (int j = 0; j < nblk; ++j) {
+        if (!active(x, j)) continue;
+        const int k0 = (kb_lo + j) * ATT_BK;
+        if (!mbar_wait(bar_s_full(x), cnt & 1, p.status, kTimeoutEpilogue)) { ok = false; break; }
+        tc_fence_after();
+        const bool need_mask = !(k0 >= ds_last_t[x] && k0 + ATT_BK - 1 <= qs) || !row_ok;
+        float sv[128];
+        {
+          uint32_t r[32];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            tmem_ld_32x32(tS(x) + lane_addr + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) sv[c * 32 + i] = __uint_as_float(r[i]);
+          }
+        }
+        float m_blk = -1e30f;
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 128; ++i) {
+            const int kk = k0 + i;
+            if (!(row_ok && kk >= ds && kk <= t)) sv[i] = -1e30f;
+            m_blk = fmaxf(m_blk, sv[i]);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 128; ++i) m_blk = fmaxf(m_blk, sv[i]);
+        }
+        // advance the reference maximum only when it is exceeded by more than 2^8
+        float alpha = 1.f;
+        const bool bump = (m_blk - m_used) * sl2 > 8.f || cnt == 0;
+        if (bump) {
+          const float m_new = fmaxf(m_used, m_blk);
+          alpha = exp2f((m_used - m_new) * sl2);
+          m_used = m_new;
+        }
+        const float mb = m_used * sl2;
+        float l_blk = 0.f;
+        uint32_t packed[64];
+#pragma unroll
+        for (int i = 0; i < 128; i += 2) {
+          const float p0 = sv[i] <= -1e30f ? 0.f : exp2f(sv[i] * sl2 - mb);
+          const float p1 = sv[i + 1] <= -1e30f ? 0.f : exp2f(sv[i + 1] * sl2 - mb);
+          l_blk += p0 + p1;
+          packed[i / 2] = pack2(p0, p1, p.fmt);
+        }
+        l_run = l_run * alpha + l_blk;
+        // P (16-bit pairs) over the first 64 columns of this thread's own S row
+        {
+          uint32_t r[32];
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = packed[c * 32 + i];
+            tmem_st_32x32(tS(x) + lane_addr + c * 32, r);
+          }
+        }
+        if (cnt > 0 && __any_sync(0xffffffffu, bump)) {
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(tO(x) + lane_addr + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st_32x32(tO(x) + lane_addr + c * 32, r);
+          }
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(bar_p_full(x));
+        cnt += 1;
+      }
+      if (ok && cnt > 0 && mbar_wait(bar_pv_done(x), (cnt - 1) & 1, p.status, kTimeoutEpilogue)) {
+        tc_fence_after();
+        const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(tO(x) + lane_addr + c * 32, r);
+          tmem_ld_wait();
+          if (row_ok) {
+            uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + (long long)t * p.ldo + head * D + c * 32;
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 u;
+              u.x = pack2(__uint_as_float(r[i]) * inv_l, __uint_as_float(r[i + 1]) * inv_l, p.fmt);
+              u.y = pack2(__uint_as_float(r[i + 2]) * inv_l, __uint_as_float(r[i + 3]) * inv_l, p.fmt);
+              u.z = pack2(__uint_as_float(r[i + 4]) * inv_l, __uint_as_float(r[i + 5]) * inv_l, p.fmt);
+              u.w = pack2(__uint_as_float(r[i + 6]) * inv_l, __uint_as_float(r[i + 7]) * inv_l, p.fmt);
+              *reinterpret_cast<uint4*>(orow + i) = u;
+            }
+          }
+        }
+        if (row_ok) p.lse[(long long)head * p.T + t] = m_used * p.scale + __logf(l_run);
+      }
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
 // delta[h, t] = sum_d dO[t, h, d] * O[t, h, d]
 template <typename T>
 __global__ void attn_delta_kernel(const T* __restrict__ o, const T* __restrict__ dout, long long ldo, long long lddo,
@@ -784,25 +1059,25 @@ extern "C" int fmsb_attn_fwd(const void* q, long long ldq, const void* k, long l
   p.T = T; p.nh = nh; p.nkv = nkv; p.d = d; p.scale = scale;
   p.doc_start = doc_start; p.doc_end = doc_end;
   p.o = o; p.ldo = ldo; p.lse = lse; p.fmt = fmt; p.status = status;
-  dim3 grid((T + ATT_BQ - 1) / ATT_BQ, nh);
+  dim3 grid((T + 255) / 256, nh);
   if (d == 128) {
     static bool cfg = false;
     if (!cfg) {
-      cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           AttnFwdCfg<128>::kSmemBytes);
+      cudaError_t e = cudaFuncSetAttribute(attn_fwd2_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           AttnFwd2Cfg<128>::kSmemBytes);
       if (e != cudaSuccess) return (int)e;
       cfg = true;
     }
-    attn_fwd_kernel<128><<<grid, 192, AttnFwdCfg<128>::kSmemBytes, stream>>>(tq, tk, tv, p);
+    attn_fwd2_kernel<128><<<grid, 320, AttnFwd2Cfg<128>::kSmemBytes, stream>>>(tq, tk, tv, p);
   } else {
     static bool cfg = false;
     if (!cfg) {
-      cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           AttnFwdCfg<64>::kSmemBytes);
+      cudaError_t e = cudaFuncSetAttribute(attn_fwd2_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           AttnFwd2Cfg<64>::kSmemBytes);
       if (e != cudaSuccess) return (int)e;
       cfg = true;
     }
-    attn_fwd_kernel<64><<<grid, 192, AttnFwdCfg<64>::kSmemBytes, stream>>>(tq, tk, tv, p);
+    attn_fwd2_kernel<64><<<grid, 320, AttnFwd2Cfg<64>::kSmemBytes, stream>>>(tq, tk, tv, p);
   }
   return (int)cudaGetLastError();
 }
