@@ -70,6 +70,11 @@ class AutoGPTQAccelerationPlugin(AccelerationPlugin):
         return model, (None,)
 
     def get_callbacks_and_ready_for_train(self, model=None, accelerator=None):
+        if (accelerator is not None and getattr(accelerator.state, "fsdp_plugin", None) is not None
+                and model is not None and next(model.parameters()).is_cuda):
+            from ...parallel.engine import install_engine
+
+            install_engine(model, accelerator)
         return []
 
 

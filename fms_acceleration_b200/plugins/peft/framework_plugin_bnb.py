@@ -89,6 +89,10 @@ class BNBAccelerationPlugin(AccelerationPlugin):
             plugin = accelerator.state.fsdp_plugin
             base = model if self._no_peft_model or not hasattr(model, "get_base_model") else model.get_base_model()
             plugin.param_init_fn = ensure_weights_retied(plugin.param_init_fn, base, accelerator.device)
+            if model is not None and next(model.parameters()).is_cuda:
+                from ...parallel.engine import install_engine
+
+                install_engine(model, accelerator)
         return []
 
 

@@ -122,7 +122,10 @@ class Trainer:
         if self.args.max_grad_norm and self.args.max_grad_norm > 0:
             torch.nn.utils.clip_grad_norm_(self.params, self.args.max_grad_norm)
         self.optimizer.step()
-        self.optimizer.zero_grad(set_to_none=True)
+        if self.engine is not None:
+            self.engine.zero_grad()
+        else:
+            self.optimizer.zero_grad(set_to_none=True)
         self.global_step += 1
         return loss.detach()
 

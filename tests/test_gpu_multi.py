@@ -1,0 +1,34 @@
+"""Multi-GPU tests: run ``tests/dist_worker.py`` under torchrun on 2 GPUs (skipped with fewer).  NVLS is switched
+off for NCCL (it only bootstraps and provides the reference results here)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(which: str, nproc: int = 2, timeout: int = 600):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", "29533", os.path.join(HERE, "dist_worker.py"), which]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+    return res
+
+
+@pytest.mark.parametrize("which,expected", [
+    ("comm", ["allgather", "allreduce", "reduce_scatter"]),
+    ("engine", ["engine", "engine_train"]),
+])
+def test_multi_gpu(which, expected):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    res = _run(which)
+    out = res.stdout + res.stderr
+    assert res.returncode == 0, out[-3000:]
+    for name in expected:
+        assert out.count(f"DIST_OK {name}") >= 2, f"{name} did not pass on both ranks\n{out[-3000:]}"
