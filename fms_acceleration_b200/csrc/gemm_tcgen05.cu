@@ -43,6 +43,22 @@ struct GemmParams {
   float alpha, beta;
   int fmt;  // 0 = fp16, 1 = bf16
   int* status;
+  // grouped execution (mixture-of-experts): see fmsb_grouped_gemm
+  int mode;                  // 0 plain, 1 grouped along M (rows of A/D segmented), 2 grouped along K (one D per group)
+  int n_groups;
+  const int* seg_off;        // [n_groups + 1] segment starts in rows, multiples of 128 (device memory)
+  int b_group_rows;          // rows of B that belong to one group
+  long long d_group_stride;  // elements between the D matrices of consecutive groups (mode 2)
+};
+
+struct TileInfo {
+  int m0, n0;        // coordinates of the A rows / B columns of this tile
+  int m_store;       // row offset used for stores (== m0 except in mode 2 where D is per group)
+  int m_end;         // rows >= m_end are not stored
+  int k_begin;       // first contraction element (mode 2: segment start)
+  int kblocks1;      // 64-wide blocks of operand pair 1 for this tile
+  int b_row_off;     // added to B's row coordinate (group offset)
+  long long d_off;   // element offset of this tile's D matrix
 };
 
 template <int BN>
@@ -64,6 +80,65 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   const int in_group = t - group * group_size;
   tm = first_m + in_group % gm;
   tn = in_group / gm;
+}
+
+// Decode persistent work item `t`.  Returns false when t is past the last tile.
+template <int BN>
+__device__ __forceinline__ bool get_tile(int t, const GemmParams& p, TileInfo& ti) {
+  const int tiles_n = (p.N + BN - 1) / BN;
+  if (p.mode == 0) {
+    const int tiles_m = (p.M + BM - 1) / BM;
+    if (t >= tiles_m * tiles_n) return false;
+    int tm, tn;
+    tile_coords(t, tiles_m, tiles_n, tm, tn);
+    ti.m0 = tm * BM;
+    ti.n0 = tn * BN;
+    ti.m_store = ti.m0;
+    ti.m_end = p.M;
+    ti.k_begin = 0;
+    ti.kblocks1 = p.kblocks1;
+    ti.b_row_off = 0;
+    ti.d_off = 0;
+    return true;
+  }
+  if (p.mode == 1) {
+    // segments of A/D rows, one B matrix per segment; M-fastest inside a segment so that the
+    // CTAs running at the same time share the segment's B tiles
+    int rem = t;
+    for (int g = 0; g < p.n_groups; ++g) {
+      const int s0 = p.seg_off[g];
+      const int mt = (p.seg_off[g + 1] - s0) / BM;
+      const int ntile = mt * tiles_n;
+      if (rem < ntile) {
+        ti.m0 = s0 + (rem % mt) * BM;
+        ti.n0 = (rem / mt) * BN;
+        ti.m_store = ti.m0;
+        ti.m_end = p.seg_off[g + 1];
+        ti.k_begin = 0;
+        ti.kblocks1 = p.kblocks1;
+        ti.b_row_off = g * p.b_group_rows;
+        ti.d_off = 0;
+        return true;
+      }
+      rem -= ntile;
+    }
+    return false;
+  }
+  // mode 2: D[g] = A[seg_g]^T B[seg_g]; the contraction runs over the rows of segment g
+  const int tiles_m = (p.M + BM - 1) / BM;
+  const int per_group = tiles_m * tiles_n;
+  if (t >= per_group * p.n_groups) return false;
+  const int g = t / per_group;
+  const int r = t - g * per_group;
+  ti.m0 = (r % tiles_m) * BM;
+  ti.n0 = (r / tiles_m) * BN;
+  ti.m_store = ti.m0;
+  ti.m_end = p.M;
+  ti.k_begin = p.seg_off[g];
+  ti.kblocks1 = (p.seg_off[g + 1] - p.seg_off[g]) / BK;
+  ti.b_row_off = 0;
+  ti.d_off = (long long)g * p.d_group_stride;
+  return true;
 }
 
 template <int BN, int A_MN, int B_MN>
@@ -117,31 +192,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_const
   uint32_t tmem_base;
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(holder));
 
-  const int tiles_m = (p.M + BM - 1) / BM;
-  const int tiles_n = (p.N + BN - 1) / BN;
-  const int num_tiles = tiles_m * tiles_n;
-  const int kblocks = p.kblocks1 + p.kblocks2;
-
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        int tm, tn;
-        tile_coords(t, tiles_m, tiles_n, tm, tn);
-        const int m0 = tm * BM, n0 = tn * BN;
+      TileInfo ti;
+      for (int t = blockIdx.x; ok && get_tile<BN>(t, p, ti); t += gridDim.x) {
+        const int m0 = ti.m0, n0 = ti.n0;
+        const int kblocks = ti.kblocks1 + p.kblocks2;
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, p.status, kTimeoutProducer)) {
             ok = false;
             break;
           }
           mbar_expect_tx(full_bar(stage), Cfg::kStageBytes);
-          const bool second = kb >= p.kblocks1;
+          const bool second = kb >= ti.kblocks1;
           const CUtensorMap* ta = second ? &tmA2 : &tmA1;
           const CUtensorMap* tb = second ? &tmB2 : &tmB1;
-          const int k0 = (second ? kb - p.kblocks1 : kb) * BK;
+          const int k0 = second ? (kb - ti.kblocks1) * BK : ti.k_begin + kb * BK;
+          // the group offset applies to B's row coordinate: the k rows of an MN-major B, the n rows of a K-major B
+          const int brow = second ? 0 : ti.b_row_off;
           if (A_MN == 0) {
             tma_load_2d(sA(stage), ta, full_bar(stage), k0, m0);
           } else {
@@ -150,11 +222,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_const
               tma_load_2d(sA(stage) + j * 8192, ta, full_bar(stage), m0 + 64 * j, k0);
           }
           if (B_MN == 0) {
-            tma_load_2d(sB(stage), tb, full_bar(stage), k0, n0);
+            tma_load_2d(sB(stage), tb, full_bar(stage), k0, n0 + brow);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(sB(stage) + j * 8192, tb, full_bar(stage), n0 + 64 * j, k0);
+              tma_load_2d(sB(stage) + j * 8192, tb, full_bar(stage), n0 + 64 * j, k0 + brow);
           }
           if (++stage == Cfg::kStages) {
             stage = 0;
@@ -172,7 +244,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_const
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      TileInfo ti;
+      for (int t = blockIdx.x; ok && get_tile<BN>(t, p, ti); t += gridDim.x) {
+        const int kblocks = ti.kblocks1 + p.kblocks2;
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, p.status, kTimeoutMma)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
@@ -197,6 +271,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_const
           }
         }
         if (!ok) break;
+        if (kblocks == 0) {
+          // empty segment (mode 2): nothing was accumulated; the epilogue writes zeros
+        }
         tc_commit(tfull_bar(acc));
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
@@ -209,11 +286,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_const
     int acc = 0;
     uint32_t acc_phase = 0;
     constexpr int CH = BN >= 32 ? 32 : 16;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-      int tm, tn;
-      tile_coords(t, tiles_m, tiles_n, tm, tn);
-      const int gm = tm * BM + row;
-      const int n0 = tn * BN;
+    TileInfo ti;
+    for (int t = blockIdx.x; get_tile<BN>(t, p, ti); t += gridDim.x) {
+      const int gm = ti.m_store + row;
+      const int n0 = ti.n0;
+      const bool empty_k = (ti.kblocks1 + p.kblocks2) == 0;
       if (!mbar_wait(tfull_bar(acc), acc_phase, p.status, kTimeoutEpilogue)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
@@ -225,22 +302,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_const
           tmem_ld_32x32(taddr + c * CH, r);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          for (int i = 0; i < 32; ++i) v[i] = empty_k ? 0.f : __uint_as_float(r[i]);
         } else {
           uint32_t r[16];
           tmem_ld_32x16(taddr + c * CH, r);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+          for (int i = 0; i < 16; ++i) v[i] = empty_k ? 0.f : __uint_as_float(r[i]);
         }
         const int gn = n0 + c * CH;
-        if (gm < p.M && gn < p.N) {
+        if (gm < ti.m_end && gn < p.N) {
           const bool full = (gn + CH <= p.N);
 #pragma unroll
           for (int i = 0; i < CH; ++i) v[i] *= p.alpha;
           if (p.C != nullptr && p.beta != 0.f) {
             if (p.fmt == 1) {
-              const __nv_bfloat16* crow = reinterpret_cast<const __nv_bfloat16*>(p.C) + (long long)gm * p.ldc + gn;
+              const __nv_bfloat16* crow = reinterpret_cast<const __nv_bfloat16*>(p.C) + ti.d_off + (long long)gm * p.ldc + gn;
               if (full && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
 #pragma unroll
                 for (int i = 0; i < CH; i += 8) {
@@ -258,13 +335,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_const
                   if (gn + i < p.N) v[i] += p.beta * __bfloat162float(crow[i]);
               }
             } else {
-              const __half* crow = reinterpret_cast<const __half*>(p.C) + (long long)gm * p.ldc + gn;
+              const __half* crow = reinterpret_cast<const __half*>(p.C) + ti.d_off + (long long)gm * p.ldc + gn;
               for (int i = 0; i < CH; ++i)
                 if (gn + i < p.N) v[i] += p.beta * __half2float(crow[i]);
             }
           }
           if (p.d_fp32) {
-            float* drow = reinterpret_cast<float*>(p.D) + (long long)gm * p.ldd + gn;
+            float* drow = reinterpret_cast<float*>(p.D) + ti.d_off + (long long)gm * p.ldd + gn;
             if (full && ((reinterpret_cast<uintptr_t>(drow) & 15) == 0)) {
 #pragma unroll
               for (int i = 0; i < CH; i += 4)
@@ -274,7 +351,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_const
                 if (gn + i < p.N) drow[i] = v[i];
             }
           } else {
-            uint16_t* drow = reinterpret_cast<uint16_t*>(p.D) + (long long)gm * p.ldd + gn;
+            uint16_t* drow = reinterpret_cast<uint16_t*>(p.D) + ti.d_off + (long long)gm * p.ldd + gn;
             if (full && ((reinterpret_cast<uintptr_t>(drow) & 15) == 0)) {
 #pragma unroll
               for (int i = 0; i < CH; i += 8) {
@@ -381,10 +458,12 @@ int launch_gemm(const CUtensorMap& a1, const CUtensorMap& b1, const CUtensorMap&
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  const int tiles = ((p.M + fmsb::BM - 1) / fmsb::BM) * ((p.N + BN - 1) / BN);
   int ctas = sm_count();
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
-  if (tiles < ctas) ctas = tiles;
+  if (p.mode == 0) {
+    const int tiles = ((p.M + fmsb::BM - 1) / fmsb::BM) * ((p.N + BN - 1) / BN);
+    if (tiles < ctas) ctas = tiles;
+  }
   if (ctas <= 0) return 0;
   kern<<<ctas, 192, Cfg::kSmemBytes, stream>>>(a1, b1, a2, b2, p);
   return static_cast<int>(cudaGetLastError());
@@ -396,12 +475,13 @@ int launch_gemm(const CUtensorMap& a1, const CUtensorMap& b1, const CUtensorMap&
 // Constraints: leading dimensions multiples of 8 elements; base pointers 16-byte aligned.  bn selects the N tile (16/32/64/128/256); MN-major B needs bn >= 64.
 // max_ctas > 0 limits the grid (used to leave SMs to a concurrent communication kernel).
 // Returns 0 or a CUDA / encode error code.  Time-outs are reported through *status.
-extern "C" int fmsb_gemm(const void* A1, long long lda1, const void* B1, long long ldb1, int K1,  //
-                         const void* A2, long long lda2, const void* B2, long long ldb2, int K2,  //
-                         int a_mn, int b_mn,                                                       //
-                         void* D, long long ldd, int d_fp32, const void* C, long long ldc,        //
-                         float alpha, float beta, int M, int N, int fmt, int bn, int max_ctas, int* status,
-                         cudaStream_t stream) {
+static int gemm_impl(const void* A1, long long lda1, const void* B1, long long ldb1, int K1,  //
+                     const void* A2, long long lda2, const void* B2, long long ldb2, int K2,  //
+                     int a_mn, int b_mn,                                                       //
+                     void* D, long long ldd, int d_fp32, const void* C, long long ldc,        //
+                     float alpha, float beta, int M, int N, int fmt, int bn, int max_ctas, int* status,
+                     cudaStream_t stream, int mode, int n_groups, const int* seg_off, int b_group_rows,
+                     long long d_group_stride, long long a_rows, long long b_rows) {
   using namespace fmsb_host;
   if (M <= 0 || N <= 0) return 0;
   if (K1 <= 0 || K2 < 0) return -2;
@@ -409,11 +489,15 @@ extern "C" int fmsb_gemm(const void* A1, long long lda1, const void* B1, long lo
   if (b_mn && bn < 64) return -3;
   CUtensorMap ta1, tb1, ta2, tb2;
   int rc;
+  // a_rows / b_rows: number of rows of the stored A / B matrices when it differs from the per-tile view
+  // (grouped modes address several segments / expert matrices through one tensor map)
   auto mk_a = [&](CUtensorMap* t, const void* A, long long lda, int K) {
-    return a_mn ? make_tmap_2d_16b(t, A, K, M, lda, 64, 64) : make_tmap_2d_16b(t, A, M, K, lda, fmsb::BM, 64);
+    if (a_mn) return make_tmap_2d_16b(t, A, a_rows > 0 ? a_rows : K, M, lda, 64, 64);
+    return make_tmap_2d_16b(t, A, a_rows > 0 ? a_rows : M, K, lda, fmsb::BM, 64);
   };
   auto mk_b = [&](CUtensorMap* t, const void* B, long long ldb, int K) {
-    return b_mn ? make_tmap_2d_16b(t, B, K, N, ldb, 64, 64) : make_tmap_2d_16b(t, B, N, K, ldb, bn, 64);
+    if (b_mn) return make_tmap_2d_16b(t, B, b_rows > 0 ? b_rows : K, N, ldb, 64, 64);
+    return make_tmap_2d_16b(t, B, b_rows > 0 ? b_rows : N, K, ldb, bn, 64);
   };
   if ((rc = mk_a(&ta1, A1, lda1, K1))) return rc;
   if ((rc = mk_b(&tb1, B1, ldb1, K1))) return rc;
@@ -438,6 +522,11 @@ extern "C" int fmsb_gemm(const void* A1, long long lda1, const void* B1, long lo
   p.beta = beta;
   p.fmt = fmt;
   p.status = status;
+  p.mode = mode;
+  p.n_groups = n_groups;
+  p.seg_off = seg_off;
+  p.b_group_rows = b_group_rows;
+  p.d_group_stride = d_group_stride;
 
 #define FMSB_DISPATCH(BNV)                                                                          \
   if (bn == BNV) {                                                                                  \
@@ -455,4 +544,38 @@ extern "C" int fmsb_gemm(const void* A1, long long lda1, const void* B1, long lo
   FMSB_DISPATCH(16)
 #undef FMSB_DISPATCH
   return -4;
+}
+
+extern "C" int fmsb_gemm(const void* A1, long long lda1, const void* B1, long long ldb1, int K1,  //
+                         const void* A2, long long lda2, const void* B2, long long ldb2, int K2,  //
+                         int a_mn, int b_mn,                                                       //
+                         void* D, long long ldd, int d_fp32, const void* C, long long ldc,        //
+                         float alpha, float beta, int M, int N, int fmt, int bn, int max_ctas, int* status,
+                         cudaStream_t stream) {
+  return gemm_impl(A1, lda1, B1, ldb1, K1, A2, lda2, B2, ldb2, K2, a_mn, b_mn, D, ldd, d_fp32, C, ldc, alpha, beta, M,
+                   N, fmt, bn, max_ctas, status, stream, 0, 0, nullptr, 0, 0, 0, 0);
+}
+
+// Grouped GEMM for mixture-of-experts layers.  seg_off[g] (device, n_groups + 1 ints, multiples of 128) are the
+// row offsets of the expert segments inside the expert-sorted activation buffers.
+//   mode 1: D[seg_g, :N] = A[seg_g, :K] . B_g      A [rows, K] K-major, rows = seg_off[n_groups] (a_rows >= that);
+//           b_mn = 1: B_g = B[g*K : (g+1)*K, :N]    (weights stored [E, in, out], forward)
+//           b_mn = 0: B_g = B[g*N : (g+1)*N, :K]^T  (same storage, input gradient)
+//   mode 2: D_g[M, N] = A[seg_g, :M]^T . B[seg_g, :N]   (weight gradient; a_mn = b_mn = 1; D_g at D + g*d_group_stride)
+extern "C" int fmsb_grouped_gemm(const void* A, long long lda, const void* B, long long ldb, int K, int b_mn, void* D,
+                                 long long ldd, int d_fp32, const void* C, long long ldc, float alpha, float beta, int M,
+                                 int N, int fmt, int bn, int mode, int n_groups, const int* seg_off,
+                                 long long d_group_stride, long long a_rows, long long b_rows, int* status,
+                                 cudaStream_t stream) {
+  if (mode == 1) {
+    const int b_group_rows = b_mn ? K : N;
+    return gemm_impl(A, lda, B, ldb, K, nullptr, 0, nullptr, 0, 0, 0, b_mn, D, ldd, d_fp32, C, ldc, alpha, beta,
+                     (int)a_rows, N, fmt, bn, 0, status, stream, 1, n_groups, seg_off, b_group_rows, 0, a_rows, b_rows);
+  }
+  if (mode == 2) {
+    // K is only a placeholder here: the contraction length of each group comes from seg_off
+    return gemm_impl(A, lda, B, ldb, 64, nullptr, 0, nullptr, 0, 0, 1, 1, D, ldd, d_fp32, C, ldc, alpha, beta, M, N,
+                     fmt, bn, 0, status, stream, 2, n_groups, seg_off, 0, d_group_stride, a_rows, b_rows);
+  }
+  return -2;
 }

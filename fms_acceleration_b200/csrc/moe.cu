@@ -1,0 +1,491 @@
+// Mixture-of-experts routing, dispatch and combine kernels (local and expert-parallel).
+//
+// Reference behaviour being reproduced (paths inside the reference project):
+//   fms_acceleration_moe/utils/scattermoe.py:306-323        router: softmax (fp32) -> top-k -> renormalise
+//   fms_acceleration_moe/utils/scattermoe.py:342-344 and
+//   .../scattermoe_utils/khd/kernels/ops/__init__.py:26-56   sort by expert, per-128-row padded block offsets
+//   .../scattermoe_utils/expert_parallel.py:97-232           expert-parallel all-to-all: exchange per-expert
+//       counts, replicate every token top_k times grouped by destination expert, exchange rows, and on the way
+//       back multiply by the routing weight and sum over top_k (with a host synchronisation per layer)
+//   .../scattermoe_utils/megablocks/kernels/gather_scatter.py:37-278   row copy / scale / weight-gradient kernels
+//
+// Design here: no sort and no host synchronisation.  Tokens keep their order; a plan is computed on the
+// device: expert histogram -> (expert-parallel: the histograms of all ranks are exchanged through peer
+// memory) -> padded segment offsets of every expert in its owner's receive buffer -> a deterministic slot for
+// every (token, k) pair.  `dispatch` then writes each token row straight into its slot, which lives in the
+// owner rank's buffer (a peer store over NVLink when the owner is another rank), and `combine` reads the
+// expert outputs back from the owners with the routing weight applied and the top-k sum fused.  Segments are
+// padded to multiples of 128 rows and the pad rows are kept zero so that the grouped tcgen05 GEMMs
+// (gemm_tcgen05.cu, modes 1 and 2) need no row masks.
+#include "common.cuh"
+
+namespace fmsb {
+
+constexpr int kMoeMaxRanks = 16;
+constexpr int kMoeMaxExperts = 512;
+
+struct MoePeers {
+  void* p[kMoeMaxRanks];
+};
+
+__device__ __forceinline__ void moe_st_release(uint32_t* addr, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t moe_ld_acquire(const uint32_t* addr) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ bool moe_wait_ge(const uint32_t* addr, uint32_t epoch, int* status) {
+  const long long t0 = clock64();
+  while (true) {
+    for (int i = 0; i < 64; ++i)
+      if ((int32_t)(moe_ld_acquire(addr) - epoch) >= 0) return true;
+    if (clock64() - t0 > kWaitBudgetCycles) {
+      report_status(status, kTimeoutPeerFlag);
+      return false;
+    }
+    if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return false;
+  }
+}
+
+// ----------------------------------------------------------------------------------------
+// router: one warp per token.  logits [T, E] (fp32) -> probs of the top-k experts, renormalised.
+// ----------------------------------------------------------------------------------------
+template <int MAXPER>
+__global__ void router_topk_kernel(const float* __restrict__ logits, int T, int E, int k, int renorm,
+                                   int* __restrict__ topk_idx, float* __restrict__ topk_w) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= T) return;
+  const float* row = logits + (long long)warp * E;
+  float v[MAXPER];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < MAXPER; ++j) {
+    const int e = lane + 32 * j;
+    v[j] = e < E ? row[e] : -INFINITY;
+    mx = fmaxf(mx, v[j]);
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < MAXPER; ++j) {
+    v[j] = (lane + 32 * j) < E ? __expf(v[j] - mx) : 0.f;
+    sum += v[j];
+  }
+  sum = warp_sum(sum);
+  const float inv = 1.f / sum;
+  float sel_sum = 0.f;
+  float my_w = 0.f;
+  int my_i = 0;
+  for (int s = 0; s < k; ++s) {
+    // arg-max over the warp; ties go to the lower expert index (as torch.topk on sorted indices)
+    float best = -1.f;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < MAXPER; ++j) {
+      const int e = lane + 32 * j;
+      if (e < E && (v[j] > best || (v[j] == best && e < best_e))) {
+        best = v[j];
+        best_e = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ob > best || (ob == best && oe < best_e)) {
+        best = ob;
+        best_e = oe;
+      }
+    }
+    if (lane == s) {
+      my_w = best * inv;
+      my_i = best_e;
+    }
+    sel_sum += best * inv;
+#pragma unroll
+    for (int j = 0; j < MAXPER; ++j)
+      if (lane + 32 * j == best_e) v[j] = -2.f;  // taken
+  }
+  if (lane < k) {
+    topk_idx[(long long)warp * k + lane] = my_i;
+    topk_w[(long long)warp * k + lane] = renorm ? my_w / sel_sum : my_w;
+  }
+}
+
+// Backward of the router: dlogits[t, e] from d(topk_w).  With p = softmax(logits), S = sum of the selected p and
+// w_j = p_j / S (renorm) or w_j = p_j:  dL/dp_j = (g_j - sum_i g_i w_i) / S for selected j (renorm), g_j otherwise,
+// 0 for unselected; then the softmax Jacobian.
+template <int MAXPER>
+__global__ void router_topk_bwd_kernel(const float* __restrict__ logits, const int* __restrict__ topk_idx,
+                                       const float* __restrict__ topk_w, const float* __restrict__ dw, int T, int E,
+                                       int k, int renorm, float* __restrict__ dlogits) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= T) return;
+  const float* row = logits + (long long)warp * E;
+  float p[MAXPER], dp[MAXPER];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < MAXPER; ++j) {
+    const int e = lane + 32 * j;
+    p[j] = e < E ? row[e] : -INFINITY;
+    mx = fmaxf(mx, p[j]);
+    dp[j] = 0.f;
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < MAXPER; ++j) {
+    p[j] = (lane + 32 * j) < E ? __expf(p[j] - mx) : 0.f;
+    sum += p[j];
+  }
+  sum = warp_sum(sum);
+#pragma unroll
+  for (int j = 0; j < MAXPER; ++j) p[j] /= sum;
+  float gw = 0.f, S = 0.f;
+  for (int s = 0; s < k; ++s) {
+    const float g = dw[(long long)warp * k + s];
+    const float w = topk_w[(long long)warp * k + s];
+    gw += g * w;
+    const int e = topk_idx[(long long)warp * k + s];
+#pragma unroll
+    for (int j = 0; j < MAXPER; ++j)
+      if (lane + 32 * j == e) S += p[j];
+  }
+  S = warp_sum(S);
+  for (int s = 0; s < k; ++s) {
+    const float g = dw[(long long)warp * k + s];
+    const int e = topk_idx[(long long)warp * k + s];
+#pragma unroll
+    for (int j = 0; j < MAXPER; ++j)
+      if (lane + 32 * j == e) dp[j] = renorm ? (g - gw) / S : g;
+  }
+  float dot = 0.f;
+#pragma unroll
+  for (int j = 0; j < MAXPER; ++j) dot += dp[j] * p[j];
+  dot = warp_sum(dot);
+#pragma unroll
+  for (int j = 0; j < MAXPER; ++j) {
+    const int e = lane + 32 * j;
+    if (e < E) dlogits[(long long)warp * E + e] = p[j] * (dp[j] - dot);
+  }
+}
+
+// ----------------------------------------------------------------------------------------
+// plan
+// ----------------------------------------------------------------------------------------
+// counts[e] = number of (token, k) pairs routed to global expert e (this rank's tokens)
+__global__ void expert_count_kernel(const int* __restrict__ topk_idx, long long n, int E, int* __restrict__ counts) {
+  extern __shared__ int sh[];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) sh[e] = 0;
+  __syncthreads();
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    atomicAdd(&sh[topk_idx[i]], 1);
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x)
+    if (sh[e]) atomicAdd(&counts[e], sh[e]);
+}
+
+// Exchange the histograms and derive the layout.  One CTA.
+//   count_tables.p[r] : rank r's table int[world][E] (row s = histogram of source rank s); every rank writes its
+//                       own histogram into row `rank` of every peer's table
+//   signals.p[r]      : rank r's flag words, uint32[world] on the plan channel
+// Outputs (local): seg_off[E_local + 1] padded (x128) offsets of my experts in my receive buffer,
+//   seg_cnt[E_local] true row counts, send_base[E] = first slot of MY rows of global expert e in its owner's buffer.
+//   status gets kCapacityOverflow when any owner's buffer (capacity rows) would overflow.
+__global__ void moe_plan_kernel(MoePeers count_tables, MoePeers signals, const int* __restrict__ my_counts, int rank,
+                                int world, int E, int capacity, uint32_t epoch, int* __restrict__ seg_off,
+                                int* __restrict__ seg_cnt, int* __restrict__ send_base, int* status) {
+  const int E_local = E / world;
+  __shared__ int ok;
+  if (threadIdx.x == 0) ok = 1;
+  __syncthreads();
+  if (world > 1) {
+    // push my histogram to every rank, then signal
+    for (int i = threadIdx.x; i < world * E; i += blockDim.x) {
+      const int r = i / E, e = i % E;
+      reinterpret_cast<int*>(count_tables.p[r])[rank * E + e] = my_counts[e];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < world) {
+      moe_st_release(reinterpret_cast<uint32_t*>(signals.p[threadIdx.x]) + rank, epoch);
+      if (!moe_wait_ge(reinterpret_cast<const uint32_t*>(signals.p[rank]) + threadIdx.x, epoch, status)) ok = 0;
+    }
+    __syncthreads();
+    if (!ok) return;
+  }
+  const int* table = world > 1 ? reinterpret_cast<const int*>(count_tables.p[rank]) : my_counts;
+  // every rank derives the layout of every owner (cheap, E <= 512)
+  if (threadIdx.x == 0) {
+    for (int owner = 0; owner < world; ++owner) {
+      int off = 0;
+      for (int el = 0; el < E_local; ++el) {
+        const int e = owner * E_local + el;
+        int total = 0, before_me = 0;
+        for (int s = 0; s < world; ++s) {
+          const int c = world > 1 ? table[s * E + e] : table[e];
+          if (s < rank) before_me += c;
+          total += c;
+        }
+        send_base[e] = off + before_me;
+        if (owner == rank) {
+          seg_off[el] = off;
+          seg_cnt[el] = total;
+        }
+        off += (total + 127) / 128 * 128;
+      }
+      if (owner == rank) seg_off[E_local] = off;
+      if (off > capacity) report_status(status, kCapacityOverflow);
+    }
+  }
+}
+
+// Deterministic slot of every (token, k) pair: the j-th pair (in token order) routed to expert e gets
+// send_base[e] + j.  One CTA per expert; block-wide compaction by ballot + prefix.
+__global__ void moe_assign_kernel(const int* __restrict__ topk_idx, long long n, const int* __restrict__ send_base,
+                                  int* __restrict__ dest_row) {
+  const int e = blockIdx.x;
+  __shared__ int warp_tot[32];
+  __shared__ int running;
+  if (threadIdx.x == 0) running = send_base[e];
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (long long base = 0; base < n; base += blockDim.x) {
+    const long long i = base + threadIdx.x;
+    const bool hit = i < n && topk_idx[i] == e;
+    const unsigned m = __ballot_sync(0xffffffffu, hit);
+    const int prefix = __popc(m & ((1u << lane) - 1));
+    if (lane == 0) warp_tot[warp] = __popc(m);
+    __syncthreads();
+    int woff = 0, tot = 0;
+    for (int w = 0; w < nwarps; ++w) {
+      if (w < warp) woff += warp_tot[w];
+      tot += warp_tot[w];
+    }
+    if (hit) dest_row[i] = running + woff + prefix;
+    __syncthreads();
+    if (threadIdx.x == 0) running += tot;
+    __syncthreads();
+  }
+}
+
+// ----------------------------------------------------------------------------------------
+// dispatch / combine
+// ----------------------------------------------------------------------------------------
+// For every (token t, k): owner_buf[dest_row][:] = x[t][:] * (scale ? scale[t, k] : 1).  One warp per pair.
+template <typename T>
+__global__ void moe_dispatch_kernel(const T* __restrict__ x, long long ldx, const int* __restrict__ topk_idx,
+                                    const int* __restrict__ dest_row, const float* __restrict__ scale, long long n_pairs,
+                                    int k, int H, int E_local, MoePeers recv, long long ld_recv) {
+  const long long pair = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (pair >= n_pairs) return;
+  const long long t = pair / k;
+  const int owner = topk_idx[pair] / E_local;
+  const long long row = dest_row[pair];
+  const T* src = x + t * ldx;
+  T* dst = reinterpret_cast<T*>(recv.p[owner]) + row * ld_recv;
+  const float sc = scale != nullptr ? scale[pair] : 1.f;
+  for (int c = lane * 8; c < H; c += 256) {
+    uint4 v = *reinterpret_cast<const uint4*>(src + c);
+    if (scale != nullptr) {
+      T* e = reinterpret_cast<T*>(&v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (std::is_same<T, __nv_bfloat16>::value)
+          reinterpret_cast<__nv_bfloat16*>(e)[i] = __float2bfloat16_rn(__bfloat162float(reinterpret_cast<__nv_bfloat16*>(e)[i]) * sc);
+        else
+          reinterpret_cast<__half*>(e)[i] = __float2half_rn(__half2float(reinterpret_cast<__half*>(e)[i]) * sc);
+      }
+    }
+    *reinterpret_cast<uint4*>(dst + c) = v;
+  }
+}
+
+// zero the pad rows [seg_off[e] + seg_cnt[e], seg_off[e + 1]) of a local buffer
+template <typename T>
+__global__ void moe_zero_pad_kernel(T* __restrict__ buf, long long ld, int H, const int* __restrict__ seg_off,
+                                    const int* __restrict__ seg_cnt, int E_local) {
+  const int e = blockIdx.x;
+  const int r0 = seg_off[e] + seg_cnt[e], r1 = seg_off[e + 1];
+  const int vec_per_row = H / 8;
+  const long long total = (long long)(r1 - r0) * vec_per_row;
+  for (long long i = threadIdx.x; i < total; i += blockDim.x) {
+    const long long r = r0 + i / vec_per_row;
+    const int c = (int)(i % vec_per_row) * 8;
+    *reinterpret_cast<uint4*>(buf + r * ld + c) = make_uint4(0, 0, 0, 0);
+  }
+}
+
+// out[t][:] = sum_k w[t, k] * owner_buf(t, k)[dest_row(t, k)][:]   (w == nullptr: plain sum).  One warp per token;
+// the expert outputs are read from the owners' buffers (peer loads when remote).
+template <typename T>
+__global__ void moe_combine_kernel(MoePeers ybuf, long long ldy, const int* __restrict__ topk_idx,
+                                   const int* __restrict__ dest_row, const float* __restrict__ w, long long T_tokens,
+                                   int k, int H, int E_local, T* __restrict__ out, long long ldo) {
+  const long long t = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (t >= T_tokens) return;
+  for (int c = lane * 8; c < H; c += 256) {
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int s = 0; s < k; ++s) {
+      const long long pair = t * k + s;
+      const int owner = topk_idx[pair] / E_local;
+      const T* src = reinterpret_cast<const T*>(ybuf.p[owner]) + (long long)dest_row[pair] * ldy + c;
+      const uint4 v = *reinterpret_cast<const uint4*>(src);
+      const float ws = w != nullptr ? w[pair] : 1.f;
+      const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float f = std::is_same<T, __nv_bfloat16>::value
+                            ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(e)[i])
+                            : __half2float(reinterpret_cast<const __half*>(e)[i]);
+        acc[i] += ws * f;
+      }
+    }
+    uint4 o;
+    if (std::is_same<T, __nv_bfloat16>::value) {
+      o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+    } else {
+      o.x = pack_f16x2(acc[0], acc[1]); o.y = pack_f16x2(acc[2], acc[3]);
+      o.z = pack_f16x2(acc[4], acc[5]); o.w = pack_f16x2(acc[6], acc[7]);
+    }
+    *reinterpret_cast<uint4*>(out + t * ldo + c) = o;
+  }
+}
+
+// dgate[t, k] = <owner_buf(t, k)[dest_row(t, k)], dout[t]>   (gradient of the routing weight).  One warp per pair.
+template <typename T>
+__global__ void moe_gate_grad_kernel(MoePeers ybuf, long long ldy, const int* __restrict__ topk_idx,
+                                     const int* __restrict__ dest_row, const T* __restrict__ dout, long long lddo,
+                                     long long n_pairs, int k, int H, int E_local, float* __restrict__ dgate) {
+  const long long pair = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (pair >= n_pairs) return;
+  const long long t = pair / k;
+  const int owner = topk_idx[pair] / E_local;
+  const T* y = reinterpret_cast<const T*>(ybuf.p[owner]) + (long long)dest_row[pair] * ldy;
+  const T* g = dout + t * lddo;
+  float acc = 0.f;
+  for (int c = lane * 8; c < H; c += 256) {
+    const uint4 a = *reinterpret_cast<const uint4*>(y + c);
+    const uint4 b = *reinterpret_cast<const uint4*>(g + c);
+    const T* ea = reinterpret_cast<const T*>(&a);
+    const T* eb = reinterpret_cast<const T*>(&b);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (std::is_same<T, __nv_bfloat16>::value)
+        acc += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(ea)[i]) * __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(eb)[i]);
+      else
+        acc += __half2float(reinterpret_cast<const __half*>(ea)[i]) * __half2float(reinterpret_cast<const __half*>(eb)[i]);
+    }
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) dgate[pair] = acc;
+}
+
+}  // namespace fmsb
+
+using namespace fmsb;
+
+static MoePeers moe_ptrs(void* const* arr, int world) {
+  MoePeers p{};
+  for (int i = 0; i < world && i < kMoeMaxRanks; ++i) p.p[i] = arr[i];
+  return p;
+}
+
+extern "C" int fmsb_moe_router(const float* logits, int T, int E, int k, int renorm, int* topk_idx, float* topk_w,
+                               cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (E > 256 || k > 32 || k > E) return -2;
+  const int grid = (T * 32 + 255) / 256;
+  if (E <= 64) router_topk_kernel<2><<<grid, 256, 0, stream>>>(logits, T, E, k, renorm, topk_idx, topk_w);
+  else router_topk_kernel<8><<<grid, 256, 0, stream>>>(logits, T, E, k, renorm, topk_idx, topk_w);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fmsb_moe_router_bwd(const float* logits, const int* topk_idx, const float* topk_w, const float* dw, int T,
+                                   int E, int k, int renorm, float* dlogits, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (E > 256 || k > 32) return -2;
+  const int grid = (T * 32 + 255) / 256;
+  if (E <= 64) router_topk_bwd_kernel<2><<<grid, 256, 0, stream>>>(logits, topk_idx, topk_w, dw, T, E, k, renorm, dlogits);
+  else router_topk_bwd_kernel<8><<<grid, 256, 0, stream>>>(logits, topk_idx, topk_w, dw, T, E, k, renorm, dlogits);
+  return (int)cudaGetLastError();
+}
+
+// counts must be zeroed by the caller.  Then plan + assign.  count_tables / signals may be null when world == 1.
+extern "C" int fmsb_moe_plan(const int* topk_idx, long long n_pairs, int E, int rank, int world, int capacity,
+                             int* counts, void* const* count_tables, void* const* signals, unsigned epoch,
+                             int* seg_off, int* seg_cnt, int* send_base, int* dest_row, int* status,
+                             cudaStream_t stream) {
+  if (E > kMoeMaxExperts || world > kMoeMaxRanks || E % world != 0) return -2;
+  if (n_pairs > 0) {
+    long long blocks = (n_pairs + 255) / 256;
+    if (blocks > 1024) blocks = 1024;
+    expert_count_kernel<<<(int)blocks, 256, E * sizeof(int), stream>>>(topk_idx, n_pairs, E, counts);
+  }
+  MoePeers ct = world > 1 ? moe_ptrs(count_tables, world) : MoePeers{};
+  MoePeers sg = world > 1 ? moe_ptrs(signals, world) : MoePeers{};
+  moe_plan_kernel<<<1, 256, 0, stream>>>(ct, sg, counts, rank, world, E, capacity, epoch, seg_off, seg_cnt, send_base,
+                                         status);
+  if (n_pairs > 0) moe_assign_kernel<<<E, 1024, 0, stream>>>(topk_idx, n_pairs, send_base, dest_row);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fmsb_moe_dispatch(const void* x, long long ldx, const int* topk_idx, const int* dest_row,
+                                 const float* scale, long long n_pairs, int k, int H, int E_local, void* const* recv,
+                                 long long ld_recv, int world, int dtype, cudaStream_t stream) {
+  if (n_pairs <= 0) return 0;
+  if (H % 8 != 0 || ldx % 8 != 0 || ld_recv % 8 != 0) return -2;
+  MoePeers r = moe_ptrs(recv, world);
+  const long long blocks = (n_pairs * 32 + 255) / 256;
+  if (dtype == 1)
+    moe_dispatch_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, topk_idx, dest_row, scale, n_pairs, k, H, E_local, r, ld_recv);
+  else
+    moe_dispatch_kernel<__half><<<(unsigned)blocks, 256, 0, stream>>>((const __half*)x, ldx, topk_idx, dest_row, scale, n_pairs, k, H, E_local, r, ld_recv);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fmsb_moe_zero_pad(void* buf, long long ld, int H, const int* seg_off, const int* seg_cnt, int E_local,
+                                 int dtype, cudaStream_t stream) {
+  if (E_local <= 0) return 0;
+  if (H % 8 != 0 || ld % 8 != 0) return -2;
+  if (dtype == 1) moe_zero_pad_kernel<__nv_bfloat16><<<E_local, 256, 0, stream>>>((__nv_bfloat16*)buf, ld, H, seg_off, seg_cnt, E_local);
+  else moe_zero_pad_kernel<__half><<<E_local, 256, 0, stream>>>((__half*)buf, ld, H, seg_off, seg_cnt, E_local);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fmsb_moe_combine(void* const* ybuf, long long ldy, const int* topk_idx, const int* dest_row,
+                                const float* w, long long T_tokens, int k, int H, int E_local, void* out, long long ldo,
+                                int world, int dtype, cudaStream_t stream) {
+  if (T_tokens <= 0) return 0;
+  if (H % 8 != 0 || ldy % 8 != 0 || ldo % 8 != 0) return -2;
+  MoePeers y = moe_ptrs(ybuf, world);
+  const long long blocks = (T_tokens * 32 + 255) / 256;
+  if (dtype == 1)
+    moe_combine_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>(y, ldy, topk_idx, dest_row, w, T_tokens, k, H, E_local, (__nv_bfloat16*)out, ldo);
+  else
+    moe_combine_kernel<__half><<<(unsigned)blocks, 256, 0, stream>>>(y, ldy, topk_idx, dest_row, w, T_tokens, k, H, E_local, (__half*)out, ldo);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fmsb_moe_gate_grad(void* const* ybuf, long long ldy, const int* topk_idx, const int* dest_row,
+                                  const void* dout, long long lddo, long long n_pairs, int k, int H, int E_local,
+                                  float* dgate, int world, int dtype, cudaStream_t stream) {
+  if (n_pairs <= 0) return 0;
+  MoePeers y = moe_ptrs(ybuf, world);
+  const long long blocks = (n_pairs * 32 + 255) / 256;
+  if (dtype == 1)
+    moe_gate_grad_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>(y, ldy, topk_idx, dest_row, (const __nv_bfloat16*)dout, lddo, n_pairs, k, H, E_local, dgate);
+  else
+    moe_gate_grad_kernel<__half><<<(unsigned)blocks, 256, 0, stream>>>(y, ldy, topk_idx, dest_row, (const __half*)dout, lddo, n_pairs, k, H, E_local, dgate);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,83 @@
+"""GraniteMoe-style decoder: Llama attention + a top-k mixture-of-experts feed-forward with fused expert weights
+in the Hugging Face layout (``block_sparse_moe.input_linear.weight [E, 2I, H]``, ``output_linear.weight [E, H, I]``,
+``router.layer.weight [E, H]``).  The eager block below loops over experts (the unaccelerated baseline); the
+ScatterMoE plugin swaps it for the grouped-GEMM module."""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from .config import DecoderConfig
+from .llama import LlamaDecoderLayer, LlamaForCausalLM, LlamaModel
+
+
+class GraniteMoeParallelExperts(nn.Module):
+    def __init__(self, num_experts: int, input_size: int, output_size: int):
+        super().__init__()
+        self.weight = nn.Parameter(torch.empty(num_experts, output_size, input_size))
+        self.num_experts, self.input_size, self.output_size = num_experts, input_size, output_size
+
+
+class GraniteMoeTopKGating(nn.Module):
+    def __init__(self, input_size: int, num_experts: int, top_k: int):
+        super().__init__()
+        self.layer = nn.Linear(input_size, num_experts, bias=False)
+        self.num_experts, self.top_k = num_experts, top_k
+
+
+class GraniteMoeMoE(nn.Module):
+    """Reference (loop-over-experts) implementation."""
+
+    def __init__(self, cfg: DecoderConfig):
+        super().__init__()
+        self.input_size = cfg.hidden_size
+        self.hidden_size = cfg.moe_intermediate_size or cfg.intermediate_size
+        self.num_experts, self.top_k = cfg.num_local_experts, cfg.num_experts_per_tok
+        self.input_linear = GraniteMoeParallelExperts(self.num_experts, self.input_size, 2 * self.hidden_size)
+        self.output_linear = GraniteMoeParallelExperts(self.num_experts, self.hidden_size, self.input_size)
+        self.router = GraniteMoeTopKGating(self.input_size, self.num_experts, self.top_k)
+        self.hidden_act = cfg.hidden_act
+        for p in (self.input_linear.weight, self.output_linear.weight):
+            nn.init.normal_(p, 0.0, cfg.initializer_range)
+
+    def forward(self, x):
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        logits = self.router.layer(x2)
+        probs = torch.softmax(logits.float(), dim=-1)
+        w, idx = torch.topk(probs, self.top_k, dim=-1)
+        w = (w / w.sum(-1, keepdim=True)).to(x.dtype)
+        out = torch.zeros_like(x2)
+        I = self.hidden_size
+        for e in range(self.num_experts):
+            tok, slot = torch.nonzero(idx == e, as_tuple=True)
+            if tok.numel() == 0:
+                continue
+            h = x2[tok] @ self.input_linear.weight[e].t()
+            h = F.silu(h[:, :I]) * h[:, I:]
+            out.index_add_(0, tok, (h @ self.output_linear.weight[e].t()) * w[tok, slot][:, None])
+        return out.view(shape), logits
+
+
+class GraniteMoeDecoderLayer(LlamaDecoderLayer):
+    def _build_mlp(self, cfg):
+        return None
+
+    def __init__(self, cfg: DecoderConfig, layer_idx: int):
+        super().__init__(cfg, layer_idx)
+        self.block_sparse_moe = GraniteMoeMoE(cfg)
+
+    def forward(self, x, pos, cos_t, sin_t, cu_seqlens):
+        rm = self.cfg.residual_multiplier
+        x = x + rm * self.self_attn(self.input_layernorm(x), pos, cos_t, sin_t, cu_seqlens)
+        moe_out, _ = self.block_sparse_moe(self.post_attention_layernorm(x))
+        return x + rm * moe_out
+
+
+class GraniteMoeModel(LlamaModel):
+    layer_cls = GraniteMoeDecoderLayer
+
+
+class GraniteMoeForCausalLM(LlamaForCausalLM):
+    model_cls = GraniteMoeModel

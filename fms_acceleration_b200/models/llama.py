@@ -108,7 +108,9 @@ class LlamaDecoderLayer(nn.Module):
         self.cfg = cfg
         self.layer_idx = layer_idx
         self.self_attn = LlamaAttention(cfg, layer_idx)
-        self.mlp = self._build_mlp(cfg)
+        mlp = self._build_mlp(cfg)
+        if mlp is not None:
+            self.mlp = mlp
         self.input_layernorm = LlamaRMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
         self.post_attention_layernorm = LlamaRMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
         self._fused_specs = None
@@ -133,7 +135,7 @@ class LlamaDecoderLayer(nn.Module):
             attn = AttentionBlockSpec(self.input_layernorm, a.q_proj, a.k_proj, a.v_proj, a.o_proj, a.num_heads,
                                       a.num_kv_heads, a.head_dim, tag, a.scaling, self.cfg.residual_multiplier)
             mlp = None
-            if isinstance(self.mlp, LlamaMLP):
+            if isinstance(getattr(self, "mlp", None), LlamaMLP):
                 m = self.mlp
                 mlp = MLPBlockSpec(self.post_attention_layernorm, m.gate_proj, m.up_proj, m.down_proj, m.hidden_act,
                                    tag, self.cfg.residual_multiplier)
@@ -148,7 +150,8 @@ class LlamaDecoderLayer(nn.Module):
         if mlp is not None:
             return mlp_block(h, mlp)
         y = RN.rmsnorm(h, self.post_attention_layernorm.weight, self.post_attention_layernorm.variance_epsilon)
-        out = self.mlp(y)
+        ffn = self.mlp if hasattr(self, "mlp") else self.block_sparse_moe
+        out = ffn(y)
         if isinstance(out, tuple):
             out = out[0]
         return torch.add(h, out, alpha=self.cfg.residual_multiplier)

@@ -184,7 +184,10 @@ class ShardedEngine:
 
     # ------------------------------------------------------------------ gradients of replicated parameters
     def _setup_grad_bucket(self, grad_dtype: Optional[torch.dtype]) -> None:
-        self.params = [p for p in self.model.parameters() if p.requires_grad]
+        # expert-parallel parameters are not replicated over the whole world: they are reduced separately
+        self.ep_params = [p for p in self.model.parameters() if p.requires_grad and getattr(p, "_fmsb_expert_parallel", False)]
+        self.params = [p for p in self.model.parameters()
+                       if p.requires_grad and not getattr(p, "_fmsb_expert_parallel", False)]
         self.bucket = None
         if not self.params:
             return
@@ -214,6 +217,10 @@ class ShardedEngine:
                 dist.broadcast(p.data, src=dist.get_global_rank(self.group, 0), group=self.group)
 
     def zero_grad(self) -> None:
+        for p in self.ep_params:
+            p.grad = None
+        if not self.params:
+            return
         self.flat_grads.zero_()
         for p, v in zip(self.params, self._grad_views):
             if p.dtype == self.grad_dtype:
@@ -223,6 +230,15 @@ class ShardedEngine:
 
     def reduce_gradients(self) -> None:
         """Average the gradients of all replicated trainable parameters across the group (one kernel)."""
+        # Experts under expert parallelism: the owner already holds the sum over all source ranks of its
+        # expert-parallel group; the global mean needs 1/world and a sum over the replicate dimension.
+        for p in self.ep_params:
+            if p.grad is None:
+                continue
+            p.grad.mul_(1.0 / self.world)
+            rep = getattr(p, "_fmsb_replicate_group", None)
+            if rep is not None and dist.get_world_size(rep) > 1:
+                dist.all_reduce(p.grad, group=rep)
         if not self.params:
             return
         for p, v in zip(self.params, self._grad_views):

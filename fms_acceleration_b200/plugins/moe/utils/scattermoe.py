@@ -1,0 +1,111 @@
+"""``ScatterMoE`` module: drop-in replacement of a Hugging Face sparse-MoE block.
+
+Parameter names and layout follow the reference (fms_acceleration_moe/utils/scattermoe.py:44-491): ``router``
+(``nn.Linear``, weight ``[E, H]``), ``w1`` / ``w3`` (``ScatteredExperts`` with ``weight [E, H, I]``) and ``w2``
+(``weight [E, I, H]``); ``forward`` returns ``(hidden_states, router_logits)``.  With expert parallelism a rank
+holds the ``E / ep`` experts ``[rank * E/ep, (rank + 1) * E/ep)``.  Execution is
+:mod:`fms_acceleration_b200.ops.moe` (device-side plan, peer-memory dispatch / combine, grouped tcgen05 GEMMs).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from ....ops import moe as MOE
+
+
+class ScatteredExperts(nn.Module):
+    def __init__(self, in_features: int, out_features: int, num_experts: int, fan_out: int = 1, grouped_in: bool = False,
+                 grouped_out: bool = False, dtype=torch.bfloat16, device=None, lora_config=None):
+        super().__init__()
+        self.weight = nn.Parameter(torch.empty(num_experts, in_features, out_features, dtype=dtype, device=device))
+        self.in_features, self.out_features, self.num_experts = in_features, out_features, num_experts
+        self.fan_out, self.grouped_in, self.grouped_out = fan_out, grouped_in, grouped_out
+        self.lora_A = self.lora_B = None
+        self.lora_r = 0
+        if lora_config is not None:
+            r = lora_config.r
+            self.lora_r = r
+            self.weight.requires_grad_(False)
+            self.lora_A = nn.Parameter(torch.zeros(num_experts, in_features, r, dtype=dtype, device=device))
+            self.lora_B = nn.Parameter(torch.empty(num_experts, r, out_features, dtype=dtype, device=device))
+            nn.init.normal_(self.lora_B)
+
+    def effective_weight(self) -> torch.Tensor:
+        """Dense expert weights including the LoRA update (scale 1, as in the reference's kernels)."""
+        if self.lora_A is None:
+            return self.weight
+        return self.weight + torch.bmm(self.lora_A, self.lora_B)
+
+    def forward(self, x, *args, **kwargs):  # pragma: no cover - experts are driven by ScatterMoE.forward
+        raise RuntimeError("ScatteredExperts is executed through its parent ScatterMoE module")
+
+
+class ScatterMoE(nn.Module):
+    def __init__(self, hidden_size: int, hidden_act: str, intermediate_size: int, num_experts: int,
+                 has_bias: bool = False, mlp_arch: Optional[str] = None, top_k: int = 2, dtype=torch.bfloat16,
+                 device=None, ep_device_mesh=None, ep_group=None, lora_config=None):
+        super().__init__()
+        assert not has_bias, "ScatterMoE does not support bias"
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.num_experts, self.top_k = num_experts, top_k
+        self.activation = hidden_act
+        if ep_device_mesh is not None and ep_group is None:
+            ep_group = ep_device_mesh.get_group(0) if hasattr(ep_device_mesh, "get_group") else None
+        self.ep_group = ep_group
+        self.expert_parallel = ep_group is not None
+        self.ep_size = torch.distributed.get_world_size(ep_group) if self.expert_parallel else 1
+        assert num_experts % self.ep_size == 0, "the expert-parallel degree must divide the number of experts"
+        self.num_experts_per_device = num_experts // self.ep_size
+        self.router = nn.Linear(hidden_size, num_experts, bias=False, dtype=dtype, device=device)
+        El = self.num_experts_per_device
+        self.w1 = ScatteredExperts(hidden_size, intermediate_size, El, top_k, dtype=dtype, device=device, lora_config=lora_config)
+        self.w2 = ScatteredExperts(intermediate_size, hidden_size, El, 1, dtype=dtype, device=device, lora_config=lora_config)
+        self.w3 = ScatteredExperts(hidden_size, intermediate_size, El, top_k, dtype=dtype, device=device, lora_config=lora_config)
+        self._ctx: Optional[MOE.MoEContext] = None
+
+    def _context(self) -> MOE.MoEContext:
+        if self._ctx is None:
+            self._ctx = MOE.MoEContext(self.hidden_size, self.intermediate_size, self.num_experts, self.top_k,
+                                       group=self.ep_group)
+        return self._ctx
+
+    def _compute_routing_weights(self, x2: torch.Tensor):
+        if x2.is_cuda and x2.dtype in (torch.bfloat16, torch.float16):
+            from ....models.llama import _DenseLinear
+
+            logits = _DenseLinear.apply(x2, self.router.weight)
+        else:
+            logits = self.router(x2)
+        w, idx = MOE.router_topk(logits, self.top_k, renorm=True)
+        return logits, w, idx
+
+    def forward(self, hidden_states: torch.Tensor):
+        shape = hidden_states.shape
+        x2 = hidden_states.reshape(-1, shape[-1])
+        if x2.stride(1) != 1 or x2.stride(0) % 8:
+            x2 = x2.contiguous()
+        logits, w, idx = self._compute_routing_weights(x2)
+        if x2.is_cuda and x2.dtype in (torch.bfloat16, torch.float16):
+            out = MOE.experts_forward(x2, w, idx, self.w1.effective_weight(), self.w3.effective_weight(),
+                                      self.w2.effective_weight(), self._context(), self.activation)
+        else:
+            assert not self.expert_parallel, "the CPU oracle path has no expert parallelism"
+            out = self._forward_reference(x2, w, idx)
+        return out.view(shape), logits
+
+    def _forward_reference(self, x2, w, idx):
+        out = torch.zeros_like(x2, dtype=torch.float32)
+        w1, w2, w3 = (m.effective_weight().float() for m in (self.w1, self.w2, self.w3))
+        act = {"silu": F.silu, "gelu": F.gelu}.get(self.activation, F.silu)
+        xf = x2.float()
+        for e in range(self.num_experts):
+            tok, slot = torch.nonzero(idx == e, as_tuple=True)
+            if tok.numel() == 0:
+                continue
+            h = act(xf[tok] @ w1[e]) * (xf[tok] @ w3[e])
+            out.index_add_(0, tok, (h @ w2[e]) * w[tok, slot][:, None].float())
+        return out.to(x2.dtype)
