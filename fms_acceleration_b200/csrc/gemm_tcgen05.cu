@@ -49,6 +49,12 @@ struct GemmParams {
   const int* seg_off;        // [n_groups + 1] segment starts in rows, multiples of 128 (device memory)
   int b_group_rows;          // rows of B that belong to one group
   long long d_group_stride;  // elements between the D matrices of consecutive groups (mode 2)
+  // mode 3: uniform batch indexed by (outer o, inner i), i < n_inner.  Operand offsets in elements of the
+  // stored 2-D matrices: rows += o * x_ro + i * x_ri, columns += (i / x_div) * x_ci.
+  int n_batch, n_inner;
+  int a_ro, a_ri, a_ci, a_div;
+  int b_ro, b_ri, b_ci, b_div;
+  int d_ro, d_ri, d_ci;
 };
 
 struct TileInfo {
@@ -59,6 +65,8 @@ struct TileInfo {
   int kblocks1;      // 64-wide blocks of operand pair 1 for this tile
   int b_row_off;     // added to B's row coordinate (group offset)
   long long d_off;   // element offset of this tile's D matrix
+  int a_r, a_c, b_r, b_c;  // batch offsets (mode 3): rows / columns of the stored A and B
+  int d_c;                 // column offset of D (mode 3)
 };
 
 template <int BN>
@@ -86,6 +94,28 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 template <int BN>
 __device__ __forceinline__ bool get_tile(int t, const GemmParams& p, TileInfo& ti) {
   const int tiles_n = (p.N + BN - 1) / BN;
+  ti.a_r = ti.a_c = ti.b_r = ti.b_c = ti.d_c = 0;
+  if (p.mode == 3) {
+    const int tiles_m = (p.M + BM - 1) / BM;
+    const int per = tiles_m * tiles_n;
+    if (t >= per * p.n_batch) return false;
+    const int b = t / per, r = t - b * per;
+    const int o = b / p.n_inner, i = b - o * p.n_inner;
+    ti.m0 = (r % tiles_m) * BM;
+    ti.n0 = (r / tiles_m) * BN;
+    ti.a_r = o * p.a_ro + i * p.a_ri;
+    ti.a_c = (i / p.a_div) * p.a_ci;
+    ti.b_r = o * p.b_ro + i * p.b_ri;
+    ti.b_c = (i / p.b_div) * p.b_ci;
+    ti.m_store = ti.m0 + o * p.d_ro + i * p.d_ri;
+    ti.m_end = ti.m_store - ti.m0 + p.M;
+    ti.d_c = i * p.d_ci;
+    ti.k_begin = 0;
+    ti.kblocks1 = p.kblocks1;
+    ti.b_row_off = 0;
+    ti.d_off = 0;
+    return true;
+  }
   if (p.mode == 0) {
     const int tiles_m = (p.M + BM - 1) / BM;
     if (t >= tiles_m * tiles_n) return false;
@@ -214,19 +244,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_const
           const int k0 = second ? (kb - ti.kblocks1) * BK : ti.k_begin + kb * BK;
           // the group offset applies to B's row coordinate: the k rows of an MN-major B, the n rows of a K-major B
           const int brow = second ? 0 : ti.b_row_off;
+          // stored A: [M, K] (K-major) or [K, M] (MN-major); the batch offsets address rows / columns of the storage
           if (A_MN == 0) {
-            tma_load_2d(sA(stage), ta, full_bar(stage), k0, m0);
+            tma_load_2d(sA(stage), ta, full_bar(stage), k0 + ti.a_c, m0 + ti.a_r);
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)
-              tma_load_2d(sA(stage) + j * 8192, ta, full_bar(stage), m0 + 64 * j, k0);
+              tma_load_2d(sA(stage) + j * 8192, ta, full_bar(stage), m0 + 64 * j + ti.a_c, k0 + ti.a_r);
           }
           if (B_MN == 0) {
-            tma_load_2d(sB(stage), tb, full_bar(stage), k0, n0 + brow);
+            tma_load_2d(sB(stage), tb, full_bar(stage), k0 + ti.b_c, n0 + brow + ti.b_r);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(sB(stage) + j * 8192, tb, full_bar(stage), n0 + 64 * j, k0 + brow);
+              tma_load_2d(sB(stage) + j * 8192, tb, full_bar(stage), n0 + 64 * j + ti.b_c, k0 + brow + ti.b_r);
           }
           if (++stage == Cfg::kStages) {
             stage = 0;
@@ -317,7 +348,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_const
           for (int i = 0; i < CH; ++i) v[i] *= p.alpha;
           if (p.C != nullptr && p.beta != 0.f) {
             if (p.fmt == 1) {
-              const __nv_bfloat16* crow = reinterpret_cast<const __nv_bfloat16*>(p.C) + ti.d_off + (long long)gm * p.ldc + gn;
+              const __nv_bfloat16* crow = reinterpret_cast<const __nv_bfloat16*>(p.C) + ti.d_off + (long long)gm * p.ldc + gn + ti.d_c;
               if (full && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
 #pragma unroll
                 for (int i = 0; i < CH; i += 8) {
@@ -335,13 +366,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_const
                   if (gn + i < p.N) v[i] += p.beta * __bfloat162float(crow[i]);
               }
             } else {
-              const __half* crow = reinterpret_cast<const __half*>(p.C) + ti.d_off + (long long)gm * p.ldc + gn;
+              const __half* crow = reinterpret_cast<const __half*>(p.C) + ti.d_off + (long long)gm * p.ldc + gn + ti.d_c;
               for (int i = 0; i < CH; ++i)
                 if (gn + i < p.N) v[i] += p.beta * __half2float(crow[i]);
             }
           }
           if (p.d_fp32) {
-            float* drow = reinterpret_cast<float*>(p.D) + ti.d_off + (long long)gm * p.ldd + gn;
+            float* drow = reinterpret_cast<float*>(p.D) + ti.d_off + (long long)gm * p.ldd + gn + ti.d_c;
             if (full && ((reinterpret_cast<uintptr_t>(drow) & 15) == 0)) {
 #pragma unroll
               for (int i = 0; i < CH; i += 4)
@@ -351,7 +382,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_const
                 if (gn + i < p.N) drow[i] = v[i];
             }
           } else {
-            uint16_t* drow = reinterpret_cast<uint16_t*>(p.D) + ti.d_off + (long long)gm * p.ldd + gn;
+            uint16_t* drow = reinterpret_cast<uint16_t*>(p.D) + ti.d_off + (long long)gm * p.ldd + gn + ti.d_c;
             if (full && ((reinterpret_cast<uintptr_t>(drow) & 15) == 0)) {
 #pragma unroll
               for (int i = 0; i < CH; i += 8) {
@@ -475,13 +506,21 @@ int launch_gemm(const CUtensorMap& a1, const CUtensorMap& b1, const CUtensorMap&
 // Constraints: leading dimensions multiples of 8 elements; base pointers 16-byte aligned.  bn selects the N tile (16/32/64/128/256); MN-major B needs bn >= 64.
 // max_ctas > 0 limits the grid (used to leave SMs to a concurrent communication kernel).
 // Returns 0 or a CUDA / encode error code.  Time-outs are reported through *status.
+struct BatchDesc {
+  int n_batch = 0, n_inner = 1;
+  int a_ro = 0, a_ri = 0, a_ci = 0, a_div = 1;
+  int b_ro = 0, b_ri = 0, b_ci = 0, b_div = 1;
+  int d_ro = 0, d_ri = 0, d_ci = 0;
+  long long a_cols = 0, b_cols = 0;  // column extents of the stored matrices (tensor-map bounds)
+};
+
 static int gemm_impl(const void* A1, long long lda1, const void* B1, long long ldb1, int K1,  //
                      const void* A2, long long lda2, const void* B2, long long ldb2, int K2,  //
                      int a_mn, int b_mn,                                                       //
                      void* D, long long ldd, int d_fp32, const void* C, long long ldc,        //
                      float alpha, float beta, int M, int N, int fmt, int bn, int max_ctas, int* status,
                      cudaStream_t stream, int mode, int n_groups, const int* seg_off, int b_group_rows,
-                     long long d_group_stride, long long a_rows, long long b_rows) {
+                     long long d_group_stride, long long a_rows, long long b_rows, const BatchDesc* bd = nullptr) {
   using namespace fmsb_host;
   if (M <= 0 || N <= 0) return 0;
   if (K1 <= 0 || K2 < 0) return -2;
@@ -491,13 +530,14 @@ static int gemm_impl(const void* A1, long long lda1, const void* B1, long long l
   int rc;
   // a_rows / b_rows: number of rows of the stored A / B matrices when it differs from the per-tile view
   // (grouped modes address several segments / expert matrices through one tensor map)
+  const long long a_cols = bd && bd->a_cols > 0 ? bd->a_cols : 0, b_cols = bd && bd->b_cols > 0 ? bd->b_cols : 0;
   auto mk_a = [&](CUtensorMap* t, const void* A, long long lda, int K) {
-    if (a_mn) return make_tmap_2d_16b(t, A, a_rows > 0 ? a_rows : K, M, lda, 64, 64);
-    return make_tmap_2d_16b(t, A, a_rows > 0 ? a_rows : M, K, lda, fmsb::BM, 64);
+    if (a_mn) return make_tmap_2d_16b(t, A, a_rows > 0 ? a_rows : K, a_cols > 0 ? a_cols : M, lda, 64, 64);
+    return make_tmap_2d_16b(t, A, a_rows > 0 ? a_rows : M, a_cols > 0 ? a_cols : K, lda, fmsb::BM, 64);
   };
   auto mk_b = [&](CUtensorMap* t, const void* B, long long ldb, int K) {
-    if (b_mn) return make_tmap_2d_16b(t, B, b_rows > 0 ? b_rows : K, N, ldb, 64, 64);
-    return make_tmap_2d_16b(t, B, b_rows > 0 ? b_rows : N, K, ldb, bn, 64);
+    if (b_mn) return make_tmap_2d_16b(t, B, b_rows > 0 ? b_rows : K, b_cols > 0 ? b_cols : N, ldb, 64, 64);
+    return make_tmap_2d_16b(t, B, b_rows > 0 ? b_rows : N, b_cols > 0 ? b_cols : K, ldb, bn, 64);
   };
   if ((rc = mk_a(&ta1, A1, lda1, K1))) return rc;
   if ((rc = mk_b(&tb1, B1, ldb1, K1))) return rc;
@@ -527,6 +567,14 @@ static int gemm_impl(const void* A1, long long lda1, const void* B1, long long l
   p.seg_off = seg_off;
   p.b_group_rows = b_group_rows;
   p.d_group_stride = d_group_stride;
+  p.n_batch = 0; p.n_inner = 1; p.a_div = p.b_div = 1;
+  p.a_ro = p.a_ri = p.a_ci = p.b_ro = p.b_ri = p.b_ci = p.d_ro = p.d_ri = p.d_ci = 0;
+  if (bd != nullptr) {
+    p.n_batch = bd->n_batch; p.n_inner = bd->n_inner > 0 ? bd->n_inner : 1;
+    p.a_ro = bd->a_ro; p.a_ri = bd->a_ri; p.a_ci = bd->a_ci; p.a_div = bd->a_div > 0 ? bd->a_div : 1;
+    p.b_ro = bd->b_ro; p.b_ri = bd->b_ri; p.b_ci = bd->b_ci; p.b_div = bd->b_div > 0 ? bd->b_div : 1;
+    p.d_ro = bd->d_ro; p.d_ri = bd->d_ri; p.d_ci = bd->d_ci;
+  }
 
 #define FMSB_DISPATCH(BNV)                                                                          \
   if (bn == BNV) {                                                                                  \
@@ -578,4 +626,24 @@ extern "C" int fmsb_grouped_gemm(const void* A, long long lda, const void* B, lo
                      fmt, bn, 0, status, stream, 2, n_groups, seg_off, 0, d_group_stride, a_rows, b_rows);
   }
   return -2;
+}
+
+// Uniform batched GEMM: for batch index (o, i), i < n_inner:  D_oi[M, N] = alpha * A_oi . B_oi^T (+ beta * C_oi),
+// where the operands are windows of stored 2-D matrices.  desc = 13 ints:
+//   {n_batch, n_inner, a_ro, a_ri, a_ci, a_div, b_ro, b_ri, b_ci, b_div, d_ro, d_ri, d_ci}
+// rows += o * x_ro + i * x_ri and columns += (i / x_div) * x_ci of the STORED matrix (for an MN-major operand the
+// stored rows are the contraction index).  a_rows/a_cols, b_rows/b_cols: extents of the stored matrices.
+extern "C" int fmsb_batched_gemm(const void* A, long long lda, long long a_rows, long long a_cols, const void* B,
+                                 long long ldb, long long b_rows, long long b_cols, int K, int a_mn, int b_mn, void* D,
+                                 long long ldd, int d_fp32, const void* C, long long ldc, float alpha, float beta, int M,
+                                 int N, int fmt, int bn, const int* desc, int* status, cudaStream_t stream) {
+  BatchDesc bd;
+  bd.n_batch = desc[0]; bd.n_inner = desc[1];
+  bd.a_ro = desc[2]; bd.a_ri = desc[3]; bd.a_ci = desc[4]; bd.a_div = desc[5];
+  bd.b_ro = desc[6]; bd.b_ri = desc[7]; bd.b_ci = desc[8]; bd.b_div = desc[9];
+  bd.d_ro = desc[10]; bd.d_ri = desc[11]; bd.d_ci = desc[12];
+  bd.a_cols = a_cols; bd.b_cols = b_cols;
+  if (bd.n_batch <= 0) return 0;
+  return gemm_impl(A, lda, B, ldb, K, nullptr, 0, nullptr, 0, 0, a_mn, b_mn, D, ldd, d_fp32, C, ldc, alpha, beta, M, N,
+                   fmt, bn, 0, status, stream, 3, 0, nullptr, 0, 0, a_rows, b_rows, &bd);
 }

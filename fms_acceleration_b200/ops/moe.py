@@ -30,12 +30,17 @@ N.declare("fmsb_moe_gate_grad", [P, L, P, P, P, L, L, I, I, I, P, I, I, P])
 
 
 # ------------------------------------------------------------------------------------------------ oracle
-def moe_ref(x, router_w, w1, w2, w3, top_k, act="silu", renorm=True):
-    """Dense fp32 oracle.  x [T,H]; router_w [E,H]; w1,w3 [E,H,I]; w2 [E,I,H]."""
+def moe_ref(x, router_w, w1, w2, w3, top_k, act="silu", renorm=True, idx=None):
+    """Dense fp32 oracle.  x [T,H]; router_w [E,H]; w1,w3 [E,H,I]; w2 [E,I,H].  ``idx`` ([T,k]) fixes the routing
+    decisions (near-ties may otherwise be broken differently by a lower-precision router)."""
     xf = x.float()
     logits = xf @ router_w.float().t()
     probs = torch.softmax(logits, dim=-1)
-    w, idx = torch.topk(probs, top_k, dim=-1)
+    if idx is None:
+        w, idx = torch.topk(probs, top_k, dim=-1)
+    else:
+        idx = idx.long()
+        w = torch.gather(probs, 1, idx)
     if renorm:
         w = w / w.sum(-1, keepdim=True)
     out = torch.zeros_like(xf)

@@ -24,12 +24,13 @@ def check_moe(dev, rank, world):
     for it in range(2):  # twice: buffers and epochs are reused
         x.grad = None
         moe.zero_grad()
-        out, _ = moe(x)
+        out, logits = moe(x)
         out.backward(g)
     NV.check_status()
+    _, kidx = MOE.router_topk(logits.detach(), k)
     xf = x.detach().float().requires_grad_()
     ws = {n: v.bfloat16().float().requires_grad_() for n, v in full.items()}
-    ref, _ = MOE.moe_ref(xf, ws["router"], ws["w1"], ws["w2"], ws["w3"], k)
+    ref, _ = MOE.moe_ref(xf, ws["router"], ws["w1"], ws["w2"], ws["w3"], k, idx=kidx)
     ref.backward(g.float())
 
     def rel(a, b):

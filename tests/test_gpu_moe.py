@@ -50,13 +50,14 @@ def test_scattermoe_matches_dense_oracle(T, H, I, E, k):
     x = (torch.randn(T, H, device=DEV) * 0.5).bfloat16().requires_grad_()
     out, logits = moe(x)
     NV.check_status()
+    _, kidx = MOE.router_topk(logits.detach(), k)
     g = torch.randn_like(out)
     out.backward(g)
     NV.check_status()
     # oracle (fp32, dense loop over experts) with the same routing decisions
     xf = x.detach().float().requires_grad_()
     ws = [p.detach().float().requires_grad_() for p in (moe.router.weight, moe.w1.weight, moe.w2.weight, moe.w3.weight)]
-    ref, _ = MOE.moe_ref(xf, ws[0], ws[1], ws[2], ws[3], k)
+    ref, _ = MOE.moe_ref(xf, ws[0], ws[1], ws[2], ws[3], k, idx=kidx)
     ref.backward(g.float())
     assert _rel(out, ref) < 2e-2
     assert _rel(x.grad, xf.grad) < 3e-2
