@@ -15,6 +15,13 @@ from __future__ import annotations
 import torch
 
 from .. import _native as N
+from .. import _native as N_
+import ctypes as _ct
+
+N.declare("fmsb_batched_gemm", [_ct.c_void_p, _ct.c_longlong, _ct.c_longlong, _ct.c_longlong, _ct.c_void_p, _ct.c_longlong,
+                                 _ct.c_longlong, _ct.c_longlong, _ct.c_int, _ct.c_int, _ct.c_int, _ct.c_void_p, _ct.c_longlong,
+                                 _ct.c_int, _ct.c_void_p, _ct.c_longlong, _ct.c_float, _ct.c_float, _ct.c_int, _ct.c_int,
+                                 _ct.c_int, _ct.c_int, _ct.c_void_p, _ct.c_void_p, _ct.c_void_p])
 
 
 def _pick_bn(n: int, b_mn: bool) -> int:
@@ -105,3 +112,28 @@ def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     lead = x.shape[:-1]
     y = gemm(x.reshape(-1, x.shape[-1]), w)
     return y.reshape(*lead, w.shape[0])
+
+
+def batched_gemm(a, b, *, M, N, K, n_batch, n_inner=1, a_off=(0, 0, 0, 1), b_off=(0, 0, 0, 1), d_off=(0, 0, 0),
+                 a_mn=False, b_mn=False, out=None, out_rows=None, out_cols=None, out_dtype=None, bn=None):
+    """Uniform batched GEMM over windows of stored 2-D matrices (``fmsb_batched_gemm``).
+
+    Batch index ``(o, i)`` with ``i < n_inner``; ``x_off = (row step per o, row step per i, column step per i,
+    divisor applied to i for the column step)`` addresses the STORED matrix (for an MN-major operand its rows are the
+    contraction index); ``d_off = (row step per o, row step per i, column step per i)``.
+    """
+    import ctypes
+
+    if out is None:
+        out = torch.empty(out_rows, out_cols, dtype=out_dtype or a.dtype, device=a.device)
+    if bn is None:
+        bn = _pick_bn(N, b_mn)
+    desc = (ctypes.c_int * 13)(n_batch, n_inner, a_off[0], a_off[1], a_off[2], a_off[3], b_off[0], b_off[1], b_off[2],
+                               b_off[3], d_off[0], d_off[1], d_off[2])
+    st = N_.status_word(a.device)
+    rc = N_.lib().fmsb_batched_gemm(a.data_ptr(), a.stride(0), a.shape[0], a.shape[1], b.data_ptr(), b.stride(0),
+                                    b.shape[0], b.shape[1], K, int(a_mn), int(b_mn), out.data_ptr(), out.stride(0),
+                                    int(out.dtype == torch.float32), None, 0, 1.0, 0.0, M, N, N_.dtype_code(a.dtype), bn,
+                                    desc, st.data_ptr(), N_.stream_ptr())
+    N_.check(rc, "fmsb_batched_gemm")
+    return out

@@ -1,0 +1,265 @@
+"""Mamba2 operators: causal conv1d + SiLU and the chunked state-space-duality (SSD) scan, forward and backward.
+
+GEMM-shaped work (C.B^T, G.X, chunk states, inter-chunk outputs and all their gradients) runs as uniform batched
+tcgen05 GEMMs (``fmsb_batched_gemm``); the recurrence over chunks, the conv and the decay/mask construction are
+CUDA kernels in ``csrc/mamba.cu``; the remaining element-wise glue is PyTorch.  The scan takes an initial state and
+returns the final state, which is the hook context parallelism uses (``parallel/context_parallel.py``).
+
+Layouts: x [T, nh, P]; dt [T, nh] (after softplus, fp32); A [nh] (negative); B, C [T, G, N]; D [nh];
+states [nh, P, N] fp32.  T must be a multiple of the chunk size Q.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+import torch.nn.functional as F
+
+from .. import _native as NV
+from .gemm import batched_gemm
+
+P_, I_, L_, F_ = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+NV.declare("fmsb_conv1d_fwd", [P_, L_, P_, P_, P_, P_, P_, L_, P_, I_, I_, I_, I_, P_])
+NV.declare("fmsb_conv1d_bwd", [P_, L_, P_, P_, P_, P_, P_, L_, P_, P_, I_, I_, I_, I_, P_])
+NV.declare("fmsb_ssd_make_g", [P_, P_, P_, P_, I_, I_, I_, I_, I_, P_])
+NV.declare("fmsb_ssd_state_fwd", [P_, P_, P_, P_, P_, I_, I_, I_, I_, P_])
+NV.declare("fmsb_ssd_state_bwd", [P_, P_, P_, P_, P_, P_, P_, I_, I_, I_, I_, P_])
+
+
+# ------------------------------------------------------------------------------------------------ oracles
+def ssd_ref(x, dt, A, B, C, D, h0=None):
+    """Sequential recurrence in fp64 (CPU oracle).  Returns (y [T,nh,P], final state [nh,P,N])."""
+    T, nh, P = x.shape
+    G, N = B.shape[1], B.shape[2]
+    xd, dtd, Ad, Bd, Cd, Dd = (t.double() for t in (x, dt, A, B, C, D))
+    rep = nh // G
+    h = torch.zeros(nh, P, N, dtype=torch.float64, device=x.device) if h0 is None else h0.double().clone()
+    ys = []
+    for t in range(T):
+        Bt = Bd[t].repeat_interleave(rep, 0)
+        Ct = Cd[t].repeat_interleave(rep, 0)
+        h = torch.exp(dtd[t] * Ad)[:, None, None] * h + dtd[t][:, None, None] * xd[t][:, :, None] * Bt[:, None, :]
+        ys.append((h * Ct[:, None, :]).sum(-1) + Dd[:, None] * xd[t])
+    return torch.stack(ys), h
+
+
+def conv1d_ref(x, w, bias, halo=None, seq_start=None):
+    """x [T, C]; w [C, K]; causal depthwise conv + SiLU (fp32 math)."""
+    T, Cc = x.shape
+    K = w.shape[1]
+    xf = x.float()
+    pad = torch.zeros(K - 1, Cc, dtype=torch.float32, device=x.device) if halo is None else halo.float()
+    xp = torch.cat([pad, xf], 0)
+    acc = bias.float()[None, :].expand(T, Cc).clone() if bias is not None else torch.zeros(T, Cc, device=x.device)
+    for j in range(K):
+        col = xp[j: j + T]
+        if seq_start is not None:
+            src = torch.arange(T, device=x.device) - (K - 1) + j
+            col = torch.where((src >= seq_start.long())[:, None], col, torch.zeros_like(col))
+        acc = acc + w.float()[:, j][None, :] * col
+    return F.silu(acc).to(x.dtype)
+
+
+# ------------------------------------------------------------------------------------------------ conv1d
+class _CausalConv1d(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias, halo, seq_start, seq_end):
+        T, Cc = x.shape
+        K = w.shape[1]
+        y = torch.empty(T, Cc, dtype=x.dtype, device=x.device)
+        pre = torch.empty(T, Cc, dtype=x.dtype, device=x.device)
+        wc = w.contiguous()
+        rc = NV.lib().fmsb_conv1d_fwd(x.data_ptr(), x.stride(0), wc.data_ptr(), NV.ptr(bias), NV.ptr(halo),
+                                      NV.ptr(seq_start), y.data_ptr(), y.stride(0), pre.data_ptr(), T, Cc, K,
+                                      NV.dtype_code(x.dtype), NV.stream_ptr())
+        NV.check(rc, "fmsb_conv1d_fwd")
+        ctx.save_for_backward(x, wc, pre, halo, seq_start, seq_end)
+        ctx.has_bias = bias is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, pre, halo, seq_start, seq_end = ctx.saved_tensors
+        T, Cc = x.shape
+        K = w.shape[1]
+        dy = dy if dy.stride(1) == 1 else dy.contiguous()
+        dx = torch.empty(T, Cc, dtype=x.dtype, device=x.device)
+        dpre = torch.empty(T, Cc, dtype=torch.float32, device=x.device)
+        dhalo = torch.empty(K - 1, Cc, dtype=x.dtype, device=x.device) if halo is not None else None
+        rc = NV.lib().fmsb_conv1d_bwd(dy.data_ptr(), dy.stride(0), pre.data_ptr(), w.data_ptr(), NV.ptr(seq_start),
+                                      NV.ptr(seq_end), dx.data_ptr(), dx.stride(0), dpre.data_ptr(), NV.ptr(dhalo), T, Cc,
+                                      K, NV.dtype_code(x.dtype), NV.stream_ptr())
+        NV.check(rc, "fmsb_conv1d_bwd")
+        # tap gradients: dw[c, j] = sum_t dpre[t, c] * xin[t - (K-1) + j, c]
+        pad = halo.float() if halo is not None else torch.zeros(K - 1, Cc, dtype=torch.float32, device=x.device)
+        xp = torch.cat([pad, x.float()], 0)
+        dws = []
+        for j in range(K):
+            col = xp[j: j + T]
+            if seq_start is not None:
+                src = torch.arange(T, device=x.device) - (K - 1) + j
+                col = torch.where((src >= seq_start.long())[:, None], col, torch.zeros_like(col))
+            dws.append((dpre * col).sum(0))
+        dw = torch.stack(dws, 1).to(w.dtype)
+        db = dpre.sum(0).to(w.dtype) if ctx.has_bias else None
+        return dx, dw, db, dhalo, None, None
+
+
+def causal_conv1d(x, w, bias=None, halo=None, seq_start=None, seq_end=None):
+    """Depthwise causal conv (kernel 4) + SiLU on packed rows ``x [T, C]``; ``w [C, K]``."""
+    if not x.is_cuda:
+        return conv1d_ref(x, w, bias, halo, seq_start)
+    return _CausalConv1d.apply(x, w, bias, halo, seq_start, seq_end)
+
+
+# ------------------------------------------------------------------------------------------------ SSD scan
+def _make_g(cb, L, dt, nc, nh, G, Q):
+    g = torch.empty(nc * nh * Q, Q, dtype=cb.dtype, device=cb.device)
+    rc = NV.lib().fmsb_ssd_make_g(cb.data_ptr(), L.data_ptr(), dt.data_ptr(), g.data_ptr(), nc, nh, G, Q,
+                                  NV.dtype_code(cb.dtype), NV.stream_ptr())
+    NV.check(rc, "fmsb_ssd_make_g")
+    return g
+
+
+class _SSDScan(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, dt, A, B, C, D, h0, Q):
+        T, nh, P = x.shape
+        G, N = B.shape[1], B.shape[2]
+        assert T % Q == 0, "sequence length must be a multiple of the chunk size"
+        nc, hpg = T // Q, nh // G
+        dev, dtp = x.device, x.dtype
+        x2 = x.reshape(T, nh * P)
+        B2, C2 = B.reshape(T, G * N), C.reshape(T, G * N)
+        dt = dt.float().contiguous()
+        a = dt * A.float()[None, :]
+        L = a.view(nc, Q, nh).cumsum(1).reshape(T, nh).contiguous()
+        Ltot = L.view(nc, Q, nh)[:, -1, :].contiguous()                     # [nc, nh]
+        # C.B^T per chunk and group
+        cb = batched_gemm(C2, B2, M=Q, N=Q, K=N, n_batch=nc * G, n_inner=G, a_off=(Q, 0, N, 1), b_off=(Q, 0, N, 1),
+                          d_off=(G * Q, Q, 0), out_rows=nc * G * Q, out_cols=Q)
+        g = _make_g(cb, L, dt, nc, nh, G, Q)                                 # [nc*nh*Q, Q]
+        y_intra = batched_gemm(g, x2, M=Q, N=P, K=Q, n_batch=nc * nh, n_inner=nh, a_off=(nh * Q, Q, 0, 1),
+                               b_off=(Q, 0, P, 1), d_off=(Q, 0, P), b_mn=True, out_rows=T, out_cols=nh * P,
+                               out_dtype=torch.float32)
+        # chunk states S[c,h] [P, N] = (x w)^T B,  w = exp(Ltot - L) dt
+        wgt = (torch.exp(Ltot.view(nc, 1, nh) - L.view(nc, Q, nh)) * dt.view(nc, Q, nh)).reshape(T, nh)
+        xw = (x.float() * wgt[:, :, None]).to(dtp).reshape(T, nh * P)
+        S = batched_gemm(xw, B2, M=P, N=N, K=Q, n_batch=nc * nh, n_inner=nh, a_off=(Q, 0, P, 1), b_off=(Q, 0, N, hpg),
+                         d_off=(nh * P, P, 0), a_mn=True, b_mn=True, out_rows=nc * nh * P, out_cols=N,
+                         out_dtype=torch.float32)
+        hprev = torch.empty(nc * nh * P, N, dtype=dtp, device=dev)
+        hT = torch.empty(nh, P, N, dtype=torch.float32, device=dev)
+        h0c = None if h0 is None else h0.float().contiguous()
+        rc = NV.lib().fmsb_ssd_state_fwd(S.data_ptr(), Ltot.data_ptr(), NV.ptr(h0c), hprev.data_ptr(), hT.data_ptr(), nc,
+                                         nh, P * N, NV.dtype_code(dtp), NV.stream_ptr())
+        NV.check(rc, "fmsb_ssd_state_fwd")
+        # inter-chunk: C_t . Hprev[c,h]  (B operand [P rows, N cols], contraction over N)
+        y_inter = batched_gemm(C2, hprev, M=Q, N=P, K=N, n_batch=nc * nh, n_inner=nh, a_off=(Q, 0, N, hpg),
+                               b_off=(nh * P, P, 0, 1), d_off=(Q, 0, P), out_rows=T, out_cols=nh * P,
+                               out_dtype=torch.float32)
+        eL = torch.exp(L)
+        y = y_intra.view(T, nh, P) + eL[:, :, None] * y_inter.view(T, nh, P) + D.float()[None, :, None] * x.float()
+        ctx.save_for_backward(x, dt, A, B, C, D, L, Ltot, cb, hprev, wgt)
+        ctx.meta = (Q, h0 is not None)
+        return y.to(dtp), hT
+
+    @staticmethod
+    def backward(ctx, dy, dhT):
+        x, dt, A, B, C, D, L, Ltot, cb, hprev, wgt = ctx.saved_tensors
+        Q, has_h0 = ctx.meta
+        T, nh, P = x.shape
+        G, N = B.shape[1], B.shape[2]
+        nc, hpg = T // Q, nh // G
+        dev, dtp = x.device, x.dtype
+        x2 = x.reshape(T, nh * P)
+        B2, C2 = B.reshape(T, G * N), C.reshape(T, G * N)
+        dyf = dy.float()
+        dy2 = dy.contiguous().reshape(T, nh * P)
+        eL = torch.exp(L)
+        dD = (dyf * x.float()).sum((0, 2))
+        dx = D.float()[None, :, None] * dyf
+        # ---- inter-chunk term  y += eL * (C . Hprev)
+        dyi = (dyf * eL[:, :, None]).to(dtp).reshape(T, nh * P)
+        y_inter = batched_gemm(C2, hprev, M=Q, N=P, K=N, n_batch=nc * nh, n_inner=nh, a_off=(Q, 0, N, hpg),
+                               b_off=(nh * P, P, 0, 1), d_off=(Q, 0, P), out_rows=T, out_cols=nh * P,
+                               out_dtype=torch.float32)
+        dL = (dyf * y_inter.view(T, nh, P)).sum(-1) * eL
+        # dC_inter[c, g] [Q, N] = dyi[c, heads of g] [Q, hpg*P] . Hprev[c, heads of g] [(h,p), N]
+        dC = batched_gemm(dyi, hprev, M=Q, N=N, K=hpg * P, n_batch=nc * G, n_inner=G, a_off=(Q, 0, hpg * P, 1),
+                          b_off=(nh * P, hpg * P, 0, 1), d_off=(Q, 0, N), b_mn=True, out_rows=T, out_cols=G * N,
+                          out_dtype=torch.float32)
+        # dHprev_direct[c,h] [P, N] = dyi[c,h]^T C[c]
+        dhp = batched_gemm(dyi, C2, M=P, N=N, K=Q, n_batch=nc * nh, n_inner=nh, a_off=(Q, 0, P, 1), b_off=(Q, 0, N, hpg),
+                           d_off=(nh * P, P, 0), a_mn=True, b_mn=True, out_rows=nc * nh * P, out_cols=N,
+                           out_dtype=torch.float32)
+        # ---- recurrence backward
+        dS = torch.empty(nc * nh * P, N, dtype=torch.float32, device=dev)
+        dh0 = torch.empty(nh, P, N, dtype=torch.float32, device=dev) if has_h0 else None
+        dLtot_part = torch.empty(nc, nh, P * N, dtype=torch.float32, device=dev)
+        dhTc = None if dhT is None else dhT.float().contiguous()
+        rc = NV.lib().fmsb_ssd_state_bwd(dhp.data_ptr(), NV.ptr(dhTc), Ltot.data_ptr(), hprev.data_ptr(), dS.data_ptr(),
+                                         NV.ptr(dh0), dLtot_part.data_ptr(), nc, nh, P * N, NV.dtype_code(dtp),
+                                         NV.stream_ptr())
+        NV.check(rc, "fmsb_ssd_state_bwd")
+        dLtot = dLtot_part.sum(-1)                                            # [nc, nh]
+        # ---- chunk state  S = (x w)^T B
+        dS16 = dS.to(dtp)
+        xw = (x.float() * wgt[:, :, None]).to(dtp).reshape(T, nh * P)
+        # dXw[c,h] [Q, P] = B[c] [Q, N] . dS[c,h]^T
+        dxw = batched_gemm(B2, dS16, M=Q, N=P, K=N, n_batch=nc * nh, n_inner=nh, a_off=(Q, 0, N, hpg),
+                           b_off=(nh * P, P, 0, 1), d_off=(Q, 0, P), out_rows=T, out_cols=nh * P,
+                           out_dtype=torch.float32).view(T, nh, P)
+        # dB_state[c, g] [Q, N] = xw[c, heads of g] [Q, hpg*P] . dS[c, heads of g] [(h,p), N]
+        dB = batched_gemm(xw, dS16, M=Q, N=N, K=hpg * P, n_batch=nc * G, n_inner=G, a_off=(Q, 0, hpg * P, 1),
+                          b_off=(nh * P, hpg * P, 0, 1), d_off=(Q, 0, N), b_mn=True, out_rows=T, out_cols=G * N,
+                          out_dtype=torch.float32)
+        dx = dx + dxw * wgt[:, :, None]
+        dw = (dxw * x.float()).sum(-1)                                        # [T, nh]
+        dww = dw * wgt
+        dLtot = dLtot + dww.view(nc, Q, nh).sum(1)
+        dL = dL - dww
+        ddt = dww / dt
+        # ---- intra-chunk term  y += G X,  G = CB o exp(L_t - L_s) dt_s (s <= t)
+        g = _make_g(cb, L, dt, nc, nh, G, Q)
+        dx_intra = batched_gemm(g, dy2, M=Q, N=P, K=Q, n_batch=nc * nh, n_inner=nh, a_off=(nh * Q, Q, 0, 1),
+                                b_off=(Q, 0, P, 1), d_off=(Q, 0, P), a_mn=True, b_mn=True, out_rows=T, out_cols=nh * P,
+                                out_dtype=torch.float32)
+        dx = dx + dx_intra.view(T, nh, P)
+        dG = batched_gemm(dy2, x2, M=Q, N=Q, K=P, n_batch=nc * nh, n_inner=nh, a_off=(Q, 0, P, 1), b_off=(Q, 0, P, 1),
+                          d_off=(nh * Q, Q, 0), out_rows=nc * nh * Q, out_cols=Q, out_dtype=torch.float32)
+        Wm = dG.view(nc, nh, Q, Q) * g.view(nc, nh, Q, Q).float()            # dG o G
+        row = Wm.sum(-1)                                                      # [nc, nh, Q] indexed by t
+        col = Wm.sum(-2)                                                      # indexed by s
+        dL = dL + (row - col).permute(0, 2, 1).reshape(T, nh)
+        ddt = ddt + col.permute(0, 2, 1).reshape(T, nh) / dt
+        # dCB[c, g] = sum_{h in g} dG o exp(L_t - L_s) dt_s mask  =  sum_h (dG o G) / CB   (avoid the division: rebuild)
+        Lc = L.view(nc, Q, nh).permute(0, 2, 1)                               # [nc, nh, Q]
+        dtc = dt.view(nc, Q, nh).permute(0, 2, 1)
+        decay = torch.exp(Lc[..., :, None] - Lc[..., None, :]) * dtc[..., None, :]
+        mask = torch.tril(torch.ones(Q, Q, dtype=torch.bool, device=dev))
+        dcb = (dG.view(nc, nh, Q, Q) * decay.masked_fill(~mask, 0.0)).view(nc, G, hpg, Q, Q).sum(2)
+        dcb16 = dcb.to(dtp).reshape(nc * G * Q, Q)
+        dC = dC + batched_gemm(dcb16, B2, M=Q, N=N, K=Q, n_batch=nc * G, n_inner=G, a_off=(G * Q, Q, 0, 1),
+                               b_off=(Q, 0, N, 1), d_off=(Q, 0, N), b_mn=True, out_rows=T, out_cols=G * N,
+                               out_dtype=torch.float32)
+        dB = dB + batched_gemm(dcb16, C2, M=Q, N=N, K=Q, n_batch=nc * G, n_inner=G, a_off=(G * Q, Q, 0, 1),
+                               b_off=(Q, 0, N, 1), d_off=(Q, 0, N), a_mn=True, b_mn=True, out_rows=T, out_cols=G * N,
+                               out_dtype=torch.float32)
+        # ---- through L = cumsum(dt A) within the chunk, Ltot = L[last]
+        dLc = dL.view(nc, Q, nh).clone()
+        dLc[:, -1, :] += dLtot
+        da = torch.flip(torch.cumsum(torch.flip(dLc, [1]), 1), [1]).reshape(T, nh)
+        ddt = ddt + da * A.float()[None, :]
+        dA = (da * dt).sum(0)
+        return (dx.to(dtp), ddt.to(dt.dtype), dA.to(A.dtype), dB.view(T, G, N).to(B.dtype), dC.view(T, G, N).to(C.dtype),
+                dD.to(D.dtype), dh0, None)
+
+
+def ssd_scan(x, dt, A, B, C, D, h0=None, chunk_size=256):
+    """Chunked SSD scan.  Returns ``(y [T, nh, P], final_state [nh, P, N] fp32)``."""
+    if not x.is_cuda:
+        y, h = ssd_ref(x, dt, A, B, C, D, h0)
+        return y.to(x.dtype), h.float()
+    return _SSDScan.apply(x, dt, A, B, C, D, h0, chunk_size)

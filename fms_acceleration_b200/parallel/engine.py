@@ -86,7 +86,8 @@ class _BackwardTrigger(torch.autograd.Function):
 
 class ShardedEngine:
     def __init__(self, model: nn.Module, group: Optional[dist.ProcessGroup] = None, shard_frozen: bool = True,
-                 shard_optimizer: bool = False, grad_dtype: Optional[torch.dtype] = None):
+                 shard_optimizer: bool = False, grad_dtype: Optional[torch.dtype] = None,
+                 grad_scale: Optional[float] = None):
         self.model = model
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
@@ -95,6 +96,7 @@ class ShardedEngine:
         self.comm = Communicator(self.group, self.device)
         self.comm_stream = torch.cuda.Stream(self.device)
         self.shard_optimizer = shard_optimizer
+        self.grad_scale = grad_scale  # None: average (1/world); 1.0: plain sum (context parallelism)
         self.layers = self._find_layers(model)
         self.blobs: List[_LayerBlob] = []
         self.arena: Optional[SymmBuffer] = None
@@ -246,7 +248,7 @@ class ShardedEngine:
                 v.copy_(p.grad)
                 p.grad = v if p.dtype == self.grad_dtype else p.grad
         if self.world > 1:
-            self.comm.allreduce_(self.bucket, self.bucket_numel, self.grad_dtype)
+            self.comm.allreduce_(self.bucket, self.bucket_numel, self.grad_dtype, scale=self.grad_scale)
             for p, v in zip(self.params, self._grad_views):
                 if p.dtype != self.grad_dtype and p.grad is not None:
                     p.grad.copy_(v)

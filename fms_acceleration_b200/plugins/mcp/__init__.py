@@ -1,1 +1,2 @@
-"""Plugin package (filled in below)."""
+"""Mamba context parallelism."""
+from .framework_plugin_mcp import MCPAccelerationPlugin  # noqa: F401
