@@ -1,0 +1,285 @@
+"""Sharded checkpoints for ScatterMoE training and their conversion back to Hugging Face safetensors.
+
+Directory contract (fms_acceleration_moe/utils/checkpoint_utils.py:72-771 of the reference): a checkpoint directory
+holds ``pytorch_model_fsdp_<i>/`` with the model state saved by ``torch.distributed.checkpoint`` under the key
+``"model"`` and ``optimizer_<i>/`` with the optimizer state under ``"optimizer"``; LoRA runs store only the
+``lora_A`` / ``lora_B`` tensors (router adapters excluded).  ``recover_safetensors_from_dcp`` (also the module's
+command line: ``python -m ...checkpoint_utils <dcp_dir> <out_dir> <pretrained_name>``) loads such a checkpoint
+without a process group, strips the PEFT prefixes, maps ScatterMoE parameters (``router`` / ``w1`` / ``w2`` /
+``w3`` ``[E, in, out]``) back to the original layout (per-expert linears or fused ``input_linear``) and writes
+safetensors shards with an index.
+"""
+from __future__ import annotations
+
+import json
+import os
+import re
+import sys
+from collections import defaultdict
+from typing import Dict, List, Optional
+
+import torch
+
+from .scattermoe_constants import (FILE_SAFETENSOR_INDEX, PARAM_NAME_ROUTER_SCATTERMOE, PARAM_NAME_WEIGHT_SCATTERMOE,
+                                   get_scattermoe_conv_spec_from_archs)
+from .scattermoe_state_dict import get_checkpoint_meta_from_sharded_safetensor, load_weight_map
+
+FSDP_MODEL_NAME = "pytorch_model_fsdp"
+OPTIMIZER_NAME = "optimizer"
+KEY_MODEL = "model"
+KEY_OPTIMIZER = "optimizer"
+SAFE_WEIGHTS_NAME = "model.safetensors"
+ADAPTER_SAFE_WEIGHTS_NAME = "adapter_model.safetensors"
+MODEL_INDEX = None  # index of the model within accelerate's model list, recorded by the save hook
+
+
+# ------------------------------------------------------------------------------------------- save / load
+def _model_state(model: torch.nn.Module, lora_only: bool) -> Dict[str, torch.Tensor]:
+    sd = model.state_dict()
+    if lora_only:
+        sd = {k: v for k, v in sd.items() if ("lora_A" in k or "lora_B" in k) and "router" not in k}
+    return sd
+
+
+def save_fsdp_model(fsdp_plugin, accelerator, model: torch.nn.Module, output_dir: str, model_index: int = 0, **kwargs):
+    """Model weights are written together with the optimizer (``save_fsdp_optimizer``); only remember the index."""
+    global MODEL_INDEX
+    MODEL_INDEX = model_index
+
+
+def save_fsdp_optimizer(fsdp_plugin, accelerator, optimizer, model: torch.nn.Module, output_dir: str,
+                        optimizer_index: int = 0, lora_only: Optional[bool] = None):
+    import torch.distributed.checkpoint as dcp
+
+    if fsdp_plugin is not None and getattr(fsdp_plugin, "state_dict_type", "SHARDED_STATE_DICT") not in (
+            "SHARDED_STATE_DICT", None) and "SHARDED" not in str(fsdp_plugin.state_dict_type):
+        raise NotImplementedError("Checkpointing for megablocks only enabled for sharded state dict.")
+    if lora_only is None:
+        lora_only = any("lora_" in n for n, _ in model.named_parameters())
+    midx = MODEL_INDEX if MODEL_INDEX is not None else 0
+    model_dir = os.path.join(output_dir, f"{FSDP_MODEL_NAME}_{midx}")
+    opt_dir = os.path.join(output_dir, f"{OPTIMIZER_NAME}_{optimizer_index}")
+    os.makedirs(model_dir, exist_ok=True)
+    os.makedirs(opt_dir, exist_ok=True)
+    no_dist = not (torch.distributed.is_available() and torch.distributed.is_initialized())
+    dcp.save({KEY_MODEL: _model_state(model, lora_only)}, storage_writer=dcp.FileSystemWriter(model_dir), no_dist=no_dist)
+    dcp.save({KEY_OPTIMIZER: optimizer.state_dict()}, storage_writer=dcp.FileSystemWriter(opt_dir), no_dist=no_dist)
+
+
+def load_fsdp_model(fsdp_plugin, accelerator, model: torch.nn.Module, input_dir: str, model_index: int = 0, **kwargs):
+    global MODEL_INDEX
+    MODEL_INDEX = model_index
+
+
+def load_fsdp_optimizer(fsdp_plugin, accelerator, optimizer, model: torch.nn.Module, input_dir: str,
+                        optimizer_index: int = 0, lora_only: Optional[bool] = None):
+    import torch.distributed.checkpoint as dcp
+
+    if accelerator is not None:
+        accelerator.wait_for_everyone()
+    if lora_only is None:
+        lora_only = any("lora_" in n for n, _ in model.named_parameters())
+    midx = MODEL_INDEX if MODEL_INDEX is not None else 0
+    no_dist = not (torch.distributed.is_available() and torch.distributed.is_initialized())
+    msd = {KEY_MODEL: _model_state(model, lora_only)}
+    dcp.load(msd, storage_reader=dcp.FileSystemReader(os.path.join(input_dir, f"{FSDP_MODEL_NAME}_{midx}")), no_dist=no_dist)
+    model.load_state_dict(msd[KEY_MODEL], strict=not lora_only)
+    osd = {KEY_OPTIMIZER: optimizer.state_dict()}
+    dcp.load(osd, storage_reader=dcp.FileSystemReader(os.path.join(input_dir, f"{OPTIMIZER_NAME}_{optimizer_index}")),
+             no_dist=no_dist)
+    optimizer.load_state_dict(osd[KEY_OPTIMIZER])
+
+
+def patch_huggingface_save_and_load_for_dtensors() -> bool:
+    """Point ``transformers.trainer``'s FSDP save / load helpers at the functions above (when transformers is there)."""
+    try:
+        import transformers.trainer as tr
+    except Exception:
+        return False
+    for name, fn in (("save_fsdp_model", save_fsdp_model), ("save_fsdp_optimizer", save_fsdp_optimizer),
+                     ("load_fsdp_model", load_fsdp_model), ("load_fsdp_optimizer", load_fsdp_optimizer)):
+        if hasattr(tr, name):
+            setattr(tr, name, fn)
+    return True
+
+
+def patch_huggingface_clip_grad_norm_fsdp2(accelerator) -> None:
+    """Give the accelerator the expert-parallel aware gradient clipping."""
+    accelerator.clip_grad_norm_ = lambda parameters, max_norm, norm_type=2.0: clip_grad_norm_(parameters, max_norm, norm_type)
+
+
+def clip_grad_norm_(parameters, max_norm: float, norm_type: float = 2.0, foreach=None) -> torch.Tensor:
+    """Total gradient norm over replicated AND expert-parallel parameters: the squared norms of expert shards are
+    summed over their expert-parallel group before the global norm is formed (the reference's FSDP2 version,
+    checkpoint_utils.py:690-731, gathers DTensor norms the same way)."""
+    params = [p for p in parameters if p.grad is not None]
+    if not params:
+        return torch.tensor(0.0)
+    dev = params[0].grad.device
+    rep = [p for p in params if not getattr(p, "_fmsb_expert_parallel", False)]
+    exp = [p for p in params if getattr(p, "_fmsb_expert_parallel", False)]
+
+    def _pow_sum(ps):
+        if not ps:
+            return torch.zeros((), device=dev)
+        return torch.stack([p.grad.float().norm(norm_type) ** norm_type for p in ps]).sum()
+
+    total = _pow_sum(rep)
+    e = _pow_sum(exp)
+    if exp and torch.distributed.is_available() and torch.distributed.is_initialized():
+        torch.distributed.all_reduce(e)  # expert shards are disjoint across the expert-parallel ranks
+        n_rep = max(torch.distributed.get_world_size() // max(_ep_size(exp[0]), 1), 1)
+        e = e / n_rep
+    norm = (total + e) ** (1.0 / norm_type)
+    coef = (max_norm / (norm + 1e-6)).clamp(max=1.0)
+    for p in params:
+        p.grad.mul_(coef.to(p.grad.dtype))
+    return norm
+
+
+def _ep_size(p) -> int:
+    g = getattr(p, "_fmsb_replicate_group", None)
+    if g is None or not torch.distributed.is_initialized():
+        return torch.distributed.get_world_size() if torch.distributed.is_initialized() else 1
+    return torch.distributed.get_world_size() // torch.distributed.get_world_size(g)
+
+
+# ------------------------------------------------------------------------------------------- readers
+def get_state_dict_from_dcp_checkpoint(dcp_checkpoint_dir: str) -> Dict[str, torch.Tensor]:
+    """Load a DCP checkpoint into plain tensors without a process group."""
+    from torch.distributed.checkpoint.default_planner import _EmptyStateDictLoadPlanner
+    from torch.distributed.checkpoint.state_dict_loader import _load_state_dict
+    import torch.distributed.checkpoint as dcp
+
+    sd: Dict = {}
+    _load_state_dict(sd, storage_reader=dcp.FileSystemReader(dcp_checkpoint_dir), planner=_EmptyStateDictLoadPlanner(),
+                     no_dist=True)
+    return sd[KEY_MODEL] if KEY_MODEL in sd else sd
+
+
+def get_state_dict_from_safe_checkpoint(safe_checkpoint_dir: str) -> Dict[str, torch.Tensor]:
+    from safetensors import safe_open
+
+    sd = {}
+    for fname in sorted(set(load_weight_map(safe_checkpoint_dir).values())):
+        with safe_open(os.path.join(safe_checkpoint_dir, fname), framework="pt") as f:
+            for k in f.keys():
+                sd[k] = f.get_tensor(k)
+    return sd
+
+
+def get_resolved_checkpoint_location(pretrained_model_name_or_path: str) -> str:
+    """A local directory is its own location (there is no hub access in this environment)."""
+    if os.path.isdir(pretrained_model_name_or_path):
+        return pretrained_model_name_or_path
+    raise FileNotFoundError(f"'{pretrained_model_name_or_path}' is not a local checkpoint directory")
+
+
+def _read_architectures(pretrained_dir: str) -> List[str]:
+    with open(os.path.join(pretrained_dir, "config.json"), encoding="utf-8") as fh:
+        return json.load(fh)["architectures"]
+
+
+# ------------------------------------------------------------------------------------------- conversion
+def recover_original_state_dict_from_checkpoint(sd: Dict[str, torch.Tensor], pretrained_model_name_or_path: str = None,
+                                                weight_map: Optional[Dict[str, str]] = None,
+                                                architectures: Optional[List[str]] = None) -> Dict[str, torch.Tensor]:
+    """Rewrite every ScatterMoE block of ``sd`` into the parameter names / layouts of the original checkpoint."""
+    if weight_map is None:
+        weight_map = load_weight_map(get_resolved_checkpoint_location(pretrained_model_name_or_path))
+    if architectures is None:
+        architectures = _read_architectures(pretrained_model_name_or_path)
+    _, router_name, expert_name, _, sharded_experts = get_scattermoe_conv_spec_from_archs(architectures)
+
+    names = "|".join([PARAM_NAME_ROUTER_SCATTERMOE, *PARAM_NAME_WEIGHT_SCATTERMOE])
+    pat = re.compile(rf"(.*)\.({names})\.weight")
+    seen: Dict[str, int] = defaultdict(int)
+    for k in sd:
+        m = pat.match(k)
+        if m:
+            seen[m.group(1)] += 1
+    for full_prefix in [p for p, c in seen.items() if c >= 3]:
+        prefix, _, module_name = full_prefix.rpartition(".")
+        meta = get_checkpoint_meta_from_sharded_safetensor(weight_map, prefix, module_name, router_name, expert_name)
+        per_model_key: Dict[str, Dict[str, torch.Tensor]] = defaultdict(dict)
+        for scatter_key, targets in meta.items():
+            fq = f"{full_prefix}.{scatter_key}"
+            param = sd.pop(fq)
+            n = len(targets)
+            is_expert = any(scatter_key.startswith(w) for w in PARAM_NAME_WEIGHT_SCATTERMOE)
+            if not is_expert:
+                assert n == 1, "Router parameters should not be sharded."
+            elif not sharded_experts:
+                assert n == 1, "Expert weights expected to be non-sharded."
+            else:
+                assert n == param.shape[0], "Sharded expert weights should be 1 expert per shard."
+            if is_expert:
+                param = param.permute(0, 2, 1)  # [E, in, out] -> [E, out, in]
+            for i, (model_key, _) in enumerate(targets):
+                per_model_key[model_key][scatter_key] = param if n == 1 else param[i]
+        for model_key, parts in per_model_key.items():
+            keys = sorted(parts)  # w1 before w3: the fused input projection is [w1 rows | w3 rows]
+            assert keys, f"Obtained zero scatter keys for model_key '{model_key}'"
+            sd[model_key] = parts[keys[0]].contiguous() if len(keys) == 1 else torch.cat([parts[k] for k in keys], dim=1)
+    return sd
+
+
+def save_sharded_safetensors(input_state_dict: Dict[str, torch.Tensor], save_directory: str,
+                             metadata: Optional[Dict] = None, max_shard_size="5GB", lora: bool = False) -> None:
+    from safetensors.torch import save_file
+
+    from ...peft.gptqmodel.utils.model import parse_size, shard_checkpoint
+
+    os.makedirs(save_directory, exist_ok=True)
+    sd = {k: v.detach().cpu().contiguous() for k, v in input_state_dict.items()}
+    meta = dict(metadata or {"format": "pt"})
+    if lora:
+        save_file(sd, os.path.join(save_directory, ADAPTER_SAFE_WEIGHTS_NAME), metadata=meta)
+        return
+    shards, index = shard_checkpoint(sd, parse_size(max_shard_size), SAFE_WEIGHTS_NAME)
+    for fname, part in shards.items():
+        save_file(part, os.path.join(save_directory, fname), metadata=meta)
+    if index is not None:
+        with open(os.path.join(save_directory, FILE_SAFETENSOR_INDEX), "w", encoding="utf-8") as fh:
+            json.dump(index, fh, indent=2, sort_keys=True)
+
+
+def recover_safetensors_from_dcp(checkpoint_dir: str, pretrained_model_name_or_path: Optional[str], output_dir: str) -> None:
+    """DCP (or safetensors) training checkpoint -> Hugging Face safetensors in the original parameter layout."""
+    fsdp_dirs = sorted(d for d in os.listdir(checkpoint_dir) if d.startswith(FSDP_MODEL_NAME))
+    if len(fsdp_dirs) > 1:
+        raise ValueError(f"Found > 1 dirs in dcp checkpoint dir {checkpoint_dir}: {fsdp_dirs}. Please spectify the exact one.")
+    if fsdp_dirs:
+        sd = get_state_dict_from_dcp_checkpoint(os.path.join(checkpoint_dir, fsdp_dirs[0]))
+    else:
+        sd = get_state_dict_from_safe_checkpoint(checkpoint_dir)
+    # strip PEFT naming: "base_model.model." prefix and the ".default" adapter infix
+    lora = False
+    cleaned = {}
+    for k, v in sd.items():
+        if "lora_A" in k or "lora_B" in k:
+            lora = True
+        nk = k[len("base_model.model."):] if (k.startswith("base_model.model.") and not ("lora_" in k)) else k
+        nk = nk.replace(".default.", ".").replace(".base_layer.", ".")
+        cleaned[nk] = v
+    sd = cleaned
+    if pretrained_model_name_or_path is not None and not lora:
+        sd = recover_original_state_dict_from_checkpoint(sd, pretrained_model_name_or_path)
+    save_sharded_safetensors({k: v.contiguous() for k, v in sd.items()}, output_dir, metadata={"format": "pt"}, lora=lora)
+
+
+def main(argv=None) -> int:
+    import argparse
+
+    ap = argparse.ArgumentParser(description="Convert a ScatterMoE training checkpoint to Hugging Face safetensors")
+    ap.add_argument("checkpoint_dir", help="directory that holds pytorch_model_fsdp_<i>/ (or safetensors files)")
+    ap.add_argument("output_dir")
+    ap.add_argument("pretrained_model_name_or_path", nargs="?", default=None,
+                    help="original checkpoint (for the parameter names and layout); optional for LoRA checkpoints")
+    a = ap.parse_args(argv)
+    recover_safetensors_from_dcp(a.checkpoint_dir, a.pretrained_model_name_or_path, a.output_dir)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -138,6 +138,10 @@ def main():
         from dist_worker_moe import check_moe
 
         check_moe(dev, rank, world)
+    if which in ("all", "cp"):
+        from dist_worker_cp import check_cp
+
+        check_cp(dev, rank, world)
     dist.barrier()
     dist.destroy_process_group()
 

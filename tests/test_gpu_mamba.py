@@ -60,3 +60,24 @@ def test_ssd_scan_matches_recurrence(T, nh, P, G, N, Q, with_h0):
         assert _rel(t.grad.cpu(), r.grad) < 5e-2, (n, _rel(t.grad.cpu(), r.grad))
     if with_h0:
         assert _rel(h0.grad.cpu(), h0r.grad) < 5e-2
+
+
+def test_mamba2_model_matches_cpu_reference():
+    from fms_acceleration_b200.models.builder import build_model
+
+    torch.manual_seed(0)
+    model = build_model("tiny-mamba2", device=DEV, dtype=torch.bfloat16, seed=0)
+    ref = build_model("tiny-mamba2", device="cpu", dtype=torch.float32, seed=0)
+    ref.load_state_dict({k: v.float().cpu() for k, v in model.state_dict().items()})
+    ids = torch.randint(0, 512, (1, 96))
+    out = model(ids.to(DEV), labels=ids.to(DEV))
+    out.loss.backward()
+    NV.check_status()
+    r = ref(ids, labels=ids)
+    r.loss.backward()
+    assert abs(out.loss.item() - r.loss.item()) < 3e-2
+    rg = dict(ref.named_parameters())
+    for n, p in model.named_parameters():
+        if rg[n].grad is None or rg[n].grad.norm() < 1e-7:
+            continue
+        assert _rel(p.grad.cpu(), rg[n].grad) < 0.1, (n, _rel(p.grad.cpu(), rg[n].grad))

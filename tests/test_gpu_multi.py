@@ -24,6 +24,7 @@ def _run(which: str, nproc: int = 2, timeout: int = 600):
     ("comm", ["allgather", "allreduce", "reduce_scatter"]),
     ("engine", ["engine", "engine_train"]),
     ("moe", ["moe_ep"]),
+    ("cp", ["mamba_cp"]),
 ])
 def test_multi_gpu(which, expected):
     if torch.cuda.device_count() < 2:
