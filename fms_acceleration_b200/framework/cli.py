@@ -1,0 +1,101 @@
+"""Command line of the framework: ``python -m fms_acceleration.cli {install,plugins,configs,arguments}``.
+
+Verbs as in fms_acceleration/cli.py:36-213 of the reference.  All plugins ship in-tree here, so ``install`` only
+reports that (and can build the native library); ``plugins`` lists the plugins and whether they import;
+``configs`` lists the sample configurations from ``sample-configurations/CONTENTS.yaml``; ``arguments <shortname>``
+prints the framework arguments to use for a sample configuration.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import os
+import sys
+
+import yaml
+
+from .constants import PLUGINS
+
+REPO_ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+CONTENTS = os.path.join(REPO_ROOT, "sample-configurations", "CONTENTS.yaml")
+PLUGIN_LONG_NAMES = {
+    "peft": "accelerated-peft", "foak": "fused-ops-and-kernels", "aadp": "attention-and-distributed-packing",
+    "moe": "accelerated-moe", "odm": "online-data-mixing", "mcp": "mamba-cp",
+}
+
+
+def _plugin_status(short: str) -> bool:
+    try:
+        importlib.import_module(f"fms_acceleration_b200.plugins.{short}")
+        return True
+    except Exception:
+        return False
+
+
+def install(plugin: str = None, build: bool = False, **kwargs) -> int:
+    known = set(PLUGINS) | set(PLUGIN_LONG_NAMES.values())
+    if plugin is not None and plugin.replace("fms-acceleration-", "") not in known:
+        print(f"unknown plugin '{plugin}'; available: {sorted(PLUGIN_LONG_NAMES.values())}")
+        return 1
+    print("all plugins are part of this package; nothing to download")
+    if build:
+        from ..build import build as _build
+
+        print("native library:", _build())
+    return 0
+
+
+def list_plugins() -> int:
+    print("\nplugins (x = importable):\n")
+    for short in PLUGINS:
+        mark = "x" if _plugin_status(short) else " "
+        print(f" [{mark}] {short:5s} {PLUGIN_LONG_NAMES[short]}")
+    return 0
+
+
+def _read_contents():
+    with open(CONTENTS, encoding="utf-8") as fh:
+        return yaml.safe_load(fh)["framework_configs"]
+
+
+def list_sample_configs() -> int:
+    print(f"\nsample configurations ({os.path.dirname(CONTENTS)}):\n")
+    for i, c in enumerate(_read_contents(), 1):
+        print(f"{i:2d}. {c['shortname']:48s} plugins: {', '.join(c['plugins'])}")
+    return 0
+
+
+def list_arguments(config_shortname: str) -> int:
+    for c in _read_contents():
+        if c["shortname"] == config_shortname:
+            path = os.path.join(os.path.dirname(CONTENTS), c["filename"])
+            print(f"--acceleration_framework_config_file {path}")
+            print(f"(or: export ACCELERATION_FRAMEWORK_CONFIG_FILE={path})")
+            print("required plugins: " + ", ".join(c["plugins"]))
+            return 0
+    print(f"no sample configuration with shortname '{config_shortname}'; see the `configs` verb")
+    return 1
+
+
+def cli(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="fms_acceleration.cli")
+    sub = ap.add_subparsers(dest="verb", required=True)
+    p = sub.add_parser("install", help="install a plugin (all plugins ship with this package)")
+    p.add_argument("plugin", nargs="?")
+    p.add_argument("--build", action="store_true", help="(re)build the native CUDA/C++ library")
+    sub.add_parser("plugins", help="list plugins")
+    sub.add_parser("configs", help="list sample configurations")
+    p = sub.add_parser("arguments", help="print the arguments for a sample configuration")
+    p.add_argument("config_shortname")
+    a = ap.parse_args(argv)
+    if a.verb == "install":
+        return install(a.plugin, a.build)
+    if a.verb == "plugins":
+        return list_plugins()
+    if a.verb == "configs":
+        return list_sample_configs()
+    return list_arguments(a.config_shortname)
+
+
+if __name__ == "__main__":
+    sys.exit(cli())

@@ -98,7 +98,7 @@ def mamba2_2p7b() -> DecoderConfig:
 
 def tiny_mamba2() -> DecoderConfig:
     return DecoderConfig(vocab_size=512, hidden_size=128, num_hidden_layers=2, num_attention_heads=4,
-                         model_type="mamba2", architectures=["Mamba2ForCausalLM"], mamba_d_state=32, mamba_d_head=64,
+                         model_type="mamba2", architectures=["Mamba2ForCausalLM"], mamba_d_state=32, mamba_d_head=32,
                          mamba_expand=2, mamba_d_conv=4, mamba_chunk_size=32, rms_norm_eps=1e-5,
                          tie_word_embeddings=True)
 

@@ -45,7 +45,8 @@ def _aligned(t: torch.Tensor) -> torch.Tensor:
 
 
 def _linear(x, lin: nn.Linear):
-    if x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and lin.bias is None:
+    if (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and lin.bias is None
+            and lin.in_features % 8 == 0 and lin.out_features % 8 == 0):
         return _DenseLinear.apply(x, lin.weight)
     return lin(x)
 

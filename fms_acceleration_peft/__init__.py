@@ -1,0 +1,16 @@
+"""Import-compatible alias of ``fms_acceleration_b200.plugins.peft``: code written against the ``fms_acceleration_peft`` package of the reference
+keeps working (``import fms_acceleration_peft``, ``from fms_acceleration_peft.<module> import ...``).  The implementation lives in
+``fms_acceleration_b200.plugins.peft``; the submodules listed below are registered under this package's name."""
+import importlib
+import sys
+
+_TARGET = "fms_acceleration_b200.plugins.peft"
+_SUBMODULES = ['framework_plugin_bnb', 'framework_plugin_autogptq', 'fsdp_utils', 'gptqmodel']
+
+_pkg = importlib.import_module(_TARGET)
+globals().update({k: v for k, v in vars(_pkg).items() if not k.startswith("__")})
+for _sub in _SUBMODULES:
+    try:
+        sys.modules[f"{__name__}.{_sub}"] = importlib.import_module(f"{_TARGET}.{_sub}")
+    except ImportError:  # an optional dependency of that submodule is missing
+        pass
