@@ -255,3 +255,17 @@ def gptq_pack_zeros(z_int: torch.Tensor, bits: int) -> torch.Tensor:
     packed = (v << shifts).sum(dim=2) & 0xFFFFFFFF
     packed = torch.where(packed >= 2 ** 31, packed - 2 ** 32, packed)
     return packed.to(torch.int32)
+
+
+def gptq_unpack(qweight: torch.Tensor, bits: int) -> torch.Tensor:
+    """Inverse of :func:`gptq_pack`: int64 codes ``[in, out]``."""
+    shifts = torch.arange(0, 32, bits, device=qweight.device, dtype=torch.int64)
+    qw = qweight.long() & 0xFFFFFFFF
+    return ((qw[:, None, :] >> shifts[None, :, None]) & ((1 << bits) - 1)).reshape(-1, qweight.shape[1])
+
+
+def gptq_unpack_zeros(qzeros: torch.Tensor, bits: int) -> torch.Tensor:
+    """Inverse of :func:`gptq_pack_zeros`: int64 zero points ``[groups, out]``."""
+    shifts = torch.arange(0, 32, bits, device=qzeros.device, dtype=torch.int64)
+    qz = qzeros.long() & 0xFFFFFFFF
+    return ((qz[:, :, None] >> shifts[None, None, :]) & ((1 << bits) - 1)).reshape(qzeros.shape[0], -1)

@@ -1,0 +1,124 @@
+"""GPTQ library on the host: quantiser, Hessian solver, packing, save / load round trip, config handling."""
+import json
+import os
+
+import pytest
+import torch
+
+from fms_acceleration_b200.nn.gptq import QuantLinear
+from fms_acceleration_b200.ops import quant as Q
+from fms_acceleration_b200.plugins.peft.gptqmodel import GPTQModel, QuantizeConfig
+from fms_acceleration_b200.plugins.peft.gptqmodel.quantization.config import FORMAT
+from fms_acceleration_b200.plugins.peft.gptqmodel.quantization.gptq import GPTQ
+from fms_acceleration_b200.plugins.peft.gptqmodel.quantization.quantizer import Quantizer
+from fms_acceleration_b200.plugins.peft.gptqmodel.utils.model import (convert_gptq_v1_to_v2_format,
+                                                                      convert_gptq_v2_to_v1_format, parse_size,
+                                                                      shard_checkpoint)
+
+
+@pytest.mark.parametrize("bits", [2, 4, 8])
+def test_pack_unpack_roundtrip(bits):
+    g = torch.Generator().manual_seed(bits)
+    q = torch.randint(0, 2 ** bits, (64, 32), generator=g)
+    packed = Q.gptq_pack(q, bits)
+    assert packed.dtype == torch.int32 and packed.shape == (64 * bits // 32, 32)
+    assert torch.equal(Q.gptq_unpack(packed, bits), q)
+    z = torch.randint(0, 2 ** bits, (4, 32), generator=g)
+    assert torch.equal(Q.gptq_unpack_zeros(Q.gptq_pack_zeros(z, bits), bits), z)
+
+
+def test_quantizer_grid():
+    w = torch.randn(16, 64)
+    qz = Quantizer()
+    qz.configure(4, perchannel=True, sym=False)
+    qz.find_params(w, weight=True)
+    dq = qz.quantize(w)
+    assert qz.scale.shape == (16, 1) and (dq - w).abs().max() <= qz.scale.max() * 0.5001
+    levels = torch.round(dq / qz.scale + qz.zero)
+    assert levels.min() >= 0 and levels.max() <= 15
+
+
+def test_gptq_solver_beats_round_to_nearest():
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(128, 48, bias=False)
+    basis = torch.randn(128, 128)
+    x = torch.randn(2048, 128) @ (basis * torch.logspace(0, -2, 128))  # correlated inputs
+    ref = lin(x)
+    W0 = lin.weight.data.clone()
+    rtn = Quantizer()
+    rtn.configure(4, perchannel=True, sym=True)
+    g = GPTQ(lin)
+    g.quantizer.configure(4, perchannel=True, sym=True)
+    g.add_batch(x, ref)
+    scale, zero, g_idx, *_ = g.fasterquant(percdamp=0.01, group_size=32, actorder=False)
+    err_gptq = (lin(x) - ref).pow(2).mean()
+    # round-to-nearest with the same group size
+    Wr = torch.empty_like(W0)
+    for s in range(0, 128, 32):
+        rtn.find_params(W0[:, s:s + 32], weight=True)
+        Wr[:, s:s + 32] = rtn.quantize(W0[:, s:s + 32])
+    err_rtn = (x @ Wr.t() - ref).pow(2).mean()
+    assert err_gptq < 0.8 * err_rtn
+    assert scale.shape == (48, 4) and zero.shape == (48, 4) and g_idx.shape == (128,)
+    # the solver's weights lie on the grid it reports, so QuantLinear.pack reproduces them exactly
+    ql = QuantLinear(4, 32, 128, 48, dtype=torch.float32)
+    ql.pack(lin, scale, zero, g_idx)
+    assert torch.allclose(ql.dequantize().t(), lin.weight.data, atol=1e-5)
+
+
+def test_v1_v2_zero_point_conversion():
+    ql = QuantLinear.random(64, 32, 4, 32, torch.float32)
+    model = torch.nn.Sequential(ql)
+    before = ql.qzeros.clone()
+    convert_gptq_v2_to_v1_format(model, 4)
+    assert torch.equal(Q.gptq_unpack_zeros(ql.qzeros, 4), Q.gptq_unpack_zeros(before, 4) - 1)
+    convert_gptq_v1_to_v2_format(model, 4)
+    assert torch.equal(ql.qzeros, before)
+
+
+def test_quantize_config_roundtrip(tmp_path):
+    qc = QuantizeConfig(bits=4, group_size=64, desc_act=False)
+    qc.save_pretrained(str(tmp_path))
+    back = QuantizeConfig.from_pretrained(str(tmp_path))
+    assert (back.bits, back.group_size, back.desc_act, back.sym) == (4, 64, False, True)
+    legacy = QuantizeConfig.from_quant_config({"bits": 4, "group_size": 128, "is_marlin_format": False,
+                                               "checkpoint_format": "gptq", "unknown_key": 1})
+    assert legacy.format == FORMAT.GPTQ and legacy.group_size == 128
+    with pytest.raises(ValueError):
+        QuantizeConfig(bits=5)
+    with pytest.raises(ValueError):
+        QuantizeConfig(bits=4, group_size=-7)
+
+
+def test_shard_checkpoint_and_sizes():
+    assert parse_size("2GB") == 2 * 2 ** 30 and parse_size("1GiB") == 2 ** 30 and parse_size(17) == 17
+    sd = {f"t{i}": torch.zeros(1000) for i in range(5)}
+    shards, index = shard_checkpoint(sd, 8500, "model.safetensors")
+    assert len(shards) == 3 and set(index["weight_map"]) == set(sd)
+    one, idx = shard_checkpoint(sd, 10 ** 9, "model.safetensors")
+    assert list(one) == ["model.safetensors"] and idx is None
+
+
+def test_quantize_save_load_tiny_llama(tmp_path):
+    torch.manual_seed(0)
+    qc = QuantizeConfig(bits=4, group_size=32, desc_act=False)
+    wrapper = GPTQModel.from_pretrained("tiny-llama", qc, torch_dtype=torch.float32)
+    model = wrapper.model
+    ids = torch.randint(0, model.config.vocab_size, (2, 24))
+    ref_logits = model(ids).logits.detach()
+    calib = [{"input_ids": torch.randint(0, model.config.vocab_size, (32,)), "attention_mask": torch.ones(32)}
+             for _ in range(8)]
+    wrapper.quantize(calib, batch_size=4)
+    n_q = sum(isinstance(m, QuantLinear) for m in model.modules())
+    assert n_q == 7 * model.config.num_hidden_layers
+    q_logits = model(ids).logits.detach()
+    rel = (q_logits - ref_logits).norm() / ref_logits.norm()
+    assert rel < 0.5  # random-init weights at 4 bits: coarse, but far from unrelated
+    out = tmp_path / "ckpt"
+    wrapper.save_quantized(str(out))
+    cfg = json.load(open(out / "config.json"))
+    assert cfg["quantization_config"]["bits"] == 4 and os.path.exists(out / "quantize_config.json")
+    loaded = GPTQModel.from_quantized(str(out), torch_dtype=torch.float32)
+    assert loaded.quantized and torch.allclose(loaded.model(ids).logits, q_logits, atol=5e-3)  # scales are stored in fp16
+    with pytest.raises(EnvironmentError):
+        wrapper.quantize(calib)
