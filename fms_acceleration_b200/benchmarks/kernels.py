@@ -106,7 +106,18 @@ def bench_attn(a):
     t_f = timeit(lambda: AT._fwd(q, k, v, ds, de, nh, nkv, d, scale), a.iters, a.warmup, a.flush)
     t_b = timeit(lambda: AT._bwd(q, k, v, o, lse, do, ds, de, nh, nkv, d, scale), a.iters, a.warmup, a.flush)
     NV.check_status()
-    print(json.dumps({"kernel": "varlen_attention", "tokens": T, "heads": nh, "kv_heads": nkv, "head_dim": d,
+    extra = {}
+    if a.compare_v1:
+        g2 = AT._bwd(q, k, v, o, lse, do, ds, de, nh, nkv, d, scale)
+        AT.BWD_PIPELINED = False
+        g1 = AT._bwd(q, k, v, o, lse, do, ds, de, nh, nkv, d, scale)
+        extra["bwd_v1_ms"] = timeit(lambda: AT._bwd(q, k, v, o, lse, do, ds, de, nh, nkv, d, scale), a.iters, a.warmup,
+                                    a.flush)
+        AT.BWD_PIPELINED = True
+        NV.check_status()
+        extra["max_abs_diff_vs_v1"] = [float((x.float() - y.float()).abs().max()) for x, y in zip(g2, g1)]
+        extra["max_abs_v1"] = [float(y.float().abs().max()) for y in g1]
+    print(json.dumps({**extra, "kernel": "varlen_attention", "tokens": T, "heads": nh, "kv_heads": nkv, "head_dim": d,
                       "causal_pairs_per_head": pairs, "fwd_ms": t_f, "fwd_tflops": fl_fwd / t_f / 1e9, "bwd_ms": t_b,
                       "bwd_tflops": 2.5 * fl_fwd / t_b / 1e9}))
 
@@ -152,6 +163,7 @@ def main(argv=None):
             p.add_argument("--heads", type=int, default=32)
             p.add_argument("--kv-heads", type=int, default=8)
             p.add_argument("--head-dim", type=int, default=128)
+            p.add_argument("--compare-v1", action="store_true", help="also run the first-generation backward")
         else:
             p.add_argument("--tokens", type=int, default=16384)
             p.add_argument("--hidden", type=int, default=4096)

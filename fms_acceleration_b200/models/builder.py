@@ -9,7 +9,7 @@ from typing import Callable, Optional
 import torch
 from torch import nn
 
-from .config import PRESETS, DecoderConfig, preset
+from .config import HUB_ALIASES, PRESETS, DecoderConfig, preset
 
 ARCH_TO_MODEL = {}
 
@@ -29,6 +29,19 @@ def _registry():
             ARCH_TO_MODEL["GraniteMoeForCausalLM"] = GraniteMoeForCausalLM
         except ImportError:
             pass
+        from .gpt_bigcode import GPTBigCodeForCausalLM
+        from .granitemoe import GraniteMoeSharedForCausalLM
+        from .mixtral import MixtralForCausalLM
+
+        ARCH_TO_MODEL.update({"MixtralForCausalLM": MixtralForCausalLM,
+                              "GraniteMoeSharedForCausalLM": GraniteMoeSharedForCausalLM,
+                              "GPTBigCodeForCausalLM": GPTBigCodeForCausalLM})
+        try:
+            from .granitemoehybrid import GraniteMoeHybridForCausalLM
+
+            ARCH_TO_MODEL["GraniteMoeHybridForCausalLM"] = GraniteMoeHybridForCausalLM
+        except ImportError:
+            pass
         try:
             from .mamba2 import Mamba2ForCausalLM
 
@@ -43,7 +56,7 @@ def resolve_config(model_name_or_cfg) -> DecoderConfig:
     if isinstance(model_name_or_cfg, DecoderConfig):
         return model_name_or_cfg
     name = str(model_name_or_cfg)
-    if name in PRESETS:
+    if name in PRESETS or name in HUB_ALIASES:
         cfg = preset(name)
         cfg.name_or_path = name
         return cfg

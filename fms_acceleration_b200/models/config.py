@@ -42,6 +42,8 @@ class DecoderConfig:
     mamba_chunk_size: int = 256
     mamba_conv_bias: bool = True
     mamba_proj_bias: bool = False
+    # hybrid decoders: "mamba" or "attention" per layer (empty: the family's default)
+    layer_types: List[str] = field(default_factory=list)
     name_or_path: str = ""
     torch_dtype: str = "bfloat16"
 
@@ -103,6 +105,61 @@ def tiny_mamba2() -> DecoderConfig:
                          tie_word_embeddings=True)
 
 
+def mixtral_8x7b() -> DecoderConfig:
+    return DecoderConfig(vocab_size=32000, hidden_size=4096, intermediate_size=14336, num_hidden_layers=32,
+                         num_attention_heads=32, num_key_value_heads=8, rms_norm_eps=1e-5, rope_theta=1e6,
+                         max_position_embeddings=32768, model_type="mixtral", architectures=["MixtralForCausalLM"],
+                         num_local_experts=8, num_experts_per_tok=2, moe_intermediate_size=14336)
+
+
+def tiny_mixtral() -> DecoderConfig:
+    return DecoderConfig(vocab_size=1024, hidden_size=256, intermediate_size=128, num_hidden_layers=2,
+                         num_attention_heads=4, num_key_value_heads=2, model_type="mixtral",
+                         architectures=["MixtralForCausalLM"], num_local_experts=4, num_experts_per_tok=2,
+                         moe_intermediate_size=128)
+
+
+def granite_8b() -> DecoderConfig:
+    """Granite 3 dense 8B."""
+    return DecoderConfig(vocab_size=49155, hidden_size=4096, intermediate_size=12800, num_hidden_layers=40,
+                         num_attention_heads=32, num_key_value_heads=8, rms_norm_eps=1e-5, rope_theta=10000.0,
+                         max_position_embeddings=4096, tie_word_embeddings=True, model_type="granite",
+                         architectures=["GraniteForCausalLM"], embedding_multiplier=12.0, attention_multiplier=0.0078125,
+                         residual_multiplier=0.22, logits_scaling=16.0)
+
+
+def tiny_granitemoeshared() -> DecoderConfig:
+    return DecoderConfig(vocab_size=1024, hidden_size=256, intermediate_size=128, num_hidden_layers=2,
+                         num_attention_heads=4, num_key_value_heads=2, tie_word_embeddings=True,
+                         model_type="granitemoeshared", architectures=["GraniteMoeSharedForCausalLM"],
+                         num_local_experts=8, num_experts_per_tok=2, moe_intermediate_size=128,
+                         shared_intermediate_size=192)
+
+
+def santacoder() -> DecoderConfig:
+    """bigcode/gpt_bigcode-santacoder: multi-query attention, learned positions, GELU MLP."""
+    return DecoderConfig(vocab_size=49280, hidden_size=2048, intermediate_size=8192, num_hidden_layers=24,
+                         num_attention_heads=16, num_key_value_heads=1, rms_norm_eps=1e-5, max_position_embeddings=2048,
+                         tie_word_embeddings=True, hidden_act="gelu_pytorch_tanh", model_type="gpt_bigcode",
+                         architectures=["GPTBigCodeForCausalLM"])
+
+
+def tiny_gpt_bigcode() -> DecoderConfig:
+    return DecoderConfig(vocab_size=1024, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                         num_attention_heads=4, num_key_value_heads=1, rms_norm_eps=1e-5, max_position_embeddings=512,
+                         tie_word_embeddings=True, hidden_act="gelu_pytorch_tanh", model_type="gpt_bigcode",
+                         architectures=["GPTBigCodeForCausalLM"])
+
+
+def tiny_granitemoehybrid() -> DecoderConfig:
+    return DecoderConfig(vocab_size=512, hidden_size=128, intermediate_size=64, num_hidden_layers=4,
+                         num_attention_heads=4, num_key_value_heads=2, tie_word_embeddings=True,
+                         model_type="granitemoehybrid", architectures=["GraniteMoeHybridForCausalLM"],
+                         num_local_experts=4, num_experts_per_tok=2, moe_intermediate_size=64,
+                         shared_intermediate_size=96, mamba_d_state=32, mamba_d_head=32, mamba_chunk_size=32,
+                         layer_types=["mamba", "attention", "mamba", "mamba"])
+
+
 PRESETS = {
     "tiny-llama": tiny_llama,
     "mistral-7b": mistral_7b,
@@ -111,8 +168,30 @@ PRESETS = {
     "tiny-granitemoe": tiny_granitemoe,
     "mamba2-2.7b": mamba2_2p7b,
     "tiny-mamba2": tiny_mamba2,
+    "mixtral-8x7b": mixtral_8x7b,
+    "tiny-mixtral": tiny_mixtral,
+    "granite-8b": granite_8b,
+    "tiny-granitemoeshared": tiny_granitemoeshared,
+    "santacoder": santacoder,
+    "tiny-gpt-bigcode": tiny_gpt_bigcode,
+    "tiny-granitemoehybrid": tiny_granitemoehybrid,
+}
+
+# Hugging Face hub ids used by the reference's benchmark scenarios -> the preset of the same architecture
+# (weights are random-init here; only the shapes are taken from the named model).
+HUB_ALIASES = {
+    "mistralai/Mistral-7B-v0.1": "mistral-7b",
+    "TheBloke/Mistral-7B-v0.1-GPTQ": "mistral-7b",
+    "NousResearch/Llama-2-70b-hf": "llama2-70b",
+    "TheBloke/Llama-2-70B-GPTQ": "llama2-70b",
+    "mistralai/Mixtral-8x7B-Instruct-v0.1": "mixtral-8x7b",
+    "TheBloke/Mixtral-8x7B-Instruct-v0.1-GPTQ": "mixtral-8x7b",
+    "ibm-granite/granite-3.0-3b-a800m-instruct": "granite-3b-a800m",
+    "ibm-granite/granite-3.0-8b-instruct": "granite-8b",
+    "bigcode/gpt_bigcode-santacoder": "santacoder",
+    "state-spaces/mamba2-2.7b": "mamba2-2.7b",
 }
 
 
 def preset(name: str) -> DecoderConfig:
-    return PRESETS[name]()
+    return PRESETS[HUB_ALIASES.get(name, name)]()

@@ -81,3 +81,49 @@ class GraniteMoeModel(LlamaModel):
 
 class GraniteMoeForCausalLM(LlamaForCausalLM):
     model_cls = GraniteMoeModel
+
+
+# ------------------------------------------------------------------------------ GraniteMoeShared
+class GraniteMoeSharedMLP(nn.Module):
+    """Dense SwiGLU branch that every token takes besides its routed experts (``shared_mlp.input_linear [2*Is, H]``,
+    ``shared_mlp.output_linear [H, Is]`` as in the Hugging Face GraniteMoeShared checkpoints)."""
+
+    def __init__(self, cfg: DecoderConfig):
+        super().__init__()
+        self.input_linear = nn.Linear(cfg.hidden_size, 2 * cfg.shared_intermediate_size, bias=False)
+        self.output_linear = nn.Linear(cfg.shared_intermediate_size, cfg.hidden_size, bias=False)
+
+    def forward(self, x):
+        g, u = self.input_linear(x).chunk(2, dim=-1)
+        return self.output_linear(F.silu(g) * u)
+
+
+class GraniteMoeSharedMoE(GraniteMoeMoE):
+    pass
+
+
+class GraniteMoeSharedDecoderLayer(GraniteMoeDecoderLayer):
+    def __init__(self, cfg: DecoderConfig, layer_idx: int):
+        super().__init__(cfg, layer_idx)
+        self.block_sparse_moe = GraniteMoeSharedMoE(cfg)
+        self.shared_mlp = GraniteMoeSharedMLP(cfg) if cfg.shared_intermediate_size else None
+
+    def _ffn(self, y):
+        out = self.block_sparse_moe(y)
+        out = out[0] if isinstance(out, tuple) else out
+        if self.shared_mlp is not None:
+            out = out + self.shared_mlp(y)
+        return out
+
+    def forward(self, x, pos, cos_t, sin_t, cu_seqlens):
+        rm = self.cfg.residual_multiplier
+        x = x + rm * self.self_attn(self.input_layernorm(x), pos, cos_t, sin_t, cu_seqlens)
+        return x + rm * self._ffn(self.post_attention_layernorm(x))
+
+
+class GraniteMoeSharedModel(LlamaModel):
+    layer_cls = GraniteMoeSharedDecoderLayer
+
+
+class GraniteMoeSharedForCausalLM(LlamaForCausalLM):
+    model_cls = GraniteMoeSharedModel

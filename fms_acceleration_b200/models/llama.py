@@ -150,7 +150,7 @@ class LlamaDecoderLayer(nn.Module):
         if mlp is not None:
             return mlp_block(h, mlp)
         y = RN.rmsnorm(h, self.post_attention_layernorm.weight, self.post_attention_layernorm.variance_epsilon)
-        ffn = self.mlp if hasattr(self, "mlp") else self.block_sparse_moe
+        ffn = getattr(self, "_ffn", None) or (self.mlp if hasattr(self, "mlp") else self.block_sparse_moe)
         out = ffn(y)
         if isinstance(out, tuple):
             out = out[0]

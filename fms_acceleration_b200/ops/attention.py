@@ -8,6 +8,7 @@ structure is handed to the kernels as per-token ``doc_start`` / ``doc_end`` arra
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -50,6 +51,11 @@ def attention_ref(q, k, v, doc_start, scale=None):
     return torch.matmul(p, vf).transpose(0, 1).contiguous()
 
 
+# True: the pipelined backward kernels (csrc/attention_bwd.cu); False: the first-generation ones kept as a
+# cross-check (csrc/attention.cu).
+BWD_PIPELINED = os.environ.get("FMSB_ATTN_BWD", "2") != "1"
+
+
 def _fwd(q2, k2, v2, doc_start, doc_end, nh, nkv, d, scale):
     T = q2.shape[0]
     o = torch.empty(T, nh * d, dtype=q2.dtype, device=q2.device)
@@ -77,16 +83,18 @@ def _bwd(q2, k2, v2, o, lse, dout, doc_start, doc_end, nh, nkv, d, scale, dq=Non
     if dv is None:
         dv = torch.empty(T, nkv * d, dtype=q2.dtype, device=dev)
     st = N.status_word(dev)
-    rc = N.lib().fmsb_attn_bwd_dq(q2.data_ptr(), q2.stride(0), k2.data_ptr(), k2.stride(0), v2.data_ptr(),
+    dq_fn, dkv_fn = ((N.lib().fmsb_attn_bwd_dq2, N.lib().fmsb_attn_bwd_dkv2) if BWD_PIPELINED
+                     else (N.lib().fmsb_attn_bwd_dq, N.lib().fmsb_attn_bwd_dkv))
+    rc = dq_fn(q2.data_ptr(), q2.stride(0), k2.data_ptr(), k2.stride(0), v2.data_ptr(),
                                   v2.stride(0), dout.data_ptr(), dout.stride(0), dq.data_ptr(), dq.stride(0),
                                   lse.data_ptr(), delta.data_ptr(), doc_start.data_ptr(), doc_end.data_ptr(), T, nh,
                                   nkv, d, float(scale), fmt, st.data_ptr(), N.stream_ptr())
     N.check(rc, "fmsb_attn_bwd_dq")
-    rc = N.lib().fmsb_attn_bwd_dkv(q2.data_ptr(), q2.stride(0), k2.data_ptr(), k2.stride(0), v2.data_ptr(),
-                                   v2.stride(0), dout.data_ptr(), dout.stride(0), dk.data_ptr(), dk.stride(0),
-                                   dv.data_ptr(), dv.stride(0), lse.data_ptr(), delta.data_ptr(), doc_start.data_ptr(),
-                                   doc_end.data_ptr(), T, nh, nkv, d, float(scale), fmt, st.data_ptr(),
-                                   N.stream_ptr())
+    rc = dkv_fn(q2.data_ptr(), q2.stride(0), k2.data_ptr(), k2.stride(0), v2.data_ptr(),
+                v2.stride(0), dout.data_ptr(), dout.stride(0), dk.data_ptr(), dk.stride(0),
+                dv.data_ptr(), dv.stride(0), lse.data_ptr(), delta.data_ptr(), doc_start.data_ptr(),
+                doc_end.data_ptr(), T, nh, nkv, d, float(scale), fmt, st.data_ptr(),
+                N.stream_ptr())
     N.check(rc, "fmsb_attn_bwd_dkv")
     return dq, dk, dv
 

@@ -117,3 +117,26 @@ def test_dcp_save_and_recover_safetensors(tmp_path):
     CU.load_fsdp_optimizer(None, None, opt2, fresh, str(ckpt), 0)
     for (k, a), (_, b) in zip(model.state_dict().items(), fresh.state_dict().items()):
         assert torch.equal(a, b), k
+
+
+@pytest.mark.parametrize("name,arch", [("tiny-mixtral", "MixtralForCausalLM"),
+                                       ("tiny-granitemoeshared", "GraniteMoeSharedForCausalLM"),
+                                       ("tiny-granitemoehybrid", "GraniteMoeHybridForCausalLM")])
+def test_swap_other_families(name, arch):
+    """Per-expert (Mixtral) and fused (GraniteMoeShared / Hybrid) layouts convert exactly and back."""
+    torch.manual_seed(0)
+    model = build_model(name, seed=0)
+    original = {k: v.clone() for k, v in model.state_dict().items()}
+    V = model.config.vocab_size
+    ids = torch.randint(0, V, (1, 40))
+    cu = torch.tensor([0, 16, 40], dtype=torch.int32)
+    ref = model(ids, labels=ids, cu_seqlens=cu).loss
+    swapped = prepare_scattermoe(model, None, 0, 1, 1)
+    assert len(swapped) == model.config.num_hidden_layers
+    assert abs(model(ids, labels=ids, cu_seqlens=cu).loss.item() - ref.item()) < 1e-5
+    sd = CU.recover_original_state_dict_from_checkpoint(dict(model.state_dict()),
+                                                        weight_map={k: "model.safetensors" for k in original},
+                                                        architectures=[arch])
+    assert set(sd) == set(original)
+    for k in original:
+        assert torch.equal(sd[k], original[k]), k
