@@ -1,0 +1,141 @@
+"""Benchmark harness on the CPU: matrix construction, command lines, output scraping, one real tiny run, tables."""
+import json
+import os
+import subprocess
+import sys
+
+import pandas as pd
+import pytest
+import yaml
+
+from fms_acceleration_b200.benchmarks import benchmark as B
+from fms_acceleration_b200.benchmarks import compare_with_reference as CMP
+from fms_acceleration_b200.benchmarks import data_processing as DP
+from fms_acceleration_b200.benchmarks import display_bench_results as DISP
+
+HERE = os.path.dirname(os.path.abspath(B.__file__))
+
+
+@pytest.mark.parametrize("fname", ["scenarios.yaml", "scenarios-orca.yaml", "scenarios-moe.yaml",
+                                   "scenarios-granite.yaml", "scenarios-liger.yaml"])
+def test_shipped_scenarios_reference_known_configs_and_models(fname):
+    from fms_acceleration_b200.models.builder import resolve_config
+
+    files = B.framework_config_files()
+    for sc in B.load_scenarios(os.path.join(HERE, fname)):
+        for fc in sc.framework_configs:
+            assert fc is None or (fc in files and os.path.exists(files[fc])), fc
+        for args in sc.argument_sets():
+            resolve_config(args["model_name_or_path"])
+
+
+def test_matrix_and_command_lines(tmp_path):
+    sc = B.Scenario("s", [None, "accelerated-peft-bnb-foak"],
+                    {"model_name_or_path": ["tiny-llama", "tiny-mixtral"], "target_modules": ["q_proj", "v_proj"],
+                     "learning_rate": 1e-4})
+    exps = B.build_experiments([sc], {"max_steps": 3, "gradient_accumulation_steps": 1}, [1, 2], [4, 6], str(tmp_path),
+                               B.framework_config_files())
+    assert len(exps) == 2 * 2 * 2 * 2
+    e = [x for x in exps if x.num_gpus == 2 and x.framework_config and x.arguments["model_name_or_path"] == "tiny-mixtral"
+         and x.arguments["per_device_train_batch_size"] == 3][0]
+    argv = e.argv()
+    assert argv[1:4] == ["-m", "torch.distributed.run", "--nnodes=1"] and "--nproc-per-node=2" in argv
+    assert argv[argv.index("--master-addr") + 1] == "127.0.0.1"
+    i = argv.index("--target_modules")
+    assert argv[i + 1:i + 3] == ["q_proj", "v_proj"]
+    env = e.environment()
+    assert env["CUDA_VISIBLE_DEVICES"] == "0,1" and env[B.ENV_CONFIG].endswith("sample-configuration.yaml")
+    e.run(dry_run=True)
+    assert "torch.distributed.run" in open(e.path(B.FILE_COMMAND)).read()
+    assert json.load(open(e.path(B.FILE_ARGS)))["framework_config"] == "accelerated-peft-bnb-foak"
+    # 5 cannot be split over 2 GPUs
+    assert all(x.num_gpus == 1 for x in B.build_experiments([sc], {}, [1, 2], [5], str(tmp_path), B.framework_config_files()))
+    with pytest.raises(KeyError):
+        B.build_experiments([B.Scenario("x", ["nope"], {"model_name_or_path": "tiny-llama"})], {}, [1], [4], str(tmp_path),
+                            B.framework_config_files())
+
+
+def test_output_scraping(tmp_path):
+    so = tmp_path / "stdout"
+    so.write_text("noise\n{'loss': 2.5, 'learning_rate': 1e-4, 'epoch': 0.1}\n{'loss': 2.25, 'epoch': 0.2}\n"
+                  "{'train_runtime': 10.0, 'train_tokens_per_second': 1234.5, 'train_loss': 2.3}\n{not a dict}\n")
+    res = B.parse_stdout(str(so))
+    assert res["train_tokens_per_second"] == 1234.5 and res["loss_trace"] == [2.5, 2.25]
+    se = tmp_path / "stderr"
+    se.write_text("warning\nTraceback (most recent call last):\n  File \"x.py\", line 1\nValueError: boom\n"
+                  "Traceback (most recent call last):\n  File \"y\"\n"
+                  "torch.distributed.elastic.multiprocessing.errors.ChildFailedError: \n")
+    tb = B.extract_tracebacks(str(se))
+    assert len(tb) == 1 and tb[0].strip().endswith("ValueError: boom")
+    mem = tmp_path / "mem.csv"
+    mem.write_text("timestamp, name, index, memory.used [MiB]\nt, NVIDIA B200, 0, 100 MiB\nt, NVIDIA B200, 0, 300 MiB\n"
+                   "t, NVIDIA B200, 1, 200 MiB\n")
+    assert B.memory_metrics(str(mem)) == {"mem_nvidia_mem_reserved": 250.0, "gpu_device_name": "NVIDIA B200"}
+
+
+def test_end_to_end_tiny_run_and_tables(tmp_path):
+    scen = tmp_path / "scen.yaml"
+    scen.write_text(yaml.safe_dump({"scenarios": [{"name": "lora", "framework_config": [None], "arguments": {
+        "model_name_or_path": ["tiny-llama"], "peft_method": "lora", "r": 4, "target_modules": ["q_proj", "v_proj"],
+        "max_seq_length": 64, "learning_rate": [1e-3, 2e-3]}}]}))
+    out = tmp_path / "results"
+    rc = B.main(["--scenarios_config_path", str(scen), "--defaults_config_path", os.path.join(HERE, "defaults.yaml"),
+                 "--results_output_path", str(out), "--max_steps", "4", "--effective_batch_size_matrix", "2"])
+    assert rc == 0
+    summary = pd.read_csv(out / B.FILE_SUMMARY)
+    assert len(summary) == 2 and (summary["train_tokens_per_second"] > 0).all()
+    assert json.load(open(out / "exp_0" / B.FILE_RESULTS))["train_loss"] > 0
+    # a second pass keeps finished experiments
+    before = os.path.getmtime(out / "exp_0" / B.FILE_RESULTS)
+    B.main(["--scenarios_config_path", str(scen), "--results_output_path", str(out), "--max_steps", "4",
+            "--effective_batch_size_matrix", "2", "--no_overwrite"])
+    assert os.path.getmtime(out / "exp_0" / B.FILE_RESULTS) == before
+    assert DISP.main([str(out), "--keep_columns", "model_name_or_path"]) == 0
+    table = pd.read_csv(out / "benchmarks.csv")
+    assert "learning_rate" in table.columns and "model_name_or_path" in table.columns and "r" not in table.columns
+    # regression check against itself (no outliers), then against a table that is 2x slower
+    ref = table.copy()
+    ref.to_csv(tmp_path / "ref.csv", index=False)
+    args = ["--result_dir", str(out), "--indices", "framework_config", "learning_rate", "--plot_columns",
+            "train_tokens_per_second", "train_loss"]
+    assert CMP.main(args + ["--reference_benchmark_filepath", str(tmp_path / "ref.csv")]) == 0
+    ref["train_tokens_per_second"] *= 0.5
+    ref.to_csv(tmp_path / "ref2.csv", index=False)
+    assert CMP.main(args + ["--reference_benchmark_filepath", str(tmp_path / "ref2.csv")]) == 1
+    assert len(pd.read_csv(out / "outliers.csv")) == 2
+
+
+def test_data_processing(tmp_path):
+    tok = DP.ByteTokenizer()
+    rec = {"instruction": "Add.", "input": "1 2", "output": "3"}
+    text = DP.build_data_formatting_func(tok)(rec)["output"]
+    assert "### Input:\n1 2" in text and text.endswith("### Response: 3<eos>")
+    assert "### Input" not in DP.build_data_formatting_func(tok)({"instruction": "Hi", "input": "", "output": "x"})["output"]
+    row = DP.build_data_formatting_func(tok, tokenize=True)(rec)
+    n_prompt = row["labels"].count(-100)
+    assert tok.decode(row["input_ids"][n_prompt:]) == " 3<eos>" and row["labels"][n_prompt:] == row["input_ids"][n_prompt:]
+    assert tok.decode(row["input_ids"][:n_prompt]).endswith("### Response:")
+    # chat template + separate response field
+    tmpl = "Q: {{ messages[0]['instruction'] }}\nA:"
+    row = DP.build_data_formatting_func(tok, tokenize=True, chat_template=tmpl, response_template=None,
+                                        response_field="output")(rec)
+    assert tok.decode(row["input_ids"]) == "Q: Add.\nA:3" and row["labels"][-1] == ord("3") and row["labels"][0] == -100
+    with pytest.raises(ValueError):
+        DP.build_data_formatting_func(tok, tokenize=True, response_template=None)
+    # records without the template are dropped from the cache; the cache is reused
+    recs = tmp_path / "r.jsonl"
+    recs.write_text("\n".join(json.dumps(r) for r in [rec, rec]))
+    path = DP.prepare_dataset(DP.read_records(str(recs)), str(tmp_path / "cache"), "t", tok, max_length=4096)
+    rows = json.load(open(path))
+    assert len(rows) == 2 and set(rows[0]) == {"input_ids", "labels"}
+    assert DP.prepare_dataset([], str(tmp_path / "cache"), "t", tok) == path and len(json.load(open(path))) == 2
+
+
+def test_shell_driver_dry_run(tmp_path):
+    out = tmp_path / "res"
+    env = dict(os.environ, DRY_RUN="true")
+    r = subprocess.run(["bash", os.path.join(HERE, "run_benchmarks.sh"), "1 2", "4", str(out),
+                        os.path.join(HERE, "scenarios-moe.yaml")], env=env, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    cmds = [open(out / d / "command.sh").read() for d in os.listdir(out) if d.startswith("exp_")]
+    assert len(cmds) == 24 and any("moe-scattermoe-granite-ep8-foak" in c for c in cmds)
