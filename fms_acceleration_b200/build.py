@@ -58,7 +58,7 @@ def _compile_one(src: str, verbose: bool, ptxas_info: bool) -> str:
     if os.path.exists(obj) and os.path.getmtime(obj) >= stamp:
         return obj
     if src.endswith(".cu"):
-        cmd = [_nvcc(), *NVCC_FLAGS, "-I", CSRC, "-c", path, "-o", obj]
+        cmd = [_nvcc(), *NVCC_FLAGS, *os.environ.get("FMSB_NVCC_EXTRA", "").split(), "-I", CSRC, "-c", path, "-o", obj]
         if ptxas_info:
             cmd[1:1] = ["-Xptxas", "-v"]
     else:

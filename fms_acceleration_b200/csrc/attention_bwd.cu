@@ -75,6 +75,15 @@ __device__ __forceinline__ void b2_store_row_chunk(uint16_t* dst, const uint32_t
   }
 }
 
+// Optional timeline trace (compile with -DFMSB_TRACE): CTA (0, 0) of the dK/dV kernel records clock64() at the
+// hand-off points of its MMA issuer and of one compute thread; read back with fmsb_attn_trace_read.
+#ifdef FMSB_TRACE
+__device__ long long g_trace[8192];
+#define FMSB_TRACE_AT(cond, slot) do { if ((cond) && (slot) < 8192) g_trace[(slot)] = clock64(); } while (0)
+#else
+#define FMSB_TRACE_AT(cond, slot) do { } while (0)
+#endif
+
 __device__ __forceinline__ void compute_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 // tensor-memory column of K-step `ks` (16 contraction elements = 8 columns) of a packed 16-bit
@@ -170,51 +179,60 @@ attn_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc_f16(128, 64, p.fmt, 0, 0);
       const uint32_t idesc_g = make_idesc_f16(128, D, p.fmt, 0, 1);
+      const SmemDescBase dK = make_smem_desc_base(sK, 16, 1024), dV = make_smem_desc_base(sV, 16, 1024);
       // S^T and dP^T of query half `h` of the block in stage `s`
       auto issue_scores = [&](int s, int h) {
+        const SmemDescBase dQ = make_smem_desc_base(sQ(s) + h * Cfg::kRowHalf, 16, 1024);
+        const SmemDescBase ddO = make_smem_desc_base(sdO(s) + h * Cfg::kRowHalf, 16, 1024);
+        const uint32_t ts = tS(h), tp = tdP(h);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t off = (ks / 4) * Cfg::kHalfBytes + (ks % 4) * 32;
-          tc_mma_f16(tS(h), make_smem_desc(sK + off, 16, 1024),
-                     make_smem_desc(sQ(s) + off + h * Cfg::kRowHalf, 16, 1024), idesc_s, ks != 0);
+          tc_mma_f16(ts, smem_desc_at(dK, off), smem_desc_at(dQ, off), idesc_s, ks != 0);
         }
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t off = (ks / 4) * Cfg::kHalfBytes + (ks % 4) * 32;
-          tc_mma_f16(tdP(h), make_smem_desc(sV + off, 16, 1024),
-                     make_smem_desc(sdO(s) + off + h * Cfg::kRowHalf, 16, 1024), idesc_s, ks != 0);
+          tc_mma_f16(tp, smem_desc_at(dV, off), smem_desc_at(ddO, off), idesc_s, ks != 0);
         }
         tc_commit(bar_s_full(h));
       };
       // dV += P^T dO, dK += dS^T Q over the 64 queries of half `h` (4 steps of 16)
       auto issue_acc = [&](int s, int h, bool first) {
+        const SmemDescBase bdO = make_smem_desc_base(sdO(s) + h * 4 * 2048, Cfg::kHalfBytes, 1024);
+        const SmemDescBase bQ = make_smem_desc_base(sQ(s) + h * 4 * 2048, Cfg::kHalfBytes, 1024);
+        const uint32_t ts = tS(h), tp = tdP(h);
+        tc_mma_f16_ts(tdV, ts + packed_col(0), smem_desc_at(bdO, 0), idesc_g, first ? 0u : 1u);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          const uint64_t b_do = make_smem_desc(sdO(s) + (h * 4 + ks) * 2048, Cfg::kHalfBytes, 1024);
-          tc_mma_f16_ts(tdV, tS(h) + packed_col(ks), b_do, idesc_g, !(first && ks == 0));
-        }
+        for (int ks = 1; ks < 4; ++ks) tc_mma_f16_ts(tdV, ts + packed_col(ks), smem_desc_at(bdO, ks * 2048), idesc_g, 1u);
+        tc_mma_f16_ts(tdK, tp + packed_col(0), smem_desc_at(bQ, 0), idesc_g, first ? 0u : 1u);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          const uint64_t b_q = make_smem_desc(sQ(s) + (h * 4 + ks) * 2048, Cfg::kHalfBytes, 1024);
-          tc_mma_f16_ts(tdK, tdP(h) + packed_col(ks), b_q, idesc_g, !(first && ks == 0));
-        }
+        for (int ks = 1; ks < 4; ++ks) tc_mma_f16_ts(tdK, tp + packed_col(ks), smem_desc_at(bQ, ks * 2048), idesc_g, 1u);
       };
       bool ok = mbar_wait(bar_kv, 0, p.status, kTimeoutMma);
+      const bool tr = blockIdx.x == 0 && blockIdx.y == 0;
       for (int it = 0; it < niter && ok; ++it) {
         const int s = it & 1;
         if (!mbar_wait(bar_qdo_full(s), (it >> 1) & 1, p.status, kTimeoutMma)) { ok = false; break; }
         tc_fence_after();
+        FMSB_TRACE_AT(tr, 4096 + 8 * it + 0);
         issue_scores(s, 0);
+        FMSB_TRACE_AT(tr, 4096 + 8 * it + 1);
         if (it > 0) {
           if (!mbar_wait(bar_p_full(1), (it - 1) & 1, p.status, kTimeoutMma)) { ok = false; break; }
           tc_fence_after();
+          FMSB_TRACE_AT(tr, 4096 + 8 * it + 2);
           issue_acc((it - 1) & 1, 1, false);
           tc_commit(bar_qdo_empty((it - 1) & 1));
+          FMSB_TRACE_AT(tr, 4096 + 8 * it + 3);
         }
         issue_scores(s, 1);
+        FMSB_TRACE_AT(tr, 4096 + 8 * it + 4);
         if (!mbar_wait(bar_p_full(0), it & 1, p.status, kTimeoutMma)) { ok = false; break; }
         tc_fence_after();
+        FMSB_TRACE_AT(tr, 4096 + 8 * it + 5);
         issue_acc(s, 0, it == 0);
+        FMSB_TRACE_AT(tr, 4096 + 8 * it + 6);
       }
       if (ok && mbar_wait(bar_p_full(1), (niter - 1) & 1, p.status, kTimeoutMma)) {
         tc_fence_after();
@@ -267,13 +285,17 @@ attn_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const bool need_mask = !(q0 >= k0 + B2_BK - 1 && bi[127] <= k0);
 #pragma unroll 1
       for (int h = 0; h < 2 && ok; ++h) {
+        const bool tr = blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 64;
+        FMSB_TRACE_AT(tr, 8 * (2 * it + h) + 0);
         if (!mbar_wait(bar_s_full(h), it & 1, p.status, kTimeoutEpilogue)) { ok = false; break; }
         tc_fence_after();
+        FMSB_TRACE_AT(tr, 8 * (2 * it + h) + 1);
         const int c0 = h * 64 + chalf * 32;  // first query column of this thread's slice
         uint32_t rs[32], rp[32];
         tmem_ld_32x32(tS(h) + lane_addr + chalf * 32, rs);
         tmem_ld_32x32(tdP(h) + lane_addr + chalf * 32, rp);
         tmem_ld_wait();
+        FMSB_TRACE_AT(tr, 8 * (2 * it + h) + 2);
         uint32_t pk[16], dk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
@@ -298,12 +320,15 @@ attn_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           dk[i / 2 + 1] =
               b2_pack2(pv[2] * (__uint_as_float(rp[i + 2]) - d4.z), pv[3] * (__uint_as_float(rp[i + 3]) - d4.w), p.fmt);
         }
+        FMSB_TRACE_AT(tr, 8 * (2 * it + h) + 3);
         tmem_st_32x16(tS(h) + lane_addr + chalf * 32, pk);
         tmem_st_32x16(tdP(h) + lane_addr + chalf * 32, dk);
         tmem_st_wait();
+        FMSB_TRACE_AT(tr, 8 * (2 * it + h) + 4);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_p_full(h));
+        FMSB_TRACE_AT(tr, 8 * (2 * it + h) + 5);
       }
       if (more) publish((it + 1) & 1, nf, ni);
       compute_bar_sync();
@@ -418,27 +443,29 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc_f16(128, 64, p.fmt, 0, 0);
       const uint32_t idesc_g = make_idesc_f16(128, D, p.fmt, 0, 1);
+      const SmemDescBase dQd = make_smem_desc_base(sQ, 16, 1024), ddO = make_smem_desc_base(sdO, 16, 1024);
       auto issue_scores = [&](int s, int h) {
+        const SmemDescBase dKh = make_smem_desc_base(sK(s) + h * Cfg::kRowHalf, 16, 1024);
+        const SmemDescBase dVh = make_smem_desc_base(sV(s) + h * Cfg::kRowHalf, 16, 1024);
+        const uint32_t ts = tS(h), tp = tdP(h);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t off = (ks / 4) * Cfg::kHalfBytes + (ks % 4) * 32;
-          tc_mma_f16(tS(h), make_smem_desc(sQ + off, 16, 1024),
-                     make_smem_desc(sK(s) + off + h * Cfg::kRowHalf, 16, 1024), idesc_s, ks != 0);
+          tc_mma_f16(ts, smem_desc_at(dQd, off), smem_desc_at(dKh, off), idesc_s, ks != 0);
         }
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t off = (ks / 4) * Cfg::kHalfBytes + (ks % 4) * 32;
-          tc_mma_f16(tdP(h), make_smem_desc(sdO + off, 16, 1024),
-                     make_smem_desc(sV(s) + off + h * Cfg::kRowHalf, 16, 1024), idesc_s, ks != 0);
+          tc_mma_f16(tp, smem_desc_at(ddO, off), smem_desc_at(dVh, off), idesc_s, ks != 0);
         }
         tc_commit(bar_s_full(h));
       };
       auto issue_acc = [&](int s, int h, bool first) {
+        const SmemDescBase bK = make_smem_desc_base(sK(s) + h * 4 * 2048, Cfg::kHalfBytes, 1024);
+        const uint32_t tp = tdP(h);
+        tc_mma_f16_ts(tdQ, tp + packed_col(0), smem_desc_at(bK, 0), idesc_g, first ? 0u : 1u);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          const uint64_t b_k = make_smem_desc(sK(s) + (h * 4 + ks) * 2048, Cfg::kHalfBytes, 1024);
-          tc_mma_f16_ts(tdQ, tdP(h) + packed_col(ks), b_k, idesc_g, !(first && ks == 0));
-        }
+        for (int ks = 1; ks < 4; ++ks) tc_mma_f16_ts(tdQ, tp + packed_col(ks), smem_desc_at(bK, ks * 2048), idesc_g, 1u);
       };
       bool ok = mbar_wait(bar_q, 0, p.status, kTimeoutMma);
       for (int j = 0; j < nblk && ok; ++j) {
@@ -533,6 +560,13 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 }  // namespace fmsb
 
 using namespace fmsb;
+
+#ifdef FMSB_TRACE
+extern "C" int fmsb_attn_trace_read(long long* host, int n) {
+  if (n > 8192) n = 8192;
+  return (int)cudaMemcpyFromSymbol(host, fmsb::g_trace, sizeof(long long) * n);
+}
+#endif
 
 static int b2_make_maps(CUtensorMap* tq, CUtensorMap* tk, CUtensorMap* tv, CUtensorMap* tdo, const void* q,
                         long long ldq, const void* k, long long ldk, const void* v, long long ldv, const void* dout,

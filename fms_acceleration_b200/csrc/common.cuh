@@ -85,16 +85,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false (after recording `code`) when the budget ran out.
+// Bounded wait.  Returns false (after recording `code`) when the budget ran out.  The fast path is a tight poll
+// of the barrier; the clock is read every 64 polls and the (global-memory) status word only once about every
+// 2^20 cycles, so that a waiter is never stuck behind a long-latency load when its barrier completes.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
+  long long next_check = t0 + (1LL << 20);
   while (true) {
 #pragma unroll 1
-    for (int i = 0; i < 256; ++i) {
+    for (int i = 0; i < 64; ++i) {
       if (mbar_try_wait(bar, parity)) return true;
     }
-    if (clock64() - t0 > kWaitBudgetCycles) {
+    const long long now = clock64();
+    if (now < next_check) continue;
+    next_check = now + (1LL << 20);
+    if (now - t0 > kWaitBudgetCycles) {
       report_status(status, code);
       return false;
     }
@@ -254,6 +260,24 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t 
   d |= static_cast<uint64_t>(1) << 46;  // descriptor version of this architecture
   d |= static_cast<uint64_t>(2) << 61;  // 128-byte swizzle
   return d;
+}
+
+// The same descriptor split into its two 32-bit words.  Only the start-address field (bits 0-13, address >> 4)
+// changes between the MMAs of one tile, so an issue loop builds the base once and adds a byte offset to the low
+// word per instruction (one integer add) instead of re-assembling 64 bits; the time between two tcgen05.mma of
+// the issuing thread is what bounds tensor-pipe utilisation for short instructions.
+struct SmemDescBase {
+  uint32_t lo, hi;
+};
+__device__ __forceinline__ SmemDescBase make_smem_desc_base(uint32_t smem_addr, uint32_t lbo_bytes,
+                                                            uint32_t sbo_bytes) {
+  SmemDescBase d;
+  d.lo = ((smem_addr & 0x3FFFF) >> 4) | (((lbo_bytes >> 4) & 0x3FFF) << 16);
+  d.hi = ((sbo_bytes >> 4) & 0x3FFF) | (1u << 14) | (2u << 29);
+  return d;
+}
+__device__ __forceinline__ uint64_t smem_desc_at(const SmemDescBase& d, uint32_t byte_offset) {
+  return (static_cast<uint64_t>(d.hi) << 32) | static_cast<uint64_t>(d.lo + (byte_offset >> 4));
 }
 
 // Instruction descriptor, kind::f16, fp32 accumulate.  fmt: 0 = fp16, 1 = bf16.
