@@ -71,6 +71,26 @@ def load_fsdp_model(fsdp_plugin, accelerator, model: torch.nn.Module, input_dir:
     MODEL_INDEX = model_index
 
 
+def _materialize_optimizer_state(optimizer) -> None:
+    """A fresh optimizer has no per-parameter state, and a template without those entries makes the checkpoint
+    reader skip them.  Create them with one step at learning rate 0 on zero gradients (parameters are unchanged)."""
+    if len(optimizer.state) > 0:
+        return
+    saved = [g["lr"] for g in optimizer.param_groups]
+    touched = []
+    for g in optimizer.param_groups:
+        g["lr"] = 0.0 if not torch.is_tensor(g["lr"]) else torch.zeros_like(g["lr"])
+        for p in g["params"]:
+            if p.requires_grad and p.grad is None:
+                p.grad = torch.zeros_like(p)
+                touched.append(p)
+    optimizer.step()
+    for p in touched:
+        p.grad = None
+    for g, lr in zip(optimizer.param_groups, saved):
+        g["lr"] = lr
+
+
 def load_fsdp_optimizer(fsdp_plugin, accelerator, optimizer, model: torch.nn.Module, input_dir: str,
                         optimizer_index: int = 0, lora_only: Optional[bool] = None):
     import torch.distributed.checkpoint as dcp
@@ -84,6 +104,7 @@ def load_fsdp_optimizer(fsdp_plugin, accelerator, optimizer, model: torch.nn.Mod
     msd = {KEY_MODEL: _model_state(model, lora_only)}
     dcp.load(msd, storage_reader=dcp.FileSystemReader(os.path.join(input_dir, f"{FSDP_MODEL_NAME}_{midx}")), no_dist=no_dist)
     model.load_state_dict(msd[KEY_MODEL], strict=not lora_only)
+    _materialize_optimizer_state(optimizer)
     osd = {KEY_OPTIMIZER: optimizer.state_dict()}
     dcp.load(osd, storage_reader=dcp.FileSystemReader(os.path.join(input_dir, f"{OPTIMIZER_NAME}_{optimizer_index}")),
              no_dist=no_dist)

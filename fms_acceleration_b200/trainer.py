@@ -137,4 +137,88 @@ class Trainer:
             loss = self.train_step(b)
             losses.append(float(loss))
             self.log_history.append({"step": self.global_step, "loss": losses[-1]})
+            if self.args.save_steps and self.global_step % self.args.save_steps == 0:
+                self.save_checkpoint()
         return losses
+
+    # ------------------------------------------------------------------ checkpoint / resume
+    def _is_lora(self) -> bool:
+        return any("lora_" in n for n, _ in self.model.named_parameters())
+
+    def save_checkpoint(self, output_dir: Optional[str] = None, scheduler=None) -> str:
+        """Write ``<output_dir>/checkpoint-<step>/``: the model (only the adapters for a LoRA run) and the optimizer as
+        torch distributed-checkpoint directories named like accelerate's FSDP checkpoints
+        (``pytorch_model_fsdp_0`` / ``optimizer_0``, cf. fms_acceleration_moe/utils/checkpoint_utils.py:129-158 of the
+        reference), ``trainer_state.json``, per-rank RNG state, and for LoRA runs a PEFT-style
+        ``adapter_model.safetensors`` + ``adapter_config.json``.  Callbacks get ``on_save`` (the data-mixing plugin
+        stores its loader state there)."""
+        import json
+
+        from .plugins.moe.utils import checkpoint_utils as CU
+
+        rank = torch.distributed.get_rank() if torch.distributed.is_available() and torch.distributed.is_initialized() else 0
+        root = output_dir or self.args.output_dir
+        ckpt = os.path.join(root, f"checkpoint-{self.global_step}")
+        os.makedirs(ckpt, exist_ok=True)
+        lora = self._is_lora()
+        CU.save_fsdp_model(None, None, self.model, ckpt, 0)
+        CU.save_fsdp_optimizer(None, None, self.optimizer, self.model, ckpt, 0, lora_only=lora)
+        torch.save({"cpu": torch.get_rng_state(),
+                    "cuda": torch.cuda.get_rng_state() if torch.cuda.is_available() else None},
+                   os.path.join(ckpt, f"rng_state_{rank}.pth"))
+        if rank == 0:
+            with open(os.path.join(ckpt, "trainer_state.json"), "w", encoding="utf-8") as fh:
+                json.dump({"global_step": self.global_step, "log_history": self.log_history}, fh, indent=1)
+            if scheduler is not None:
+                torch.save(scheduler.state_dict(), os.path.join(ckpt, "scheduler.pt"))
+            if lora:
+                from safetensors.torch import save_file
+
+                sd = {k: v.detach().cpu().contiguous() for k, v in self.model.state_dict().items() if "lora_" in k}
+                save_file(sd, os.path.join(ckpt, "adapter_model.safetensors"), metadata={"format": "pt"})
+                cfg = getattr(self.model, "peft_config", None)
+                cfg = cfg.get("default") if isinstance(cfg, dict) else cfg
+                if cfg is not None and hasattr(cfg, "to_dict"):
+                    with open(os.path.join(ckpt, "adapter_config.json"), "w", encoding="utf-8") as fh:
+                        json.dump(cfg.to_dict(), fh, indent=1)
+        state = type("State", (), {"global_step": self.global_step})()
+        for cb in self.callbacks:
+            if hasattr(cb, "on_save"):
+                cb.on_save(self.args, state, None)
+        return ckpt
+
+    def load_checkpoint(self, ckpt: str, scheduler=None) -> None:
+        """Resume model (or adapters), optimizer, step counter, log history and RNG state from ``save_checkpoint``."""
+        import json
+
+        from .plugins.moe.utils import checkpoint_utils as CU
+
+        rank = torch.distributed.get_rank() if torch.distributed.is_available() and torch.distributed.is_initialized() else 0
+        from torch.distributed.checkpoint.api import CheckpointException
+
+        try:
+            CU.load_fsdp_model(None, None, self.model, ckpt, 0)
+            CU.load_fsdp_optimizer(None, None, self.optimizer, self.model, ckpt, 0, lora_only=self._is_lora())
+        except CheckpointException as exc:  # derives from BaseException: turn it into an ordinary error
+            raise RuntimeError(f"checkpoint {ckpt!r} is incomplete or damaged: {str(exc).splitlines()[0]}") from exc
+        with open(os.path.join(ckpt, "trainer_state.json"), encoding="utf-8") as fh:
+            st = json.load(fh)
+        self.global_step = int(st["global_step"])
+        self.log_history = list(st.get("log_history", []))
+        rng_file = os.path.join(ckpt, f"rng_state_{rank}.pth")
+        if os.path.exists(rng_file):
+            rng = torch.load(rng_file, weights_only=False)
+            torch.set_rng_state(rng["cpu"])
+            if rng.get("cuda") is not None and torch.cuda.is_available():
+                torch.cuda.set_rng_state(rng["cuda"])
+        if scheduler is not None and os.path.exists(os.path.join(ckpt, "scheduler.pt")):
+            scheduler.load_state_dict(torch.load(os.path.join(ckpt, "scheduler.pt"), weights_only=False))
+
+    @staticmethod
+    def latest_checkpoint(output_dir: str) -> Optional[str]:
+        best, best_step = None, -1
+        if os.path.isdir(output_dir):
+            for name in os.listdir(output_dir):
+                if name.startswith("checkpoint-") and name[11:].isdigit() and int(name[11:]) > best_step:
+                    best, best_step = os.path.join(output_dir, name), int(name[11:])
+        return best
