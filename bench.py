@@ -93,82 +93,116 @@ class ClockSampler:
         return out
 
 
-def write_framework_config(path: str) -> None:
-    import yaml
-
-    cfg = {"plugins": {
-        "peft": {"quantization": {
-            "bitsandbytes": {"quant_type": "nf4", "no_peft_model": False},
-            "fused_ops_and_kernels": {"base_layer": "bitsandbytes", "fused_lora": True, "fast_loss": "fused_ce_liger",
-                                      "fast_rms_layernorm": True, "fast_rope_embeddings": True}}},
-        "training": {"attention": {"padding_free": {"method": "huggingface"}}},
-    }}
-    with open(path, "w", encoding="utf-8") as fh:
-        yaml.safe_dump(cfg, fh)
+# ------------------------------------------------------------------------------------------- benchmark configs
+# name -> (metric label, model preset, per-device batch, sequence length, published A100 number or None)
+CONFIGS = {
+    "mistral-qlora": ("train tokens/sec, Mistral-7B NF4 QLoRA", "mistral-7b", 4, 4096, 4128.0),
+    "granite-moe": ("train tokens/sec, Granite-3B-A800M ScatterMoE full fine-tune", "granite-3b-a800m", 8, 2048, 6216.0),
+    "llama70b-gptq": ("train tokens/sec, Llama-2-70B GPTQ-LoRA", "llama2-70b", 1, 4096, 496.0),
+    "mamba-cp": ("train tokens/sec, Mamba2-2.7B context parallel", "mamba2-2.7b", 1, 65536, None),
+}
+FOAK = {"fused_lora": True, "fast_loss": "fused_ce_liger", "fast_rms_layernorm": True, "fast_rope_embeddings": True}
 
 
-def main() -> int:
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--model", default="mistral-7b")
-    ap.add_argument("--batch", type=int, default=4, help="per-device batch")
-    ap.add_argument("--seq", type=int, default=4096)
-    ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (result marked invalid)")
-    args = ap.parse_args()
-    if args.impl == "reference":
-        return reference_arm(args)
-    if args.warmup < 3:
-        args.warmup = 3
+def framework_config(name: str, world: int) -> dict:
+    if name == "mistral-qlora":
+        return {"peft": {"quantization": {"bitsandbytes": {"quant_type": "nf4", "no_peft_model": False},
+                                          "fused_ops_and_kernels": dict(FOAK, base_layer="bitsandbytes")}},
+                "training": {"attention": {"padding_free": {"method": "huggingface"}}}}
+    if name == "llama70b-gptq":
+        return {"peft": {"quantization": {"auto_gptq": {"kernel": "triton_v2", "from_quantized": True},
+                                          "fused_ops_and_kernels": dict(FOAK, base_layer="auto_gptq")}},
+                "training": {"attention": {"padding_free": {"method": "huggingface"}}}}
+    if name == "granite-moe":
+        ep = max(d for d in (1, 2, 4, 8) if world % d == 0 and d <= world)
+        foak = {k: v for k, v in FOAK.items() if k != "fused_lora"}
+        return {"training": {"moe": {"scattermoe": {"ep_degree": ep}},
+                             "attention": {"padding_free": {"method": "huggingface"}},
+                             "fused_ops_and_kernels": foak}}
+    if name == "mamba-cp":
+        cfg = {"training": {"fused_ops_and_kernels": {k: v for k, v in FOAK.items() if k != "fused_lora"}}}
+        if world > 1:
+            cfg["training"]["mamba"] = {"cp": {"degree": world, "mamba_impl": "allgather", "mamba_recompute": False}}
+        return cfg
+    raise KeyError(name)
 
+
+def make_batches(name, cfg, batch, seq, rank, world, n_batches):
+    import torch
+
+    from fms_acceleration_b200.trainer import synthetic_packed_batch
+
+    if name != "mamba-cp":
+        lo = min(128, seq)
+        return [synthetic_packed_batch(cfg.vocab_size, batch, seq, (lo, seq), seed=1000 * rank + i)
+                for i in range(n_batches)], batch * seq * world
+    # one sequence of `seq` tokens split evenly over the context-parallel ranks (same tokens on every rank's view)
+    out = []
+    per = seq // world
+    for i in range(n_batches):
+        g = torch.Generator().manual_seed(77 + i)
+        ids = torch.randint(0, cfg.vocab_size, (1, seq), generator=g, dtype=torch.int64)
+        sl = ids[:, rank * per:(rank + 1) * per].contiguous()
+        b = {"input_ids": sl, "labels": sl.clone()}
+        if torch.cuda.is_available():
+            b = {k: v.pin_memory() for k, v in b.items()}
+        out.append(b)
+    return out, seq
+
+
+def run_config(name: str, args, ctx) -> dict:
+    """Build the model through the framework's public lifecycle and time `args.steps` optimizer steps."""
     import torch
     import torch.distributed as dist
-
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+    import yaml
 
     from fms_acceleration_b200 import _native as NV
+    from fms_acceleration_b200.compat import Accelerator
     from fms_acceleration_b200.framework import AccelerationFramework
-    from fms_acceleration_b200.models.builder import resolve_config
+    from fms_acceleration_b200.models.builder import build_model, resolve_config
     from fms_acceleration_b200.nn import LoraConfig
-    from fms_acceleration_b200.trainer import TrainArgs, Trainer, synthetic_packed_batch, to_device
-    import fms_acceleration_b200.plugins  # registers the plugins  # noqa: F401
+    from fms_acceleration_b200.trainer import TrainArgs, Trainer, to_device
 
-    cfg = resolve_config(args.model)
+    rank, local_rank, world, dev = ctx["rank"], ctx["local_rank"], ctx["world"], ctx["dev"]
+    metric, preset, batch, seq, published = CONFIGS[name]
+    batch = args.batch or batch
+    seq = args.seq or seq
+    cfg = resolve_config(args.model or preset)
     if args.layers:
         cfg.num_hidden_layers = args.layers
+    dtype = torch.float16 if name == "llama70b-gptq" and args.fp16 else torch.bfloat16
     with tempfile.TemporaryDirectory() as td:
         cfg_path = os.path.join(td, "accel.yaml")
-        write_framework_config(cfg_path)
+        with open(cfg_path, "w", encoding="utf-8") as fh:
+            yaml.safe_dump({"plugins": framework_config(name, world)}, fh)
+        AccelerationFramework.reset()
         framework = AccelerationFramework(cfg_path)
-    train_args = TrainArgs(per_device_train_batch_size=args.batch, learning_rate=1e-4, bf16=True,
-                           max_seq_length=args.seq, padding_free=True, world_size=world,
+    train_args = TrainArgs(per_device_train_batch_size=batch, learning_rate=1e-4 if "lora" in metric.lower() else 2e-5,
+                           bf16=dtype == torch.bfloat16, fp16=dtype == torch.float16, max_seq_length=seq,
+                           padding_free=name != "mamba-cp", world_size=world,
                            parallel_mode="DISTRIBUTED" if world > 1 else "NOT_DISTRIBUTED")
     torch.manual_seed(1234)
-    model = framework.model_loader(cfg, torch_dtype=torch.bfloat16, device=dev)
-    peft_config = LoraConfig(r=16, lora_alpha=16, lora_dropout=0.0,
-                             target_modules=["q_proj", "k_proj", "v_proj", "o_proj"])
+    if framework.requires_custom_loading:
+        model = framework.model_loader(cfg, torch_dtype=dtype, device=dev)
+    else:
+        model = build_model(cfg, device=dev, dtype=dtype, seed=1234)
+    peft_config = None
+    if name in ("mistral-qlora", "llama70b-gptq"):
+        peft_config = LoraConfig(r=16, lora_alpha=16, lora_dropout=0.0,
+                                 target_modules=["q_proj", "k_proj", "v_proj", "o_proj"])
     model, _ = framework.augmentation(model, train_args, modifiable_args=(peft_config,))
-    from fms_acceleration_b200.compat import Accelerator
-
     accelerator = Accelerator(device=dev)
     callbacks = framework.get_callbacks_and_ready_for_train(model, accelerator)
     engine = getattr(accelerator, "engine", None)
+    if engine is None and world > 1:
+        from fms_acceleration_b200.parallel.engine import install_engine
+
+        engine = install_engine(model, accelerator, shard_frozen=False)
     trainer = Trainer(model, train_args, engine=engine, callbacks=callbacks)
 
     n_batches = 4
-    host_batches = [synthetic_packed_batch(cfg.vocab_size, args.batch, args.seq, (128, 4096),
-                                           seed=1000 * rank + i) for i in range(n_batches)]
+    host_batches, tokens_per_step = make_batches(name, cfg, batch, seq, rank, world, n_batches)
     dev_batches = [to_device(b, dev) for b in host_batches]
-    tokens_per_step = args.batch * args.seq * world
 
     def barrier():
         if world > 1:
@@ -210,26 +244,93 @@ def main() -> int:
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_ms = float(t[0]), float(t[1])
+    value = tokens_per_step * args.steps / (ms / 1e3)
+    e2e_value = tokens_per_step * args.steps / (e2e_ms / 1e3)
+    par = {"mistral-qlora": f"fsdp{world}", "llama70b-gptq": f"fsdp{world}",
+           "granite-moe": f"ep{framework_config(name, world)['training']['moe']['scattermoe']['ep_degree']}"
+                          f"xdp{world}" if name == "granite-moe" else "", "mamba-cp": f"cp{world}"}[name]
+    line = {
+        "metric": metric, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "strong" if name == "mamba-cp" else "weak",
+        "vs_baseline": (value / world / published) if published else None,
+        "dtype": "fp16" if dtype == torch.float16 else "bf16",
+        "data": "synthetic uniform-random tokens, random-init weights of the named architecture",
+        "config": {"model": (args.model or preset) + ("" if not args.layers else f" (INVALID: {args.layers} layers)"),
+                   "global_batch": batch * world if name != "mamba-cp" else 1, "seq_len": seq,
+                   "parallelism": par if world > 1 else "single",
+                   "l2": "step working set (tens of GB) far exceeds the 126 MB L2; no explicit flush"},
+        "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+                "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": launches,
+        "final_loss": last,
+        "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30,
+    }
+    if name == "mistral-qlora":
+        line["config"].update({"lora": "r16 a16 qkvo", "packing": "padding-free docs U[128,4096]"})
+        line["vs_baseline"] = value / world / published  # published number is per device
+    # release everything before another configuration is built in the same process
+    del trainer, model, dev_batches, engine, accelerator, callbacks
+    import gc
+
+    gc.collect()
+    torch.cuda.empty_cache()
+    torch.cuda.reset_peak_memory_stats()
+    return line
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--config", default="mistral-qlora", choices=sorted(CONFIGS))
+    ap.add_argument("--also", nargs="*", default=None, choices=sorted(CONFIGS),
+                    help="further configurations to time in the same run (reported under 'secondary'); default: "
+                         "granite-moe next to the headline configuration")
+    ap.add_argument("--model", default=None, help="override the model preset of the configuration")
+    ap.add_argument("--batch", type=int, default=0, help="per-device batch (0: the configuration's)")
+    ap.add_argument("--seq", type=int, default=0)
+    ap.add_argument("--fp16", action="store_true")
+    ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (result marked invalid)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    import fms_acceleration_b200.plugins  # registers the plugins  # noqa: F401
+
+    ctx = {"rank": rank, "local_rank": local_rank, "world": world, "dev": dev}
+    line = run_config(args.config, args, ctx)
+    also = args.also if args.also is not None else (["granite-moe"] if args.config == "mistral-qlora" and not args.layers
+                                                    and not args.model else [])
+    secondary = []
+    for name in also:
+        if name == args.config:
+            continue
+        sub = argparse.Namespace(**vars(args))
+        sub.batch, sub.seq, sub.model = 0, 0, None
+        try:
+            secondary.append(run_config(name, sub, ctx))
+        except Exception as exc:  # the headline number must survive a failure of an extra configuration
+            secondary.append({"metric": CONFIGS[name][0], "error": f"{type(exc).__name__}: {exc}"[:300]})
+    if secondary:
+        line["secondary"] = secondary
     if rank == 0:
-        value = tokens_per_step * args.steps / (ms / 1e3)
-        e2e_value = tokens_per_step * args.steps / (e2e_ms / 1e3)
-        line = {
-            "metric": "train tokens/sec, Mistral-7B NF4 QLoRA", "value": value, "unit": "tokens/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": value / BASELINE_TOK_S, "dtype": "bf16",
-            "data": "synthetic uniform-random tokens, random-init weights quantised to NF4",
-            "config": {"model": args.model + ("" if not args.layers else f" (INVALID: {args.layers} layers)"),
-                       "global_batch": args.batch * world, "seq_len": args.seq,
-                       "parallelism": f"fsdp{world}" if world > 1 else "single",
-                       "lora": "r16 a16 qkvo", "packing": "padding-free docs U[128,4096]",
-                       "l2": "step working set (tens of GB) far exceeds the 126 MB L2; no explicit flush"},
-            "clocks": clocks,
-            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
-                    "ms_per_step": e2e_ms / args.steps},
-            "gpu_launches": launches,
-            "final_loss": last,
-            "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30,
-        }
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -77,6 +77,13 @@ class AccelerationFramework:
     active_plugins: List[Tuple[str, AccelerationPlugin]] = []
     plugins_require_custom_loading: List[str] = []
 
+    @classmethod
+    def reset(cls) -> None:
+        """Forget the plugins activated by an earlier instance.  The active lists are class-level (one framework per
+        process, as in the reference); a process that configures a second framework calls this first."""
+        cls.active_plugins = []
+        cls.plugins_require_custom_loading = []
+
     def __init__(self, configuration_file: Optional[str] = None, require_packages_check: bool = True):
         env_file = os.environ.get(ACCELERATION_FRAMEWORK_ENV_KEY)
         if configuration_file is None and env_file is None:

@@ -140,10 +140,11 @@ class _FusedLinearCE(torch.autograd.Function):
         dw = torch.zeros(V, H, dtype=torch.float32, device=x.device) if need_dw else None
         loss_rows = torch.empty(T, dtype=torch.float32, device=x.device)
         C = _chunk_rows(T, V, x.element_size())
-        logits = torch.empty(C, V, dtype=x.dtype, device=x.device)
+        # rows of the logits chunk start on 16-byte boundaries whatever the vocabulary size (49155 for Granite)
+        logits = torch.empty(C, (V + 7) // 8 * 8, dtype=x.dtype, device=x.device)
         for s in range(0, T, C):
             e = min(T, s + C)
-            lg = logits[: e - s]
+            lg = logits[: e - s, :V]
             gemm(x[s:e], weight, out=lg)
             l, _ = ce_forward(lg, lab[s:e], ignore_index, label_smoothing, write_grad=True, scale=scale)
             loss_rows[s:e] = l

@@ -47,6 +47,7 @@ class FastKernelsAccelerationPlugin(AccelerationPlugin):
     restricted_model_archs = [
         "GraniteForCausalLM", "GraniteMoeForCausalLM", "GPTBigCodeForCausalLM", "MixtralForCausalLM",
         "LlamaForCausalLM", "MistralForCausalLM", "GraniteMoeSharedForCausalLM", "GraniteMoeHybridForCausalLM",
+        "Mamba2ForCausalLM",  # in-tree Mamba2: fused loss (its scan / conv / norm kernels are always the native ones)
     ]
 
     def __init__(self, configurations: Dict[str, Dict]):

@@ -45,6 +45,11 @@ class AutoGPTQAccelerationPlugin(AccelerationPlugin):
         if device is None:
             device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else "cpu"
         quantize_config = kwargs.get("quantize_config")
+        is_dir = isinstance(model_name, str) and os.path.isdir(model_name)
+        if quantize_config is None and not is_dir:
+            # an architecture preset instead of a checkpoint: synthetic 4-bit weights, group size 128, symmetric,
+            # sequential groups (the layout of the published GPTQ checkpoints the reference benchmarks)
+            quantize_config = QuantizeConfig(bits=4, group_size=128, desc_act=False, sym=True)
         model = GPTQModel.from_quantized(model_name, quantize_config=quantize_config, torch_dtype=torch_dtype,
                                          device=device, low_cpu_mem_usage=kwargs.get("low_cpu_mem_usage", False))
         inner = getattr(model, "model", model)

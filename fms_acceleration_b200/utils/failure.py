@@ -12,7 +12,8 @@ stalled is noticed *before* the next kernel that would wait for it is launched:
   propagates, so the survivors stop with a clear error instead of running into their wait budgets;
 * :meth:`Heartbeat.rendezvous` is the host-side gate in front of a step's first collective.
 
-The store is any ``torch.distributed`` store (TCPStore from the default process group, FileStore, HashStore); nothing
+The rank that hosts the store should be the last to exit after a failure (it lingers for a moment), otherwise the
+others only learn that the store is gone.  The store is any ``torch.distributed`` store (TCPStore from the default process group, FileStore, HashStore); nothing
 here touches a GPU, so the logic is tested with gloo ranks on the CPU.
 """
 from __future__ import annotations
@@ -74,8 +75,11 @@ class Heartbeat:
                 if hasattr(self.store, "check") and not self.store.check([self._key(r)]):
                     continue  # the peer has not started yet
                 out[r] = json.loads(self.store.get(self._key(r)).decode())
-            except (RuntimeError, ValueError, KeyError):
+            except (ValueError, KeyError):
                 continue
+            except RuntimeError as exc:
+                # the store itself is gone: the rank that hosts it (rank 0 for the default TCP store) has exited
+                raise PeerFailure(0, "unreachable", f"key-value store does not answer ({exc})".splitlines()[0]) from exc
         return out
 
     def check_peers(self) -> None:

@@ -167,6 +167,8 @@ WORKER = textwrap.dedent("""
         print(f"rank {rank} finished", flush=True)
     except PeerFailure as exc:
         print(f"rank {rank} stopped cleanly: {exc}", flush=True)
+        if rank == 0:
+            time.sleep(1.5)   # host of the store: let the others read the failure record first
         os._exit(3)
     except RuntimeError as exc:
         print(f"rank {rank} raised: {exc}", flush=True)
