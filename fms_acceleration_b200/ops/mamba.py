@@ -122,6 +122,12 @@ def _make_g(cb, L, dt, nc, nh, G, Q):
     return g
 
 
+def _slabs(nc: int, nh: int, Q: int, budget_bytes: int = 256 << 20):
+    """Ranges of chunks whose [chunks, heads, Q, Q] fp32 temporaries stay below ``budget_bytes``."""
+    step = max(1, budget_bytes // (nh * Q * Q * 4))
+    return [(c0, min(nc, c0 + step)) for c0 in range(0, nc, step)]
+
+
 class _SSDScan(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, dt, A, B, C, D, h0, Q):
@@ -139,10 +145,14 @@ class _SSDScan(torch.autograd.Function):
         # C.B^T per chunk and group
         cb = batched_gemm(C2, B2, M=Q, N=Q, K=N, n_batch=nc * G, n_inner=G, a_off=(Q, 0, N, 1), b_off=(Q, 0, N, 1),
                           d_off=(G * Q, Q, 0), out_rows=nc * G * Q, out_cols=Q)
-        g = _make_g(cb, L, dt, nc, nh, G, Q)                                 # [nc*nh*Q, Q]
-        y_intra = batched_gemm(g, x2, M=Q, N=P, K=Q, n_batch=nc * nh, n_inner=nh, a_off=(nh * Q, Q, 0, 1),
-                               b_off=(Q, 0, P, 1), d_off=(Q, 0, P), b_mn=True, out_rows=T, out_cols=nh * P,
-                               out_dtype=torch.float32)
+        # intra-chunk term in slabs of chunks: the [chunks, heads, Q, Q] decay-weighted matrices are transient
+        y_intra = torch.empty(T, nh * P, dtype=torch.float32, device=dev)
+        for c0, c1 in _slabs(nc, nh, Q):
+            n = c1 - c0
+            g = _make_g(cb[c0 * G * Q: c1 * G * Q], L[c0 * Q: c1 * Q], dt[c0 * Q: c1 * Q], n, nh, G, Q)  # [n*nh*Q, Q]
+            batched_gemm(g, x2[c0 * Q: c1 * Q], M=Q, N=P, K=Q, n_batch=n * nh, n_inner=nh, a_off=(nh * Q, Q, 0, 1),
+                         b_off=(Q, 0, P, 1), d_off=(Q, 0, P), b_mn=True, out=y_intra[c0 * Q: c1 * Q])
+            del g
         # chunk states S[c,h] [P, N] = (x w)^T B,  w = exp(Ltot - L) dt
         wgt = (torch.exp(Ltot.view(nc, 1, nh) - L.view(nc, Q, nh)) * dt.view(nc, Q, nh)).reshape(T, nh)
         xw = (x.float() * wgt[:, :, None]).to(dtp).reshape(T, nh * P)
@@ -221,32 +231,38 @@ class _SSDScan(torch.autograd.Function):
         dLtot = dLtot + dww.view(nc, Q, nh).sum(1)
         dL = dL - dww
         ddt = dww / dt
-        # ---- intra-chunk term  y += G X,  G = CB o exp(L_t - L_s) dt_s (s <= t)
-        g = _make_g(cb, L, dt, nc, nh, G, Q)
-        dx_intra = batched_gemm(g, dy2, M=Q, N=P, K=Q, n_batch=nc * nh, n_inner=nh, a_off=(nh * Q, Q, 0, 1),
-                                b_off=(Q, 0, P, 1), d_off=(Q, 0, P), a_mn=True, b_mn=True, out_rows=T, out_cols=nh * P,
-                                out_dtype=torch.float32)
-        dx = dx + dx_intra.view(T, nh, P)
-        dG = batched_gemm(dy2, x2, M=Q, N=Q, K=P, n_batch=nc * nh, n_inner=nh, a_off=(Q, 0, P, 1), b_off=(Q, 0, P, 1),
-                          d_off=(nh * Q, Q, 0), out_rows=nc * nh * Q, out_cols=Q, out_dtype=torch.float32)
-        Wm = dG.view(nc, nh, Q, Q) * g.view(nc, nh, Q, Q).float()            # dG o G
-        row = Wm.sum(-1)                                                      # [nc, nh, Q] indexed by t
-        col = Wm.sum(-2)                                                      # indexed by s
-        dL = dL + (row - col).permute(0, 2, 1).reshape(T, nh)
-        ddt = ddt + col.permute(0, 2, 1).reshape(T, nh) / dt
-        # dCB[c, g] = sum_{h in g} dG o exp(L_t - L_s) dt_s mask  =  sum_h (dG o G) / CB   (avoid the division: rebuild)
-        Lc = L.view(nc, Q, nh).permute(0, 2, 1)                               # [nc, nh, Q]
-        dtc = dt.view(nc, Q, nh).permute(0, 2, 1)
-        decay = torch.exp(Lc[..., :, None] - Lc[..., None, :]) * dtc[..., None, :]
+        # ---- intra-chunk term  y += G X,  G = CB o exp(L_t - L_s) dt_s (s <= t); slabs of chunks bound the
+        # [chunks, heads, Q, Q] temporaries
         mask = torch.tril(torch.ones(Q, Q, dtype=torch.bool, device=dev))
-        dcb = (dG.view(nc, nh, Q, Q) * decay.masked_fill(~mask, 0.0)).view(nc, G, hpg, Q, Q).sum(2)
-        dcb16 = dcb.to(dtp).reshape(nc * G * Q, Q)
-        dC = dC + batched_gemm(dcb16, B2, M=Q, N=N, K=Q, n_batch=nc * G, n_inner=G, a_off=(G * Q, Q, 0, 1),
-                               b_off=(Q, 0, N, 1), d_off=(Q, 0, N), b_mn=True, out_rows=T, out_cols=G * N,
-                               out_dtype=torch.float32)
-        dB = dB + batched_gemm(dcb16, C2, M=Q, N=N, K=Q, n_batch=nc * G, n_inner=G, a_off=(G * Q, Q, 0, 1),
-                               b_off=(Q, 0, N, 1), d_off=(Q, 0, N), a_mn=True, b_mn=True, out_rows=T, out_cols=G * N,
-                               out_dtype=torch.float32)
+        for c0, c1 in _slabs(nc, nh, Q):
+            n = c1 - c0
+            rows = slice(c0 * Q, c1 * Q)
+            g = _make_g(cb[c0 * G * Q: c1 * G * Q], L[rows], dt[rows], n, nh, G, Q)
+            dx_intra = batched_gemm(g, dy2[rows], M=Q, N=P, K=Q, n_batch=n * nh, n_inner=nh, a_off=(nh * Q, Q, 0, 1),
+                                    b_off=(Q, 0, P, 1), d_off=(Q, 0, P), a_mn=True, b_mn=True, out_rows=n * Q,
+                                    out_cols=nh * P, out_dtype=torch.float32)
+            dx[rows] += dx_intra.view(n * Q, nh, P)
+            dG = batched_gemm(dy2[rows], x2[rows], M=Q, N=Q, K=P, n_batch=n * nh, n_inner=nh, a_off=(Q, 0, P, 1),
+                              b_off=(Q, 0, P, 1), d_off=(nh * Q, Q, 0), out_rows=n * nh * Q, out_cols=Q,
+                              out_dtype=torch.float32).view(n, nh, Q, Q)
+            Wm = dG * g.view(n, nh, Q, Q).float()                             # dG o G
+            row = Wm.sum(-1)                                                  # [n, nh, Q] indexed by t
+            col = Wm.sum(-2)                                                  # indexed by s
+            del Wm, g
+            dL[rows] += (row - col).permute(0, 2, 1).reshape(n * Q, nh)
+            ddt[rows] += col.permute(0, 2, 1).reshape(n * Q, nh) / dt[rows]
+            # dCB[c, g] = sum_{h in g} dG o exp(L_t - L_s) dt_s mask
+            Lc = L[rows].view(n, Q, nh).permute(0, 2, 1)                      # [n, nh, Q]
+            dtc = dt[rows].view(n, Q, nh).permute(0, 2, 1)
+            decay = (torch.exp(Lc[..., :, None] - Lc[..., None, :]) * dtc[..., None, :]).masked_fill_(~mask, 0.0)
+            dcb16 = (dG * decay).view(n, G, hpg, Q, Q).sum(2).to(dtp).reshape(n * G * Q, Q)
+            del decay, dG
+            dC[rows] += batched_gemm(dcb16, B2[rows], M=Q, N=N, K=Q, n_batch=n * G, n_inner=G, a_off=(G * Q, Q, 0, 1),
+                                     b_off=(Q, 0, N, 1), d_off=(Q, 0, N), b_mn=True, out_rows=n * Q, out_cols=G * N,
+                                     out_dtype=torch.float32)
+            dB[rows] += batched_gemm(dcb16, C2[rows], M=Q, N=N, K=Q, n_batch=n * G, n_inner=G, a_off=(G * Q, Q, 0, 1),
+                                     b_off=(Q, 0, N, 1), d_off=(Q, 0, N), a_mn=True, b_mn=True, out_rows=n * Q,
+                                     out_cols=G * N, out_dtype=torch.float32)
         # ---- through L = cumsum(dt A) within the chunk, Ltot = L[last]
         dLc = dL.view(nc, Q, nh).clone()
         dLc[:, -1, :] += dLtot
