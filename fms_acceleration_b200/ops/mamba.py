@@ -122,9 +122,12 @@ def _make_g(cb, L, dt, nc, nh, G, Q):
     return g
 
 
-def _slabs(nc: int, nh: int, Q: int, budget_bytes: int = 256 << 20):
-    """Ranges of chunks whose [chunks, heads, Q, Q] fp32 temporaries stay below ``budget_bytes``."""
-    step = max(1, budget_bytes // (nh * Q * Q * 4))
+SLAB_BYTES = 256 << 20  # bound on each [chunks, heads, Q, Q] fp32 temporary of the scan
+
+
+def _slabs(nc: int, nh: int, Q: int):
+    """Ranges of chunks whose [chunks, heads, Q, Q] fp32 temporaries stay below ``SLAB_BYTES``."""
+    step = max(1, SLAB_BYTES // (nh * Q * Q * 4))
     return [(c0, min(nc, c0 + step)) for c0 in range(0, nc, step)]
 
 
