@@ -194,8 +194,9 @@ __global__ void expert_count_kernel(const int* __restrict__ topk_idx, long long 
 //                       own histogram into row `rank` of every peer's table
 //   signals.p[r]      : rank r's flag words, uint32[world] on the plan channel
 // Outputs (local): seg_off[E_local + 1] padded (x128) offsets of my experts in my receive buffer,
-//   seg_cnt[E_local] true row counts, send_base[E] = first slot of MY rows of global expert e in its owner's buffer.
-//   status gets kCapacityOverflow when any owner's buffer (capacity rows) would overflow.
+//   seg_cnt[E_local] row counts, send_base[0..E) = first slot of MY rows of global expert e in its owner's buffer,
+//   send_base[E..2E) = end of the valid slots of expert e.  When an owner's buffer (capacity rows) would overflow,
+//   the excess rows are dropped consistently on every rank and status gets kCapacityOverflow.
 __global__ void moe_plan_kernel(MoePeers count_tables, MoePeers signals, const int* __restrict__ my_counts, int rank,
                                 int world, int E, int capacity, uint32_t epoch, int* __restrict__ seg_off,
                                 int* __restrict__ seg_cnt, int* __restrict__ send_base, int* status) {
@@ -231,15 +232,23 @@ __global__ void moe_plan_kernel(MoePeers count_tables, MoePeers signals, const i
           if (s < rank) before_me += c;
           total += c;
         }
+        // rows that do not fit into the owner's buffer are DROPPED (slot -1): nothing is ever written past the
+        // buffer; the status word tells the host that the capacity factor was too small
+        const int room = capacity - off;  // capacity and off are multiples of 128
+        int kept = total;
+        if (kept > room) {
+          kept = room > 0 ? room : 0;
+          report_status(status, kCapacityOverflow);
+        }
         send_base[e] = off + before_me;
+        send_base[E + e] = off + kept;  // first slot that is no longer valid for expert e
         if (owner == rank) {
           seg_off[el] = off;
-          seg_cnt[el] = total;
+          seg_cnt[el] = kept;
         }
-        off += (total + 127) / 128 * 128;
+        off += (kept + 127) / 128 * 128;
       }
       if (owner == rank) seg_off[E_local] = off;
-      if (off > capacity) report_status(status, kCapacityOverflow);
     }
   }
 }
@@ -253,6 +262,7 @@ __global__ void moe_assign_kernel(const int* __restrict__ topk_idx, long long n,
   __shared__ int running;
   if (threadIdx.x == 0) running = send_base[e];
   __syncthreads();
+  const int limit = send_base[gridDim.x + e];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   for (long long base = 0; base < n; base += blockDim.x) {
     const long long i = base + threadIdx.x;
@@ -266,7 +276,10 @@ __global__ void moe_assign_kernel(const int* __restrict__ topk_idx, long long n,
       if (w < warp) woff += warp_tot[w];
       tot += warp_tot[w];
     }
-    if (hit) dest_row[i] = running + woff + prefix;
+    if (hit) {
+      const int slot = running + woff + prefix;
+      dest_row[i] = slot < limit ? slot : -1;  // -1: dropped (capacity overflow)
+    }
     __syncthreads();
     if (threadIdx.x == 0) running += tot;
     __syncthreads();
@@ -287,6 +300,7 @@ __global__ void moe_dispatch_kernel(const T* __restrict__ x, long long ldx, cons
   const long long t = pair / k;
   const int owner = topk_idx[pair] / E_local;
   const long long row = dest_row[pair];
+  if (row < 0) return;  // dropped pair
   const T* src = x + t * ldx;
   T* dst = reinterpret_cast<T*>(recv.p[owner]) + row * ld_recv;
   const float sc = scale != nullptr ? scale[pair] : 1.f;
@@ -336,6 +350,7 @@ __global__ void moe_combine_kernel(MoePeers ybuf, long long ldy, const int* __re
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
     for (int s = 0; s < k; ++s) {
       const long long pair = t * k + s;
+      if (dest_row[pair] < 0) continue;  // dropped pair contributes nothing
       const int owner = topk_idx[pair] / E_local;
       const T* src = reinterpret_cast<const T*>(ybuf.p[owner]) + (long long)dest_row[pair] * ldy + c;
       const uint4 v = *reinterpret_cast<const uint4*>(src);
@@ -370,6 +385,10 @@ __global__ void moe_gate_grad_kernel(MoePeers ybuf, long long ldy, const int* __
   const int lane = threadIdx.x & 31;
   if (pair >= n_pairs) return;
   const long long t = pair / k;
+  if (dest_row[pair] < 0) {
+    if (lane == 0) dgate[pair] = 0.f;
+    return;
+  }
   const int owner = topk_idx[pair] / E_local;
   const T* y = reinterpret_cast<const T*>(ybuf.p[owner]) + (long long)dest_row[pair] * ldy;
   const T* g = dout + t * lddo;

@@ -189,7 +189,7 @@ def _plan(ctx: MoEContext, topk_idx, T, device):
     counts = torch.zeros(E, dtype=torch.int32, device=device)
     seg_off = torch.empty(ctx.E_local + 1, dtype=torch.int32, device=device)
     seg_cnt = torch.empty(ctx.E_local, dtype=torch.int32, device=device)
-    send_base = torch.empty(E, dtype=torch.int32, device=device)
+    send_base = torch.empty(2 * E, dtype=torch.int32, device=device)  # [first slot | end of valid slots] per expert
     dest_row = torch.empty(T, k, dtype=torch.int32, device=device)
     st = N.status_word(device)
     if ctx.world > 1:

@@ -81,3 +81,41 @@ def test_granitemoe_fused_model_trains():
     assert abs(out.loss.item() - ref_loss.item()) < 5e-2
     grads = [p.grad for p in model.parameters() if p.requires_grad]
     assert all(g is not None and torch.isfinite(g).all() for g in grads)
+
+
+def test_capacity_overflow_drops_rows_and_reports():
+    """A receive buffer that is too small: excess (token, expert) pairs get slot -1, segment counts are clipped to
+    the capacity, the status word carries the overflow code, and dispatch / combine touch nothing out of range."""
+    torch.manual_seed(0)
+    T, H, E, k = 512, 128, 4, 2
+    ctx = MOE.MoEContext(H, 64, E, k)
+    ctx.cap = 384  # instead of T*k + padding = 1024 + ...
+    idx = torch.randint(0, E, (T, k), dtype=torch.int32, device=DEV)
+    st = NV.status_word(DEV)
+    st.zero_()
+    seg_off, seg_cnt, dest_row = MOE._plan(ctx, idx, T, DEV)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 7
+    st.zero_()
+    so, sc, dr = seg_off.cpu(), seg_cnt.cpu(), dest_row.cpu()
+    assert int(so[-1]) <= ctx.cap and int(sc.sum()) <= ctx.cap
+    kept = dr[dr >= 0]
+    assert kept.numel() == int(sc.sum()) and kept.numel() < T * k
+    assert kept.max() < ctx.cap and kept.unique().numel() == kept.numel()  # distinct, in-range slots
+    for e in range(E):
+        rows = dr[(idx.cpu() == e) & (dr >= 0)]
+        assert rows.numel() == int(sc[e]) and (rows >= so[e]).all() and (rows < so[e] + sc[e]).all()
+    # dispatch with a canary behind the buffer, then combine: dropped pairs contribute zero
+    x = torch.randn(T, H, device=DEV).bfloat16()
+    buf = torch.zeros(ctx.cap + 8, H, dtype=torch.bfloat16, device=DEV)
+    buf[ctx.cap:] = 7.0
+    import ctypes
+
+    ptrs = (ctypes.c_void_p * 1)(buf.data_ptr())
+    MOE._dispatch(ctx, x, idx, dest_row, None, ptrs, buf.stride(0))
+    out = MOE._combine(ctx, ptrs, buf.stride(0), idx, dest_row, None, T, H, torch.bfloat16, DEV)
+    torch.cuda.synchronize()
+    assert (buf[ctx.cap:] == 7.0).all()
+    n_kept = (dest_row >= 0).sum(1, keepdim=True).float()
+    assert torch.allclose(out.float(), x.float() * n_kept, atol=0.08, rtol=0.02)
+    NV.check_status()
