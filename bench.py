@@ -331,9 +331,15 @@ def main() -> int:
     if secondary:
         line["secondary"] = secondary
     if rank == 0:
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # leave together, and without running the teardown of the communication libraries rank by rank: the result
+        # line is out, and nothing below could change it
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
     return 0
 
 
