@@ -267,6 +267,11 @@ def run_config(name: str, args, ctx) -> dict:
         "final_loss": last,
         "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30,
     }
+    if name == "granite-moe":
+        from fms_acceleration_b200.ops.moe import MoEContext
+
+        need = MoEContext.max_rows_needed(dev) / float(batch * seq * cfg.num_experts_per_tok)
+        line["config"]["moe_rows_needed_over_balanced"] = round(need, 3)
     if name == "mistral-qlora":
         line["config"].update({"lora": "r16 a16 qkvo", "packing": "padding-free docs U[128,4096]"})
         line["vs_baseline"] = value / world / published  # published number is per device

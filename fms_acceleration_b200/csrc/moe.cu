@@ -199,7 +199,7 @@ __global__ void expert_count_kernel(const int* __restrict__ topk_idx, long long 
 //   the excess rows are dropped consistently on every rank and status gets kCapacityOverflow.
 __global__ void moe_plan_kernel(MoePeers count_tables, MoePeers signals, const int* __restrict__ my_counts, int rank,
                                 int world, int E, int capacity, uint32_t epoch, int* __restrict__ seg_off,
-                                int* __restrict__ seg_cnt, int* __restrict__ send_base, int* status) {
+                                int* __restrict__ seg_cnt, int* __restrict__ send_base, int* needed, int* status) {
   const int E_local = E / world;
   __shared__ int ok;
   if (threadIdx.x == 0) ok = 1;
@@ -223,7 +223,7 @@ __global__ void moe_plan_kernel(MoePeers count_tables, MoePeers signals, const i
   // every rank derives the layout of every owner (cheap, E <= 512)
   if (threadIdx.x == 0) {
     for (int owner = 0; owner < world; ++owner) {
-      int off = 0;
+      int off = 0, want = 0;  // want: rows the owner would need for nothing to be dropped
       for (int el = 0; el < E_local; ++el) {
         const int e = owner * E_local + el;
         int total = 0, before_me = 0;
@@ -234,6 +234,7 @@ __global__ void moe_plan_kernel(MoePeers count_tables, MoePeers signals, const i
         }
         // rows that do not fit into the owner's buffer are DROPPED (slot -1): nothing is ever written past the
         // buffer; the status word tells the host that the capacity factor was too small
+        want += (total + 127) / 128 * 128;
         const int room = capacity - off;  // capacity and off are multiples of 128
         int kept = total;
         if (kept > room) {
@@ -249,6 +250,7 @@ __global__ void moe_plan_kernel(MoePeers count_tables, MoePeers signals, const i
         off += (kept + 127) / 128 * 128;
       }
       if (owner == rank) seg_off[E_local] = off;
+      if (needed != nullptr) atomicMax(needed, want);  // same value on every rank: all see all owners
     }
   }
 }
@@ -443,7 +445,7 @@ extern "C" int fmsb_moe_router_bwd(const float* logits, const int* topk_idx, con
 // counts must be zeroed by the caller.  Then plan + assign.  count_tables / signals may be null when world == 1.
 extern "C" int fmsb_moe_plan(const int* topk_idx, long long n_pairs, int E, int rank, int world, int capacity,
                              int* counts, void* const* count_tables, void* const* signals, unsigned epoch,
-                             int* seg_off, int* seg_cnt, int* send_base, int* dest_row, int* status,
+                             int* seg_off, int* seg_cnt, int* send_base, int* dest_row, int* needed, int* status,
                              cudaStream_t stream) {
   if (E > kMoeMaxExperts || world > kMoeMaxRanks || E % world != 0) return -2;
   if (n_pairs > 0) {
@@ -454,7 +456,7 @@ extern "C" int fmsb_moe_plan(const int* topk_idx, long long n_pairs, int E, int 
   MoePeers ct = world > 1 ? moe_ptrs(count_tables, world) : MoePeers{};
   MoePeers sg = world > 1 ? moe_ptrs(signals, world) : MoePeers{};
   moe_plan_kernel<<<1, 256, 0, stream>>>(ct, sg, counts, rank, world, E, capacity, epoch, seg_off, seg_cnt, send_base,
-                                         status);
+                                         needed, status);
   if (n_pairs > 0) moe_assign_kernel<<<E, 1024, 0, stream>>>(topk_idx, n_pairs, send_base, dest_row);
   return (int)cudaGetLastError();
 }

@@ -12,6 +12,8 @@ from __future__ import annotations
 import ctypes
 from typing import List, Optional
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -22,7 +24,7 @@ P, I, L, F, U = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
 N.declare("fmsb_grouped_gemm", [P, L, P, L, I, I, P, L, I, P, L, F, F, I, I, I, I, I, I, P, L, L, L, P, P])
 N.declare("fmsb_moe_router", [P, I, I, I, I, P, P, P])
 N.declare("fmsb_moe_router_bwd", [P, P, P, P, I, I, I, I, P, P])
-N.declare("fmsb_moe_plan", [P, L, I, I, I, I, P, P, P, U, P, P, P, P, P, P])
+N.declare("fmsb_moe_plan", [P, L, I, I, I, I, P, P, P, U, P, P, P, P, P, P, P])
 N.declare("fmsb_moe_dispatch", [P, L, P, P, P, L, I, I, I, P, L, I, I, P])
 N.declare("fmsb_moe_zero_pad", [P, L, I, P, P, I, I, P])
 N.declare("fmsb_moe_combine", [P, L, P, P, P, L, I, I, I, P, L, I, I, P])
@@ -124,8 +126,10 @@ class MoEContext:
 
     _shared: dict = {}
 
-    def __init__(self, hidden: int, inter: int, num_experts: int, top_k: int, group=None, capacity_factor: float = 1.25,
-                 layer_tag: str = "moe"):
+    def __init__(self, hidden: int, inter: int, num_experts: int, top_k: int, group=None,
+                 capacity_factor: Optional[float] = None, layer_tag: str = "moe"):
+        if capacity_factor is None:
+            capacity_factor = float(os.environ.get("FMSB_MOE_CAPACITY_FACTOR", "2.0"))
         self.H, self.I, self.E, self.k = hidden, inter, num_experts, top_k
         self.group = group
         self.world = dist.get_world_size(group) if (group is not None and dist.is_initialized()) else 1
@@ -160,7 +164,9 @@ class MoEContext:
         if self.world == 1:
             rows = T * self.k  # exact upper bound: the local buffer can never overflow
         else:
-            rows = int(self.capacity_factor * T * self.k)  # T*k rows arrive per rank when routing is balanced
+            # T*k rows arrive per rank when routing is balanced, world*T*k when every token of every rank picks this
+            # rank's experts; rows beyond the capacity are dropped and reported (status 7), never written
+            rows = int(min(self.capacity_factor, float(self.world)) * T * self.k)
         cap = (rows + self.E_local * 128 + 127) // 128 * 128
         if cap != self.cap:
             self.cap = cap
@@ -178,6 +184,24 @@ class MoEContext:
     def barrier(self, chan):
         if self.world > 1:
             self.comm.barrier(chan)
+
+    # rows an owner would have needed so far for nothing to be dropped (maximum over layers, steps and owners)
+    _needed: dict = {}
+
+    @classmethod
+    def needed_counter(cls, device) -> torch.Tensor:
+        dev = torch.device(device)
+        key = dev.index if dev.index is not None else torch.cuda.current_device()
+        t = cls._needed.get(key)
+        if t is None:
+            t = torch.zeros(1, dtype=torch.int32, device=f"cuda:{key}")
+            cls._needed[key] = t
+        return t
+
+    @classmethod
+    def max_rows_needed(cls, device=None) -> int:
+        """Host-synchronising read of the counter; compare with ``T * top_k`` to choose ``capacity_factor``."""
+        return int(cls.needed_counter(device if device is not None else torch.cuda.current_device()).item())
 
 
 PLAN_CHAN = 8
@@ -201,7 +225,7 @@ def _plan(ctx: MoEContext, topk_idx, T, device):
         epoch, tab, sig = 0, None, None
     rc = N.lib().fmsb_moe_plan(topk_idx.data_ptr(), T * k, E, ctx.rank, ctx.world, ctx.cap, counts.data_ptr(), tab, sig,
                                epoch, seg_off.data_ptr(), seg_cnt.data_ptr(), send_base.data_ptr(), dest_row.data_ptr(),
-                               st.data_ptr(), N.stream_ptr())
+                               MoEContext.needed_counter(device).data_ptr(), st.data_ptr(), N.stream_ptr())
     N.check(rc, "fmsb_moe_plan")
     return seg_off, seg_cnt, dest_row
 
