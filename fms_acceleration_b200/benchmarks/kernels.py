@@ -122,6 +122,37 @@ def bench_attn(a):
                       "bwd_tflops": 2.5 * fl_fwd / t_b / 1e9}))
 
 
+def bench_q4gemm(a):
+    """Fused gather+dequant+GEMM+LoRA for few rows against dequantise-then-GEMM."""
+    from fms_acceleration_b200 import _native as NV
+    from fms_acceleration_b200.ops import quant as Q
+    from fms_acceleration_b200.ops.gemm import gemm, gemm_q4_fused
+
+    pk = peaks()
+    Nn, K, R = a.n, a.k, 16
+    w = (torch.randn(Nn, K, device="cuda") * 0.02).bfloat16()
+    qs = Q.quantize_4bit(w, "nf4", 64, True)
+    del w
+    bl = (torch.randn(Nn, R, device="cuda") * 0.1).bfloat16()
+    wd = torch.empty(Nn, K, dtype=torch.bfloat16, device="cuda")
+    for M in a.rows:
+        x = torch.randn(M, K, device="cuda").bfloat16()
+        xa = torch.randn(M, R, device="cuda").bfloat16()
+
+        def two_step():
+            Q.dequantize_4bit(qs, torch.bfloat16, out=wd)
+            return gemm(x, wd, a2=xa, b2=bl)
+
+        t_f = timeit(lambda: gemm_q4_fused(x, qs, xa, bl), a.iters, a.warmup, True)
+        t_2 = timeit(two_step, a.iters, a.warmup, True)
+        NV.check_status()
+        by = Nn * K / 2 + Nn * K / 64 + 2.0 * M * (K + Nn)
+        print(json.dumps({"kernel": "gemm_q4_fused", "m": M, "n": Nn, "k": K, "lora_r": R, "fused_ms": t_f,
+                          "dequant_then_gemm_ms": t_2, "speedup": t_2 / t_f, "algorithmic_gbs": by / t_f / 1e6,
+                          "frac_of_%s_hbm" % pk["source"]: by / t_f / 1e6 / pk["hbm_gbs"],
+                          "tflops": 2.0 * M * Nn * K / t_f / 1e9}))
+
+
 def bench_elementwise(a):
     from fms_acceleration_b200.ops import activation as ACT
     from fms_acceleration_b200.ops import rmsnorm as RN
@@ -146,7 +177,7 @@ def bench_elementwise(a):
 def main(argv=None):
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="what", required=True)
-    for name in ("gemm", "attn", "elementwise"):
+    for name in ("gemm", "attn", "elementwise", "q4gemm"):
         p = sub.add_parser(name)
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--warmup", type=int, default=5)
@@ -157,6 +188,10 @@ def main(argv=None):
             p.add_argument("--k", type=int, default=4096)
             p.add_argument("--layout", default="nt", choices=["nt", "nn"], help="nt: B is [N,K]; nn: B is [K,N]")
             p.add_argument("--cublas", action="store_true", help="also time torch.matmul (cuBLAS) for comparison")
+        elif name == "q4gemm":
+            p.add_argument("--n", type=int, default=14336)
+            p.add_argument("--k", type=int, default=4096)
+            p.add_argument("--rows", type=int, nargs="+", default=[16, 64, 128, 256, 512])
         elif name == "attn":
             p.add_argument("--batch", type=int, default=4)
             p.add_argument("--seq", type=int, default=4096)
@@ -169,7 +204,7 @@ def main(argv=None):
             p.add_argument("--hidden", type=int, default=4096)
             p.add_argument("--inter", type=int, default=14336)
     a = ap.parse_args(argv)
-    {"gemm": bench_gemm, "attn": bench_attn, "elementwise": bench_elementwise}[a.what](a)
+    {"gemm": bench_gemm, "attn": bench_attn, "elementwise": bench_elementwise, "q4gemm": bench_q4gemm}[a.what](a)
     return 0
 
 

@@ -1,0 +1,289 @@
+// Fused gather + NF4/FP4 dequantise + GEMM + LoRA for sm_100a:
+//
+//     y[M, N] = alpha * ( x[M, K] . dequant(Wq)[N, K]^T  +  xa[M, R] . Bl[N, R]^T )
+//
+// The 4-bit weight never exists in 16 bits in global memory: dequant warps read the packed bytes (two
+// values per byte, blocks of 64 values sharing one scale, the scales themselves optionally 8-bit "double
+// quantised") straight from where they are stored - this GPU's memory or a PEER's shard of the flat
+// packed array, through plain loads over NVLink - expand them with the 16-entry code book and write
+// 16-bit values directly into the 128-byte-swizzled shared-memory operand tile that tcgen05.mma reads
+// (generic-proxy stores, then fence.proxy.async, then an mbarrier arrive).  The activation tiles come
+// in by TMA; the LoRA update (xa = x A^T computed beforehand, Bl = s*B) is accumulated by extra K blocks
+// into the same tensor-memory accumulator.
+//
+// This is the kernel for FEW ROWS (M up to a few hundred: one or two 128-row tiles), where every weight
+// byte is used once and the job is to stream 4-bit data at memory / link speed.  With thousands of rows
+// each weight tile would be expanded again by every row tile; there the framework dequantises once into
+// an L2-resident 16-bit buffer and runs gemm_tcgen05.cu.
+//
+// Reference counterparts: bitsandbytes' cgemm_4bit_inference_naive / dequantize + matmul as called from
+// fms_acceleration_foak/fused_ops/unsloth_lora/utils.py:119-136,190-203,262-279 and the NCCL all-gather
+// of the FSDP-sharded packed parameter that precedes them.
+//
+// Roles (192 threads): warp 0 TMA producer (x, and xa/Bl for the LoRA blocks), warp 1 MMA issuer,
+// warps 2-5 dequantise W tiles and afterwards run the epilogue.  4-stage ring.  Every wait is bounded.
+#include "common.cuh"
+
+namespace fmsb {
+
+constexpr int Q4_BM = 128;
+constexpr int Q4_BK = 64;
+constexpr int Q4_STAGES = 4;
+constexpr int Q4_MAX_RANKS = 16;
+
+struct Q4Params {
+  int M, N, K;
+  int kblocks1, kblocks2;
+  const uint8_t* shard[Q4_MAX_RANKS];  // flat packed array [N*K/2] split into `world` equal shards
+  long long shard_bytes;
+  int world;
+  const float* absmax;       // [N*K/64] fp32, or null when double quantised
+  const uint8_t* absmax_q;   // [N*K/64] codes into code256
+  const float* code256;      // [256]
+  const float* absmax2;      // [N*K/64/256]
+  float offset;
+  float code16[16];
+  void* D;
+  long long ldd;
+  float alpha;
+  int fmt;  // 0 fp16, 1 bf16
+  int* status;
+};
+
+template <int BN>
+struct Q4Cfg {
+  static constexpr int kABytes = Q4_BM * Q4_BK * 2;
+  static constexpr int kBBytes = 128 * Q4_BK * 2;  // room for the widest tile (the LoRA B tile is BN rows too)
+  static constexpr int kSmemBytes = Q4_STAGES * (kABytes + kBBytes) + 1024 + 256;
+};
+
+__device__ __forceinline__ uint32_t q4_pack2(float a, float b, int fmt) {
+  return fmt == 1 ? pack_bf16x2(a, b) : pack_f16x2(a, b);
+}
+
+template <int BN>
+__global__ void __launch_bounds__(192, 1)
+gemm_q4_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmXa,
+                     const __grid_constant__ CUtensorMap tmBl, const Q4Params p) {
+  using Cfg = Q4Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  auto sA = [&](int s) { return base + s * (Cfg::kABytes + Cfg::kBBytes); };
+  auto sB = [&](int s) { return base + s * (Cfg::kABytes + Cfg::kBBytes) + Cfg::kABytes; };
+  const uint32_t bars = base + Q4_STAGES * (Cfg::kABytes + Cfg::kBBytes);
+  auto bar_a_full = [&](int s) { return bars + 8u * s; };
+  auto bar_b_full = [&](int s) { return bars + 8u * (Q4_STAGES + s); };
+  auto bar_empty = [&](int s) { return bars + 8u * (2 * Q4_STAGES + s); };
+  const uint32_t bar_acc = bars + 8u * (3 * Q4_STAGES);
+  const uint32_t holder = bar_acc + 8u;
+  __shared__ float s_code[16];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BN;
+  const int m0 = blockIdx.y * Q4_BM;
+  const int kbt = p.kblocks1 + p.kblocks2;
+
+  if (threadIdx.x < 16) s_code[threadIdx.x] = p.code16[threadIdx.x];
+  if (warp == 1 && lane == 0) {
+    for (int s = 0; s < Q4_STAGES; ++s) {
+      mbar_init(bar_a_full(s), 1);
+      mbar_init(bar_b_full(s), 128);
+      mbar_init(bar_empty(s), 1);
+    }
+    mbar_init(bar_acc, 1);
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(holder, 128);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  uint32_t tmem;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem) : "r"(holder));
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < kbt; ++kb) {
+        const int s = kb % Q4_STAGES;
+        if (!mbar_wait(bar_empty(s), ((kb / Q4_STAGES) & 1) ^ 1u, p.status, kTimeoutProducer)) break;
+        if (kb < p.kblocks1) {
+          mbar_expect_tx(bar_a_full(s), Cfg::kABytes);
+          tma_load_2d(sA(s), &tmX, bar_a_full(s), kb * Q4_BK, m0);
+        } else {
+          const int k2 = (kb - p.kblocks1) * Q4_BK;
+          mbar_expect_tx(bar_a_full(s), Cfg::kABytes + BN * Q4_BK * 2);
+          tma_load_2d(sA(s), &tmXa, bar_a_full(s), k2, m0);
+          tma_load_2d(sB(s), &tmBl, bar_a_full(s), k2, n0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_f16(128, BN, p.fmt, 0, 0);
+      bool ok = true;
+      for (int kb = 0; kb < kbt && ok; ++kb) {
+        const int s = kb % Q4_STAGES;
+        const uint32_t par = (kb / Q4_STAGES) & 1;
+        if (!mbar_wait(bar_a_full(s), par, p.status, kTimeoutMma)) { ok = false; break; }
+        if (kb < p.kblocks1 && !mbar_wait(bar_b_full(s), par, p.status, kTimeoutMma)) { ok = false; break; }
+        tc_fence_after();
+        const SmemDescBase da = make_smem_desc_base(sA(s), 16, 1024), db = make_smem_desc_base(sB(s), 16, 1024);
+#pragma unroll
+        for (int ks = 0; ks < Q4_BK / 16; ++ks)
+          tc_mma_f16(tmem, smem_desc_at(da, ks * 32), smem_desc_at(db, ks * 32), idesc, (kb | ks) != 0);
+        tc_commit(bar_empty(s));
+      }
+      if (ok) tc_commit(bar_acc);
+    }
+  } else {
+    // ------------------------------------------------------------------ dequantise W tiles [BN rows x 64]
+    constexpr int TPR = 128 / BN;        // threads per weight row
+    constexpr int EPT = Q4_BK / TPR;     // elements per thread and K block: 64, 32 or 16
+    const int tid = threadIdx.x - 64;    // 0..127
+    const int r = tid / TPR;             // row inside the tile
+    const int part = tid % TPR;          // which slice of the row's 64 elements
+    const int n = n0 + r;
+    const bool row_ok = n < p.N;
+    bool ok = true;
+    for (int kb = 0; kb < p.kblocks1 && ok; ++kb) {
+      const int s = kb % Q4_STAGES;
+      // operands first (global / peer loads in flight while waiting for the stage)
+      uint32_t w[EPT / 8];
+      float scale = 0.f;
+#pragma unroll
+      for (int i = 0; i < EPT / 8; ++i) w[i] = 0u;
+      const int k0 = kb * Q4_BK;
+      if (row_ok && k0 < p.K) {
+        const long long e0 = (long long)n * p.K + k0;       // first element of the 64-block (K % 64 == 0)
+        const long long blk = e0 >> 6;
+        scale = p.absmax_q != nullptr ? p.code256[p.absmax_q[blk]] * p.absmax2[blk >> 8] + p.offset : p.absmax[blk];
+        const long long byte_off = (e0 >> 1) + part * (EPT / 2);
+        const uint8_t* src = p.shard[byte_off / p.shard_bytes] + (byte_off % p.shard_bytes);
+        if constexpr (EPT == 64) {
+          const uint4 u0 = *reinterpret_cast<const uint4*>(src), u1 = *reinterpret_cast<const uint4*>(src + 16);
+          w[0] = u0.x; w[1] = u0.y; w[2] = u0.z; w[3] = u0.w;
+          w[4] = u1.x; w[5] = u1.y; w[6] = u1.z; w[7] = u1.w;
+        } else if constexpr (EPT == 32) {
+          const uint4 u0 = *reinterpret_cast<const uint4*>(src);
+          w[0] = u0.x; w[1] = u0.y; w[2] = u0.z; w[3] = u0.w;
+        } else {
+          const uint2 u0 = *reinterpret_cast<const uint2*>(src);
+          w[0] = u0.x; w[1] = u0.y;
+        }
+      }
+      if (!mbar_wait(bar_empty(s), ((kb / Q4_STAGES) & 1) ^ 1u, p.status, kTimeoutDequant)) { ok = false; break; }
+      // one 32-bit word = 8 values = one 16-byte chunk of the swizzled row
+#pragma unroll
+      for (int i = 0; i < EPT / 8; ++i) {
+        uint32_t o[4];
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const uint32_t byte = (w[i] >> (8 * b)) & 0xffu;
+          o[b] = q4_pack2(s_code[byte >> 4] * scale, s_code[byte & 15] * scale, p.fmt);
+        }
+        const int chunk = part * (EPT / 8) + i;  // 0..7 within the row
+        const uint32_t addr = sB(s) + static_cast<uint32_t>(r * 128 + ((chunk ^ (r & 7)) << 4));
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
+                     : "memory");
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(bar_b_full(s));
+    }
+    // ------------------------------------------------------------------ epilogue
+    if (ok && mbar_wait(bar_acc, 0, p.status, kTimeoutEpilogue)) {
+      tc_fence_after();
+      const int q = warp & 3;
+      const int row = m0 + q * 32 + lane;
+      const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem + lane_addr + c * 32, v);
+        tmem_ld_wait();
+        if (row < p.M) {
+          uint16_t* dst = reinterpret_cast<uint16_t*>(p.D) + (long long)row * p.ldd + n0 + c * 32;
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            if (n0 + c * 32 + i < p.N) {  // N % 8 == 0: a group of 8 columns is in range as a whole
+              uint4 u;
+              u.x = q4_pack2(__uint_as_float(v[i]) * p.alpha, __uint_as_float(v[i + 1]) * p.alpha, p.fmt);
+              u.y = q4_pack2(__uint_as_float(v[i + 2]) * p.alpha, __uint_as_float(v[i + 3]) * p.alpha, p.fmt);
+              u.z = q4_pack2(__uint_as_float(v[i + 4]) * p.alpha, __uint_as_float(v[i + 5]) * p.alpha, p.fmt);
+              u.w = q4_pack2(__uint_as_float(v[i + 6]) * p.alpha, __uint_as_float(v[i + 7]) * p.alpha, p.fmt);
+              *reinterpret_cast<uint4*>(dst + i) = u;
+            }
+          }
+        }
+      }
+    }
+  }
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 128);
+  }
+}
+
+}  // namespace fmsb
+
+using namespace fmsb;
+
+template <int BN>
+static int q4_launch(const CUtensorMap& tx, const CUtensorMap& txa, const CUtensorMap& tbl, const Q4Params& p,
+                     cudaStream_t stream) {
+  static bool cfg = false;
+  if (!cfg) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_q4_fused_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Q4Cfg<BN>::kSmemBytes);
+    if (e != cudaSuccess) return (int)e;
+    cfg = true;
+  }
+  dim3 grid((p.N + BN - 1) / BN, (p.M + Q4_BM - 1) / Q4_BM);
+  gemm_q4_fused_kernel<BN><<<grid, 192, Q4Cfg<BN>::kSmemBytes, stream>>>(tx, txa, tbl, p);
+  return (int)cudaGetLastError();
+}
+
+// x [M, K] (ldx), packed shards (world pointers, shard_bytes each; world = 1: one local pointer), scales either
+// `absmax` (fp32 per 64-block) or the double-quantised triple (absmax_q, code256, absmax2, offset); code16 = the
+// 16-entry NF4 / FP4 table (host pointer); optional LoRA pair xa [M, R] (ldxa), bl [N, R] (ldbl), R = r2;
+// y [M, N] (ldy).  K % 64 == 0, N % 8 == 0, leading dimensions % 8 == 0, bn in {32, 64, 128}.
+extern "C" int fmsb_gemm_q4_fused(const void* x, long long ldx, void* const* packed_shards, long long shard_bytes,
+                                  int world, const float* absmax, const void* absmax_q, const float* code256,
+                                  const float* absmax2, float offset, const float* code16_host, const void* xa,
+                                  long long ldxa, const void* bl, long long ldbl, int r2, void* y, long long ldy,
+                                  float alpha, int M, int N, int K, int fmt, int bn, int* status,
+                                  cudaStream_t stream) {
+  using namespace fmsb_host;
+  if (M <= 0 || N <= 0) return 0;
+  if (K % 64 != 0 || N % 8 != 0 || (ldx % 8) || (ldy % 8) || world < 1 || world > Q4_MAX_RANKS) return -2;
+  if (shard_bytes % 32 != 0 || shard_bytes * world < (long long)N * K / 2) return -2;
+  if ((absmax == nullptr) == (absmax_q == nullptr)) return -2;
+  if (xa != nullptr && ((ldxa % 8) || (ldbl % 8) || r2 <= 0 || bl == nullptr)) return -2;
+  Q4Params p{};
+  p.M = M; p.N = N; p.K = K;
+  p.kblocks1 = K / 64;
+  p.kblocks2 = xa != nullptr ? (r2 + 63) / 64 : 0;
+  for (int i = 0; i < world; ++i) p.shard[i] = (const uint8_t*)packed_shards[i];
+  p.shard_bytes = shard_bytes; p.world = world;
+  p.absmax = absmax; p.absmax_q = (const uint8_t*)absmax_q; p.code256 = code256; p.absmax2 = absmax2; p.offset = offset;
+  for (int i = 0; i < 16; ++i) p.code16[i] = code16_host[i];
+  p.D = y; p.ldd = ldy; p.alpha = alpha; p.fmt = fmt; p.status = status;
+  CUtensorMap tx, txa, tbl;
+  int rc;
+  if ((rc = make_tmap_2d_16b(&tx, x, M, K, ldx, 128, 64))) return rc;
+  if (xa != nullptr) {
+    if ((rc = make_tmap_2d_16b(&txa, xa, M, r2, ldxa, 128, 64))) return rc;
+    if ((rc = make_tmap_2d_16b(&tbl, bl, N, r2, ldbl, bn, 64))) return rc;
+  } else {
+    txa = tx;
+    tbl = tx;
+  }
+  if (bn == 128) return q4_launch<128>(tx, txa, tbl, p, stream);
+  if (bn == 64) return q4_launch<64>(tx, txa, tbl, p, stream);
+  if (bn == 32) return q4_launch<32>(tx, txa, tbl, p, stream);
+  return -2;
+}

@@ -137,3 +137,61 @@ def batched_gemm(a, b, *, M, N, K, n_batch, n_inner=1, a_off=(0, 0, 0, 1), b_off
                                     desc, st.data_ptr(), N_.stream_ptr())
     N_.check(rc, "fmsb_batched_gemm")
     return out
+
+
+# ------------------------------------------------------------------------------------------------
+# fused gather + 4-bit dequantise + GEMM + LoRA for few rows (csrc/gemm_q4_fused.cu)
+# ------------------------------------------------------------------------------------------------
+N.declare("fmsb_gemm_q4_fused", [_ct.c_void_p, _ct.c_longlong, _ct.c_void_p, _ct.c_longlong, _ct.c_int, _ct.c_void_p,
+                                  _ct.c_void_p, _ct.c_void_p, _ct.c_void_p, _ct.c_float, _ct.c_void_p, _ct.c_void_p,
+                                  _ct.c_longlong, _ct.c_void_p, _ct.c_longlong, _ct.c_int, _ct.c_void_p, _ct.c_longlong,
+                                  _ct.c_float, _ct.c_int, _ct.c_int, _ct.c_int, _ct.c_int, _ct.c_int, _ct.c_void_p,
+                                  _ct.c_void_p])
+
+FUSED_Q4_MAX_ROWS = 256  # above this the weight is dequantised once and the plain GEMM is used
+
+
+def gemm_q4_fused(x: torch.Tensor, qs, xa: torch.Tensor | None = None, bl: torch.Tensor | None = None,
+                  shard_ptrs=None, shard_bytes: int | None = None, alpha: float = 1.0, out: torch.Tensor | None = None,
+                  bn: int | None = None) -> torch.Tensor:
+    """``x [M, K] @ dequant(qs) [N, K]^T (+ xa [M, R] @ bl [N, R]^T)`` without materialising the 16-bit weight.
+
+    ``qs`` is a ``Quant4State`` of a ``[N, K]`` weight with block size 64.  ``shard_ptrs`` (a ctypes array of
+    ``world`` device pointers, each ``shard_bytes`` long) replaces ``qs.packed`` when the flat packed array lives in
+    equal shards on several GPUs; the kernel then reads the peers' shards directly.
+    """
+    if qs.blocksize != 64:
+        raise ValueError("the fused kernel needs quantisation blocks of 64 values")
+    Nn, K = qs.shape
+    M = x.shape[0]
+    if x.dtype not in (torch.bfloat16, torch.float16) or x.stride(1) != 1 or x.stride(0) % 8 or K % 64 or Nn % 8:
+        raise ValueError("x must be a 16-bit row-major matrix; K % 64 == 0 and N % 8 == 0")
+    if out is None:
+        out = torch.empty(M, Nn, dtype=x.dtype, device=x.device)
+    if shard_ptrs is None:
+        world, shard_bytes = 1, (qs.packed.numel() + 31) // 32 * 32
+        shard_ptrs = (_ct.c_void_p * 1)(qs.packed.data_ptr())
+    else:
+        world = len(shard_ptrs)
+    if bn is None:
+        # enough CTAs to put every SM to work on a thin problem
+        bn = 128 if (Nn // 128) * ((M + 127) // 128) >= 148 else (64 if (Nn // 64) * ((M + 127) // 128) >= 148 else 32)
+    code = qs.code if qs.code is not None else None
+    if code is None:
+        from .quant import code_book
+
+        code = code_book(qs.quant_type)
+    code_host = (_ct.c_float * 16)(*[float(v) for v in code.detach().float().cpu().tolist()])
+    r2 = 0
+    if xa is not None:
+        if bl is None or xa.shape[0] != M or bl.shape[0] != Nn or xa.shape[1] != bl.shape[1]:
+            raise ValueError("LoRA pair: xa [M, R] and bl [N, R]")
+        r2 = xa.shape[1]
+    st = N.status_word(x.device)
+    rc = N.lib().fmsb_gemm_q4_fused(
+        x.data_ptr(), x.stride(0), shard_ptrs, int(shard_bytes), world, N.ptr(qs.absmax), N.ptr(qs.absmax_q),
+        N.ptr(qs.code2), N.ptr(qs.absmax2), float(qs.offset), code_host, N.ptr(xa), xa.stride(0) if xa is not None else 0,
+        N.ptr(bl), bl.stride(0) if bl is not None else 0, r2, out.data_ptr(), out.stride(0), float(alpha), M, Nn, K,
+        N.dtype_code(x.dtype), bn, st.data_ptr(), N.stream_ptr())
+    N.check(rc, "fmsb_gemm_q4_fused")
+    return out

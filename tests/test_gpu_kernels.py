@@ -226,3 +226,36 @@ def test_gptq_dequant(bits, dtype):
     W = Q.gptq_dequant(qw, sc, qz, g2, bits, gs, 0)
     ref = sc[g2.long()].float() * (wi - zi[g2.long()]).float()
     assert _rel(W, ref) < 5e-3
+
+
+@pytest.mark.parametrize("M,Nn,K,bn,double_quant,lora", [(64, 512, 256, 128, True, False), (128, 384, 512, 64, False, True),
+                                                       (200, 256, 1024, 32, True, True), (7, 4096, 4096, None, True, True)])
+def test_fused_q4_gemm_matches_dequant_then_gemm(M, Nn, K, bn, double_quant, lora):
+    """In-kernel NF4 dequantisation (+ LoRA pair) against dequantise-to-bf16 followed by an fp32 matmul."""
+    from fms_acceleration_b200.ops.gemm import gemm_q4_fused
+
+    torch.manual_seed(M + Nn)
+    w = torch.randn(Nn, K, device=DEV) * 0.05
+    qs = Q.quantize_4bit(w.bfloat16(), "nf4", 64, double_quant)
+    wd = Q.dequantize_4bit(qs, torch.bfloat16).view(Nn, K)
+    x = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
+    xa = bl = None
+    ref = x.float() @ wd.float().t()
+    if lora:
+        xa = (torch.randn(M, 16, device=DEV) * 0.3).bfloat16()
+        bl = (torch.randn(Nn, 16, device=DEV) * 0.3).bfloat16()
+        ref = ref + xa.float() @ bl.float().t()
+    y = gemm_q4_fused(x, qs, xa, bl, bn=bn)
+    NV.check_status()
+    assert y.shape == (M, Nn)
+    assert (y.float() - ref).abs().max() <= 2e-2 * ref.abs().max() + 1e-3
+    # several equal shards of the packed array addressed through a pointer table (here all on one GPU)
+    import ctypes
+
+    if (Nn * K // 2) % (4 * 32) == 0:
+        sb = Nn * K // 2 // 4
+        parts = [qs.packed[i * sb:(i + 1) * sb].clone() for i in range(4)]
+        ptrs = (ctypes.c_void_p * 4)(*[t.data_ptr() for t in parts])
+        y2 = gemm_q4_fused(x, qs, xa, bl, shard_ptrs=ptrs, shard_bytes=sb, bn=bn)
+        NV.check_status()
+        assert torch.equal(y2, y)
