@@ -20,8 +20,8 @@
 // fms_acceleration_foak/fused_ops/unsloth_lora/utils.py:119-136,190-203,262-279 and the NCCL all-gather
 // of the FSDP-sharded packed parameter that precedes them.
 //
-// Roles (192 threads): warp 0 TMA producer (x, and xa/Bl for the LoRA blocks), warp 1 MMA issuer,
-// warps 2-5 dequantise W tiles and afterwards run the epilogue.  4-stage ring.  Every wait is bounded.
+// Roles (320 threads): warp 0 TMA producer (x, and xa/Bl for the LoRA blocks), warp 1 MMA issuer,
+// warps 2-9 dequantise W tiles and afterwards run the epilogue.  4-stage ring.  Every wait is bounded.
 #include "common.cuh"
 
 namespace fmsb {
@@ -30,6 +30,7 @@ constexpr int Q4_BM = 128;
 constexpr int Q4_BK = 64;
 constexpr int Q4_STAGES = 4;
 constexpr int Q4_MAX_RANKS = 16;
+constexpr int Q4_DQ_THREADS = 256;  // 8 dequant warps: two per scheduler, so table look-ups of one hide behind the other
 
 struct Q4Params {
   int M, N, K;
@@ -57,12 +58,32 @@ struct Q4Cfg {
   static constexpr int kSmemBytes = Q4_STAGES * (kABytes + kBBytes) + 1024 + 256;
 };
 
+// Streaming loads of packed weights.  A thread's bytes of one K block are a 16- or 32-byte piece of a row whose
+// neighbours along K are needed a few blocks later: ask L2 for the whole 256-byte neighbourhood on a miss so that
+// DRAM is read in long bursts and the following K blocks of the row hit in L2.
+__device__ __forceinline__ uint4 q4_ld16(const uint8_t* p) {
+  uint4 v;
+  asm volatile("ld.global.L2::256B.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint2 q4_ld8(const uint8_t* p) {
+  uint2 v;
+  asm volatile("ld.global.L2::256B.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ uint32_t q4_ld4(const uint8_t* p) {
+  uint32_t v;
+  asm volatile("ld.global.L2::256B.u32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+
 __device__ __forceinline__ uint32_t q4_pack2(float a, float b, int fmt) {
   return fmt == 1 ? pack_bf16x2(a, b) : pack_f16x2(a, b);
 }
 
 template <int BN>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(64 + Q4_DQ_THREADS, 1)
 gemm_q4_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmXa,
                      const __grid_constant__ CUtensorMap tmBl, const Q4Params p) {
   using Cfg = Q4Cfg<BN>;
@@ -77,6 +98,7 @@ gemm_q4_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
   const uint32_t bar_acc = bars + 8u * (3 * Q4_STAGES);
   const uint32_t holder = bar_acc + 8u;
   __shared__ float s_code[16];
+  __shared__ float s_code256[256];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BN;
@@ -84,10 +106,12 @@ gemm_q4_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
   const int kbt = p.kblocks1 + p.kblocks2;
 
   if (threadIdx.x < 16) s_code[threadIdx.x] = p.code16[threadIdx.x];
+  if (p.absmax_q != nullptr)
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) s_code256[i] = p.code256[i];
   if (warp == 1 && lane == 0) {
     for (int s = 0; s < Q4_STAGES; ++s) {
       mbar_init(bar_a_full(s), 1);
-      mbar_init(bar_b_full(s), 128);
+      mbar_init(bar_b_full(s), Q4_DQ_THREADS);
       mbar_init(bar_empty(s), 1);
     }
     mbar_init(bar_acc, 1);
@@ -139,57 +163,76 @@ gemm_q4_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
     }
   } else {
     // ------------------------------------------------------------------ dequantise W tiles [BN rows x 64]
-    constexpr int TPR = 128 / BN;        // threads per weight row
-    constexpr int EPT = Q4_BK / TPR;     // elements per thread and K block: 64, 32 or 16
-    const int tid = threadIdx.x - 64;    // 0..127
+    constexpr int TPR = Q4_DQ_THREADS / BN;  // threads per weight row
+    constexpr int EPT = Q4_BK / TPR;     // elements per thread and K block: 32, 16 or 8
+    const int tid = threadIdx.x - 64;    // 0..Q4_DQ_THREADS-1
     const int r = tid / TPR;             // row inside the tile
     const int part = tid % TPR;          // which slice of the row's 64 elements
     const int n = n0 + r;
     const bool row_ok = n < p.N;
     bool ok = true;
-    for (int kb = 0; kb < p.kblocks1 && ok; ++kb) {
-      const int s = kb % Q4_STAGES;
-      // operands first (global / peer loads in flight while waiting for the stage)
-      uint32_t w[EPT / 8];
-      float scale = 0.f;
+    // The packed bytes and the scale code of the next PF K blocks are kept in flight in registers: a weight
+    // byte is used exactly once, so the loop is a stream and its speed is set by how many loads are outstanding.
+    constexpr int PF = 8;
+    constexpr int WPT = EPT / 8;  // 32-bit words (= 16-byte output chunks) per thread and K block
+    uint32_t w[PF][WPT];
+    uint32_t sq[PF];   // 8-bit code of the block scale (double quantised) or the fp32 scale's bits
+    float s2[PF];      // second-level scale of the block
+    auto issue = [&](int slot, int kb) {
 #pragma unroll
-      for (int i = 0; i < EPT / 8; ++i) w[i] = 0u;
-      const int k0 = kb * Q4_BK;
-      if (row_ok && k0 < p.K) {
-        const long long e0 = (long long)n * p.K + k0;       // first element of the 64-block (K % 64 == 0)
-        const long long blk = e0 >> 6;
-        scale = p.absmax_q != nullptr ? p.code256[p.absmax_q[blk]] * p.absmax2[blk >> 8] + p.offset : p.absmax[blk];
-        const long long byte_off = (e0 >> 1) + part * (EPT / 2);
-        const uint8_t* src = p.shard[byte_off / p.shard_bytes] + (byte_off % p.shard_bytes);
-        if constexpr (EPT == 64) {
-          const uint4 u0 = *reinterpret_cast<const uint4*>(src), u1 = *reinterpret_cast<const uint4*>(src + 16);
-          w[0] = u0.x; w[1] = u0.y; w[2] = u0.z; w[3] = u0.w;
-          w[4] = u1.x; w[5] = u1.y; w[6] = u1.z; w[7] = u1.w;
-        } else if constexpr (EPT == 32) {
-          const uint4 u0 = *reinterpret_cast<const uint4*>(src);
-          w[0] = u0.x; w[1] = u0.y; w[2] = u0.z; w[3] = u0.w;
-        } else {
-          const uint2 u0 = *reinterpret_cast<const uint2*>(src);
-          w[0] = u0.x; w[1] = u0.y;
-        }
+      for (int i = 0; i < WPT; ++i) w[slot][i] = 0u;
+      sq[slot] = 0u;
+      s2[slot] = 0.f;
+      if (!row_ok || kb >= p.kblocks1) return;
+      const long long e0 = (long long)n * p.K + (long long)kb * Q4_BK;  // first element of the 64-block
+      const long long blk = e0 >> 6;
+      if (p.absmax_q != nullptr) {
+        sq[slot] = p.absmax_q[blk];
+        s2[slot] = p.absmax2[blk >> 8];
+      } else {
+        sq[slot] = __float_as_uint(p.absmax[blk]);
       }
-      if (!mbar_wait(bar_empty(s), ((kb / Q4_STAGES) & 1) ^ 1u, p.status, kTimeoutDequant)) { ok = false; break; }
-      // one 32-bit word = 8 values = one 16-byte chunk of the swizzled row
-#pragma unroll
-      for (int i = 0; i < EPT / 8; ++i) {
-        uint32_t o[4];
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
-          const uint32_t byte = (w[i] >> (8 * b)) & 0xffu;
-          o[b] = q4_pack2(s_code[byte >> 4] * scale, s_code[byte & 15] * scale, p.fmt);
-        }
-        const int chunk = part * (EPT / 8) + i;  // 0..7 within the row
-        const uint32_t addr = sB(s) + static_cast<uint32_t>(r * 128 + ((chunk ^ (r & 7)) << 4));
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
-                     : "memory");
+      const long long byte_off = (e0 >> 1) + part * (EPT / 2);
+      const uint8_t* src = p.shard[byte_off / p.shard_bytes] + (byte_off % p.shard_bytes);
+      if constexpr (EPT == 32) {
+        const uint4 u0 = q4_ld16(src);
+        w[slot][0] = u0.x; w[slot][1] = u0.y; w[slot][2] = u0.z; w[slot][3] = u0.w;
+      } else if constexpr (EPT == 16) {
+        const uint2 u0 = q4_ld8(src);
+        w[slot][0] = u0.x; w[slot][1] = u0.y;
+      } else {
+        w[slot][0] = q4_ld4(src);
       }
-      fence_proxy_async_smem();
-      mbar_arrive(bar_b_full(s));
+    };
+#pragma unroll
+    for (int j = 0; j < PF; ++j) issue(j, j);
+    for (int kb0 = 0; kb0 < p.kblocks1 && ok; kb0 += PF) {
+#pragma unroll
+      for (int j = 0; j < PF; ++j) {
+        const int kb = kb0 + j;
+        if (kb >= p.kblocks1 || !ok) break;
+        const int s = kb % Q4_STAGES;
+        const float scale = p.absmax_q != nullptr ? s_code256[sq[j]] * s2[j] + p.offset : __uint_as_float(sq[j]);
+        if (!mbar_wait(bar_empty(s), ((kb / Q4_STAGES) & 1) ^ 1u, p.status, kTimeoutDequant)) { ok = false; break; }
+        // one 32-bit word = 8 values = one 16-byte chunk of the swizzled row
+#pragma unroll
+        for (int i = 0; i < WPT; ++i) {
+          uint32_t o[4];
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {
+            const uint32_t byte = (w[j][i] >> (8 * b)) & 0xffu;
+            o[b] = q4_pack2(s_code[byte >> 4] * scale, s_code[byte & 15] * scale, p.fmt);
+          }
+          const int chunk = part * WPT + i;  // 0..7 within the row
+          const uint32_t addr = sB(s) + static_cast<uint32_t>(r * 128 + ((chunk ^ (r & 7)) << 4));
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]),
+                       "r"(o[3])
+                       : "memory");
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(bar_b_full(s));
+        issue(j, kb + PF);
+      }
     }
     // ------------------------------------------------------------------ epilogue
     if (ok && mbar_wait(bar_acc, 0, p.status, kTimeoutEpilogue)) {
@@ -197,8 +240,9 @@ gemm_q4_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       const int q = warp & 3;
       const int row = m0 + q * 32 + lane;
       const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+      // two warps share a lane quarter: warps 2-5 take the even 32-column groups, warps 6-9 the odd ones
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = (warp - 2) >> 2; c < BN / 32; c += 2) {
         uint32_t v[32];
         tmem_ld_32x32(tmem + lane_addr + c * 32, v);
         tmem_ld_wait();
@@ -243,7 +287,7 @@ static int q4_launch(const CUtensorMap& tx, const CUtensorMap& txa, const CUtens
     cfg = true;
   }
   dim3 grid((p.N + BN - 1) / BN, (p.M + Q4_BM - 1) / Q4_BM);
-  gemm_q4_fused_kernel<BN><<<grid, 192, Q4Cfg<BN>::kSmemBytes, stream>>>(tx, txa, tbl, p);
+  gemm_q4_fused_kernel<BN><<<grid, 64 + Q4_DQ_THREADS, Q4Cfg<BN>::kSmemBytes, stream>>>(tx, txa, tbl, p);
   return (int)cudaGetLastError();
 }
 

@@ -12,7 +12,7 @@ import torch
 from torch import nn
 
 from ..ops import quant as Q
-from ..ops.gemm import gemm
+from ..ops.gemm import FUSED_Q4_MAX_ROWS, gemm, gemm_q4_fused
 
 
 class Linear4bit(nn.Module):
@@ -75,6 +75,12 @@ class Linear4bit(nn.Module):
         return Q.dequantize_4bit(self.quant_state(), dtype or self.compute_dtype, out=out)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        rows = x.numel() // max(1, x.shape[-1])
+        if (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and rows <= FUSED_Q4_MAX_ROWS
+                and self.blocksize == 64 and self.in_features % 64 == 0 and self.out_features % 8 == 0):
+            # few rows: the weight is streamed as 4-bit data and expanded inside the GEMM kernel
+            y = _FusedQuantMatmul.apply(x, self)
+            return y if self.bias is None else y + self.bias.to(y.dtype)
         w = self.dequantize(dtype=x.dtype if x.dtype in (torch.bfloat16, torch.float16) else None)
         if x.is_cuda and x.dtype in (torch.bfloat16, torch.float16):
             y = _QuantMatmul.apply(x, w)
@@ -86,6 +92,28 @@ class Linear4bit(nn.Module):
 
     def extra_repr(self) -> str:
         return f"in={self.in_features}, out={self.out_features}, {self.quant_type}, blocksize={self.blocksize}"
+
+
+class _FusedQuantMatmul(torch.autograd.Function):
+    """Forward through the fused dequantise+GEMM kernel; the backward (dx only) expands the weight once."""
+
+    @staticmethod
+    def forward(ctx, x, layer):
+        ctx.layer = layer
+        ctx.shape = x.shape
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.stride(1) != 1 or x2.stride(0) % 8:
+            x2 = x2.contiguous()
+        y = gemm_q4_fused(x2, layer.quant_state())
+        return y.view(*x.shape[:-1], layer.out_features)
+
+    @staticmethod
+    def backward(ctx, dy):
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if dy2.stride(1) != 1 or dy2.stride(0) % 8:
+            dy2 = dy2.contiguous()
+        w = ctx.layer.dequantize(dtype=dy.dtype)
+        return gemm(dy2, w, b_mn=True).view(ctx.shape), None
 
 
 class _QuantMatmul(torch.autograd.Function):

@@ -148,7 +148,21 @@ N.declare("fmsb_gemm_q4_fused", [_ct.c_void_p, _ct.c_longlong, _ct.c_void_p, _ct
                                   _ct.c_float, _ct.c_int, _ct.c_int, _ct.c_int, _ct.c_int, _ct.c_int, _ct.c_void_p,
                                   _ct.c_void_p])
 
-FUSED_Q4_MAX_ROWS = 256  # above this the weight is dequantised once and the plain GEMM is used
+_CODE16_HOST: dict = {}
+
+
+def _code16_host(quant_type: str):
+    arr = _CODE16_HOST.get(quant_type)
+    if arr is None:
+        from .quant import FP4_CODE, NF4_CODE
+
+        vals = {"nf4": NF4_CODE, "fp4": FP4_CODE}[quant_type]
+        arr = (_ct.c_float * 16)(*[float(v) for v in vals])
+        _CODE16_HOST[quant_type] = arr
+    return arr
+
+
+FUSED_Q4_MAX_ROWS = 128  # above this the weight is dequantised once and the plain GEMM is used
 
 
 def gemm_q4_fused(x: torch.Tensor, qs, xa: torch.Tensor | None = None, bl: torch.Tensor | None = None,
@@ -176,12 +190,7 @@ def gemm_q4_fused(x: torch.Tensor, qs, xa: torch.Tensor | None = None, bl: torch
     if bn is None:
         # enough CTAs to put every SM to work on a thin problem
         bn = 128 if (Nn // 128) * ((M + 127) // 128) >= 148 else (64 if (Nn // 64) * ((M + 127) // 128) >= 148 else 32)
-    code = qs.code if qs.code is not None else None
-    if code is None:
-        from .quant import code_book
-
-        code = code_book(qs.quant_type)
-    code_host = (_ct.c_float * 16)(*[float(v) for v in code.detach().float().cpu().tolist()])
+    code_host = _code16_host(qs.quant_type)  # host constants: no device read on the launch path
     r2 = 0
     if xa is not None:
         if bl is None or xa.shape[0] != M or bl.shape[0] != Nn or xa.shape[1] != bl.shape[1]:

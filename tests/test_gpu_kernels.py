@@ -259,3 +259,28 @@ def test_fused_q4_gemm_matches_dequant_then_gemm(M, Nn, K, bn, double_quant, lor
         y2 = gemm_q4_fused(x, qs, xa, bl, shard_ptrs=ptrs, shard_bytes=sb, bn=bn)
         NV.check_status()
         assert torch.equal(y2, y)
+
+
+def test_linear4bit_few_rows_uses_the_fused_kernel():
+    """Same numbers as the dequantise-then-GEMM path, forward and backward, for a handful of rows."""
+    from fms_acceleration_b200.nn import Linear4bit
+    from fms_acceleration_b200.nn import linear4bit as L4
+
+    torch.manual_seed(3)
+    lin = torch.nn.Linear(512, 384, bias=False, device=DEV, dtype=torch.bfloat16)
+    q = Linear4bit.from_linear(lin, "nf4", 64, torch.bfloat16)
+    x = (torch.randn(2, 5, 512, device=DEV) * 0.5).bfloat16().requires_grad_()
+    y = q(x)
+    y.float().square().sum().backward()
+    NV.check_status()
+    gx = x.grad.clone()
+    x.grad = None
+    saved = L4.FUSED_Q4_MAX_ROWS
+    L4.FUSED_Q4_MAX_ROWS = 0
+    try:
+        y2 = q(x)
+        y2.float().square().sum().backward()
+    finally:
+        L4.FUSED_Q4_MAX_ROWS = saved
+    assert (y.float() - y2.float()).abs().max() <= 1e-2 * y2.float().abs().max() + 1e-3
+    assert (gx.float() - x.grad.float()).abs().max() <= 2e-2 * x.grad.float().abs().max() + 1e-3
