@@ -111,7 +111,7 @@ gemm_q4_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
   if (warp == 1 && lane == 0) {
     for (int s = 0; s < Q4_STAGES; ++s) {
       mbar_init(bar_a_full(s), 1);
-      mbar_init(bar_b_full(s), Q4_DQ_THREADS);
+      mbar_init(bar_b_full(s), Q4_DQ_THREADS / 32);  // one arrival per dequant warp
       mbar_init(bar_empty(s), 1);
     }
     mbar_init(bar_acc, 1);
@@ -229,8 +229,9 @@ gemm_q4_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
                        "r"(o[3])
                        : "memory");
         }
-        fence_proxy_async_smem();
-        mbar_arrive(bar_b_full(s));
+        fence_proxy_async_smem();  // every writer orders its own stores before the tensor core's reads
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_b_full(s));
         issue(j, kb + PF);
       }
     }
