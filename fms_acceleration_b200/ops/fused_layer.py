@@ -104,16 +104,17 @@ class _AttentionBlock(torch.autograd.Function):
         T, H = x.shape
         nh, nkv, d = spec.nh, spec.nkv, spec.d
         y1, _, inv1 = RN._fwd_native(x, spec.norm.weight, _norm_eps(spec.norm), spec.gemma, None, False)
-        qkv, xa_qkv = spec.qkv.forward(y1)
+        ctx.aux_qkv, ctx.aux_o = {}, {}
+        qkv, xa_qkv = spec.qkv.forward(y1, aux=ctx.aux_qkv)
         rope_inplace_(qkv, nh + nkv, d, batch.pos, batch.cos, batch.sin, 1.0)
         q2 = qkv[:, : nh * d]
         k2 = qkv[:, nh * d: (nh + nkv) * d]
         v2 = qkv[:, (nh + nkv) * d:]
         o_attn, lse = ATT._fwd(q2, k2, v2, batch.doc_start, batch.doc_end, nh, nkv, d, spec.scale)
         if spec.res_mult == 1.0:
-            h, xa_o = spec.o.forward(o_attn, residual=x)
+            h, xa_o = spec.o.forward(o_attn, residual=x, aux=ctx.aux_o)
         else:
-            part, xa_o = spec.o.forward(o_attn)
+            part, xa_o = spec.o.forward(o_attn, aux=ctx.aux_o)
             h = torch.add(x, part, alpha=spec.res_mult)
         ctx.spec, ctx.batch = spec, batch
         ctx.save_for_backward(x, inv1, y1, qkv, o_attn, lse, xa_qkv, xa_o)
@@ -125,7 +126,7 @@ class _AttentionBlock(torch.autograd.Function):
         x, inv1, y1, qkv, o_attn, lse, xa_qkv, xa_o = ctx.saved_tensors
         nh, nkv, d = spec.nh, spec.nkv, spec.d
         dh = dh.contiguous()
-        d_oattn, g_o = spec.o.backward(_scaled(dh, spec.res_mult), o_attn, xa_o)
+        d_oattn, g_o = spec.o.backward(_scaled(dh, spec.res_mult), o_attn, xa_o, aux=ctx.aux_o)
         dqkv = torch.empty_like(qkv)
         q2 = qkv[:, : nh * d]
         k2 = qkv[:, nh * d: (nh + nkv) * d]
@@ -135,7 +136,7 @@ class _AttentionBlock(torch.autograd.Function):
         rope_inplace_(dqkv, nh + nkv, d, batch.pos, batch.cos, batch.sin, -1.0)
         need_dx = ctx.needs_input_grad[0]
         norm_trains = spec.norm.weight.requires_grad
-        dy1, g_qkv = spec.qkv.backward(dqkv, y1, xa_qkv, need_dx=need_dx or norm_trains)
+        dy1, g_qkv = spec.qkv.backward(dqkv, y1, xa_qkv, need_dx=need_dx or norm_trains, aux=ctx.aux_qkv)
         dx = None
         grads: List[Optional[torch.Tensor]] = []
         if need_dx or norm_trains:
@@ -151,12 +152,13 @@ class _MLPBlock(torch.autograd.Function):
     def forward(ctx, h, spec: MLPBlockSpec, *params):
         I = spec.inter
         y2, _, inv2 = RN._fwd_native(h, spec.norm.weight, _norm_eps(spec.norm), spec.gemma, None, False)
-        gu, xa_gu = spec.gate_up.forward(y2)
+        ctx.aux_gu, ctx.aux_d = {}, {}
+        gu, xa_gu = spec.gate_up.forward(y2, aux=ctx.aux_gu)
         act = ACT.glu_fwd(gu[:, :I], gu[:, I:], spec.act)
         if spec.res_mult == 1.0:
-            out, xa_d = spec.down.forward(act, residual=h)
+            out, xa_d = spec.down.forward(act, residual=h, aux=ctx.aux_d)
         else:
-            part, xa_d = spec.down.forward(act)
+            part, xa_d = spec.down.forward(act, aux=ctx.aux_d)
             out = torch.add(h, part, alpha=spec.res_mult)
         keep_y2 = len(spec.gate_up.trainable()) > 0
         ctx.spec = spec
@@ -173,12 +175,12 @@ class _MLPBlock(torch.autograd.Function):
         act = None
         if len(spec.down.trainable()) > 0:
             act = ACT.glu_fwd(gu[:, :I], gu[:, I:], spec.act)
-        dact, g_d = spec.down.backward(_scaled(dout, spec.res_mult), act, xa_d)
+        dact, g_d = spec.down.backward(_scaled(dout, spec.res_mult), act, xa_d, aux=ctx.aux_d)
         # in place: gu <- (d gate | d up)
         ACT.glu_bwd(dact, gu[:, :I], gu[:, I:], spec.act, de=gu[:, :I], dg=gu[:, I:])
         if y2 is None and len(spec.gate_up.trainable()) > 0:
             y2, _, _ = RN._fwd_native(h, spec.norm.weight, _norm_eps(spec.norm), spec.gemma, None, False)
-        dy2, g_gu = spec.gate_up.backward(gu, y2, xa_gu)
+        dy2, g_gu = spec.gate_up.backward(gu, y2, xa_gu, aux=ctx.aux_gu)
         norm_trains = spec.norm.weight.requires_grad
         dh, dw = RN._bwd_native(dy2, h, spec.norm.weight, inv2, spec.gemma, dout, norm_trains)
         grads: List[Optional[torch.Tensor]] = []

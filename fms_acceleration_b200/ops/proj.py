@@ -134,14 +134,37 @@ class ProjGroup:
         return A_cat, B_blk, slices
 
     # ------------------------------------------------------------------ forward
-    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None):
-        """x [T, in] -> (y [T, total_out], xa [T, R] or None).  ``residual`` is added in the GEMM epilogue."""
+    def dropout_p(self) -> float:
+        """LoRA input dropout of this group while training (0.0 in eval mode or without dropout)."""
+        for l in self.loras:
+            if l is None or not l.training:
+                continue
+            name = l.active_adapters[0] if hasattr(l, "active_adapters") else "default"
+            d = l.lora_dropout[name] if hasattr(l, "lora_dropout") else None
+            p = float(getattr(d, "p", 0.0)) if d is not None else 0.0
+            if p > 0.0:
+                return p
+        return 0.0
+
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                aux: Optional[dict] = None):
+        """x [T, in] -> (y [T, total_out], xa [T, R] or None).  ``residual`` is added in the GEMM epilogue.
+        With LoRA dropout the keep mask is left in ``aux["mask"]`` for :meth:`backward` (the adapter branch sees
+        ``dropout(x)``, the base branch sees ``x``, as in the reference's fused LoRA functions)."""
         dtype, dev = x.dtype, x.device
         xa = None
         a2 = b2 = None
         if self.has_lora:
             A_cat, B_blk, _ = self.lora_cat(dtype, dev)
-            xa = gemm(x, A_cat)
+            p = self.dropout_p()
+            if p > 0.0:
+                if aux is None:
+                    raise ValueError("LoRA dropout is active: pass an `aux` dict to keep the mask for the backward")
+                mask = torch.rand(x.shape, device=dev) >= p
+                aux["mask"], aux["keep_scale"] = mask, 1.0 / (1.0 - p)
+                xa = gemm(x * mask * aux["keep_scale"], A_cat)
+            else:
+                xa = gemm(x, A_cat)
             a2, b2 = xa, B_blk
         beta = 1.0 if residual is not None else 0.0
         if self.kind == "dense" and len(self.bases) > 1:
@@ -158,24 +181,27 @@ class ProjGroup:
 
     # ------------------------------------------------------------------ backward
     def backward(self, dy: torch.Tensor, x: torch.Tensor, xa: Optional[torch.Tensor], need_dx: bool = True,
-                 dx_residual: Optional[torch.Tensor] = None):
+                 dx_residual: Optional[torch.Tensor] = None, aux: Optional[dict] = None):
         """Returns (dx [T, in] or None, grads aligned with ``trainable()``).  ``dx_residual`` is added to dx."""
         dtype, dev = dy.dtype, dy.device
         grads: List[torch.Tensor] = []
         dxa_s = None
         A_cat = None
+        mask = aux.get("mask") if aux else None
         if self.has_lora:
             A_cat, B_blk, slices = self.lora_cat(dtype, dev)
             R = A_cat.shape[0]
             # dxa = dy @ B_blk  (already carries the scaling)
             dxa_s = gemm(dy, B_blk, b_mn=True)
-            # dB_blk = dy^T @ xa ; dA_cat = dxa^T @ x
+            # dB_blk = dy^T @ xa ; dA_cat = dxa^T @ dropout(x)
             dB_blk = gemm(dy, xa, a_mn=True, b_mn=True, out_dtype=torch.float32)
-            dA_cat = gemm(dxa_s, x, a_mn=True, b_mn=True, out_dtype=torch.float32)
+            xd = x if mask is None else x * mask * aux["keep_scale"]
+            dA_cat = gemm(dxa_s, xd, a_mn=True, b_mn=True, out_dtype=torch.float32)
         dx = None
         if need_dx:
             beta = 1.0 if dx_residual is not None else 0.0
-            a2 = dxa_s if self.has_lora else None
+            # with dropout the adapter's input gradient is masked, so it cannot ride on the base GEMM
+            a2 = dxa_s if (self.has_lora and mask is None) else None
             if self.kind == "dense" and len(self.bases) > 1:
                 dx = torch.empty(dy.shape[0], self.in_features, dtype=dtype, device=dev)
                 first = True
@@ -192,6 +218,9 @@ class ProjGroup:
                     dx = gemm(dy, W, b_mn=False, a2=a2, b2=b2, c=dx_residual, beta=beta)
                 else:
                     dx = gemm(dy, W, b_mn=True, a2=a2, b2=A_cat, c=dx_residual, beta=beta)
+            if mask is not None:
+                dxl = gemm(dxa_s, A_cat, b_mn=True)  # [T, in]
+                dx = torch.addcmul(dx, dxl, mask.to(dtype), value=aux["keep_scale"])
         # parameter gradients in the order of trainable()
         for i, (b, l) in enumerate(zip(self.bases, self.loras)):
             o0, o1 = self.offsets[i], self.offsets[i + 1]

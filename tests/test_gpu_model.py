@@ -94,3 +94,47 @@ def test_fused_path_matches_eager(quant, d):
     # cu_seqlens form of the same batch gives the same loss
     out2 = model(input_ids=batch["input_ids"].to(dev), labels=batch["labels"].to(dev), cu_seqlens=batch["cu_seqlens"].to(dev))
     assert abs(out2.loss.item() - out.loss.item()) < 1e-3
+
+
+def test_fused_lora_dropout_matches_masked_reference():
+    """LoRA dropout in the fused projection group: forward and all gradients equal an fp32 reference that applies
+    the SAME keep mask to the adapter branch only."""
+    from fms_acceleration_b200.nn.lora import LoraLinear
+    from fms_acceleration_b200.ops.proj import ProjGroup
+
+    torch.manual_seed(0)
+    dev = "cuda"
+    T, H, O, r, p = 256, 512, 384, 16, 0.25
+    lin = torch.nn.Linear(H, O, bias=False, device=dev, dtype=torch.bfloat16)
+    lin.weight.requires_grad_(False)
+    q = Linear4bit.from_linear(lin, "nf4", 64, torch.bfloat16)
+    lora = LoraLinear(q, r, 16, lora_dropout=p).to(dev)
+    with torch.no_grad():
+        lora.lora_B["default"].weight.normal_(0, 0.05)  # B starts at zero: make the adapter branch visible
+    lora.train()
+    grp = ProjGroup([lora], "t")
+    assert grp.dropout_p() == p
+    x = (torch.randn(T, H, device=dev) * 0.5).bfloat16()
+    dy = (torch.randn(T, O, device=dev) * 0.1).bfloat16()
+    aux = {}
+    y, xa = grp.forward(x, aux=aux)
+    dx, grads = grp.backward(dy, x, xa, aux=aux)
+    NV.check_status()
+    mask, ks = aux["mask"], aux["keep_scale"]
+    assert 0.6 < mask.float().mean() < 0.9 and abs(ks - 1 / (1 - p)) < 1e-6
+    W = q.dequantize(dtype=torch.bfloat16).float()
+    A = lora.lora_A["default"].weight.detach().float().requires_grad_()
+    B = lora.lora_B["default"].weight.detach().float().requires_grad_()
+    s = lora.scaling["default"]
+    xr = x.float().requires_grad_()
+    yr = xr @ W.t() + s * ((xr * mask * ks) @ A.t()) @ B.t()
+    yr.backward(dy.float())
+
+    def rel(a, b):
+        return ((a.float() - b.float()).norm() / b.float().norm().clamp(min=1e-9)).item()
+
+    assert rel(y, yr) < 2e-2
+    assert rel(dx, xr.grad) < 3e-2
+    assert rel(grads[0], A.grad) < 3e-2 and rel(grads[1], B.grad) < 3e-2
+    lora.eval()
+    assert grp.dropout_p() == 0.0
