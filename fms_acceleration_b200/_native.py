@@ -37,7 +37,7 @@ _SIGNATURES = {
     "fmsb_quant4": [P, L, P, I, P, P, I, P],
     "fmsb_quant8_blockwise": [P, L, F, P, P, P, P],
     "fmsb_dequant4": [P, P, P, P, P, F, P, I, L, P, I, P],
-    "fmsb_gptq_dequant": [P, P, P, P, I, I, I, I, I, P, I, P],
+    "fmsb_gptq_dequant": [P, P, P, P, I, I, I, I, I, P, L, I, P],
 }
 
 

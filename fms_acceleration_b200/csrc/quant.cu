@@ -156,7 +156,7 @@ template <typename T>
 __global__ void gptq_dequant_kernel(const int* __restrict__ qweight, const T* __restrict__ scales,
                                     const int* __restrict__ qzeros, const int* __restrict__ g_idx, int in_features,
                                     int out_features, int bits, int group_size, int zero_offset,
-                                    T* __restrict__ out) {
+                                    T* __restrict__ out, long long ldo) {
   const int per = 32 / bits;
   const uint32_t mask = (1u << bits) - 1u;
   const long long total = (long long)in_features * out_features;
@@ -171,11 +171,88 @@ __global__ void gptq_dequant_kernel(const int* __restrict__ qweight, const T* __
     const int zv = (int)((qz >> ((c % per) * bits)) & mask) + zero_offset;
     const float s = to_f<T>(scales[(long long)g * out_features + c]);
     const float v = s * (float)(wv - zv);
+    const long long o = (long long)r * ldo + c;
     if (std::is_same<T, __nv_bfloat16>::value)
-      reinterpret_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(v);
+      reinterpret_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(v);
     else
-      reinterpret_cast<__half*>(out)[idx] = __float2half_rn(v);
+      reinterpret_cast<__half*>(out)[o] = __float2half_rn(v);
   }
+}
+
+// Vectorised form used whenever out_features % 8 == 0: one thread expands one packed word row (32/BITS input rows)
+// of 8 consecutive output columns: 8 coalesced int32 loads, then 32/BITS coalesced 16-byte stores.  Every packed
+// word is read once (the scalar kernel above reads it 32/BITS times and stores 2 bytes at a time).
+template <typename T, int BITS>
+__global__ void gptq_dequant_vec_kernel(const int* __restrict__ qweight, const T* __restrict__ scales,
+                                        const int* __restrict__ qzeros, const int* __restrict__ g_idx,
+                                        int in_features, int out_features, int group_size, int zero_offset,
+                                        T* __restrict__ out, long long ldo) {
+  constexpr int PER = 32 / BITS;
+  constexpr uint32_t MASK = (1u << BITS) - 1u;
+  const int cgroups = out_features / 8;
+  const long long total = (long long)(in_features / PER) * cgroups;
+  const int zwords = out_features / PER;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int pr = (int)(idx / cgroups);
+    const int c0 = (int)(idx % cgroups) * 8;
+    const uint4 qa = *reinterpret_cast<const uint4*>(qweight + (long long)pr * out_features + c0);
+    const uint4 qb = *reinterpret_cast<const uint4*>(qweight + (long long)pr * out_features + c0 + 4);
+    const uint32_t qw[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+    const int r0 = pr * PER;
+    int g_prev = -1;
+    float sc[8], zs[8];  // scale and scale * zero per column for the current group
+#pragma unroll 1
+    for (int j = 0; j < PER; ++j) {
+      const int r = r0 + j;
+      const int g = g_idx != nullptr ? g_idx[r] : r / group_size;
+      if (g != g_prev) {
+        g_prev = g;
+        const uint4 sv = *reinterpret_cast<const uint4*>(scales + (long long)g * out_features + c0);
+        const T* sp = reinterpret_cast<const T*>(&sv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int c = c0 + i;
+          const uint32_t qz = (uint32_t)qzeros[(long long)g * zwords + c / PER];
+          const int zv = (int)((qz >> ((c % PER) * BITS)) & MASK) + zero_offset;
+          sc[i] = to_f<T>(sp[i]);
+          zs[i] = (float)zv;
+        }
+      }
+      float v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = sc[i] * ((float)((qw[i] >> (j * BITS)) & MASK) - zs[i]);
+      uint4 o;
+      if (std::is_same<T, __nv_bfloat16>::value) {
+        o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+        o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+      } else {
+        o.x = pack_f16x2(v[0], v[1]); o.y = pack_f16x2(v[2], v[3]);
+        o.z = pack_f16x2(v[4], v[5]); o.w = pack_f16x2(v[6], v[7]);
+      }
+      *reinterpret_cast<uint4*>(out + (long long)r * ldo + c0) = o;
+    }
+  }
+}
+
+template <typename T>
+static int gptq_launch_vec(const int* qweight, const T* scales, const int* qzeros, const int* g_idx, int in_features,
+                           int out_features, int bits, int group_size, int zero_offset, T* out, long long ldo,
+                           cudaStream_t stream) {
+  const int per = 32 / bits;
+  const long long total = (long long)(in_features / per) * (out_features / 8);
+  long long ctas = (total + 255) / 256;
+  if (ctas > 148 * 32) ctas = 148 * 32;
+  if (bits == 4)
+    gptq_dequant_vec_kernel<T, 4><<<(int)ctas, 256, 0, stream>>>(qweight, scales, qzeros, g_idx, in_features,
+                                                                out_features, group_size, zero_offset, out, ldo);
+  else if (bits == 8)
+    gptq_dequant_vec_kernel<T, 8><<<(int)ctas, 256, 0, stream>>>(qweight, scales, qzeros, g_idx, in_features,
+                                                                out_features, group_size, zero_offset, out, ldo);
+  else
+    gptq_dequant_vec_kernel<T, 2><<<(int)ctas, 256, 0, stream>>>(qweight, scales, qzeros, g_idx, in_features,
+                                                                out_features, group_size, zero_offset, out, ldo);
+  return (int)cudaGetLastError();
 }
 
 }  // namespace fmsb
@@ -233,21 +310,32 @@ extern "C" int fmsb_dequant4(const void* packed, const float* absmax, const void
 
 extern "C" int fmsb_gptq_dequant(const int* qweight, const void* scales, const int* qzeros, const int* g_idx,
                                  int in_features, int out_features, int bits, int group_size, int zero_offset,
-                                 void* out, int dtype, cudaStream_t stream) {
+                                 void* out, long long ldo, int dtype, cudaStream_t stream) {
   if (!(bits == 2 || bits == 4 || bits == 8)) return -2;
   if (out_features % (32 / bits) != 0 || in_features % (32 / bits) != 0) return -2;
   const long long total = (long long)in_features * out_features;
   if (total <= 0) return 0;
+  // (v - z) * s in the vector kernel equals s * (v - z) of the scalar one: one fp32 product of the same operands
+  if (ldo < out_features) return -2;
+  const bool aligned = ((uintptr_t)qweight % 16 == 0) && ((uintptr_t)scales % 16 == 0) && ((uintptr_t)out % 16 == 0) &&
+                       (ldo % 8 == 0);
+  if (out_features % 8 == 0 && aligned && (dtype == 0 || dtype == 1)) {
+    if (dtype == 1)
+      return gptq_launch_vec<__nv_bfloat16>(qweight, (const __nv_bfloat16*)scales, qzeros, g_idx, in_features,
+                                            out_features, bits, group_size, zero_offset, (__nv_bfloat16*)out, ldo, stream);
+    return gptq_launch_vec<__half>(qweight, (const __half*)scales, qzeros, g_idx, in_features, out_features, bits,
+                                   group_size, zero_offset, (__half*)out, ldo, stream);
+  }
   long long ctas = (total + 255) / 256;
   if (ctas > 148 * 32) ctas = 148 * 32;
   if (dtype == 1)
     gptq_dequant_kernel<__nv_bfloat16><<<(int)ctas, 256, 0, stream>>>(qweight, (const __nv_bfloat16*)scales, qzeros,
                                                                       g_idx, in_features, out_features, bits,
-                                                                      group_size, zero_offset, (__nv_bfloat16*)out);
+                                                                      group_size, zero_offset, (__nv_bfloat16*)out, ldo);
   else if (dtype == 0)
     gptq_dequant_kernel<__half><<<(int)ctas, 256, 0, stream>>>(qweight, (const __half*)scales, qzeros, g_idx,
                                                                in_features, out_features, bits, group_size,
-                                                               zero_offset, (__half*)out);
+                                                               zero_offset, (__half*)out, ldo);
   else
     return -2;
   return (int)cudaGetLastError();

@@ -87,7 +87,13 @@ class QuantLinear(nn.Module):
     # ------------------------------------------------------------------ compute
     def dequantize(self, out=None, dtype=None) -> torch.Tensor:
         """Dense ``[in, out]`` weight."""
-        scales = self.scales if dtype is None or dtype == self.scales.dtype else self.scales.to(dtype)
+        scales = self.scales
+        if dtype is not None and dtype != scales.dtype:
+            cached = getattr(self, "_scales_cast", None)
+            if cached is None or cached[0] != dtype or cached[1] is not self.scales:
+                cached = (dtype, self.scales, self.scales.to(dtype))  # the weights are frozen: convert once
+                self._scales_cast = cached
+            scales = cached[2]
         g_idx = None if self._sequential_groups else self.g_idx
         return Q.gptq_dequant(self.qweight, scales, self.qzeros, g_idx if self.qweight.is_cuda else self.g_idx,
                               self.bits, self.group_size, self.zero_offset, out=out)

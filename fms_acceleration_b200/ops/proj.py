@@ -103,9 +103,7 @@ class ProjGroup:
             self.bases[0].dequantize(out=W, dtype=dtype)
         else:
             for b, o0, o1 in zip(self.bases, self.offsets[:-1], self.offsets[1:]):
-                tmp = WS.get2d("wdeq_part", self.in_features, o1 - o0, dtype, device)
-                b.dequantize(out=tmp, dtype=dtype)
-                W[:, o0:o1].copy_(tmp)
+                b.dequantize(out=W[:, o0:o1], dtype=dtype)  # written in place through the row stride
         return W, True
 
     def lora_cat(self, dtype, device):

@@ -228,9 +228,11 @@ def gptq_dequant(qweight, scales, qzeros, g_idx, bits: int, group_size: int, zer
         return gptq_dequant_ref(qweight, scales, qzeros, g_idx, bits, zero_offset)
     if out is None:
         out = torch.empty(in_features, out_features, dtype=scales.dtype, device=qweight.device)
+    elif out.shape != (in_features, out_features) or out.stride(1) != 1 or out.dtype != scales.dtype:
+        raise ValueError("`out` must be [in, out] with unit column stride and the dtype of the scales")
     rc = N.lib().fmsb_gptq_dequant(qweight.data_ptr(), scales.data_ptr(), qzeros.data_ptr(), N.ptr(g_idx),
                                    in_features, out_features, bits, group_size, zero_offset, out.data_ptr(),
-                                   N.dtype_code(scales.dtype), N.stream_ptr())
+                                   out.stride(0), N.dtype_code(scales.dtype), N.stream_ptr())
     N.check(rc, "fmsb_gptq_dequant")
     return out
 
