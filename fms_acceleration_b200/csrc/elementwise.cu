@@ -149,21 +149,23 @@ rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ residual, cons
 }
 
 // dx = inv/H * (H * dy*w - xhat * sum(dy*w*xhat)) [+ dres_in];   dw_partial[block] += dy * xhat
-template <typename T>
+// MAXV vectors of 8 are cached per thread (2 covers H <= 4096 with a third of the registers of 4); the weight-gradient
+// accumulators exist only when WITH_DW, so the common frozen-norm case runs several CTAs per SM.
+template <typename T, int MAXV, bool WITH_DW>
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
                    const float* __restrict__ inv_rms, const T* __restrict__ dres_in, T* __restrict__ dx,
                    float* __restrict__ dw_partial, int rows, int H, int gemma) {
   __shared__ float red[NORM_THREADS / 32];
   const int nvec = H / 8;
-  float dwacc[NORM_MAXV][8];
+  float dwacc[WITH_DW ? MAXV : 1][8];
 #pragma unroll
-  for (int j = 0; j < NORM_MAXV; ++j)
+  for (int j = 0; j < (WITH_DW ? MAXV : 1); ++j)
 #pragma unroll
     for (int i = 0; i < 8; ++i) dwacc[j][i] = 0.f;
-  float wf[NORM_MAXV][8];
+  float wf[MAXV][8];
 #pragma unroll
-  for (int j = 0; j < NORM_MAXV; ++j) {
+  for (int j = 0; j < MAXV; ++j) {
     const int v = threadIdx.x + j * NORM_THREADS;
     if (v < nvec) {
       Vec8<T> wv;
@@ -177,10 +179,10 @@ rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* _
   }
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const float inv = inv_rms[row];
-    float xh[NORM_MAXV][8], g[NORM_MAXV][8];
+    float xh[MAXV][8], g[MAXV][8];
     float dot = 0.f;
 #pragma unroll
-    for (int j = 0; j < NORM_MAXV; ++j) {
+    for (int j = 0; j < MAXV; ++j) {
       const int v = threadIdx.x + j * NORM_THREADS;
       if (v < nvec) {
         Vec8<T> a, b;
@@ -194,14 +196,14 @@ rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* _
           xh[j][i] *= inv;
           g[j][i] = dyf[i] * wf[j][i];
           dot += g[j][i] * xh[j][i];
-          dwacc[j][i] += dyf[i] * xh[j][i];
+          if (WITH_DW) dwacc[WITH_DW ? j : 0][i] += dyf[i] * xh[j][i];
         }
       }
     }
     const float tot = block_sum(dot, red);
     const float c = tot / (float)H;
 #pragma unroll
-    for (int j = 0; j < NORM_MAXV; ++j) {
+    for (int j = 0; j < MAXV; ++j) {
       const int v = threadIdx.x + j * NORM_THREADS;
       if (v < nvec) {
         float out[8];
@@ -221,9 +223,9 @@ rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* _
       }
     }
   }
-  if (dw_partial != nullptr) {
+  if (WITH_DW && dw_partial != nullptr) {
 #pragma unroll
-    for (int j = 0; j < NORM_MAXV; ++j) {
+    for (int j = 0; j < (WITH_DW ? MAXV : 1); ++j) {
       const int v = threadIdx.x + j * NORM_THREADS;
       if (v < nvec) {
         float* dst = dw_partial + (long long)blockIdx.x * H + v * 8;
@@ -425,19 +427,24 @@ extern "C" int fmsb_rmsnorm_bwd(const void* dy, const void* x, const void* w, co
                                 int rows, int H, int gemma, int dtype, cudaStream_t stream) {
   if (H % 8 != 0 || H > 8 * NORM_THREADS * NORM_MAXV) return -2;
   if (rows <= 0) return 0;
-  int grid = rows < 148 * 4 ? rows : 148 * 4;
+  // without a weight gradient the kernel is light on registers: several CTAs per SM, 8 waves of rows each
+  int grid = rows < 148 * 8 ? rows : 148 * 8;
   if (dw_partial != nullptr) {
     if (n_partial_blocks <= 0) return -2;
     grid = n_partial_blocks;
   }
-  if (dtype == 1)
-    rmsnorm_bwd_kernel<__nv_bfloat16><<<grid, NORM_THREADS, 0, stream>>>(
-        (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, inv_rms,
-        (const __nv_bfloat16*)dres_in, (__nv_bfloat16*)dx, dw_partial, rows, H, gemma);
-  else
-    rmsnorm_bwd_kernel<__half><<<grid, NORM_THREADS, 0, stream>>>((const __half*)dy, (const __half*)x,
-                                                                  (const __half*)w, inv_rms, (const __half*)dres_in,
-                                                                  (__half*)dx, dw_partial, rows, H, gemma);
+  const bool small = H <= 8 * NORM_THREADS * 2;
+#define FMSB_NORM_BWD(T, MAXV, DW)                                                                                  \
+  rmsnorm_bwd_kernel<T, MAXV, DW><<<grid, NORM_THREADS, 0, stream>>>((const T*)dy, (const T*)x, (const T*)w, inv_rms, \
+                                                                     (const T*)dres_in, (T*)dx, dw_partial, rows, H, gemma)
+  if (dtype == 1) {
+    if (dw_partial != nullptr) { if (small) FMSB_NORM_BWD(__nv_bfloat16, 2, true); else FMSB_NORM_BWD(__nv_bfloat16, 4, true); }
+    else { if (small) FMSB_NORM_BWD(__nv_bfloat16, 2, false); else FMSB_NORM_BWD(__nv_bfloat16, 4, false); }
+  } else {
+    if (dw_partial != nullptr) { if (small) FMSB_NORM_BWD(__half, 2, true); else FMSB_NORM_BWD(__half, 4, true); }
+    else { if (small) FMSB_NORM_BWD(__half, 2, false); else FMSB_NORM_BWD(__half, 4, false); }
+  }
+#undef FMSB_NORM_BWD
   if (dw_partial != nullptr && dw != nullptr) {
     colsum_kernel<<<(H + 255) / 256, 256, 0, stream>>>(dw_partial, dw, grid, H);
   }
