@@ -69,16 +69,30 @@ __global__ void barrier_kernel(PeerPtrs signals, int rank, int world, int chan, 
 // ----------------------------------------------------------------------------------------
 __global__ void allgather_pull_kernel(PeerPtrs src, uint8_t* __restrict__ dst, long long shard_bytes, int rank,
                                       int world) {
-  const long long total16 = shard_bytes * world / 16;
+  // Each thread keeps UNROLL independent 16-byte peer loads in flight: over NVLink the latency is microseconds, so
+  // the bandwidth of a pull is (bytes in flight) / latency.  Work is split per source shard, starting with the
+  // successor of this rank so that the peers are not all hit in the same order.
+  constexpr int UNROLL = 8;
   const long long shard16 = shard_bytes / 16;
   const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total16; i += stride) {
-    // start each rank on its own shard's successor so peers are not all hit in the same order
-    const long long j = (i + (long long)(rank + 1) * shard16) % total16;
-    const int owner = (int)(j / shard16);
-    const long long off = j - (long long)owner * shard16;
-    const uint4 v = *(reinterpret_cast<const uint4*>(src.p[owner]) + off);
-    *(reinterpret_cast<uint4*>(dst) + j) = v;
+  const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  for (int s = 0; s < world; ++s) {
+    const int owner = (rank + 1 + s) % world;
+    const uint4* __restrict__ from = reinterpret_cast<const uint4*>(src.p[owner]);
+    uint4* __restrict__ to = reinterpret_cast<uint4*>(dst) + (long long)owner * shard16;
+    for (long long base = tid; base < shard16; base += stride * UNROLL) {
+      uint4 v[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const long long i = base + u * stride;
+        if (i < shard16) v[u] = from[i];
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const long long i = base + u * stride;
+        if (i < shard16) to[i] = v[u];
+      }
+    }
   }
 }
 

@@ -16,6 +16,8 @@ adapters (fms_acceleration_foak/utils.py:27-80).
 """
 from __future__ import annotations
 
+import os
+
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -151,7 +153,7 @@ class ShardedEngine:
             if self._released[slot] is not None:
                 self.comm_stream.wait_event(self._released[slot])
             blob = self.blobs[i]
-            self.comm.allgather_into(self.arena, self.shard_offsets[i], blob.shard_bytes, self.staging[slot], ctas=16)
+            self.comm.allgather_into(self.arena, self.shard_offsets[i], blob.shard_bytes, self.staging[slot], ctas=32)
             ev = torch.cuda.Event()
             ev.record(self.comm_stream)
         self._ready[slot] = ev
@@ -260,5 +262,7 @@ def install_engine(model: nn.Module, accelerator, **kwargs) -> Optional[ShardedE
         return accelerator.engine
     if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
         return None
+    if os.environ.get("FMSB_SHARD_FROZEN", "1") == "0":
+        kwargs["shard_frozen"] = False  # keep the frozen weights replicated (memory for less traffic)
     accelerator.engine = ShardedEngine(model, **kwargs)
     return accelerator.engine
