@@ -176,3 +176,5 @@ declare("fmsb_attn_bwd_dq", [P, L, P, L, P, L, P, L, P, L, P, P, P, P, I, I, I, 
 declare("fmsb_attn_bwd_dkv", [P, L, P, L, P, L, P, L, P, L, P, L, P, P, P, P, I, I, I, I, F, I, P, P])
 declare("fmsb_attn_bwd_dq2", [P, L, P, L, P, L, P, L, P, L, P, P, P, P, I, I, I, I, F, I, P, P])
 declare("fmsb_attn_bwd_dkv2", [P, L, P, L, P, L, P, L, P, L, P, L, P, P, P, P, I, I, I, I, F, I, P, P])
+declare("fmsb_attn_bwd_dq3", [P, L, P, L, P, L, P, L, P, L, P, P, P, P, I, I, I, I, F, I, P, P])
+declare("fmsb_attn_bwd_dkv3", [P, L, P, L, P, L, P, L, P, L, P, L, P, P, P, P, I, I, I, I, F, I, P, P])
