@@ -172,8 +172,6 @@ def check_status(device=None) -> None:
 
 declare("fmsb_attn_fwd", [P, L, P, L, P, L, P, L, P, P, P, I, I, I, I, F, I, P, P])
 declare("fmsb_attn_delta", [P, P, L, L, P, I, I, I, I, P])
-declare("fmsb_attn_bwd_dq", [P, L, P, L, P, L, P, L, P, L, P, P, P, P, I, I, I, I, F, I, P, P])
-declare("fmsb_attn_bwd_dkv", [P, L, P, L, P, L, P, L, P, L, P, L, P, P, P, P, I, I, I, I, F, I, P, P])
 declare("fmsb_attn_bwd_dq2", [P, L, P, L, P, L, P, L, P, L, P, P, P, P, I, I, I, I, F, I, P, P])
 declare("fmsb_attn_bwd_dkv2", [P, L, P, L, P, L, P, L, P, L, P, L, P, P, P, P, I, I, I, I, F, I, P, P])
 declare("fmsb_attn_bwd_dq3", [P, L, P, L, P, L, P, L, P, L, P, P, P, P, I, I, I, I, F, I, P, P])

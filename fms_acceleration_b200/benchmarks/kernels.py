@@ -109,7 +109,7 @@ def bench_attn(a):
     extra = {}
     if a.compare_v1:
         g3 = AT._bwd(q, k, v, o, lse, do, ds, de, nh, nkv, d, scale)
-        for gen in (2, 1):
+        for gen in (2,):
             AT.BWD_GENERATION = gen
             g = AT._bwd(q, k, v, o, lse, do, ds, de, nh, nkv, d, scale)
             extra[f"bwd_gen{gen}_ms"] = timeit(lambda: AT._bwd(q, k, v, o, lse, do, ds, de, nh, nkv, d, scale), a.iters,

@@ -9,18 +9,8 @@
 // Layout: q [T, nh*d], k/v [T, nkv*d] (any row stride, e.g. slices of one packed qkv buffer),
 // o [T, nh*d], lse [nh, T] fp32 (natural log).  d in {64, 128}.
 //
-// Forward, one CTA per (128-query tile, head); 6 warps:
-//   warp 0     TMA producer: Q once, then K/V blocks of 128 keys through a 2-stage ring
-//   warp 1     MMA issuer:   S_j = Q K_j^T (fp32 in tensor memory, double buffered) and
-//                            O  += P_j V_j (P_j read from shared memory, V_j MN-major)
-//   warps 2-5  softmax: one thread per query row reads its S row from tensor memory, applies
-//              the document/causal mask, keeps the running max and sum, writes P_j (bf16) into
-//              the 128-byte-swizzled K-major operand layout and rescales O in tensor memory
-//              when the running max moved.
-// Backward = three kernels: delta = rowsum(dO*O); dQ (fixed query tile, loop over key blocks);
-// dK/dV (fixed key tile, loop over the query heads of the group and their query blocks).  Both
-// recompute S and dP; the same shared-memory tile is used through a K-major and an MN-major
-// descriptor where a matrix is needed in both orientations, so nothing is transposed in memory.
+// This file holds the forward kernel (two query tiles per CTA, see below) and the delta = rowsum(dO*O)
+// kernel; the backward kernels live in attention_bwd3.cu (in use) and attention_bwd.cu (cross-check).
 #include "common.cuh"
 
 namespace fmsb {
@@ -48,260 +38,6 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, int fmt) {
 // [rows x 64] 16-bit tile stored with the 128-byte swizzle.
 __device__ __forceinline__ uint32_t swz_off(int r, int c16) {
   return static_cast<uint32_t>(r * 128 + ((c16 ^ (r & 7)) << 4));
-}
-
-template <int D>
-struct AttnFwdCfg {
-  static constexpr int kTileBytes = 128 * D * 2;          // one [128 x D] operand tile
-  static constexpr int kHalfBytes = 128 * 64 * 2;         // one 64-column block of it
-  static constexpr int kStages = 2;
-  static constexpr int kPBytes = 128 * 128 * 2;
-  static constexpr int kSmemBytes = kTileBytes /*Q*/ + kStages * 2 * kTileBytes /*K,V*/ + kPBytes + 1024 + 256;
-  static constexpr int kTmemCols = 512;  // S0 | S1 | O | (spare)
-};
-
-template <int D>
-__global__ void __launch_bounds__(192, 1)
-attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
-  using Cfg = AttnFwdCfg<D>;
-  constexpr int NH = D / 64;  // 64-column blocks per head dim
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t sQ = base;
-  auto sK = [&](int s) { return base + Cfg::kTileBytes * (1 + 2 * s); };
-  auto sV = [&](int s) { return base + Cfg::kTileBytes * (2 + 2 * s); };
-  const uint32_t sP = base + Cfg::kTileBytes * (1 + 2 * Cfg::kStages);
-  const uint32_t bars = sP + Cfg::kPBytes;
-  const uint32_t bar_q = bars;
-  auto bar_kv_full = [&](int s) { return bars + 8u * (1 + s); };
-  auto bar_kv_empty = [&](int s) { return bars + 8u * (3 + s); };
-  auto bar_s_full = [&](int b) { return bars + 8u * (5 + b); };
-  auto bar_s_empty = [&](int b) { return bars + 8u * (7 + b); };
-  const uint32_t bar_p_full = bars + 8u * 9;
-  const uint32_t bar_pv_done = bars + 8u * 10;
-  const uint32_t holder = bars + 8u * 11;
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = gridDim.x - 1 - blockIdx.x;  // late (long-context) tiles first
-  const int head = blockIdx.y;
-  const int hk = head / (p.nh / p.nkv);
-  const int q0 = qt * ATT_BQ;
-  const int q_last = min(q0 + ATT_BQ - 1, p.T - 1);
-  const int ds_first = p.doc_start[q0];
-  const int ds_last = p.doc_start[q_last];
-  const int kb_lo = ds_first / ATT_BK;
-  const int kb_hi = q_last / ATT_BK;
-  const int nblk = kb_hi - kb_lo + 1;
-
-  if (warp == 1 && lane == 0) {
-    mbar_init(bar_q, 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(bar_kv_full(s), 1);
-      mbar_init(bar_kv_empty(s), 1);
-      mbar_init(bar_s_full(s), 1);
-      mbar_init(bar_s_empty(s), 128);
-    }
-    mbar_init(bar_p_full, 128);
-    mbar_init(bar_pv_done, 1);
-    fence_barrier_init();
-  }
-  if (warp == 0) {
-    tmem_alloc(holder, Cfg::kTmemCols);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  uint32_t tmem;
-  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem) : "r"(holder));
-  const uint32_t tS0 = tmem, tO = tmem + 256;
-
-  if (warp == 0) {
-    if (lane == 0) {
-      mbar_expect_tx(bar_q, Cfg::kTileBytes);
-#pragma unroll
-      for (int h = 0; h < NH; ++h) tma_load_2d(sQ + h * Cfg::kHalfBytes, &tmQ, bar_q, head * D + 64 * h, q0);
-      for (int j = 0; j < nblk; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(bar_kv_empty(s), ph ^ 1u, p.status, kTimeoutProducer)) break;
-        mbar_expect_tx(bar_kv_full(s), 2 * Cfg::kTileBytes);
-        const int k0 = (kb_lo + j) * ATT_BK;
-#pragma unroll
-        for (int h = 0; h < NH; ++h) {
-          tma_load_2d(sK(s) + h * Cfg::kHalfBytes, &tmK, bar_kv_full(s), hk * D + 64 * h, k0);
-          tma_load_2d(sV(s) + h * Cfg::kHalfBytes, &tmV, bar_kv_full(s), hk * D + 64 * h, k0);
-        }
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc_s = make_idesc_f16(128, 128, p.fmt, 0, 0);
-      const uint32_t idesc_o = make_idesc_f16(128, D, p.fmt, 0, 1);
-      auto issue_s = [&](int j) {
-        const int s = j & 1;
-        const uint32_t d_tmem = tS0 + 128u * (j & 1);
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (ks / 4) * Cfg::kHalfBytes + (ks % 4) * 32;
-          tc_mma_f16(d_tmem, make_smem_desc(sQ + off, 16, 1024), make_smem_desc(sK(s) + off, 16, 1024), idesc_s,
-                     ks != 0);
-        }
-        tc_commit(bar_s_full(j & 1));
-      };
-      bool ok = mbar_wait(bar_q, 0, p.status, kTimeoutMma);
-      if (ok) ok = mbar_wait(bar_kv_full(0), 0, p.status, kTimeoutMma);
-      if (ok) {
-        tc_fence_after();
-        issue_s(0);
-      }
-      for (int j = 0; j < nblk && ok; ++j) {
-        if (j + 1 < nblk) {
-          const int jn = j + 1;
-          if (!mbar_wait(bar_kv_full(jn & 1), (jn >> 1) & 1, p.status, kTimeoutMma)) { ok = false; break; }
-          // S buffer (jn & 1) was last used by block jn-2: wait until the softmax warps finished reading it
-          if (jn >= 2 && !mbar_wait(bar_s_empty(jn & 1), ((jn - 2) >> 1) & 1, p.status, kTimeoutMma)) { ok = false; break; }
-          tc_fence_after();
-          issue_s(jn);
-        }
-        if (!mbar_wait(bar_p_full, j & 1, p.status, kTimeoutMma)) { ok = false; break; }
-        tc_fence_after();
-        const int s = j & 1;
-#pragma unroll
-        for (int ks = 0; ks < ATT_BK / 16; ++ks) {
-          const uint64_t adesc = make_smem_desc(sP + (ks / 4) * 16384 + (ks % 4) * 32, 16, 1024);
-          const uint64_t bdesc = make_smem_desc(sV(s) + ks * 2048, Cfg::kHalfBytes, 1024);
-          tc_mma_f16(tO, adesc, bdesc, idesc_o, (j | ks) != 0);
-        }
-        tc_commit(bar_kv_empty(s));
-        tc_commit(bar_pv_done);
-      }
-    }
-  } else {
-    // ------------------------------------------------------------------ softmax / output
-    const int q = warp & 3;
-    const int row = q * 32 + lane;
-    const int t = q0 + row;
-    const bool row_ok = t < p.T;
-    const int ds = row_ok ? p.doc_start[t] : 0;
-    const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
-    const float sl2 = p.scale * 1.4426950408889634f;  // scale * log2(e)
-    float m_run = -1e30f, l_run = 0.f;
-    bool ok = true;
-    for (int j = 0; j < nblk; ++j) {
-      const int k0 = (kb_lo + j) * ATT_BK;
-      if (!mbar_wait(bar_s_full(j & 1), (j >> 1) & 1, p.status, kTimeoutEpilogue)) { ok = false; break; }
-      tc_fence_after();
-      const uint32_t tS = tS0 + 128u * (j & 1) + lane_addr;
-      const bool need_mask = !(k0 >= ds_last && k0 + ATT_BK - 1 <= q0) || !row_ok;
-      // pass 1: row maximum
-      float m_blk = -1e30f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tS + c * 32, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float v = __uint_as_float(r[i]);
-          if (need_mask) {
-            const int kk = k0 + c * 32 + i;
-            if (!(row_ok && kk >= ds && kk <= t)) v = -1e30f;
-          }
-          m_blk = fmaxf(m_blk, v);
-        }
-      }
-      const float m_new = fmaxf(m_run, m_blk);
-      const float alpha = exp2f((m_run - m_new) * sl2);
-      const float mb = m_new * sl2;
-      // the previous P.V must be complete before P is overwritten and O is rescaled
-      if (j > 0 && !mbar_wait(bar_pv_done, (j - 1) & 1, p.status, kTimeoutEpilogue)) { ok = false; break; }
-      tc_fence_after();
-      // pass 2: probabilities -> shared memory (K-major, 128-byte swizzle), running sum
-      float l_blk = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tS + c * 32, r);
-        tmem_ld_wait();
-        uint32_t packed[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float v0 = __uint_as_float(r[i]), v1 = __uint_as_float(r[i + 1]);
-          float p0 = exp2f(v0 * sl2 - mb), p1 = exp2f(v1 * sl2 - mb);
-          if (need_mask) {
-            const int kk = k0 + c * 32 + i;
-            if (!(row_ok && kk >= ds && kk <= t)) p0 = 0.f;
-            if (!(row_ok && kk + 1 >= ds && kk + 1 <= t)) p1 = 0.f;
-          }
-          l_blk += p0 + p1;
-          packed[i / 2] = pack2(p0, p1, p.fmt);
-        }
-        // columns c*32 .. c*32+31 -> 64-column block (c/2), 16-byte chunks (c%2)*4 .. +3
-        const uint32_t blk = sP + (c / 2) * 16384;
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const uint32_t addr = blk + swz_off(row, (c % 2) * 4 + g);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[4 * g]),
-                       "r"(packed[4 * g + 1]), "r"(packed[4 * g + 2]), "r"(packed[4 * g + 3])
-                       : "memory");
-        }
-      }
-      // S buffer may now be overwritten by block j+2
-      tc_fence_before();
-      mbar_arrive(bar_s_empty(j & 1));
-      l_run = l_run * alpha + l_blk;
-      m_run = m_new;
-      // rescale O (skipped by a whole warp when no row of it moved its maximum)
-      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-#pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(tO + lane_addr + c * 32, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-          tmem_st_32x32(tO + lane_addr + c * 32, r);
-        }
-        tmem_st_wait();
-      }
-      fence_proxy_async_smem();
-      tc_fence_before();
-      mbar_arrive(bar_p_full);
-    }
-    if (ok && mbar_wait(bar_pv_done, (nblk - 1) & 1, p.status, kTimeoutEpilogue)) {
-      tc_fence_after();
-      const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
-#pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tO + lane_addr + c * 32, r);
-        tmem_ld_wait();
-        if (row_ok) {
-          uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + (long long)t * p.ldo + head * D + c * 32;
-#pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 u;
-            u.x = pack2(__uint_as_float(r[i]) * inv_l, __uint_as_float(r[i + 1]) * inv_l, p.fmt);
-            u.y = pack2(__uint_as_float(r[i + 2]) * inv_l, __uint_as_float(r[i + 3]) * inv_l, p.fmt);
-            u.z = pack2(__uint_as_float(r[i + 4]) * inv_l, __uint_as_float(r[i + 5]) * inv_l, p.fmt);
-            u.w = pack2(__uint_as_float(r[i + 6]) * inv_l, __uint_as_float(r[i + 7]) * inv_l, p.fmt);
-            *reinterpret_cast<uint4*>(orow + i) = u;
-          }
-        }
-      }
-      if (row_ok) p.lse[(long long)head * p.T + t] = m_run * p.scale + __logf(l_run);
-    }
-  }
-
-  __syncwarp();
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) {
-    tc_fence_after();
-    tmem_dealloc(tmem, Cfg::kTmemCols);
-  }
 }
 
 // ----------------------------------------------------------------------------------------
@@ -608,433 +344,6 @@ __global__ void attn_delta_kernel(const T* __restrict__ o, const T* __restrict__
   if (lane == 0) delta[(long long)h * T_tokens + t] = acc;
 }
 
-// ----------------------------------------------------------------------------------------
-// backward
-// ----------------------------------------------------------------------------------------
-struct AttnBwdParams {
-  int T, nh, nkv, d;
-  float scale;
-  const int* doc_start;
-  const int* doc_end;
-  const float* lse;    // [nh, T]
-  const float* delta;  // [nh, T]
-  void* dq;            // [T, nh*d]
-  long long lddq;
-  void* dk;            // [T, nkv*d]
-  long long lddk;
-  void* dv;
-  long long lddv;
-  int fmt;
-  int* status;
-};
-
-template <int D>
-struct AttnBwdCfg {
-  static constexpr int kTileBytes = 128 * D * 2;
-  static constexpr int kHalfBytes = 128 * 64 * 2;
-  static constexpr int kPBytes = 128 * 128 * 2;
-  // dQ kernel: Q, dO, 2 x (K, V), dS
-  static constexpr int kSmemDq = 6 * kTileBytes + kPBytes + 1024 + 256;
-  // dK/dV kernel: K, V, Q, dO, P, dS
-  static constexpr int kSmemDkv = 4 * kTileBytes + 2 * kPBytes + 1024 + 256;
-};
-
-// store one fp32 accumulator row chunk (32 columns) scaled, as 16-bit
-__device__ __forceinline__ void store_row_chunk(uint16_t* dst, const uint32_t (&r)[32], float mul, int fmt) {
-#pragma unroll
-  for (int i = 0; i < 32; i += 8) {
-    uint4 u;
-    u.x = pack2(__uint_as_float(r[i]) * mul, __uint_as_float(r[i + 1]) * mul, fmt);
-    u.y = pack2(__uint_as_float(r[i + 2]) * mul, __uint_as_float(r[i + 3]) * mul, fmt);
-    u.z = pack2(__uint_as_float(r[i + 4]) * mul, __uint_as_float(r[i + 5]) * mul, fmt);
-    u.w = pack2(__uint_as_float(r[i + 6]) * mul, __uint_as_float(r[i + 7]) * mul, fmt);
-    *reinterpret_cast<uint4*>(dst + i) = u;
-  }
-}
-
-// write 32 consecutive columns [c*32, c*32+32) of row `row` of a [128 x 128] 16-bit tile
-__device__ __forceinline__ void st_tile_chunk(uint32_t tile, int row, int c, const uint32_t (&packed)[16]) {
-  const uint32_t blk = tile + (c / 2) * 16384;
-#pragma unroll
-  for (int g = 0; g < 4; ++g) {
-    const uint32_t addr = blk + swz_off(row, (c % 2) * 4 + g);
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[4 * g]), "r"(packed[4 * g + 1]),
-                 "r"(packed[4 * g + 2]), "r"(packed[4 * g + 3])
-                 : "memory");
-  }
-}
-
-// dQ[q tile, head] = scale * sum_j dS_j K_j,  dS = P o (dP - delta),  P = exp(scale*S - lse)
-template <int D>
-__global__ void __launch_bounds__(192, 1)
-attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                   const AttnBwdParams p) {
-  using Cfg = AttnBwdCfg<D>;
-  constexpr int NH = D / 64;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t sQ = base;
-  const uint32_t sdO = base + Cfg::kTileBytes;
-  auto sK = [&](int s) { return base + Cfg::kTileBytes * (2 + 2 * s); };
-  auto sV = [&](int s) { return base + Cfg::kTileBytes * (3 + 2 * s); };
-  const uint32_t sdS = base + Cfg::kTileBytes * 6;
-  const uint32_t bars = sdS + Cfg::kPBytes;
-  const uint32_t bar_q = bars;
-  auto bar_kv_full = [&](int s) { return bars + 8u * (1 + s); };
-  auto bar_kv_empty = [&](int s) { return bars + 8u * (3 + s); };
-  const uint32_t bar_sdp_full = bars + 8u * 5;
-  const uint32_t bar_ds_full = bars + 8u * 6;
-  const uint32_t bar_dq_done = bars + 8u * 7;
-  const uint32_t holder = bars + 8u * 8;
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = gridDim.x - 1 - blockIdx.x;
-  const int head = blockIdx.y;
-  const int hk = head / (p.nh / p.nkv);
-  const int q0 = qt * ATT_BQ;
-  const int q_last = min(q0 + ATT_BQ - 1, p.T - 1);
-  const int ds_last = p.doc_start[q_last];
-  const int kb_lo = p.doc_start[q0] / ATT_BK;
-  const int nblk = q_last / ATT_BK - kb_lo + 1;
-
-  if (warp == 1 && lane == 0) {
-    mbar_init(bar_q, 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(bar_kv_full(s), 1);
-      mbar_init(bar_kv_empty(s), 1);
-    }
-    mbar_init(bar_sdp_full, 1);
-    mbar_init(bar_ds_full, 128);
-    mbar_init(bar_dq_done, 1);
-    fence_barrier_init();
-  }
-  if (warp == 0) {
-    tmem_alloc(holder, 512);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  uint32_t tmem;
-  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem) : "r"(holder));
-  const uint32_t tS = tmem, tdP = tmem + 128, tdQ = tmem + 256;
-
-  if (warp == 0) {
-    if (lane == 0) {
-      mbar_expect_tx(bar_q, 2 * Cfg::kTileBytes);
-#pragma unroll
-      for (int h = 0; h < NH; ++h) {
-        tma_load_2d(sQ + h * Cfg::kHalfBytes, &tmQ, bar_q, head * D + 64 * h, q0);
-        tma_load_2d(sdO + h * Cfg::kHalfBytes, &tmdO, bar_q, head * D + 64 * h, q0);
-      }
-      for (int j = 0; j < nblk; ++j) {
-        const int s = j & 1;
-        if (!mbar_wait(bar_kv_empty(s), ((j >> 1) & 1) ^ 1u, p.status, kTimeoutProducer)) break;
-        mbar_expect_tx(bar_kv_full(s), 2 * Cfg::kTileBytes);
-        const int k0 = (kb_lo + j) * ATT_BK;
-#pragma unroll
-        for (int h = 0; h < NH; ++h) {
-          tma_load_2d(sK(s) + h * Cfg::kHalfBytes, &tmK, bar_kv_full(s), hk * D + 64 * h, k0);
-          tma_load_2d(sV(s) + h * Cfg::kHalfBytes, &tmV, bar_kv_full(s), hk * D + 64 * h, k0);
-        }
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc_s = make_idesc_f16(128, 128, p.fmt, 0, 0);
-      const uint32_t idesc_q = make_idesc_f16(128, D, p.fmt, 0, 1);
-      auto issue_sdp = [&](int j) {
-        const int s = j & 1;
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (ks / 4) * Cfg::kHalfBytes + (ks % 4) * 32;
-          tc_mma_f16(tS, make_smem_desc(sQ + off, 16, 1024), make_smem_desc(sK(s) + off, 16, 1024), idesc_s, ks != 0);
-        }
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (ks / 4) * Cfg::kHalfBytes + (ks % 4) * 32;
-          tc_mma_f16(tdP, make_smem_desc(sdO + off, 16, 1024), make_smem_desc(sV(s) + off, 16, 1024), idesc_s, ks != 0);
-        }
-        tc_commit(bar_sdp_full);
-      };
-      bool ok = mbar_wait(bar_q, 0, p.status, kTimeoutMma);
-      if (ok) ok = mbar_wait(bar_kv_full(0), 0, p.status, kTimeoutMma);
-      if (ok) {
-        tc_fence_after();
-        issue_sdp(0);
-      }
-      for (int j = 0; j < nblk && ok; ++j) {
-        if (!mbar_wait(bar_ds_full, j & 1, p.status, kTimeoutMma)) { ok = false; break; }
-        tc_fence_after();
-        const int s = j & 1;
-#pragma unroll
-        for (int ks = 0; ks < ATT_BK / 16; ++ks) {
-          const uint64_t adesc = make_smem_desc(sdS + (ks / 4) * 16384 + (ks % 4) * 32, 16, 1024);
-          const uint64_t bdesc = make_smem_desc(sK(s) + ks * 2048, Cfg::kHalfBytes, 1024);
-          tc_mma_f16(tdQ, adesc, bdesc, idesc_q, (j | ks) != 0);
-        }
-        tc_commit(bar_kv_empty(s));
-        tc_commit(bar_dq_done);
-        if (j + 1 < nblk) {
-          const int jn = j + 1;
-          if (!mbar_wait(bar_kv_full(jn & 1), (jn >> 1) & 1, p.status, kTimeoutMma)) { ok = false; break; }
-          tc_fence_after();
-          issue_sdp(jn);
-        }
-      }
-    }
-  } else {
-    const int q = warp & 3;
-    const int row = q * 32 + lane;
-    const int t = q0 + row;
-    const bool row_ok = t < p.T;
-    const int ds = row_ok ? p.doc_start[t] : 0;
-    const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
-    const float LOG2E = 1.4426950408889634f;
-    const float sl2 = p.scale * LOG2E;
-    const float lse2 = row_ok ? p.lse[(long long)head * p.T + t] * LOG2E : 0.f;
-    const float dlt = row_ok ? p.delta[(long long)head * p.T + t] : 0.f;
-    bool ok = true;
-    for (int j = 0; j < nblk; ++j) {
-      const int k0 = (kb_lo + j) * ATT_BK;
-      if (!mbar_wait(bar_sdp_full, j & 1, p.status, kTimeoutEpilogue)) { ok = false; break; }
-      tc_fence_after();
-      const bool need_mask = !(k0 >= ds_last && k0 + ATT_BK - 1 <= q0) || !row_ok;
-      if (j > 0 && !mbar_wait(bar_dq_done, (j - 1) & 1, p.status, kTimeoutEpilogue)) { ok = false; break; }
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t rs[32], rp[32];
-        tmem_ld_32x32(tS + lane_addr + c * 32, rs);
-        tmem_ld_32x32(tdP + lane_addr + c * 32, rp);
-        tmem_ld_wait();
-        uint32_t packed[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = exp2f(__uint_as_float(rs[i]) * sl2 - lse2);
-          float p1 = exp2f(__uint_as_float(rs[i + 1]) * sl2 - lse2);
-          if (need_mask) {
-            const int kk = k0 + c * 32 + i;
-            if (!(row_ok && kk >= ds && kk <= t)) p0 = 0.f;
-            if (!(row_ok && kk + 1 >= ds && kk + 1 <= t)) p1 = 0.f;
-          }
-          const float d0 = p0 * (__uint_as_float(rp[i]) - dlt);
-          const float d1 = p1 * (__uint_as_float(rp[i + 1]) - dlt);
-          packed[i / 2] = pack2(d0, d1, p.fmt);
-        }
-        st_tile_chunk(sdS, row, c, packed);
-      }
-      fence_proxy_async_smem();
-      tc_fence_before();
-      mbar_arrive(bar_ds_full);
-    }
-    if (ok && mbar_wait(bar_dq_done, (nblk - 1) & 1, p.status, kTimeoutEpilogue)) {
-      tc_fence_after();
-#pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tdQ + lane_addr + c * 32, r);
-        tmem_ld_wait();
-        if (row_ok)
-          store_row_chunk(reinterpret_cast<uint16_t*>(p.dq) + (long long)t * p.lddq + head * D + c * 32, r, p.scale,
-                          p.fmt);
-      }
-    }
-  }
-  __syncwarp();
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) {
-    tc_fence_after();
-    tmem_dealloc(tmem, 512);
-  }
-}
-
-// dV[kv tile, kv head] = sum_{g,i} P^T dO ,  dK = scale * sum_{g,i} dS^T Q   (g: query heads of the group)
-template <int D>
-__global__ void __launch_bounds__(192, 1)
-attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
-                    const AttnBwdParams p) {
-  using Cfg = AttnBwdCfg<D>;
-  constexpr int NH = D / 64;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t sK = base;
-  const uint32_t sV = base + Cfg::kTileBytes;
-  const uint32_t sQ = base + 2 * Cfg::kTileBytes;
-  const uint32_t sdO = base + 3 * Cfg::kTileBytes;
-  const uint32_t sP = base + 4 * Cfg::kTileBytes;
-  const uint32_t sdS = sP + Cfg::kPBytes;
-  const uint32_t bars = sdS + Cfg::kPBytes;
-  const uint32_t bar_kv = bars;
-  const uint32_t bar_qdo_full = bars + 8u;
-  const uint32_t bar_sdp_full = bars + 16u;
-  const uint32_t bar_pds_full = bars + 24u;
-  const uint32_t bar_iter_done = bars + 32u;
-  const uint32_t holder = bars + 40u;
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kt = blockIdx.x;
-  const int hk = blockIdx.y;
-  const int G = p.nh / p.nkv;
-  const int k0 = kt * ATT_BK;
-  const int k_last = min(k0 + ATT_BK - 1, p.T - 1);
-  const int de_last = p.doc_end[k_last];
-  const int qb_lo = kt;  // queries before the tile cannot see its keys
-  const int qb_hi = (de_last - 1) / ATT_BQ;
-  const int nq = qb_hi - qb_lo + 1;
-  const int niter = nq * G;
-
-  if (warp == 1 && lane == 0) {
-    mbar_init(bar_kv, 1);
-    mbar_init(bar_qdo_full, 1);
-    mbar_init(bar_sdp_full, 1);
-    mbar_init(bar_pds_full, 128);
-    mbar_init(bar_iter_done, 1);
-    fence_barrier_init();
-  }
-  if (warp == 0) {
-    tmem_alloc(holder, 512);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  uint32_t tmem;
-  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem) : "r"(holder));
-  const uint32_t tS = tmem, tdP = tmem + 128, tdV = tmem + 256, tdK = tmem + 384;
-
-  if (warp == 0) {
-    if (lane == 0) {
-      mbar_expect_tx(bar_kv, 2 * Cfg::kTileBytes);
-#pragma unroll
-      for (int h = 0; h < NH; ++h) {
-        tma_load_2d(sK + h * Cfg::kHalfBytes, &tmK, bar_kv, hk * D + 64 * h, k0);
-        tma_load_2d(sV + h * Cfg::kHalfBytes, &tmV, bar_kv, hk * D + 64 * h, k0);
-      }
-      for (int it = 0; it < niter; ++it) {
-        if (it > 0 && !mbar_wait(bar_iter_done, (it - 1) & 1, p.status, kTimeoutProducer)) break;
-        const int head = hk * G + it / nq;
-        const int q0 = (qb_lo + it % nq) * ATT_BQ;
-        mbar_expect_tx(bar_qdo_full, 2 * Cfg::kTileBytes);
-#pragma unroll
-        for (int h = 0; h < NH; ++h) {
-          tma_load_2d(sQ + h * Cfg::kHalfBytes, &tmQ, bar_qdo_full, head * D + 64 * h, q0);
-          tma_load_2d(sdO + h * Cfg::kHalfBytes, &tmdO, bar_qdo_full, head * D + 64 * h, q0);
-        }
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc_s = make_idesc_f16(128, 128, p.fmt, 0, 0);
-      const uint32_t idesc_g = make_idesc_f16(128, D, p.fmt, 1, 1);
-      bool ok = mbar_wait(bar_kv, 0, p.status, kTimeoutMma);
-      for (int it = 0; it < niter && ok; ++it) {
-        if (!mbar_wait(bar_qdo_full, it & 1, p.status, kTimeoutMma)) { ok = false; break; }
-        tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (ks / 4) * Cfg::kHalfBytes + (ks % 4) * 32;
-          tc_mma_f16(tS, make_smem_desc(sQ + off, 16, 1024), make_smem_desc(sK + off, 16, 1024), idesc_s, ks != 0);
-        }
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (ks / 4) * Cfg::kHalfBytes + (ks % 4) * 32;
-          tc_mma_f16(tdP, make_smem_desc(sdO + off, 16, 1024), make_smem_desc(sV + off, 16, 1024), idesc_s, ks != 0);
-        }
-        tc_commit(bar_sdp_full);
-        if (!mbar_wait(bar_pds_full, it & 1, p.status, kTimeoutMma)) { ok = false; break; }
-        tc_fence_after();
-        // contraction over the 128 query rows of this block, 16 rows per instruction
-#pragma unroll
-        for (int ks = 0; ks < ATT_BQ / 16; ++ks) {
-          const uint64_t a_p = make_smem_desc(sP + ks * 2048, 16384, 1024);
-          const uint64_t b_do = make_smem_desc(sdO + ks * 2048, Cfg::kHalfBytes, 1024);
-          tc_mma_f16(tdV, a_p, b_do, idesc_g, (it | ks) != 0);
-        }
-#pragma unroll
-        for (int ks = 0; ks < ATT_BQ / 16; ++ks) {
-          const uint64_t a_ds = make_smem_desc(sdS + ks * 2048, 16384, 1024);
-          const uint64_t b_q = make_smem_desc(sQ + ks * 2048, Cfg::kHalfBytes, 1024);
-          tc_mma_f16(tdK, a_ds, b_q, idesc_g, (it | ks) != 0);
-        }
-        tc_commit(bar_iter_done);
-      }
-    }
-  } else {
-    const int q = warp & 3;
-    const int row = q * 32 + lane;
-    const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
-    const float LOG2E = 1.4426950408889634f;
-    const float sl2 = p.scale * LOG2E;
-    bool ok = true;
-    for (int it = 0; it < niter; ++it) {
-      const int head = hk * G + it / nq;
-      const int q0 = (qb_lo + it % nq) * ATT_BQ;
-      const int t = q0 + row;
-      const bool row_ok = t < p.T;
-      const int ds = row_ok ? p.doc_start[t] : 0;
-      const int ds_blk_last = p.doc_start[min(q0 + ATT_BQ - 1, p.T - 1)];
-      const float lse2 = row_ok ? p.lse[(long long)head * p.T + t] * LOG2E : 0.f;
-      const float dlt = row_ok ? p.delta[(long long)head * p.T + t] : 0.f;
-      const bool need_mask = !(q0 >= k0 + ATT_BK - 1 && ds_blk_last <= k0) || !row_ok;
-      if (!mbar_wait(bar_sdp_full, it & 1, p.status, kTimeoutEpilogue)) { ok = false; break; }
-      tc_fence_after();
-      if (it > 0 && !mbar_wait(bar_iter_done, (it - 1) & 1, p.status, kTimeoutEpilogue)) { ok = false; break; }
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t rs[32], rp[32];
-        tmem_ld_32x32(tS + lane_addr + c * 32, rs);
-        tmem_ld_32x32(tdP + lane_addr + c * 32, rp);
-        tmem_ld_wait();
-        uint32_t pk[16], dk[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = exp2f(__uint_as_float(rs[i]) * sl2 - lse2);
-          float p1 = exp2f(__uint_as_float(rs[i + 1]) * sl2 - lse2);
-          if (need_mask) {
-            const int kk = k0 + c * 32 + i;
-            if (!(row_ok && kk >= ds && kk <= t)) p0 = 0.f;
-            if (!(row_ok && kk + 1 >= ds && kk + 1 <= t)) p1 = 0.f;
-          }
-          pk[i / 2] = pack2(p0, p1, p.fmt);
-          dk[i / 2] = pack2(p0 * (__uint_as_float(rp[i]) - dlt), p1 * (__uint_as_float(rp[i + 1]) - dlt), p.fmt);
-        }
-        st_tile_chunk(sP, row, c, pk);
-        st_tile_chunk(sdS, row, c, dk);
-      }
-      fence_proxy_async_smem();
-      tc_fence_before();
-      mbar_arrive(bar_pds_full);
-    }
-    if (ok && mbar_wait(bar_iter_done, (niter - 1) & 1, p.status, kTimeoutEpilogue)) {
-      tc_fence_after();
-      const int kr = k0 + row;  // accumulator lane = key row
-#pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tdV + lane_addr + c * 32, r);
-        tmem_ld_wait();
-        if (kr < p.T)
-          store_row_chunk(reinterpret_cast<uint16_t*>(p.dv) + (long long)kr * p.lddv + hk * D + c * 32, r, 1.f, p.fmt);
-        tmem_ld_32x32(tdK + lane_addr + c * 32, r);
-        tmem_ld_wait();
-        if (kr < p.T)
-          store_row_chunk(reinterpret_cast<uint16_t*>(p.dk) + (long long)kr * p.lddk + hk * D + c * 32, r, p.scale,
-                          p.fmt);
-      }
-    }
-  }
-  __syncwarp();
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) {
-    tc_fence_after();
-    tmem_dealloc(tmem, 512);
-  }
-}
-
 }  // namespace fmsb
 
 using namespace fmsb;
@@ -1094,77 +403,5 @@ extern "C" int fmsb_attn_delta(const void* o, const void* dout, long long ldo, l
   else
     attn_delta_kernel<__half><<<grid, wpb * 32, 0, stream>>>((const __half*)o, (const __half*)dout, ldo, lddo, delta, T,
                                                              nh, d);
-  return (int)cudaGetLastError();
-}
-
-static int make_bwd_maps(CUtensorMap* tq, CUtensorMap* tk, CUtensorMap* tv, CUtensorMap* tdo, const void* q,
-                         long long ldq, const void* k, long long ldk, const void* v, long long ldv, const void* dout,
-                         long long lddo, int T, int nh, int nkv, int d) {
-  using namespace fmsb_host;
-  int rc;
-  if ((rc = make_tmap_2d_16b(tq, q, T, (uint64_t)nh * d, ldq, 128, 64))) return rc;
-  if ((rc = make_tmap_2d_16b(tk, k, T, (uint64_t)nkv * d, ldk, 128, 64))) return rc;
-  if ((rc = make_tmap_2d_16b(tv, v, T, (uint64_t)nkv * d, ldv, 128, 64))) return rc;
-  if ((rc = make_tmap_2d_16b(tdo, dout, T, (uint64_t)nh * d, lddo, 128, 64))) return rc;
-  return 0;
-}
-
-template <typename K>
-static int set_smem(K kern, int bytes) {
-  return (int)cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-}
-
-extern "C" int fmsb_attn_bwd_dq(const void* q, long long ldq, const void* k, long long ldk, const void* v,
-                                long long ldv, const void* dout, long long lddo, void* dq, long long lddq,
-                                const float* lse, const float* delta, const int* doc_start, const int* doc_end, int T,
-                                int nh, int nkv, int d, float scale, int fmt, int* status, cudaStream_t stream) {
-  if (T <= 0) return 0;
-  if (!(d == 64 || d == 128) || nh % nkv != 0) return -2;
-  if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (lddo % 8) || (lddq % 8)) return -2;
-  CUtensorMap tq, tk, tv, tdo;
-  int rc = make_bwd_maps(&tq, &tk, &tv, &tdo, q, ldq, k, ldk, v, ldv, dout, lddo, T, nh, nkv, d);
-  if (rc) return rc;
-  AttnBwdParams p{};
-  p.T = T; p.nh = nh; p.nkv = nkv; p.d = d; p.scale = scale;
-  p.doc_start = doc_start; p.doc_end = doc_end; p.lse = lse; p.delta = delta;
-  p.dq = dq; p.lddq = lddq; p.fmt = fmt; p.status = status;
-  dim3 grid((T + ATT_BQ - 1) / ATT_BQ, nh);
-  if (d == 128) {
-    static bool cfg = false;
-    if (!cfg) { if ((rc = set_smem(attn_bwd_dq_kernel<128>, AttnBwdCfg<128>::kSmemDq))) return rc; cfg = true; }
-    attn_bwd_dq_kernel<128><<<grid, 192, AttnBwdCfg<128>::kSmemDq, stream>>>(tq, tk, tv, tdo, p);
-  } else {
-    static bool cfg = false;
-    if (!cfg) { if ((rc = set_smem(attn_bwd_dq_kernel<64>, AttnBwdCfg<64>::kSmemDq))) return rc; cfg = true; }
-    attn_bwd_dq_kernel<64><<<grid, 192, AttnBwdCfg<64>::kSmemDq, stream>>>(tq, tk, tv, tdo, p);
-  }
-  return (int)cudaGetLastError();
-}
-
-extern "C" int fmsb_attn_bwd_dkv(const void* q, long long ldq, const void* k, long long ldk, const void* v,
-                                 long long ldv, const void* dout, long long lddo, void* dk, long long lddk, void* dv,
-                                 long long lddv, const float* lse, const float* delta, const int* doc_start,
-                                 const int* doc_end, int T, int nh, int nkv, int d, float scale, int fmt, int* status,
-                                 cudaStream_t stream) {
-  if (T <= 0) return 0;
-  if (!(d == 64 || d == 128) || nh % nkv != 0) return -2;
-  if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (lddo % 8) || (lddk % 8) || (lddv % 8)) return -2;
-  CUtensorMap tq, tk, tv, tdo;
-  int rc = make_bwd_maps(&tq, &tk, &tv, &tdo, q, ldq, k, ldk, v, ldv, dout, lddo, T, nh, nkv, d);
-  if (rc) return rc;
-  AttnBwdParams p{};
-  p.T = T; p.nh = nh; p.nkv = nkv; p.d = d; p.scale = scale;
-  p.doc_start = doc_start; p.doc_end = doc_end; p.lse = lse; p.delta = delta;
-  p.dk = dk; p.lddk = lddk; p.dv = dv; p.lddv = lddv; p.fmt = fmt; p.status = status;
-  dim3 grid((T + ATT_BK - 1) / ATT_BK, nkv);
-  if (d == 128) {
-    static bool cfg = false;
-    if (!cfg) { if ((rc = set_smem(attn_bwd_dkv_kernel<128>, AttnBwdCfg<128>::kSmemDkv))) return rc; cfg = true; }
-    attn_bwd_dkv_kernel<128><<<grid, 192, AttnBwdCfg<128>::kSmemDkv, stream>>>(tq, tk, tv, tdo, p);
-  } else {
-    static bool cfg = false;
-    if (!cfg) { if ((rc = set_smem(attn_bwd_dkv_kernel<64>, AttnBwdCfg<64>::kSmemDkv))) return rc; cfg = true; }
-    attn_bwd_dkv_kernel<64><<<grid, 192, AttnBwdCfg<64>::kSmemDkv, stream>>>(tq, tk, tv, tdo, p);
-  }
   return (int)cudaGetLastError();
 }

@@ -51,8 +51,8 @@ def attention_ref(q, k, v, doc_start, scale=None):
     return torch.matmul(p, vf).transpose(0, 1).contiguous()
 
 
-# Backward kernel generation: 3 = full-width issue order (csrc/attention_bwd3.cu, the default), 2 = half-tile
-# pipeline (csrc/attention_bwd.cu), 1 = first generation (csrc/attention.cu); 1 and 2 are kept as cross-checks.
+# Backward kernels: 3 = full-width issue order (csrc/attention_bwd3.cu, the default), 2 = half-tile pipeline
+# (csrc/attention_bwd.cu, kept as an independent cross-check of the same mathematics).
 BWD_GENERATION = int(os.environ.get("FMSB_ATTN_BWD", "3"))
 
 
@@ -84,8 +84,7 @@ def _bwd(q2, k2, v2, o, lse, dout, doc_start, doc_end, nh, nkv, d, scale, dq=Non
         dv = torch.empty(T, nkv * d, dtype=q2.dtype, device=dev)
     st = N.status_word(dev)
     dq_fn, dkv_fn = {3: (N.lib().fmsb_attn_bwd_dq3, N.lib().fmsb_attn_bwd_dkv3),
-                     2: (N.lib().fmsb_attn_bwd_dq2, N.lib().fmsb_attn_bwd_dkv2),
-                     1: (N.lib().fmsb_attn_bwd_dq, N.lib().fmsb_attn_bwd_dkv)}[BWD_GENERATION]
+                     2: (N.lib().fmsb_attn_bwd_dq2, N.lib().fmsb_attn_bwd_dkv2)}[BWD_GENERATION]
     rc = dq_fn(q2.data_ptr(), q2.stride(0), k2.data_ptr(), k2.stride(0), v2.data_ptr(),
                                   v2.stride(0), dout.data_ptr(), dout.stride(0), dq.data_ptr(), dq.stride(0),
                                   lse.data_ptr(), delta.data_ptr(), doc_start.data_ptr(), doc_end.data_ptr(), T, nh,
