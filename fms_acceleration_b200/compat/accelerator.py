@@ -9,12 +9,11 @@ the same fields configure this package's own sharded-parameter engine.
 from __future__ import annotations
 
 import os
-from dataclasses import dataclass, field
-from typing import Any, Callable, List, Optional
+from dataclasses import dataclass
+from typing import Callable, List, Optional
 
 import torch
 import torch.distributed as dist
-from torch.utils.data import DataLoader
 
 
 @dataclass

@@ -9,7 +9,6 @@ Block: ``zxbcdt = in_proj(u)``; split into gate ``z``, conv input ``xBC`` and ``
 from __future__ import annotations
 
 import math
-from typing import Optional
 
 import torch
 import torch.nn.functional as F

@@ -6,7 +6,6 @@ over ``e`` and ``g``; here in place is optional).
 """
 from __future__ import annotations
 
-import math
 
 import torch
 import torch.nn.functional as F

@@ -19,7 +19,6 @@ from typing import List, Optional
 
 import torch
 
-from .. import _native as N
 from . import activation as ACT
 from . import attention as ATT
 from . import rmsnorm as RN

@@ -11,7 +11,6 @@ states [nh, P, N] fp32.  T must be a multiple of the chunk size Q.
 from __future__ import annotations
 
 import ctypes
-import math
 
 import torch
 import torch.nn.functional as F

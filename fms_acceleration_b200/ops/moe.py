@@ -10,7 +10,7 @@ stores and results come back by peer loads, two device-side barriers per layer a
 from __future__ import annotations
 
 import ctypes
-from typing import List, Optional
+from typing import Optional
 
 import os
 

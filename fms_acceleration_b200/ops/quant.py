@@ -9,7 +9,7 @@ with the weight, so any 16-entry / 256-entry table is supported.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 import torch
 

@@ -18,7 +18,7 @@ from __future__ import annotations
 
 import os
 
-from typing import Dict, List, Optional, Tuple
+from typing import List, Optional, Tuple
 
 import torch
 import torch.distributed as dist

@@ -1,7 +1,6 @@
 """Collators and helpers for padding-free training (role of fms_acceleration_aadp/aadp_utils.py:25-89)."""
 from __future__ import annotations
 
-import warnings
 from types import MethodType
 from typing import Any, Dict, List
 

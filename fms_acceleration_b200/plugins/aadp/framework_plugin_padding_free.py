@@ -11,7 +11,6 @@ from __future__ import annotations
 
 from typing import Dict, Tuple
 
-import torch
 
 from ...framework.framework_plugin import AccelerationPlugin
 from .aadp_utils import DataCollatorWithFlattening, patch_torch_call_remove_padding
@@ -38,7 +37,7 @@ class PaddingFreeAccelerationPlugin(AccelerationPlugin):
 
     def augmentation(self, model, train_args, modifiable_args: Tuple):
         from ...framework.accelerator_patcher import AcceleratorPatcher, AcceleratorPatcherComponent
-        from ...framework.model_patcher import ModelPatcher, ModelPatcherRule, ModelPatcherTrigger
+        from ...framework.model_patcher import ModelPatcher, ModelPatcherRule
 
         def _collator_check(collate_fn) -> bool:
             name = _unwrap_collator(collate_fn).__class__.__name__

@@ -13,9 +13,8 @@ from __future__ import annotations
 
 import importlib
 from functools import partial
-from typing import List, Optional
+from typing import List
 
-import torch
 
 from ....framework.model_patcher import (ModelPatcherRule, ModelPatcherTrigger, combine_functions, combine_triggers)
 from ....ops.cross_entropy import FastCrossEntropyLoss, causal_lm_loss, fused_linear_cross_entropy

@@ -10,7 +10,6 @@ from __future__ import annotations
 
 from typing import Dict, Optional
 
-import torch
 import torch.distributed as dist
 
 KEY_DP, KEY_CP = "dp_shard", "cp"

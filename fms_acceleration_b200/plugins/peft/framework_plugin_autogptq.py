@@ -15,7 +15,6 @@ from typing import Dict, Tuple
 import torch
 
 from ...framework.framework_plugin import AccelerationPlugin
-from ...nn.lora import get_peft_model
 from .framework_plugin_bnb import _prepare_model_for_kbit_training
 
 

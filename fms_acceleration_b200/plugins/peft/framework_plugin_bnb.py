@@ -17,7 +17,7 @@ from ...framework.framework_plugin import AccelerationPlugin
 from ...models.builder import build_model, quantize_linears_
 from ...nn.linear4bit import Linear4bit
 from ...nn.lora import get_peft_model
-from .fsdp_utils import ensure_weights_retied, put_selected_meta_tensors_on_cpu
+from .fsdp_utils import ensure_weights_retied
 
 
 def _prepare_model_for_kbit_training(model, use_gradient_checkpointing=True, gradient_checkpointing_kwargs=None):

@@ -18,8 +18,7 @@ from torch import nn
 
 from fms_acceleration_b200.models.builder import build_model, resolve_config
 from fms_acceleration_b200.nn.gptq import QuantLinear
-from ..quantization.config import (FORMAT, META_FIELD_QUANTIZER, META_QUANTIZER_NAME, QUANT_CONFIG_FILENAME,
-                                   QuantizeConfig)
+from ..quantization.config import FORMAT, META_FIELD_QUANTIZER, META_QUANTIZER_NAME, QuantizeConfig
 from ..quantization.gptq import GPTQ
 from ..utils.backend import Backend
 from ..utils.data import collate_data

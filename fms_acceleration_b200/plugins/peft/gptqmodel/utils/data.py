@@ -1,7 +1,7 @@
 """Calibration-data helpers for GPTQ quantisation (role of fms_acceleration_peft/gptqmodel/utils/data.py)."""
 from __future__ import annotations
 
-from typing import Dict, List, Optional
+from typing import Dict, List
 
 import torch
 

@@ -6,11 +6,9 @@ get_callbacks_and_ready_for_train`` followed by ``Trainer.train_step`` per batch
 """
 from __future__ import annotations
 
-import math
 import os
-import time
-from dataclasses import dataclass, field
-from typing import Callable, Dict, List, Optional
+from dataclasses import dataclass
+from typing import Dict, List, Optional
 
 import torch
 from torch import nn
