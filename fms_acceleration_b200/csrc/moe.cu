@@ -295,7 +295,8 @@ __global__ void moe_assign_kernel(const int* __restrict__ topk_idx, long long n,
 template <typename T>
 __global__ void moe_dispatch_kernel(const T* __restrict__ x, long long ldx, const int* __restrict__ topk_idx,
                                     const int* __restrict__ dest_row, const float* __restrict__ scale, long long n_pairs,
-                                    int k, int H, int E_local, MoePeers recv, long long ld_recv) {
+                                    int k, int H, int E_local, MoePeers recv, long long ld_recv,
+                                    const float* __restrict__ meta_vals, MoePeers meta_recv) {
   const long long pair = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (pair >= n_pairs) return;
@@ -306,6 +307,8 @@ __global__ void moe_dispatch_kernel(const T* __restrict__ x, long long ldx, cons
   const T* src = x + t * ldx;
   T* dst = reinterpret_cast<T*>(recv.p[owner]) + row * ld_recv;
   const float sc = scale != nullptr ? scale[pair] : 1.f;
+  // optional per-row scalar travelling with the row (the routing weight in the backward pass)
+  if (meta_vals != nullptr && lane == 0) reinterpret_cast<float*>(meta_recv.p[owner])[row] = meta_vals[pair];
   for (int c = lane * 8; c < H; c += 256) {
     uint4 v = *reinterpret_cast<const uint4*>(src + c);
     if (scale != nullptr) {
@@ -412,6 +415,49 @@ __global__ void moe_gate_grad_kernel(MoePeers ybuf, long long ldy, const int* __
   if (lane == 0) dgate[pair] = acc;
 }
 
+template <typename T>
+__global__ void moe_rowdot_scale_kernel(const T* __restrict__ y, long long ldy, T* __restrict__ dy, long long lddy,
+                                        const float* __restrict__ gate, float* __restrict__ dots,
+                                        const int* __restrict__ seg_off, int E_local, int capacity, int H) {
+  const long long row = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= capacity || row >= seg_off[E_local]) return;
+  const float g = gate[row];
+  const T* yr = y + row * ldy;
+  T* dr = dy + row * lddy;
+  float acc = 0.f;
+  for (int c = lane * 8; c < H; c += 256) {
+    const uint4 a = *reinterpret_cast<const uint4*>(yr + c);
+    uint4 b = *reinterpret_cast<const uint4*>(dr + c);
+    const T* ea = reinterpret_cast<const T*>(&a);
+    T* eb = reinterpret_cast<T*>(&b);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (std::is_same<T, __nv_bfloat16>::value) {
+        const float fb = __bfloat162float(reinterpret_cast<__nv_bfloat16*>(eb)[i]);
+        acc += __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(ea)[i]) * fb;
+        reinterpret_cast<__nv_bfloat16*>(eb)[i] = __float2bfloat16_rn(fb * g);
+      } else {
+        const float fb = __half2float(reinterpret_cast<__half*>(eb)[i]);
+        acc += __half2float(reinterpret_cast<const __half*>(ea)[i]) * fb;
+        reinterpret_cast<__half*>(eb)[i] = __float2half_rn(fb * g);
+      }
+    }
+    *reinterpret_cast<uint4*>(dr + c) = b;
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) dots[row] = acc;
+}
+
+__global__ void moe_gather_scalar_kernel(MoePeers vals, const int* __restrict__ topk_idx,
+                                         const int* __restrict__ dest_row, long long n_pairs, int E_local,
+                                         float* __restrict__ out) {
+  const long long pair = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (pair >= n_pairs) return;
+  const int row = dest_row[pair];
+  out[pair] = row < 0 ? 0.f : reinterpret_cast<const float*>(vals.p[topk_idx[pair] / E_local])[row];
+}
+
 }  // namespace fmsb
 
 using namespace fmsb;
@@ -469,9 +515,49 @@ extern "C" int fmsb_moe_dispatch(const void* x, long long ldx, const int* topk_i
   MoePeers r = moe_ptrs(recv, world);
   const long long blocks = (n_pairs * 32 + 255) / 256;
   if (dtype == 1)
-    moe_dispatch_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, topk_idx, dest_row, scale, n_pairs, k, H, E_local, r, ld_recv);
+    moe_dispatch_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, topk_idx, dest_row, scale, n_pairs, k, H, E_local, r, ld_recv, nullptr, MoePeers{});
   else
-    moe_dispatch_kernel<__half><<<(unsigned)blocks, 256, 0, stream>>>((const __half*)x, ldx, topk_idx, dest_row, scale, n_pairs, k, H, E_local, r, ld_recv);
+    moe_dispatch_kernel<__half><<<(unsigned)blocks, 256, 0, stream>>>((const __half*)x, ldx, topk_idx, dest_row, scale, n_pairs, k, H, E_local, r, ld_recv, nullptr, MoePeers{});
+  return (int)cudaGetLastError();
+}
+
+// Dispatch that also delivers one fp32 value per (token, k) pair into the owner's per-row array `meta_recv`.
+extern "C" int fmsb_moe_dispatch_meta(const void* x, long long ldx, const int* topk_idx, const int* dest_row,
+                                      const float* meta_vals, long long n_pairs, int k, int H, int E_local,
+                                      void* const* recv, long long ld_recv, void* const* meta_recv, int world, int dtype,
+                                      cudaStream_t stream) {
+  if (n_pairs <= 0) return 0;
+  if (H % 8 != 0 || ldx % 8 != 0 || ld_recv % 8 != 0 || meta_vals == nullptr) return -2;
+  MoePeers r = moe_ptrs(recv, world), m = moe_ptrs(meta_recv, world);
+  const long long blocks = (n_pairs * 32 + 255) / 256;
+  if (dtype == 1)
+    moe_dispatch_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, topk_idx, dest_row, nullptr, n_pairs, k, H, E_local, r, ld_recv, meta_vals, m);
+  else
+    moe_dispatch_kernel<__half><<<(unsigned)blocks, 256, 0, stream>>>((const __half*)x, ldx, topk_idx, dest_row, nullptr, n_pairs, k, H, E_local, r, ld_recv, meta_vals, m);
+  return (int)cudaGetLastError();
+}
+
+// Owner side of the routing-weight gradient: dots[row] = <y[row], dy[row]>, then dy[row] *= gate[row]; rows below
+// seg_off[E_local] only (everything this rank received).  One warp per row.
+extern "C" int fmsb_moe_rowdot_scale(const void* y, long long ldy, void* dy, long long lddy, const float* gate,
+                                     float* dots, const int* seg_off, int E_local, int capacity, int H, int dtype,
+                                     cudaStream_t stream) {
+  if (capacity <= 0) return 0;
+  if (H % 8 != 0 || ldy % 8 != 0 || lddy % 8 != 0) return -2;
+  const long long blocks = ((long long)capacity * 32 + 255) / 256;
+  if (dtype == 1)
+    moe_rowdot_scale_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>((const __nv_bfloat16*)y, ldy, (__nv_bfloat16*)dy, lddy, gate, dots, seg_off, E_local, capacity, H);
+  else
+    moe_rowdot_scale_kernel<__half><<<(unsigned)blocks, 256, 0, stream>>>((const __half*)y, ldy, (__half*)dy, lddy, gate, dots, seg_off, E_local, capacity, H);
+  return (int)cudaGetLastError();
+}
+
+// out[pair] = owner's vals[dest_row[pair]] (0 for a dropped pair): 4 bytes per pair cross the link.
+extern "C" int fmsb_moe_gather_scalar(void* const* vals, const int* topk_idx, const int* dest_row, long long n_pairs,
+                                      int E_local, float* out, int world, cudaStream_t stream) {
+  if (n_pairs <= 0) return 0;
+  MoePeers v = moe_ptrs(vals, world);
+  moe_gather_scalar_kernel<<<(unsigned)((n_pairs + 255) / 256), 256, 0, stream>>>(v, topk_idx, dest_row, n_pairs, E_local, out);
   return (int)cudaGetLastError();
 }
 

@@ -29,6 +29,9 @@ N.declare("fmsb_moe_dispatch", [P, L, P, P, P, L, I, I, I, P, L, I, I, P])
 N.declare("fmsb_moe_zero_pad", [P, L, I, P, P, I, I, P])
 N.declare("fmsb_moe_combine", [P, L, P, P, P, L, I, I, I, P, L, I, I, P])
 N.declare("fmsb_moe_gate_grad", [P, L, P, P, P, L, L, I, I, I, P, I, I, P])
+N.declare("fmsb_moe_dispatch_meta", [P, L, P, P, P, L, I, I, I, P, L, P, I, I, P])
+N.declare("fmsb_moe_rowdot_scale", [P, L, P, L, P, P, P, I, I, I, I, P])
+N.declare("fmsb_moe_gather_scalar", [P, P, P, L, I, P, I, P])
 
 
 # ------------------------------------------------------------------------------------------------ oracle
@@ -291,15 +294,22 @@ class _Experts(torch.autograd.Function):
         Ys, Ys_ptrs, _ = mctx._alloc("Ys", cap, H, dt, dev)
         dYs, dYs_ptrs, _ = mctx._alloc("dYs", cap, H, dt, dev, shared=True)
         dXs, dXs_ptrs, _ = mctx._alloc("dXs", cap, H, dt, dev, shared=True)
+        # dout rows travel unscaled together with their routing weight; the OWNER forms <expert output, dout> per row
+        # (the routing-weight gradient) and applies the weight, so only 4 bytes per pair come back instead of a second
+        # pull of every expert-output row
+        rgate, rgate_ptrs, _ = mctx._alloc("rgate", cap, 1, torch.float32, dev, shared=True)
+        rdots, rdots_ptrs, _ = mctx._alloc("rdots", cap, 1, torch.float32, dev, shared=True)
         _zero_pad(mctx, dYs, seg_off, seg_cnt)
-        _dispatch(mctx, dout, idx, dest_row, gates, dYs_ptrs, dYs.stride(0))
-        # gradient of the routing weights: <expert output, dout> pulled from the owners
-        dgate = torch.empty(T, mctx.k, dtype=torch.float32, device=dev)
-        rc = N.lib().fmsb_moe_gate_grad(Ys_ptrs, Ys.stride(0), idx.data_ptr(), dest_row.data_ptr(), dout.data_ptr(),
-                                        dout.stride(0), T * mctx.k, mctx.k, H, El, dgate.data_ptr(), mctx.world,
-                                        N.dtype_code(dt), N.stream_ptr())
-        N.check(rc, "fmsb_moe_gate_grad")
+        gates_c = gates.contiguous()
+        rc = N.lib().fmsb_moe_dispatch_meta(dout.data_ptr(), dout.stride(0), idx.data_ptr(), dest_row.data_ptr(),
+                                            gates_c.data_ptr(), T * mctx.k, mctx.k, H, El, dYs_ptrs, dYs.stride(0),
+                                            rgate_ptrs, mctx.world, N.dtype_code(dt), N.stream_ptr())
+        N.check(rc, "fmsb_moe_dispatch_meta")
         mctx.barrier(BAR_C)
+        rc = N.lib().fmsb_moe_rowdot_scale(Ys.data_ptr(), Ys.stride(0), dYs.data_ptr(), dYs.stride(0), rgate.data_ptr(),
+                                           rdots.data_ptr(), seg_off.data_ptr(), El, cap, H, N.dtype_code(dt),
+                                           N.stream_ptr())
+        N.check(rc, "fmsb_moe_rowdot_scale")
         hs = ACT.glu_fwd(gu[:, :I_], gu[:, I_:], act)
         dw2 = grouped_gemm(hs, dYs, seg_off, El, mode=2, m=I_, n=H)
         dhs = grouped_gemm(dYs, w2.view(El * I_, H), seg_off, El, mode=1, b_mn=False, n=I_)
@@ -312,6 +322,10 @@ class _Experts(torch.autograd.Function):
         grouped_gemm(dg3, w3.view(El * H, I_), seg_off, El, mode=1, b_mn=False, n=H, out=dXs, c=dXs, beta=1.0)
         mctx.barrier(BAR_D)
         dx = _combine(mctx, dXs_ptrs, dXs.stride(0), idx, dest_row, None, T, H, dt, dev)
+        dgate = torch.empty(T, mctx.k, dtype=torch.float32, device=dev)
+        rc = N.lib().fmsb_moe_gather_scalar(rdots_ptrs, idx.data_ptr(), dest_row.data_ptr(), T * mctx.k, El,
+                                            dgate.data_ptr(), mctx.world, N.stream_ptr())
+        N.check(rc, "fmsb_moe_gather_scalar")
         return dx, dgate, None, dw1.to(w1.dtype), dw3.to(w3.dtype), dw2.to(w2.dtype), None, None
 
 
