@@ -17,6 +17,7 @@ import torch
 import ctypes as _ct
 
 from .. import _native as N
+from .. import _native as _NV  # second alias: `N` is also the name of a matrix dimension argument below
 
 N.declare("fmsb_batched_gemm", [_ct.c_void_p, _ct.c_longlong, _ct.c_longlong, _ct.c_longlong, _ct.c_void_p, _ct.c_longlong,
                                  _ct.c_longlong, _ct.c_longlong, _ct.c_int, _ct.c_int, _ct.c_int, _ct.c_void_p, _ct.c_longlong,
@@ -130,12 +131,12 @@ def batched_gemm(a, b, *, M, N, K, n_batch, n_inner=1, a_off=(0, 0, 0, 1), b_off
         bn = _pick_bn(N, b_mn)
     desc = (ctypes.c_int * 13)(n_batch, n_inner, a_off[0], a_off[1], a_off[2], a_off[3], b_off[0], b_off[1], b_off[2],
                                b_off[3], d_off[0], d_off[1], d_off[2])
-    st = N.status_word(a.device)
-    rc = N.lib().fmsb_batched_gemm(a.data_ptr(), a.stride(0), a.shape[0], a.shape[1], b.data_ptr(), b.stride(0),
+    st = _NV.status_word(a.device)
+    rc = _NV.lib().fmsb_batched_gemm(a.data_ptr(), a.stride(0), a.shape[0], a.shape[1], b.data_ptr(), b.stride(0),
                                     b.shape[0], b.shape[1], K, int(a_mn), int(b_mn), out.data_ptr(), out.stride(0),
-                                    int(out.dtype == torch.float32), None, 0, 1.0, 0.0, M, N, N.dtype_code(a.dtype), bn,
-                                    desc, st.data_ptr(), N.stream_ptr())
-    N.check(rc, "fmsb_batched_gemm")
+                                    int(out.dtype == torch.float32), None, 0, 1.0, 0.0, M, N, _NV.dtype_code(a.dtype), bn,
+                                    desc, st.data_ptr(), _NV.stream_ptr())
+    _NV.check(rc, "fmsb_batched_gemm")
     return out
 
 
