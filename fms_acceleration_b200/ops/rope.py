@@ -67,11 +67,15 @@ def apply_rope(x, pos, cos_t, sin_t):
     return _Rope.apply(x, pos, cos_t, sin_t)
 
 
-def fast_rope_embedding(q, k, cos, sin, position_ids=None):
+def fast_rope_embedding(q, k, cos, sin, position_ids=None, unsqueeze_dim=1):
     """HF-shaped entry: q,k ``[B, heads, S, d]``, cos/sin ``[B, S, d]`` (already gathered per token).
     Mirrors fms_acceleration_foak/kernels/unsloth/rope_embedding.py:136-139 but honours positions."""
     B, Hq, S, d = q.shape
     half = d // 2
+    if cos.dim() == 2:  # [S, d]
+        cos, sin = cos[None], sin[None]
+    if cos.shape[0] != B:  # one set of positions broadcast over the batch
+        cos, sin = cos.expand(B, S, d), sin.expand(B, S, d)
     cos_t = cos.reshape(B * S, d)[:, :half].float().contiguous()
     sin_t = sin.reshape(B * S, d)[:, :half].float().contiguous()
     pos = torch.arange(B * S, device=q.device, dtype=torch.int32)

@@ -233,7 +233,8 @@ def recover_original_state_dict_from_checkpoint(sd: Dict[str, torch.Tensor], pre
             elif not sharded_experts:
                 assert n == 1, "Expert weights expected to be non-sharded."
             else:
-                assert n == param.shape[0], "Sharded expert weights should be 1 expert per shard."
+                # one tensor per expert, or (transformers >= 5 layout of the same family) one fused 3-D tensor
+                assert n in (1, param.shape[0]), "Sharded expert weights should be 1 expert per shard."
             if is_expert:
                 param = param.permute(0, 2, 1)  # [E, in, out] -> [E, out, in]
             for i, (model_key, _) in enumerate(targets):

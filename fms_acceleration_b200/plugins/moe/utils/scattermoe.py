@@ -95,7 +95,7 @@ class ScatterMoE(nn.Module):
         else:
             assert not self.expert_parallel, "the CPU oracle path has no expert parallelism"
             out = self._forward_reference(x2, w, idx)
-        return out.view(shape), logits
+        return (out.view(shape), logits) if getattr(self, "return_router_logits", True) else out.view(shape)
 
     def _forward_reference(self, x2, w, idx):
         out = torch.zeros_like(x2, dtype=torch.float32)

@@ -30,6 +30,19 @@ def _moe_dims(moe_block: nn.Module, config):
     return num_experts, top_k, inter
 
 
+def _returns_router_logits(module: nn.Module) -> bool:
+    """Whether the block being replaced hands back ``(hidden, router_logits)`` (transformers < 5 and the in-tree
+    models) or the hidden states only (transformers >= 5 collects router logits through output recorders)."""
+    if module.__class__.__module__.startswith("transformers."):
+        try:
+            import transformers
+
+            return int(transformers.__version__.split(".")[0]) < 5
+        except Exception:  # pragma: no cover
+            return True
+    return True
+
+
 def build_ep_groups(world_size: int, ep_degree: int, rank: int):
     """(expert-parallel group of this rank, replicate group of this rank) or (None, None) for ep_degree 1."""
     if ep_degree == 1 or world_size == 1:
@@ -111,6 +124,7 @@ def prepare_scattermoe(model: nn.Module, checkpoint_name_or_path: Optional[str] 
                     p._fmsb_expert_parallel = True
                     p._fmsb_replicate_group = rep_group
         moe._fmsb_replicate_group = rep_group
+        moe.return_router_logits = _returns_router_logits(module)
         setattr(parent, leaf, moe)
         swapped.append(name)
         del module

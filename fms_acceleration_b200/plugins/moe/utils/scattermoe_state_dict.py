@@ -48,10 +48,18 @@ def get_checkpoint_meta_from_sharded_safetensor(weight_map: Dict, prefix: str, i
     out: Dict[str, List] = defaultdict(list)
     full_prefix = f"{prefix}.{instance_name}."
     pattern = re.compile(rf"({router_name}|{expert_name})\.?(\d+)?\.?(\w+)?\.weight")
+    # transformers >= 5 stores a per-expert-linear family (Mixtral) as two fused 3-D parameters without ".weight":
+    # "<experts>.gate_up_proj" [E, 2I, H] (gate rows first) and "<experts>.down_proj" [E, H, I]
+    fused3d = {"gate_up_proj": ["w1", "w3"], "down_proj": ["w2"]}
     for key, st_file in weight_map.items():
         if not key.startswith(full_prefix):
             continue
         rel = key[len(full_prefix):]
+        head, _, tail = rel.rpartition(".")
+        if head == expert_name.split("|")[0] and tail in fused3d:
+            for w in fused3d[tail]:
+                _set_at(out[f"{w}.weight"], 0, (key, st_file))
+            continue
         m = pattern.match(rel)
         if m is None:
             raise ValueError(

@@ -1,0 +1,95 @@
+"""Hugging Face model classes through the framework on the CPU: the fused-ops plugin patches RMSNorm, rotary
+embedding and the loss of a real ``transformers`` Llama, and the patched model computes what the original computes
+(on the CPU every op takes its PyTorch oracle path, so this checks the plumbing: rules, triggers, replacements)."""
+import copy
+
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+
+import fms_acceleration_b200.plugins  # noqa: F401,E402  (registers the plugins)
+from fms_acceleration_b200.framework.model_patcher import ModelPatcher  # noqa: E402
+from fms_acceleration_b200.framework.utils.test_utils import instantiate_framework  # noqa: E402
+from fms_acceleration_b200.trainer import TrainArgs  # noqa: E402
+
+
+def _tiny_llama():
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    cfg = LlamaConfig(vocab_size=512, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, max_position_embeddings=128, rms_norm_eps=1e-6, tie_word_embeddings=False,
+                      architectures=["LlamaForCausalLM"])
+    torch.manual_seed(0)
+    return LlamaForCausalLM(cfg)
+
+
+@pytest.mark.parametrize("fast_loss", [True, "fused_ce_liger"])
+def test_foak_patches_hf_llama_and_keeps_the_numbers(fast_loss):
+    model = _tiny_llama()
+    ref = copy.deepcopy(model)
+    ids = torch.randint(0, 512, (2, 24))
+    cfg = {"training": {"fused_ops_and_kernels": {"fused_lora": False, "fast_loss": fast_loss, "fast_rms_layernorm": True,
+                                                 "fast_rope_embeddings": True}}}
+    saved_rules, saved_hist = dict(ModelPatcher.rules), list(ModelPatcher.history)
+    try:
+        with instantiate_framework(cfg, require_packages_check=False) as fw:
+            model, _ = fw.augmentation(model, TrainArgs(bf16=False), modifiable_args=(None,))
+            fw.get_callbacks_and_ready_for_train(model, None)
+            ModelPatcher.patch(model)
+            applied = {h.rule_id for h in ModelPatcher.history}
+            assert "llama-rms" in applied, applied
+            assert any(r.startswith("llama-") and ("loss" in r or "lce" in r) for r in applied), applied
+            model.train()
+            ref.train()
+            out = model(input_ids=ids, labels=ids)
+            want = ref(input_ids=ids, labels=ids)
+            assert torch.allclose(out.loss, want.loss, atol=1e-4, rtol=1e-4)
+            out.loss.backward()
+            want.loss.backward()
+            g1 = model.model.layers[0].self_attn.q_proj.weight.grad
+            g2 = ref.model.layers[0].self_attn.q_proj.weight.grad
+            assert torch.allclose(g1, g2, atol=1e-5, rtol=1e-3)
+            if fast_loss == "fused_ce_liger":
+                assert out.logits is None  # the training branch never materialises the logits
+    finally:
+        ModelPatcher.rules.clear()
+        ModelPatcher.rules.update(saved_rules)
+        ModelPatcher.history[:] = saved_hist
+        import importlib
+
+        import transformers.models.llama.modeling_llama as ml
+
+        importlib.reload(ml)
+
+
+@pytest.mark.parametrize("family", ["granitemoe", "mixtral"])
+def test_scattermoe_swaps_hf_moe_blocks_exactly_and_converts_back(family):
+    """The module swap works on the installed transformers' MoE classes (fused 3-D expert parameters and hidden-only
+    return value in transformers >= 5; one linear per expert and a tuple before), and the ScatterMoE state converts
+    back to the original parameter names and values."""
+    from fms_acceleration_b200.plugins.moe.utils import checkpoint_utils as CU
+    from fms_acceleration_b200.plugins.moe.utils import prepare_scattermoe
+
+    if family == "granitemoe":
+        from transformers import GraniteMoeConfig as C
+        from transformers import GraniteMoeForCausalLM as M
+    else:
+        from transformers import MixtralConfig as C
+        from transformers import MixtralForCausalLM as M
+    torch.manual_seed(0)
+    cfg = C(vocab_size=512, hidden_size=64, intermediate_size=32, num_hidden_layers=2, num_attention_heads=4,
+            num_key_value_heads=2, num_local_experts=4, num_experts_per_tok=2, architectures=[M.__name__])
+    model = M(cfg).eval()
+    original = {k: v.clone() for k, v in model.state_dict().items()}
+    ids = torch.randint(0, 512, (2, 16))
+    ref = model(input_ids=ids, labels=ids).loss
+    swapped = prepare_scattermoe(model, None, 0, 1, 1)
+    assert len(swapped) == 2
+    assert abs(model(input_ids=ids, labels=ids).loss.item() - ref.item()) < 1e-5
+    sd = CU.recover_original_state_dict_from_checkpoint(dict(model.state_dict()),
+                                                        weight_map={k: "model.safetensors" for k in original},
+                                                        architectures=[M.__name__])
+    assert set(sd) == set(original)
+    for k in original:
+        assert torch.equal(sd[k], original[k]), k
