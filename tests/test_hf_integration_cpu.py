@@ -93,3 +93,29 @@ def test_scattermoe_swaps_hf_moe_blocks_exactly_and_converts_back(family):
     assert set(sd) == set(original)
     for k in original:
         assert torch.equal(sd[k], original[k]), k
+
+
+@pytest.mark.parametrize("family", ["llama", "granitemoe"])
+def test_in_tree_models_load_hf_checkpoints(tmp_path, family):
+    """A checkpoint written by ``save_pretrained`` (config.json + model.safetensors) loads into the in-tree model of
+    the same architecture and gives the same logits."""
+    from fms_acceleration_b200.models.builder import build_model
+
+    torch.manual_seed(0)
+    if family == "llama":
+        hf = _tiny_llama().eval()
+    else:
+        from transformers import GraniteMoeConfig, GraniteMoeForCausalLM
+
+        hf = GraniteMoeForCausalLM(GraniteMoeConfig(
+            vocab_size=512, hidden_size=64, intermediate_size=32, num_hidden_layers=2, num_attention_heads=4,
+            num_key_value_heads=2, num_local_experts=4, num_experts_per_tok=2, architectures=["GraniteMoeForCausalLM"],
+            tie_word_embeddings=True)).eval()
+    path = tmp_path / family
+    hf.save_pretrained(str(path), safe_serialization=True)
+    mine = build_model(str(path), dtype=torch.float32).eval()
+    ids = torch.randint(0, 512, (2, 20))
+    with torch.no_grad():
+        want = hf(input_ids=ids).logits
+        got = mine(input_ids=ids).logits
+    assert torch.allclose(got, want, atol=2e-4, rtol=1e-3), (got - want).abs().max()
