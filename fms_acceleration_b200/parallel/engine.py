@@ -109,6 +109,9 @@ class ShardedEngine:
         if shard_frozen and self.world > 1 and self.layers:
             self._shard_frozen_layers()
         self._setup_grad_bucket(grad_dtype)
+        self.sharded_optimizer: Optional["ShardedOptimizer"] = None
+        if shard_optimizer and self.world > 1 and self.params:
+            self._setup_param_bucket()
 
     # ------------------------------------------------------------------ frozen quantised weights
     @staticmethod
@@ -220,6 +223,37 @@ class ShardedEngine:
             for p in self.params:
                 dist.broadcast(p.data, src=dist.get_global_rank(self.group, 0), group=self.group)
 
+    # ------------------------------------------------------------------ optimizer state sharding (ZeRO-1)
+    def _setup_param_bucket(self) -> None:
+        """Replicated trainable parameters become views into one flat symmetric buffer, laid out like the gradient
+        bucket, so that rank r can update slice r and everybody can pull the updated slices."""
+        dtypes = {p.dtype for p in self.params}
+        if len(dtypes) != 1:
+            raise ValueError("optimizer sharding needs all replicated trainable parameters in one dtype")
+        self.param_dtype = dtypes.pop()
+        esize = torch.empty((), dtype=self.param_dtype).element_size()
+        self.param_bucket = SymmBuffer(self.bucket_numel * esize, self.group, self.device)
+        flat = self.param_bucket.view(0, self.bucket_numel, self.param_dtype)
+        off = 0
+        with torch.no_grad():
+            for p in self.params:
+                v = flat[off: off + p.numel()].view_as(p)
+                v.copy_(p.data)
+                p.data = v
+                off += p.numel()
+        self.flat_params = flat
+        self.n_own = self.bucket_numel // self.world
+        self.own_slice = slice(self.rank * self.n_own, (self.rank + 1) * self.n_own)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+
+    def build_optimizer(self, lr: float, weight_decay: float = 0.0, betas=(0.9, 0.999), eps: float = 1e-8):
+        """AdamW over this rank's 1/world slice of the flat parameters (fp32 master copy and moments)."""
+        if not hasattr(self, "flat_params"):
+            raise RuntimeError("the engine was created without shard_optimizer=True (or runs on one rank)")
+        self.sharded_optimizer = ShardedOptimizer(self, lr, weight_decay, betas, eps)
+        return self.sharded_optimizer
+
     def zero_grad(self) -> None:
         for p in self.ep_params:
             p.grad = None
@@ -231,6 +265,13 @@ class ShardedEngine:
                 p.grad = v
             else:
                 p.grad = None
+
+    def _collect_grads(self) -> None:
+        """Gradients that autograd did not write straight into the bucket views are copied there."""
+        for p, v in zip(self.params, self._grad_views):
+            if p.grad is not None and p.grad.data_ptr() != v.data_ptr():
+                v.copy_(p.grad)
+                p.grad = v if p.dtype == self.grad_dtype else p.grad
 
     def reduce_gradients(self) -> None:
         """Average the gradients of all replicated trainable parameters across the group (one kernel)."""
@@ -245,15 +286,67 @@ class ShardedEngine:
                 dist.all_reduce(p.grad, group=rep)
         if not self.params:
             return
-        for p, v in zip(self.params, self._grad_views):
-            if p.grad is not None and p.grad.data_ptr() != v.data_ptr():
-                v.copy_(p.grad)
-                p.grad = v if p.dtype == self.grad_dtype else p.grad
+        self._collect_grads()
         if self.world > 1:
             self.comm.allreduce_(self.bucket, self.bucket_numel, self.grad_dtype, scale=self.grad_scale)
             for p, v in zip(self.params, self._grad_views):
                 if p.dtype != self.grad_dtype and p.grad is not None:
                     p.grad.copy_(v)
+
+
+class ShardedOptimizer:
+    """ZeRO-1 step for the engine's replicated parameters.
+
+    ``step()`` = reduce-scatter of the flat gradient bucket with the 1/world scale and the cast to fp32 fused (each
+    rank pulls its slice from all peers), AdamW on the fp32 master slice, cast of the updated slice into the flat
+    parameter buffer, then a pull all-gather of the other ranks' slices.  Optimizer memory per rank is 12 bytes per
+    parameter divided by the world size instead of replicated.  Expert-parallel parameters keep their own optimizer.
+    """
+
+    def __init__(self, engine: "ShardedEngine", lr, weight_decay, betas, eps):
+        self.engine = engine
+        e = engine
+        self.master = e.flat_params[e.own_slice].float().clone().requires_grad_(False)
+        self.master.grad = torch.zeros_like(self.master)
+        self.inner = torch.optim.AdamW([self.master], lr=lr, weight_decay=weight_decay, betas=betas, eps=eps, fused=True)
+        self.param_groups = self.inner.param_groups
+        self.max_grad_norm = 0.0
+        esize = torch.empty((), dtype=e.param_dtype).element_size()
+        # rank r's updated slice lives at byte offset r * slice inside ITS OWN flat buffer
+        self._slice_bytes = e.n_own * esize
+        import ctypes
+
+        self._slice_ptrs = (ctypes.c_void_p * e.world)(*[p + r * self._slice_bytes
+                                                         for r, p in enumerate(e.param_bucket.ptrs)])
+
+    def step(self) -> None:
+        e = self.engine
+        e._collect_grads()
+        e.comm.reduce_scatter(e.bucket, e.n_own, e.grad_dtype, self.master.grad, scale=e.grad_scale)
+        if self.max_grad_norm and self.max_grad_norm > 0:
+            # global norm of the averaged gradient = sqrt of the sum over ranks of the slices' squared norms
+            sq = self.master.grad.pow(2).sum()
+            dist.all_reduce(sq, group=e.group)
+            self.master.grad.mul_(torch.clamp(self.max_grad_norm / (sq.sqrt() + 1e-6), max=1.0))
+        self.inner.step()
+        e.flat_params[e.own_slice].copy_(self.master)
+        e.comm.barrier(6)  # every rank's slice is written
+        from .. import _native as NV
+
+        rc = NV.lib().fmsb_comm_allgather(self._slice_ptrs, e.flat_params.data_ptr(), self._slice_bytes, e.rank,
+                                          e.world, 32, NV.stream_ptr())
+        NV.check(rc, "fmsb_comm_allgather")
+        e.comm.barrier(7)  # nobody rewrites a slice that a peer is still pulling
+
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        self.engine.zero_grad()
+
+    def state_dict(self):
+        return {"inner": self.inner.state_dict(), "master": self.master}
+
+    def load_state_dict(self, sd) -> None:
+        self.inner.load_state_dict(sd["inner"])
+        self.master.copy_(sd["master"])
 
 
 def install_engine(model: nn.Module, accelerator, **kwargs) -> Optional[ShardedEngine]:

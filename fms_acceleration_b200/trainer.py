@@ -85,6 +85,10 @@ class Trainer:
         self.engine = engine
         self.callbacks = callbacks or []
         params = [p for p in model.parameters() if p.requires_grad]
+        if optimizer is None and engine is not None and getattr(engine, "shard_optimizer", False) \
+                and hasattr(engine, "flat_params") and not engine.ep_params:
+            # optimizer states sharded over the ranks (the engine owns the flat parameter and gradient buffers)
+            optimizer = engine.build_optimizer(args.learning_rate, args.weight_decay)
         if optimizer is None:
             fused = bool(params) and params[0].is_cuda
             optimizer = torch.optim.AdamW(params, lr=args.learning_rate, weight_decay=args.weight_decay, fused=fused)
@@ -115,9 +119,13 @@ class Trainer:
         out = self.model(**kwargs)
         loss = out.loss
         loss.backward()
-        if self.engine is not None:
+        sharded = self.engine is not None and self.optimizer is getattr(self.engine, "sharded_optimizer", None) \
+            and self.optimizer is not None
+        if self.engine is not None and not sharded:
             self.engine.reduce_gradients()
-        if self.args.max_grad_norm and self.args.max_grad_norm > 0:
+        if sharded:
+            self.optimizer.max_grad_norm = self.args.max_grad_norm or 0.0  # clipped on the reduced slices
+        elif self.args.max_grad_norm and self.args.max_grad_norm > 0:
             torch.nn.utils.clip_grad_norm_(self.params, self.args.max_grad_norm)
         self.optimizer.step()
         if self.engine is not None:
@@ -160,7 +168,13 @@ class Trainer:
         os.makedirs(ckpt, exist_ok=True)
         lora = self._is_lora()
         CU.save_fsdp_model(None, None, self.model, ckpt, 0)
-        CU.save_fsdp_optimizer(None, None, self.optimizer, self.model, ckpt, 0, lora_only=lora)
+        if self.engine is not None and self.optimizer is getattr(self.engine, "sharded_optimizer", None):
+            # every rank owns a different slice of the optimizer state: one file per rank; the (replicated) model as usual
+            inner = torch.optim.SGD([torch.nn.Parameter(torch.zeros(1, device=self.device()))], lr=0.0)
+            CU.save_fsdp_optimizer(None, None, inner, self.model, ckpt, 0, lora_only=lora)
+            torch.save(self.optimizer.state_dict(), os.path.join(ckpt, f"optimizer_shard_{rank}.pt"))
+        else:
+            CU.save_fsdp_optimizer(None, None, self.optimizer, self.model, ckpt, 0, lora_only=lora)
         torch.save({"cpu": torch.get_rng_state(),
                     "cuda": torch.cuda.get_rng_state() if torch.cuda.is_available() else None},
                    os.path.join(ckpt, f"rng_state_{rank}.pth"))

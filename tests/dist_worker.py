@@ -122,6 +122,47 @@ def check_engine(dev, rank, world):
     print("DIST_OK engine_train", flush=True)
 
 
+def check_zero1(dev, rank, world):
+    """Optimizer-state sharding: a full fine-tune in fp32 with the sharded AdamW ends at the same parameters as the
+    replicated optimizer (all-reduced gradients), and every rank holds the same parameters afterwards."""
+    from fms_acceleration_b200 import _native as NV
+    from fms_acceleration_b200.models.builder import build_model
+    from fms_acceleration_b200.models.config import DecoderConfig
+    from fms_acceleration_b200.parallel.engine import ShardedEngine
+    from fms_acceleration_b200.trainer import TrainArgs, Trainer, synthetic_packed_batch
+
+    cfg = DecoderConfig(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                        num_attention_heads=4, num_key_value_heads=2, head_dim=64)
+    batches = [synthetic_packed_batch(512, 1, 256, (32, 256), seed=7 * rank + i, pin=False) for i in range(3)]
+
+    def run(shard: bool):
+        torch.manual_seed(0)
+        m = build_model(cfg, device=dev, dtype=torch.float32, seed=0)
+        eng = ShardedEngine(m, shard_frozen=False, shard_optimizer=shard)
+        tr = Trainer(m, TrainArgs(learning_rate=1e-3, weight_decay=0.01, max_grad_norm=1.0), engine=eng)
+        assert (tr.optimizer is eng.sharded_optimizer) == shard
+        eng.zero_grad()
+        losses = [float(tr.train_step(b)) for b in batches]
+        NV.check_status()
+        return m, losses, tr
+
+    m_ref, l_ref, _ = run(False)
+    m_sh, l_sh, tr = run(True)
+    assert abs(l_ref[0] - l_sh[0]) < 1e-5
+    worst = 0.0
+    for (n, a), (_, b) in zip(m_ref.named_parameters(), m_sh.named_parameters()):
+        worst = max(worst, ((a - b).norm() / a.norm().clamp(min=1e-9)).item())
+    assert worst < 2e-4, worst
+    flat = m_sh.lm_head.weight.detach().clone()
+    other = flat.clone()
+    dist.broadcast(other, src=0)
+    assert torch.equal(flat, other)  # every rank pulled the same updated slices
+    n_state = sum(v.numel() for st in tr.optimizer.inner.state.values() for v in st.values() if torch.is_tensor(v))
+    n_params = sum(p.numel() for p in m_sh.parameters())
+    assert n_state <= 2 * (n_params // world + 4096) + 8  # two moments over 1/world of the parameters
+    print(f"DIST_OK zero1 (worst rel parameter diff {worst:.1e}, state elements {n_state})", flush=True)
+
+
 def main():
     rank = int(os.environ["RANK"])
     world = int(os.environ["WORLD_SIZE"])
@@ -134,6 +175,8 @@ def main():
         check_comm(dev, rank, world)
     if which in ("all", "engine"):
         check_engine(dev, rank, world)
+    if which in ("all", "zero1"):
+        check_zero1(dev, rank, world)
     if which in ("all", "moe") and os.path.exists(os.path.join(os.path.dirname(__file__), "dist_worker_moe.py")):
         from dist_worker_moe import check_moe
 

@@ -23,6 +23,7 @@ def _run(which: str, nproc: int = 2, timeout: int = 600):
 @pytest.mark.parametrize("which,expected", [
     ("comm", ["allgather", "allreduce", "reduce_scatter"]),
     ("engine", ["engine", "engine_train"]),
+    ("zero1", ["zero1"]),
     ("moe", ["moe_ep"]),
     ("cp", ["mamba_cp"]),
 ])
