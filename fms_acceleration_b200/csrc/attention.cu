@@ -55,7 +55,7 @@ struct AttnFwd2Cfg {
   static constexpr int kSmemBytes = 2 * kTileBytes /*Qa,Qb*/ + 2 * 2 * kTileBytes /*K,V x2 stages*/ + 1024 + 256;
 };
 
-template <int D>
+template <int D, int FMT>
 __global__ void __launch_bounds__(320, 1)
 attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
@@ -143,8 +143,8 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc_s = make_idesc_f16(128, 128, p.fmt, 0, 0);
-      const uint32_t idesc_o = make_idesc_f16(128, D, p.fmt, 0, 1);
+      const uint32_t idesc_s = make_idesc_f16(128, 128, FMT, 0, 0);
+      const uint32_t idesc_o = make_idesc_f16(128, D, FMT, 0, 1);
       auto issue_s = [&](int x, int j) {
         const int s = j & 1;
 #pragma unroll
@@ -240,7 +240,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const bool bump = (m_blk - m_used) * sl2 > 8.f || cnt == 0;
         if (bump) {
           const float m_new = fmaxf(m_used, m_blk);
-          alpha = exp2f((m_used - m_new) * sl2);
+          alpha = fast_exp2((m_used - m_new) * sl2);
           m_used = m_new;
         }
         const float mb = m_used * sl2;
@@ -248,10 +248,10 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         uint32_t packed[64];
 #pragma unroll
         for (int i = 0; i < 128; i += 2) {
-          const float p0 = sv[i] <= -1e30f ? 0.f : exp2f(sv[i] * sl2 - mb);
-          const float p1 = sv[i + 1] <= -1e30f ? 0.f : exp2f(sv[i + 1] * sl2 - mb);
+          const float p0 = sv[i] <= -1e30f ? 0.f : fast_exp2(sv[i] * sl2 - mb);
+          const float p1 = sv[i + 1] <= -1e30f ? 0.f : fast_exp2(sv[i + 1] * sl2 - mb);
           l_blk += p0 + p1;
-          packed[i / 2] = pack2(p0, p1, p.fmt);
+          packed[i / 2] = pack2(p0, p1, FMT);
         }
         l_run = l_run * alpha + l_blk;
         // P (16-bit pairs) over the first 64 columns of this thread's own S row
@@ -293,10 +293,10 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
               uint4 u;
-              u.x = pack2(__uint_as_float(r[i]) * inv_l, __uint_as_float(r[i + 1]) * inv_l, p.fmt);
-              u.y = pack2(__uint_as_float(r[i + 2]) * inv_l, __uint_as_float(r[i + 3]) * inv_l, p.fmt);
-              u.z = pack2(__uint_as_float(r[i + 4]) * inv_l, __uint_as_float(r[i + 5]) * inv_l, p.fmt);
-              u.w = pack2(__uint_as_float(r[i + 6]) * inv_l, __uint_as_float(r[i + 7]) * inv_l, p.fmt);
+              u.x = pack2(__uint_as_float(r[i]) * inv_l, __uint_as_float(r[i + 1]) * inv_l, FMT);
+              u.y = pack2(__uint_as_float(r[i + 2]) * inv_l, __uint_as_float(r[i + 3]) * inv_l, FMT);
+              u.z = pack2(__uint_as_float(r[i + 4]) * inv_l, __uint_as_float(r[i + 5]) * inv_l, FMT);
+              u.w = pack2(__uint_as_float(r[i + 6]) * inv_l, __uint_as_float(r[i + 7]) * inv_l, FMT);
               *reinterpret_cast<uint4*>(orow + i) = u;
             }
           }
@@ -369,25 +369,22 @@ extern "C" int fmsb_attn_fwd(const void* q, long long ldq, const void* k, long l
   p.doc_start = doc_start; p.doc_end = doc_end;
   p.o = o; p.ldo = ldo; p.lse = lse; p.fmt = fmt; p.status = status;
   dim3 grid((T + 255) / 256, nh);
-  if (d == 128) {
-    static bool cfg = false;
-    if (!cfg) {
-      cudaError_t e = cudaFuncSetAttribute(attn_fwd2_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           AttnFwd2Cfg<128>::kSmemBytes);
-      if (e != cudaSuccess) return (int)e;
-      cfg = true;
-    }
-    attn_fwd2_kernel<128><<<grid, 320, AttnFwd2Cfg<128>::kSmemBytes, stream>>>(tq, tk, tv, p);
-  } else {
-    static bool cfg = false;
-    if (!cfg) {
-      cudaError_t e = cudaFuncSetAttribute(attn_fwd2_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           AttnFwd2Cfg<64>::kSmemBytes);
-      if (e != cudaSuccess) return (int)e;
-      cfg = true;
-    }
-    attn_fwd2_kernel<64><<<grid, 320, AttnFwd2Cfg<64>::kSmemBytes, stream>>>(tq, tk, tv, p);
-  }
+#define FMSB_FWD2(DD, FF)                                                                                         \
+  do {                                                                                                            \
+    static bool cfg = false;                                                                                      \
+    if (!cfg) {                                                                                                   \
+      cudaError_t e = cudaFuncSetAttribute(attn_fwd2_kernel<DD, FF>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                           AttnFwd2Cfg<DD>::kSmemBytes);                                          \
+      if (e != cudaSuccess) return (int)e;                                                                        \
+      cfg = true;                                                                                                 \
+    }                                                                                                             \
+    attn_fwd2_kernel<DD, FF><<<grid, 320, AttnFwd2Cfg<DD>::kSmemBytes, stream>>>(tq, tk, tv, p);                  \
+  } while (0)
+  if (d == 128 && fmt == 1) FMSB_FWD2(128, 1);
+  else if (d == 128) FMSB_FWD2(128, 0);
+  else if (fmt == 1) FMSB_FWD2(64, 1);
+  else FMSB_FWD2(64, 0);
+#undef FMSB_FWD2
   return (int)cudaGetLastError();
 }
 

@@ -302,10 +302,10 @@ attn_bwd_dkv2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           const float4 l4 = *reinterpret_cast<const float4*>(b + c0 + i);
           const float4 d4 = *reinterpret_cast<const float4*>(b + 128 + c0 + i);
           float pv[4];
-          pv[0] = exp2f(__uint_as_float(rs[i]) * sl2 - l4.x);
-          pv[1] = exp2f(__uint_as_float(rs[i + 1]) * sl2 - l4.y);
-          pv[2] = exp2f(__uint_as_float(rs[i + 2]) * sl2 - l4.z);
-          pv[3] = exp2f(__uint_as_float(rs[i + 3]) * sl2 - l4.w);
+          pv[0] = fast_exp2(__uint_as_float(rs[i]) * sl2 - l4.x);
+          pv[1] = fast_exp2(__uint_as_float(rs[i + 1]) * sl2 - l4.y);
+          pv[2] = fast_exp2(__uint_as_float(rs[i + 2]) * sl2 - l4.z);
+          pv[3] = fast_exp2(__uint_as_float(rs[i + 3]) * sl2 - l4.w);
           if (need_mask) {
             const int4 s4 = *reinterpret_cast<const int4*>(bi + c0 + i);
             const int t = q0 + c0 + i;
@@ -518,8 +518,8 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         uint32_t dk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float p0 = exp2f(__uint_as_float(rs[i]) * sl2 - lse2);
-          float p1 = exp2f(__uint_as_float(rs[i + 1]) * sl2 - lse2);
+          float p0 = fast_exp2(__uint_as_float(rs[i]) * sl2 - lse2);
+          float p1 = fast_exp2(__uint_as_float(rs[i + 1]) * sl2 - lse2);
           if (need_mask) {
             const int kk = kk0 + i;
             if (!(row_ok && kk >= ds && kk <= t)) p0 = 0.f;

@@ -76,6 +76,15 @@ __device__ __forceinline__ void b3_store_row_chunk(uint16_t* dst, const uint32_t
     *reinterpret_cast<uint4*>(dst + i) = u;
   }
 }
+// Optional timeline trace (compile with -DFMSB_TRACE): one CTA of the dQ kernel records clock64() at the hand-off
+// points of its MMA issuer and of one compute thread; read back with fmsb_attn_trace3_read.
+#ifdef FMSB_TRACE
+__device__ long long g_trace3[8192];
+#define FMSB_TRACE3(cond, slot) do { if ((cond) && (slot) < 8192) g_trace3[(slot)] = clock64(); } while (0)
+#else
+#define FMSB_TRACE3(cond, slot) do { } while (0)
+#endif
+
 __device__ __forceinline__ void b3_compute_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 // Column of K-step `ks` (16 elements = 8 packed columns) of a packed 128-element row: the warp of columns 0-63
@@ -85,7 +94,7 @@ __device__ __forceinline__ uint32_t b3_pcol(int ks) { return static_cast<uint32_
 // ----------------------------------------------------------------------------------------
 // dV[kv tile, kv head] = sum P^T dO ,  dK = scale * sum dS^T Q
 // ----------------------------------------------------------------------------------------
-template <int D>
+template <int D, int FMT>
 __global__ void __launch_bounds__(320, 1)
 attn_bwd_dkv3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
@@ -168,8 +177,8 @@ attn_bwd_dkv3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc_s = make_idesc_f16(128, 128, p.fmt, 0, 0);
-      const uint32_t idesc_g = make_idesc_f16(128, D, p.fmt, 0, 1);
+      const uint32_t idesc_s = make_idesc_f16(128, 128, FMT, 0, 0);
+      const uint32_t idesc_g = make_idesc_f16(128, D, FMT, 0, 1);
       const SmemDescBase dK = make_smem_desc_base(sK, 16, 1024), dV = make_smem_desc_base(sV, 16, 1024);
       auto issue_s = [&](int s) {  // S^T = K Q^T
         const SmemDescBase dQ = make_smem_desc_base(sQ(s), 16, 1024);
@@ -274,10 +283,10 @@ attn_bwd_dkv3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             const int col = c0 + c * 32 + i;
             const float4 l4 = *reinterpret_cast<const float4*>(b + col);
             float pv[4];
-            pv[0] = exp2f(__uint_as_float(rs[i]) * sl2 - l4.x);
-            pv[1] = exp2f(__uint_as_float(rs[i + 1]) * sl2 - l4.y);
-            pv[2] = exp2f(__uint_as_float(rs[i + 2]) * sl2 - l4.z);
-            pv[3] = exp2f(__uint_as_float(rs[i + 3]) * sl2 - l4.w);
+            pv[0] = fast_exp2(__uint_as_float(rs[i]) * sl2 - l4.x);
+            pv[1] = fast_exp2(__uint_as_float(rs[i + 1]) * sl2 - l4.y);
+            pv[2] = fast_exp2(__uint_as_float(rs[i + 2]) * sl2 - l4.z);
+            pv[3] = fast_exp2(__uint_as_float(rs[i + 3]) * sl2 - l4.w);
             if (need_mask) {
               const int4 s4 = *reinterpret_cast<const int4*>(bi + col);
               const int t = q0 + col;
@@ -286,8 +295,8 @@ attn_bwd_dkv3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
               if (!(kr >= s4.z && kr <= t + 2)) pv[2] = 0.f;
               if (!(kr >= s4.w && kr <= t + 3)) pv[3] = 0.f;
             }
-            pk[c * 16 + i / 2] = b3_pack2(pv[0], pv[1], p.fmt);
-            pk[c * 16 + i / 2 + 1] = b3_pack2(pv[2], pv[3], p.fmt);
+            pk[c * 16 + i / 2] = b3_pack2(pv[0], pv[1], FMT);
+            pk[c * 16 + i / 2 + 1] = b3_pack2(pv[2], pv[3], FMT);
           }
         }
         tmem_st_32x32(tS + lane_addr + c0, pk);
@@ -310,11 +319,11 @@ attn_bwd_dkv3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           for (int i = 0; i < 32; i += 4) {
             const float4 d4 = *reinterpret_cast<const float4*>(b + 128 + c0 + c * 32 + i);
             float p0, p1, p2, p3;
-            b3_unpack2(pk[c * 16 + i / 2], p.fmt, p0, p1);
-            b3_unpack2(pk[c * 16 + i / 2 + 1], p.fmt, p2, p3);
-            dk[c * 16 + i / 2] = b3_pack2(p0 * (__uint_as_float(rp[i]) - d4.x), p1 * (__uint_as_float(rp[i + 1]) - d4.y), p.fmt);
+            b3_unpack2(pk[c * 16 + i / 2], FMT, p0, p1);
+            b3_unpack2(pk[c * 16 + i / 2 + 1], FMT, p2, p3);
+            dk[c * 16 + i / 2] = b3_pack2(p0 * (__uint_as_float(rp[i]) - d4.x), p1 * (__uint_as_float(rp[i + 1]) - d4.y), FMT);
             dk[c * 16 + i / 2 + 1] =
-                b3_pack2(p2 * (__uint_as_float(rp[i + 2]) - d4.z), p3 * (__uint_as_float(rp[i + 3]) - d4.w), p.fmt);
+                b3_pack2(p2 * (__uint_as_float(rp[i + 2]) - d4.z), p3 * (__uint_as_float(rp[i + 3]) - d4.w), FMT);
           }
         }
         tmem_st_32x32(tdP + lane_addr + c0, dk);
@@ -335,12 +344,12 @@ attn_bwd_dkv3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         tmem_ld_32x32(tdV + lane_addr + col, r);
         tmem_ld_wait();
         if (kr < p.T)
-          b3_store_row_chunk(reinterpret_cast<uint16_t*>(p.dv) + (long long)kr * p.lddv + hk * D + col, r, 1.f, p.fmt);
+          b3_store_row_chunk(reinterpret_cast<uint16_t*>(p.dv) + (long long)kr * p.lddv + hk * D + col, r, 1.f, FMT);
         tmem_ld_32x32(tdK + lane_addr + col, r);
         tmem_ld_wait();
         if (kr < p.T)
           b3_store_row_chunk(reinterpret_cast<uint16_t*>(p.dk) + (long long)kr * p.lddk + hk * D + col, r, p.scale,
-                             p.fmt);
+                             FMT);
       }
     }
   }
@@ -356,7 +365,7 @@ attn_bwd_dkv3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 // ----------------------------------------------------------------------------------------
 // dQ[q tile, head] = scale * sum_j dS_j K_j
 // ----------------------------------------------------------------------------------------
-template <int D>
+template <int D, int FMT>
 __global__ void __launch_bounds__(320, 1)
 attn_bwd_dq3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
@@ -435,8 +444,8 @@ attn_bwd_dq3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc_s = make_idesc_f16(128, 128, p.fmt, 0, 0);
-      const uint32_t idesc_g = make_idesc_f16(128, D, p.fmt, 0, 1);
+      const uint32_t idesc_s = make_idesc_f16(128, 128, FMT, 0, 0);
+      const uint32_t idesc_g = make_idesc_f16(128, D, FMT, 0, 1);
       auto issue_scores = [&](uint32_t acc, uint32_t a_tmem, uint32_t b_tile, uint32_t bar) {  // acc = A[tmem] . B^T
         const SmemDescBase b = make_smem_desc_base(b_tile, 16, 1024);
 #pragma unroll
@@ -452,30 +461,41 @@ attn_bwd_dq3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
         for (int ks = 1; ks < 8; ++ks) tc_mma_f16_ts(tdQ, tdP + b3_pcol(ks), smem_desc_at(b, ks * 2048), idesc_g, 1u);
       };
+      const bool tr = blockIdx.x == gridDim.x / 2 && blockIdx.y == 0;
+      FMSB_TRACE3(tr, 4000);
       bool ok = mbar_wait(bar_qtm_full, 0, p.status, kTimeoutMma);
+      FMSB_TRACE3(tr, 4001);
       if (ok) ok = mbar_wait(bar_kv_full(0), 0, p.status, kTimeoutMma);
       if (ok) {
         tc_fence_after();
         issue_scores(tS, tQ, sK(0), bar_s_full);
         issue_scores(tdP, tdO, sV(0), bar_dp_full);
       }
+      FMSB_TRACE3(tr, 4002);
       for (int j = 0; j < nblk && ok; ++j) {
         const int s = j & 1;
         const bool more = j + 1 < nblk;
+        FMSB_TRACE3(tr, 4096 + 8 * j + 0);
         if (more) {
           // S(j) is in the compute warps' registers: S(j+1) may overwrite it while they work
           if (!mbar_wait(bar_sa_done, j & 1, p.status, kTimeoutMma)) { ok = false; break; }
           if (!mbar_wait(bar_kv_full(s ^ 1), ((j + 1) >> 1) & 1, p.status, kTimeoutMma)) { ok = false; break; }
           tc_fence_after();
+          FMSB_TRACE3(tr, 4096 + 8 * j + 1);
           issue_scores(tS, tQ, sK(s ^ 1), bar_s_full);
+          FMSB_TRACE3(tr, 4096 + 8 * j + 2);
         }
         if (!mbar_wait(bar_pb_full, j & 1, p.status, kTimeoutMma)) { ok = false; break; }
         tc_fence_after();
+        FMSB_TRACE3(tr, 4096 + 8 * j + 3);
         issue_dq(s, j == 0);
         tc_commit(bar_kv_empty(s));
+        FMSB_TRACE3(tr, 4096 + 8 * j + 4);
         if (more) issue_scores(tdP, tdO, sV(s ^ 1), bar_dp_full);
+        FMSB_TRACE3(tr, 4096 + 8 * j + 5);
       }
       if (ok) tc_commit(bar_acc_done);
+      FMSB_TRACE3(tr, 4003);
     }
   } else {
     const int quarter = warp & 3;
@@ -490,7 +510,10 @@ attn_bwd_dq3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const float lse2 = row_ok ? p.lse[(long long)head * p.T + t] * LOG2E : 0.f;
     const float dlt = row_ok ? p.delta[(long long)head * p.T + t] : 0.f;
     const int c0 = chalf * 64;
+    const bool trc = blockIdx.x == gridDim.x / 2 && blockIdx.y == 0 && threadIdx.x == 64;
+    FMSB_TRACE3(trc, 10);
     bool ok = mbar_wait(bar_q, 0, p.status, kTimeoutEpilogue);
+    FMSB_TRACE3(trc, 11);
     // ---- Q and dO rows into tensor memory as packed 16-bit A operands (row = lane)
     if (ok) {
 #pragma unroll
@@ -525,11 +548,14 @@ attn_bwd_dq3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_qtm_full);
     }
+    FMSB_TRACE3(trc, 12);
     for (int j = 0; j < nblk && ok; ++j) {
       const int k0 = (kb_lo + j) * B3_T;
       const bool need_mask = !(q0 >= k0 + B3_T - 1 && ds_last <= k0) || !row_ok;
+      FMSB_TRACE3(trc, 64 + 8 * j + 0);
       if (!mbar_wait(bar_s_full, j & 1, p.status, kTimeoutEpilogue)) { ok = false; break; }
       tc_fence_after();
+      FMSB_TRACE3(trc, 64 + 8 * j + 1);
       uint32_t pk[32];
       {
         uint32_t rs0[32], rs1[32];
@@ -541,10 +567,10 @@ attn_bwd_dq3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (lane == 0) mbar_arrive(bar_sa_done);
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float p0 = exp2f(__uint_as_float(rs0[i]) * sl2 - lse2);
-          float p1 = exp2f(__uint_as_float(rs0[i + 1]) * sl2 - lse2);
-          float p2 = exp2f(__uint_as_float(rs1[i]) * sl2 - lse2);
-          float p3 = exp2f(__uint_as_float(rs1[i + 1]) * sl2 - lse2);
+          float p0 = fast_exp2(__uint_as_float(rs0[i]) * sl2 - lse2);
+          float p1 = fast_exp2(__uint_as_float(rs0[i + 1]) * sl2 - lse2);
+          float p2 = fast_exp2(__uint_as_float(rs1[i]) * sl2 - lse2);
+          float p3 = fast_exp2(__uint_as_float(rs1[i + 1]) * sl2 - lse2);
           if (need_mask) {
             const int kk = k0 + c0 + i;
             if (!(row_ok && kk >= ds && kk <= t)) p0 = 0.f;
@@ -552,12 +578,14 @@ attn_bwd_dq3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             if (!(row_ok && kk + 32 >= ds && kk + 32 <= t)) p2 = 0.f;
             if (!(row_ok && kk + 33 >= ds && kk + 33 <= t)) p3 = 0.f;
           }
-          pk[i / 2] = b3_pack2(p0, p1, p.fmt);
-          pk[16 + i / 2] = b3_pack2(p2, p3, p.fmt);
+          pk[i / 2] = b3_pack2(p0, p1, FMT);
+          pk[16 + i / 2] = b3_pack2(p2, p3, FMT);
         }
       }
+      FMSB_TRACE3(trc, 64 + 8 * j + 2);
       if (!mbar_wait(bar_dp_full, j & 1, p.status, kTimeoutEpilogue)) { ok = false; break; }
       tc_fence_after();
+      FMSB_TRACE3(trc, 64 + 8 * j + 3);
       uint32_t dk[32];
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
@@ -567,8 +595,8 @@ attn_bwd_dq3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           float p0, p1;
-          b3_unpack2(pk[c * 16 + i / 2], p.fmt, p0, p1);
-          dk[c * 16 + i / 2] = b3_pack2(p0 * (__uint_as_float(rp[i]) - dlt), p1 * (__uint_as_float(rp[i + 1]) - dlt), p.fmt);
+          b3_unpack2(pk[c * 16 + i / 2], FMT, p0, p1);
+          dk[c * 16 + i / 2] = b3_pack2(p0 * (__uint_as_float(rp[i]) - dlt), p1 * (__uint_as_float(rp[i + 1]) - dlt), FMT);
         }
       }
       tmem_st_32x32(tdP + lane_addr + c0, dk);
@@ -576,9 +604,12 @@ attn_bwd_dq3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_pb_full);
+      FMSB_TRACE3(trc, 64 + 8 * j + 4);
     }
+    FMSB_TRACE3(trc, 13);
     if (ok && mbar_wait(bar_acc_done, 0, p.status, kTimeoutEpilogue)) {
       tc_fence_after();
+      FMSB_TRACE3(trc, 14);
 #pragma unroll 1
       for (int c = 0; c < D / 64; ++c) {
         const int col = chalf * (D / 2) + c * 32;
@@ -587,7 +618,7 @@ attn_bwd_dq3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tmem_ld_wait();
         if (row_ok)
           b3_store_row_chunk(reinterpret_cast<uint16_t*>(p.dq) + (long long)t * p.lddq + head * D + col, r, p.scale,
-                             p.fmt);
+                             FMT);
       }
     }
   }
@@ -603,6 +634,13 @@ attn_bwd_dq3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 }  // namespace fmsb
 
 using namespace fmsb;
+
+#ifdef FMSB_TRACE
+extern "C" int fmsb_attn_trace3_read(long long* host, int n) {
+  if (n > 8192) n = 8192;
+  return (int)cudaMemcpyFromSymbol(host, fmsb::g_trace3, sizeof(long long) * n);
+}
+#endif
 
 static int b3_make_maps(CUtensorMap* tq, CUtensorMap* tk, CUtensorMap* tv, CUtensorMap* tdo, const void* q,
                         long long ldq, const void* k, long long ldk, const void* v, long long ldv, const void* dout,
@@ -637,15 +675,20 @@ extern "C" int fmsb_attn_bwd_dq3(const void* q, long long ldq, const void* k, lo
   p.doc_start = doc_start; p.doc_end = doc_end; p.lse = lse; p.delta = delta;
   p.dq = dq; p.lddq = lddq; p.fmt = fmt; p.status = status;
   dim3 grid((T + B3_T - 1) / B3_T, nh);
-  if (d == 128) {
-    static bool cfg = false;
-    if (!cfg) { if ((rc = b3_set_smem(attn_bwd_dq3_kernel<128>, AttnBwd3Cfg<128>::kSmemBytes))) return rc; cfg = true; }
-    attn_bwd_dq3_kernel<128><<<grid, 320, AttnBwd3Cfg<128>::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
-  } else {
-    static bool cfg = false;
-    if (!cfg) { if ((rc = b3_set_smem(attn_bwd_dq3_kernel<64>, AttnBwd3Cfg<64>::kSmemBytes))) return rc; cfg = true; }
-    attn_bwd_dq3_kernel<64><<<grid, 320, AttnBwd3Cfg<64>::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
-  }
+#define FMSB_B3(DD, FF)                                                                                          \
+  do {                                                                                                           \
+    static bool cfg = false;                                                                                     \
+    if (!cfg) {                                                                                                  \
+      if ((rc = b3_set_smem(attn_bwd_dq3_kernel<DD, FF>, AttnBwd3Cfg<DD>::kSmemBytes))) return rc;             \
+      cfg = true;                                                                                                \
+    }                                                                                                            \
+    attn_bwd_dq3_kernel<DD, FF><<<grid, 320, AttnBwd3Cfg<DD>::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);       \
+  } while (0)
+  if (d == 128 && fmt == 1) FMSB_B3(128, 1);
+  else if (d == 128) FMSB_B3(128, 0);
+  else if (fmt == 1) FMSB_B3(64, 1);
+  else FMSB_B3(64, 0);
+#undef FMSB_B3
   return (int)cudaGetLastError();
 }
 
@@ -665,14 +708,19 @@ extern "C" int fmsb_attn_bwd_dkv3(const void* q, long long ldq, const void* k, l
   p.doc_start = doc_start; p.doc_end = doc_end; p.lse = lse; p.delta = delta;
   p.dk = dk; p.lddk = lddk; p.dv = dv; p.lddv = lddv; p.fmt = fmt; p.status = status;
   dim3 grid((T + B3_T - 1) / B3_T, nkv);
-  if (d == 128) {
-    static bool cfg = false;
-    if (!cfg) { if ((rc = b3_set_smem(attn_bwd_dkv3_kernel<128>, AttnBwd3Cfg<128>::kSmemBytes))) return rc; cfg = true; }
-    attn_bwd_dkv3_kernel<128><<<grid, 320, AttnBwd3Cfg<128>::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
-  } else {
-    static bool cfg = false;
-    if (!cfg) { if ((rc = b3_set_smem(attn_bwd_dkv3_kernel<64>, AttnBwd3Cfg<64>::kSmemBytes))) return rc; cfg = true; }
-    attn_bwd_dkv3_kernel<64><<<grid, 320, AttnBwd3Cfg<64>::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
-  }
+#define FMSB_B3(DD, FF)                                                                                          \
+  do {                                                                                                           \
+    static bool cfg = false;                                                                                     \
+    if (!cfg) {                                                                                                  \
+      if ((rc = b3_set_smem(attn_bwd_dkv3_kernel<DD, FF>, AttnBwd3Cfg<DD>::kSmemBytes))) return rc;             \
+      cfg = true;                                                                                                \
+    }                                                                                                            \
+    attn_bwd_dkv3_kernel<DD, FF><<<grid, 320, AttnBwd3Cfg<DD>::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);       \
+  } while (0)
+  if (d == 128 && fmt == 1) FMSB_B3(128, 1);
+  else if (d == 128) FMSB_B3(128, 0);
+  else if (fmt == 1) FMSB_B3(64, 1);
+  else FMSB_B3(64, 0);
+#undef FMSB_B3
   return (int)cudaGetLastError();
 }

@@ -290,6 +290,13 @@ __host__ __device__ constexpr uint32_t make_idesc_f16(int m, int n, int fmt, int
 // ----------------------------------------------------------------------------------------
 // small numeric helpers
 // ----------------------------------------------------------------------------------------
+// 2^x on the special-function unit, one instruction (ex2.approx.ftz: about 2 ulp, flushes denormal results to 0,
+// which is what a softmax weight that small should be).  exp2f() without fast-math expands to a much longer sequence.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
