@@ -271,3 +271,32 @@ def gptq_unpack_zeros(qzeros: torch.Tensor, bits: int) -> torch.Tensor:
     shifts = torch.arange(0, 32, bits, device=qzeros.device, dtype=torch.int64)
     qz = qzeros.long() & 0xFFFFFFFF
     return ((qz[:, :, None] >> shifts[None, None, :]) & ((1 << bits) - 1)).reshape(qzeros.shape[0], -1)
+
+
+# ------------------------------------------------------------------ names the reference's fused-LoRA code uses
+def fast_dequantize(W, quant_state: "Quant4State | None" = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Dense view of a frozen base weight (fms_acceleration_foak/fused_ops/unsloth_lora/utils.py:86-141).
+
+    ``W`` is a ``Linear4bit`` module, or packed 4-bit data with its :class:`Quant4State`, or (no state) an
+    already dense tensor, which is returned untouched."""
+    if quant_state is None:
+        if hasattr(W, "quant_state"):
+            return dequantize_4bit(W.quant_state(), out=out)
+        return W
+    return dequantize_4bit(quant_state, out=out)
+
+
+def fast_gemv(x: torch.Tensor, W, quant_state: "Quant4State | None" = None, out: torch.Tensor | None = None):
+    """Inference product of a few rows with a 4-bit weight: ``x [..., in] -> [..., out]``
+    (fms_acceleration_foak/fused_ops/unsloth_lora/utils.py:144-206).  The packed weight is streamed once and
+    expanded inside the tcgen05 GEMM kernel; nothing dense is written to memory."""
+    from .gemm import FUSED_Q4_MAX_ROWS, gemm_q4_fused
+
+    qs = quant_state if quant_state is not None else W.quant_state()
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.shape[0] > FUSED_Q4_MAX_ROWS:
+        raise ValueError(f"fast_gemv is for at most {FUSED_Q4_MAX_ROWS} rows, got {x2.shape[0]}")
+    if x2.stride(1) != 1 or x2.stride(0) % 8:
+        x2 = x2.contiguous()
+    y = gemm_q4_fused(x2, qs, out=out)
+    return y.view(*x.shape[:-1], y.shape[-1])

@@ -168,3 +168,80 @@ def auto_dtype_from_config(config, quant_inference: bool = False) -> torch.dtype
     if dt in (torch.float16, torch.bfloat16):
         return dt
     return torch.float16
+
+
+EXPERT_INDEX_PLACEHOLDER = "{expert_index}"
+
+
+def get_moe_layer_modules(layer_modules: List[List[str]], num_experts: int) -> List[List[str]]:
+    """Expand every name that carries ``{expert_index}`` into one name per expert, keeping the grouping of the
+    per-layer quantisation order (fms_acceleration_peft/gptqmodel/utils/model.py:704-717)."""
+    out: List[List[str]] = []
+    for group in layer_modules:
+        expanded: List[str] = []
+        for name in group:
+            if EXPERT_INDEX_PLACEHOLDER in name:
+                expanded += [name.replace(EXPERT_INDEX_PLACEHOLDER, str(e)) for e in range(num_experts)]
+            else:
+                expanded.append(name)
+        out.append(expanded)
+    return out
+
+
+def simple_dispatch_model(model: nn.Module, device_map: Dict[str, str]) -> nn.Module:
+    """Place a model according to a device map (fms_acceleration_peft/gptqmodel/utils/model.py:407-448).
+
+    One GPU holds a whole 70B GPTQ model here, so only two kinds of map are meaningful: ``{"": device}`` moves
+    everything, and a per-module map moves each named sub-tree to its device and makes the module's forward
+    bring its inputs along.  Offload to "cpu"/"disk" with execution elsewhere is not provided."""
+    if "" in device_map:
+        model = model.to(torch.device(device_map[""]))
+        model.hf_device_map = dict(device_map)
+        return model
+    if any(d in ("cpu", "disk") for d in device_map.values()) and len(set(device_map.values())) > 1:
+        raise NotImplementedError("offloaded execution is not provided; map every module to one accelerator")
+    tied = find_tied_parameters(model)
+    for name, dev in device_map.items():
+        mod = get_module_by_name_suffix(model, name)
+        if mod is None:
+            raise KeyError(f"device_map names {name!r}, which the model does not have")
+        target = torch.device(dev)
+        mod.to(target)
+
+        def _pre(_m, args, kwargs, _t=target):
+            mv = lambda v: v.to(_t) if isinstance(v, torch.Tensor) else v  # noqa: E731
+            return tuple(mv(a) for a in args), {k: mv(v) for k, v in kwargs.items()}
+
+        mod.register_forward_pre_hook(_pre, with_kwargs=True)
+    retie_parameters(model, tied)
+    model.hf_device_map = dict(device_map)
+    return model
+
+
+def find_tied_parameters(model: nn.Module) -> List[List[str]]:
+    """Groups of parameter names that share one storage."""
+    seen: Dict[int, List[str]] = {}
+    for name, p in model.named_parameters(remove_duplicate=False):
+        seen.setdefault(id(p), []).append(name)
+    return [names for names in seen.values() if len(names) > 1]
+
+
+def retie_parameters(model: nn.Module, tied: List[List[str]]) -> None:
+    for names in tied:
+        src = recurse_getattr(model, names[0])
+        for other in names[1:]:
+            recurse_setattr(model, other, src)
+
+
+def verify_file_hash(path: str, expected: str) -> bool:
+    """``expected`` is ``"<algorithm>:<hex digest>"`` (md5, sha256 ...); the file is read in 1 MiB pieces."""
+    import hashlib
+
+    algo, _, digest = expected.partition(":")
+    if not digest or algo.lower() not in hashlib.algorithms_available:
+        raise ValueError(f"hash must look like 'sha256:<hex>', got {expected!r}")
+    h = hashlib.new(algo.lower())
+    with open(path, "rb") as fh:
+        for piece in iter(lambda: fh.read(1 << 20), b""):
+            h.update(piece)
+    return h.hexdigest() == digest.lower()

@@ -122,3 +122,63 @@ def test_quantize_save_load_tiny_llama(tmp_path):
     assert loaded.quantized and torch.allclose(loaded.model(ids).logits, q_logits, atol=5e-3)  # scales are stored in fp16
     with pytest.raises(EnvironmentError):
         wrapper.quantize(calib)
+
+
+def test_moe_layer_names_expand_per_expert():
+    from fms_acceleration_b200.plugins.peft.gptqmodel.utils.model import EXPERT_INDEX_PLACEHOLDER, get_moe_layer_modules
+
+    groups = [["self_attn.q_proj"], [f"moe.experts.{EXPERT_INDEX_PLACEHOLDER}.w1", "moe.gate"]]
+    out = get_moe_layer_modules(groups, 3)
+    assert out == [["self_attn.q_proj"], ["moe.experts.0.w1", "moe.experts.1.w1", "moe.experts.2.w1", "moe.gate"]]
+
+
+def test_simple_dispatch_and_hash(tmp_path):
+    from fms_acceleration_b200.plugins.peft.gptqmodel.utils.model import (find_tied_parameters, simple_dispatch_model,
+                                                                         verify_file_hash)
+    import hashlib
+
+    class Tiny(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.emb = torch.nn.Embedding(8, 4)
+            self.body = torch.nn.Linear(4, 4)
+            self.head = torch.nn.Linear(4, 8, bias=False)
+            self.head.weight = self.emb.weight
+
+        def forward(self, ids):
+            return self.head(self.body(self.emb(ids)))
+
+    m = Tiny()
+    assert find_tied_parameters(m) == [["emb.weight", "head.weight"]]
+    m = simple_dispatch_model(m, {"emb": "cpu", "body": "cpu", "head": "cpu"})
+    assert m.head.weight is m.emb.weight and m.hf_device_map["body"] == "cpu"
+    assert m(torch.tensor([[1, 2]])).shape == (1, 2, 8)
+    m2 = simple_dispatch_model(Tiny(), {"": "cpu"})
+    assert m2.hf_device_map == {"": "cpu"}
+    f = tmp_path / "blob.bin"
+    f.write_bytes(b"abc" * 1000)
+    assert verify_file_hash(str(f), "sha256:" + hashlib.sha256(b"abc" * 1000).hexdigest())
+    assert not verify_file_hash(str(f), "md5:" + "0" * 32)
+
+
+def test_gptq_lora_model_never_merges():
+    from fms_acceleration_b200.nn.lora import LoraConfig
+    from fms_acceleration_b200.plugins.peft.gptqmodel.utils.peft import (PEFT_TYPE_TO_MODEL_MAPPING, GPTQLoraLinear,
+                                                                        GPTQLoraModel, get_gptq_peft_model,
+                                                                        hijack_peft_mappings)
+
+    class Block(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.q_proj = QuantLinear(4, 32, 32, 16, bias=False)
+            self.lm_head = torch.nn.Linear(16, 8)
+
+    before = PEFT_TYPE_TO_MODEL_MAPPING["LORA"]
+    with hijack_peft_mappings():
+        assert PEFT_TYPE_TO_MODEL_MAPPING["LORA"] is GPTQLoraModel
+    assert PEFT_TYPE_TO_MODEL_MAPPING["LORA"] is before
+    pm = get_gptq_peft_model(Block(), LoraConfig(r=4, lora_alpha=8, target_modules=None), auto_find_all_linears=True)
+    assert isinstance(pm, GPTQLoraModel)
+    assert isinstance(pm.base_model.model.q_proj, GPTQLoraLinear)
+    with pytest.raises(NotImplementedError):
+        pm.merge_and_unload()

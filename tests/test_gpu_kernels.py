@@ -284,3 +284,19 @@ def test_linear4bit_few_rows_uses_the_fused_kernel():
         L4.FUSED_Q4_MAX_ROWS = saved
     assert (y.float() - y2.float()).abs().max() <= 1e-2 * y2.float().abs().max() + 1e-3
     assert (gx.float() - x.grad.float()).abs().max() <= 2e-2 * x.grad.float().abs().max() + 1e-3
+
+
+def test_fast_gemv_matches_dequantised_product():
+    from fms_acceleration_b200.nn import Linear4bit
+    from fms_acceleration_b200.ops.quant import fast_dequantize, fast_gemv
+
+    torch.manual_seed(5)
+    lin = torch.nn.Linear(1024, 768, bias=False, device=DEV, dtype=torch.bfloat16)
+    q = Linear4bit.from_linear(lin, "nf4", 64, torch.bfloat16)
+    x = (torch.randn(1, 3, 1024, device=DEV) * 0.5).bfloat16()
+    y = fast_gemv(x, q)
+    NV.check_status()
+    w = fast_dequantize(q)
+    ref = x.float() @ w.float().t()
+    assert y.shape == (1, 3, 768)
+    assert (y.float() - ref).abs().max() <= 1e-2 * ref.abs().max() + 1e-3
