@@ -19,7 +19,6 @@ import statistics
 import subprocess
 import sys
 import tempfile
-import time
 
 REPO = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, REPO)
@@ -231,16 +230,18 @@ def run_config(name: str, args, ctx) -> dict:
 
     # ---- end-to-end region: pinned host batch -> device every step, loss read back every step
     h2d = sum(v.numel() * v.element_size() for v in host_batches[0].values())
+    e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
-    t0 = time.perf_counter()
+    e_start.record()
     last = 0.0
     for i in range(args.steps):
         loss = trainer.train_step(host_batches[i % n_batches])
         last = float(loss.item())
+    e_end.record()
     barrier()
-    e2e_s = time.perf_counter() - t0
+    e2e_ms_local = e_start.elapsed_time(e_end)
 
-    t = torch.tensor([ms, e2e_s * 1e3], device=dev, dtype=torch.float64)
+    t = torch.tensor([ms, e2e_ms_local], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_ms = float(t[0]), float(t[1])

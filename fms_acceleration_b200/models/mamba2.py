@@ -43,6 +43,23 @@ def _aligned(t: torch.Tensor) -> torch.Tensor:
     return t.contiguous()
 
 
+class _SplitCols(torch.autograd.Function):
+    """Column blocks of a 2-D tensor as views.  The backward is ONE concatenation of the block gradients; the
+    stock slicing backward zero-fills a full-width tensor per block and then adds them up."""
+
+    @staticmethod
+    def forward(ctx, t, *sizes):
+        ctx.sizes, ctx.rows, ctx.meta = sizes, t.shape[0], (t.dtype, t.device)
+        return tuple(t.split(list(sizes), dim=1))
+
+    @staticmethod
+    def backward(ctx, *grads):
+        dtype, dev = ctx.meta
+        parts = [g if g is not None else torch.zeros(ctx.rows, n, dtype=dtype, device=dev)
+                 for g, n in zip(grads, ctx.sizes)]
+        return (torch.cat(parts, dim=1),) + (None,) * len(ctx.sizes)
+
+
 def _linear(x, lin: nn.Linear):
     if (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and lin.bias is None
             and lin.in_features % 8 == 0 and lin.out_features % 8 == 0):
@@ -80,16 +97,15 @@ class Mamba2Mixer(nn.Module):
         T = u.shape[0]
         zxbcdt = _linear(u, self.in_proj)
         di, gn = self.d_inner, self.ngroups * self.d_state
-        z = zxbcdt[:, :di]
-        xBC = zxbcdt[:, di: di + self.conv_dim]
-        dt_raw = zxbcdt[:, di + self.conv_dim:]
+        z, xBC, dt_raw = _SplitCols.apply(zxbcdt, di, self.conv_dim, zxbcdt.shape[1] - di - self.conv_dim)
         w = self.conv1d.weight.squeeze(1)
         halo = self.cp.exchange_halo(xBC, self.d_conv - 1, self.layer_idx) if self.cp is not None else None
         xBC = MB.causal_conv1d(_aligned(xBC), w.to(xBC.dtype),
                                None if self.conv1d.bias is None else self.conv1d.bias.to(xBC.dtype), halo, seq_start, seq_end)
-        x = xBC[:, :di].reshape(T, self.nheads, self.headdim)
-        B = xBC[:, di: di + gn].reshape(T, self.ngroups, self.d_state)
-        C = xBC[:, di + gn:].reshape(T, self.ngroups, self.d_state)
+        xs, Bs, Cs = _SplitCols.apply(xBC, di, gn, gn)
+        x = xs.reshape(T, self.nheads, self.headdim)
+        B = Bs.reshape(T, self.ngroups, self.d_state)
+        C = Cs.reshape(T, self.ngroups, self.d_state)
         dt = F.softplus(dt_raw.float() + self.dt_bias.float())
         A = -torch.exp(self.A_log.float())
         Q = min(self.chunk_size, T)

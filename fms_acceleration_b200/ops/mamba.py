@@ -1,8 +1,9 @@
 """Mamba2 operators: causal conv1d + SiLU and the chunked state-space-duality (SSD) scan, forward and backward.
 
 GEMM-shaped work (C.B^T, G.X, chunk states, inter-chunk outputs and all their gradients) runs as uniform batched
-tcgen05 GEMMs (``fmsb_batched_gemm``); the recurrence over chunks, the conv and the decay/mask construction are
-CUDA kernels in ``csrc/mamba.cu``; the remaining element-wise glue is PyTorch.  The scan takes an initial state and
+tcgen05 GEMMs (``fmsb_batched_gemm``); the recurrence over chunks and the conv are CUDA kernels in
+``csrc/mamba.cu``; every pass over a [chunks, heads, Q, Q] or [T, heads, P] tensor between the GEMMs is a kernel of
+``csrc/mamba_scan.cu``; PyTorch only handles the [T, heads]-sized decay bookkeeping.  The scan takes an initial state and
 returns the final state, which is the hook context parallelism uses (``parallel/context_parallel.py``).
 
 Layouts: x [T, nh, P]; dt [T, nh] (after softplus, fp32); A [nh] (negative); B, C [T, G, N]; D [nh];
@@ -19,9 +20,15 @@ from .. import _native as NV
 from .gemm import batched_gemm
 
 P_, I_, L_, F_ = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
-NV.declare("fmsb_conv1d_fwd", [P_, L_, P_, P_, P_, P_, P_, L_, P_, I_, I_, I_, I_, P_])
-NV.declare("fmsb_conv1d_bwd", [P_, L_, P_, P_, P_, P_, P_, L_, P_, P_, I_, I_, I_, I_, P_])
-NV.declare("fmsb_ssd_make_g", [P_, P_, P_, P_, I_, I_, I_, I_, I_, P_])
+NV.declare("fmsb_conv1d_fwd", [P_, L_, P_, P_, P_, P_, P_, L_, I_, I_, I_, I_, P_])
+NV.declare("fmsb_conv1d_bwd", [P_, L_, P_, L_, P_, P_, P_, P_, P_, L_, P_, P_, P_, I_, I_, I_, I_, P_])
+NV.declare("fmsb_ssd_make_g2", [P_, P_, P_, P_, I_, I_, I_, I_, I_, P_])
+NV.declare("fmsb_ssd_dcb", [P_, P_, P_, P_, I_, I_, I_, I_, I_, P_])
+NV.declare("fmsb_ssd_rowscale", [P_, P_, P_, L_, I_, I_, P_])
+NV.declare("fmsb_ssd_fwd_combine", [P_, P_, P_, P_, P_, P_, L_, I_, I_, I_, P_])
+NV.declare("fmsb_ssd_addscaled", [P_, P_, P_, P_, L_, I_, I_, P_])
+NV.declare("fmsb_ssd_rowdot", [P_, P_, P_, P_, L_, I_, I_, P_])
+NV.declare("fmsb_ssd_bwd_combine", [P_, P_, P_, P_, P_, P_, P_, P_, P_, P_, P_, L_, I_, I_, I_, P_])
 NV.declare("fmsb_ssd_state_fwd", [P_, P_, P_, P_, P_, I_, I_, I_, I_, P_])
 NV.declare("fmsb_ssd_state_bwd", [P_, P_, P_, P_, P_, P_, P_, I_, I_, I_, I_, P_])
 
@@ -61,48 +68,49 @@ def conv1d_ref(x, w, bias, halo=None, seq_start=None):
 
 
 # ------------------------------------------------------------------------------------------------ conv1d
+def _vec_rows(t):
+    """Rows with unit stride, a row step that is a multiple of 8 elements and a 16-byte aligned base."""
+    if t.stride(1) == 1 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0:
+        return t
+    return t.contiguous()
+
+
 class _CausalConv1d(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, bias, halo, seq_start, seq_end):
         T, Cc = x.shape
         K = w.shape[1]
+        if Cc % 8 != 0 or K != 4:
+            raise ValueError("the conv kernel needs 4 taps and a channel count that is a multiple of 8")
+        x = _vec_rows(x)
         y = torch.empty(T, Cc, dtype=x.dtype, device=x.device)
-        pre = torch.empty(T, Cc, dtype=x.dtype, device=x.device)
         wc = w.contiguous()
-        rc = NV.lib().fmsb_conv1d_fwd(x.data_ptr(), x.stride(0), wc.data_ptr(), NV.ptr(bias), NV.ptr(halo),
-                                      NV.ptr(seq_start), y.data_ptr(), y.stride(0), pre.data_ptr(), T, Cc, K,
-                                      NV.dtype_code(x.dtype), NV.stream_ptr())
+        bc = None if bias is None else bias.contiguous()
+        hc = None if halo is None else halo.contiguous()
+        rc = NV.lib().fmsb_conv1d_fwd(x.data_ptr(), x.stride(0), wc.data_ptr(), NV.ptr(bc), NV.ptr(hc),
+                                      NV.ptr(seq_start), y.data_ptr(), y.stride(0), T, Cc, K, NV.dtype_code(x.dtype),
+                                      NV.stream_ptr())
         NV.check(rc, "fmsb_conv1d_fwd")
-        ctx.save_for_backward(x, wc, pre, halo, seq_start, seq_end)
-        ctx.has_bias = bias is not None
+        ctx.save_for_backward(x, wc, bc, hc, seq_start)
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        x, w, pre, halo, seq_start, seq_end = ctx.saved_tensors
+        x, w, bias, halo, seq_start = ctx.saved_tensors
         T, Cc = x.shape
         K = w.shape[1]
-        dy = dy if dy.stride(1) == 1 else dy.contiguous()
+        dy = _vec_rows(dy)
         dx = torch.empty(T, Cc, dtype=x.dtype, device=x.device)
-        dpre = torch.empty(T, Cc, dtype=torch.float32, device=x.device)
         dhalo = torch.empty(K - 1, Cc, dtype=x.dtype, device=x.device) if halo is not None else None
-        rc = NV.lib().fmsb_conv1d_bwd(dy.data_ptr(), dy.stride(0), pre.data_ptr(), w.data_ptr(), NV.ptr(seq_start),
-                                      NV.ptr(seq_end), dx.data_ptr(), dx.stride(0), dpre.data_ptr(), NV.ptr(dhalo), T, Cc,
-                                      K, NV.dtype_code(x.dtype), NV.stream_ptr())
+        # tap and bias gradients are accumulated by the kernel: dw[c, j] = sum_t dpre[t, c] * xin[t - (K-1) + j, c]
+        dwb = torch.zeros(Cc * (K + 1), dtype=torch.float32, device=x.device)
+        dw32, db32 = dwb[: Cc * K].view(Cc, K), dwb[Cc * K:]
+        rc = NV.lib().fmsb_conv1d_bwd(dy.data_ptr(), dy.stride(0), x.data_ptr(), x.stride(0), w.data_ptr(), NV.ptr(bias),
+                                      NV.ptr(halo), NV.ptr(seq_start), dx.data_ptr(), dx.stride(0), NV.ptr(dhalo),
+                                      dw32.data_ptr(), db32.data_ptr() if bias is not None else None, T, Cc, K,
+                                      NV.dtype_code(x.dtype), NV.stream_ptr())
         NV.check(rc, "fmsb_conv1d_bwd")
-        # tap gradients: dw[c, j] = sum_t dpre[t, c] * xin[t - (K-1) + j, c]
-        pad = halo.float() if halo is not None else torch.zeros(K - 1, Cc, dtype=torch.float32, device=x.device)
-        xp = torch.cat([pad, x.float()], 0)
-        dws = []
-        for j in range(K):
-            col = xp[j: j + T]
-            if seq_start is not None:
-                src = torch.arange(T, device=x.device) - (K - 1) + j
-                col = torch.where((src >= seq_start.long())[:, None], col, torch.zeros_like(col))
-            dws.append((dpre * col).sum(0))
-        dw = torch.stack(dws, 1).to(w.dtype)
-        db = dpre.sum(0).to(w.dtype) if ctx.has_bias else None
-        return dx, dw, db, dhalo, None, None
+        return dx, dw32.to(w.dtype), (db32.to(w.dtype) if bias is not None else None), dhalo, None, None
 
 
 def causal_conv1d(x, w, bias=None, halo=None, seq_start=None, seq_end=None):
@@ -113,15 +121,34 @@ def causal_conv1d(x, w, bias=None, halo=None, seq_start=None, seq_end=None):
 
 
 # ------------------------------------------------------------------------------------------------ SSD scan
-def _make_g(cb, L, dt, nc, nh, G, Q):
+def _rows16(t2):
+    """The [T, heads*P] kernels use 16-byte accesses: make the base address fit (row lengths already do)."""
+    return t2 if t2.data_ptr() % 16 == 0 and t2.is_contiguous() else t2.contiguous().clone()
+
+
+def _chunk_major(v, nc, Q, nh):
+    """[T, nh] fp32 -> [nc, nh, Q] contiguous (unit stride along the chunk for the Q x Q kernels)."""
+    return v.view(nc, Q, nh).transpose(1, 2).contiguous()
+
+
+def _make_g(cb, Lt, dtt, nc, nh, G, Q):
     g = torch.empty(nc * nh * Q, Q, dtype=cb.dtype, device=cb.device)
-    rc = NV.lib().fmsb_ssd_make_g(cb.data_ptr(), L.data_ptr(), dt.data_ptr(), g.data_ptr(), nc, nh, G, Q,
-                                  NV.dtype_code(cb.dtype), NV.stream_ptr())
-    NV.check(rc, "fmsb_ssd_make_g")
+    rc = NV.lib().fmsb_ssd_make_g2(cb.data_ptr(), Lt.data_ptr(), dtt.data_ptr(), g.data_ptr(), nc, nh, G, Q,
+                                   NV.dtype_code(cb.dtype), NV.stream_ptr())
+    NV.check(rc, "fmsb_ssd_make_g2")
     return g
 
 
-SLAB_BYTES = 256 << 20  # bound on each [chunks, heads, Q, Q] fp32 temporary of the scan
+def _rowscale(x2, w, nh, P):
+    """x2 [T, nh*P] (16-bit) times w [T, nh] (fp32), rounded back to 16 bits."""
+    out = torch.empty_like(x2)
+    rc = NV.lib().fmsb_ssd_rowscale(x2.data_ptr(), w.data_ptr(), out.data_ptr(), x2.shape[0] * nh, P,
+                                    NV.dtype_code(x2.dtype), NV.stream_ptr())
+    NV.check(rc, "fmsb_ssd_rowscale")
+    return out
+
+
+SLAB_BYTES = 1 << 30  # bound on each [chunks, heads, Q, Q] fp32 temporary of the scan
 
 
 def _slabs(nc: int, nh: int, Q: int):
@@ -136,14 +163,16 @@ class _SSDScan(torch.autograd.Function):
         T, nh, P = x.shape
         G, N = B.shape[1], B.shape[2]
         assert T % Q == 0, "sequence length must be a multiple of the chunk size"
+        assert Q % 32 == 0 and P % 8 == 0, "chunk size must be a multiple of 32 and the head dimension of 8"
         nc, hpg = T // Q, nh // G
         dev, dtp = x.device, x.dtype
-        x2 = x.reshape(T, nh * P)
+        x2 = _rows16(x.reshape(T, nh * P))
         B2, C2 = B.reshape(T, G * N), C.reshape(T, G * N)
         dt = dt.float().contiguous()
         a = dt * A.float()[None, :]
         L = a.view(nc, Q, nh).cumsum(1).reshape(T, nh).contiguous()
         Ltot = L.view(nc, Q, nh)[:, -1, :].contiguous()                     # [nc, nh]
+        Lt, dtt = _chunk_major(L, nc, Q, nh), _chunk_major(dt, nc, Q, nh)
         # C.B^T per chunk and group
         cb = batched_gemm(C2, B2, M=Q, N=Q, K=N, n_batch=nc * G, n_inner=G, a_off=(Q, 0, N, 1), b_off=(Q, 0, N, 1),
                           d_off=(G * Q, Q, 0), out_rows=nc * G * Q, out_cols=Q)
@@ -151,31 +180,38 @@ class _SSDScan(torch.autograd.Function):
         y_intra = torch.empty(T, nh * P, dtype=torch.float32, device=dev)
         for c0, c1 in _slabs(nc, nh, Q):
             n = c1 - c0
-            g = _make_g(cb[c0 * G * Q: c1 * G * Q], L[c0 * Q: c1 * Q], dt[c0 * Q: c1 * Q], n, nh, G, Q)  # [n*nh*Q, Q]
+            g = _make_g(cb[c0 * G * Q: c1 * G * Q], Lt[c0:c1], dtt[c0:c1], n, nh, G, Q)     # [n*nh*Q, Q]
             batched_gemm(g, x2[c0 * Q: c1 * Q], M=Q, N=P, K=Q, n_batch=n * nh, n_inner=nh, a_off=(nh * Q, Q, 0, 1),
                          b_off=(Q, 0, P, 1), d_off=(Q, 0, P), b_mn=True, out=y_intra[c0 * Q: c1 * Q])
             del g
         # chunk states S[c,h] [P, N] = (x w)^T B,  w = exp(Ltot - L) dt
-        wgt = (torch.exp(Ltot.view(nc, 1, nh) - L.view(nc, Q, nh)) * dt.view(nc, Q, nh)).reshape(T, nh)
-        xw = (x.float() * wgt[:, :, None]).to(dtp).reshape(T, nh * P)
+        wgt = (torch.exp(Ltot.view(nc, 1, nh) - L.view(nc, Q, nh)) * dt.view(nc, Q, nh)).reshape(T, nh).contiguous()
+        xw = _rowscale(x2, wgt, nh, P)
         S = batched_gemm(xw, B2, M=P, N=N, K=Q, n_batch=nc * nh, n_inner=nh, a_off=(Q, 0, P, 1), b_off=(Q, 0, N, hpg),
                          d_off=(nh * P, P, 0), a_mn=True, b_mn=True, out_rows=nc * nh * P, out_cols=N,
                          out_dtype=torch.float32)
+        del xw
         hprev = torch.empty(nc * nh * P, N, dtype=dtp, device=dev)
         hT = torch.empty(nh, P, N, dtype=torch.float32, device=dev)
         h0c = None if h0 is None else h0.float().contiguous()
         rc = NV.lib().fmsb_ssd_state_fwd(S.data_ptr(), Ltot.data_ptr(), NV.ptr(h0c), hprev.data_ptr(), hT.data_ptr(), nc,
                                          nh, P * N, NV.dtype_code(dtp), NV.stream_ptr())
         NV.check(rc, "fmsb_ssd_state_fwd")
+        del S
         # inter-chunk: C_t . Hprev[c,h]  (B operand [P rows, N cols], contraction over N)
         y_inter = batched_gemm(C2, hprev, M=Q, N=P, K=N, n_batch=nc * nh, n_inner=nh, a_off=(Q, 0, N, hpg),
                                b_off=(nh * P, P, 0, 1), d_off=(Q, 0, P), out_rows=T, out_cols=nh * P,
                                out_dtype=torch.float32)
-        eL = torch.exp(L)
-        y = y_intra.view(T, nh, P) + eL[:, :, None] * y_inter.view(T, nh, P) + D.float()[None, :, None] * x.float()
+        # y = y_intra + exp(L) y_inter + D x
+        y = torch.empty(T, nh, P, dtype=dtp, device=dev)
+        Df = D.float().contiguous()
+        rc = NV.lib().fmsb_ssd_fwd_combine(y_intra.data_ptr(), y_inter.data_ptr(), x2.data_ptr(), L.data_ptr(),
+                                           Df.data_ptr(), y.data_ptr(), T * nh, P, nh, NV.dtype_code(dtp),
+                                           NV.stream_ptr())
+        NV.check(rc, "fmsb_ssd_fwd_combine")
         ctx.save_for_backward(x, dt, A, B, C, D, L, Ltot, cb, hprev, wgt)
         ctx.meta = (Q, h0 is not None)
-        return y.to(dtp), hT
+        return y, hT
 
     @staticmethod
     def backward(ctx, dy, dhT):
@@ -185,19 +221,16 @@ class _SSDScan(torch.autograd.Function):
         G, N = B.shape[1], B.shape[2]
         nc, hpg = T // Q, nh // G
         dev, dtp = x.device, x.dtype
-        x2 = x.reshape(T, nh * P)
+        code = NV.dtype_code(dtp)
+        x2 = _rows16(x.reshape(T, nh * P))
         B2, C2 = B.reshape(T, G * N), C.reshape(T, G * N)
-        dyf = dy.float()
-        dy2 = dy.contiguous().reshape(T, nh * P)
-        eL = torch.exp(L)
-        dD = (dyf * x.float()).sum((0, 2))
-        dx = D.float()[None, :, None] * dyf
-        # ---- inter-chunk term  y += eL * (C . Hprev)
-        dyi = (dyf * eL[:, :, None]).to(dtp).reshape(T, nh * P)
+        dy2 = _rows16(dy.reshape(T, nh * P))
+        Lt, dtt = _chunk_major(L, nc, Q, nh), _chunk_major(dt, nc, Q, nh)
+        # ---- inter-chunk term  y += exp(L) * (C . Hprev)
+        dyi = _rowscale(dy2, torch.exp(L), nh, P)
         y_inter = batched_gemm(C2, hprev, M=Q, N=P, K=N, n_batch=nc * nh, n_inner=nh, a_off=(Q, 0, N, hpg),
                                b_off=(nh * P, P, 0, 1), d_off=(Q, 0, P), out_rows=T, out_cols=nh * P,
                                out_dtype=torch.float32)
-        dL = (dyf * y_inter.view(T, nh, P)).sum(-1) * eL
         # dC_inter[c, g] [Q, N] = dyi[c, heads of g] [Q, hpg*P] . Hprev[c, heads of g] [(h,p), N]
         dC = batched_gemm(dyi, hprev, M=Q, N=N, K=hpg * P, n_batch=nc * G, n_inner=G, a_off=(Q, 0, hpg * P, 1),
                           b_off=(nh * P, hpg * P, 0, 1), d_off=(Q, 0, N), b_mn=True, out_rows=T, out_cols=G * N,
@@ -206,73 +239,161 @@ class _SSDScan(torch.autograd.Function):
         dhp = batched_gemm(dyi, C2, M=P, N=N, K=Q, n_batch=nc * nh, n_inner=nh, a_off=(Q, 0, P, 1), b_off=(Q, 0, N, hpg),
                            d_off=(nh * P, P, 0), a_mn=True, b_mn=True, out_rows=nc * nh * P, out_cols=N,
                            out_dtype=torch.float32)
+        del dyi
         # ---- recurrence backward
-        dS = torch.empty(nc * nh * P, N, dtype=torch.float32, device=dev)
+        dS16 = torch.empty(nc * nh * P, N, dtype=dtp, device=dev)
         dh0 = torch.empty(nh, P, N, dtype=torch.float32, device=dev) if has_h0 else None
-        dLtot_part = torch.empty(nc, nh, P * N, dtype=torch.float32, device=dev)
+        dLtot = torch.zeros(nc, nh, dtype=torch.float32, device=dev)
         dhTc = None if dhT is None else dhT.float().contiguous()
-        rc = NV.lib().fmsb_ssd_state_bwd(dhp.data_ptr(), NV.ptr(dhTc), Ltot.data_ptr(), hprev.data_ptr(), dS.data_ptr(),
-                                         NV.ptr(dh0), dLtot_part.data_ptr(), nc, nh, P * N, NV.dtype_code(dtp),
+        rc = NV.lib().fmsb_ssd_state_bwd(dhp.data_ptr(), NV.ptr(dhTc), Ltot.data_ptr(), hprev.data_ptr(),
+                                         dS16.data_ptr(), NV.ptr(dh0), dLtot.data_ptr(), nc, nh, P * N, code,
                                          NV.stream_ptr())
         NV.check(rc, "fmsb_ssd_state_bwd")
-        dLtot = dLtot_part.sum(-1)                                            # [nc, nh]
+        del dhp
         # ---- chunk state  S = (x w)^T B
-        dS16 = dS.to(dtp)
-        xw = (x.float() * wgt[:, :, None]).to(dtp).reshape(T, nh * P)
+        xw = _rowscale(x2, wgt, nh, P)
         # dXw[c,h] [Q, P] = B[c] [Q, N] . dS[c,h]^T
         dxw = batched_gemm(B2, dS16, M=Q, N=P, K=N, n_batch=nc * nh, n_inner=nh, a_off=(Q, 0, N, hpg),
                            b_off=(nh * P, P, 0, 1), d_off=(Q, 0, P), out_rows=T, out_cols=nh * P,
-                           out_dtype=torch.float32).view(T, nh, P)
+                           out_dtype=torch.float32)
         # dB_state[c, g] [Q, N] = xw[c, heads of g] [Q, hpg*P] . dS[c, heads of g] [(h,p), N]
         dB = batched_gemm(xw, dS16, M=Q, N=N, K=hpg * P, n_batch=nc * G, n_inner=G, a_off=(Q, 0, hpg * P, 1),
                           b_off=(nh * P, hpg * P, 0, 1), d_off=(Q, 0, N), b_mn=True, out_rows=T, out_cols=G * N,
                           out_dtype=torch.float32)
-        dx = dx + dxw * wgt[:, :, None]
-        dw = (dxw * x.float()).sum(-1)                                        # [T, nh]
-        dww = dw * wgt
-        dLtot = dLtot + dww.view(nc, Q, nh).sum(1)
-        dL = dL - dww
-        ddt = dww / dt
+        del xw, dS16
         # ---- intra-chunk term  y += G X,  G = CB o exp(L_t - L_s) dt_s (s <= t); slabs of chunks bound the
         # [chunks, heads, Q, Q] temporaries
-        mask = torch.tril(torch.ones(Q, Q, dtype=torch.bool, device=dev))
+        dx_intra = torch.empty(T, nh * P, dtype=torch.float32, device=dev)
+        y_intra = torch.empty(T, nh * P, dtype=torch.float32, device=dev)
         for c0, c1 in _slabs(nc, nh, Q):
             n = c1 - c0
             rows = slice(c0 * Q, c1 * Q)
-            g = _make_g(cb[c0 * G * Q: c1 * G * Q], L[rows], dt[rows], n, nh, G, Q)
-            dx_intra = batched_gemm(g, dy2[rows], M=Q, N=P, K=Q, n_batch=n * nh, n_inner=nh, a_off=(nh * Q, Q, 0, 1),
-                                    b_off=(Q, 0, P, 1), d_off=(Q, 0, P), a_mn=True, b_mn=True, out_rows=n * Q,
-                                    out_cols=nh * P, out_dtype=torch.float32)
-            dx[rows] += dx_intra.view(n * Q, nh, P)
+            g = _make_g(cb[c0 * G * Q: c1 * G * Q], Lt[c0:c1], dtt[c0:c1], n, nh, G, Q)
+            batched_gemm(g, dy2[rows], M=Q, N=P, K=Q, n_batch=n * nh, n_inner=nh, a_off=(nh * Q, Q, 0, 1),
+                         b_off=(Q, 0, P, 1), d_off=(Q, 0, P), a_mn=True, b_mn=True, out=dx_intra[rows])
+            batched_gemm(g, x2[rows], M=Q, N=P, K=Q, n_batch=n * nh, n_inner=nh, a_off=(nh * Q, Q, 0, 1),
+                         b_off=(Q, 0, P, 1), d_off=(Q, 0, P), b_mn=True, out=y_intra[rows])
+            del g
             dG = batched_gemm(dy2[rows], x2[rows], M=Q, N=Q, K=P, n_batch=n * nh, n_inner=nh, a_off=(Q, 0, P, 1),
                               b_off=(Q, 0, P, 1), d_off=(nh * Q, Q, 0), out_rows=n * nh * Q, out_cols=Q,
-                              out_dtype=torch.float32).view(n, nh, Q, Q)
-            Wm = dG * g.view(n, nh, Q, Q).float()                             # dG o G
-            row = Wm.sum(-1)                                                  # [n, nh, Q] indexed by t
-            col = Wm.sum(-2)                                                  # indexed by s
-            del Wm, g
-            dL[rows] += (row - col).permute(0, 2, 1).reshape(n * Q, nh)
-            ddt[rows] += col.permute(0, 2, 1).reshape(n * Q, nh) / dt[rows]
-            # dCB[c, g] = sum_{h in g} dG o exp(L_t - L_s) dt_s mask
-            Lc = L[rows].view(n, Q, nh).permute(0, 2, 1)                      # [n, nh, Q]
-            dtc = dt[rows].view(n, Q, nh).permute(0, 2, 1)
-            decay = (torch.exp(Lc[..., :, None] - Lc[..., None, :]) * dtc[..., None, :]).masked_fill_(~mask, 0.0)
-            dcb16 = (dG * decay).view(n, G, hpg, Q, Q).sum(2).to(dtp).reshape(n * G * Q, Q)
-            del decay, dG
+                              out_dtype=torch.float32)
+            # dCB[c, g] = sum_{h in g} dG o exp(L_t - L_s) dt_s (s <= t)
+            dcb16 = torch.empty(n * G * Q, Q, dtype=dtp, device=dev)
+            rc = NV.lib().fmsb_ssd_dcb(dG.data_ptr(), Lt[c0:c1].data_ptr(), dtt[c0:c1].data_ptr(), dcb16.data_ptr(), n,
+                                       nh, G, Q, code, NV.stream_ptr())
+            NV.check(rc, "fmsb_ssd_dcb")
+            del dG
             dC[rows] += batched_gemm(dcb16, B2[rows], M=Q, N=N, K=Q, n_batch=n * G, n_inner=G, a_off=(G * Q, Q, 0, 1),
                                      b_off=(Q, 0, N, 1), d_off=(Q, 0, N), b_mn=True, out_rows=n * Q, out_cols=G * N,
                                      out_dtype=torch.float32)
             dB[rows] += batched_gemm(dcb16, C2[rows], M=Q, N=N, K=Q, n_batch=n * G, n_inner=G, a_off=(G * Q, Q, 0, 1),
                                      b_off=(Q, 0, N, 1), d_off=(Q, 0, N), a_mn=True, b_mn=True, out_rows=n * Q,
                                      out_cols=G * N, out_dtype=torch.float32)
+            del dcb16
+        # ---- dx and the per-(t, h) dot products, one pass over the [T, heads, P] tensors
+        dx = torch.empty(T, nh, P, dtype=dtp, device=dev)
+        red = torch.empty(5, T, nh, dtype=torch.float32, device=dev)
+        Df = D.float().contiguous()
+        rc = NV.lib().fmsb_ssd_bwd_combine(dy2.data_ptr(), x2.data_ptr(), y_inter.data_ptr(), dxw.data_ptr(),
+                                           dx_intra.data_ptr(), y_intra.data_ptr(), L.data_ptr(), wgt.data_ptr(),
+                                           Df.data_ptr(), dx.data_ptr(), red.data_ptr(), T * nh, P, nh, code,
+                                           NV.stream_ptr())
+        NV.check(rc, "fmsb_ssd_bwd_combine")
+        del y_inter, dxw, dx_intra, y_intra
+        dD = red[0].sum(0)
+        dww = red[2] * wgt                                                    # through w = exp(Ltot - L) dt
+        row, col = red[3], red[4]                                             # sums of dG o G over s / over t
+        dL = red[1] - dww + row - col
+        ddt = (dww + col) / dt
+        dLtot = dLtot + dww.view(nc, Q, nh).sum(1)
         # ---- through L = cumsum(dt A) within the chunk, Ltot = L[last]
         dLc = dL.view(nc, Q, nh).clone()
         dLc[:, -1, :] += dLtot
         da = torch.flip(torch.cumsum(torch.flip(dLc, [1]), 1), [1]).reshape(T, nh)
         ddt = ddt + da * A.float()[None, :]
         dA = (da * dt).sum(0)
-        return (dx.to(dtp), ddt.to(dt.dtype), dA.to(A.dtype), dB.view(T, G, N).to(B.dtype), dC.view(T, G, N).to(C.dtype),
+        return (dx, ddt.to(dt.dtype), dA.to(A.dtype), dB.view(T, G, N).to(B.dtype), dC.view(T, G, N).to(C.dtype),
                 dD.to(D.dtype), dh0, None)
+
+
+class _StateCorrection(torch.autograd.Function):
+    """y = y0 + exp(Lg) (C . H_in): what a state ``H_in [nh, P, N]`` entering the slice adds to the outputs of a
+    zero-initial-state scan ``y0 [T, nh, P]``, with ``Lg`` the cumulative ``dt*A`` from the start of the slice."""
+
+    @staticmethod
+    def forward(ctx, y0, h_in, dt, A, C, Q):
+        T, nh, P = y0.shape
+        G, N = C.shape[1], C.shape[2]
+        nc, hpg = T // Q, nh // G
+        dtp = y0.dtype
+        dt = dt.float().contiguous()
+        Lg = torch.cumsum(dt * A.float()[None, :], 0).contiguous()            # [T, nh]
+        hin16 = h_in.to(dtp).reshape(nh * P, N).contiguous()
+        C2 = C.reshape(T, G * N)
+        yc = _state_gemm(C2, hin16, T, Q, nh, P, N, hpg)
+        y02 = _rows16(y0.reshape(T, nh * P))
+        y = torch.empty(T, nh, P, dtype=dtp, device=y0.device)
+        rc = NV.lib().fmsb_ssd_addscaled(y02.data_ptr(), yc.data_ptr(), Lg.data_ptr(), y.data_ptr(), T * nh, P,
+                                         NV.dtype_code(dtp), NV.stream_ptr())
+        NV.check(rc, "fmsb_ssd_addscaled")
+        ctx.save_for_backward(hin16, dt, A, C, Lg)
+        ctx.meta = (Q, h_in.dtype)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        hin16, dt, A, C, Lg = ctx.saved_tensors
+        Q, h_dtype = ctx.meta
+        T, nh, P = dy.shape
+        G, N = C.shape[1], C.shape[2]
+        nc, hpg = T // Q, nh // G
+        dtp = dy.dtype
+        code = NV.dtype_code(dtp)
+        C2 = C.reshape(T, G * N)
+        dy2 = _rows16(dy.reshape(T, nh * P))
+        dyi = _rowscale(dy2, torch.exp(Lg), nh, P)
+        # dC[c, g] [Q, N] = dyi[c, heads of g] [Q, hpg*P] . H_in[heads of g] [(h,p), N]
+        dC = batched_gemm(dyi, hin16, M=Q, N=N, K=hpg * P, n_batch=nc * G, n_inner=G, a_off=(Q, 0, hpg * P, 1),
+                          b_off=(0, hpg * P, 0, 1), d_off=(Q, 0, N), b_mn=True, out_rows=T, out_cols=G * N,
+                          out_dtype=torch.float32)
+        # dH_in[h] [P, N] = dyi[:, h]^T C  (contraction over the T rows of the slice)
+        dh = batched_gemm(dyi, C2, M=P, N=N, K=T, n_batch=nh, n_inner=nh, a_off=(0, 0, P, 1), b_off=(0, 0, N, hpg),
+                          d_off=(0, P, 0), a_mn=True, b_mn=True, out_rows=nh * P, out_cols=N, out_dtype=torch.float32)
+        del dyi
+        # dLg[t, h] = exp(Lg) dy[t, h, :] . (C_t . H_in[h])
+        yc = _state_gemm(C2, hin16, T, Q, nh, P, N, hpg)
+        dLg = torch.empty(T, nh, dtype=torch.float32, device=dy.device)
+        rc = NV.lib().fmsb_ssd_rowdot(dy2.data_ptr(), yc.data_ptr(), Lg.data_ptr(), dLg.data_ptr(), T * nh, P, code,
+                                      NV.stream_ptr())
+        NV.check(rc, "fmsb_ssd_rowdot")
+        del yc
+        da = torch.flip(torch.cumsum(torch.flip(dLg, [0]), 0), [0])           # through Lg = cumsum(dt A)
+        ddt = da * A.float()[None, :]
+        dA = (da * dt).sum(0)
+        return dy, dh.view(nh, P, N).to(h_dtype), ddt, dA.to(A.dtype), dC.view(T, G, N).to(C.dtype), None
+
+
+def _state_gemm(C2, hin16, T, Q, nh, P, N, hpg):
+    """[T, nh*P] fp32: row t, head h = C_t . H_in[h]^T, as nc*nh products of [Q, N] x [N, P] on tcgen05."""
+    nc = T // Q
+    return batched_gemm(C2, hin16, M=Q, N=P, K=N, n_batch=nc * nh, n_inner=nh, a_off=(Q, 0, N, hpg),
+                        b_off=(0, P, 0, 1), d_off=(Q, 0, P), out_rows=T, out_cols=nh * P, out_dtype=torch.float32)
+
+
+def state_correction_ref(y0, h_in, dt, A, C):
+    """PyTorch statement of :class:`_StateCorrection` (oracle)."""
+    T, nh, P = y0.shape
+    G = C.shape[1]
+    Lg = torch.cumsum(dt.float() * A.float()[None, :], 0)
+    Ch = C.float().repeat_interleave(nh // G, 1)
+    return y0.float() + torch.exp(Lg)[:, :, None] * torch.einsum("thn,hpn->thp", Ch, h_in.float())
+
+
+def state_correction(y0, h_in, dt, A, C, chunk_size=256):
+    """Add the contribution of the state entering the slice to a zero-initial-state scan output."""
+    if not y0.is_cuda:
+        return state_correction_ref(y0, h_in, dt, A, C).to(y0.dtype)
+    return _StateCorrection.apply(y0, h_in, dt, A, C, chunk_size)
 
 
 def ssd_scan(x, dt, A, B, C, D, h0=None, chunk_size=256):

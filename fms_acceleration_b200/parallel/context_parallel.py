@@ -89,8 +89,7 @@ class ContextParallel:
         logP = (dt.float() * A.float()[None, :]).sum(0)                       # [nh]
         h_in = _StateExchange.apply(F_local, logP, self, layer)
         # the entering state only adds  exp(L_global(t)) * C_t . H_in  to every output row of the slice
-        corr = _state_correction(h_in, dt, A, C, x.shape, Q)
-        return (y0.float() + corr).to(x.dtype)
+        return MB.state_correction(y0, h_in, dt, A, C, Q)
 
     # ------------------------------------------------------------------ loss helpers
     def shift_labels(self, flat_labels: torch.Tensor) -> torch.Tensor:
@@ -104,15 +103,6 @@ class ContextParallel:
         n = mask.sum().float().reshape(1)
         dist.all_reduce(n, group=self.group)
         return n.clamp(min=1)
-
-
-def _state_correction(h_in, dt, A, C, xshape, Q):
-    """y_corr[t, h, :] = exp(sum_{s<=t} dt_s A) * C_t . H_in[h]   (contraction over the state dimension)."""
-    T, nh, P = xshape
-    G, N = C.shape[1], C.shape[2]
-    Lg = torch.cumsum(dt.float() * A.float()[None, :], 0)                     # [T, nh] decay from the slice start
-    Ch = C.float().repeat_interleave(nh // G, 1)                              # [T, nh, N]
-    return torch.exp(Lg)[:, :, None] * torch.einsum("thn,hpn->thp", Ch, h_in.float())
 
 
 class _StateExchange(torch.autograd.Function):

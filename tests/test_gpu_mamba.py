@@ -33,6 +33,28 @@ def test_conv1d_matches_reference():
     assert _rel(b.grad, br.grad) < 2e-2 and _rel(halo.grad, hr.grad) < 2e-2
 
 
+def test_conv1d_packed_sequences_do_not_leak():
+    """Three packed sequences: no tap reads across a boundary, forward and backward; fp16; no bias, no halo."""
+    torch.manual_seed(1)
+    T, Cc = 731, 264
+    bounds = [0, 130, 131, 600, T]
+    start = torch.empty(T, dtype=torch.int32)
+    for a, b in zip(bounds[:-1], bounds[1:]):
+        start[a:b] = a
+    start = start.to(DEV)
+    x = torch.randn(T, Cc, device=DEV).half().requires_grad_()
+    w = (torch.randn(Cc, 4, device=DEV) * 0.5).half().requires_grad_()
+    y = MB.causal_conv1d(x, w, None, None, start, None)
+    g = torch.randn_like(y)
+    y.backward(g)
+    NV.check_status()
+    xr, wr = (t.detach().float().requires_grad_() for t in (x, w))
+    yr = MB.conv1d_ref(xr, wr, None, None, start)
+    yr.backward(g.float())
+    assert _rel(y, yr) < 1e-2
+    assert _rel(x.grad, xr.grad) < 2e-2 and _rel(w.grad, wr.grad) < 2e-2
+
+
 @pytest.mark.parametrize("T,nh,P,G,N,Q,with_h0", [(256, 4, 64, 1, 128, 64, False), (512, 8, 64, 2, 64, 128, True),
                                                   (512, 4, 64, 1, 128, 256, True)])
 def test_ssd_scan_matches_recurrence(T, nh, P, G, N, Q, with_h0, monkeypatch):
@@ -88,3 +110,26 @@ def test_mamba2_model_matches_cpu_reference():
             # forward resolves; their exact gradients are covered by test_ssd_scan_matches_recurrence
             continue
         assert _rel(p.grad.cpu(), rg[n].grad) < 0.1, (n, _rel(p.grad.cpu(), rg[n].grad))
+
+
+def test_state_correction_matches_einsum():
+    """Entering-state correction of context parallelism (tcgen05 products + fused element-wise kernels) against the
+    einsum statement, forward and every gradient."""
+    torch.manual_seed(2)
+    T, nh, P, G, N, Q = 512, 8, 64, 2, 128, 128
+    y0 = (torch.randn(T, nh, P, device=DEV) * 0.5).bfloat16().requires_grad_()
+    h_in = (torch.randn(nh, P, N, device=DEV) * 0.3).requires_grad_()
+    dt = (torch.rand(T, nh, device=DEV) * 0.02 + 0.001).requires_grad_()
+    A = (-(torch.rand(nh, device=DEV) * 2 + 0.5)).requires_grad_()
+    C = (torch.randn(T, G, N, device=DEV) * 0.3).bfloat16().requires_grad_()
+    y = MB.state_correction(y0, h_in, dt, A, C, Q)
+    NV.check_status()
+    gy = torch.randn_like(y)
+    (y.float() * gy.float()).sum().backward()
+    NV.check_status()
+    ins = [t.detach().double().requires_grad_() for t in (y0, h_in, dt, A, C)]
+    yr = MB.state_correction_ref(*ins)
+    (yr * gy.double()).sum().backward()
+    assert _rel(y, yr) < 1e-2
+    for n, t, r in zip(["y0", "h_in", "dt", "A", "C"], (y0, h_in, dt, A, C), ins):
+        assert _rel(t.grad, r.grad) < 3e-2, (n, _rel(t.grad, r.grad))
