@@ -90,18 +90,23 @@ __device__ __forceinline__ void cv_load_row(const T* __restrict__ x, long long l
   }
 }
 
-constexpr int CONV_RT = 64;  // rows per thread
+constexpr int CONV_RT_FWD = 16;  // rows per thread, forward (3 extra row loads per run)
+constexpr int CONV_RT = 32;      // rows per thread, backward (3 extra output rows per run)
 
-// grid (ceil(C/8 / 128), ceil(T / CONV_RT)), block 128
+// grid (ceil(C/8 / 128), ceil(T / CONV_RT_FWD)), block 128
 template <typename T>
 __global__ void __launch_bounds__(128) conv1d_fwd_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ w,
                                                          const T* __restrict__ bias, const T* __restrict__ halo,
                                                          const int* __restrict__ seq_start, T* __restrict__ y,
-                                                         long long ldy, int T_tokens, int C) {
+                                                         long long ldy, T* __restrict__ y2, long long ldy2, int split,
+                                                         int T_tokens, int C) {
   const int cv = blockIdx.x * blockDim.x + threadIdx.x;
   if (cv * 8 >= C) return;
   const int c0 = cv * 8;
-  const int t0 = blockIdx.y * CONV_RT, t1 = min(T_tokens, t0 + CONV_RT);
+  // channels [0, split) go to y, the rest to y2 (the scan wants x dense and B|C apart)
+  T* const yo = c0 < split ? y + c0 : y2 + (c0 - split);
+  const long long ldo = c0 < split ? ldy : ldy2;
+  const int t0 = blockIdx.y * CONV_RT_FWD, t1 = min(T_tokens, t0 + CONV_RT_FWD);
   float wf[4][8], bf[8], win[3][8];
   cv_load_taps<T>(w, bias, c0, wf, bf);
 #pragma unroll
@@ -119,7 +124,7 @@ __global__ void __launch_bounds__(128) conv1d_fwd_kernel(const T* __restrict__ x
         if (s0 == 0 || t - 3 + j >= s0) a += wf[j][ch] * win[j][ch];
       acc[ch] = silu_f(a);
     }
-    *reinterpret_cast<uint4*>(y + (long long)t * ldy + c0) = cv_pack8<T>(acc);
+    *reinterpret_cast<uint4*>(yo + (long long)t * ldo) = cv_pack8<T>(acc);
 #pragma unroll
     for (int ch = 0; ch < 8; ++ch) {
       win[0][ch] = win[1][ch];
@@ -176,6 +181,7 @@ __device__ __forceinline__ void cv_load_row4(const T* __restrict__ x, long long 
 // grid (ceil(C/4 / 64), ceil(T / (CONV_RT * 4))), block (64, 4); dw32 [C, 4] and db32 [C] fp32, zeroed by the caller.
 template <typename T>
 __global__ void __launch_bounds__(256, 2) conv1d_bwd_kernel(const T* __restrict__ dy, long long lddy,
+                                                            const T* __restrict__ dy2, long long lddy2, int split,
                                                             const T* __restrict__ x, long long ldx,
                                                             const T* __restrict__ w, const T* __restrict__ bias,
                                                             const T* __restrict__ halo, const int* __restrict__ seq_start,
@@ -215,9 +221,12 @@ __global__ void __launch_bounds__(256, 2) conv1d_bwd_kernel(const T* __restrict_
     for (int j = 0; j < 4; ++j)
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) dxa[j][ch] = 0.f;
+    // output gradient of channels [0, split) comes from dy, of the rest from dy2
+    const T* const gy = c0 < split ? dy + c0 : dy2 + (c0 - split);
+    const long long ldg = c0 < split ? lddy : lddy2;
     // the next row's loads are issued before this row's arithmetic
     uint2 nx = *reinterpret_cast<const uint2*>(x + (long long)t0 * ldx + c0);
-    uint2 ng = *reinterpret_cast<const uint2*>(dy + (long long)t0 * lddy + c0);
+    uint2 ng = *reinterpret_cast<const uint2*>(gy + (long long)t0 * ldg);
 #pragma unroll 2
     for (int to = t0; to < to_end; ++to) {
       float cur[4], g[4];
@@ -225,7 +234,7 @@ __global__ void __launch_bounds__(256, 2) conv1d_bwd_kernel(const T* __restrict_
       cv_unpack4<T>(ng, g);
       if (to + 1 < to_end) {
         nx = *reinterpret_cast<const uint2*>(x + (long long)(to + 1) * ldx + c0);
-        ng = *reinterpret_cast<const uint2*>(dy + (long long)(to + 1) * lddy + c0);
+        ng = *reinterpret_cast<const uint2*>(gy + (long long)(to + 1) * ldg);
       }
       const int s0 = seq_start != nullptr ? seq_start[to] : 0;
       const bool own = to < own_end;
@@ -361,38 +370,43 @@ static bool conv_shape_ok(const void* p, long long ld, int C) {
   return C % 8 == 0 && ld % 8 == 0 && (reinterpret_cast<uintptr_t>(p) & 15) == 0;
 }
 
+// y2/ldy2/split: channels [split, C) are written to y2 (row step ldy2); pass y2 = nullptr for one output.
 extern "C" int fmsb_conv1d_fwd(const void* x, long long ldx, const void* w, const void* bias, const void* halo,
-                               const int* seq_start, void* y, long long ldy, int T, int C, int K, int dtype,
-                               cudaStream_t stream) {
+                               const int* seq_start, void* y, long long ldy, void* y2, long long ldy2, int split, int T,
+                               int C, int K, int dtype, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (K != 4 || !conv_shape_ok(x, ldx, C) || !conv_shape_ok(y, ldy, C) || !conv_shape_ok(w, 8, C) ||
-      (bias != nullptr && !conv_shape_ok(bias, 8, C)) || (halo != nullptr && !conv_shape_ok(halo, 8, C)))
+  if (y2 == nullptr) { split = C; y2 = y; ldy2 = ldy; }
+  if (K != 4 || split % 8 != 0 || split < 0 || split > C || !conv_shape_ok(x, ldx, C) || !conv_shape_ok(y, ldy, C) ||
+      !conv_shape_ok(y2, ldy2, C) || !conv_shape_ok(w, 8, C) || (bias != nullptr && !conv_shape_ok(bias, 8, C)) ||
+      (halo != nullptr && !conv_shape_ok(halo, 8, C)))
     return -2;
-  const dim3 grid((C / 8 + 127) / 128, (T + CONV_RT - 1) / CONV_RT);
+  const dim3 grid((C / 8 + 127) / 128, (T + CONV_RT_FWD - 1) / CONV_RT_FWD);
   if (dtype == 1)
-    conv1d_fwd_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)halo, seq_start, (__nv_bfloat16*)y, ldy, T, C);
+    conv1d_fwd_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)halo, seq_start, (__nv_bfloat16*)y, ldy, (__nv_bfloat16*)y2, ldy2, split, T, C);
   else if (dtype == 0)
-    conv1d_fwd_kernel<__half><<<grid, 128, 0, stream>>>((const __half*)x, ldx, (const __half*)w, (const __half*)bias, (const __half*)halo, seq_start, (__half*)y, ldy, T, C);
+    conv1d_fwd_kernel<__half><<<grid, 128, 0, stream>>>((const __half*)x, ldx, (const __half*)w, (const __half*)bias, (const __half*)halo, seq_start, (__half*)y, ldy, (__half*)y2, ldy2, split, T, C);
   else
     return -2;
   return (int)cudaGetLastError();
 }
 
-extern "C" int fmsb_conv1d_bwd(const void* dy, long long lddy, const void* x, long long ldx, const void* w,
-                               const void* bias, const void* halo, const int* seq_start, void* dx, long long lddx,
-                               void* dhalo, float* dw32, float* db32, int T, int C, int K, int dtype,
-                               cudaStream_t stream) {
+extern "C" int fmsb_conv1d_bwd(const void* dy, long long lddy, const void* dy2, long long lddy2, int split,
+                               const void* x, long long ldx, const void* w, const void* bias, const void* halo,
+                               const int* seq_start, void* dx, long long lddx, void* dhalo, float* dw32, float* db32,
+                               int T, int C, int K, int dtype, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (K != 4 || !conv_shape_ok(x, ldx, C) || !conv_shape_ok(dy, lddy, C) || !conv_shape_ok(dx, lddx, C) ||
-      !conv_shape_ok(w, 8, C) || (bias != nullptr && !conv_shape_ok(bias, 8, C)) ||
-      (halo != nullptr && !conv_shape_ok(halo, 8, C)) || (dhalo != nullptr && !conv_shape_ok(dhalo, 8, C)))
+  if (dy2 == nullptr) { split = C; dy2 = dy; lddy2 = lddy; }
+  if (K != 4 || split % 8 != 0 || split < 0 || split > C || !conv_shape_ok(x, ldx, C) || !conv_shape_ok(dy, lddy, C) ||
+      !conv_shape_ok(dy2, lddy2, C) || !conv_shape_ok(dx, lddx, C) || !conv_shape_ok(w, 8, C) ||
+      (bias != nullptr && !conv_shape_ok(bias, 8, C)) || (halo != nullptr && !conv_shape_ok(halo, 8, C)) ||
+      (dhalo != nullptr && !conv_shape_ok(dhalo, 8, C)))
     return -2;
   const dim3 grid((C / 4 + 63) / 64, (T + CONV_RT * 4 - 1) / (CONV_RT * 4));
   const dim3 block(64, 4);
   if (dtype == 1)
-    conv1d_bwd_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>((const __nv_bfloat16*)dy, lddy, (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)halo, seq_start, (__nv_bfloat16*)dx, lddx, (__nv_bfloat16*)dhalo, dw32, db32, T, C);
+    conv1d_bwd_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>((const __nv_bfloat16*)dy, lddy, (const __nv_bfloat16*)dy2, lddy2, split, (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)halo, seq_start, (__nv_bfloat16*)dx, lddx, (__nv_bfloat16*)dhalo, dw32, db32, T, C);
   else if (dtype == 0)
-    conv1d_bwd_kernel<__half><<<grid, block, 0, stream>>>((const __half*)dy, lddy, (const __half*)x, ldx, (const __half*)w, (const __half*)bias, (const __half*)halo, seq_start, (__half*)dx, lddx, (__half*)dhalo, dw32, db32, T, C);
+    conv1d_bwd_kernel<__half><<<grid, block, 0, stream>>>((const __half*)dy, lddy, (const __half*)dy2, lddy2, split, (const __half*)x, ldx, (const __half*)w, (const __half*)bias, (const __half*)halo, seq_start, (__half*)dx, lddx, (__half*)dhalo, dw32, db32, T, C);
   else
     return -2;
   return (int)cudaGetLastError();

@@ -3,7 +3,7 @@
 // the scan to the external mamba_ssm package, fms_acceleration_mcp/utils/utils.py:17-24,64-80.)
 //
 //   ssd_make_g2      G[c,h,t,s] = CB[c,g(h),t,s] exp(L_t - L_s) dt_s  (s <= t)         16-byte loads and stores
-//   ssd_dcb          dCB[c,g,t,s] = sum_{h in g} dG[c,h,t,s] exp(L_t - L_s) dt_s (s <= t), heads summed in registers
+//   ssd_dcb          dCB[c,g,t,s] = sum_{h in g} dG[c,h,t,s] exp(L_t - L_s) dt_s (s <= t), heads summed in fp32 registers
 //   ssd_rowscale     out[t,h,:] = x[t,h,:] * w[t,h]
 //   ssd_fwd_combine  y = y_intra + exp(L) y_inter + D x
 //   ssd_bwd_combine  dx = D dy + dxw wgt + dx_intra, and the five per-(t,h) dot products the gradients of
@@ -59,88 +59,122 @@ __device__ __forceinline__ void ld8f(const float* p, float (&f)[8]) {
   f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
 }
 
-constexpr int G2_ROWS = 32;  // rows of one (chunk, head) tile per CTA in ssd_make_g2
+constexpr int G2_ROWS = 64;  // rows of one (chunk, head) tile per CTA in ssd_make_g2
 
-// grid (Q / G2_ROWS, nh, nc); CB [nc*G, Q, Q]; Lt, dtt [nc, nh, Q]; out [nc*nh, Q, Q].  Q % 32 == 0, Q <= 1024.
+// grid (ceil(Q / G2_ROWS), nh, nc), block 256; CB [nc*G, Q, Q]; Lt, dtt [nc, nh, Q]; out [nc*nh, Q, Q].
+// Q % 8 == 0 and (Q / 8) divides 256, so a thread keeps the same 8 columns for all its rows and holds their
+// L_s and dt_s in registers.
 template <typename T>
 __global__ void __launch_bounds__(256) ssd_make_g2_kernel(const T* __restrict__ cb, const float* __restrict__ Lt,
                                                           const float* __restrict__ dtt, T* __restrict__ g, int nh,
                                                           int G, int Q) {
-  __shared__ float sL[1024], sdt[1024];
   const int c = blockIdx.z, h = blockIdx.y, t0 = blockIdx.x * G2_ROWS;
   const long long lbase = ((long long)c * nh + h) * Q;
-  // only columns s <= t0 + G2_ROWS - 1 matter for this tile
-  const int s_need = min(Q, t0 + G2_ROWS);
-  for (int i = threadIdx.x; i < s_need; i += blockDim.x) {
-    sL[i] = Lt[lbase + i];
-    sdt[i] = dtt[lbase + i];
+  const int vpr = Q >> 3, rpp = 256 / vpr;  // vectors per row, rows per pass of the block
+  const int s0 = (threadIdx.x % vpr) << 3, r0 = threadIdx.x / vpr;
+  const int t_end = min(Q, t0 + G2_ROWS);
+  float ls[8], ds[8];
+  if (s0 < t_end) {
+    ld8f(Lt + lbase + s0, ls);
+    ld8f(dtt + lbase + s0, ds);
   }
-  __syncthreads();
   const int gi = h / (nh / G);
   const T* cbt = cb + ((long long)c * G + gi) * Q * Q;
   T* gt = g + ((long long)c * nh + h) * Q * Q;
-  const int vpr = Q >> 3;
-  for (int i = threadIdx.x; i < G2_ROWS * vpr; i += blockDim.x) {
-    const int r = i / vpr, s0 = (i - r * vpr) << 3;
-    const int t = t0 + r;
+#pragma unroll 4
+  for (int t = t0 + r0; t < t_end; t += rpp) {
     uint4 out = make_uint4(0u, 0u, 0u, 0u);
     if (s0 <= t) {
       const uint4 u = *reinterpret_cast<const uint4*>(cbt + (long long)t * Q + s0);
+      const float lt = __ldg(Lt + lbase + t);
       float f[8];
       unpack8<T>(u, f);
-      const float lt = sL[t];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int s = s0 + j;
-        f[j] = (s <= t) ? f[j] * __expf(lt - sL[s]) * sdt[s] : 0.f;
-      }
+      for (int j = 0; j < 8; ++j) f[j] = (s0 + j <= t) ? f[j] * __expf(lt - ls[j]) * ds[j] : 0.f;
       out = pack8<T>(f);
     }
     *reinterpret_cast<uint4*>(gt + (long long)t * Q + s0) = out;
   }
 }
 
-constexpr int DCB_ROWS = 16;  // rows of one (chunk, group) tile per CTA in ssd_dcb
-
-// grid (Q / DCB_ROWS, G, n), block Q threads (one column each).  dG [n*nh, Q, Q] fp32; out [n*G, Q, Q].
+// dCB[c, g, t, s] = sum_{h in g} dG[c, h, t, s] exp(L_t - L_s) dt_s  (s <= t).
+// grid (ceil(Q / (2 * rpp)), G, n), block 256, rpp = 256 / (Q / 8): a thread owns 8 columns of two rows and sums
+// the heads of the group in fp32 registers; dG [n*nh, Q, Q] (16-bit), out [n*G, Q, Q].  The head's L and dt
+// (Q values each) pass through shared memory, double-buffered, and the next head's dG vectors are loaded before
+// the current head's arithmetic.  Q <= 1024.
 template <typename T>
-__global__ void __launch_bounds__(1024) ssd_dcb_kernel(const float* __restrict__ dG, const float* __restrict__ Lt,
-                                                        const float* __restrict__ dtt, T* __restrict__ dcb, int nh,
-                                                        int G, int Q) {
-  const int c = blockIdx.z, gi = blockIdx.y, t0 = blockIdx.x * DCB_ROWS;
-  const int s = threadIdx.x;
+__global__ void __launch_bounds__(256) ssd_dcb_kernel(const T* __restrict__ dG, const float* __restrict__ Lt,
+                                                       const float* __restrict__ dtt, T* __restrict__ dcb, int nh,
+                                                       int G, int Q) {
+  __shared__ __align__(16) float sL[2][1024];
+  __shared__ __align__(16) float sD[2][1024];
+  const int c = blockIdx.z, gi = blockIdx.y;
+  const int vpr = Q >> 3, rpp = 256 / vpr;
+  const int s0 = (threadIdx.x % vpr) << 3;
+  const int ta = blockIdx.x * 2 * rpp + threadIdx.x / vpr, tb = ta + rpp;
   const int hpg = nh / G;
-  float acc[DCB_ROWS];
+  const bool on_a = ta < Q && s0 <= ta, on_b = tb < Q && s0 <= tb;
+  const long long base0 = ((long long)c * nh + gi * hpg) * Q;
+  float acc_a[8], acc_b[8];
 #pragma unroll
-  for (int r = 0; r < DCB_ROWS; ++r) acc[r] = 0.f;
-  // a column right of the tile's last row is zero for every head: such a thread loads nothing
-  const bool any = s <= t0 + DCB_ROWS - 1;
-  if (any) {
-    // two heads per trip: 2 * DCB_ROWS independent loads in flight per thread
-    for (int hh = 0; hh < hpg; hh += 2) {
-      const bool two = hh + 1 < hpg;
-      const long long lb0 = ((long long)c * nh + gi * hpg + hh) * Q;
-      const long long lb1 = two ? lb0 + Q : lb0;
-      const float ls0 = Lt[lb0 + s], ds0 = dtt[lb0 + s];
-      const float ls1 = Lt[lb1 + s], ds1 = two ? dtt[lb1 + s] : 0.f;
-      const float* dg0 = dG + (lb0 + t0) * Q + s;
-      const float* dg1 = dG + (lb1 + t0) * Q + s;
-      float v0[DCB_ROWS], v1[DCB_ROWS];
+  for (int j = 0; j < 8; ++j) acc_a[j] = acc_b[j] = 0.f;
+  // head 0 into buffer 0
+  for (int i = threadIdx.x; i < Q; i += 256) {
+    sL[0][i] = Lt[base0 + i];
+    sD[0][i] = dtt[base0 + i];
+  }
+  uint4 ua = make_uint4(0u, 0u, 0u, 0u), ub = ua;
+  if (on_a) ua = *reinterpret_cast<const uint4*>(dG + (base0 + ta) * Q + s0);
+  if (on_b) ub = *reinterpret_cast<const uint4*>(dG + (base0 + tb) * Q + s0);
+  for (int hh = 0; hh < hpg; ++hh) {
+    const int buf = hh & 1;
+    __syncthreads();  // buffer `buf` is complete; nobody still reads the other one
+    // next head: loads go out now, their results are used after this head's arithmetic
+    const bool more = hh + 1 < hpg;
+    const long long nbase = base0 + (long long)(hh + 1) * Q;
+    float nl[4], nd[4];
+    uint4 na = make_uint4(0u, 0u, 0u, 0u), nb = na;
+    if (more) {
 #pragma unroll
-      for (int r = 0; r < DCB_ROWS; ++r) {
-        v0[r] = dg0[(long long)r * Q];
-        v1[r] = dg1[(long long)r * Q];
+      for (int k = 0; k < 4; ++k) {
+        const int i = threadIdx.x + k * 256;
+        if (i < Q) {
+          nl[k] = Lt[nbase + i];
+          nd[k] = dtt[nbase + i];
+        }
       }
+      if (on_a) na = *reinterpret_cast<const uint4*>(dG + (nbase + ta) * Q + s0);
+      if (on_b) nb = *reinterpret_cast<const uint4*>(dG + (nbase + tb) * Q + s0);
+    }
+    if (on_a || on_b) {
+      float ls[8], ds[8], fa[8], fb[8];
+      ld8f(&sL[buf][s0], ls);
+      ld8f(&sD[buf][s0], ds);
+      const float la = on_a ? sL[buf][ta] : 0.f, lb = on_b ? sL[buf][tb] : 0.f;
+      unpack8<T>(ua, fa);
+      unpack8<T>(ub, fb);
 #pragma unroll
-      for (int r = 0; r < DCB_ROWS; ++r) {
-        const float lt0 = __ldg(Lt + lb0 + t0 + r), lt1 = __ldg(Lt + lb1 + t0 + r);
-        if (s <= t0 + r) acc[r] += v0[r] * __expf(lt0 - ls0) * ds0 + v1[r] * __expf(lt1 - ls1) * ds1;
+      for (int j = 0; j < 8; ++j) {
+        if (on_a && s0 + j <= ta) acc_a[j] += fa[j] * __expf(la - ls[j]) * ds[j];
+        if (on_b && s0 + j <= tb) acc_b[j] += fb[j] * __expf(lb - ls[j]) * ds[j];
       }
     }
-  }
-  T* out = dcb + (((long long)c * G + gi) * Q + t0) * Q + s;
+    if (more) {
 #pragma unroll
-  for (int r = 0; r < DCB_ROWS; ++r) out[(long long)r * Q] = (T)acc[r];
+      for (int k = 0; k < 4; ++k) {
+        const int i = threadIdx.x + k * 256;
+        if (i < Q) {
+          sL[buf ^ 1][i] = nl[k];
+          sD[buf ^ 1][i] = nd[k];
+        }
+      }
+      ua = na;
+      ub = nb;
+    }
+  }
+  T* out = dcb + ((long long)c * G + gi) * Q * Q;
+  if (ta < Q) *reinterpret_cast<uint4*>(out + (long long)ta * Q + s0) = pack8<T>(acc_a);
+  if (tb < Q) *reinterpret_cast<uint4*>(out + (long long)tb * Q + s0) = pack8<T>(acc_b);
 }
 
 // out[row, :] = x[row, :] * w[row]   rows = T*nh, P % 8 == 0
@@ -277,8 +311,8 @@ using namespace fmsb::ssd;
 extern "C" int fmsb_ssd_make_g2(const void* cb, const float* Lt, const float* dtt, void* g, int nc, int nh, int G, int Q,
                                 int dtype, cudaStream_t stream) {
   if (nc <= 0) return 0;
-  if (Q % G2_ROWS != 0 || Q > 1024 || nh % G != 0 || nc > 65535 || nh > 65535) return -2;
-  const dim3 grid(Q / G2_ROWS, nh, nc);
+  if (Q % 8 != 0 || 256 % (Q / 8) != 0 || nh % G != 0 || nc > 65535 || nh > 65535) return -2;
+  const dim3 grid((Q + G2_ROWS - 1) / G2_ROWS, nh, nc);
   if (dtype == 1)
     ssd_make_g2_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)cb, Lt, dtt, (__nv_bfloat16*)g, nh, G, Q);
   else if (dtype == 0)
@@ -288,15 +322,16 @@ extern "C" int fmsb_ssd_make_g2(const void* cb, const float* Lt, const float* dt
   return (int)cudaGetLastError();
 }
 
-extern "C" int fmsb_ssd_dcb(const float* dG, const float* Lt, const float* dtt, void* dcb, int nc, int nh, int G, int Q,
+extern "C" int fmsb_ssd_dcb(const void* dG, const float* Lt, const float* dtt, void* dcb, int nc, int nh, int G, int Q,
                             int dtype, cudaStream_t stream) {
   if (nc <= 0) return 0;
-  if (Q % 32 != 0 || Q > 1024 || nh % G != 0 || nc > 65535 || G > 65535) return -2;
-  const dim3 grid(Q / DCB_ROWS, G, nc);
+  if (Q % 8 != 0 || 256 % (Q / 8) != 0 || Q > 1024 || nh % G != 0 || nc > 65535 || G > 65535) return -2;
+  const int rows_per_cta = 2 * (256 / (Q / 8));
+  const dim3 grid((Q + rows_per_cta - 1) / rows_per_cta, G, nc);
   if (dtype == 1)
-    ssd_dcb_kernel<__nv_bfloat16><<<grid, Q, 0, stream>>>(dG, Lt, dtt, (__nv_bfloat16*)dcb, nh, G, Q);
+    ssd_dcb_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)dG, Lt, dtt, (__nv_bfloat16*)dcb, nh, G, Q);
   else if (dtype == 0)
-    ssd_dcb_kernel<__half><<<grid, Q, 0, stream>>>(dG, Lt, dtt, (__half*)dcb, nh, G, Q);
+    ssd_dcb_kernel<__half><<<grid, 256, 0, stream>>>((const __half*)dG, Lt, dtt, (__half*)dcb, nh, G, Q);
   else
     return -2;
   return (int)cudaGetLastError();

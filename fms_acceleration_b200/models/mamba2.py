@@ -100,9 +100,10 @@ class Mamba2Mixer(nn.Module):
         z, xBC, dt_raw = _SplitCols.apply(zxbcdt, di, self.conv_dim, zxbcdt.shape[1] - di - self.conv_dim)
         w = self.conv1d.weight.squeeze(1)
         halo = self.cp.exchange_halo(xBC, self.d_conv - 1, self.layer_idx) if self.cp is not None else None
-        xBC = MB.causal_conv1d(_aligned(xBC), w.to(xBC.dtype),
-                               None if self.conv1d.bias is None else self.conv1d.bias.to(xBC.dtype), halo, seq_start, seq_end)
-        xs, Bs, Cs = _SplitCols.apply(xBC, di, gn, gn)
+        xs, BC = MB.causal_conv1d(_aligned(xBC), w.to(xBC.dtype),
+                                  None if self.conv1d.bias is None else self.conv1d.bias.to(xBC.dtype), halo, seq_start,
+                                  seq_end, split=di)
+        Bs, Cs = _SplitCols.apply(BC, gn, gn)
         x = xs.reshape(T, self.nheads, self.headdim)
         B = Bs.reshape(T, self.ngroups, self.d_state)
         C = Cs.reshape(T, self.ngroups, self.d_state)

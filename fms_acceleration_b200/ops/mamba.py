@@ -20,8 +20,8 @@ from .. import _native as NV
 from .gemm import batched_gemm
 
 P_, I_, L_, F_ = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
-NV.declare("fmsb_conv1d_fwd", [P_, L_, P_, P_, P_, P_, P_, L_, I_, I_, I_, I_, P_])
-NV.declare("fmsb_conv1d_bwd", [P_, L_, P_, L_, P_, P_, P_, P_, P_, L_, P_, P_, P_, I_, I_, I_, I_, P_])
+NV.declare("fmsb_conv1d_fwd", [P_, L_, P_, P_, P_, P_, P_, L_, P_, L_, I_, I_, I_, I_, I_, P_])
+NV.declare("fmsb_conv1d_bwd", [P_, L_, P_, L_, I_, P_, L_, P_, P_, P_, P_, P_, L_, P_, P_, P_, I_, I_, I_, I_, P_])
 NV.declare("fmsb_ssd_make_g2", [P_, P_, P_, P_, I_, I_, I_, I_, I_, P_])
 NV.declare("fmsb_ssd_dcb", [P_, P_, P_, P_, I_, I_, I_, I_, I_, P_])
 NV.declare("fmsb_ssd_rowscale", [P_, P_, P_, L_, I_, I_, P_])
@@ -77,47 +77,66 @@ def _vec_rows(t):
 
 class _CausalConv1d(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, bias, halo, seq_start, seq_end):
+    def forward(ctx, x, w, bias, halo, seq_start, seq_end, split):
         T, Cc = x.shape
         K = w.shape[1]
-        if Cc % 8 != 0 or K != 4:
-            raise ValueError("the conv kernel needs 4 taps and a channel count that is a multiple of 8")
+        if Cc % 8 != 0 or K != 4 or split % 8 != 0:
+            raise ValueError("the conv kernel needs 4 taps and channel counts that are multiples of 8")
         x = _vec_rows(x)
-        y = torch.empty(T, Cc, dtype=x.dtype, device=x.device)
+        two = 0 < split < Cc
+        y = torch.empty(T, split if two else Cc, dtype=x.dtype, device=x.device)
+        y2 = torch.empty(T, Cc - split, dtype=x.dtype, device=x.device) if two else None
         wc = w.contiguous()
         bc = None if bias is None else bias.contiguous()
         hc = None if halo is None else halo.contiguous()
         rc = NV.lib().fmsb_conv1d_fwd(x.data_ptr(), x.stride(0), wc.data_ptr(), NV.ptr(bc), NV.ptr(hc),
-                                      NV.ptr(seq_start), y.data_ptr(), y.stride(0), T, Cc, K, NV.dtype_code(x.dtype),
-                                      NV.stream_ptr())
+                                      NV.ptr(seq_start), y.data_ptr(), y.stride(0), NV.ptr(y2),
+                                      y2.stride(0) if two else 0, split if two else Cc, T, Cc, K,
+                                      NV.dtype_code(x.dtype), NV.stream_ptr())
         NV.check(rc, "fmsb_conv1d_fwd")
         ctx.save_for_backward(x, wc, bc, hc, seq_start)
-        return y
+        ctx.split = split if two else Cc
+        if two:
+            return y, y2
+        return y, y.new_empty(0)
 
     @staticmethod
-    def backward(ctx, dy):
+    def backward(ctx, dy, dy2):
         x, w, bias, halo, seq_start = ctx.saved_tensors
         T, Cc = x.shape
         K = w.shape[1]
+        split = ctx.split
+        two = split < Cc
+        if dy is None:
+            dy = torch.zeros(T, split, dtype=x.dtype, device=x.device)
+        if two and dy2 is None:
+            dy2 = torch.zeros(T, Cc - split, dtype=x.dtype, device=x.device)
         dy = _vec_rows(dy)
+        dy2 = _vec_rows(dy2) if two else None
         dx = torch.empty(T, Cc, dtype=x.dtype, device=x.device)
         dhalo = torch.empty(K - 1, Cc, dtype=x.dtype, device=x.device) if halo is not None else None
         # tap and bias gradients are accumulated by the kernel: dw[c, j] = sum_t dpre[t, c] * xin[t - (K-1) + j, c]
         dwb = torch.zeros(Cc * (K + 1), dtype=torch.float32, device=x.device)
         dw32, db32 = dwb[: Cc * K].view(Cc, K), dwb[Cc * K:]
-        rc = NV.lib().fmsb_conv1d_bwd(dy.data_ptr(), dy.stride(0), x.data_ptr(), x.stride(0), w.data_ptr(), NV.ptr(bias),
-                                      NV.ptr(halo), NV.ptr(seq_start), dx.data_ptr(), dx.stride(0), NV.ptr(dhalo),
-                                      dw32.data_ptr(), db32.data_ptr() if bias is not None else None, T, Cc, K,
-                                      NV.dtype_code(x.dtype), NV.stream_ptr())
+        rc = NV.lib().fmsb_conv1d_bwd(dy.data_ptr(), dy.stride(0), NV.ptr(dy2), dy2.stride(0) if two else 0, split,
+                                      x.data_ptr(), x.stride(0), w.data_ptr(), NV.ptr(bias), NV.ptr(halo),
+                                      NV.ptr(seq_start), dx.data_ptr(), dx.stride(0), NV.ptr(dhalo), dw32.data_ptr(),
+                                      db32.data_ptr() if bias is not None else None, T, Cc, K, NV.dtype_code(x.dtype),
+                                      NV.stream_ptr())
         NV.check(rc, "fmsb_conv1d_bwd")
-        return dx, dw32.to(w.dtype), (db32.to(w.dtype) if bias is not None else None), dhalo, None, None
+        return dx, dw32.to(w.dtype), (db32.to(w.dtype) if bias is not None else None), dhalo, None, None, None
 
 
-def causal_conv1d(x, w, bias=None, halo=None, seq_start=None, seq_end=None):
-    """Depthwise causal conv (kernel 4) + SiLU on packed rows ``x [T, C]``; ``w [C, K]``."""
+def causal_conv1d(x, w, bias=None, halo=None, seq_start=None, seq_end=None, split=None):
+    """Depthwise causal conv (kernel 4) + SiLU on packed rows ``x [T, C]``; ``w [C, K]``.  With ``split`` the
+    result comes back as two dense tensors, channels ``[0, split)`` and ``[split, C)`` (the scan wants its ``x``
+    dense and ``B|C`` apart, so no copy is needed afterwards)."""
     if not x.is_cuda:
-        return conv1d_ref(x, w, bias, halo, seq_start)
-    return _CausalConv1d.apply(x, w, bias, halo, seq_start, seq_end)
+        y = conv1d_ref(x, w, bias, halo, seq_start)
+        return y if split is None else (y[:, :split], y[:, split:])
+    if split is None:
+        return _CausalConv1d.apply(x, w, bias, halo, seq_start, seq_end, x.shape[1])[0]
+    return _CausalConv1d.apply(x, w, bias, halo, seq_start, seq_end, split)
 
 
 # ------------------------------------------------------------------------------------------------ SSD scan
@@ -148,7 +167,7 @@ def _rowscale(x2, w, nh, P):
     return out
 
 
-SLAB_BYTES = 1 << 30  # bound on each [chunks, heads, Q, Q] fp32 temporary of the scan
+SLAB_BYTES = 1 << 30  # bound on the [chunks, heads, Q, Q] temporaries of the scan (counted at 4 bytes per value)
 
 
 def _slabs(nc: int, nh: int, Q: int):
@@ -163,16 +182,18 @@ class _SSDScan(torch.autograd.Function):
         T, nh, P = x.shape
         G, N = B.shape[1], B.shape[2]
         assert T % Q == 0, "sequence length must be a multiple of the chunk size"
-        assert Q % 32 == 0 and P % 8 == 0, "chunk size must be a multiple of 32 and the head dimension of 8"
+        assert Q % 8 == 0 and 256 % (Q // 8) == 0 and Q <= 1024 and P % 8 == 0, \
+            "chunk size must be 8 times a divisor of 256, at most 1024 (32 ... 256, 512, 1024) and the head dimension a multiple of 8"
         nc, hpg = T // Q, nh // G
         dev, dtp = x.device, x.dtype
         x2 = _rows16(x.reshape(T, nh * P))
         B2, C2 = B.reshape(T, G * N), C.reshape(T, G * N)
         dt = dt.float().contiguous()
-        a = dt * A.float()[None, :]
-        L = a.view(nc, Q, nh).cumsum(1).reshape(T, nh).contiguous()
-        Ltot = L.view(nc, Q, nh)[:, -1, :].contiguous()                     # [nc, nh]
-        Lt, dtt = _chunk_major(L, nc, Q, nh), _chunk_major(dt, nc, Q, nh)
+        # within-chunk cumulative sum of dt*A, taken along the unit-stride axis of the chunk-major layout
+        dtt = _chunk_major(dt, nc, Q, nh)
+        Lt = (dtt * A.float()[None, :, None]).cumsum(-1)                    # [nc, nh, Q]
+        L = Lt.transpose(1, 2).reshape(T, nh).contiguous()
+        Ltot = Lt[:, :, -1].contiguous()                                    # [nc, nh]
         # C.B^T per chunk and group
         cb = batched_gemm(C2, B2, M=Q, N=Q, K=N, n_batch=nc * G, n_inner=G, a_off=(Q, 0, N, 1), b_off=(Q, 0, N, 1),
                           d_off=(G * Q, Q, 0), out_rows=nc * G * Q, out_cols=Q)
@@ -275,8 +296,7 @@ class _SSDScan(torch.autograd.Function):
                          b_off=(Q, 0, P, 1), d_off=(Q, 0, P), b_mn=True, out=y_intra[rows])
             del g
             dG = batched_gemm(dy2[rows], x2[rows], M=Q, N=Q, K=P, n_batch=n * nh, n_inner=nh, a_off=(Q, 0, P, 1),
-                              b_off=(Q, 0, P, 1), d_off=(nh * Q, Q, 0), out_rows=n * nh * Q, out_cols=Q,
-                              out_dtype=torch.float32)
+                              b_off=(Q, 0, P, 1), d_off=(nh * Q, Q, 0), out_rows=n * nh * Q, out_cols=Q)
             # dCB[c, g] = sum_{h in g} dG o exp(L_t - L_s) dt_s (s <= t)
             dcb16 = torch.empty(n * G * Q, Q, dtype=dtp, device=dev)
             rc = NV.lib().fmsb_ssd_dcb(dG.data_ptr(), Lt[c0:c1].data_ptr(), dtt[c0:c1].data_ptr(), dcb16.data_ptr(), n,
@@ -306,10 +326,11 @@ class _SSDScan(torch.autograd.Function):
         dL = red[1] - dww + row - col
         ddt = (dww + col) / dt
         dLtot = dLtot + dww.view(nc, Q, nh).sum(1)
-        # ---- through L = cumsum(dt A) within the chunk, Ltot = L[last]
-        dLc = dL.view(nc, Q, nh).clone()
-        dLc[:, -1, :] += dLtot
-        da = torch.flip(torch.cumsum(torch.flip(dLc, [1]), 1), [1]).reshape(T, nh)
+        # ---- through L = cumsum(dt A) within the chunk, Ltot = L[last]: a reverse cumulative sum per chunk
+        dLt = _chunk_major(dL, nc, Q, nh)
+        dLt[:, :, -1] += dLtot
+        dat = dLt.sum(-1, keepdim=True) - dLt.cumsum(-1) + dLt
+        da = dat.transpose(1, 2).reshape(T, nh)
         ddt = ddt + da * A.float()[None, :]
         dA = (da * dt).sum(0)
         return (dx, ddt.to(dt.dtype), dA.to(A.dtype), dB.view(T, G, N).to(B.dtype), dC.view(T, G, N).to(C.dtype),
@@ -327,7 +348,7 @@ class _StateCorrection(torch.autograd.Function):
         nc, hpg = T // Q, nh // G
         dtp = y0.dtype
         dt = dt.float().contiguous()
-        Lg = torch.cumsum(dt * A.float()[None, :], 0).contiguous()            # [T, nh]
+        Lg = (dt * A.float()[None, :]).t().contiguous().cumsum(-1).t().contiguous()   # [T, nh]
         hin16 = h_in.to(dtp).reshape(nh * P, N).contiguous()
         C2 = C.reshape(T, G * N)
         yc = _state_gemm(C2, hin16, T, Q, nh, P, N, hpg)
@@ -367,7 +388,8 @@ class _StateCorrection(torch.autograd.Function):
                                       NV.stream_ptr())
         NV.check(rc, "fmsb_ssd_rowdot")
         del yc
-        da = torch.flip(torch.cumsum(torch.flip(dLg, [0]), 0), [0])           # through Lg = cumsum(dt A)
+        dLgt = dLg.t().contiguous()                                           # through Lg = cumsum(dt A)
+        da = (dLgt.sum(-1, keepdim=True) - dLgt.cumsum(-1) + dLgt).t()
         ddt = da * A.float()[None, :]
         dA = (da * dt).sum(0)
         return dy, dh.view(nh, P, N).to(h_dtype), ddt, dA.to(A.dtype), dC.view(T, G, N).to(C.dtype), None

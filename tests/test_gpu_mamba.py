@@ -31,6 +31,15 @@ def test_conv1d_matches_reference():
     assert _rel(y, yr) < 1e-2
     assert _rel(x.grad, xr.grad) < 2e-2 and _rel(w.grad, wr.grad) < 2e-2
     assert _rel(b.grad, br.grad) < 2e-2 and _rel(halo.grad, hr.grad) < 2e-2
+    # two dense outputs (channels [0, 64) and [64, C)): same numbers, same gradients
+    x2, w2, b2, h2 = (t.detach().clone().requires_grad_() for t in (x, w, b, halo))
+    ya, yb = MB.causal_conv1d(x2, w2, b2, h2, split=64)
+    assert ya.shape == (T, 64) and yb.shape == (T, Cc - 64) and ya.is_contiguous() and yb.is_contiguous()
+    assert torch.equal(torch.cat([ya, yb], 1), y)
+    (ya.float() * g[:, :64].float()).sum().backward(retain_graph=True)
+    (yb.float() * g[:, 64:].float()).sum().backward()
+    NV.check_status()
+    assert _rel(x2.grad, x.grad) < 1e-3 and _rel(w2.grad, w.grad) < 1e-3 and _rel(h2.grad, halo.grad) < 1e-3
 
 
 def test_conv1d_packed_sequences_do_not_leak():
