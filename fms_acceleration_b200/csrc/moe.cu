@@ -256,35 +256,77 @@ __global__ void moe_plan_kernel(MoePeers count_tables, MoePeers signals, const i
 }
 
 // Deterministic slot of every (token, k) pair: the j-th pair (in token order) routed to expert e gets
-// send_base[e] + j.  One CTA per expert; block-wide compaction by ballot + prefix.
-__global__ void moe_assign_kernel(const int* __restrict__ topk_idx, long long n, const int* __restrict__ send_base,
-                                  int* __restrict__ dest_row) {
-  const int e = blockIdx.x;
-  __shared__ int warp_tot[32];
-  __shared__ int running;
-  if (threadIdx.x == 0) running = send_base[e];
+// send_base[e] + j (or -1 past the expert's limit).  Three small launches over chunks of kAssignChunk pairs:
+//   count   chunk_cnt[chunk][e] = pairs of the chunk routed to e
+//   scan    chunk_cnt[chunk][e] <- send_base[e] + pairs of EARLIER chunks routed to e
+//   assign  slot = chunk_cnt[chunk][e] + pairs of earlier warps of the chunk + earlier lanes of the warp with the same e
+// Equal experts inside a warp are found with __match_any_sync, so there is no atomic and no sort anywhere.
+constexpr int kAssignChunk = 1024;
+
+// per-warp, per-expert pair counts of one chunk into wcnt[warp][e]; returns this lane's expert (or -1) and the
+// mask of lanes of the warp that share it
+__device__ __forceinline__ int assign_warp_counts(const int* __restrict__ topk_idx, long long n, int E, int* wcnt,
+                                                  unsigned& peers) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < 32 * E; i += blockDim.x) wcnt[i] = 0;
   __syncthreads();
-  const int limit = send_base[gridDim.x + e];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  for (long long base = 0; base < n; base += blockDim.x) {
-    const long long i = base + threadIdx.x;
-    const bool hit = i < n && topk_idx[i] == e;
-    const unsigned m = __ballot_sync(0xffffffffu, hit);
-    const int prefix = __popc(m & ((1u << lane) - 1));
-    if (lane == 0) warp_tot[warp] = __popc(m);
-    __syncthreads();
-    int woff = 0, tot = 0;
-    for (int w = 0; w < nwarps; ++w) {
-      if (w < warp) woff += warp_tot[w];
-      tot += warp_tot[w];
+  const long long i = (long long)blockIdx.x * kAssignChunk + threadIdx.x;
+  const int e = i < n ? topk_idx[i] : -1;
+  // lanes without a pair get distinct keys so that they match nobody
+  peers = __match_any_sync(0xffffffffu, e >= 0 ? e : -1 - lane);
+  if (e >= 0 && lane == __ffs(peers) - 1) wcnt[warp * E + e] = __popc(peers);
+  __syncthreads();
+  return e;
+}
+
+__global__ void __launch_bounds__(kAssignChunk) moe_assign_count_kernel(const int* __restrict__ topk_idx, long long n,
+                                                                        int E, int* __restrict__ chunk_cnt) {
+  extern __shared__ int wcnt[];
+  unsigned peers;
+  assign_warp_counts(topk_idx, n, E, wcnt, peers);
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int tot = 0;
+#pragma unroll 8
+    for (int w = 0; w < 32; ++w) tot += wcnt[w * E + e];
+    chunk_cnt[(long long)blockIdx.x * E + e] = tot;
+  }
+}
+
+__global__ void moe_assign_scan_kernel(int* __restrict__ chunk_cnt, int n_chunks, int E,
+                                       const int* __restrict__ send_base) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= E) return;
+  int run = send_base[e];
+#pragma unroll 8
+  for (int c = 0; c < n_chunks; ++c) {
+    const int v = chunk_cnt[(long long)c * E + e];
+    chunk_cnt[(long long)c * E + e] = run;
+    run += v;
+  }
+}
+
+__global__ void __launch_bounds__(kAssignChunk) moe_assign_kernel(const int* __restrict__ topk_idx, long long n, int E,
+                                                                  const int* __restrict__ chunk_cnt,
+                                                                  const int* __restrict__ send_base,
+                                                                  int* __restrict__ dest_row) {
+  extern __shared__ int wcnt[];
+  unsigned peers;
+  const int e = assign_warp_counts(topk_idx, n, E, wcnt, peers);
+  // exclusive prefix over the warps of the chunk, offset by the chunk's first slot
+  for (int x = threadIdx.x; x < E; x += blockDim.x) {
+    int run = chunk_cnt[(long long)blockIdx.x * E + x];
+    for (int w = 0; w < 32; ++w) {
+      const int v = wcnt[w * E + x];
+      wcnt[w * E + x] = run;
+      run += v;
     }
-    if (hit) {
-      const int slot = running + woff + prefix;
-      dest_row[i] = slot < limit ? slot : -1;  // -1: dropped (capacity overflow)
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) running += tot;
-    __syncthreads();
+  }
+  __syncthreads();
+  if (e >= 0) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int slot = wcnt[warp * E + e] + __popc(peers & ((1u << lane) - 1));
+    const long long i = (long long)blockIdx.x * kAssignChunk + threadIdx.x;
+    dest_row[i] = slot < send_base[E + e] ? slot : -1;  // -1: dropped (capacity overflow)
   }
 }
 
@@ -489,11 +531,13 @@ extern "C" int fmsb_moe_router_bwd(const float* logits, const int* topk_idx, con
 }
 
 // counts must be zeroed by the caller.  Then plan + assign.  count_tables / signals may be null when world == 1.
+// chunk_scratch: ceil(n_pairs / 1024) * E ints of work space for the slot assignment.
 extern "C" int fmsb_moe_plan(const int* topk_idx, long long n_pairs, int E, int rank, int world, int capacity,
                              int* counts, void* const* count_tables, void* const* signals, unsigned epoch,
-                             int* seg_off, int* seg_cnt, int* send_base, int* dest_row, int* needed, int* status,
-                             cudaStream_t stream) {
+                             int* seg_off, int* seg_cnt, int* send_base, int* dest_row, int* needed,
+                             int* chunk_scratch, int* status, cudaStream_t stream) {
   if (E > kMoeMaxExperts || world > kMoeMaxRanks || E % world != 0) return -2;
+  if (n_pairs > 0 && chunk_scratch == nullptr) return -2;
   if (n_pairs > 0) {
     long long blocks = (n_pairs + 255) / 256;
     if (blocks > 1024) blocks = 1024;
@@ -503,7 +547,17 @@ extern "C" int fmsb_moe_plan(const int* topk_idx, long long n_pairs, int E, int 
   MoePeers sg = world > 1 ? moe_ptrs(signals, world) : MoePeers{};
   moe_plan_kernel<<<1, 256, 0, stream>>>(ct, sg, counts, rank, world, E, capacity, epoch, seg_off, seg_cnt, send_base,
                                          needed, status);
-  if (n_pairs > 0) moe_assign_kernel<<<E, 1024, 0, stream>>>(topk_idx, n_pairs, send_base, dest_row);
+  if (n_pairs > 0) {
+    const int n_chunks = (int)((n_pairs + kAssignChunk - 1) / kAssignChunk);
+    const size_t smem = (size_t)32 * E * sizeof(int);  // at most 64 KB (E <= 512)
+    if (smem > 48 * 1024) {
+      cudaFuncSetAttribute(moe_assign_count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      cudaFuncSetAttribute(moe_assign_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    }
+    moe_assign_count_kernel<<<n_chunks, kAssignChunk, smem, stream>>>(topk_idx, n_pairs, E, chunk_scratch);
+    moe_assign_scan_kernel<<<(E + 127) / 128, 128, 0, stream>>>(chunk_scratch, n_chunks, E, send_base);
+    moe_assign_kernel<<<n_chunks, kAssignChunk, smem, stream>>>(topk_idx, n_pairs, E, chunk_scratch, send_base, dest_row);
+  }
   return (int)cudaGetLastError();
 }
 

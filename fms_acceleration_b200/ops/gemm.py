@@ -94,6 +94,10 @@ def gemm(
             raise ValueError("bad `c`")
     if bn is None:
         bn = _pick_bn(Nn, b_mn)
+    if a_mn and b_mn and a2 is None and c is None and alpha == 1.0 and max_ctas == 0:
+        splits = _split_k(M, Nn, K, bn)
+        if splits > 1:
+            return _gemm_split_k(a, b, M, Nn, K, splits, out, bn)
     status = N.status_word(a.device)
     rc = N.lib().fmsb_gemm(
         a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), K,
@@ -105,6 +109,35 @@ def gemm(
         status.data_ptr(), N.stream_ptr(),
     )
     N.check(rc, "fmsb_gemm")
+    return out
+
+
+SM_COUNT = 148
+SPLIT_K_MIN = 512  # shortest contraction slice worth a tile of its own
+
+
+def _split_k(M: int, Nn: int, K: int, bn: int) -> int:
+    """Number of contraction slices for a weight-gradient product (``a^T b`` with a long contraction, the token
+    axis): when the output has fewer tiles than half the SMs, the contraction is cut so that every SM gets a tile."""
+    tiles = -(-M // 128) * -(-Nn // bn)
+    if tiles * 2 > SM_COUNT or K < 2 * SPLIT_K_MIN:
+        return 1
+    splits = 1
+    while tiles * splits * 2 <= 2 * SM_COUNT and K % (splits * 2 * 64) == 0 and K // (splits * 2) >= SPLIT_K_MIN:
+        splits *= 2
+    return splits
+
+
+def _gemm_split_k(a, b, M, Nn, K, splits, out, bn):
+    """``a [K, M]^T b [K, N]`` as ``splits`` batched products over slices of the contraction, partial results in
+    fp32, then one sum."""
+    part = torch.empty(splits * M, Nn, dtype=torch.float32, device=a.device)
+    ks = K // splits
+    batched_gemm(a, b, M=M, N=Nn, K=ks, n_batch=splits, n_inner=1, a_off=(ks, 0, 0, 1), b_off=(ks, 0, 0, 1),
+                 d_off=(M, 0, 0), a_mn=True, b_mn=True, out=part, bn=bn)
+    if out.dtype == torch.float32:
+        return torch.sum(part.view(splits, M, Nn), dim=0, out=out)
+    out.copy_(part.view(splits, M, Nn).sum(0))
     return out
 
 

@@ -24,7 +24,7 @@ P, I, L, F, U = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
 N.declare("fmsb_grouped_gemm", [P, L, P, L, I, I, P, L, I, P, L, F, F, I, I, I, I, I, I, P, L, L, L, P, P])
 N.declare("fmsb_moe_router", [P, I, I, I, I, P, P, P])
 N.declare("fmsb_moe_router_bwd", [P, P, P, P, I, I, I, I, P, P])
-N.declare("fmsb_moe_plan", [P, L, I, I, I, I, P, P, P, U, P, P, P, P, P, P, P])
+N.declare("fmsb_moe_plan", [P, L, I, I, I, I, P, P, P, U, P, P, P, P, P, P, P, P])
 N.declare("fmsb_moe_dispatch", [P, L, P, P, P, L, I, I, I, P, L, I, I, P])
 N.declare("fmsb_moe_zero_pad", [P, L, I, P, P, I, I, P])
 N.declare("fmsb_moe_combine", [P, L, P, P, P, L, I, I, I, P, L, I, I, P])
@@ -218,6 +218,7 @@ def _plan(ctx: MoEContext, topk_idx, T, device):
     seg_cnt = torch.empty(ctx.E_local, dtype=torch.int32, device=device)
     send_base = torch.empty(2 * E, dtype=torch.int32, device=device)  # [first slot | end of valid slots] per expert
     dest_row = torch.empty(T, k, dtype=torch.int32, device=device)
+    scratch = torch.empty(max(1, -(-T * k // 1024)) * E, dtype=torch.int32, device=device)  # per-chunk expert counts
     st = N.status_word(device)
     if ctx.world > 1:
         epoch = ctx.comm.next_epoch(PLAN_CHAN)
@@ -228,7 +229,8 @@ def _plan(ctx: MoEContext, topk_idx, T, device):
         epoch, tab, sig = 0, None, None
     rc = N.lib().fmsb_moe_plan(topk_idx.data_ptr(), T * k, E, ctx.rank, ctx.world, ctx.cap, counts.data_ptr(), tab, sig,
                                epoch, seg_off.data_ptr(), seg_cnt.data_ptr(), send_base.data_ptr(), dest_row.data_ptr(),
-                               MoEContext.needed_counter(device).data_ptr(), st.data_ptr(), N.stream_ptr())
+                               MoEContext.needed_counter(device).data_ptr(), scratch.data_ptr(), st.data_ptr(),
+                               N.stream_ptr())
     N.check(rc, "fmsb_moe_plan")
     return seg_off, seg_cnt, dest_row
 

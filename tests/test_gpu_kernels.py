@@ -300,3 +300,21 @@ def test_fast_gemv_matches_dequantised_product():
     ref = x.float() @ w.float().t()
     assert y.shape == (1, 3, 768)
     assert (y.float() - ref).abs().max() <= 1e-2 * ref.abs().max() + 1e-3
+
+
+@pytest.mark.parametrize("M,Nn,K,dtype", [(48, 4096, 16384, torch.float32), (6144, 48, 8192, torch.float32),
+                                          (1536, 512, 4096, torch.bfloat16)])
+def test_weight_gradient_gemm_splits_the_contraction(M, Nn, K, dtype):
+    """dW = dy^T x with few output tiles and a long token axis runs as slices of the contraction + one sum."""
+    from fms_acceleration_b200.ops import gemm as GM
+
+    torch.manual_seed(7)
+    dy = (torch.randn(K, M, device=DEV) * 0.5).bfloat16()
+    x = (torch.randn(K, Nn, device=DEV) * 0.5).bfloat16()
+    assert GM._split_k(M, Nn, K, GM._pick_bn(Nn, True)) > 1
+    out = GM.gemm(dy, x, a_mn=True, b_mn=True, out_dtype=dtype)
+    NV.check_status()
+    ref = dy.float().t() @ x.float()
+    assert out.dtype == dtype and out.shape == (M, Nn)
+    tol = 2e-3 if dtype == torch.float32 else 1e-2
+    assert (out.float() - ref).abs().max() <= tol * ref.abs().max()
