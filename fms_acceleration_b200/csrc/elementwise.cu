@@ -236,13 +236,24 @@ rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* _
   }
 }
 
-// out[c] = sum_b partial[b, c]
+// out[c] = sum_b partial[b, c].  Block (32, 8): 32 neighbouring columns, the rows dealt over the 8 row lanes and
+// folded in shared memory.
 __global__ void colsum_kernel(const float* __restrict__ partial, float* __restrict__ out, int nblocks, int H) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= H) return;
+  __shared__ float red[8][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
   float s = 0.f;
-  for (int b = 0; b < nblocks; ++b) s += partial[(long long)b * H + c];
-  out[c] = s;
+  if (c < H) {
+#pragma unroll 4
+    for (int b = threadIdx.y; b < nblocks; b += 8) s += partial[(long long)b * H + c];
+  }
+  red[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < H) {
+    float t = 0.f;
+#pragma unroll
+    for (int y = 0; y < 8; ++y) t += red[y][threadIdx.x];
+    out[c] = t;
+  }
 }
 
 // Rotary embedding on a packed [T, row_stride] buffer holding n_heads heads of size d starting
@@ -433,20 +444,24 @@ extern "C" int fmsb_rmsnorm_bwd(const void* dy, const void* x, const void* w, co
     if (n_partial_blocks <= 0) return -2;
     grid = n_partial_blocks;
   }
-  const bool small = H <= 8 * NORM_THREADS * 2;
+  // vectors of 8 cached per thread: the fewer, the more CTAs (rows in flight) an SM holds
+  const int maxv = H <= 8 * NORM_THREADS ? 1 : (H <= 8 * NORM_THREADS * 2 ? 2 : 4);
 #define FMSB_NORM_BWD(T, MAXV, DW)                                                                                  \
   rmsnorm_bwd_kernel<T, MAXV, DW><<<grid, NORM_THREADS, 0, stream>>>((const T*)dy, (const T*)x, (const T*)w, inv_rms, \
                                                                      (const T*)dres_in, (T*)dx, dw_partial, rows, H, gemma)
-  if (dtype == 1) {
-    if (dw_partial != nullptr) { if (small) FMSB_NORM_BWD(__nv_bfloat16, 2, true); else FMSB_NORM_BWD(__nv_bfloat16, 4, true); }
-    else { if (small) FMSB_NORM_BWD(__nv_bfloat16, 2, false); else FMSB_NORM_BWD(__nv_bfloat16, 4, false); }
-  } else {
-    if (dw_partial != nullptr) { if (small) FMSB_NORM_BWD(__half, 2, true); else FMSB_NORM_BWD(__half, 4, true); }
-    else { if (small) FMSB_NORM_BWD(__half, 2, false); else FMSB_NORM_BWD(__half, 4, false); }
+#define FMSB_NORM_BWD_T(T)                                                                     \
+  if (dw_partial != nullptr) {                                                                 \
+    if (maxv == 1) FMSB_NORM_BWD(T, 1, true); else if (maxv == 2) FMSB_NORM_BWD(T, 2, true);   \
+    else FMSB_NORM_BWD(T, 4, true);                                                            \
+  } else {                                                                                     \
+    if (maxv == 1) FMSB_NORM_BWD(T, 1, false); else if (maxv == 2) FMSB_NORM_BWD(T, 2, false); \
+    else FMSB_NORM_BWD(T, 4, false);                                                           \
   }
+  if (dtype == 1) { FMSB_NORM_BWD_T(__nv_bfloat16) } else { FMSB_NORM_BWD_T(__half) }
+#undef FMSB_NORM_BWD_T
 #undef FMSB_NORM_BWD
   if (dw_partial != nullptr && dw != nullptr) {
-    colsum_kernel<<<(H + 255) / 256, 256, 0, stream>>>(dw_partial, dw, grid, H);
+    colsum_kernel<<<(H + 31) / 32, dim3(32, 8), 0, stream>>>(dw_partial, dw, grid, H);
   }
   return (int)cudaGetLastError();
 }

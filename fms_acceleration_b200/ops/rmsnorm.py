@@ -42,7 +42,7 @@ def _bwd_native(dy2, h2, w, inv, gemma, dres2, need_dw):
     dw = partial = None
     nblk = 0
     if need_dw:
-        nblk = min(rows, 148 * 2)
+        nblk = min(rows, 148 * (4 if H <= 2048 else 2))  # CTAs of the launch, one partial row of dw each
         partial = torch.empty(nblk, H, dtype=torch.float32, device=h2.device)
         dw = torch.empty(H, dtype=torch.float32, device=h2.device)
     rc = N.lib().fmsb_rmsnorm_bwd(dy2.data_ptr(), h2.data_ptr(), w.data_ptr(), inv.data_ptr(), N.ptr(dres2),
