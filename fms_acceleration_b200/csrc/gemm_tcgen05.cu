@@ -13,10 +13,12 @@
 //   b_mn = 0 : B stored [N, K] row-major          b_mn = 1 : B stored [K, N] row-major
 // so y = x W^T, dx = dy W and dW = dy^T x are all served without a transposed copy.
 //
-// Structure of one CTA (192 threads, one CTA per SM, persistent over output tiles):
+// Structure of one CTA (320 threads, one CTA per SM, persistent over output tiles):
 //   warp 0      : TMA producer  (cp.async.bulk.tensor, 128-byte swizzle, no multicast)
 //   warp 1      : MMA issuer    (one lane issues tcgen05.mma, 128 x BN x 16 per instruction)
-//   warps 2..5  : epilogue      (tcgen05.ld of the fp32 accumulator, scale/add, 16-byte stores)
+//   warps 2..9  : epilogue      (tcgen05.ld of the fp32 accumulator, scale/add, 16-byte stores); two warps per
+//                 tensor-memory lane quarter, taking the even and the odd 32-column chunks of the tile, so that a
+//                 short main loop (K of a few hundred) still covers the epilogue of the previous tile
 // The accumulator is double buffered in tensor memory (2 x BN columns) so the epilogue of
 // tile i overlaps the main loop of tile i+1.  All mbarrier waits are bounded (common.cuh).
 //
@@ -31,6 +33,8 @@ namespace fmsb {
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int GROUP_M = 16;
+constexpr int kGemmThreads = 320;   // 2 + 8 warps
+constexpr int kEpilogueThreads = 256;
 
 struct GemmParams {
   int M, N;
@@ -172,7 +176,7 @@ __device__ __forceinline__ bool get_tile(int t, const GemmParams& p, TileInfo& t
 }
 
 template <int BN, int A_MN, int B_MN>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
                     const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
                     const GemmParams p) {
@@ -199,7 +203,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_const
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 128);
+      mbar_init(tempty_bar(a), kEpilogueThreads);
     }
     fence_barrier_init();
   }
@@ -311,8 +315,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_const
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (4 warps)
-    const int q = warp & 3;  // tensor-memory lane quarter this warp may read
+    // ------------------------------------------------------------------ epilogue (8 warps)
+    const int q = warp & 3;           // tensor-memory lane quarter this warp may read
+    const int cpar = (warp - 2) >> 2;  // 0: even column chunks, 1: odd column chunks
     const int row = q * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -326,7 +331,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_const
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
 #pragma unroll 1
-      for (int c = 0; c < BN / CH; ++c) {
+      for (int c = cpar; c < BN / CH; c += 2) {
         float v[CH];
         if constexpr (CH == 32) {
           uint32_t r[32];
@@ -496,7 +501,7 @@ int launch_gemm(const CUtensorMap& a1, const CUtensorMap& b1, const CUtensorMap&
     if (tiles < ctas) ctas = tiles;
   }
   if (ctas <= 0) return 0;
-  kern<<<ctas, 192, Cfg::kSmemBytes, stream>>>(a1, b1, a2, b2, p);
+  kern<<<ctas, fmsb::kGemmThreads, Cfg::kSmemBytes, stream>>>(a1, b1, a2, b2, p);
   return static_cast<int>(cudaGetLastError());
 }
 
