@@ -174,38 +174,65 @@ __global__ void allreduce_bucket_kernel(PeerPtrs buckets, PeerPtrs signals, long
   __syncthreads();
   if (!ok_sh) return;
 
-  // ---- phase 2: reduce own slice, push the result to all ranks
+  // ---- phase 2: reduce own slice, push the result to all ranks.  A thread keeps U vectors of two peers in
+  // flight (2 * U independent 16-byte loads), so that a few CTAs already cover the NVLink latency.
+  constexpr int U = 4;
   const long long n_own = n / world;  // n is padded to a multiple of world * V by the caller
   const long long nvec = n_own / V;
   const long long base = (long long)rank * n_own;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
-       i += (long long)gridDim.x * blockDim.x) {
-    float acc[V];
-#pragma unroll
-    for (int k = 0; k < V; ++k) acc[k] = 0.f;
-    for (int rr = 0; rr < world; ++rr) {
-      const int r = (rank + rr) % world;
-      const uint4 v = *(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(buckets.p[r]) + base) + i);
-      const T* e = reinterpret_cast<const T*>(&v);
-#pragma unroll
-      for (int k = 0; k < V; ++k) {
-        if (sizeof(T) == 4) acc[k] += *reinterpret_cast<const float*>(e + k);
-        else if (std::is_same<T, __nv_bfloat16>::value) acc[k] += __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(e + k));
-        else acc[k] += __half2float(*reinterpret_cast<const __half*>(e + k));
-      }
-    }
-    uint4 outv;
-    T* oe = reinterpret_cast<T*>(&outv);
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  auto add_vec = [](float (&acc)[V], const uint4& v) {
+    const T* e = reinterpret_cast<const T*>(&v);
 #pragma unroll
     for (int k = 0; k < V; ++k) {
-      const float v = acc[k] * scale;
-      if (sizeof(T) == 4) *reinterpret_cast<float*>(oe + k) = v;
-      else if (std::is_same<T, __nv_bfloat16>::value) *reinterpret_cast<__nv_bfloat16*>(oe + k) = __float2bfloat16_rn(v);
-      else *reinterpret_cast<__half*>(oe + k) = __float2half_rn(v);
+      if (sizeof(T) == 4) acc[k] += *reinterpret_cast<const float*>(e + k);
+      else if (std::is_same<T, __nv_bfloat16>::value) acc[k] += __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(e + k));
+      else acc[k] += __half2float(*reinterpret_cast<const __half*>(e + k));
     }
-    for (int rr = 0; rr < world; ++rr) {
-      const int r = (rank + rr) % world;
-      *(reinterpret_cast<uint4*>(reinterpret_cast<T*>(buckets.p[r]) + base) + i) = outv;
+  };
+  for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * U) {
+    float acc[U][V];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int k = 0; k < V; ++k) acc[u][k] = 0.f;
+    for (int rr = 0; rr < world; rr += 2) {
+      const bool two = rr + 1 < world;
+      const uint4* pa = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(buckets.p[(rank + rr) % world]) + base);
+      const uint4* pb = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(buckets.p[(rank + rr + (two ? 1 : 0)) % world]) + base);
+      uint4 va[U], vb[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        va[u] = vb[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (i < nvec) {
+          va[u] = pa[i];
+          if (two) vb[u] = pb[i];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        add_vec(acc[u], va[u]);
+        if (two) add_vec(acc[u], vb[u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= nvec) continue;
+      uint4 outv;
+      T* oe = reinterpret_cast<T*>(&outv);
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        const float v = acc[u][k] * scale;
+        if (sizeof(T) == 4) *reinterpret_cast<float*>(oe + k) = v;
+        else if (std::is_same<T, __nv_bfloat16>::value) *reinterpret_cast<__nv_bfloat16*>(oe + k) = __float2bfloat16_rn(v);
+        else *reinterpret_cast<__half*>(oe + k) = __float2half_rn(v);
+      }
+      for (int rr = 0; rr < world; ++rr) {
+        const int r = (rank + rr) % world;
+        *(reinterpret_cast<uint4*>(reinterpret_cast<T*>(buckets.p[r]) + base) + i) = outv;
+      }
     }
   }
   // ---- phase 3: everyone's pushes are visible before anybody reads its bucket

@@ -96,8 +96,13 @@ class Communicator:
         N.check(rc, "fmsb_comm_allgather")
 
     def allreduce_(self, bucket: SymmBuffer, numel: int, dtype: torch.dtype, scale: Optional[float] = None,
-                   chan: int = 2, ctas: int = 32) -> None:
-        """In-place sum (times ``scale``, default 1/world) of the first ``numel`` elements of a symmetric bucket."""
+                   chan: int = 2, ctas: Optional[int] = None) -> None:
+        """In-place sum (times ``scale``, default 1/world) of the first ``numel`` elements of a symmetric bucket.
+        ``ctas`` defaults to 32 for adapter-sized buckets and to 128 for buckets of 32 MiB and more (a full
+        fine-tune's gradients), which runs at the end of the backward when nothing else needs the SMs."""
+        if ctas is None:
+            nbytes = numel * torch.empty((), dtype=dtype).element_size()
+            ctas = 32 if nbytes < (32 << 20) else 128
         st = N.status_word(self.device)
         scale = 1.0 / self.world if scale is None else scale
         self.epochs[chan + 1] = self.epochs[chan] + 1
