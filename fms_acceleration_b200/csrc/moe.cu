@@ -333,37 +333,62 @@ __global__ void __launch_bounds__(kAssignChunk) moe_assign_kernel(const int* __r
 // ----------------------------------------------------------------------------------------
 // dispatch / combine
 // ----------------------------------------------------------------------------------------
-// For every (token t, k): owner_buf[dest_row][:] = x[t][:] * (scale ? scale[t, k] : 1).  One warp per pair.
-template <typename T>
-__global__ void moe_dispatch_kernel(const T* __restrict__ x, long long ldx, const int* __restrict__ topk_idx,
-                                    const int* __restrict__ dest_row, const float* __restrict__ scale, long long n_pairs,
-                                    int k, int H, int E_local, MoePeers recv, long long ld_recv,
-                                    const float* __restrict__ meta_vals, MoePeers meta_recv) {
-  const long long pair = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+// For every (token t, k): owner_buf[dest_row][:] = x[t][:] * (scale ? scale[t, k] : 1).  One warp per TOKEN: the
+// row is read once into registers (up to 8 vectors of 16 bytes per lane at a time) and stored to its k
+// destinations; lanes 0..k-1 fetch the (owner, row, scale) of the k pairs and hand them round by shuffle.
+template <typename T, bool SCALED>
+__global__ void __launch_bounds__(256) moe_dispatch_kernel(const T* __restrict__ x, long long ldx,
+                                                           const int* __restrict__ topk_idx,
+                                                           const int* __restrict__ dest_row,
+                                                           const float* __restrict__ scale, long long n_tokens, int k,
+                                                           int H, int E_local, MoePeers recv, long long ld_recv,
+                                                           const float* __restrict__ meta_vals, MoePeers meta_recv) {
+  const long long t = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
-  if (pair >= n_pairs) return;
-  const long long t = pair / k;
-  const int owner = topk_idx[pair] / E_local;
-  const long long row = dest_row[pair];
-  if (row < 0) return;  // dropped pair
+  if (t >= n_tokens) return;
+  int my_owner = 0, my_row = -1;
+  float my_scale = 1.f;
+  if (lane < k) {
+    const long long pair = t * k + lane;
+    my_owner = topk_idx[pair] / E_local;
+    my_row = dest_row[pair];
+    if (SCALED) my_scale = scale[pair];
+    // optional per-row scalar travelling with the row (the routing weight in the backward pass)
+    if (meta_vals != nullptr && my_row >= 0) reinterpret_cast<float*>(meta_recv.p[my_owner])[my_row] = meta_vals[pair];
+  }
   const T* src = x + t * ldx;
-  T* dst = reinterpret_cast<T*>(recv.p[owner]) + row * ld_recv;
-  const float sc = scale != nullptr ? scale[pair] : 1.f;
-  // optional per-row scalar travelling with the row (the routing weight in the backward pass)
-  if (meta_vals != nullptr && lane == 0) reinterpret_cast<float*>(meta_recv.p[owner])[row] = meta_vals[pair];
-  for (int c = lane * 8; c < H; c += 256) {
-    uint4 v = *reinterpret_cast<const uint4*>(src + c);
-    if (scale != nullptr) {
-      T* e = reinterpret_cast<T*>(&v);
+  const int nvec = H >> 3;
+  for (int v0 = 0; v0 < nvec; v0 += 256) {
+    uint4 v[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        if (std::is_same<T, __nv_bfloat16>::value)
-          reinterpret_cast<__nv_bfloat16*>(e)[i] = __float2bfloat16_rn(__bfloat162float(reinterpret_cast<__nv_bfloat16*>(e)[i]) * sc);
-        else
-          reinterpret_cast<__half*>(e)[i] = __float2half_rn(__half2float(reinterpret_cast<__half*>(e)[i]) * sc);
+    for (int j = 0; j < 8; ++j) {
+      const int vi = v0 + lane + 32 * j;
+      if (vi < nvec) v[j] = *reinterpret_cast<const uint4*>(src + vi * 8);
+    }
+    for (int s = 0; s < k; ++s) {
+      const int owner = __shfl_sync(0xffffffffu, my_owner, s);
+      const int row = __shfl_sync(0xffffffffu, my_row, s);
+      const float sc = __shfl_sync(0xffffffffu, my_scale, s);
+      if (row < 0) continue;  // dropped pair
+      T* dst = reinterpret_cast<T*>(recv.p[owner]) + (long long)row * ld_recv;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int vi = v0 + lane + 32 * j;
+        if (vi >= nvec) continue;
+        uint4 o = v[j];
+        if (SCALED) {
+          T* e = reinterpret_cast<T*>(&o);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            if (std::is_same<T, __nv_bfloat16>::value)
+              reinterpret_cast<__nv_bfloat16*>(e)[i] = __float2bfloat16_rn(__bfloat162float(reinterpret_cast<__nv_bfloat16*>(e)[i]) * sc);
+            else
+              reinterpret_cast<__half*>(e)[i] = __float2half_rn(__half2float(reinterpret_cast<__half*>(e)[i]) * sc);
+          }
+        }
+        *reinterpret_cast<uint4*>(dst + vi * 8) = o;
       }
     }
-    *reinterpret_cast<uint4*>(dst + c) = v;
   }
 }
 
@@ -383,43 +408,83 @@ __global__ void moe_zero_pad_kernel(T* __restrict__ buf, long long ld, int H, co
 }
 
 // out[t][:] = sum_k w[t, k] * owner_buf(t, k)[dest_row(t, k)][:]   (w == nullptr: plain sum).  One warp per token;
-// the expert outputs are read from the owners' buffers (peer loads when remote).
+// the expert outputs are read from the owners' buffers (peer loads when remote).  Lanes 0..k-1 fetch the pair
+// metadata once; the rows of two pairs (8 vectors of 16 bytes per lane) are in flight together.
 template <typename T>
-__global__ void moe_combine_kernel(MoePeers ybuf, long long ldy, const int* __restrict__ topk_idx,
-                                   const int* __restrict__ dest_row, const float* __restrict__ w, long long T_tokens,
-                                   int k, int H, int E_local, T* __restrict__ out, long long ldo) {
+__device__ __forceinline__ void combine_add(float (&acc)[8], const uint4& v, float ws) {
+  const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float f = std::is_same<T, __nv_bfloat16>::value
+                        ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(e)[i])
+                        : __half2float(reinterpret_cast<const __half*>(e)[i]);
+    acc[i] += ws * f;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) moe_combine_kernel(MoePeers ybuf, long long ldy, const int* __restrict__ topk_idx,
+                                                          const int* __restrict__ dest_row, const float* __restrict__ w,
+                                                          long long T_tokens, int k, int H, int E_local,
+                                                          T* __restrict__ out, long long ldo) {
   const long long t = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (t >= T_tokens) return;
-  for (int c = lane * 8; c < H; c += 256) {
-    float acc[8];
+  int my_owner = 0, my_row = -1;
+  float my_w = 1.f;
+  if (lane < k) {
+    const long long pair = t * k + lane;
+    my_owner = topk_idx[pair] / E_local;
+    my_row = dest_row[pair];
+    if (w != nullptr) my_w = w[pair];
+  }
+  constexpr int CV = 4;  // vectors of 16 bytes per lane and pass (1024 columns per pass)
+  const int nvec = H >> 3;
+  for (int v0 = 0; v0 < nvec; v0 += 32 * CV) {
+    float acc[CV][8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-    for (int s = 0; s < k; ++s) {
-      const long long pair = t * k + s;
-      if (dest_row[pair] < 0) continue;  // dropped pair contributes nothing
-      const int owner = topk_idx[pair] / E_local;
-      const T* src = reinterpret_cast<const T*>(ybuf.p[owner]) + (long long)dest_row[pair] * ldy + c;
-      const uint4 v = *reinterpret_cast<const uint4*>(src);
-      const float ws = w != nullptr ? w[pair] : 1.f;
-      const T* e = reinterpret_cast<const T*>(&v);
+    for (int j = 0; j < CV; ++j)
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float f = std::is_same<T, __nv_bfloat16>::value
-                            ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(e)[i])
-                            : __half2float(reinterpret_cast<const __half*>(e)[i]);
-        acc[i] += ws * f;
+      for (int i = 0; i < 8; ++i) acc[j][i] = 0.f;
+    for (int s = 0; s < k; s += 2) {
+      const int o0 = __shfl_sync(0xffffffffu, my_owner, s), r0 = __shfl_sync(0xffffffffu, my_row, s);
+      const float w0 = __shfl_sync(0xffffffffu, my_w, s);
+      const int s1 = s + 1 < k ? s + 1 : s;
+      const int o1 = __shfl_sync(0xffffffffu, my_owner, s1);
+      const int r1 = s + 1 < k ? __shfl_sync(0xffffffffu, my_row, s1) : -1;
+      const float w1 = __shfl_sync(0xffffffffu, my_w, s1);
+      const T* p0 = reinterpret_cast<const T*>(ybuf.p[o0]) + (long long)(r0 < 0 ? 0 : r0) * ldy;
+      const T* p1 = reinterpret_cast<const T*>(ybuf.p[o1]) + (long long)(r1 < 0 ? 0 : r1) * ldy;
+      uint4 a[CV], b[CV];
+#pragma unroll
+      for (int j = 0; j < CV; ++j) {
+        const int vi = v0 + lane + 32 * j;
+        a[j] = b[j] = make_uint4(0u, 0u, 0u, 0u);
+        if (vi < nvec) {
+          if (r0 >= 0) a[j] = *reinterpret_cast<const uint4*>(p0 + vi * 8);  // a dropped pair contributes nothing
+          if (r1 >= 0) b[j] = *reinterpret_cast<const uint4*>(p1 + vi * 8);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < CV; ++j) {
+        combine_add<T>(acc[j], a[j], w0);
+        combine_add<T>(acc[j], b[j], w1);
       }
     }
-    uint4 o;
-    if (std::is_same<T, __nv_bfloat16>::value) {
-      o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
-      o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
-    } else {
-      o.x = pack_f16x2(acc[0], acc[1]); o.y = pack_f16x2(acc[2], acc[3]);
-      o.z = pack_f16x2(acc[4], acc[5]); o.w = pack_f16x2(acc[6], acc[7]);
+#pragma unroll
+    for (int j = 0; j < CV; ++j) {
+      const int vi = v0 + lane + 32 * j;
+      if (vi >= nvec) continue;
+      uint4 o;
+      if (std::is_same<T, __nv_bfloat16>::value) {
+        o.x = pack_bf16x2(acc[j][0], acc[j][1]); o.y = pack_bf16x2(acc[j][2], acc[j][3]);
+        o.z = pack_bf16x2(acc[j][4], acc[j][5]); o.w = pack_bf16x2(acc[j][6], acc[j][7]);
+      } else {
+        o.x = pack_f16x2(acc[j][0], acc[j][1]); o.y = pack_f16x2(acc[j][2], acc[j][3]);
+        o.z = pack_f16x2(acc[j][4], acc[j][5]); o.w = pack_f16x2(acc[j][6], acc[j][7]);
+      }
+      *reinterpret_cast<uint4*>(out + t * ldo + vi * 8) = o;
     }
-    *reinterpret_cast<uint4*>(out + t * ldo + c) = o;
   }
 }
 
@@ -565,13 +630,15 @@ extern "C" int fmsb_moe_dispatch(const void* x, long long ldx, const int* topk_i
                                  const float* scale, long long n_pairs, int k, int H, int E_local, void* const* recv,
                                  long long ld_recv, int world, int dtype, cudaStream_t stream) {
   if (n_pairs <= 0) return 0;
-  if (H % 8 != 0 || ldx % 8 != 0 || ld_recv % 8 != 0) return -2;
+  if (H % 8 != 0 || ldx % 8 != 0 || ld_recv % 8 != 0 || k < 1 || k > 32 || n_pairs % k != 0) return -2;
   MoePeers r = moe_ptrs(recv, world);
-  const long long blocks = (n_pairs * 32 + 255) / 256;
-  if (dtype == 1)
-    moe_dispatch_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, topk_idx, dest_row, scale, n_pairs, k, H, E_local, r, ld_recv, nullptr, MoePeers{});
-  else
-    moe_dispatch_kernel<__half><<<(unsigned)blocks, 256, 0, stream>>>((const __half*)x, ldx, topk_idx, dest_row, scale, n_pairs, k, H, E_local, r, ld_recv, nullptr, MoePeers{});
+  const long long n_tokens = n_pairs / k;
+  const long long blocks = (n_tokens * 32 + 255) / 256;
+#define FMSB_DISPATCH_CALL(T, SC) \
+  moe_dispatch_kernel<T, SC><<<(unsigned)blocks, 256, 0, stream>>>((const T*)x, ldx, topk_idx, dest_row, scale, n_tokens, k, H, E_local, r, ld_recv, nullptr, MoePeers{})
+  if (dtype == 1) { if (scale != nullptr) FMSB_DISPATCH_CALL(__nv_bfloat16, true); else FMSB_DISPATCH_CALL(__nv_bfloat16, false); }
+  else { if (scale != nullptr) FMSB_DISPATCH_CALL(__half, true); else FMSB_DISPATCH_CALL(__half, false); }
+#undef FMSB_DISPATCH_CALL
   return (int)cudaGetLastError();
 }
 
@@ -581,13 +648,15 @@ extern "C" int fmsb_moe_dispatch_meta(const void* x, long long ldx, const int* t
                                       void* const* recv, long long ld_recv, void* const* meta_recv, int world, int dtype,
                                       cudaStream_t stream) {
   if (n_pairs <= 0) return 0;
-  if (H % 8 != 0 || ldx % 8 != 0 || ld_recv % 8 != 0 || meta_vals == nullptr) return -2;
+  if (H % 8 != 0 || ldx % 8 != 0 || ld_recv % 8 != 0 || meta_vals == nullptr || k < 1 || k > 32 || n_pairs % k != 0)
+    return -2;
   MoePeers r = moe_ptrs(recv, world), m = moe_ptrs(meta_recv, world);
-  const long long blocks = (n_pairs * 32 + 255) / 256;
+  const long long n_tokens = n_pairs / k;
+  const long long blocks = (n_tokens * 32 + 255) / 256;
   if (dtype == 1)
-    moe_dispatch_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, topk_idx, dest_row, nullptr, n_pairs, k, H, E_local, r, ld_recv, meta_vals, m);
+    moe_dispatch_kernel<__nv_bfloat16, false><<<(unsigned)blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, topk_idx, dest_row, nullptr, n_tokens, k, H, E_local, r, ld_recv, meta_vals, m);
   else
-    moe_dispatch_kernel<__half><<<(unsigned)blocks, 256, 0, stream>>>((const __half*)x, ldx, topk_idx, dest_row, nullptr, n_pairs, k, H, E_local, r, ld_recv, meta_vals, m);
+    moe_dispatch_kernel<__half, false><<<(unsigned)blocks, 256, 0, stream>>>((const __half*)x, ldx, topk_idx, dest_row, nullptr, n_tokens, k, H, E_local, r, ld_recv, meta_vals, m);
   return (int)cudaGetLastError();
 }
 
@@ -628,7 +697,7 @@ extern "C" int fmsb_moe_combine(void* const* ybuf, long long ldy, const int* top
                                 const float* w, long long T_tokens, int k, int H, int E_local, void* out, long long ldo,
                                 int world, int dtype, cudaStream_t stream) {
   if (T_tokens <= 0) return 0;
-  if (H % 8 != 0 || ldy % 8 != 0 || ldo % 8 != 0) return -2;
+  if (H % 8 != 0 || ldy % 8 != 0 || ldo % 8 != 0 || k < 1 || k > 32) return -2;
   MoePeers y = moe_ptrs(ybuf, world);
   const long long blocks = (T_tokens * 32 + 255) / 256;
   if (dtype == 1)
