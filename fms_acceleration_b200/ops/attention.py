@@ -55,6 +55,12 @@ def attention_ref(q, k, v, doc_start, scale=None):
 # (csrc/attention_bwd.cu, kept as an independent cross-check of the same mathematics).
 BWD_GENERATION = int(os.environ.get("FMSB_ATTN_BWD", "3"))
 
+# The reference asks flash-attn for a deterministic backward when FLASH_ATTENTION_DETERMINISTIC is set
+# (fms_acceleration_aadp/flash_attn.py:152).  Here the variable is accepted and changes nothing: dQ and dK/dV are
+# produced by separate kernels that each own their output rows, so no gradient is accumulated with atomics and two
+# runs of the same step give the same bits.
+DETERMINISTIC_BACKWARD = True
+
 
 def _fwd(q2, k2, v2, doc_start, doc_end, nh, nkv, d, scale):
     T = q2.shape[0]
