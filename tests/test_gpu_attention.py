@@ -83,3 +83,22 @@ def test_backward_generations_agree(d, nh, nkv):
     NV.check_status()
     for a, b in zip(g3, g2):
         assert _rel(a, b) < 5e-3
+
+
+def test_backward_is_bitwise_reproducible():
+    """No gradient is accumulated with atomics: two runs of the same backward give the same bits."""
+    lens = [700, 129, 1, 450]
+    T, nh, nkv, d = sum(lens), 8, 2, 128
+    qkv, ds, de = _make(T, nh, nkv, d, lens, torch.bfloat16, seed=3)
+    grads = []
+    for _ in range(2):
+        q = qkv[:, : nh * d].reshape(T, nh, d).clone().requires_grad_()
+        k = qkv[:, nh * d: (nh + nkv) * d].reshape(T, nkv, d).clone().requires_grad_()
+        v = qkv[:, (nh + nkv) * d:].reshape(T, nkv, d).clone().requires_grad_()
+        o = AT.varlen_attention(q, k, v, ds, de)
+        torch.manual_seed(11)
+        o.backward(torch.randn_like(o))
+        NV.check_status()
+        grads.append((o.detach().clone(), q.grad.clone(), k.grad.clone(), v.grad.clone()))
+    for a, b in zip(*grads):
+        assert torch.equal(a, b)
