@@ -292,16 +292,32 @@ __global__ void __launch_bounds__(kAssignChunk) moe_assign_count_kernel(const in
   }
 }
 
-__global__ void moe_assign_scan_kernel(int* __restrict__ chunk_cnt, int n_chunks, int E,
-                                       const int* __restrict__ send_base) {
-  const int e = blockIdx.x * blockDim.x + threadIdx.x;
-  if (e >= E) return;
-  int run = send_base[e];
-#pragma unroll 8
-  for (int c = 0; c < n_chunks; ++c) {
-    const int v = chunk_cnt[(long long)c * E + e];
-    chunk_cnt[(long long)c * E + e] = run;
-    run += v;
+// one CTA of 256 threads per expert: block-wide exclusive scan over the chunks, 256 chunks per trip
+__global__ void __launch_bounds__(256) moe_assign_scan_kernel(int* __restrict__ chunk_cnt, int n_chunks, int E,
+                                                              const int* __restrict__ send_base) {
+  __shared__ int warp_tot[8];
+  __shared__ int running;
+  const int e = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) running = send_base[e];
+  __syncthreads();
+  for (int c0 = 0; c0 < n_chunks; c0 += 256) {
+    const int c = c0 + threadIdx.x;
+    const int v = c < n_chunks ? chunk_cnt[(long long)c * E + e] : 0;
+    int incl = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += up;
+    }
+    if (lane == 31) warp_tot[warp] = incl;
+    __syncthreads();
+    int before = running;
+    for (int w = 0; w < warp; ++w) before += warp_tot[w];
+    if (c < n_chunks) chunk_cnt[(long long)c * E + e] = before + incl - v;
+    __syncthreads();
+    if (threadIdx.x == 255) running = before + incl;
+    __syncthreads();
   }
 }
 
@@ -620,7 +636,7 @@ extern "C" int fmsb_moe_plan(const int* topk_idx, long long n_pairs, int E, int 
       cudaFuncSetAttribute(moe_assign_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     }
     moe_assign_count_kernel<<<n_chunks, kAssignChunk, smem, stream>>>(topk_idx, n_pairs, E, chunk_scratch);
-    moe_assign_scan_kernel<<<(E + 127) / 128, 128, 0, stream>>>(chunk_scratch, n_chunks, E, send_base);
+    moe_assign_scan_kernel<<<E, 256, 0, stream>>>(chunk_scratch, n_chunks, E, send_base);
     moe_assign_kernel<<<n_chunks, kAssignChunk, smem, stream>>>(topk_idx, n_pairs, E, chunk_scratch, send_base, dest_row);
   }
   return (int)cudaGetLastError();
