@@ -106,9 +106,15 @@ class ProjGroup:
                 b.dequantize(out=W[:, o0:o1], dtype=dtype)  # written in place through the row stride
         return W, True
 
-    def lora_cat(self, dtype, device):
+    def lora_cat(self, dtype, device, reuse: bool = False):
         """(A_cat [R_pad, in], B_blk [total_out, R_pad], slices) with the scaling folded into B_blk; R is padded
         with zero rows/columns to a multiple of 8."""
+        # the backward of a step asks for the same matrices as its forward built (``reuse``); a forward always
+        # rebuilds them, so an optimizer that updates the adapters through a flat buffer is seen as well
+        key = (dtype, tuple((id(p), p._version) for l in self.loras if l is not None for p in _lora_parts(l)[:2]))
+        cached = getattr(self, "_lora_cat_cache", None)
+        if reuse and cached is not None and cached[0] == key:
+            return cached[1]
         As, R = [], 0
         slices = []
         for l in self.loras:
@@ -129,6 +135,7 @@ class ProjGroup:
                 continue
             _, B, s = _lora_parts(l)
             B_blk[o0:o1, sl[0]:sl[1]] = B.to(dtype) * s
+        self._lora_cat_cache = (key, (A_cat, B_blk, slices))
         return A_cat, B_blk, slices
 
     # ------------------------------------------------------------------ forward
@@ -187,7 +194,7 @@ class ProjGroup:
         A_cat = None
         mask = aux.get("mask") if aux else None
         if self.has_lora:
-            A_cat, B_blk, slices = self.lora_cat(dtype, dev)
+            A_cat, B_blk, slices = self.lora_cat(dtype, dev, reuse=True)
             R = A_cat.shape[0]
             # dxa = dy @ B_blk  (already carries the scaling)
             dxa_s = gemm(dy, B_blk, b_mn=True)
