@@ -175,10 +175,96 @@ def bench_elementwise(a):
     print(json.dumps({"kernel": "swiglu_fwd", "ms": t, "gbs": by / t / 1e6, "frac_of_%s_hbm" % pk["source"]: by / t / 1e6 / pk["hbm_gbs"]}))
 
 
+def _line(kernel, ms, nbytes, pk, **extra):
+    d = {"kernel": kernel, "ms": ms, "gbs": nbytes / ms / 1e6,
+         "frac_of_%s_hbm" % pk["source"]: nbytes / ms / 1e6 / pk["hbm_gbs"]}
+    d.update(extra)
+    print(json.dumps(d))
+
+
+def bench_mamba(a):
+    """Mamba2 pieces at the per-rank shape of the context-parallel benchmark (80 heads x 64, state 128, chunk 256):
+    conv1d forward / backward, the decay-matrix builder, the masked head-sum of dG and the whole scan."""
+    from fms_acceleration_b200 import _native as NV
+    from fms_acceleration_b200.ops import mamba as MB
+
+    pk = peaks()
+    T, nh, P, G, N, Q = a.tokens, a.heads, a.head_dim, 1, a.state, a.chunk
+    nc = T // Q
+    dev, dt16 = "cuda", torch.bfloat16
+    Cc = nh * P + 2 * G * N
+    xc = torch.randn(T, Cc, device=dev, dtype=dt16)
+    w = (torch.randn(Cc, 4, device=dev) * 0.5).to(dt16)
+    b = torch.randn(Cc, device=dev, dtype=dt16)
+    t = timeit(lambda: MB.causal_conv1d(xc, w, b), a.iters, a.warmup, a.flush)
+    _line("conv1d_fwd", t, 2.0 * T * Cc * 2, pk)
+    xg = xc.clone().requires_grad_()
+    y = MB.causal_conv1d(xg, w, b)
+    gy = torch.randn_like(y)
+    t = timeit(lambda: torch.autograd.grad(y, xg, gy, retain_graph=True), a.iters, a.warmup, a.flush)
+    _line("conv1d_bwd", t, 3.0 * T * Cc * 2, pk)
+    # decay-matrix builder and masked head-sum on their own
+    cb = torch.randn(nc * G * Q, Q, device=dev, dtype=dt16)
+    dtv = torch.rand(T, nh, device=dev) * 0.05 + 0.001
+    A = -(torch.rand(nh, device=dev) * 4 + 0.5)
+    dtt = MB._chunk_major(dtv, nc, Q, nh)
+    Lt = (dtt * A[None, :, None]).cumsum(-1)
+    t = timeit(lambda: MB._make_g(cb, Lt, dtt, nc, nh, G, Q), a.iters, a.warmup, a.flush)
+    _line("ssd_make_g2", t, nc * nh * Q * Q * 2.0, pk, note="bytes written; the lower triangle is computed, the rest zero-filled")
+    dG = torch.randn(nc * nh * Q, Q, device=dev, dtype=dt16)
+    dcb = torch.empty(nc * G * Q, Q, device=dev, dtype=dt16)
+
+    def run_dcb():
+        NV.check(NV.lib().fmsb_ssd_dcb(dG.data_ptr(), Lt.data_ptr(), dtt.data_ptr(), dcb.data_ptr(), nc, nh, G, Q,
+                                       NV.dtype_code(dt16), NV.stream_ptr()), "fmsb_ssd_dcb")
+
+    t = timeit(run_dcb, a.iters, a.warmup, a.flush)
+    _line("ssd_dcb", t, nc * nh * Q * Q * 2.0 / 2, pk, note="bytes read: the lower triangle of dG")
+    # whole scan
+    x = (torch.randn(T, nh, P, device=dev) * 0.5).to(dt16).requires_grad_()
+    B = (torch.randn(T, G, N, device=dev) * 0.3).to(dt16).requires_grad_()
+    C = (torch.randn(T, G, N, device=dev) * 0.3).to(dt16).requires_grad_()
+    D = torch.ones(nh, device=dev)
+    dtp = dtv.clone().requires_grad_()
+    t = timeit(lambda: MB.ssd_scan(x, dtp, A, B, C, D, None, Q), a.iters, a.warmup, a.flush)
+    print(json.dumps({"kernel": "ssd_scan_fwd", "ms": t, "tokens": T}))
+    yo, _ = MB.ssd_scan(x, dtp, A, B, C, D, None, Q)
+    go = torch.randn_like(yo)
+    t = timeit(lambda: torch.autograd.grad(yo, (x, dtp, B, C), go, retain_graph=True), a.iters, a.warmup, a.flush)
+    print(json.dumps({"kernel": "ssd_scan_bwd", "ms": t, "tokens": T}))
+    NV.check_status()
+
+
+def bench_moe(a):
+    """Single-GPU dispatch and combine of a Granite-3B-A800M layer (40 experts, top-8, hidden 1536)."""
+    from fms_acceleration_b200 import _native as NV
+    from fms_acceleration_b200.ops import moe as MOE
+
+    pk = peaks()
+    T, H, E, k = a.tokens, a.hidden, a.experts, a.top_k
+    dev = torch.device("cuda", torch.cuda.current_device())
+    x = torch.randn(T, H, device=dev, dtype=torch.bfloat16)
+    g = torch.Generator(device=dev).manual_seed(0)
+    idx = torch.rand(T, E, device=dev, generator=g).topk(k, dim=-1).indices.int().contiguous()
+    wts = torch.full((T, k), 1.0 / k, device=dev)
+    ctx = MOE.MoEContext(H, 512, E, k)
+    cap = ctx.ensure(T, x.dtype, dev)
+    seg_off, seg_cnt, dest_row = MOE._plan(ctx, idx, T, dev)
+    t = timeit(lambda: MOE._plan(ctx, idx, T, dev), a.iters, a.warmup, a.flush)
+    print(json.dumps({"kernel": "moe_plan (count + plan + 3-phase slot assignment)", "ms": t, "pairs": T * k}))
+    buf, ptrs, _ = ctx._alloc("bench_recv", cap, H, x.dtype, dev)
+    ld = buf.stride(0)
+    t = timeit(lambda: MOE._dispatch(ctx, x, idx, dest_row, None, ptrs, ld), a.iters, a.warmup, a.flush)
+    _line("moe_dispatch", t, (T * H + T * k * H) * 2.0, pk)
+    t = timeit(lambda: MOE._combine(ctx, ptrs, ld, idx, dest_row, wts, T, H, x.dtype, dev), a.iters, a.warmup, a.flush)
+    _line("moe_combine", t, (T * H + T * k * H) * 2.0, pk)
+    NV.check_status()
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="what", required=True)
-    for name in ("gemm", "attn", "elementwise", "q4gemm"):
+    for name in ("gemm", "attn", "elementwise", "q4gemm", "mamba", "moe"):
         p = sub.add_parser(name)
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--warmup", type=int, default=5)
@@ -200,12 +286,24 @@ def main(argv=None):
             p.add_argument("--kv-heads", type=int, default=8)
             p.add_argument("--head-dim", type=int, default=128)
             p.add_argument("--compare-v1", action="store_true", help="also run the earlier backward generations")
+        elif name == "mamba":
+            p.add_argument("--tokens", type=int, default=8192)
+            p.add_argument("--heads", type=int, default=80)
+            p.add_argument("--head-dim", type=int, default=64)
+            p.add_argument("--state", type=int, default=128)
+            p.add_argument("--chunk", type=int, default=256)
+        elif name == "moe":
+            p.add_argument("--tokens", type=int, default=16384)
+            p.add_argument("--hidden", type=int, default=1536)
+            p.add_argument("--experts", type=int, default=40)
+            p.add_argument("--top-k", type=int, default=8)
         else:
             p.add_argument("--tokens", type=int, default=16384)
             p.add_argument("--hidden", type=int, default=4096)
             p.add_argument("--inter", type=int, default=14336)
     a = ap.parse_args(argv)
-    {"gemm": bench_gemm, "attn": bench_attn, "elementwise": bench_elementwise, "q4gemm": bench_q4gemm}[a.what](a)
+    {"gemm": bench_gemm, "attn": bench_attn, "elementwise": bench_elementwise, "q4gemm": bench_q4gemm,
+     "mamba": bench_mamba, "moe": bench_moe}[a.what](a)
     return 0
 
 

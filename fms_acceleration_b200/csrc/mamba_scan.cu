@@ -98,83 +98,104 @@ __global__ void __launch_bounds__(256) ssd_make_g2_kernel(const T* __restrict__ 
 }
 
 // dCB[c, g, t, s] = sum_{h in g} dG[c, h, t, s] exp(L_t - L_s) dt_s  (s <= t).
-// grid (ceil(Q / (2 * rpp)), G, n), block 256, rpp = 256 / (Q / 8): a thread owns 8 columns of two rows and sums
-// the heads of the group in fp32 registers; dG [n*nh, Q, Q] (16-bit), out [n*G, Q, Q].  The head's L and dt
-// (Q values each) pass through shared memory, double-buffered, and the next head's dG vectors are loaded before
-// the current head's arithmetic.  Q <= 1024.
+// grid (ceil(Q / rpp), G, n), block 256, rpp = 256 / (Q / 8): a thread owns 8 columns of one row and sums the heads
+// of the group in fp32 registers; dG [n*nh, Q, Q] (16-bit), out [n*G, Q, Q].  Heads are taken two at a time: their L
+// and dt (Q values each) pass through shared memory, double-buffered, and the next pair's dG vectors and L/dt values
+// are loaded before the current pair's arithmetic, so a thread has two 16-byte loads and up to 16 scalars in
+// flight and the CTAs are small enough for several to share an SM.  Q <= 1024.
 template <typename T>
-__global__ void __launch_bounds__(256) ssd_dcb_kernel(const T* __restrict__ dG, const float* __restrict__ Lt,
+__global__ void __launch_bounds__(256, 4) ssd_dcb_kernel(const T* __restrict__ dG, const float* __restrict__ Lt,
                                                        const float* __restrict__ dtt, T* __restrict__ dcb, int nh,
                                                        int G, int Q) {
-  __shared__ __align__(16) float sL[2][1024];
-  __shared__ __align__(16) float sD[2][1024];
+  __shared__ __align__(16) float sL[2][2][1024];
+  __shared__ __align__(16) float sD[2][2][1024];
   const int c = blockIdx.z, gi = blockIdx.y;
   const int vpr = Q >> 3, rpp = 256 / vpr;
   const int s0 = (threadIdx.x % vpr) << 3;
-  const int ta = blockIdx.x * 2 * rpp + threadIdx.x / vpr, tb = ta + rpp;
+  const int t = blockIdx.x * rpp + threadIdx.x / vpr;
   const int hpg = nh / G;
-  const bool on_a = ta < Q && s0 <= ta, on_b = tb < Q && s0 <= tb;
-  const long long base0 = ((long long)c * nh + gi * hpg) * Q;
-  float acc_a[8], acc_b[8];
+  const bool on = t < Q && s0 <= t;
+  const long long base0 = ((long long)c * nh + gi * hpg) * Q;  // L/dt offset of the group's first head
+  float acc[8];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) acc_a[j] = acc_b[j] = 0.f;
-  // head 0 into buffer 0
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  // first pair into buffer 0
   for (int i = threadIdx.x; i < Q; i += 256) {
-    sL[0][i] = Lt[base0 + i];
-    sD[0][i] = dtt[base0 + i];
+    sL[0][0][i] = Lt[base0 + i];
+    sD[0][0][i] = dtt[base0 + i];
+    if (hpg > 1) {
+      sL[0][1][i] = Lt[base0 + Q + i];
+      sD[0][1][i] = dtt[base0 + Q + i];
+    }
   }
-  uint4 ua = make_uint4(0u, 0u, 0u, 0u), ub = ua;
-  if (on_a) ua = *reinterpret_cast<const uint4*>(dG + (base0 + ta) * Q + s0);
-  if (on_b) ub = *reinterpret_cast<const uint4*>(dG + (base0 + tb) * Q + s0);
-  for (int hh = 0; hh < hpg; ++hh) {
-    const int buf = hh & 1;
+  uint4 u0 = make_uint4(0u, 0u, 0u, 0u), u1 = u0;
+  if (on) {
+    u0 = *reinterpret_cast<const uint4*>(dG + (base0 + t) * Q + s0);
+    if (hpg > 1) u1 = *reinterpret_cast<const uint4*>(dG + (base0 + Q + t) * Q + s0);
+  }
+  for (int h0 = 0; h0 < hpg; h0 += 2) {
+    const int buf = (h0 >> 1) & 1;
     __syncthreads();  // buffer `buf` is complete; nobody still reads the other one
-    // next head: loads go out now, their results are used after this head's arithmetic
-    const bool more = hh + 1 < hpg;
-    const long long nbase = base0 + (long long)(hh + 1) * Q;
-    float nl[4], nd[4];
-    uint4 na = make_uint4(0u, 0u, 0u, 0u), nb = na;
-    if (more) {
+    const bool have1 = h0 + 1 < hpg;                  // this pair has a second head
+    const bool more0 = h0 + 2 < hpg, more1 = h0 + 3 < hpg;  // heads of the next pair
+    const long long nbase = base0 + (long long)(h0 + 2) * Q;
+    float nl[2][4], nd[2][4];
+    uint4 n0 = make_uint4(0u, 0u, 0u, 0u), n1 = n0;
+    if (more0) {
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         const int i = threadIdx.x + k * 256;
         if (i < Q) {
-          nl[k] = Lt[nbase + i];
-          nd[k] = dtt[nbase + i];
+          nl[0][k] = Lt[nbase + i];
+          nd[0][k] = dtt[nbase + i];
+          if (more1) {
+            nl[1][k] = Lt[nbase + Q + i];
+            nd[1][k] = dtt[nbase + Q + i];
+          }
         }
       }
-      if (on_a) na = *reinterpret_cast<const uint4*>(dG + (nbase + ta) * Q + s0);
-      if (on_b) nb = *reinterpret_cast<const uint4*>(dG + (nbase + tb) * Q + s0);
-    }
-    if (on_a || on_b) {
-      float ls[8], ds[8], fa[8], fb[8];
-      ld8f(&sL[buf][s0], ls);
-      ld8f(&sD[buf][s0], ds);
-      const float la = on_a ? sL[buf][ta] : 0.f, lb = on_b ? sL[buf][tb] : 0.f;
-      unpack8<T>(ua, fa);
-      unpack8<T>(ub, fb);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        if (on_a && s0 + j <= ta) acc_a[j] += fa[j] * __expf(la - ls[j]) * ds[j];
-        if (on_b && s0 + j <= tb) acc_b[j] += fb[j] * __expf(lb - ls[j]) * ds[j];
+      if (on) {
+        n0 = *reinterpret_cast<const uint4*>(dG + (nbase + t) * Q + s0);
+        if (more1) n1 = *reinterpret_cast<const uint4*>(dG + (nbase + Q + t) * Q + s0);
       }
     }
-    if (more) {
+    if (on) {
+      float ls[8], ds[8], f[8];
+      ld8f(&sL[buf][0][s0], ls);
+      ld8f(&sD[buf][0][s0], ds);
+      const float l0 = sL[buf][0][t];
+      unpack8<T>(u0, f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (s0 + j <= t) acc[j] += f[j] * __expf(l0 - ls[j]) * ds[j];
+      if (have1) {
+        ld8f(&sL[buf][1][s0], ls);
+        ld8f(&sD[buf][1][s0], ds);
+        const float l1 = sL[buf][1][t];
+        unpack8<T>(u1, f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (s0 + j <= t) acc[j] += f[j] * __expf(l1 - ls[j]) * ds[j];
+      }
+    }
+    if (more0) {
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         const int i = threadIdx.x + k * 256;
         if (i < Q) {
-          sL[buf ^ 1][i] = nl[k];
-          sD[buf ^ 1][i] = nd[k];
+          sL[buf ^ 1][0][i] = nl[0][k];
+          sD[buf ^ 1][0][i] = nd[0][k];
+          if (more1) {
+            sL[buf ^ 1][1][i] = nl[1][k];
+            sD[buf ^ 1][1][i] = nd[1][k];
+          }
         }
       }
-      ua = na;
-      ub = nb;
+      u0 = n0;
+      u1 = n1;
     }
   }
-  T* out = dcb + ((long long)c * G + gi) * Q * Q;
-  if (ta < Q) *reinterpret_cast<uint4*>(out + (long long)ta * Q + s0) = pack8<T>(acc_a);
-  if (tb < Q) *reinterpret_cast<uint4*>(out + (long long)tb * Q + s0) = pack8<T>(acc_b);
+  if (t < Q) *reinterpret_cast<uint4*>(dcb + (((long long)c * G + gi) * Q + t) * Q + s0) = pack8<T>(acc);
 }
 
 // out[row, :] = x[row, :] * w[row]   rows = T*nh, P % 8 == 0
@@ -326,7 +347,7 @@ extern "C" int fmsb_ssd_dcb(const void* dG, const float* Lt, const float* dtt, v
                             int dtype, cudaStream_t stream) {
   if (nc <= 0) return 0;
   if (Q % 8 != 0 || 256 % (Q / 8) != 0 || Q > 1024 || nh % G != 0 || nc > 65535 || G > 65535) return -2;
-  const int rows_per_cta = 2 * (256 / (Q / 8));
+  const int rows_per_cta = 256 / (Q / 8);
   const dim3 grid((Q + rows_per_cta - 1) / rows_per_cta, G, nc);
   if (dtype == 1)
     ssd_dcb_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)dG, Lt, dtt, (__nv_bfloat16*)dcb, nh, G, Q);
