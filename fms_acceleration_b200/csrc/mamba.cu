@@ -111,25 +111,34 @@ __global__ void __launch_bounds__(128) conv1d_fwd_kernel(const T* __restrict__ x
   cv_load_taps<T>(w, bias, c0, wf, bf);
 #pragma unroll
   for (int j = 0; j < 3; ++j) cv_load_row<T>(x, ldx, halo, C, c0, t0 - 3 + j, T_tokens, win[j]);
-#pragma unroll 4
-  for (int t = t0; t < t1; ++t) {
-    float cur[8], acc[8];
-    cv_unpack8<T>(*reinterpret_cast<const uint4*>(x + (long long)t * ldx + c0), cur);
-    const int s0 = seq_start != nullptr ? seq_start[t] : 0;
+  // four rows per trip: their loads go out together, then the window slides over them
+  for (int tb = t0; tb < t1; tb += 4) {
+    uint4 raw[4];
 #pragma unroll
-    for (int ch = 0; ch < 8; ++ch) {
-      float a = bf[ch] + wf[3][ch] * cur[ch];
+    for (int u = 0; u < 4; ++u)
+      if (tb + u < t1) raw[u] = *reinterpret_cast<const uint4*>(x + (long long)(tb + u) * ldx + c0);
 #pragma unroll
-      for (int j = 0; j < 3; ++j)
-        if (s0 == 0 || t - 3 + j >= s0) a += wf[j][ch] * win[j][ch];
-      acc[ch] = silu_f(a);
-    }
-    *reinterpret_cast<uint4*>(yo + (long long)t * ldo) = cv_pack8<T>(acc);
+    for (int u = 0; u < 4; ++u) {
+      const int t = tb + u;
+      if (t >= t1) break;
+      float cur[8], acc[8];
+      cv_unpack8<T>(raw[u], cur);
+      const int s0 = seq_start != nullptr ? seq_start[t] : 0;
 #pragma unroll
-    for (int ch = 0; ch < 8; ++ch) {
-      win[0][ch] = win[1][ch];
-      win[1][ch] = win[2][ch];
-      win[2][ch] = cur[ch];
+      for (int ch = 0; ch < 8; ++ch) {
+        float a = bf[ch] + wf[3][ch] * cur[ch];
+#pragma unroll
+        for (int j = 0; j < 3; ++j)
+          if (s0 == 0 || t - 3 + j >= s0) a += wf[j][ch] * win[j][ch];
+        acc[ch] = silu_f(a);
+      }
+      *reinterpret_cast<uint4*>(yo + (long long)t * ldo) = cv_pack8<T>(acc);
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        win[0][ch] = win[1][ch];
+        win[1][ch] = win[2][ch];
+        win[2][ch] = cur[ch];
+      }
     }
   }
 }
@@ -224,58 +233,76 @@ __global__ void __launch_bounds__(256, 2) conv1d_bwd_kernel(const T* __restrict_
     // output gradient of channels [0, split) comes from dy, of the rest from dy2
     const T* const gy = c0 < split ? dy + c0 : dy2 + (c0 - split);
     const long long ldg = c0 < split ? lddy : lddy2;
-    // the next row's loads are issued before this row's arithmetic
-    uint2 nx = *reinterpret_cast<const uint2*>(x + (long long)t0 * ldx + c0);
-    uint2 ng = *reinterpret_cast<const uint2*>(gy + (long long)t0 * ldg);
-#pragma unroll 2
-    for (int to = t0; to < to_end; ++to) {
-      float cur[4], g[4];
-      cv_unpack4<T>(nx, cur);
-      cv_unpack4<T>(ng, g);
-      if (to + 1 < to_end) {
-        nx = *reinterpret_cast<const uint2*>(x + (long long)(to + 1) * ldx + c0);
-        ng = *reinterpret_cast<const uint2*>(gy + (long long)(to + 1) * ldg);
+    // two output rows per trip; the next trip's four loads are issued before this trip's arithmetic
+    uint2 nx[2], ng[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      nx[u] = ng[u] = make_uint2(0u, 0u);
+      if (t0 + u < to_end) {
+        nx[u] = *reinterpret_cast<const uint2*>(x + (long long)(t0 + u) * ldx + c0);
+        ng[u] = *reinterpret_cast<const uint2*>(gy + (long long)(t0 + u) * ldg);
       }
-      const int s0 = seq_start != nullptr ? seq_start[to] : 0;
-      const bool own = to < own_end;
-      bool valid[4];
+    }
+    for (int tb = t0; tb < to_end; tb += 2) {
+      uint2 cx[2], cg[2];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) valid[j] = (s0 == 0) || (to - 3 + j >= s0);
-#pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        float p = bf[ch] + wf[3][ch] * cur[ch];
-#pragma unroll
-        for (int j = 0; j < 3; ++j)
-          if (valid[j]) p += wf[j][ch] * win[j][ch];
-        const float sg = 1.f / (1.f + __expf(-p));
-        const float d = g[ch] * sg * (1.f + p * (1.f - sg));
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (valid[j]) dxa[j][ch] += wf[j][ch] * d;
-        if (own) {
-          dba[ch] += d;
-#pragma unroll
-          for (int j = 0; j < 3; ++j)
-            if (valid[j]) dwa[j][ch] += d * win[j][ch];
-          dwa[3][ch] += d * cur[ch];
+      for (int u = 0; u < 2; ++u) {
+        cx[u] = nx[u];
+        cg[u] = ng[u];
+        const int tn = tb + 2 + u;
+        if (tn < to_end) {
+          nx[u] = *reinterpret_cast<const uint2*>(x + (long long)tn * ldx + c0);
+          ng[u] = *reinterpret_cast<const uint2*>(gy + (long long)tn * ldg);
         }
       }
-      // row to - 3 has now seen its four outputs
-      const int r = to - 3;
-      if (r >= t0 && r < own_end) {
-        *reinterpret_cast<uint2*>(dx + (long long)r * lddx + c0) = cv_pack4<T>(dxa[0]);
-      } else if (r < 0 && t0 == 0 && dhalo != nullptr) {
-        *reinterpret_cast<uint2*>(dhalo + (long long)(r + 3) * C + c0) = cv_pack4<T>(dxa[0]);
-      }
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        dxa[0][ch] = dxa[1][ch];
-        dxa[1][ch] = dxa[2][ch];
-        dxa[2][ch] = dxa[3][ch];
-        dxa[3][ch] = 0.f;
-        win[0][ch] = win[1][ch];
-        win[1][ch] = win[2][ch];
-        win[2][ch] = cur[ch];
+      for (int u = 0; u < 2; ++u) {
+        const int to = tb + u;
+        if (to >= to_end) break;
+        float cur[4], g[4];
+        cv_unpack4<T>(cx[u], cur);
+        cv_unpack4<T>(cg[u], g);
+        const int s0 = seq_start != nullptr ? seq_start[to] : 0;
+        const bool own = to < own_end;
+        bool valid[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) valid[j] = (s0 == 0) || (to - 3 + j >= s0);
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          float p = bf[ch] + wf[3][ch] * cur[ch];
+#pragma unroll
+          for (int j = 0; j < 3; ++j)
+            if (valid[j]) p += wf[j][ch] * win[j][ch];
+          const float sg = 1.f / (1.f + __expf(-p));
+          const float d = g[ch] * sg * (1.f + p * (1.f - sg));
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (valid[j]) dxa[j][ch] += wf[j][ch] * d;
+          if (own) {
+            dba[ch] += d;
+#pragma unroll
+            for (int j = 0; j < 3; ++j)
+              if (valid[j]) dwa[j][ch] += d * win[j][ch];
+            dwa[3][ch] += d * cur[ch];
+          }
+        }
+        // row to - 3 has now seen its four outputs
+        const int r = to - 3;
+        if (r >= t0 && r < own_end) {
+          *reinterpret_cast<uint2*>(dx + (long long)r * lddx + c0) = cv_pack4<T>(dxa[0]);
+        } else if (r < 0 && t0 == 0 && dhalo != nullptr) {
+          *reinterpret_cast<uint2*>(dhalo + (long long)(r + 3) * C + c0) = cv_pack4<T>(dxa[0]);
+        }
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          dxa[0][ch] = dxa[1][ch];
+          dxa[1][ch] = dxa[2][ch];
+          dxa[2][ch] = dxa[3][ch];
+          dxa[3][ch] = 0.f;
+          win[0][ch] = win[1][ch];
+          win[1][ch] = win[2][ch];
+          win[2][ch] = cur[ch];
+        }
       }
     }
     // rows that no later output reads (the end of the tensor, or fewer than three rows in all)
