@@ -176,9 +176,37 @@ def _slabs(nc: int, nh: int, Q: int):
     return [(c0, min(nc, c0 + step)) for c0 in range(0, nc, step)]
 
 
+def _chunk_states(x2, dt, A, B2, C2, h0, T, nh, P, G, N, Q, dtp, dev):
+    """Decay bookkeeping and the state entering every chunk: (L, Ltot, cb, wgt, hprev, hT).  Shared by the forward
+    and, with ``recompute``, by the backward (which then keeps none of these between the two passes)."""
+    nc, hpg = T // Q, nh // G
+    # within-chunk cumulative sum of dt*A, taken along the unit-stride axis of the chunk-major layout
+    dtt = _chunk_major(dt, nc, Q, nh)
+    Lt = (dtt * A.float()[None, :, None]).cumsum(-1)                        # [nc, nh, Q]
+    L = Lt.transpose(1, 2).reshape(T, nh).contiguous()
+    Ltot = Lt[:, :, -1].contiguous()                                        # [nc, nh]
+    # C.B^T per chunk and group
+    cb = batched_gemm(C2, B2, M=Q, N=Q, K=N, n_batch=nc * G, n_inner=G, a_off=(Q, 0, N, 1), b_off=(Q, 0, N, 1),
+                      d_off=(G * Q, Q, 0), out_rows=nc * G * Q, out_cols=Q)
+    # chunk states S[c,h] [P, N] = (x w)^T B,  w = exp(Ltot - L) dt
+    wgt = (torch.exp(Ltot.view(nc, 1, nh) - L.view(nc, Q, nh)) * dt.view(nc, Q, nh)).reshape(T, nh).contiguous()
+    xw = _rowscale(x2, wgt, nh, P)
+    S = batched_gemm(xw, B2, M=P, N=N, K=Q, n_batch=nc * nh, n_inner=nh, a_off=(Q, 0, P, 1), b_off=(Q, 0, N, hpg),
+                     d_off=(nh * P, P, 0), a_mn=True, b_mn=True, out_rows=nc * nh * P, out_cols=N,
+                     out_dtype=torch.float32)
+    del xw
+    hprev = torch.empty(nc * nh * P, N, dtype=dtp, device=dev)
+    hT = torch.empty(nh, P, N, dtype=torch.float32, device=dev)
+    h0c = None if h0 is None else h0.float().contiguous()
+    rc = NV.lib().fmsb_ssd_state_fwd(S.data_ptr(), Ltot.data_ptr(), NV.ptr(h0c), hprev.data_ptr(), hT.data_ptr(), nc,
+                                     nh, P * N, NV.dtype_code(dtp), NV.stream_ptr())
+    NV.check(rc, "fmsb_ssd_state_fwd")
+    return L, Ltot, Lt, dtt, cb, wgt, hprev, hT
+
+
 class _SSDScan(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, dt, A, B, C, D, h0, Q):
+    def forward(ctx, x, dt, A, B, C, D, h0, Q, recompute):
         T, nh, P = x.shape
         G, N = B.shape[1], B.shape[2]
         assert T % Q == 0, "sequence length must be a multiple of the chunk size"
@@ -189,14 +217,7 @@ class _SSDScan(torch.autograd.Function):
         x2 = _rows16(x.reshape(T, nh * P))
         B2, C2 = B.reshape(T, G * N), C.reshape(T, G * N)
         dt = dt.float().contiguous()
-        # within-chunk cumulative sum of dt*A, taken along the unit-stride axis of the chunk-major layout
-        dtt = _chunk_major(dt, nc, Q, nh)
-        Lt = (dtt * A.float()[None, :, None]).cumsum(-1)                    # [nc, nh, Q]
-        L = Lt.transpose(1, 2).reshape(T, nh).contiguous()
-        Ltot = Lt[:, :, -1].contiguous()                                    # [nc, nh]
-        # C.B^T per chunk and group
-        cb = batched_gemm(C2, B2, M=Q, N=Q, K=N, n_batch=nc * G, n_inner=G, a_off=(Q, 0, N, 1), b_off=(Q, 0, N, 1),
-                          d_off=(G * Q, Q, 0), out_rows=nc * G * Q, out_cols=Q)
+        L, Ltot, Lt, dtt, cb, wgt, hprev, hT = _chunk_states(x2, dt, A, B2, C2, h0, T, nh, P, G, N, Q, dtp, dev)
         # intra-chunk term in slabs of chunks: the [chunks, heads, Q, Q] decay-weighted matrices are transient
         y_intra = torch.empty(T, nh * P, dtype=torch.float32, device=dev)
         for c0, c1 in _slabs(nc, nh, Q):
@@ -205,20 +226,6 @@ class _SSDScan(torch.autograd.Function):
             batched_gemm(g, x2[c0 * Q: c1 * Q], M=Q, N=P, K=Q, n_batch=n * nh, n_inner=nh, a_off=(nh * Q, Q, 0, 1),
                          b_off=(Q, 0, P, 1), d_off=(Q, 0, P), b_mn=True, out=y_intra[c0 * Q: c1 * Q])
             del g
-        # chunk states S[c,h] [P, N] = (x w)^T B,  w = exp(Ltot - L) dt
-        wgt = (torch.exp(Ltot.view(nc, 1, nh) - L.view(nc, Q, nh)) * dt.view(nc, Q, nh)).reshape(T, nh).contiguous()
-        xw = _rowscale(x2, wgt, nh, P)
-        S = batched_gemm(xw, B2, M=P, N=N, K=Q, n_batch=nc * nh, n_inner=nh, a_off=(Q, 0, P, 1), b_off=(Q, 0, N, hpg),
-                         d_off=(nh * P, P, 0), a_mn=True, b_mn=True, out_rows=nc * nh * P, out_cols=N,
-                         out_dtype=torch.float32)
-        del xw
-        hprev = torch.empty(nc * nh * P, N, dtype=dtp, device=dev)
-        hT = torch.empty(nh, P, N, dtype=torch.float32, device=dev)
-        h0c = None if h0 is None else h0.float().contiguous()
-        rc = NV.lib().fmsb_ssd_state_fwd(S.data_ptr(), Ltot.data_ptr(), NV.ptr(h0c), hprev.data_ptr(), hT.data_ptr(), nc,
-                                         nh, P * N, NV.dtype_code(dtp), NV.stream_ptr())
-        NV.check(rc, "fmsb_ssd_state_fwd")
-        del S
         # inter-chunk: C_t . Hprev[c,h]  (B operand [P rows, N cols], contraction over N)
         y_inter = batched_gemm(C2, hprev, M=Q, N=P, K=N, n_batch=nc * nh, n_inner=nh, a_off=(Q, 0, N, hpg),
                                b_off=(nh * P, P, 0, 1), d_off=(Q, 0, P), out_rows=T, out_cols=nh * P,
@@ -230,14 +237,18 @@ class _SSDScan(torch.autograd.Function):
                                            Df.data_ptr(), y.data_ptr(), T * nh, P, nh, NV.dtype_code(dtp),
                                            NV.stream_ptr())
         NV.check(rc, "fmsb_ssd_fwd_combine")
-        ctx.save_for_backward(x, dt, A, B, C, D, L, Ltot, cb, hprev, wgt)
-        ctx.meta = (Q, h0 is not None)
+        if recompute:
+            # keep the inputs only; the backward rebuilds the bookkeeping and the entering states
+            ctx.save_for_backward(x, dt, A, B, C, D, h0)
+        else:
+            ctx.save_for_backward(x, dt, A, B, C, D, L, Ltot, cb, hprev, wgt)
+        ctx.meta = (Q, h0 is not None, recompute)
         return y, hT
 
     @staticmethod
     def backward(ctx, dy, dhT):
-        x, dt, A, B, C, D, L, Ltot, cb, hprev, wgt = ctx.saved_tensors
-        Q, has_h0 = ctx.meta
+        Q, has_h0, recompute = ctx.meta
+        x, dt, A, B, C, D = ctx.saved_tensors[:6]
         T, nh, P = x.shape
         G, N = B.shape[1], B.shape[2]
         nc, hpg = T // Q, nh // G
@@ -246,7 +257,12 @@ class _SSDScan(torch.autograd.Function):
         x2 = _rows16(x.reshape(T, nh * P))
         B2, C2 = B.reshape(T, G * N), C.reshape(T, G * N)
         dy2 = _rows16(dy.reshape(T, nh * P))
-        Lt, dtt = _chunk_major(L, nc, Q, nh), _chunk_major(dt, nc, Q, nh)
+        if recompute:
+            L, Ltot, Lt, dtt, cb, wgt, hprev, _ = _chunk_states(x2, dt, A, B2, C2, ctx.saved_tensors[6], T, nh, P, G, N,
+                                                                Q, dtp, dev)
+        else:
+            L, Ltot, cb, hprev, wgt = ctx.saved_tensors[6:]
+            Lt, dtt = _chunk_major(L, nc, Q, nh), _chunk_major(dt, nc, Q, nh)
         # ---- inter-chunk term  y += exp(L) * (C . Hprev)
         dyi = _rowscale(dy2, torch.exp(L), nh, P)
         y_inter = batched_gemm(C2, hprev, M=Q, N=P, K=N, n_batch=nc * nh, n_inner=nh, a_off=(Q, 0, N, hpg),
@@ -334,7 +350,7 @@ class _SSDScan(torch.autograd.Function):
         ddt = ddt + da * A.float()[None, :]
         dA = (da * dt).sum(0)
         return (dx, ddt.to(dt.dtype), dA.to(A.dtype), dB.view(T, G, N).to(B.dtype), dC.view(T, G, N).to(C.dtype),
-                dD.to(D.dtype), dh0, None)
+                dD.to(D.dtype), dh0, None, None)
 
 
 class _StateCorrection(torch.autograd.Function):
@@ -418,9 +434,11 @@ def state_correction(y0, h_in, dt, A, C, chunk_size=256):
     return _StateCorrection.apply(y0, h_in, dt, A, C, chunk_size)
 
 
-def ssd_scan(x, dt, A, B, C, D, h0=None, chunk_size=256):
-    """Chunked SSD scan.  Returns ``(y [T, nh, P], final_state [nh, P, N] fp32)``."""
+def ssd_scan(x, dt, A, B, C, D, h0=None, chunk_size=256, recompute=False):
+    """Chunked SSD scan.  Returns ``(y [T, nh, P], final_state [nh, P, N] fp32)``.  ``recompute``: keep only the
+    inputs for the backward, which rebuilds the per-chunk entering states (the ``mamba_recompute`` switch of the
+    context-parallel plugin, fms_acceleration_mcp/framework_plugin_mcp.py:37-44)."""
     if not x.is_cuda:
         y, h = ssd_ref(x, dt, A, B, C, D, h0)
         return y.to(x.dtype), h.float()
-    return _SSDScan.apply(x, dt, A, B, C, D, h0, chunk_size)
+    return _SSDScan.apply(x, dt, A, B, C, D, h0, chunk_size, bool(recompute))

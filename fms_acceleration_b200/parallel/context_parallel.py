@@ -48,6 +48,10 @@ class ContextParallel:
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
         self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        # impl: "allgather" and "serial" give the same entering state.  Both use the all-to-later push: through
+        # NVSwitch every later rank is one hop away at full bandwidth and a (state, decay) pair is a few MB, so a
+        # rank-to-rank chain would only add world-1 latencies to the last rank.  recompute: the scan keeps only its
+        # inputs and rebuilds the per-chunk entering states in the backward.
         self.impl, self.recompute = impl, recompute
         self.comm = Communicator(self.group, self.device)
         self._slots = {}
@@ -85,7 +89,7 @@ class ContextParallel:
         """Context-parallel SSD scan of this rank's slice; returns y."""
         nh = x.shape[1]
         # pass 1: zero-initial-state scan gives the slice's final state F and total decay P
-        y0, F_local = MB.ssd_scan(x, dt, A, B, C, D, None, Q)
+        y0, F_local = MB.ssd_scan(x, dt, A, B, C, D, None, Q, recompute=self.recompute)
         logP = (dt.float() * A.float()[None, :]).sum(0)                       # [nh]
         h_in = _StateExchange.apply(F_local, logP, self, layer)
         # the entering state only adds  exp(L_global(t)) * C_t . H_in  to every output row of the slice
