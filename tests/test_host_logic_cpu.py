@@ -1,0 +1,66 @@
+"""Host-side decisions that steer the kernels, checked on the CPU: contraction splitting of weight-gradient GEMMs,
+the one-concatenation column split of the Mamba2 mixer, slab ranges of the scan, and the CPU oracle of the
+entering-state correction against the sequential recurrence."""
+import torch
+
+from fms_acceleration_b200.models.mamba2 import _SplitCols
+from fms_acceleration_b200.ops import gemm as GM
+from fms_acceleration_b200.ops import mamba as MB
+
+
+def test_split_k_only_for_few_tiles_and_long_contractions():
+    # plenty of tiles: never split
+    assert GM._split_k(14336, 4096, 16384, 256) == 1
+    # short contraction: never split
+    assert GM._split_k(48, 4096, 512, 256) == 1
+    for M, N, K in [(48, 4096, 16384), (6144, 48, 16384), (1536, 1536, 16384), (40, 1536, 16384), (1536, 512, 4096)]:
+        bn = GM._pick_bn(N, True)
+        s = GM._split_k(M, N, K, bn)
+        tiles = -(-M // 128) * -(-N // bn)
+        assert s > 1 and s & (s - 1) == 0, (M, N, K, s)
+        assert K % (s * 64) == 0 and K // s >= GM.SPLIT_K_MIN
+        assert tiles * s <= 2 * GM.SM_COUNT
+    # a token count that only divides by 64 once cannot be split evenly
+    assert GM._split_k(48, 4096, 64 * 33, 256) == 1
+
+
+def test_split_cols_backward_is_the_slicing_backward():
+    torch.manual_seed(0)
+    t = torch.randn(7, 12, requires_grad=True)
+    a, b, c = _SplitCols.apply(t, 5, 4, 3)
+    assert a.shape == (7, 5) and b.shape == (7, 4) and c.shape == (7, 3)
+    (a.sum() * 2 + (b * b).sum()).backward()          # c is unused: its block of the gradient is zero
+    g = t.grad.clone()
+    t.grad = None
+    a2, b2 = t[:, :5], t[:, 5:9]
+    (a2.sum() * 2 + (b2 * b2).sum()).backward()
+    assert torch.equal(g, t.grad)
+    assert torch.count_nonzero(g[:, 9:]) == 0
+
+
+def test_slabs_cover_all_chunks_once():
+    for nc, nh, Q in [(1, 4, 64), (32, 80, 256), (257, 8, 128)]:
+        ranges = MB._slabs(nc, nh, Q)
+        assert ranges[0][0] == 0 and ranges[-1][1] == nc
+        assert all(a1 == b0 for (_, a1), (b0, _) in zip(ranges[:-1], ranges[1:]))
+        assert all((c1 - c0) * nh * Q * Q * 4 <= max(MB.SLAB_BYTES, nh * Q * Q * 4) for c0, c1 in ranges)
+
+
+def test_state_correction_oracle_equals_scan_with_initial_state():
+    """y(h0) = y(0) + correction(h0): the identity context parallelism relies on, in fp64 on the CPU."""
+    torch.manual_seed(1)
+    T, nh, P, G, N = 48, 4, 8, 2, 16
+    x = torch.randn(T, nh, P, dtype=torch.float64)
+    dt = torch.rand(T, nh, dtype=torch.float64) * 0.1 + 0.01
+    A = -(torch.rand(nh, dtype=torch.float64) + 0.5)
+    B = torch.randn(T, G, N, dtype=torch.float64)
+    C = torch.randn(T, G, N, dtype=torch.float64)
+    D = torch.randn(nh, dtype=torch.float64)
+    h0 = torch.randn(nh, P, N, dtype=torch.float64)
+    y0, _ = MB.ssd_ref(x, dt, A, B, C, D, None)
+    y1, _ = MB.ssd_ref(x, dt, A, B, C, D, h0)
+    rep = nh // G
+    Lg = torch.cumsum(dt * A[None, :], 0)
+    Ch = C.repeat_interleave(rep, 1)
+    corr = torch.exp(Lg)[:, :, None] * torch.einsum("thn,hpn->thp", Ch, h0)
+    assert torch.allclose(y0 + corr, y1, rtol=1e-9, atol=1e-9)
