@@ -19,6 +19,8 @@ RESULT_DIR=${3:-"benchmark_results"}
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
 ROOT="$(cd "$HERE/../.." && pwd)"
 SCENARIOS_CONFIG=${4:-"$HERE/scenarios.yaml"}
+# a bare file name means one of the scenario files that sit beside this script
+if [ ! -f "$SCENARIOS_CONFIG" ] && [ -f "$HERE/$SCENARIOS_CONFIG" ]; then SCENARIOS_CONFIG="$HERE/$SCENARIOS_CONFIG"; fi
 shift $(( $# > 4 ? 4 : $# )) || true
 SCENARIOS_FILTER=("$@")
 
