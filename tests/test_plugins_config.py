@@ -111,3 +111,18 @@ def test_sample_configurations_are_current_and_loadable():
     for c in contents:
         body = yaml.safe_load(files[c["filename"]])
         assert "plugins" in body and body["plugins"]
+
+
+def test_rule_filter_keeps_or_drops_by_id_suffix():
+    """Rule-id suffix filtering of the fused-ops plugin (intent of the reference's tests/test_model_utils.py)."""
+    from fms_acceleration_b200.framework.model_patcher import ModelPatcherRule
+    from fms_acceleration_b200.plugins.foak.utils import filter_mp_rules
+
+    fwd = lambda self, x: x  # noqa: E731
+    ids = ["llama-rms", "llama-qkvo", "llama-mlp", "llama-rope", "llama-fused-lce", "llama-custom-loss"]
+    rules = [ModelPatcherRule(rule_id=i, forward=fwd) for i in ids]
+    kept = filter_mp_rules(rules, {"qkvo", "mlp"})
+    assert [r.rule_id for r in kept] == ["llama-qkvo", "llama-mlp"]
+    dropped = filter_mp_rules(rules, {"qkvo", "mlp"}, drop=True)
+    assert [r.rule_id for r in dropped] == ["llama-rms", "llama-rope", "llama-fused-lce", "llama-custom-loss"]
+    assert filter_mp_rules(rules, {"nothing"}) == []
