@@ -109,6 +109,33 @@ class ContextParallel:
         return n.clamp(min=1)
 
 
+def prefix_state(Fs: torch.Tensor, lPs: torch.Tensor, r: int) -> torch.Tensor:
+    """State entering rank ``r``'s slice from the zero-initial-state final states ``Fs [>=r, nh, P, N]`` and the log
+    total decays ``lPs [>=r, nh]`` of the earlier ranks: left to right, ``H <- exp(lP_j) H + F_j``."""
+    h = torch.zeros_like(Fs[0], dtype=torch.float32)
+    for j in range(r):
+        h = torch.exp(lPs[j])[:, None, None] * h + Fs[j]
+    return h
+
+
+def prefix_state_grads(dh: torch.Tensor, Fs: torch.Tensor, lPs: torch.Tensor, r: int, world: int):
+    """Gradients of :func:`prefix_state` with respect to every earlier rank's ``F_j`` and ``lP_j``:
+    ``(dF [world, nh, P, N], dlP [world, nh])``, rows ``>= r`` zero."""
+    nh = dh.shape[0]
+    dF = torch.zeros(world, *dh.shape, dtype=torch.float32, device=dh.device)
+    dlP = torch.zeros(world, nh, dtype=torch.float32, device=dh.device)
+    g = dh.float().clone()
+    # prefixes H^{(j)}: the state after absorbing the ranks below j
+    prefix = [torch.zeros_like(g)]
+    for j in range(r):
+        prefix.append(torch.exp(lPs[j])[:, None, None] * prefix[-1] + Fs[j])
+    for j in range(r - 1, -1, -1):
+        dF[j] = g
+        dlP[j] = (g * prefix[j]).sum((1, 2)) * torch.exp(lPs[j])
+        g = torch.exp(lPs[j])[:, None, None] * g
+    return dF, dlP
+
+
 class _StateExchange(torch.autograd.Function):
     """(F [nh,P,N], logP [nh]) of every rank -> the state entering this rank's slice."""
 
@@ -121,9 +148,7 @@ class _StateExchange(torch.autograd.Function):
         n = F_local.numel()
         Fs = recv[:, :n].view(cp.world, *F_local.shape)
         lPs = recv[:, n:].view(cp.world, nh)
-        h = torch.zeros_like(F_local, dtype=torch.float32)
-        for j in range(cp.rank):                                              # left to right: H = P_j H + F_j
-            h = torch.exp(lPs[j])[:, None, None] * h + Fs[j]
+        h = prefix_state(Fs, lPs, cp.rank) if cp.rank > 0 else torch.zeros_like(F_local, dtype=torch.float32)
         ctx.cp = cp
         ctx.save_for_backward(Fs[: cp.rank].clone(), lPs[: cp.rank].clone())
         return h
@@ -134,17 +159,7 @@ class _StateExchange(torch.autograd.Function):
         Fs, lPs = ctx.saved_tensors
         r, nh = cp.rank, dh.shape[0]
         # local chain: H_r = sum_{j<r} (prod_{j<i<r} P_i) F_j ; gradients w.r.t. the F_j / logP_j of EARLIER ranks
-        dF = torch.zeros(cp.world, *dh.shape, dtype=torch.float32, device=dh.device)
-        dlP = torch.zeros(cp.world, nh, dtype=torch.float32, device=dh.device)
-        g = dh.float().clone()
-        # recompute prefixes H^{(j)} (state after absorbing ranks < j)
-        prefix = [torch.zeros_like(g)]
-        for j in range(r):
-            prefix.append(torch.exp(lPs[j])[:, None, None] * prefix[-1] + Fs[j])
-        for j in range(r - 1, -1, -1):
-            dF[j] = g
-            dlP[j] = (g * prefix[j]).sum((1, 2)) * torch.exp(lPs[j])
-            g = torch.exp(lPs[j])[:, None, None] * g
+        dF, dlP = prefix_state_grads(dh, Fs, lPs, r, cp.world)
         # send each earlier rank its share; collect what later ranks computed for THIS rank
         n = dh.numel()
         mine_F = torch.zeros_like(dh, dtype=torch.float32)

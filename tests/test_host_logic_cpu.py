@@ -64,3 +64,24 @@ def test_state_correction_oracle_equals_scan_with_initial_state():
     Ch = C.repeat_interleave(rep, 1)
     corr = torch.exp(Lg)[:, :, None] * torch.einsum("thn,hpn->thp", Ch, h0)
     assert torch.allclose(y0 + corr, y1, rtol=1e-9, atol=1e-9)
+
+
+def test_context_parallel_prefix_state_and_its_gradients():
+    """The state entering rank r and the hand-written gradients sent back to the earlier ranks, against autograd."""
+    from fms_acceleration_b200.parallel.context_parallel import prefix_state, prefix_state_grads
+
+    torch.manual_seed(4)
+    world, nh, P, N = 4, 3, 5, 7
+    Fs = torch.randn(world, nh, P, N, dtype=torch.float64, requires_grad=True)
+    lPs = (-torch.rand(world, nh, dtype=torch.float64)).requires_grad_()
+    for r in range(1, world):
+        h = prefix_state(Fs, lPs, r)
+        # closed form: sum_j (prod_{j<i<r} P_i) F_j
+        ref = sum(torch.exp(lPs[j + 1: r].sum(0))[:, None, None] * Fs[j] for j in range(r))
+        assert torch.allclose(h.double(), ref.double(), rtol=1e-5, atol=1e-6)
+        dh = torch.randn(nh, P, N, dtype=torch.float64)
+        gF, glP = torch.autograd.grad((ref * dh).sum(), (Fs, lPs))
+        dF, dlP = prefix_state_grads(dh, Fs.detach(), lPs.detach(), r, world)
+        assert torch.allclose(dF.double(), gF, rtol=1e-4, atol=1e-5)
+        assert torch.allclose(dlP.double(), glP, rtol=1e-4, atol=1e-5)
+        assert torch.count_nonzero(dF[r:]) == 0 and torch.count_nonzero(dlP[r:]) == 0
