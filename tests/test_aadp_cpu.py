@@ -1,6 +1,5 @@
 """Padding-free collators and the multipack sampler (host side)."""
 import numpy as np
-import torch
 
 from fms_acceleration_b200.plugins.aadp.aadp_utils import DataCollatorWithFlattening, calculate_token_lengths
 from fms_acceleration_b200.plugins.aadp.multipack_sampler import (MultipackDistributedBatchSampler, allocate,

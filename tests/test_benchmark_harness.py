@@ -2,7 +2,6 @@
 import json
 import os
 import subprocess
-import sys
 
 import pandas as pd
 import pytest

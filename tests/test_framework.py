@@ -1,6 +1,4 @@
 """Framework core: configuration matching (AND / OR key paths), plugin activation rules, lifecycle dispatch."""
-import os
-
 import pytest
 import torch
 import yaml
@@ -159,3 +157,14 @@ def test_callbacks_collected_and_patchers_run():
         with build_framework_and_maybe_instantiate([(["a"], CB)], {"a": {"k": 1}}) as fw:
             cbs = fw.get_callbacks_and_ready_for_train(torch.nn.Linear(2, 2), Accelerator(device="cpu"))
     assert cbs == ["cb-from-plugin"]
+
+
+def test_configure_framework_from_json_builds_from_a_dict():
+    """The helper writes ``{plugins: contents}`` to a temporary YAML file and builds the framework from it."""
+    P = create_plugin_cls("FromJson", requires_augmentation=True, augmentation=dummy_augmentation)
+    with build_framework_and_maybe_instantiate([(["json_section"], P)], instantiate=False):
+        fw = configure_framework_from_json({"json_section": {"k": 1}}, require_packages_check=False)
+        assert [name for name, _ in fw.active_plugins] == ["FromJson"]
+        AccelerationFramework.reset()  # the active-plugin lists are class attributes, as in the reference
+        with pytest.raises(ValueError, match="No plugins could be configured"):
+            configure_framework_from_json({"other_section": {"k": 1}}, require_packages_check=False)

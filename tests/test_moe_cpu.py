@@ -1,6 +1,5 @@
 """ScatterMoE on CPU: checkpoint key mapping with fake weight maps, module swap parity, checkpoint round trip."""
 import json
-import os
 
 import pytest
 import torch
