@@ -70,7 +70,13 @@ class PaddingFreeAccelerationPlugin(AccelerationPlugin):
         if hasattr(train_args, "padding_free"):
             train_args.padding_free = True
 
-        # Hugging Face models: route their flash-attention entry point to the in-tree varlen kernel
+        # Hugging Face models: attention goes to the in-tree varlen kernel, through the attention registry where
+        # transformers has one, and through its flash-attention entry point for older versions
+        if model.__class__.__module__.startswith("transformers.") or hasattr(getattr(model, "config", None),
+                                                                             "_attn_implementation"):
+            from .flash_attn import use_in_tree_attention
+
+            use_in_tree_attention(model)
         try:
             import transformers.modeling_flash_attention_utils as fa_utils  # noqa: F401
 

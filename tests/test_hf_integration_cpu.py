@@ -119,3 +119,33 @@ def test_in_tree_models_load_hf_checkpoints(tmp_path, family):
         want = hf(input_ids=ids).logits
         got = mine(input_ids=ids).logits
     assert torch.allclose(got, want, atol=2e-4, rtol=1e-3), (got - want).abs().max()
+
+
+def test_padding_free_plugin_routes_hf_attention_to_the_in_tree_kernel():
+    """With the padding-free plugin a Hugging Face Llama runs a packed row (position ids restarting per document)
+    through the registered in-tree attention and gives, per document, what the unpatched model gives on that
+    document alone."""
+    from fms_acceleration_b200.plugins.aadp.flash_attn import HF_ATTENTION_NAME
+
+    model = _tiny_llama().eval()
+    ref = copy.deepcopy(model)
+    lens = [9, 17, 6]
+    docs = [torch.randint(0, 512, (1, n)) for n in lens]
+    with torch.no_grad():
+        ref_logits = torch.cat([ref(input_ids=d).logits[0] for d in docs], 0)
+    with instantiate_framework({"training": {"attention": {"padding_free": {"method": "huggingface"}}}},
+                               require_packages_check=False) as fw:
+        args = TrainArgs(padding_free=False)
+        model, _ = fw.augmentation(model, args, modifiable_args=(None,))
+        assert args.padding_free is True
+    assert model.config._attn_implementation == HF_ATTENTION_NAME
+    ids = torch.cat(docs, 1)
+    pos = torch.cat([torch.arange(n) for n in lens])[None]
+    with torch.no_grad():
+        out = model(input_ids=ids, position_ids=pos).logits[0]
+    assert torch.allclose(out, ref_logits, rtol=1e-4, atol=1e-4)
+    # without position ids every row of the batch is one document: plain causal attention
+    with torch.no_grad():
+        a = model(input_ids=docs[1]).logits
+        b = ref(input_ids=docs[1]).logits
+    assert torch.allclose(a, b, rtol=1e-4, atol=1e-4)
