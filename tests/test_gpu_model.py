@@ -138,3 +138,28 @@ def test_fused_lora_dropout_matches_masked_reference():
     assert rel(grads[0], A.grad) < 3e-2 and rel(grads[1], B.grad) < 3e-2
     lora.eval()
     assert grp.dropout_p() == 0.0
+
+
+def test_hf_llama_uses_the_in_tree_attention_on_packed_rows():
+    """A transformers Llama pointed at the registered in-tree attention: a packed row with position ids restarting
+    per document gives, per document, the logits of the eager model on that document alone."""
+    transformers = pytest.importorskip("transformers")
+    from fms_acceleration_b200.plugins.aadp.flash_attn import HF_ATTENTION_NAME, use_in_tree_attention
+
+    cfg = transformers.LlamaConfig(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                                   num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=1024,
+                                   tie_word_embeddings=False)
+    torch.manual_seed(0)
+    model = transformers.LlamaForCausalLM(cfg).to("cuda", torch.bfloat16).eval()
+    ref = copy.deepcopy(model)
+    ref.config._attn_implementation = "eager"
+    assert use_in_tree_attention(model) and model.config._attn_implementation == HF_ATTENTION_NAME
+    lens = [130, 41, 129]
+    docs = [torch.randint(0, 512, (1, n), device="cuda") for n in lens]
+    with torch.no_grad():
+        want = torch.cat([ref(input_ids=d).logits[0] for d in docs], 0).float()
+        ids = torch.cat(docs, 1)
+        pos = torch.cat([torch.arange(n, device="cuda") for n in lens])[None]
+        got = model(input_ids=ids, position_ids=pos).logits[0].float()
+    NV.check_status()
+    assert ((got - want).norm() / want.norm()).item() < 3e-2
