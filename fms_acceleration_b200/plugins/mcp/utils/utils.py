@@ -10,7 +10,9 @@ from __future__ import annotations
 
 from typing import Dict, Optional
 
+import torch
 import torch.distributed as dist
+from torch import nn
 
 KEY_DP, KEY_CP = "dp_shard", "cp"
 
@@ -26,6 +28,79 @@ def hf_config_ssm_config(hf_config) -> Dict:
         "conv_bias": getattr(hf_config, "mamba_conv_bias", True),
         "d_conv": getattr(hf_config, "mamba_d_conv", 4),
     }
+
+
+def _adapter_class():
+    """``HFMamba2Adapter`` is a subclass of the in-tree mixer (so parameter names, and with them checkpoints, are
+    those of the Hugging Face module); the class is made on first use to keep this module importable without the
+    model zoo."""
+    global _ADAPTER
+    if _ADAPTER is not None:
+        return _ADAPTER
+    from ....models.config import DecoderConfig
+    from ....models.mamba2 import Mamba2Mixer
+
+    class HFMamba2Adapter(Mamba2Mixer):
+        """The in-tree Mamba2 mixer behind the call convention of a Hugging Face Mamba2 layer.
+
+        Built from a ``transformers`` mixer (``Mamba2Mixer``, ``GraniteMoeHybridMambaLayer``, ``BambaMixer``: same
+        parameter names and projection layout) whose state dict it loads unchanged; ``forward(hidden_states
+        [B, S, H], ...)`` ignores cache, mask and sequence-index arguments like the reference's ``Mamba2CPHF``
+        (fms_acceleration_mcp/utils/utils.py:64-80) and runs every row of the batch as one sequence."""
+
+        def __init__(self, hf_mixer: nn.Module, layer_idx: int = 0, eps: Optional[float] = None):
+            hidden = hf_mixer.in_proj.in_features
+            d_inner = hf_mixer.intermediate_size
+            if d_inner % hidden != 0:
+                raise ValueError("the inner width must be a multiple of the hidden size")
+            if hf_mixer.n_groups != 1 and getattr(hf_mixer.norm, "group_size", d_inner) != d_inner:
+                raise NotImplementedError("grouped gated RMSNorm (n_groups > 1) is not supported")
+            lim = tuple(getattr(hf_mixer, "time_step_limit", (0.0, float("inf"))))
+            if lim[0] > 0.0 or lim[1] != float("inf"):
+                raise NotImplementedError("a time-step clamp is not supported")
+            cfg = DecoderConfig(
+                hidden_size=hidden, mamba_expand=d_inner // hidden, mamba_d_head=hf_mixer.head_dim,
+                mamba_d_state=hf_mixer.ssm_state_size, mamba_n_groups=hf_mixer.n_groups,
+                mamba_d_conv=hf_mixer.conv_kernel_size, mamba_chunk_size=hf_mixer.chunk_size,
+                mamba_conv_bias=hf_mixer.conv1d.bias is not None, mamba_proj_bias=hf_mixer.in_proj.bias is not None,
+                rms_norm_eps=eps if eps is not None else getattr(hf_mixer.norm, "variance_epsilon", 1e-5))
+            super().__init__(cfg, layer_idx)
+            self.to(device=hf_mixer.in_proj.weight.device, dtype=hf_mixer.in_proj.weight.dtype)
+            self.load_state_dict(hf_mixer.state_dict())
+            # per-head parameters stay in the precision the source module keeps them in
+            for name in ("A_log", "D", "dt_bias"):
+                getattr(self, name).data = getattr(hf_mixer, name).data.clone()
+
+        def forward(self, hidden_states, *args, **kwargs):  # noqa: D401  (Hugging Face call convention)
+            if hidden_states.dim() == 2:
+                return super().forward(hidden_states)
+            return torch.stack([super(HFMamba2Adapter, self).forward(row) for row in hidden_states], 0)
+
+    _ADAPTER = HFMamba2Adapter
+    return _ADAPTER
+
+
+_ADAPTER = None
+
+
+def _is_hf_mamba_module(m: nn.Module) -> bool:
+    return all(hasattr(m, a) for a in ("in_proj", "conv1d", "A_log", "dt_bias", "out_proj", "ssm_state_size"))
+
+
+def swap_hf_mamba_modules(model, names=("mamba", "mixer")) -> int:
+    """Replace every Hugging Face Mamba2 layer found under one of ``names`` on a decoder layer by an
+    ``HFMamba2Adapter`` (a subclass of the in-tree mixer, see :func:`_adapter_class`) with the same weights; returns how many were replaced."""
+    from ....models.mamba2 import Mamba2Mixer
+
+    adapter = _adapter_class()
+    n = 0
+    for parent in list(model.modules()):
+        for name in names:
+            child = getattr(parent, name, None)
+            if isinstance(child, nn.Module) and not isinstance(child, Mamba2Mixer) and _is_hf_mamba_module(child):
+                setattr(parent, name, adapter(child, layer_idx=getattr(child, "layer_idx", n)))
+                n += 1
+    return n
 
 
 def build_cp_group(world_size: int, cp_degree: int, rank: int):
@@ -56,6 +131,7 @@ def patch_mamba_layers_with_cp_head(model, checkpoint_name_or_path: Optional[str
     device = next(model.parameters()).device
     cp = ContextParallel(group, device, impl=cp_mamba_impl, recompute=cp_mamba_recompute)
     base = model.get_base_model() if hasattr(model, "get_base_model") else model
+    swap_hf_mamba_modules(base, names=("mamba",))  # Hugging Face layers become the in-tree mixer, same weights
     inner = getattr(base, "model", base)
     patched = 0
     for layer in inner.layers:

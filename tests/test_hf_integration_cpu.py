@@ -149,3 +149,37 @@ def test_padding_free_plugin_routes_hf_attention_to_the_in_tree_kernel():
         a = model(input_ids=docs[1]).logits
         b = ref(input_ids=docs[1]).logits
     assert torch.allclose(a, b, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("family", ["mamba2", "granitemoehybrid"])
+def test_hf_mamba_layers_swap_to_the_in_tree_mixer(family):
+    """What the context-parallel plugin does to a Hugging Face model before it installs the communicator: every
+    Mamba2 layer becomes the in-tree mixer with the same weights, the same parameter names and the same outputs."""
+    from fms_acceleration_b200.plugins.mcp.utils.utils import swap_hf_mamba_modules
+
+    torch.manual_seed(0)
+    if family == "mamba2":
+        cfg = transformers.Mamba2Config(vocab_size=256, hidden_size=64, state_size=16, num_hidden_layers=2, expand=2,
+                                        head_dim=16, num_heads=8, n_groups=1, conv_kernel=4, chunk_size=32,
+                                        tie_word_embeddings=False)
+        model, names, expect = transformers.Mamba2ForCausalLM(cfg).eval(), ("mixer",), 2
+    else:
+        cfg = transformers.GraniteMoeHybridConfig(
+            vocab_size=256, hidden_size=64, intermediate_size=64, num_hidden_layers=3, num_attention_heads=4,
+            num_key_value_heads=2, num_local_experts=4, num_experts_per_tok=2, shared_intermediate_size=64,
+            layer_types=["mamba", "attention", "mamba"], mamba_n_heads=8, mamba_d_head=16, mamba_d_state=16,
+            mamba_n_groups=1, mamba_d_conv=4, mamba_expand=2, mamba_chunk_size=32, mamba_conv_bias=True,
+            mamba_proj_bias=False, tie_word_embeddings=False, position_embedding_type="rope")
+        model, names, expect = transformers.GraniteMoeHybridForCausalLM(cfg).eval(), ("mamba",), 2
+    ids = torch.randint(0, 256, (2, 48))
+    with torch.no_grad():
+        ref = model(input_ids=ids).logits
+    before = {k: v.clone() for k, v in model.state_dict().items()}
+    assert swap_hf_mamba_modules(model, names=names) == expect
+    assert swap_hf_mamba_modules(model, names=names) == 0          # already in-tree: nothing left to swap
+    with torch.no_grad():
+        out = model(input_ids=ids).logits
+    assert torch.allclose(out, ref, rtol=1e-4, atol=1e-5)
+    after = model.state_dict()
+    assert sorted(after) == sorted(before) and all(torch.equal(after[k], before[k]) for k in before)
+    assert not model.load_state_dict(before).missing_keys
