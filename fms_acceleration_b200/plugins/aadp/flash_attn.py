@@ -41,15 +41,18 @@ _BOUNDS_CACHE: dict = {}
 
 
 def _doc_bounds(position_ids, cu_seq_lens, total: int, device):
-    """Document start / end per row of the flattened batch; computed once per batch, not once per layer."""
+    """Document start / end per row of the flattened batch; computed once per batch, not once per layer.  The cache
+    holds a weak reference to the tensor object the layers of one forward pass share: a later batch is a different
+    object even when the allocator hands it the same address."""
+    import weakref
+
     src = cu_seq_lens if cu_seq_lens is not None else position_ids
-    key = (src.data_ptr(), tuple(src.shape), src._version, total, cu_seq_lens is not None)
     hit = _BOUNDS_CACHE.get("last")
-    if hit is not None and hit[0] == key:
-        return hit[1]
+    if hit is not None and hit[0]() is src and hit[1] == (src._version, total):
+        return hit[2]
     cu = cu_seq_lens.to(torch.int32) if cu_seq_lens is not None else cu_seqlens_from_position_ids(position_ids)
     bounds = doc_bounds_from_cu_seqlens(cu.to(device), total)
-    _BOUNDS_CACHE["last"] = (key, bounds)
+    _BOUNDS_CACHE["last"] = (weakref.ref(src), (src._version, total), bounds)
     return bounds
 
 
@@ -70,10 +73,13 @@ def hf_attention_forward(module, query, key, value, attention_mask, dropout: flo
     q = query.transpose(1, 2).reshape(B * S, nh, d).contiguous()
     k = key.transpose(1, 2).reshape(B * S, key.shape[1], d).contiguous()
     v = value.transpose(1, 2).reshape(B * S, value.shape[1], d).contiguous()
-    position_ids = kwargs.get("position_ids")
-    if position_ids is None and kwargs.get("cu_seq_lens_q") is None:
-        position_ids = torch.arange(S, device=query.device).expand(B, S)
-    ds, de = _doc_bounds(position_ids, kwargs.get("cu_seq_lens_q"), B * S, query.device)
+    position_ids, cu_q = kwargs.get("position_ids"), kwargs.get("cu_seq_lens_q")
+    if position_ids is None and cu_q is None:
+        # no packing information: every row of the batch is one document
+        cu_q = torch.arange(0, (B + 1) * S, S, dtype=torch.int32, device=query.device)
+        ds, de = doc_bounds_from_cu_seqlens(cu_q, B * S)
+    else:
+        ds, de = _doc_bounds(position_ids, cu_q, B * S, query.device)
     out = varlen_attention(q, k, v, ds, de, scaling)
     return out.view(B, S, nh, d), None
 
