@@ -67,3 +67,35 @@ def test_reference_arm_prints_one_json_line_and_exits_zero():
     assert out.returncode == 0
     line = json.loads(out.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and ("unavailable" in line or "value" in line)
+
+
+def test_clock_sampler_parses_nvidia_smi_lines():
+    """Median SM clock, maximum clock and the set of active throttle reasons from `nvidia-smi --format=csv` lines."""
+    import tempfile
+
+    b = _bench()
+
+    class _Done:
+        def terminate(self):
+            pass
+
+        def wait(self, timeout=None):
+            return 0
+
+        def kill(self):
+            pass
+
+    s = b.ClockSampler.__new__(b.ClockSampler)
+    s.tmp = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+    s.tmp.write("0, 1965, 1965, 412.5, 0x0000000000000000, Not Active, Not Active, Not Active, Not Active\n"
+                "0, 1500, 1965, 998.1, 0x0000000000000004, Not Active, Not Active, Not Active, Active\n"
+                "0, 1470, 1965, 1001.0, 0x0000000000000004, Not Active, Not Active, Not Active, Active\n"
+                "garbage line\n")
+    s.proc = _Done()
+    out = s.stop()
+    assert out["sm_mhz"] == 1500.0 and out["sm_max_mhz"] == 1965.0 and out["samples"] == 3
+    assert out["reasons"] == ["sw_power_cap"]
+    # no sampler process (nvidia-smi missing): the keys are still there
+    s2 = b.ClockSampler.__new__(b.ClockSampler)
+    s2.proc, s2.tmp = None, None
+    assert s2.stop() == {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
