@@ -139,3 +139,34 @@ def test_swap_other_families(name, arch):
     assert set(sd) == set(original)
     for k in original:
         assert torch.equal(sd[k], original[k]), k
+
+
+def test_expert_lora_starts_at_the_base_and_trains_only_the_adapters():
+    """Per-expert LoRA (lora_A [E, in, r] zeros, lora_B [E, r, out] normal, scale 1 as in the reference's kernels):
+    the output equals the base model's at initialisation, the base expert weights are frozen, both adapter
+    matrices and the router receive gradients."""
+    from types import SimpleNamespace
+
+    from fms_acceleration_b200.plugins.moe.utils.scattermoe import ScatterMoE
+
+    torch.manual_seed(0)
+    kw = dict(hidden_size=16, hidden_act="silu", intermediate_size=24, num_experts=4, top_k=2, dtype=torch.float32)
+    base = ScatterMoE(**kw)
+    for m in (base.w1, base.w2, base.w3):
+        torch.nn.init.normal_(m.weight, std=0.2)
+    torch.nn.init.normal_(base.router.weight, std=0.5)
+    lora = ScatterMoE(**kw, lora_config=SimpleNamespace(r=4, lora_alpha=8))
+    lora.load_state_dict(base.state_dict(), strict=False)
+    x = torch.randn(10, 16)
+    y0, _ = base(x)
+    y1, _ = lora(x)
+    assert torch.allclose(y0, y1, atol=1e-6)
+    assert lora.w1.lora_A.shape == (4, 16, 4) and lora.w1.lora_B.shape == (4, 4, 24)
+    assert not lora.w1.weight.requires_grad and lora.w1.lora_A.requires_grad
+    with torch.no_grad():
+        lora.w2.lora_A.normal_(std=0.1)          # move one adapter off zero so that lora_B sees a gradient too
+    y2, _ = lora(x)
+    y2.square().sum().backward()
+    assert lora.w2.lora_A.grad is not None and lora.w2.lora_B.grad.abs().sum() > 0
+    assert lora.w1.lora_A.grad.abs().sum() > 0 and lora.w1.weight.grad is None
+    assert lora.router.weight.grad is not None
