@@ -6,6 +6,7 @@ untouched, and equal a hand-written reference that applies the same LoRA update 
 """
 import copy
 
+import pytest
 import torch
 
 import fms_acceleration_b200.plugins  # noqa: F401  (registers the plugins)
@@ -91,3 +92,36 @@ def test_through_the_framework_with_lora_plugin_config():
     with instantiate_framework(cfg, require_packages_check=False) as fw:
         assert fw.requires_custom_loading and fw.requires_augmentation
         assert [n for n, _ in fw.active_plugins] == ["BNBAccelerationPlugin"]
+
+
+@pytest.mark.parametrize("which", ["bitsandbytes", "auto_gptq"])
+def test_quantised_lora_lifecycle_on_the_cpu(which):
+    """Loader plugin -> augmentation -> one forward/backward with the PyTorch oracle paths: the base is quantised and
+    frozen, the adapters on the targeted projections are the only trainable parameters and all of them receive a
+    gradient; the consumed ``peft_config`` comes back as None."""
+    from fms_acceleration_b200.nn import LoraConfig
+    from fms_acceleration_b200.trainer import TrainArgs
+
+    if which == "bitsandbytes":
+        cfg = {"peft": {"quantization": {"bitsandbytes": {"quant_type": "nf4", "no_peft_model": False}}}}
+        dtype, layer_cls, args = torch.bfloat16, "Linear4bit", TrainArgs(bf16=True)
+    else:
+        cfg = {"peft": {"quantization": {"auto_gptq": {"kernel": "triton_v2", "from_quantized": True}}}}
+        dtype, layer_cls, args = torch.float16, "QuantLinear", TrainArgs(fp16=True)
+    with instantiate_framework(cfg, require_packages_check=False) as fw:
+        model = fw.model_loader("tiny-llama", torch_dtype=dtype, device="cpu")
+        n_quant = sum(1 for m in model.modules() if m.__class__.__name__ == layer_cls)
+        assert n_quant == 7 * model.config.num_hidden_layers        # q, k, v, o, gate, up, down of every layer
+        peft_config = LoraConfig(r=4, lora_alpha=8, target_modules=["q_proj", "v_proj"])
+        model, (returned,) = fw.augmentation(model, args, modifiable_args=(peft_config,))
+        assert returned is None
+    trainable = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
+    assert trainable and all("lora_" in n for n, _ in trainable)
+    assert len(trainable) == 2 * 2 * model.config.num_hidden_layers  # A and B of q_proj and v_proj per layer
+    ids = torch.randint(0, 512, (2, 16))
+    out = model(input_ids=ids, labels=ids)
+    out.loss.backward()
+    assert torch.isfinite(out.loss.detach())
+    assert all(p.grad is not None for _, p in trainable)
+    # lora_B starts at zero, so only it sees a gradient on the first step; lora_A follows once B has moved
+    assert any(p.grad.abs().sum() > 0 for n, p in trainable if "lora_B" in n)
