@@ -21,6 +21,28 @@ from ..ops.gemm import gemm
 class QuantLinear(nn.Module):
     QUANT_TYPE = "b200"
     SUPPORTED_BITS = (2, 4, 8)
+    SUPPORTED_GROUP_SIZE = ()          # empty: any group size (-1 = one group per column)
+    SUPPORTED_DESC_ACT = (True, False)
+    SUPPORTED_SYM = (True, False)
+    SUPPORTED_SHARDS = True
+
+    @classmethod
+    def validate(cls, bits: int, group_size: int, desc_act: bool, sym: bool, raise_error: bool = True) -> bool:
+        """Whether this layer can hold a weight quantised with these settings (the check the reference's
+        ``BaseQuantLinear.validate`` makes before a kernel class is chosen,
+        fms_acceleration_peft/gptqmodel/nn_modules/qlinear/__init__.py:16-43)."""
+        err = None
+        if bits not in cls.SUPPORTED_BITS:
+            err = f"{cls.QUANT_TYPE} only supports {cls.SUPPORTED_BITS} bits: actual bits = {bits}"
+        elif cls.SUPPORTED_GROUP_SIZE and group_size not in cls.SUPPORTED_GROUP_SIZE:
+            err = f"{cls.QUANT_TYPE} only supports group sizes {cls.SUPPORTED_GROUP_SIZE}: actual group_size = {group_size}"
+        elif sym not in cls.SUPPORTED_SYM:
+            err = f"{cls.QUANT_TYPE} does not support sym = {sym}"
+        elif desc_act not in cls.SUPPORTED_DESC_ACT:
+            err = f"{cls.QUANT_TYPE} does not support desc_act = {desc_act}"
+        if err is not None and raise_error:
+            raise NotImplementedError(err)
+        return err is None
 
     def __init__(self, bits: int, group_size: int, infeatures: int, outfeatures: int, bias: bool = False,
                  dtype: torch.dtype = torch.float16, zero_offset: int = 0, device=None, **kwargs):

@@ -182,3 +182,40 @@ def test_gptq_lora_model_never_merges():
     assert isinstance(pm.base_model.model.q_proj, GPTQLoraLinear)
     with pytest.raises(NotImplementedError):
         pm.merge_and_unload()
+
+
+def test_importer_and_reference_import_paths():
+    from fms_acceleration_peft.gptqmodel.nn_modules.qlinear import BaseQuantLinear
+    from fms_acceleration_peft.gptqmodel.nn_modules.qlinear.qlinear_tritonv2 import QuantLinear as TV2
+    from fms_acceleration_peft.gptqmodel.nn_modules.triton_utils.dequant import dequant248, quant_matmul_248
+    from fms_acceleration_peft.gptqmodel.utils.backend import Backend
+    from fms_acceleration_peft.gptqmodel.utils.importer import select_quant_linear
+
+    assert TV2 is QuantLinear and BaseQuantLinear is QuantLinear
+    assert select_quant_linear(4, 128, False, True, Backend.AUTO, FORMAT.GPTQ, pack=True) is QuantLinear
+    assert select_quant_linear(8, -1, True, False, Backend.TRITON, FORMAT.GPTQ_V2) is QuantLinear
+    assert not QuantLinear.validate(3, 128, False, True, raise_error=False)
+    with pytest.raises(NotImplementedError):
+        select_quant_linear(3, 128, False, True, Backend.TRITON, FORMAT.GPTQ_V2)
+    # dequantise-then-matmul helpers on the CPU oracle path
+    torch.manual_seed(0)
+    layer = QuantLinear(4, 32, 64, 48, dtype=torch.float32)
+    lin = torch.nn.Linear(64, 48, bias=False)
+    q = Quantizer()
+    q.configure(4, perchannel=True, sym=True)
+    groups = []
+    for g in range(2):
+        q.find_params(lin.weight.data[:, g * 32:(g + 1) * 32], weight=True)
+        groups.append((q.scale.clone(), q.zero.clone()))
+    scales = torch.cat([s for s, _ in groups], 1)
+    zeros = torch.cat([z for _, z in groups], 1)
+    layer.pack(lin, scales, zeros, None)
+    W = dequant248(layer.qweight, layer.scales, layer.qzeros, layer.g_idx, 4, zero_offset=layer.zero_offset)
+    assert W.shape == (64, 48)
+    x = torch.randn(3, 64)
+    if layer.zero_offset == 0:
+        y = quant_matmul_248(x, layer.qweight, layer.scales, layer.qzeros, layer.g_idx, 4)
+        assert torch.allclose(y, x @ W, atol=1e-5)
+        yt = quant_matmul_248(torch.randn(3, 48), layer.qweight, layer.scales, layer.qzeros, layer.g_idx, 4, transpose=True)
+        assert yt.shape == (3, 64)
+    assert (W.t() - lin.weight.data).abs().max() < 0.2 * lin.weight.data.abs().max()
