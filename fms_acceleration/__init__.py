@@ -8,6 +8,10 @@ _TARGET = "fms_acceleration_b200.framework"
 _SUBMODULES = ['constants', 'framework', 'framework_plugin', 'model_patcher', 'accelerator_patcher', 'utils', 'utils.test_utils']
 
 _pkg = importlib.import_module(_TARGET)
+# any other submodule resolves to the module of the same relative name under the target package
+from fms_acceleration_b200.compat.alias import install_alias  # noqa: E402
+
+install_alias(__name__, _TARGET)
 globals().update({k: v for k, v in vars(_pkg).items() if not k.startswith("__")})
 for _sub in _SUBMODULES:
     try:

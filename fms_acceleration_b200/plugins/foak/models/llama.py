@@ -1,0 +1,7 @@
+"""Patch rules of the ``llama`` family under the reference's module name (fms_acceleration_foak/models/llama.py)."""
+from functools import partial
+
+from .hf import get_mp_rules as _rules
+
+get_mp_rules = partial(_rules, "llama")
+get_mp_rules.__doc__ = "get_mp_rules(base_type, config=None) -> list of ModelPatcherRule for llama"
