@@ -35,3 +35,19 @@ def matmul_lora(X, W, W_quant, A, B, s, out=None, dropout=None):
         xd = dropout(x2) if dropout is not None else x2
         y = y + s * ((xd @ A.to(x2.dtype).t()) @ B.to(x2.dtype).t())
     return y.reshape(*X.shape[:-1], y.shape[-1])
+
+
+def fast_linear_forward(proj, X, temp_lora=None, out=None):
+    """Inference forward of a (LoRA-wrapped, possibly 4-bit) projection: ``X W^T (+ bias) + s (X A^T) B^T``
+    (reference :209-247).  A few rows on a 4-bit base go through the fused dequantise+GEMM kernel."""
+    W, qs, A, B, s, _ = get_lora_parameters(proj)
+    base, _lora = _unwrap(proj)
+    rows = X.numel() // X.shape[-1]
+    if qs is not None and X.is_cuda and rows <= 128:
+        y = fast_gemv(X, base, qs)
+        if A is not None:
+            y = y + s * ((X @ A.to(X.dtype).t()) @ B.to(X.dtype).t())
+    else:
+        y = matmul_lora(X, W, qs, A, B, s)
+    bias = getattr(base, "bias", None)
+    return y if bias is None else y + bias.to(y.dtype)

@@ -129,6 +129,26 @@ def patch_huggingface_clip_grad_norm_fsdp2(accelerator) -> None:
     accelerator.clip_grad_norm_ = lambda parameters, max_norm, norm_type=2.0: clip_grad_norm_(parameters, max_norm, norm_type)
 
 
+def patch_prepare_sd_options() -> bool:
+    """The reference replaces accelerate's ``_prepare_sd_options`` so that FSDP2 writes sharded state dicts that
+    include the ScatterMoE DTensors (fms_acceleration_moe/utils/checkpoint_utils.py:161-180).  Checkpoints here are
+    written by :func:`save_fsdp_model` / :func:`save_fsdp_optimizer` without FSDP, so there is nothing to prepare;
+    the function exists for callers of the reference's name and reports whether accelerate is importable."""
+    try:
+        import accelerate.utils.fsdp_utils  # noqa: F401
+    except Exception:
+        return False
+    return True
+
+
+def patch_huggingface_fsdp2_load_full_state_dict() -> bool:
+    """Counterpart of the reference's patch of ``fsdp2_load_full_state_dict`` / ``fsdp2_prepare_model``
+    (:775-1037), which teaches accelerate's rank-0 loading to skip the already-placed expert shards.  Expert shards
+    are read per rank straight from the safetensors files in ``prepare_scattermoe`` and no FSDP2 wrapper is
+    involved, so no patch is applied; returns whether accelerate is importable."""
+    return patch_prepare_sd_options()
+
+
 def clip_grad_norm_(parameters, max_norm: float, norm_type: float = 2.0, foreach=None) -> torch.Tensor:
     """Total gradient norm over replicated AND expert-parallel parameters: the squared norms of expert shards are
     summed over their expert-parallel group before the global norm is formed (the reference's FSDP2 version,

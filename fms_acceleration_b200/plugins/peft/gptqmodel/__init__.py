@@ -4,3 +4,5 @@ from .models.auto import GPTQModel  # noqa: F401
 from .models.base import BaseGPTQModel  # noqa: F401
 from .quantization.config import QuantizeConfig, FORMAT, QUANT_METHOD  # noqa: F401
 from .utils.backend import Backend  # noqa: F401
+from .quantization.config import QuantizeConfig as BaseQuantizeConfig  # noqa: F401,E402  (older name of the same class)
+from .utils.backend import get_backend  # noqa: F401,E402
