@@ -1,0 +1,18 @@
+"""Context-parallel Mamba2 (scan hand-off and conv halo) stated with library collectives on gloo ranks equals the
+single-sequence computation: the algorithm the peer-memory kernels implement, checked without a GPU."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_context_parallel_scan_equals_the_whole_sequence(world):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29670 + world), os.path.join(HERE, "dist_worker_cp_baseline.py")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, MASTER_ADDR="127.0.0.1"))
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    assert "CP_BASELINE_OK" in out.stdout
