@@ -144,7 +144,6 @@ _STATUS_NAMES = {
     4: "wait on a peer flag timed out",
     5: "bad argument detected on device",
     6: "dequant warps timed out",
-    7: "receive-buffer capacity overflow",
 }
 
 _status_words: dict[int, torch.Tensor] = {}
@@ -169,6 +168,37 @@ def check_status(device=None) -> None:
     if v != 0:
         w.zero_()
         raise NativeError(f"device status {v}: {_STATUS_NAMES.get(v, 'unknown')}")
+
+
+class StatusMonitor:
+    """Checks the status word once per step WITHOUT a host synchronisation: ``poll()`` (end of a step) enqueues a
+    4-byte copy into pinned host memory and records an event; ``raise_if_set()`` (start of the next step) looks at
+    the snapshot only if its event has completed, so the host never waits for the device.  A time-out is therefore
+    raised at most one step late; the word is cleared when it is raised, because every bounded wait on the device
+    gives up early while it is non-zero."""
+
+    def __init__(self, device=None):
+        self.word = status_word(device)
+        self.host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.event = None
+
+    def poll(self) -> None:
+        self.host.copy_(self.word, non_blocking=True)
+        self.event = torch.cuda.Event()
+        self.event.record(torch.cuda.current_stream(self.word.device))
+
+    def raise_if_set(self, wait: bool = False) -> None:
+        if self.event is None:
+            return
+        if wait:
+            self.event.synchronize()
+        elif not self.event.query():
+            return
+        self.event = None
+        v = int(self.host[0])
+        if v != 0:
+            self.word.zero_()
+            raise NativeError(f"device status {v}: {_STATUS_NAMES.get(v, 'unknown')} (reported by an earlier step)")
 
 declare("fmsb_attn_fwd", [P, L, P, L, P, L, P, L, P, P, P, I, I, I, I, F, I, P, P])
 declare("fmsb_attn_delta", [P, P, L, L, P, I, I, I, I, P])

@@ -27,7 +27,8 @@ enum StatusCode : int {
   kTimeoutPeerFlag = 4,   // a wait on another rank's flag ran out
   kBadArgument = 5,
   kTimeoutDequant = 6,    // dequant warps waited too long for a free stage
-  kCapacityOverflow = 7,  // a fixed-capacity receive buffer would have overflowed
+  kCapacityOverflow = 7,  // reserved: capacity overflows are counted in a separate word (see moe.cu), because every
+                          // bounded wait reads the status word as "somebody gave up, follow it out"
 };
 
 // Budget of one bounded wait, in SM clock cycles (about one second at 1.9 GHz).

@@ -52,6 +52,10 @@ struct GemmParams {
   int n_groups;
   const int* seg_off;        // [n_groups + 1] segment starts in rows, multiples of 128 (device memory)
   int b_group_rows;          // rows of B that belong to one group
+  int b2_group_rows;         // rows of B2 that belong to one group (mode 1 with a second operand pair)
+  int n_split;               // > 0: output columns >= n_split take their B tiles from the second B map at column - n_split
+                             //      (two weight matrices side by side in one pass over A; needs kblocks2 == 0)
+  int c_fp32;                // C holds fp32 (accumulating into an fp32 D over several launches)
   long long d_group_stride;  // elements between the D matrices of consecutive groups (mode 2)
   // mode 3: uniform batch indexed by (outer o, inner i), i < n_inner.  Operand offsets in elements of the
   // stored 2-D matrices: rows += o * x_ro + i * x_ri, columns += (i / x_div) * x_ci.
@@ -68,6 +72,7 @@ struct TileInfo {
   int k_begin;       // first contraction element (mode 2: segment start)
   int kblocks1;      // 64-wide blocks of operand pair 1 for this tile
   int b_row_off;     // added to B's row coordinate (group offset)
+  int b2_row_off;    // the same for the second operand pair
   long long d_off;   // element offset of this tile's D matrix
   int a_r, a_c, b_r, b_c;  // batch offsets (mode 3): rows / columns of the stored A and B
   int d_c;                 // column offset of D (mode 3)
@@ -99,6 +104,7 @@ template <int BN>
 __device__ __forceinline__ bool get_tile(int t, const GemmParams& p, TileInfo& ti) {
   const int tiles_n = (p.N + BN - 1) / BN;
   ti.a_r = ti.a_c = ti.b_r = ti.b_c = ti.d_c = 0;
+  ti.b2_row_off = 0;
   if (p.mode == 3) {
     const int tiles_m = (p.M + BM - 1) / BM;
     const int per = tiles_m * tiles_n;
@@ -151,6 +157,7 @@ __device__ __forceinline__ bool get_tile(int t, const GemmParams& p, TileInfo& t
         ti.k_begin = 0;
         ti.kblocks1 = p.kblocks1;
         ti.b_row_off = g * p.b_group_rows;
+        ti.b2_row_off = g * p.b2_group_rows;
         ti.d_off = 0;
         return true;
       }
@@ -234,7 +241,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_const
       bool ok = true;
       TileInfo ti;
       for (int t = blockIdx.x; ok && get_tile<BN>(t, p, ti); t += gridDim.x) {
-        const int m0 = ti.m0, n0 = ti.n0;
+        const int m0 = ti.m0;
         const int kblocks = ti.kblocks1 + p.kblocks2;
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, p.status, kTimeoutProducer)) {
@@ -243,11 +250,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_const
           }
           mbar_expect_tx(full_bar(stage), Cfg::kStageBytes);
           const bool second = kb >= ti.kblocks1;
+          const bool alt = p.n_split > 0 && ti.n0 >= p.n_split;  // right-hand weight matrix of a side-by-side pair
+          const int n0 = alt ? ti.n0 - p.n_split : ti.n0;
           const CUtensorMap* ta = second ? &tmA2 : &tmA1;
-          const CUtensorMap* tb = second ? &tmB2 : &tmB1;
+          const CUtensorMap* tb = (second || alt) ? &tmB2 : &tmB1;
           const int k0 = second ? (kb - ti.kblocks1) * BK : ti.k_begin + kb * BK;
           // the group offset applies to B's row coordinate: the k rows of an MN-major B, the n rows of a K-major B
-          const int brow = second ? 0 : ti.b_row_off;
+          const int brow = second ? ti.b2_row_off : ti.b_row_off;
           // stored A: [M, K] (K-major) or [K, M] (MN-major); the batch offsets address rows / columns of the storage
           if (A_MN == 0) {
             tma_load_2d(sA(stage), ta, full_bar(stage), k0 + ti.a_c, m0 + ti.a_r);
@@ -352,7 +361,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_const
 #pragma unroll
           for (int i = 0; i < CH; ++i) v[i] *= p.alpha;
           if (p.C != nullptr && p.beta != 0.f) {
-            if (p.fmt == 1) {
+            if (p.c_fp32) {
+              const float* crow = reinterpret_cast<const float*>(p.C) + ti.d_off + (long long)gm * p.ldc + gn + ti.d_c;
+              if (full && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
+#pragma unroll
+                for (int i = 0; i < CH; i += 4) {
+                  const float4 f = *reinterpret_cast<const float4*>(crow + i);
+                  v[i] += p.beta * f.x;
+                  v[i + 1] += p.beta * f.y;
+                  v[i + 2] += p.beta * f.z;
+                  v[i + 3] += p.beta * f.w;
+                }
+              } else {
+                for (int i = 0; i < CH; ++i)
+                  if (gn + i < p.N) v[i] += p.beta * crow[i];
+              }
+            } else if (p.fmt == 1) {
               const __nv_bfloat16* crow = reinterpret_cast<const __nv_bfloat16*>(p.C) + ti.d_off + (long long)gm * p.ldc + gn + ti.d_c;
               if (full && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
 #pragma unroll
@@ -511,6 +535,14 @@ int launch_gemm(const CUtensorMap& a1, const CUtensorMap& b1, const CUtensorMap&
 // Constraints: leading dimensions multiples of 8 elements; base pointers 16-byte aligned.  bn selects the N tile (16/32/64/128/256); MN-major B needs bn >= 64.
 // max_ctas > 0 limits the grid (used to leave SMs to a concurrent communication kernel).
 // Returns 0 or a CUDA / encode error code.  Time-outs are reported through *status.
+// Optional extras of the grouped modes.
+struct GroupExtra {
+  const void* B_alt = nullptr;  // second weight matrix for output columns >= n_split (same layout and ldb as B)
+  int n_split = 0;
+  int b2_group_rows = 0;
+  int c_fp32 = 0;
+};
+
 struct BatchDesc {
   int n_batch = 0, n_inner = 1;
   int a_ro = 0, a_ri = 0, a_ci = 0, a_div = 1;
@@ -525,7 +557,8 @@ static int gemm_impl(const void* A1, long long lda1, const void* B1, long long l
                      void* D, long long ldd, int d_fp32, const void* C, long long ldc,        //
                      float alpha, float beta, int M, int N, int fmt, int bn, int max_ctas, int* status,
                      cudaStream_t stream, int mode, int n_groups, const int* seg_off, int b_group_rows,
-                     long long d_group_stride, long long a_rows, long long b_rows, const BatchDesc* bd = nullptr) {
+                     long long d_group_stride, long long a_rows, long long b_rows, const BatchDesc* bd = nullptr,
+                     const GroupExtra* gx = nullptr) {
   using namespace fmsb_host;
   if (M <= 0 || N <= 0) return 0;
   if (K1 <= 0 || K2 < 0) return -2;
@@ -540,18 +573,26 @@ static int gemm_impl(const void* A1, long long lda1, const void* B1, long long l
     if (a_mn) return make_tmap_2d_16b(t, A, a_rows > 0 ? a_rows : K, a_cols > 0 ? a_cols : M, lda, 64, 64);
     return make_tmap_2d_16b(t, A, a_rows > 0 ? a_rows : M, a_cols > 0 ? a_cols : K, lda, fmsb::BM, 64);
   };
+  // with n_split every one of the two side-by-side weight matrices is n_split columns wide
+  const long long n_each = (gx != nullptr && gx->n_split > 0) ? gx->n_split : N;
   auto mk_b = [&](CUtensorMap* t, const void* B, long long ldb, int K) {
-    if (b_mn) return make_tmap_2d_16b(t, B, b_rows > 0 ? b_rows : K, b_cols > 0 ? b_cols : N, ldb, 64, 64);
+    if (b_mn) return make_tmap_2d_16b(t, B, b_rows > 0 ? b_rows : K, b_cols > 0 ? b_cols : n_each, ldb, 64, 64);
     return make_tmap_2d_16b(t, B, b_rows > 0 ? b_rows : N, b_cols > 0 ? b_cols : K, ldb, bn, 64);
   };
   if ((rc = mk_a(&ta1, A1, lda1, K1))) return rc;
   if ((rc = mk_b(&tb1, B1, ldb1, K1))) return rc;
   if (K2 > 0) {
+    if (gx != nullptr && gx->n_split > 0) return -2;  // the second B map is taken
     if ((rc = mk_a(&ta2, A2, lda2, K2))) return rc;
     if ((rc = mk_b(&tb2, B2, ldb2, K2))) return rc;
   } else {
     ta2 = ta1;
     tb2 = tb1;
+    if (gx != nullptr && gx->n_split > 0) {
+      if (gx->B_alt == nullptr || gx->n_split % bn != 0 || gx->n_split >= N) return -2;
+      // same shape as B1: the column extent of one matrix is n_split (MN-major) / its row extent per group (K-major)
+      if ((rc = mk_b(&tb2, gx->B_alt, ldb1, K1))) return rc;
+    }
   }
   fmsb::GemmParams p;
   p.M = M;
@@ -572,6 +613,9 @@ static int gemm_impl(const void* A1, long long lda1, const void* B1, long long l
   p.seg_off = seg_off;
   p.b_group_rows = b_group_rows;
   p.d_group_stride = d_group_stride;
+  p.b2_group_rows = gx != nullptr ? gx->b2_group_rows : 0;
+  p.n_split = gx != nullptr ? gx->n_split : 0;
+  p.c_fp32 = gx != nullptr ? gx->c_fp32 : 0;
   p.n_batch = 0; p.n_inner = 1; p.a_div = p.b_div = 1;
   p.a_ro = p.a_ri = p.a_ci = p.b_ro = p.b_ri = p.b_ci = p.d_ro = p.d_ri = p.d_ci = 0;
   if (bd != nullptr) {
@@ -651,4 +695,39 @@ extern "C" int fmsb_batched_gemm(const void* A, long long lda, long long a_rows,
   if (bd.n_batch <= 0) return 0;
   return gemm_impl(A, lda, B, ldb, K, nullptr, 0, nullptr, 0, 0, a_mn, b_mn, D, ldd, d_fp32, C, ldc, alpha, beta, M, N,
                    fmt, bn, 0, status, stream, 3, 0, nullptr, 0, 0, a_rows, b_rows, &bd);
+}
+
+// Grouped GEMM with the extras of the mixture-of-experts layer:
+//   * B_alt / n_split (mode 1 forward and mode 2): output columns [n_split, N) are produced from B_alt instead of B,
+//     so gate and up projection (two weight tensors of the same shape) run as ONE pass over A with N = 2 * n_split;
+//     for mode 2 the analogue is the pair of weight gradients (B = the left, B_alt = the right gradient operand).
+//   * A2 / B2 / K2 (mode 1): a second operand pair accumulated into the same tile, with its own per-group row
+//     offset b2_group_rows: D[seg_g] = A[seg_g] . B_g + A2[seg_g] . B2_g  (input gradient through gate and up in one
+//     launch, or a per-expert low-rank update next to the frozen expert weight).
+//   * c_fp32: C is fp32 (D += over several launches when D is fp32).
+extern "C" int fmsb_grouped_gemm2(const void* A, long long lda, const void* B, long long ldb, int K, int b_mn,
+                                  const void* B_alt, int n_split, const void* A2, long long lda2, const void* B2,
+                                  long long ldb2, int K2, void* D, long long ldd, int d_fp32, const void* C,
+                                  long long ldc, int c_fp32, float alpha, float beta, int M, int N, int fmt, int bn,
+                                  int mode, int n_groups, const int* seg_off, long long d_group_stride, long long a_rows,
+                                  long long b_rows, int max_ctas, int* status, cudaStream_t stream) {
+  GroupExtra gx;
+  gx.B_alt = B_alt;
+  gx.n_split = n_split;
+  gx.c_fp32 = c_fp32;
+  if (mode == 1) {
+    const int b_group_rows = b_mn ? K : N;
+    // with n_split the K-major (b_mn = 0) form would need per-matrix row counts: only the MN-major form is offered
+    if (n_split > 0 && !b_mn) return -2;
+    gx.b2_group_rows = K2 > 0 ? (b_mn ? K2 : N) : 0;
+    return gemm_impl(A, lda, B, ldb, K, A2, lda2, B2, ldb2, K2, 0, b_mn, D, ldd, d_fp32, C, ldc, alpha, beta, (int)a_rows,
+                     N, fmt, bn, max_ctas, status, stream, 1, n_groups, seg_off, b_group_rows, 0, a_rows, b_rows, nullptr,
+                     &gx);
+  }
+  if (mode == 2) {
+    if (K2 > 0) return -2;
+    return gemm_impl(A, lda, B, ldb, 64, nullptr, 0, nullptr, 0, 0, 1, 1, D, ldd, d_fp32, C, ldc, alpha, beta, M, N, fmt,
+                     bn, max_ctas, status, stream, 2, n_groups, seg_off, 0, d_group_stride, a_rows, b_rows, nullptr, &gx);
+  }
+  return -2;
 }

@@ -182,8 +182,10 @@ __global__ void expert_count_kernel(const int* __restrict__ topk_idx, long long 
   extern __shared__ int sh[];
   for (int e = threadIdx.x; e < E; e += blockDim.x) sh[e] = 0;
   __syncthreads();
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
-    atomicAdd(&sh[topk_idx[i]], 1);
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int e = topk_idx[i];
+    if (e >= 0 && e < E) atomicAdd(&sh[e], 1);  // negative keys: entries without a pair
+  }
   __syncthreads();
   for (int e = threadIdx.x; e < E; e += blockDim.x)
     if (sh[e]) atomicAdd(&counts[e], sh[e]);
@@ -196,10 +198,13 @@ __global__ void expert_count_kernel(const int* __restrict__ topk_idx, long long 
 // Outputs (local): seg_off[E_local + 1] padded (x128) offsets of my experts in my receive buffer,
 //   seg_cnt[E_local] row counts, send_base[0..E) = first slot of MY rows of global expert e in its owner's buffer,
 //   send_base[E..2E) = end of the valid slots of expert e.  When an owner's buffer (capacity rows) would overflow,
-//   the excess rows are dropped consistently on every rank and status gets kCapacityOverflow.
+//   the excess rows are dropped consistently on every rank and *overflow is incremented.  That counter is
+//   information for the host; it is NOT the status word, so the bounded waits of later kernels do not give up
+//   because rows were dropped.
 __global__ void moe_plan_kernel(MoePeers count_tables, MoePeers signals, const int* __restrict__ my_counts, int rank,
                                 int world, int E, int capacity, uint32_t epoch, int* __restrict__ seg_off,
-                                int* __restrict__ seg_cnt, int* __restrict__ send_base, int* needed, int* status) {
+                                int* __restrict__ seg_cnt, int* __restrict__ send_base, int* needed, int* overflow,
+                                int* status) {
   const int E_local = E / world;
   __shared__ int ok;
   if (threadIdx.x == 0) ok = 1;
@@ -239,7 +244,7 @@ __global__ void moe_plan_kernel(MoePeers count_tables, MoePeers signals, const i
         int kept = total;
         if (kept > room) {
           kept = room > 0 ? room : 0;
-          report_status(status, kCapacityOverflow);
+          if (overflow != nullptr) atomicAdd(overflow, 1);
         }
         send_base[e] = off + before_me;
         send_base[E + e] = off + kept;  // first slot that is no longer valid for expert e
@@ -343,6 +348,9 @@ __global__ void __launch_bounds__(kAssignChunk) moe_assign_kernel(const int* __r
     const int slot = wcnt[warp * E + e] + __popc(peers & ((1u << lane) - 1));
     const long long i = (long long)blockIdx.x * kAssignChunk + threadIdx.x;
     dest_row[i] = slot < send_base[E + e] ? slot : -1;  // -1: dropped (capacity overflow)
+  } else {
+    const long long i = (long long)blockIdx.x * kAssignChunk + threadIdx.x;
+    if (i < n) dest_row[i] = -1;  // entry without a pair (negative key)
   }
 }
 
@@ -358,15 +366,19 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(const T* __restrict__
                                                            const int* __restrict__ dest_row,
                                                            const float* __restrict__ scale, long long n_tokens, int k,
                                                            int H, int E_local, MoePeers recv, long long ld_recv,
-                                                           const float* __restrict__ meta_vals, MoePeers meta_recv) {
+                                                           const float* __restrict__ meta_vals, MoePeers meta_recv,
+                                                           int rows_per_src, const int* __restrict__ valid_cnt) {
   const long long t = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (t >= n_tokens) return;
+  // staged input (rows_per_src > 0): row t belongs to source block t / rows_per_src and is valid only below that
+  // block's row count
+  if (rows_per_src > 0 && (int)(t % rows_per_src) >= valid_cnt[t / rows_per_src]) return;
   int my_owner = 0, my_row = -1;
   float my_scale = 1.f;
   if (lane < k) {
     const long long pair = t * k + lane;
-    my_owner = topk_idx[pair] / E_local;
+    my_owner = topk_idx != nullptr ? topk_idx[pair] / E_local : 0;
     my_row = dest_row[pair];
     if (SCALED) my_scale = scale[pair];
     // optional per-row scalar travelling with the row (the routing weight in the backward pass)
@@ -442,16 +454,19 @@ template <typename T>
 __global__ void __launch_bounds__(256) moe_combine_kernel(MoePeers ybuf, long long ldy, const int* __restrict__ topk_idx,
                                                           const int* __restrict__ dest_row, const float* __restrict__ w,
                                                           long long T_tokens, int k, int H, int E_local,
-                                                          T* __restrict__ out, long long ldo) {
+                                                          T* __restrict__ out, long long ldo, int rows_per_src,
+                                                          const int* __restrict__ valid_cnt) {
   const long long t = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (t >= T_tokens) return;
+  if (rows_per_src > 0 && (int)(t % rows_per_src) >= valid_cnt[t / rows_per_src]) return;  // see moe_dispatch_kernel
   int my_owner = 0, my_row = -1;
   float my_w = 1.f;
   if (lane < k) {
     const long long pair = t * k + lane;
-    my_owner = topk_idx[pair] / E_local;
     my_row = dest_row[pair];
+    // entries without a row may carry a negative key: never index the peer table with it
+    my_owner = (topk_idx != nullptr && my_row >= 0) ? topk_idx[pair] / E_local : 0;
     if (w != nullptr) my_w = w[pair];
   }
   constexpr int CV = 4;  // vectors of 16 bytes per lane and pass (1024 columns per pass)
@@ -581,6 +596,90 @@ __global__ void moe_gather_scalar_kernel(MoePeers vals, const int* __restrict__ 
   out[pair] = row < 0 ? 0.f : reinterpret_cast<const float*>(vals.p[topk_idx[pair] / E_local])[row];
 }
 
+
+// ----------------------------------------------------------------------------------------
+// one row per (token, destination rank): staging
+// ----------------------------------------------------------------------------------------
+// A token whose top-k experts live on r different ranks crosses the links r times, not k times: the source
+// writes the row ONCE per destination rank into that rank's staging block, together with the k slots (or -1) the
+// row has to be replicated to inside the owner's expert-sorted buffer and the k routing weights.  The owner then
+// replicates locally (moe_dispatch_kernel on its own memory), and on the way back reduces the up-to-k expert
+// outputs of a staged row into one row before the source pulls it (moe_combine_kernel on its own memory).
+//
+// hit[t, r] = r when token t has at least one kept pair on rank r, else -1; cnt[r] = number of such tokens.
+__global__ void moe_rank_hits_kernel(const int* __restrict__ topk_idx, const int* __restrict__ dest_row,
+                                     long long n_tokens, int k, int E_local, int world, int* __restrict__ hit,
+                                     int* __restrict__ cnt) {
+  __shared__ int sh[kMoeMaxRanks];
+  if (threadIdx.x < kMoeMaxRanks) sh[threadIdx.x] = 0;
+  __syncthreads();
+  const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (t < n_tokens) {
+    unsigned mask = 0;
+    for (int j = 0; j < k; ++j)
+      if (dest_row[t * k + j] >= 0) mask |= 1u << (topk_idx[t * k + j] / E_local);
+    for (int r = 0; r < world; ++r) {
+      const bool on = (mask >> r) & 1u;
+      hit[t * world + r] = on ? r : -1;
+      if (on) atomicAdd(&sh[r], 1);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < world && sh[threadIdx.x]) atomicAdd(&cnt[threadIdx.x], sh[threadIdx.x]);
+}
+
+// One warp per token: x[t] goes to stage.p[r][stage_row[t, r]] for every rank r with stage_row >= 0; lanes 0..k-1
+// deliver the row's metadata: meta_slot.p[r][row * k + j] = slot of pair j inside r's expert-sorted buffer when
+// expert j lives on r (else -1), meta_gate.p[r][row * k + j] = routing weight of pair j.  CTA 0 also tells every
+// rank how many rows this rank staged there (cnt_recv.p[r][me] = stage_cnt[r]).
+template <typename T>
+__global__ void __launch_bounds__(256) moe_dispatch_staged_kernel(
+    const T* __restrict__ x, long long ldx, const int* __restrict__ topk_idx, const int* __restrict__ dest_row,
+    const float* __restrict__ gates, const int* __restrict__ stage_row, const int* __restrict__ stage_cnt,
+    long long n_tokens, int k, int H, int E_local, int world, int me, MoePeers stage, long long ld_stage,
+    MoePeers meta_slot, MoePeers meta_gate, MoePeers cnt_recv) {
+  if (blockIdx.x == 0 && threadIdx.x < world)
+    reinterpret_cast<int*>(cnt_recv.p[threadIdx.x])[me] = stage_cnt[threadIdx.x];
+  const long long t = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (t >= n_tokens) return;
+  int my_owner = -1, my_slot = -1;
+  float my_gate = 1.f;
+  if (lane < k) {
+    const long long pair = t * k + lane;
+    my_slot = dest_row[pair];
+    my_owner = topk_idx[pair] / E_local;
+    if (gates != nullptr) my_gate = gates[pair];
+  }
+  const int* srow = stage_row + t * world;
+  for (int r = 0; r < world; ++r) {
+    const int row = srow[r];
+    if (row < 0 || lane >= k) continue;
+    reinterpret_cast<int*>(meta_slot.p[r])[(long long)row * k + lane] = (my_owner == r) ? my_slot : -1;
+    reinterpret_cast<float*>(meta_gate.p[r])[(long long)row * k + lane] = my_gate;
+  }
+  const T* src = x + t * ldx;
+  const int nvec = H >> 3;
+  for (int v0 = 0; v0 < nvec; v0 += 256) {
+    uint4 v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int vi = v0 + lane + 32 * j;
+      if (vi < nvec) v[j] = *reinterpret_cast<const uint4*>(src + vi * 8);
+    }
+    for (int r = 0; r < world; ++r) {
+      const int row = srow[r];
+      if (row < 0) continue;
+      T* dst = reinterpret_cast<T*>(stage.p[r]) + (long long)row * ld_stage;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int vi = v0 + lane + 32 * j;
+        if (vi < nvec) *reinterpret_cast<uint4*>(dst + vi * 8) = v[j];
+      }
+    }
+  }
+}
+
 }  // namespace fmsb
 
 using namespace fmsb;
@@ -613,10 +712,11 @@ extern "C" int fmsb_moe_router_bwd(const float* logits, const int* topk_idx, con
 
 // counts must be zeroed by the caller.  Then plan + assign.  count_tables / signals may be null when world == 1.
 // chunk_scratch: ceil(n_pairs / 1024) * E ints of work space for the slot assignment.
+// overflow (may be null): incremented once per expert whose rows did not all fit; separate from the status word.
 extern "C" int fmsb_moe_plan(const int* topk_idx, long long n_pairs, int E, int rank, int world, int capacity,
                              int* counts, void* const* count_tables, void* const* signals, unsigned epoch,
                              int* seg_off, int* seg_cnt, int* send_base, int* dest_row, int* needed,
-                             int* chunk_scratch, int* status, cudaStream_t stream) {
+                             int* chunk_scratch, int* overflow, int* status, cudaStream_t stream) {
   if (E > kMoeMaxExperts || world > kMoeMaxRanks || E % world != 0) return -2;
   if (n_pairs > 0 && chunk_scratch == nullptr) return -2;
   if (n_pairs > 0) {
@@ -627,7 +727,7 @@ extern "C" int fmsb_moe_plan(const int* topk_idx, long long n_pairs, int E, int 
   MoePeers ct = world > 1 ? moe_ptrs(count_tables, world) : MoePeers{};
   MoePeers sg = world > 1 ? moe_ptrs(signals, world) : MoePeers{};
   moe_plan_kernel<<<1, 256, 0, stream>>>(ct, sg, counts, rank, world, E, capacity, epoch, seg_off, seg_cnt, send_base,
-                                         needed, status);
+                                         needed, overflow, status);
   if (n_pairs > 0) {
     const int n_chunks = (int)((n_pairs + kAssignChunk - 1) / kAssignChunk);
     const size_t smem = (size_t)32 * E * sizeof(int);  // at most 64 KB (E <= 512)
@@ -651,7 +751,7 @@ extern "C" int fmsb_moe_dispatch(const void* x, long long ldx, const int* topk_i
   const long long n_tokens = n_pairs / k;
   const long long blocks = (n_tokens * 32 + 255) / 256;
 #define FMSB_DISPATCH_CALL(T, SC) \
-  moe_dispatch_kernel<T, SC><<<(unsigned)blocks, 256, 0, stream>>>((const T*)x, ldx, topk_idx, dest_row, scale, n_tokens, k, H, E_local, r, ld_recv, nullptr, MoePeers{})
+  moe_dispatch_kernel<T, SC><<<(unsigned)blocks, 256, 0, stream>>>((const T*)x, ldx, topk_idx, dest_row, scale, n_tokens, k, H, E_local, r, ld_recv, nullptr, MoePeers{}, 0, nullptr)
   if (dtype == 1) { if (scale != nullptr) FMSB_DISPATCH_CALL(__nv_bfloat16, true); else FMSB_DISPATCH_CALL(__nv_bfloat16, false); }
   else { if (scale != nullptr) FMSB_DISPATCH_CALL(__half, true); else FMSB_DISPATCH_CALL(__half, false); }
 #undef FMSB_DISPATCH_CALL
@@ -670,9 +770,9 @@ extern "C" int fmsb_moe_dispatch_meta(const void* x, long long ldx, const int* t
   const long long n_tokens = n_pairs / k;
   const long long blocks = (n_tokens * 32 + 255) / 256;
   if (dtype == 1)
-    moe_dispatch_kernel<__nv_bfloat16, false><<<(unsigned)blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, topk_idx, dest_row, nullptr, n_tokens, k, H, E_local, r, ld_recv, meta_vals, m);
+    moe_dispatch_kernel<__nv_bfloat16, false><<<(unsigned)blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, topk_idx, dest_row, nullptr, n_tokens, k, H, E_local, r, ld_recv, meta_vals, m, 0, nullptr);
   else
-    moe_dispatch_kernel<__half, false><<<(unsigned)blocks, 256, 0, stream>>>((const __half*)x, ldx, topk_idx, dest_row, nullptr, n_tokens, k, H, E_local, r, ld_recv, meta_vals, m);
+    moe_dispatch_kernel<__half, false><<<(unsigned)blocks, 256, 0, stream>>>((const __half*)x, ldx, topk_idx, dest_row, nullptr, n_tokens, k, H, E_local, r, ld_recv, meta_vals, m, 0, nullptr);
   return (int)cudaGetLastError();
 }
 
@@ -717,9 +817,9 @@ extern "C" int fmsb_moe_combine(void* const* ybuf, long long ldy, const int* top
   MoePeers y = moe_ptrs(ybuf, world);
   const long long blocks = (T_tokens * 32 + 255) / 256;
   if (dtype == 1)
-    moe_combine_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>(y, ldy, topk_idx, dest_row, w, T_tokens, k, H, E_local, (__nv_bfloat16*)out, ldo);
+    moe_combine_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>(y, ldy, topk_idx, dest_row, w, T_tokens, k, H, E_local, (__nv_bfloat16*)out, ldo, 0, nullptr);
   else
-    moe_combine_kernel<__half><<<(unsigned)blocks, 256, 0, stream>>>(y, ldy, topk_idx, dest_row, w, T_tokens, k, H, E_local, (__half*)out, ldo);
+    moe_combine_kernel<__half><<<(unsigned)blocks, 256, 0, stream>>>(y, ldy, topk_idx, dest_row, w, T_tokens, k, H, E_local, (__half*)out, ldo, 0, nullptr);
   return (int)cudaGetLastError();
 }
 
@@ -733,5 +833,91 @@ extern "C" int fmsb_moe_gate_grad(void* const* ybuf, long long ldy, const int* t
     moe_gate_grad_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>(y, ldy, topk_idx, dest_row, (const __nv_bfloat16*)dout, lddo, n_pairs, k, H, E_local, dgate);
   else
     moe_gate_grad_kernel<__half><<<(unsigned)blocks, 256, 0, stream>>>(y, ldy, topk_idx, dest_row, (const __half*)dout, lddo, n_pairs, k, H, E_local, dgate);
+  return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------- staged exchange
+// Staging layout of the per-(token, rank) exchange.  hit / stage_row are [n_tokens, world]; stage_base holds
+// 2 * world ints: the first staging row of this rank's block (rank * rows_per_src) world times, then its end.
+// chunk_scratch: ceil(n_tokens * world / 1024) * world ints.  stage_cnt[world] is zeroed here.
+extern "C" int fmsb_moe_stage_plan(const int* topk_idx, const int* dest_row, long long n_tokens, int k, int E_local,
+                                   int world, const int* stage_base, int* hit, int* stage_row, int* stage_cnt,
+                                   int* chunk_scratch, cudaStream_t stream) {
+  if (world > kMoeMaxRanks || k < 1 || k > 32) return -2;
+  cudaError_t e = cudaMemsetAsync(stage_cnt, 0, sizeof(int) * world, stream);
+  if (e != cudaSuccess) return (int)e;
+  if (n_tokens <= 0) return 0;
+  moe_rank_hits_kernel<<<(unsigned)((n_tokens + 255) / 256), 256, 0, stream>>>(topk_idx, dest_row, n_tokens, k, E_local,
+                                                                             world, hit, stage_cnt);
+  const long long n = n_tokens * world;
+  const int n_chunks = (int)((n + kAssignChunk - 1) / kAssignChunk);
+  const size_t smem = (size_t)32 * world * sizeof(int);
+  moe_assign_count_kernel<<<n_chunks, kAssignChunk, smem, stream>>>(hit, n, world, chunk_scratch);
+  moe_assign_scan_kernel<<<world, 256, 0, stream>>>(chunk_scratch, n_chunks, world, stage_base);
+  moe_assign_kernel<<<n_chunks, kAssignChunk, smem, stream>>>(hit, n, world, chunk_scratch, stage_base, stage_row);
+  return (int)cudaGetLastError();
+}
+
+// Source side: push every token row once per destination rank, with its slots and routing weights.
+extern "C" int fmsb_moe_dispatch_staged(const void* x, long long ldx, const int* topk_idx, const int* dest_row,
+                                        const float* gates, const int* stage_row, const int* stage_cnt,
+                                        long long n_tokens, int k, int H, int E_local, int world, int me,
+                                        void* const* stage, long long ld_stage, void* const* meta_slot,
+                                        void* const* meta_gate, void* const* cnt_recv, int dtype, cudaStream_t stream) {
+  if (world > kMoeMaxRanks || H % 8 != 0 || ldx % 8 != 0 || ld_stage % 8 != 0 || k < 1 || k > 32) return -2;
+  MoePeers st = moe_ptrs(stage, world), ms = moe_ptrs(meta_slot, world), mg = moe_ptrs(meta_gate, world),
+           cr = moe_ptrs(cnt_recv, world);
+  long long blocks = (n_tokens * 32 + 255) / 256;
+  if (blocks < 1) blocks = 1;  // the row counts are delivered even when this rank has no token
+  if (dtype == 1)
+    moe_dispatch_staged_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>(
+        (const __nv_bfloat16*)x, ldx, topk_idx, dest_row, gates, stage_row, stage_cnt, n_tokens, k, H, E_local, world, me,
+        st, ld_stage, ms, mg, cr);
+  else
+    moe_dispatch_staged_kernel<__half><<<(unsigned)blocks, 256, 0, stream>>>(
+        (const __half*)x, ldx, topk_idx, dest_row, gates, stage_row, stage_cnt, n_tokens, k, H, E_local, world, me, st,
+        ld_stage, ms, mg, cr);
+  return (int)cudaGetLastError();
+}
+
+// Owner side, local memory only: staged row i (block i / rows_per_src, valid below cnt[block]) is copied to the
+// slots meta_slot[i, 0..k) of the expert-sorted buffer; slot_vals (optional, [rows, k]) is delivered per slot into
+// slot_out (the routing weight of every received row in the backward pass).
+extern "C" int fmsb_moe_replicate(const void* stage, long long ld_stage, const int* meta_slot, const float* slot_vals,
+                                  float* slot_out, long long n_rows, int rows_per_src, const int* cnt, int k, int H,
+                                  void* buf, long long ld_buf, int dtype, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (H % 8 != 0 || ld_stage % 8 != 0 || ld_buf % 8 != 0 || k < 1 || k > 32 || rows_per_src <= 0) return -2;
+  MoePeers r{}, m{};
+  r.p[0] = buf;
+  m.p[0] = slot_out;
+  const float* mv = slot_out != nullptr ? slot_vals : nullptr;
+  const long long blocks = (n_rows * 32 + 255) / 256;
+  if (dtype == 1)
+    moe_dispatch_kernel<__nv_bfloat16, false><<<(unsigned)blocks, 256, 0, stream>>>(
+        (const __nv_bfloat16*)stage, ld_stage, nullptr, meta_slot, nullptr, n_rows, k, H, 1, r, ld_buf, mv, m,
+        rows_per_src, cnt);
+  else
+    moe_dispatch_kernel<__half, false><<<(unsigned)blocks, 256, 0, stream>>>(
+        (const __half*)stage, ld_stage, nullptr, meta_slot, nullptr, n_rows, k, H, 1, r, ld_buf, mv, m, rows_per_src, cnt);
+  return (int)cudaGetLastError();
+}
+
+// Owner side, local memory only: out[i] = sum_j w[i, j] * buf[meta_slot[i, j]] over the slots >= 0 of staged row i
+// (w null: plain sum).  This is the reduction that lets one row per (token, rank) travel back.
+extern "C" int fmsb_moe_prereduce(const void* buf, long long ld_buf, const int* meta_slot, const float* w,
+                                  long long n_rows, int rows_per_src, const int* cnt, int k, int H, void* out,
+                                  long long ld_out, int dtype, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (H % 8 != 0 || ld_buf % 8 != 0 || ld_out % 8 != 0 || k < 1 || k > 32 || rows_per_src <= 0) return -2;
+  MoePeers y{};
+  y.p[0] = const_cast<void*>(buf);
+  const long long blocks = (n_rows * 32 + 255) / 256;
+  if (dtype == 1)
+    moe_combine_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>(
+        y, ld_buf, nullptr, meta_slot, w, n_rows, k, H, 1, (__nv_bfloat16*)out, ld_out, rows_per_src, cnt);
+  else
+    moe_combine_kernel<__half><<<(unsigned)blocks, 256, 0, stream>>>(y, ld_buf, nullptr, meta_slot, w, n_rows, k, H, 1,
+                                                                   (__half*)out, ld_out, rows_per_src, cnt);
   return (int)cudaGetLastError();
 }

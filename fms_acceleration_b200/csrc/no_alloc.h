@@ -26,9 +26,17 @@ extern "C" {
 //
 //   * H must be a multiple of 8 and at most FMSB_NOALLOC_MAX_H; larger rows are rejected with
 //     FMSB_NOALLOC_ERR_TOO_LARGE and a message retrievable through fmsb_noalloc_last_error().
+//   * dy, x, w, dres_in (when given) and dx must be 16-byte aligned (the kernels use 16-byte accesses; rows are
+//     H elements apart, so with H a multiple of 8 every row is aligned when the base is); inv_rms and dw 4-byte
+//     aligned.  A pointer off these boundaries is rejected with FMSB_NOALLOC_ERR_BAD_ARG; nothing is launched.
 //   * The first call on a device looks up the device address of the scratch array (cudaGetSymbolAddress, with
 //     that device current).  Make that first call outside of any stream capture.
-//   * No cudaMalloc / cudaFree / allocating library routine is called, on any path.
+//   * The entry point itself calls no cudaMalloc / cudaFree / allocating library routine, on any path.  What it
+//     cannot control is the CUDA runtime's own module loading: with lazy loading (the default) the library's
+//     device code, this 4 MiB array included, is placed on a device the first time something from the library is
+//     used there, which can be this entry point's first call.  A caller with a no-allocation region should
+//     therefore make one warm-up call per device (any small valid input) before entering that region; from then
+//     on nothing is reserved or released.
 //   * All calls on one device share the one scratch array and it keeps whatever the last call left in it.
 //     Nothing in it has to start at zero: a call overwrites every partial row before it reads it.  Two calls
 //     that overlap on the GPU (different streams, or one stream per thread) race on the scratch: serialise them.

@@ -3,6 +3,8 @@
 // no_alloc.h for the contract.  This entry point has no counterpart in the reference project.
 #include "no_alloc.h"
 
+#include <atomic>
+#include <cstdint>
 #include <cstdio>
 #include <cstring>
 
@@ -155,23 +157,23 @@ __global__ void colsum_noalloc_kernel(const float* __restrict__ partial, float* 
 
 // Device address of the scratch array, looked up once per device (with that device current).
 constexpr int kMaxDevices = 64;
-float* g_scratch_addr[kMaxDevices] = {};
+std::atomic<float*> g_scratch_addr[kMaxDevices] = {};
 
 int scratch_for_current_device(float** out) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
   if (dev < 0 || dev >= kMaxDevices) return FMSB_NOALLOC_ERR_SETUP;
-  if (g_scratch_addr[dev] == nullptr) {
+  if (g_scratch_addr[dev].load(std::memory_order_acquire) == nullptr) {
     float* p = nullptr;
     e = cudaGetSymbolAddress((void**)&p, g_dw_partial);
     if (e != cudaSuccess || p == nullptr) {
       set_error("cudaGetSymbolAddress for the built-in scratch failed on device %lld (CUDA error %lld)", dev, (long long)e);
       return e != cudaSuccess ? (int)e : FMSB_NOALLOC_ERR_SETUP;
     }
-    g_scratch_addr[dev] = p;
+    g_scratch_addr[dev].store(p, std::memory_order_release);  // every thread that looks it up stores the same value
   }
-  *out = g_scratch_addr[dev];
+  *out = g_scratch_addr[dev].load(std::memory_order_acquire);
   return 0;
 }
 
@@ -186,6 +188,19 @@ extern "C" int fmsb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const voi
   if (dy == nullptr || x == nullptr || w == nullptr || inv_rms == nullptr || dx == nullptr || dw == nullptr ||
       rows < 0 || H <= 0 || H % 8 != 0 || (dtype != 0 && dtype != 1)) {
     set_error("bad argument (null pointer, H not a positive multiple of 8, or dtype not 0/1): rows=%lld H=%lld", rows, H);
+    return FMSB_NOALLOC_ERR_BAD_ARG;
+  }
+  // the kernels move 16 bytes per access on every row-sized operand; a pointer off that boundary would fault
+  // on the device, so it is refused here instead
+  const void* const vec_ptrs[] = {dy, x, w, dres_in, dx};
+  for (const void* q : vec_ptrs) {
+    if ((reinterpret_cast<uintptr_t>(q) & 15u) != 0) {
+      set_error("dy, x, w, dres_in and dx must be 16-byte aligned (rows=%lld H=%lld)", rows, H);
+      return FMSB_NOALLOC_ERR_BAD_ARG;
+    }
+  }
+  if (((reinterpret_cast<uintptr_t>(inv_rms) | reinterpret_cast<uintptr_t>(dw)) & 3u) != 0) {
+    set_error("inv_rms and dw must be 4-byte aligned (rows=%lld H=%lld)", rows, H);
     return FMSB_NOALLOC_ERR_BAD_ARG;
   }
   if (H > FMSB_NOALLOC_MAX_H) {

@@ -15,7 +15,7 @@ from torch import nn
 
 from ..ops import cross_entropy as CE
 from .config import DecoderConfig
-from .llama import CausalLMOutput, _init_weights
+from .llama import CausalLMOutput, _init_weights, _run_layer
 
 
 class GPTBigCodeAttention(nn.Module):
@@ -112,7 +112,7 @@ class GPTBigCodeModel(nn.Module):
             cu = torch.nonzero(pos == 0).reshape(-1).tolist() + [T]
         x = self.wte(input_ids.reshape(-1)) + self.wpe(pos)
         for blk in self.h:
-            x = blk(x, cu)
+            x = _run_layer(self, blk, x, cu)
         return self.ln_f(x)
 
 
@@ -131,8 +131,11 @@ class GPTBigCodeForCausalLM(nn.Module):
     def get_output_embeddings(self):
         return self.lm_head
 
-    def gradient_checkpointing_enable(self, **kwargs):
-        self._gradient_checkpointing = True
+    def gradient_checkpointing_enable(self, gradient_checkpointing_kwargs=None, **kwargs):
+        self.transformer.gradient_checkpointing = True
+
+    def gradient_checkpointing_disable(self):
+        self.transformer.gradient_checkpointing = False
 
     def enable_input_require_grads(self):
         self.transformer.wte.register_forward_hook(lambda m, i, o: o.requires_grad_(True))

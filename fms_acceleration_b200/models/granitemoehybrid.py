@@ -11,7 +11,7 @@ from torch import nn
 
 from .config import DecoderConfig
 from .granitemoe import GraniteMoeMoE, GraniteMoeSharedMLP
-from .llama import LlamaAttention, LlamaForCausalLM, LlamaRMSNorm, _init_weights
+from .llama import _run_layer, LlamaAttention, LlamaForCausalLM, LlamaRMSNorm, _init_weights
 from .mamba2 import Mamba2Mixer
 
 
@@ -86,7 +86,7 @@ class GraniteMoeHybridModel(nn.Module):
         sin_t = torch.zeros(1, self.cfg.head_dim // 2, device=dev)
         pos = torch.zeros(T, dtype=torch.long, device=dev)
         for layer in self.layers:
-            x = layer(x, pos, cos_t, sin_t, cu)
+            x = _run_layer(self, layer, x, pos, cos_t, sin_t, cu)
         return self.norm(x)
 
 

@@ -157,6 +157,17 @@ class LlamaDecoderLayer(nn.Module):
         return torch.add(h, out, alpha=self.cfg.residual_multiplier)
 
 
+def _run_layer(model, fn, x, *args):
+    """One decoder layer, under activation checkpointing when the model asks for it (the reference benchmarks run
+    with it on, scripts/benchmarks/defaults.yaml:15): only the layer input is kept and the layer runs a second time
+    in backward."""
+    if getattr(model, "gradient_checkpointing", False) and model.training and torch.is_grad_enabled() and x.requires_grad:
+        from torch.utils.checkpoint import checkpoint
+
+        return checkpoint(fn, x, *args, use_reentrant=False)
+    return fn(x, *args)
+
+
 class LlamaModel(nn.Module):
     layer_cls = LlamaDecoderLayer
 
@@ -177,6 +188,7 @@ class LlamaModel(nn.Module):
         self.norm = LlamaRMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
         self._rope = None
         self.fused = False
+        self.gradient_checkpointing = False  # recompute every decoder layer in backward instead of keeping its activations
 
     def rope(self, device, max_pos: int):
         if self._rope is None or self._rope[0].device != torch.device(device) or self._rope[0].shape[0] < max_pos:
@@ -205,7 +217,7 @@ class LlamaModel(nn.Module):
                 batch = PackedBatch.from_position_ids(position_ids, cos_t, sin_t)
             x = x.contiguous()
             for layer in self.layers:
-                x = layer.forward_fused(x, batch)
+                x = _run_layer(self, layer.forward_fused, x, batch)
             return RN.rmsnorm(x, self.norm.weight, self.norm.variance_epsilon)
         # eager
         if cu_seqlens is None:
@@ -220,7 +232,7 @@ class LlamaModel(nn.Module):
             doc = torch.searchsorted(cu_t, idx, right=True) - 1
             pos = idx - cu_t[doc]
         for layer in self.layers:
-            x = layer(x, pos, cos_t, sin_t, cu)
+            x = _run_layer(self, layer, x, pos, cos_t, sin_t, cu)
         return self.norm(x)
 
 
@@ -245,8 +257,11 @@ class LlamaForCausalLM(nn.Module):
     def get_output_embeddings(self):
         return self.lm_head
 
-    def gradient_checkpointing_enable(self, **kwargs):
-        self._gradient_checkpointing = True
+    def gradient_checkpointing_enable(self, gradient_checkpointing_kwargs=None, **kwargs):
+        self.model.gradient_checkpointing = True
+
+    def gradient_checkpointing_disable(self):
+        self.model.gradient_checkpointing = False
 
     def enable_input_require_grads(self):
         self.model.embed_tokens.register_forward_hook(lambda m, i, o: o.requires_grad_(True))

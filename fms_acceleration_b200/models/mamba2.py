@@ -19,7 +19,7 @@ from ..ops import cross_entropy as CE
 from ..ops import mamba as MB
 from ..ops import rmsnorm as RN
 from .config import DecoderConfig
-from .llama import CausalLMOutput, LlamaRMSNorm, _DenseLinear, _init_weights
+from .llama import CausalLMOutput, LlamaRMSNorm, _DenseLinear, _init_weights, _run_layer
 
 
 class MambaRMSNormGated(nn.Module):
@@ -155,7 +155,7 @@ class Mamba2Model(nn.Module):
     def forward(self, input_ids):
         x = self.embed_tokens(input_ids.reshape(-1))
         for blk in self.layers:
-            x = blk(x)
+            x = _run_layer(self, blk, x)
         return RN.rmsnorm(x, self.norm_f.weight, self.norm_f.variance_epsilon) if x.is_cuda else self.norm_f(x)
 
 
@@ -176,6 +176,12 @@ class Mamba2ForCausalLM(nn.Module):
     def enable_fused(self, fast_loss="fused_ce_liger"):
         self.fast_loss = fast_loss
         return self
+
+    def gradient_checkpointing_enable(self, gradient_checkpointing_kwargs=None, **kwargs):
+        self.model.gradient_checkpointing = True
+
+    def gradient_checkpointing_disable(self):
+        self.model.gradient_checkpointing = False
 
     def forward(self, input_ids, labels=None, num_items_in_batch=None, **kwargs):
         """One sequence (or this rank's slice of it under context parallelism): ``input_ids [1, T]``."""

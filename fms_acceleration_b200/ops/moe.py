@@ -4,15 +4,31 @@
 Same math as the reference's ScatterMoE path (fms_acceleration_moe/utils/scattermoe.py:411-491,
 scattermoe_utils/khd/kernels/ops/__init__.py:59-278, scattermoe_utils/expert_parallel.py:97-232):
 ``out[t] = sum_k gate[t,k] * W2[e] (act(W1[e] x_t) * W3[e] x_t)`` with ``e = topk(t, k)``, expert weights stored
-``[E, in, out]``.  With expert parallelism every rank owns ``E / ep`` experts; rows travel to the owner by peer
-stores and results come back by peer loads, two device-side barriers per layer and direction, no host sync.
+``[E, in, out]``.  Gate and up projection run as one grouped GEMM over the two weight tensors side by side, and so
+do their weight gradients and the input gradient through both.
+
+Expert parallelism (every rank owns ``E / ep`` experts), no host synchronisation anywhere:
+
+* **One row per (token, destination rank).**  A token whose experts live on ``r`` ranks crosses NVLink ``r`` times
+  instead of ``top_k`` times: the source stores the row once into each destination's staging block together with
+  the slots it must be replicated to and its routing weights; the owner replicates locally into its expert-sorted
+  buffer, and on the way back sums the (weighted) expert outputs of a staged row into one row that the source
+  pulls.  For 40 experts on 8 ranks with top-8 that is 5.6 instead of 8 rows per token and direction, on 2 ranks
+  2 instead of 8.
+* **Token chunks pipelined over two streams.**  The tokens of a call are cut into ``n_chunks`` slices; dispatch and
+  combine of one slice run on a communication stream while the grouped GEMMs of the neighbouring slice run on the
+  compute stream (two staging sets, reused every other chunk; the cross-rank barriers that order the reuse are on
+  the communication stream).
+* **Fixed layout from an agreed token budget.**  Staging blocks and the expert-sorted capacity are sized once from
+  the largest number of tokens a rank may bring to one call (agreed over the group at set-up), so ranks whose
+  padding-free batches differ in length still address the same layout and nothing is re-allocated per step.  Rows
+  beyond the capacity are dropped on every rank alike and counted (:func:`overflow_count`), never written.
 """
 from __future__ import annotations
 
 import ctypes
-from typing import Optional
-
 import os
+from typing import Optional
 
 import torch
 import torch.distributed as dist
@@ -22,9 +38,11 @@ from . import activation as ACT
 
 P, I, L, F, U = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_uint
 N.declare("fmsb_grouped_gemm", [P, L, P, L, I, I, P, L, I, P, L, F, F, I, I, I, I, I, I, P, L, L, L, P, P])
+N.declare("fmsb_grouped_gemm2", [P, L, P, L, I, I, P, I, P, L, P, L, I, P, L, I, P, L, I, F, F, I, I, I, I, I, I, P, L,
+                                 L, L, I, P, P])
 N.declare("fmsb_moe_router", [P, I, I, I, I, P, P, P])
 N.declare("fmsb_moe_router_bwd", [P, P, P, P, I, I, I, I, P, P])
-N.declare("fmsb_moe_plan", [P, L, I, I, I, I, P, P, P, U, P, P, P, P, P, P, P, P])
+N.declare("fmsb_moe_plan", [P, L, I, I, I, I, P, P, P, U, P, P, P, P, P, P, P, P, P])
 N.declare("fmsb_moe_dispatch", [P, L, P, P, P, L, I, I, I, P, L, I, I, P])
 N.declare("fmsb_moe_zero_pad", [P, L, I, P, P, I, I, P])
 N.declare("fmsb_moe_combine", [P, L, P, P, P, L, I, I, I, P, L, I, I, P])
@@ -32,6 +50,10 @@ N.declare("fmsb_moe_gate_grad", [P, L, P, P, P, L, L, I, I, I, P, I, I, P])
 N.declare("fmsb_moe_dispatch_meta", [P, L, P, P, P, L, I, I, I, P, L, P, I, I, P])
 N.declare("fmsb_moe_rowdot_scale", [P, L, P, L, P, P, P, I, I, I, I, P])
 N.declare("fmsb_moe_gather_scalar", [P, P, P, L, I, P, I, P])
+N.declare("fmsb_moe_stage_plan", [P, P, L, I, I, I, P, P, P, P, P, P])
+N.declare("fmsb_moe_dispatch_staged", [P, L, P, P, P, P, P, L, I, I, I, I, I, P, L, P, P, P, I, P])
+N.declare("fmsb_moe_replicate", [P, L, P, P, P, L, I, P, I, I, P, L, I, P])
+N.declare("fmsb_moe_prereduce", [P, L, P, P, L, I, P, I, I, P, L, I, P])
 
 
 # ------------------------------------------------------------------------------------------------ oracle
@@ -61,28 +83,43 @@ def moe_ref(x, router_w, w1, w2, w3, top_k, act="silu", renorm=True, idx=None):
 
 
 # ------------------------------------------------------------------------------------------------ kernels
-def grouped_gemm(a, b, seg_off, n_groups, *, mode, b_mn=True, out=None, out_dtype=None, c=None, beta=0.0, n=None, m=None):
-    """mode 1: out[rows, n] = a[rows, K] @ B_g per segment; b [E*in, out] viewed 2-D.
-    mode 2: out[g] = a[seg_g]^T @ b[seg_g]  -> out [n_groups, m, n]."""
+def _bn(n: int) -> int:
+    return 256 if n >= 192 else (128 if n > 64 else 64)
+
+
+def grouped_gemm(a, b, seg_off, n_groups, *, mode, b_mn=True, out=None, out_dtype=None, c=None, beta=0.0, n=None, m=None,
+                 b_alt=None, a2=None, b2=None, max_ctas=0):
+    """mode 1: out[rows, n] = a[rows, K] @ B_g per segment; b [E*in, out] viewed 2-D.  ``b_alt``: a second weight
+    tensor of the same shape whose product fills the right half of ``out`` (n = 2 * b.shape[1]).  ``a2``/``b2``: a
+    second operand pair accumulated into the same tile (``out = a @ B_g + a2 @ B2_g``).
+    mode 2: out[g] = a[seg_g]^T @ b[seg_g]  -> out [n_groups, m, n]; ``c`` (fp32, = out) with ``beta=1`` accumulates."""
     st = N.status_word(a.device)
     fmt = N.dtype_code(a.dtype)
     if mode == 1:
         rows, K = a.shape
         if out is None:
             out = torch.empty(rows, n, dtype=out_dtype or a.dtype, device=a.device)
-        bn = 256 if n >= 192 else (128 if n > 64 else 64)
-        rc = N.lib().fmsb_grouped_gemm(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), K, int(b_mn), out.data_ptr(),
-                                       out.stride(0), int(out.dtype == torch.float32), N.ptr(c),
-                                       c.stride(0) if c is not None else 0, 1.0, float(beta), 0, n, fmt, bn, 1, n_groups,
-                                       seg_off.data_ptr(), 0, rows, b.shape[0], st.data_ptr(), N.stream_ptr())
+        n_split = b.shape[1] if b_alt is not None else 0
+        bn = _bn(n_split if n_split else n)
+        if n_split and n_split % bn:
+            bn = 128 if n_split % 128 == 0 else 64
+        K2 = a2.shape[1] if a2 is not None else 0
+        rc = N.lib().fmsb_grouped_gemm2(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), K, int(b_mn), N.ptr(b_alt),
+                                        n_split, N.ptr(a2), a2.stride(0) if a2 is not None else 0, N.ptr(b2),
+                                        b2.stride(0) if b2 is not None else 0, K2, out.data_ptr(), out.stride(0),
+                                        int(out.dtype == torch.float32), N.ptr(c), c.stride(0) if c is not None else 0,
+                                        int(c is not None and c.dtype == torch.float32), 1.0, float(beta), 0, n, fmt, bn,
+                                        1, n_groups, seg_off.data_ptr(), 0, rows, b.shape[0], int(max_ctas),
+                                        st.data_ptr(), N.stream_ptr())
     else:
         if out is None:
             out = torch.empty(n_groups, m, n, dtype=out_dtype or torch.float32, device=a.device)
-        bn = 256 if n >= 192 else (128 if n > 64 else 64)
-        rc = N.lib().fmsb_grouped_gemm(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), 64, 1, out.data_ptr(),
-                                       out.stride(1), int(out.dtype == torch.float32), None, 0, 1.0, 0.0, m, n, fmt, bn, 2,
-                                       n_groups, seg_off.data_ptr(), out.stride(0), a.shape[0], b.shape[0], st.data_ptr(),
-                                       N.stream_ptr())
+        rc = N.lib().fmsb_grouped_gemm2(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), 64, 1, None, 0, None, 0,
+                                        None, 0, 0, out.data_ptr(), out.stride(1), int(out.dtype == torch.float32),
+                                        N.ptr(c), c.stride(1) if c is not None else 0,
+                                        int(c is not None and c.dtype == torch.float32), 1.0, float(beta), m, n, fmt,
+                                        _bn(n), 2, n_groups, seg_off.data_ptr(), out.stride(0), a.shape[0], b.shape[0],
+                                        int(max_ctas), st.data_ptr(), N.stream_ptr())
     N.check(rc, "fmsb_grouped_gemm")
     return out
 
@@ -124,13 +161,102 @@ def router_topk(logits, k, renorm=True):
     return _RouterTopK.apply(logits, k, renorm)
 
 
+# ------------------------------------------------------------------------------------------------ state
+_overflow: dict = {}
+_needed: dict = {}
+
+
+def _dev_index(device) -> int:
+    dev = torch.device(device) if device is not None else None
+    return dev.index if dev is not None and dev.index is not None else torch.cuda.current_device()
+
+
+def _counter(store: dict, device) -> torch.Tensor:
+    key = _dev_index(device)
+    t = store.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=f"cuda:{key}")
+        store[key] = t
+    return t
+
+
+def overflow_count(device=None, reset: bool = False) -> int:
+    """Host-synchronising read of the number of experts (summed over calls) whose rows did not all fit into an
+    owner's receive capacity, i.e. whose excess rows were dropped.  Informational: training continues."""
+    t = _counter(_overflow, device)
+    v = int(t.item())
+    if reset:
+        t.zero_()
+    return v
+
+
+def _round_up(n: int, a: int) -> int:
+    return (n + a - 1) // a * a
+
+
+class _EPShared:
+    """What all mixture-of-experts layers of one expert-parallel group share: the communicator, the histogram
+    tables of the plan, and two sets of staging buffers.  Allocated ONCE (one symmetric allocation, one
+    rendezvous), sized from the agreed token budget."""
+
+    def __init__(self, group, device, dtype, H: int, k: int, E: int, token_budget: int, n_chunks: int,
+                 capacity_factor: float):
+        from ..parallel.symm import Communicator, SymmBuffer
+
+        self.group, self.device, self.dtype = group, device, dtype
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.H, self.k, self.E = H, k, E
+        self.E_local = E // self.world
+        # the budget must be the same everywhere: take the largest one any rank asks for
+        t = torch.tensor([int(token_budget), int(n_chunks)], dtype=torch.int64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+        self.token_budget, self.C = int(t[0]), max(1, int(t[1]))
+        self.Tbc = _round_up(-(-self.token_budget // self.C), 8)  # staging rows per source rank and chunk
+        self.cap = _round_up(int(min(capacity_factor, float(self.world)) * self.Tbc * k), 128) + self.E_local * 128
+        self.comm = Communicator(group, device)
+        self.stream = torch.cuda.Stream(device, priority=-1)
+        esize = torch.empty((), dtype=dtype).element_size()
+        rows = self.world * self.Tbc
+        lay, off = {}, 0
+        for s in range(2):
+            for name, nbytes in (("x", rows * H * esize), ("y", rows * H * esize), ("slot", rows * k * 4),
+                                 ("gate", rows * k * 4), ("cnt", 64 * 4), ("rdots", self.cap * 4)):
+                lay[(name, s)] = off
+                off = _round_up(off + nbytes, 256)
+        lay["tables"] = off
+        off = _round_up(off + 2 * self.world * E * 4, 256)
+        self.buf = SymmBuffer(off, group, device, zero=True)
+        self.off = lay
+        self.ptrs = {key: self.buf.ptr_array(o) for key, o in lay.items()}
+        self.stage_base = torch.tensor([self.rank * self.Tbc] * self.world + [(self.rank + 1) * self.Tbc] * self.world,
+                                       dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+
+    def local(self, name: str, s: int, dtype, rows: int, cols: int) -> torch.Tensor:
+        return self.buf.view(self.off[(name, s)], rows * cols, dtype).view(rows, cols)
+
+    def local_ptr(self, name: str, s: int) -> int:
+        return self.buf.local.data_ptr() + self.off[(name, s)]
+
+    def table_ptrs(self, slot: int):
+        return self.buf.ptr_array(self.off["tables"] + slot * self.world * self.E * 4)
+
+
 class MoEContext:
-    """Per-layer buffers and the communication state of one mixture-of-experts layer."""
+    """Geometry and communication state of one mixture-of-experts layer.
+
+    ``token_budget``: the largest number of tokens this rank may hand to one call (expert parallelism only; default
+    ``FMSB_MOE_TOKEN_BUDGET`` or, failing that, the maximum over the ranks of the first call's token count).
+    ``n_chunks``: slices a call is pipelined in (``FMSB_MOE_CHUNKS``, default 2).  ``capacity_factor`` (default
+    ``FMSB_MOE_CAPACITY_FACTOR`` or 2.0): receive capacity of an owner in units of the balanced load."""
 
     _shared: dict = {}
 
     def __init__(self, hidden: int, inter: int, num_experts: int, top_k: int, group=None,
-                 capacity_factor: Optional[float] = None, layer_tag: str = "moe"):
+                 capacity_factor: Optional[float] = None, layer_tag: str = "moe", token_budget: Optional[int] = None,
+                 n_chunks: Optional[int] = None):
         if capacity_factor is None:
             capacity_factor = float(os.environ.get("FMSB_MOE_CAPACITY_FACTOR", "2.0"))
         self.H, self.I, self.E, self.k = hidden, inter, num_experts, top_k
@@ -139,71 +265,38 @@ class MoEContext:
         self.rank = dist.get_rank(group) if self.world > 1 else 0
         self.E_local = num_experts // self.world
         self.capacity_factor = capacity_factor
+        self.token_budget = token_budget or int(os.environ.get("FMSB_MOE_TOKEN_BUDGET", "0")) or None
+        self.n_chunks = n_chunks or int(os.environ.get("FMSB_MOE_CHUNKS", "2"))
+        self.gemm_ctas = int(os.environ.get("FMSB_MOE_GEMM_CTAS", "0"))  # 0: every SM
         self.tag = layer_tag
-        self.cap = 0
-        self.comm = None
-        self._bufs = {}
+        self.cap = 0  # world == 1: rows of the expert-sorted buffer (tests may lower it to provoke an overflow)
+        self.shared: Optional[_EPShared] = None
 
-    # symmetric (world > 1) or plain buffers
-    def _alloc(self, key, rows, cols, dtype, device, shared=False):
-        store = MoEContext._shared if shared else self._bufs
-        k = (key, rows, cols, dtype, self.world, id(self.group) if shared else 0)
-        ent = store.get(k)
-        if ent is None:
-            nbytes = rows * cols * torch.empty((), dtype=dtype).element_size()
-            if self.world > 1:
-                from ..parallel.symm import SymmBuffer
-
-                sb = SymmBuffer(nbytes, self.group, device, zero=True)
-                t = sb.view(0, rows * cols, dtype).view(rows, cols)
-                ent = (t, sb.ptr_array(), sb)
-            else:
-                t = torch.zeros(rows, cols, dtype=dtype, device=device)
-                ent = (t, (ctypes.c_void_p * 1)(t.data_ptr()), None)
-            store[k] = ent
-        return ent
-
-    def ensure(self, T: int, dtype, device):
-        if self.world == 1:
-            rows = T * self.k  # exact upper bound: the local buffer can never overflow
-        else:
-            # T*k rows arrive per rank when routing is balanced, world*T*k when every token of every rank picks this
-            # rank's experts; rows beyond the capacity are dropped and reported (status 7), never written
-            rows = int(min(self.capacity_factor, float(self.world)) * T * self.k)
-        cap = (rows + self.E_local * 128 + 127) // 128 * 128
-        if cap != self.cap:
-            self.cap = cap
-        if self.world > 1 and self.comm is None:
-            key = ("comm", id(self.group))
-            if key not in MoEContext._shared:
-                from ..parallel.symm import Communicator, SymmBuffer
-
-                comm = Communicator(self.group, device)
-                tables = SymmBuffer(2 * self.world * self.E * 4, self.group, device)
-                MoEContext._shared[key] = (comm, tables)
-            self.comm, self.tables = MoEContext._shared[key]
-        return cap
-
-    def barrier(self, chan):
-        if self.world > 1:
-            self.comm.barrier(chan)
-
-    # rows an owner would have needed so far for nothing to be dropped (maximum over layers, steps and owners)
-    _needed: dict = {}
+    def ensure_shared(self, T: int, dtype, device) -> _EPShared:
+        if self.shared is None:
+            key = (id(self.group), self.H, self.k, self.E, dtype)
+            sh = MoEContext._shared.get(key)
+            if sh is None:
+                sh = _EPShared(self.group, device, dtype, self.H, self.k, self.E, self.token_budget or T, self.n_chunks,
+                               self.capacity_factor)
+                MoEContext._shared[key] = sh
+            self.shared = sh
+        if T > self.shared.token_budget:
+            raise RuntimeError(
+                f"{T} tokens in one mixture-of-experts call exceed the token budget {self.shared.token_budget} that the "
+                "expert-parallel buffers were sized for; set FMSB_MOE_TOKEN_BUDGET (or token_budget=) to the largest "
+                "per-rank token count of a step (per-device batch size x maximum sequence length)")
+        return self.shared
 
     @classmethod
     def needed_counter(cls, device) -> torch.Tensor:
-        dev = torch.device(device)
-        key = dev.index if dev.index is not None else torch.cuda.current_device()
-        t = cls._needed.get(key)
-        if t is None:
-            t = torch.zeros(1, dtype=torch.int32, device=f"cuda:{key}")
-            cls._needed[key] = t
-        return t
+        return _counter(_needed, device)
 
     @classmethod
     def max_rows_needed(cls, device=None) -> int:
-        """Host-synchronising read of the counter; compare with ``T * top_k`` to choose ``capacity_factor``."""
+        """Host-synchronising read of the rows the busiest owner would have needed so far for nothing to be dropped
+        (maximum over layers, steps, chunks and owners); compare with tokens-per-chunk x top_k to choose
+        ``capacity_factor``."""
         return int(cls.needed_counter(device if device is not None else torch.cuda.current_device()).item())
 
 
@@ -211,8 +304,10 @@ PLAN_CHAN = 8
 BAR_A, BAR_B, BAR_C, BAR_D = 10, 11, 12, 13
 
 
-def _plan(ctx: MoEContext, topk_idx, T, device):
+def _plan(ctx: MoEContext, topk_idx, T, device, cap=None):
+    """Expert histogram -> (exchange over the group) -> segment layout of my experts and the slot of every pair."""
     E, k = ctx.E, ctx.k
+    cap = ctx.cap if cap is None else cap
     counts = torch.zeros(E, dtype=torch.int32, device=device)
     seg_off = torch.empty(ctx.E_local + 1, dtype=torch.int32, device=device)
     seg_cnt = torch.empty(ctx.E_local, dtype=torch.int32, device=device)
@@ -221,15 +316,16 @@ def _plan(ctx: MoEContext, topk_idx, T, device):
     scratch = torch.empty(max(1, -(-T * k // 1024)) * E, dtype=torch.int32, device=device)  # per-chunk expert counts
     st = N.status_word(device)
     if ctx.world > 1:
-        epoch = ctx.comm.next_epoch(PLAN_CHAN)
-        slot = epoch & 1
-        tab = ctx.tables.ptr_array(slot * ctx.world * E * 4)
-        sig = ctx.comm.signals.ptr_array(PLAN_CHAN * ctx.world * 4)
+        sh = ctx.shared
+        epoch = sh.comm.next_epoch(PLAN_CHAN)
+        tab = sh.table_ptrs(epoch & 1)
+        sig = sh.comm.signals.ptr_array(PLAN_CHAN * ctx.world * 4)
     else:
         epoch, tab, sig = 0, None, None
-    rc = N.lib().fmsb_moe_plan(topk_idx.data_ptr(), T * k, E, ctx.rank, ctx.world, ctx.cap, counts.data_ptr(), tab, sig,
-                               epoch, seg_off.data_ptr(), seg_cnt.data_ptr(), send_base.data_ptr(), dest_row.data_ptr(),
-                               MoEContext.needed_counter(device).data_ptr(), scratch.data_ptr(), st.data_ptr(),
+    rc = N.lib().fmsb_moe_plan(N.ptr(topk_idx) if T else None, T * k, E, ctx.rank, ctx.world, cap, counts.data_ptr(),
+                               tab, sig, epoch, seg_off.data_ptr(), seg_cnt.data_ptr(), send_base.data_ptr(),
+                               dest_row.data_ptr() if T else None, MoEContext.needed_counter(device).data_ptr(),
+                               scratch.data_ptr(), _counter(_overflow, device).data_ptr(), st.data_ptr(),
                                N.stream_ptr())
     N.check(rc, "fmsb_moe_plan")
     return seg_off, seg_cnt, dest_row
@@ -249,87 +345,293 @@ def _zero_pad(ctx, buf, seg_off, seg_cnt):
     N.check(rc, "fmsb_moe_zero_pad")
 
 
-def _combine(ctx, buf_ptrs, ld, topk_idx, dest_row, w, T, H, dtype, device):
-    out = torch.empty(T, H, dtype=dtype, device=device)
-    rc = N.lib().fmsb_moe_combine(buf_ptrs, ld, topk_idx.data_ptr(), dest_row.data_ptr(), N.ptr(w), T, ctx.k, H,
-                                  ctx.E_local, out.data_ptr(), out.stride(0), ctx.world, N.dtype_code(dtype),
-                                  N.stream_ptr())
+def _combine(ctx, buf_ptrs, ld, topk_idx, dest_row, w, T, H, dtype, device, out=None, k=None, e_local=None, world=None):
+    if out is None:
+        out = torch.empty(T, H, dtype=dtype, device=device)
+    if T == 0:
+        return out
+    rc = N.lib().fmsb_moe_combine(buf_ptrs, ld, topk_idx.data_ptr(), dest_row.data_ptr(), N.ptr(w), T,
+                                  ctx.k if k is None else k, H, ctx.E_local if e_local is None else e_local,
+                                  out.data_ptr(), out.stride(0), ctx.world if world is None else world,
+                                  N.dtype_code(dtype), N.stream_ptr())
     N.check(rc, "fmsb_moe_combine")
     return out
 
 
+def _one_ptr(t):
+    return (ctypes.c_void_p * 1)(t.data_ptr())
+
+
+# ------------------------------------------------------------------------------------------------ expert math
+def _experts_fwd_local(mctx, Xs, seg_off, w1, w3, w2, act, Ys=None):
+    """gate|up (one grouped GEMM over the two weight tensors), activation, down projection."""
+    I_, El, H = mctx.I, mctx.E_local, mctx.H
+    gu = grouped_gemm(Xs, w1.view(El * H, I_), seg_off, El, mode=1, n=2 * I_, b_alt=w3.view(El * H, I_),
+                      max_ctas=mctx.gemm_ctas)
+    hs = ACT.glu_fwd(gu[:, :I_], gu[:, I_:], act)
+    Ys = grouped_gemm(hs, w2.view(El * I_, H), seg_off, El, mode=1, n=H, out=Ys, max_ctas=mctx.gemm_ctas)
+    return gu, Ys
+
+
+def _experts_bwd_local(mctx, Xs, gu, dYs, seg_off, w1, w3, w2, act, acc, need_dw=True):
+    """Gradients of the three expert weight tensors (accumulated into ``acc`` when it already holds a chunk) and the
+    input gradient in the expert-sorted layout.  ``gu`` is overwritten with the pre-activation gradients."""
+    I_, El, H = mctx.I, mctx.E_local, mctx.H
+    hs = ACT.glu_fwd(gu[:, :I_], gu[:, I_:], act)
+    first = "dw2" not in acc
+    if need_dw:
+        if first:
+            acc["dw2"] = grouped_gemm(hs, dYs, seg_off, El, mode=2, m=I_, n=H, max_ctas=mctx.gemm_ctas)
+        else:
+            grouped_gemm(hs, dYs, seg_off, El, mode=2, m=I_, n=H, out=acc["dw2"], c=acc["dw2"], beta=1.0,
+                         max_ctas=mctx.gemm_ctas)
+    dhs = grouped_gemm(dYs, w2.view(El * I_, H), seg_off, El, mode=1, b_mn=False, n=I_, max_ctas=mctx.gemm_ctas)
+    ACT.glu_bwd(dhs, gu[:, :I_], gu[:, I_:], act, de=gu[:, :I_], dg=gu[:, I_:])
+    if need_dw:
+        # [d gate | d up] side by side in gu: both weight gradients in one pass over Xs
+        if first:
+            acc["dw13"] = grouped_gemm(Xs, gu, seg_off, El, mode=2, m=H, n=2 * I_, max_ctas=mctx.gemm_ctas)
+        else:
+            grouped_gemm(Xs, gu, seg_off, El, mode=2, m=H, n=2 * I_, out=acc["dw13"], c=acc["dw13"], beta=1.0,
+                         max_ctas=mctx.gemm_ctas)
+    dXs = grouped_gemm(gu[:, :I_], w1.view(El * H, I_), seg_off, El, mode=1, b_mn=False, n=H, a2=gu[:, I_:],
+                       b2=w3.view(El * H, I_), max_ctas=mctx.gemm_ctas)
+    return dXs
+
+
+def _weight_grads(mctx, acc, w1, w3, w2, needs):
+    I_ = mctx.I
+    dw1 = acc["dw13"][:, :, :I_].to(w1.dtype) if needs[0] and "dw13" in acc else None
+    dw3 = acc["dw13"][:, :, I_:].to(w3.dtype) if needs[1] and "dw13" in acc else None
+    dw2 = acc["dw2"].to(w2.dtype) if needs[2] and "dw2" in acc else None
+    return dw1, dw3, dw2
+
+
 class _Experts(torch.autograd.Function):
-    """x [T,H], gates fp32 [T,k], idx int32 [T,k], w1/w3 [E_local,H,I], w2 [E_local,I,H] -> [T,H]."""
+    """One rank owns every expert.  x [T,H], gates fp32 [T,k], idx int32 [T,k], w1/w3 [E,H,I], w2 [E,I,H] -> [T,H]."""
 
     @staticmethod
     def forward(ctx, x, gates, idx, w1, w3, w2, mctx: MoEContext, act: str):
         T, H = x.shape
-        I_, El = mctx.I, mctx.E_local
         dev, dt = x.device, x.dtype
-        cap = mctx.ensure(T, dt, dev)
+        cap = mctx.cap = _round_up(T * mctx.k + mctx.E_local * 128, 128)  # exact upper bound: never overflows
         seg_off, seg_cnt, dest_row = _plan(mctx, idx, T, dev)
-        Xs, Xs_ptrs, _ = mctx._alloc("Xs", cap, H, dt, dev)
-        Ys, Ys_ptrs, _ = mctx._alloc("Ys", cap, H, dt, dev)
+        Xs = torch.empty(cap, H, dtype=dt, device=dev)
         _zero_pad(mctx, Xs, seg_off, seg_cnt)
-        _dispatch(mctx, x, idx, dest_row, None, Xs_ptrs, Xs.stride(0))
-        mctx.barrier(BAR_A)
-        gu = torch.empty(cap, 2 * I_, dtype=dt, device=dev)
-        grouped_gemm(Xs, w1.view(El * H, I_), seg_off, El, mode=1, n=I_, out=gu[:, :I_])
-        grouped_gemm(Xs, w3.view(El * H, I_), seg_off, El, mode=1, n=I_, out=gu[:, I_:])
-        hs = ACT.glu_fwd(gu[:, :I_], gu[:, I_:], act)
-        grouped_gemm(hs, w2.view(El * I_, H), seg_off, El, mode=1, n=H, out=Ys)
-        mctx.barrier(BAR_B)
-        out = _combine(mctx, Ys_ptrs, Ys.stride(0), idx, dest_row, gates, T, H, dt, dev)
+        _dispatch(mctx, x, idx, dest_row, None, _one_ptr(Xs), Xs.stride(0))
+        gu, Ys = _experts_fwd_local(mctx, Xs, seg_off, w1, w3, w2, act)
+        out = _combine(mctx, _one_ptr(Ys), Ys.stride(0), idx, dest_row, gates, T, H, dt, dev)
         ctx.mctx, ctx.act = mctx, act
-        ctx.save_for_backward(gates, idx, w1, w3, w2, seg_off, seg_cnt, dest_row, gu)
+        ctx.save_for_backward(gates, idx, w1, w3, w2, seg_off, seg_cnt, dest_row, gu, Xs, Ys)
         return out
 
     @staticmethod
     def backward(ctx, dout):
         mctx, act = ctx.mctx, ctx.act
-        gates, idx, w1, w3, w2, seg_off, seg_cnt, dest_row, gu = ctx.saved_tensors
+        gates, idx, w1, w3, w2, seg_off, seg_cnt, dest_row, gu, Xs, Ys = ctx.saved_tensors
         dout = dout.contiguous()
         T, H = dout.shape
-        I_, El, cap = mctx.I, mctx.E_local, gu.shape[0]
+        El, cap = mctx.E_local, gu.shape[0]
         dev, dt = dout.device, dout.dtype
-        Xs, Xs_ptrs, _ = mctx._alloc("Xs", cap, H, dt, dev)
-        Ys, Ys_ptrs, _ = mctx._alloc("Ys", cap, H, dt, dev)
-        dYs, dYs_ptrs, _ = mctx._alloc("dYs", cap, H, dt, dev, shared=True)
-        dXs, dXs_ptrs, _ = mctx._alloc("dXs", cap, H, dt, dev, shared=True)
-        # dout rows travel unscaled together with their routing weight; the OWNER forms <expert output, dout> per row
-        # (the routing-weight gradient) and applies the weight, so only 4 bytes per pair come back instead of a second
-        # pull of every expert-output row
-        rgate, rgate_ptrs, _ = mctx._alloc("rgate", cap, 1, torch.float32, dev, shared=True)
-        rdots, rdots_ptrs, _ = mctx._alloc("rdots", cap, 1, torch.float32, dev, shared=True)
+        dYs = torch.empty(cap, H, dtype=dt, device=dev)
+        rgate = torch.zeros(cap, dtype=torch.float32, device=dev)
+        rdots = torch.empty(cap, dtype=torch.float32, device=dev)
         _zero_pad(mctx, dYs, seg_off, seg_cnt)
-        gates_c = gates.contiguous()
+        # dout rows are placed unscaled together with their routing weight; <expert output, dout> per row is the
+        # routing-weight gradient, then the weight is applied in place
         rc = N.lib().fmsb_moe_dispatch_meta(dout.data_ptr(), dout.stride(0), idx.data_ptr(), dest_row.data_ptr(),
-                                            gates_c.data_ptr(), T * mctx.k, mctx.k, H, El, dYs_ptrs, dYs.stride(0),
-                                            rgate_ptrs, mctx.world, N.dtype_code(dt), N.stream_ptr())
+                                            gates.contiguous().data_ptr(), T * mctx.k, mctx.k, H, El, _one_ptr(dYs),
+                                            dYs.stride(0), _one_ptr(rgate), 1, N.dtype_code(dt), N.stream_ptr())
         N.check(rc, "fmsb_moe_dispatch_meta")
-        mctx.barrier(BAR_C)
         rc = N.lib().fmsb_moe_rowdot_scale(Ys.data_ptr(), Ys.stride(0), dYs.data_ptr(), dYs.stride(0), rgate.data_ptr(),
                                            rdots.data_ptr(), seg_off.data_ptr(), El, cap, H, N.dtype_code(dt),
                                            N.stream_ptr())
         N.check(rc, "fmsb_moe_rowdot_scale")
-        hs = ACT.glu_fwd(gu[:, :I_], gu[:, I_:], act)
-        dw2 = grouped_gemm(hs, dYs, seg_off, El, mode=2, m=I_, n=H)
-        dhs = grouped_gemm(dYs, w2.view(El * I_, H), seg_off, El, mode=1, b_mn=False, n=I_)
-        ACT.glu_bwd(dhs, gu[:, :I_], gu[:, I_:], act, de=gu[:, :I_], dg=gu[:, I_:])
-        dg1 = gu[:, :I_]
-        dg3 = gu[:, I_:]
-        dw1 = grouped_gemm(Xs, dg1, seg_off, El, mode=2, m=H, n=I_)
-        dw3 = grouped_gemm(Xs, dg3, seg_off, El, mode=2, m=H, n=I_)
-        grouped_gemm(dg1, w1.view(El * H, I_), seg_off, El, mode=1, b_mn=False, n=H, out=dXs)
-        grouped_gemm(dg3, w3.view(El * H, I_), seg_off, El, mode=1, b_mn=False, n=H, out=dXs, c=dXs, beta=1.0)
-        mctx.barrier(BAR_D)
-        dx = _combine(mctx, dXs_ptrs, dXs.stride(0), idx, dest_row, None, T, H, dt, dev)
+        acc: dict = {}
+        need_dw = any(ctx.needs_input_grad[3:6])
+        dXs = _experts_bwd_local(mctx, Xs, gu, dYs, seg_off, w1, w3, w2, act, acc, need_dw)
+        dx = _combine(mctx, _one_ptr(dXs), dXs.stride(0), idx, dest_row, None, T, H, dt, dev)
         dgate = torch.empty(T, mctx.k, dtype=torch.float32, device=dev)
-        rc = N.lib().fmsb_moe_gather_scalar(rdots_ptrs, idx.data_ptr(), dest_row.data_ptr(), T * mctx.k, El,
-                                            dgate.data_ptr(), mctx.world, N.stream_ptr())
+        rc = N.lib().fmsb_moe_gather_scalar(_one_ptr(rdots), idx.data_ptr(), dest_row.data_ptr(), T * mctx.k, El,
+                                            dgate.data_ptr(), 1, N.stream_ptr())
         N.check(rc, "fmsb_moe_gather_scalar")
-        return dx, dgate, None, dw1.to(w1.dtype), dw3.to(w3.dtype), dw2.to(w2.dtype), None, None
+        dw1, dw3, dw2 = _weight_grads(mctx, acc, w1, w3, w2, ctx.needs_input_grad[3:6])
+        return dx, dgate, None, dw1, dw3, dw2, None, None
+
+
+# ------------------------------------------------------------------------------------------------ expert parallel
+class _Chunk:
+    """Plan and buffers of one token slice of an expert-parallel call."""
+    __slots__ = ("t0", "t1", "s", "seg_off", "seg_cnt", "dest_row", "hit", "stage_row", "stage_cnt", "Xs", "gu", "Ys")
+
+
+def _stage_plan(sh: _EPShared, idx_c, dest_row, n, dev):
+    hit = torch.empty(max(n, 1), sh.world, dtype=torch.int32, device=dev)
+    stage_row = torch.empty(max(n, 1), sh.world, dtype=torch.int32, device=dev)
+    stage_cnt = torch.empty(sh.world, dtype=torch.int32, device=dev)
+    scratch = torch.empty(max(1, -(-n * sh.world // 1024)) * sh.world, dtype=torch.int32, device=dev)
+    rc = N.lib().fmsb_moe_stage_plan(N.ptr(idx_c) if n else None, N.ptr(dest_row) if n else None, n, sh.k, sh.E_local,
+                                     sh.world, sh.stage_base.data_ptr(), hit.data_ptr(), stage_row.data_ptr(),
+                                     stage_cnt.data_ptr(), scratch.data_ptr(), N.stream_ptr())
+    N.check(rc, "fmsb_moe_stage_plan")
+    return hit, stage_row, stage_cnt
+
+
+def _push(sh: _EPShared, ch: _Chunk, rows, idx, gates, chan):
+    """Communication stream: store the slice's rows once per destination rank, then the barrier after which every
+    rank's staging block is complete."""
+    n = ch.t1 - ch.t0
+    x = rows[ch.t0:ch.t1]
+    g = gates[ch.t0:ch.t1] if gates is not None else None
+    rc = N.lib().fmsb_moe_dispatch_staged(
+        x.data_ptr() if n else None, rows.stride(0), idx[ch.t0:ch.t1].data_ptr() if n else None,
+        ch.dest_row.data_ptr() if n else None, N.ptr(g) if n else None, ch.stage_row.data_ptr(), ch.stage_cnt.data_ptr(), n,
+        sh.k, sh.H, sh.E_local, sh.world, sh.rank, sh.ptrs[("x", ch.s)], sh.H, sh.ptrs[("slot", ch.s)],
+        sh.ptrs[("gate", ch.s)], sh.ptrs[("cnt", ch.s)], N.dtype_code(rows.dtype), N.stream_ptr())
+    N.check(rc, "fmsb_moe_dispatch_staged")
+    sh.comm.barrier(chan)
+
+
+def _replicate(sh: _EPShared, ch: _Chunk, buf, slot_out=None):
+    n_rows = sh.world * sh.Tbc
+    rc = N.lib().fmsb_moe_replicate(sh.local_ptr("x", ch.s), sh.H, sh.local_ptr("slot", ch.s),
+                                    sh.local_ptr("gate", ch.s) if slot_out is not None else None, N.ptr(slot_out), n_rows,
+                                    sh.Tbc, sh.local_ptr("cnt", ch.s), sh.k, sh.H, buf.data_ptr(), buf.stride(0),
+                                    N.dtype_code(buf.dtype), N.stream_ptr())
+    N.check(rc, "fmsb_moe_replicate")
+
+
+def _prereduce(sh: _EPShared, ch: _Chunk, buf, weighted: bool):
+    n_rows = sh.world * sh.Tbc
+    rc = N.lib().fmsb_moe_prereduce(buf.data_ptr(), buf.stride(0), sh.local_ptr("slot", ch.s),
+                                    sh.local_ptr("gate", ch.s) if weighted else None, n_rows, sh.Tbc,
+                                    sh.local_ptr("cnt", ch.s), sh.k, sh.H, sh.local_ptr("y", ch.s), sh.H,
+                                    N.dtype_code(buf.dtype), N.stream_ptr())
+    N.check(rc, "fmsb_moe_prereduce")
+
+
+def _pull(sh: _EPShared, mctx, ch: _Chunk, out, chan):
+    """Communication stream: barrier (every owner's reduced rows are written), then one row per (token, rank) is
+    read back and summed."""
+    sh.comm.barrier(chan)
+    n = ch.t1 - ch.t0
+    if n:
+        _combine(mctx, sh.ptrs[("y", ch.s)], sh.H, ch.hit, ch.stage_row, None, n, sh.H, out.dtype, out.device,
+                 out=out[ch.t0:ch.t1], k=sh.world, e_local=1, world=sh.world)
+
+
+def _pipeline(sh: _EPShared, chunks, push, compute, pull):
+    """push(c), pull(c) on the communication stream, compute(c) on the caller's stream; slice c+1 is pushed while
+    slice c computes, slice c is pulled while slice c+1 computes.  Staging set c % 2 is reused by slice c+2 only
+    after pull(c) (whose barrier every rank passes after its compute(c))."""
+    main = torch.cuda.current_stream(sh.device)
+    comm = sh.stream
+    C = len(chunks)
+    ready = [torch.cuda.Event() for _ in range(C)]
+    done = [torch.cuda.Event() for _ in range(C)]
+
+    def do_push(c):
+        with torch.cuda.stream(comm):
+            push(chunks[c])
+            ready[c].record(comm)
+
+    start = torch.cuda.Event()
+    start.record(main)
+    comm.wait_event(start)
+    do_push(0)
+    if C > 1:
+        do_push(1)
+    for c in range(C):
+        main.wait_event(ready[c])
+        compute(chunks[c])
+        done[c].record(main)
+        with torch.cuda.stream(comm):
+            comm.wait_event(done[c])
+            pull(chunks[c])
+        if c + 2 < C:
+            do_push(c + 2)
+    end = torch.cuda.Event()
+    end.record(comm)
+    main.wait_event(end)
+
+
+class _ExpertsEP(torch.autograd.Function):
+    """Expert-parallel form: this rank owns ``E / world`` experts (w1/w3 [E_local,H,I], w2 [E_local,I,H])."""
+
+    @staticmethod
+    def forward(ctx, x, gates, idx, w1, w3, w2, mctx: MoEContext, act: str):
+        T, H = x.shape
+        dev, dt = x.device, x.dtype
+        sh = mctx.ensure_shared(T, dt, dev)
+        gates = gates.contiguous()
+        Tc = max(1, -(-T // sh.C))
+        chunks = []
+        for c in range(sh.C):
+            ch = _Chunk()
+            ch.t0, ch.t1, ch.s = min(T, c * Tc), min(T, (c + 1) * Tc), c % 2
+            n = ch.t1 - ch.t0
+            ch.seg_off, ch.seg_cnt, ch.dest_row = _plan(mctx, idx[ch.t0:ch.t1], n, dev, cap=sh.cap)
+            ch.hit, ch.stage_row, ch.stage_cnt = _stage_plan(sh, idx[ch.t0:ch.t1], ch.dest_row, n, dev)
+            chunks.append(ch)
+        out = torch.empty(T, H, dtype=dt, device=dev)
+
+        def compute(ch):
+            ch.Xs = torch.empty(sh.cap, H, dtype=dt, device=dev)
+            _zero_pad(mctx, ch.Xs, ch.seg_off, ch.seg_cnt)
+            _replicate(sh, ch, ch.Xs)
+            ch.gu, ch.Ys = _experts_fwd_local(mctx, ch.Xs, ch.seg_off, w1, w3, w2, act)
+            _prereduce(sh, ch, ch.Ys, weighted=True)
+
+        _pipeline(sh, chunks, lambda ch: _push(sh, ch, x, idx, gates, BAR_A), compute,
+                  lambda ch: _pull(sh, mctx, ch, out, BAR_B))
+        ctx.mctx, ctx.act, ctx.chunks = mctx, act, chunks
+        ctx.save_for_backward(gates, idx, w1, w3, w2)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        mctx, act, chunks = ctx.mctx, ctx.act, ctx.chunks
+        gates, idx, w1, w3, w2 = ctx.saved_tensors
+        sh = mctx.shared
+        dout = dout.contiguous()
+        T, H = dout.shape
+        dev, dt = dout.device, dout.dtype
+        El = mctx.E_local
+        dx = torch.empty(T, H, dtype=dt, device=dev)
+        dgate = torch.zeros(T, mctx.k, dtype=torch.float32, device=dev)
+        acc: dict = {}
+        need_dw = any(ctx.needs_input_grad[3:6])
+
+        def compute(ch):
+            dYs = torch.empty(sh.cap, H, dtype=dt, device=dev)
+            rgate = torch.zeros(sh.cap, dtype=torch.float32, device=dev)
+            _zero_pad(mctx, dYs, ch.seg_off, ch.seg_cnt)
+            # unscaled dout rows and the routing weight of every received row; the owner forms <expert output, dout>
+            # per row (read back by the source, 4 bytes per pair) and applies the weight in place
+            _replicate(sh, ch, dYs, slot_out=rgate)
+            rc = N.lib().fmsb_moe_rowdot_scale(ch.Ys.data_ptr(), ch.Ys.stride(0), dYs.data_ptr(), dYs.stride(0),
+                                               rgate.data_ptr(), sh.local_ptr("rdots", ch.s), ch.seg_off.data_ptr(), El,
+                                               sh.cap, H, N.dtype_code(dt), N.stream_ptr())
+            N.check(rc, "fmsb_moe_rowdot_scale")
+            dXs = _experts_bwd_local(mctx, ch.Xs, ch.gu, dYs, ch.seg_off, w1, w3, w2, act, acc, need_dw)
+            _prereduce(sh, ch, dXs, weighted=False)
+            ch.Xs = ch.gu = ch.Ys = None
+
+        def pull(ch):
+            _pull(sh, mctx, ch, dx, BAR_D)
+            n = ch.t1 - ch.t0
+            if n:
+                rc = N.lib().fmsb_moe_gather_scalar(sh.ptrs[("rdots", ch.s)], idx[ch.t0:ch.t1].data_ptr(),
+                                                    ch.dest_row.data_ptr(), n * mctx.k, El,
+                                                    dgate[ch.t0:ch.t1].data_ptr(), sh.world, N.stream_ptr())
+                N.check(rc, "fmsb_moe_gather_scalar")
+
+        _pipeline(sh, chunks, lambda ch: _push(sh, ch, dout, idx, gates, BAR_C), compute, pull)
+        dw1, dw3, dw2 = _weight_grads(mctx, acc, w1, w3, w2, ctx.needs_input_grad[3:6])
+        return dx, dgate, None, dw1, dw3, dw2, None, None
 
 
 def experts_forward(x, gates, idx, w1, w3, w2, mctx: MoEContext, act="silu"):
+    if mctx.world > 1:
+        return _ExpertsEP.apply(x, gates, idx, w1, w3, w2, mctx, act)
     return _Experts.apply(x, gates, idx, w1, w3, w2, mctx, act)

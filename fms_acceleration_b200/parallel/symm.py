@@ -56,6 +56,10 @@ class SymmBuffer:
             return self._arr
         return _ptr_array([p + offset for p in self.ptrs])
 
+    def ptr_array_strided(self, offset: int, stride: int):
+        """ctypes array whose entry r is rank r's base address + ``offset`` + r * ``stride`` bytes."""
+        return _ptr_array([p + offset + r * stride for r, p in enumerate(self.ptrs)])
+
     def view(self, offset: int, numel: int, dtype: torch.dtype) -> torch.Tensor:
         nb = numel * torch.empty((), dtype=dtype).element_size()
         return self.local[offset: offset + nb].view(dtype)
@@ -97,6 +101,10 @@ class Communicator:
 
     def allreduce_(self, bucket: SymmBuffer, numel: int, dtype: torch.dtype, scale: Optional[float] = None,
                    chan: int = 2, ctas: Optional[int] = None) -> None:
+        self.allreduce_ptrs(bucket.ptr_array(), numel, dtype, scale, chan, ctas)
+
+    def allreduce_ptrs(self, ptrs, numel: int, dtype: torch.dtype, scale: Optional[float] = None,
+                       chan: int = 2, ctas: Optional[int] = None) -> None:
         """In-place sum (times ``scale``, default 1/world) of the first ``numel`` elements of a symmetric bucket.
         ``ctas`` defaults to 32 for adapter-sized buckets and to 128 for buckets of 32 MiB and more (a full
         fine-tune's gradients), which runs at the end of the backward when nothing else needs the SMs."""
@@ -106,7 +114,7 @@ class Communicator:
         st = N.status_word(self.device)
         scale = 1.0 / self.world if scale is None else scale
         self.epochs[chan + 1] = self.epochs[chan] + 1
-        rc = N.lib().fmsb_comm_allreduce(bucket.ptr_array(), self.signals.ptr_array(), numel, self.rank, self.world,
+        rc = N.lib().fmsb_comm_allreduce(ptrs, self.signals.ptr_array(), numel, self.rank, self.world,
                                          float(scale), N.dtype_code(dtype), chan, self.next_epoch(chan),
                                          self.grid_sync.data_ptr(), ctas, st.data_ptr(), N.stream_ptr())
         N.check(rc, "fmsb_comm_allreduce")
@@ -114,9 +122,14 @@ class Communicator:
     def reduce_scatter(self, bucket: SymmBuffer, n_own: int, dtype: torch.dtype, out: torch.Tensor,
                        scale: Optional[float] = None, chan: int = 4, ctas: int = 64) -> None:
         """out[n_own] <- scale * sum over ranks of their bucket slice owned by this rank (barriers included)."""
+        self.reduce_scatter_ptrs(bucket.ptr_array(), n_own, dtype, out, scale, chan, ctas)
+
+    def reduce_scatter_ptrs(self, ptrs, n_own: int, dtype: torch.dtype, out: torch.Tensor,
+                            scale: Optional[float] = None, chan: int = 4, ctas: int = 64) -> None:
+        """The same on a window of the peers' buffers: ``ptrs[r]`` is where rank r's world * n_own elements start."""
         scale = 1.0 / self.world if scale is None else scale
         self.barrier(chan)
-        rc = N.lib().fmsb_comm_reduce_scatter(bucket.ptr_array(), out.data_ptr(), n_own, self.rank, self.world,
+        rc = N.lib().fmsb_comm_reduce_scatter(ptrs, out.data_ptr(), n_own, self.rank, self.world,
                                               float(scale), N.dtype_code(dtype), int(out.dtype == torch.float32),
                                               ctas, N.stream_ptr())
         N.check(rc, "fmsb_comm_reduce_scatter")

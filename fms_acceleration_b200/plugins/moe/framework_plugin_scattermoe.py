@@ -39,10 +39,14 @@ class ScatterMoEAccelerationPlugin(AccelerationPlugin):
         (peft_config,) = modifiable_args if len(modifiable_args) == 1 else (None,)
         if self._ep_degree > 1 and peft_config is not None:
             raise NotImplementedError("LoRA on the experts is only supported with ep_degree 1")
+        budget = None
+        bs, sl = getattr(train_args, "per_device_train_batch_size", None), getattr(train_args, "max_seq_length", None)
+        if bs and sl:
+            budget = int(bs) * int(sl)
         self._swapped = prepare_scattermoe(
             model, checkpoint_name_or_path=getattr(model.config, "name_or_path", None), rank=rank, world_size=world,
             ep_degree=self._ep_degree, disable_distributed=self._disable_distributed,
-            mixed_precision=False, lora_config=peft_config)
+            mixed_precision=False, lora_config=peft_config, token_budget=budget)
         return model, modifiable_args
 
     def get_callbacks_and_ready_for_train(self, model: torch.nn.Module = None, accelerator=None):

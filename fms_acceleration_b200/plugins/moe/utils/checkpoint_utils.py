@@ -34,11 +34,88 @@ MODEL_INDEX = None  # index of the model within accelerate's model list, recorde
 
 
 # ------------------------------------------------------------------------------------------- save / load
+# Expert parallelism: every rank holds the experts [rank * E/ep, (rank + 1) * E/ep) as an ordinary tensor under the
+# SAME name.  Written as such, the checkpoint writer would treat them as replicas and keep one rank's copy.  They
+# are therefore presented to torch.distributed.checkpoint as DTensors sharded on dim 0 over the expert-parallel
+# group (what the reference's parameters are in the first place, scattermoe_prepare.py:64-99): every shard is
+# written with its offset, a reader without a process group sees the full [E, in, out] tensor, and a reader with
+# the same layout gets its own shard back.  AdamW moments of those parameters are wrapped the same way.
+_MESHES: dict = {}
+
+
+def _ep_mesh(group, device_type: str):
+    from torch.distributed.device_mesh import DeviceMesh
+
+    key = (id(group), device_type)
+    if key not in _MESHES:
+        _MESHES[key] = DeviceMesh.from_group(group, device_type)
+    return _MESHES[key]
+
+
+def _as_sharded(t: torch.Tensor, group):
+    """Local expert shard -> DTensor Shard(0) over the expert-parallel group (shares storage with ``t``)."""
+    from torch.distributed.tensor import DTensor, Shard
+
+    return DTensor.from_local(t.detach(), _ep_mesh(group, t.device.type), [Shard(0)], run_check=False)
+
+
+def _ep_param_names(model: torch.nn.Module) -> Dict[str, object]:
+    """name -> expert-parallel group of every parameter sharded over experts."""
+    out = {}
+    if not (torch.distributed.is_available() and torch.distributed.is_initialized()):
+        return out
+    for n, p in model.named_parameters():
+        g = getattr(p, "_fmsb_ep_group", None)
+        if getattr(p, "_fmsb_expert_parallel", False) and g is not None and torch.distributed.get_world_size(g) > 1:
+            out[n] = g
+    return out
+
+
 def _model_state(model: torch.nn.Module, lora_only: bool) -> Dict[str, torch.Tensor]:
     sd = model.state_dict()
     if lora_only:
         sd = {k: v for k, v in sd.items() if ("lora_A" in k or "lora_B" in k) and "router" not in k}
+    for n, g in _ep_param_names(model).items():
+        if n in sd:
+            sd[n] = _as_sharded(sd[n], g)
     return sd
+
+
+def _unwrap_state(sd: Dict) -> Dict:
+    from torch.distributed.tensor import DTensor
+
+    return {k: (v.to_local() if isinstance(v, DTensor) else v) for k, v in sd.items()}
+
+
+def _optimizer_state(optimizer, model: torch.nn.Module) -> Dict:
+    """``optimizer.state_dict()`` with the moments of expert-parallel parameters wrapped as sharded DTensors."""
+    osd = optimizer.state_dict()
+    ep = _ep_param_names(model)
+    if not ep or not hasattr(optimizer, "param_groups"):
+        return osd
+    by_id = {id(p): n for n, p in model.named_parameters()}
+    idx = 0
+    for g in optimizer.param_groups:
+        for p in g["params"]:
+            name = by_id.get(id(p))
+            st = osd["state"].get(idx)
+            if name in ep and st is not None:
+                st = dict(st)  # the optimizer hands out its live per-parameter dict: wrap in a copy
+                osd["state"][idx] = st
+                for k, v in list(st.items()):
+                    if torch.is_tensor(v) and v.dim() > 0 and v.shape == p.shape:
+                        st[k] = _as_sharded(v, ep[name])
+            idx += 1
+    return osd
+
+
+def _unwrap_optimizer_state(osd: Dict) -> Dict:
+    from torch.distributed.tensor import DTensor
+
+    for idx, st in list(osd.get("state", {}).items()):
+        if any(isinstance(v, DTensor) for v in st.values()):
+            osd["state"][idx] = {k: (v.to_local() if isinstance(v, DTensor) else v) for k, v in st.items()}
+    return osd
 
 
 def save_fsdp_model(fsdp_plugin, accelerator, model: torch.nn.Module, output_dir: str, model_index: int = 0, **kwargs):
@@ -63,7 +140,8 @@ def save_fsdp_optimizer(fsdp_plugin, accelerator, optimizer, model: torch.nn.Mod
     os.makedirs(opt_dir, exist_ok=True)
     no_dist = not (torch.distributed.is_available() and torch.distributed.is_initialized())
     dcp.save({KEY_MODEL: _model_state(model, lora_only)}, storage_writer=dcp.FileSystemWriter(model_dir), no_dist=no_dist)
-    dcp.save({KEY_OPTIMIZER: optimizer.state_dict()}, storage_writer=dcp.FileSystemWriter(opt_dir), no_dist=no_dist)
+    osd = optimizer.sharded_state_dict() if hasattr(optimizer, "sharded_state_dict") else _optimizer_state(optimizer, model)
+    dcp.save({KEY_OPTIMIZER: osd}, storage_writer=dcp.FileSystemWriter(opt_dir), no_dist=no_dist)
 
 
 def load_fsdp_model(fsdp_plugin, accelerator, model: torch.nn.Module, input_dir: str, model_index: int = 0, **kwargs):
@@ -103,12 +181,18 @@ def load_fsdp_optimizer(fsdp_plugin, accelerator, optimizer, model: torch.nn.Mod
     no_dist = not (torch.distributed.is_available() and torch.distributed.is_initialized())
     msd = {KEY_MODEL: _model_state(model, lora_only)}
     dcp.load(msd, storage_reader=dcp.FileSystemReader(os.path.join(input_dir, f"{FSDP_MODEL_NAME}_{midx}")), no_dist=no_dist)
-    model.load_state_dict(msd[KEY_MODEL], strict=not lora_only)
+    model.load_state_dict(_unwrap_state(msd[KEY_MODEL]), strict=not lora_only)
+    opt_dir = os.path.join(input_dir, f"{OPTIMIZER_NAME}_{optimizer_index}")
+    if hasattr(optimizer, "load_sharded_state_dict"):
+        # optimizer states sharded over the ranks: every rank reads its own slice of the flat state
+        osd = {KEY_OPTIMIZER: optimizer.sharded_state_dict()}
+        dcp.load(osd, storage_reader=dcp.FileSystemReader(opt_dir), no_dist=no_dist)
+        optimizer.load_sharded_state_dict(osd[KEY_OPTIMIZER])
+        return
     _materialize_optimizer_state(optimizer)
-    osd = {KEY_OPTIMIZER: optimizer.state_dict()}
-    dcp.load(osd, storage_reader=dcp.FileSystemReader(os.path.join(input_dir, f"{OPTIMIZER_NAME}_{optimizer_index}")),
-             no_dist=no_dist)
-    optimizer.load_state_dict(osd[KEY_OPTIMIZER])
+    osd = {KEY_OPTIMIZER: _optimizer_state(optimizer, model)}
+    dcp.load(osd, storage_reader=dcp.FileSystemReader(opt_dir), no_dist=no_dist)
+    optimizer.load_state_dict(_unwrap_optimizer_state(osd[KEY_OPTIMIZER]))
 
 
 def patch_huggingface_save_and_load_for_dtensors() -> bool:

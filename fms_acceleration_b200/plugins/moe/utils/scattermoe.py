@@ -8,6 +8,7 @@ holds the ``E / ep`` experts ``[rank * E/ep, (rank + 1) * E/ep)``.  Execution is
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -47,7 +48,7 @@ class ScatteredExperts(nn.Module):
 class ScatterMoE(nn.Module):
     def __init__(self, hidden_size: int, hidden_act: str, intermediate_size: int, num_experts: int,
                  has_bias: bool = False, mlp_arch: Optional[str] = None, top_k: int = 2, dtype=torch.bfloat16,
-                 device=None, ep_device_mesh=None, ep_group=None, lora_config=None):
+                 device=None, ep_device_mesh=None, ep_group=None, lora_config=None, token_budget: Optional[int] = None):
         super().__init__()
         assert not has_bias, "ScatterMoE does not support bias"
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
@@ -65,12 +66,18 @@ class ScatterMoE(nn.Module):
         self.w1 = ScatteredExperts(hidden_size, intermediate_size, El, top_k, dtype=dtype, device=device, lora_config=lora_config)
         self.w2 = ScatteredExperts(intermediate_size, hidden_size, El, 1, dtype=dtype, device=device, lora_config=lora_config)
         self.w3 = ScatteredExperts(hidden_size, intermediate_size, El, top_k, dtype=dtype, device=device, lora_config=lora_config)
+        # largest number of tokens this rank hands to one forward (sizes the expert-parallel staging once)
+        self.token_budget = token_budget
         self._ctx: Optional[MOE.MoEContext] = None
+        # "fused": this package's kernels (peer-memory dispatch / combine around grouped tcgen05 GEMMs).
+        # "library": torch ops and, under expert parallelism, all_to_all_single of the process group's backend
+        # (NCCL on GPUs, gloo on CPUs): the like-for-like baseline of the fused path and the CPU execution path.
+        self.backend = os.environ.get("FMSB_MOE_BACKEND", "fused")
 
     def _context(self) -> MOE.MoEContext:
         if self._ctx is None:
             self._ctx = MOE.MoEContext(self.hidden_size, self.intermediate_size, self.num_experts, self.top_k,
-                                       group=self.ep_group)
+                                       group=self.ep_group, token_budget=self.token_budget)
         return self._ctx
 
     def _compute_routing_weights(self, x2: torch.Tensor):
@@ -89,13 +96,34 @@ class ScatterMoE(nn.Module):
         if x2.stride(1) != 1 or x2.stride(0) % 8:
             x2 = x2.contiguous()
         logits, w, idx = self._compute_routing_weights(x2)
-        if x2.is_cuda and x2.dtype in (torch.bfloat16, torch.float16):
+        if x2.is_cuda and x2.dtype in (torch.bfloat16, torch.float16) and self.backend == "fused":
             out = MOE.experts_forward(x2, w, idx, self.w1.effective_weight(), self.w3.effective_weight(),
                                       self.w2.effective_weight(), self._context(), self.activation)
+        elif self.expert_parallel:
+            out = self._forward_library_ep(x2, w, idx)
         else:
-            assert not self.expert_parallel, "the CPU oracle path has no expert parallelism"
             out = self._forward_reference(x2, w, idx)
         return (out.view(shape), logits) if getattr(self, "return_router_logits", True) else out.view(shape)
+
+    def _forward_library_ep(self, x2, w, idx):
+        """Expert parallelism with library collectives (the exchange of the reference,
+        fms_acceleration_moe/utils/scattermoe_utils/expert_parallel.py:97-232): rows sorted by expert, counts and
+        rows exchanged with all-to-all (one host synchronisation for the split sizes), local experts as dense
+        matmuls per expert, rows sent back and summed with the routing weights."""
+        from .scattermoe_utils import all_to_all_gather_inputs, scatter_with_routing_weights
+
+        El = self.num_experts_per_device
+        rows, local_e, state = all_to_all_gather_inputs(x2, idx, self.ep_group, self.top_k, El)
+        w1, w2, w3 = (m.effective_weight() for m in (self.w1, self.w2, self.w3))
+        act = {"silu": F.silu, "gelu": F.gelu}.get(self.activation, F.silu)
+        counts = torch.bincount(local_e, minlength=El).tolist()  # rows arrive ordered by local expert
+        outs, start = [], 0
+        for e in range(El):
+            xe = rows[start:start + counts[e]]
+            start += counts[e]
+            outs.append((act(xe @ w1[e]) * (xe @ w3[e])) @ w2[e])
+        y = torch.cat(outs) if outs else rows.new_zeros(0, x2.shape[1])
+        return scatter_with_routing_weights(y, w, state).to(x2.dtype)
 
     def _forward_reference(self, x2, w, idx):
         out = torch.zeros_like(x2, dtype=torch.float32)

@@ -65,7 +65,9 @@ def build_ep_groups(world_size: int, ep_degree: int, rank: int):
 def prepare_scattermoe(model: nn.Module, checkpoint_name_or_path: Optional[str] = None, rank: Optional[int] = None,
                        world_size: Optional[int] = None, ep_degree: int = 1, disable_distributed: bool = False,
                        key_rep: str = KEY_REPLICATE, key_ep: str = KEY_EXPERT_PARALLEL, device_type: str = "cuda",
-                       mixed_precision: bool = False, lora_config=None):
+                       mixed_precision: bool = False, lora_config=None, token_budget: Optional[int] = None):
+    """``token_budget``: upper bound of the tokens one rank brings to one forward (per-device batch size x maximum
+    sequence length); the expert-parallel buffers are sized from it once.  ``None``: taken from the first batch."""
     world_size = world_size if world_size is not None else (dist.get_world_size() if dist.is_initialized() else 1)
     rank = rank if rank is not None else (dist.get_rank() if dist.is_initialized() else 0)
     if disable_distributed and ep_degree > 1:
@@ -112,7 +114,7 @@ def prepare_scattermoe(model: nn.Module, checkpoint_name_or_path: Optional[str] 
 
         moe = ScatterMoE(hidden_size=config.hidden_size, hidden_act=getattr(config, "hidden_act", "silu"),
                          intermediate_size=inter, num_experts=num_experts, top_k=top_k, dtype=dtype, device=device,
-                         ep_group=ep_group, lora_config=lora_config)
+                         ep_group=ep_group, lora_config=lora_config, token_budget=token_budget)
         with torch.no_grad():
             moe.router.weight.copy_(sd[KEY_SCATTERMOE_ROUTER].to(device))
             for w in ("w1", "w2", "w3"):
@@ -123,6 +125,7 @@ def prepare_scattermoe(model: nn.Module, checkpoint_name_or_path: Optional[str] 
                 for p in getattr(moe, w).parameters():
                     p._fmsb_expert_parallel = True
                     p._fmsb_replicate_group = rep_group
+                    p._fmsb_ep_group = ep_group
         moe._fmsb_replicate_group = rep_group
         moe.return_router_logits = _returns_router_logits(module)
         setattr(parent, leaf, moe)

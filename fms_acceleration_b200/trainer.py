@@ -86,9 +86,14 @@ class Trainer:
         self.callbacks = callbacks or []
         params = [p for p in model.parameters() if p.requires_grad]
         if optimizer is None and engine is not None and getattr(engine, "shard_optimizer", False) \
-                and hasattr(engine, "flat_params") and not engine.ep_params:
-            # optimizer states sharded over the ranks (the engine owns the flat parameter and gradient buffers)
+                and hasattr(engine, "flat_params"):
+            # optimizer states of the replicated parameters sharded over the ranks (the engine owns the flat parameter
+            # and gradient buffers); expert-parallel parameters, already disjoint over the ranks, get a plain AdamW
             optimizer = engine.build_optimizer(args.learning_rate, args.weight_decay)
+            if engine.ep_params:
+                optimizer.ep_optimizer = torch.optim.AdamW(engine.ep_params, lr=args.learning_rate,
+                                                           weight_decay=args.weight_decay,
+                                                           fused=engine.ep_params[0].is_cuda)
         if optimizer is None:
             fused = bool(params) and params[0].is_cuda
             optimizer = torch.optim.AdamW(params, lr=args.learning_rate, weight_decay=args.weight_decay, fused=fused)
@@ -96,6 +101,12 @@ class Trainer:
         self.params = params
         self.global_step = 0
         self.log_history: List[dict] = []
+        self._micro = 0          # micro-batches accumulated since the last optimizer step
+        self._status = None      # asynchronous view of the device status word (GPU runs only)
+        if getattr(args, "gradient_checkpointing", False):
+            base = model.get_base_model() if hasattr(model, "get_base_model") else model
+            if hasattr(base, "gradient_checkpointing_enable"):
+                base.gradient_checkpointing_enable(getattr(args, "gradient_checkpointing_kwargs", None))
 
     def device(self):
         for p in self.model.parameters():
@@ -104,9 +115,22 @@ class Trainer:
             return b.device
         return torch.device("cpu")
 
+    def _has_expert_parallel(self) -> bool:
+        return any(getattr(p, "_fmsb_expert_parallel", False) for p in self.params)
+
     def train_step(self, batch: Dict[str, torch.Tensor]) -> torch.Tensor:
-        """One optimizer step on one (host or device) batch; returns the detached loss (device tensor)."""
+        """Forward + backward of one (host or device) batch; every ``gradient_accumulation_steps``-th call also
+        reduces the gradients across ranks, clips, and steps the optimizer.  Returns the detached loss (device
+        tensor) of this batch."""
         dev = self.device()
+        if dev.type == "cuda":
+            if self._status is None:
+                from . import _native as NV
+
+                self._status = NV.StatusMonitor(dev)
+            # a kernel of an EARLIER step whose bounded wait ran out left its code in the status word; raise it here
+            # (no host synchronisation: the snapshot is only looked at once its copy has completed)
+            self._status.raise_if_set()
         if batch["input_ids"].device != dev:
             batch = to_device(batch, dev)
         self.model.train()
@@ -116,23 +140,44 @@ class Trainer:
         if "cu_seqlens" in batch and getattr(self.args, "padding_free", False):
             kwargs["cu_seqlens"] = batch["cu_seqlens"]
             kwargs.pop("position_ids", None)
+        accum = max(1, int(getattr(self.args, "gradient_accumulation_steps", 1) or 1))
+        last = (self._micro + 1) % accum == 0
+        if self.engine is not None:
+            self.engine.begin_micro_step(last)
         out = self.model(**kwargs)
         loss = out.loss
-        loss.backward()
+        (loss / accum if accum > 1 else loss).backward()
+        if self.engine is not None:
+            self.engine.end_micro_step()
+        self._micro += 1
+        if not last:
+            return loss.detach()
+        self._micro = 0
         sharded = self.engine is not None and self.optimizer is getattr(self.engine, "sharded_optimizer", None) \
             and self.optimizer is not None
-        if self.engine is not None and not sharded:
+        if self.engine is not None:
             self.engine.reduce_gradients()
         if sharded:
             self.optimizer.max_grad_norm = self.args.max_grad_norm or 0.0  # clipped on the reduced slices
         elif self.args.max_grad_norm and self.args.max_grad_norm > 0:
-            torch.nn.utils.clip_grad_norm_(self.params, self.args.max_grad_norm)
+            if self._has_expert_parallel():
+                # expert shards differ per rank: their squared norms are summed over the expert-parallel group, so
+                # that every rank scales by the same factor
+                from .plugins.moe.utils.checkpoint_utils import clip_grad_norm_
+
+                clip_grad_norm_(self.params, self.args.max_grad_norm)
+            else:
+                torch.nn.utils.clip_grad_norm_(self.params, self.args.max_grad_norm)
         self.optimizer.step()
         if self.engine is not None:
             self.engine.zero_grad()
+            if sharded and self.optimizer.ep_optimizer is not None:
+                self.optimizer.ep_optimizer.zero_grad(set_to_none=True)
         else:
             self.optimizer.zero_grad(set_to_none=True)
         self.global_step += 1
+        if self._status is not None:
+            self._status.poll()
         return loss.detach()
 
     def train(self, batches, max_steps: Optional[int] = None):
@@ -168,13 +213,9 @@ class Trainer:
         os.makedirs(ckpt, exist_ok=True)
         lora = self._is_lora()
         CU.save_fsdp_model(None, None, self.model, ckpt, 0)
-        if self.engine is not None and self.optimizer is getattr(self.engine, "sharded_optimizer", None):
-            # every rank owns a different slice of the optimizer state: one file per rank; the (replicated) model as usual
-            inner = torch.optim.SGD([torch.nn.Parameter(torch.zeros(1, device=self.device()))], lr=0.0)
-            CU.save_fsdp_optimizer(None, None, inner, self.model, ckpt, 0, lora_only=lora)
-            torch.save(self.optimizer.state_dict(), os.path.join(ckpt, f"optimizer_shard_{rank}.pt"))
-        else:
-            CU.save_fsdp_optimizer(None, None, self.optimizer, self.model, ckpt, 0, lora_only=lora)
+        # a rank-sharded optimizer hands its slices over as shards of group-wide tensors, expert-parallel parameters
+        # and their moments likewise: one checkpoint directory holds the whole state whatever the layout
+        CU.save_fsdp_optimizer(None, None, self.optimizer, self.model, ckpt, 0, lora_only=lora)
         torch.save({"cpu": torch.get_rng_state(),
                     "cuda": torch.cuda.get_rng_state() if torch.cuda.is_available() else None},
                    os.path.join(ckpt, f"rng_state_{rank}.pth"))

@@ -1,0 +1,33 @@
+"""Host-side logic of the multi-rank engine on gloo ranks: gradient segments reduced from autograd hooks, gradient
+accumulation, the rank-sharded optimizer and its resume, and the expert-parallel checkpoint (every rank's experts
+written, converted and resumed)."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(which, world, tmp_path, port):
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", FMSB_MOE_BACKEND="library")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "dist_worker_engine_cpu.py"), which, str(tmp_path)]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-5000:]
+    return out.stdout
+
+
+def test_gradient_segments_are_reduced_from_the_hooks(tmp_path):
+    assert _run("reduce", 2, tmp_path, 29701).count("CPU_OK overlapped_reduce") == 2
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_sharded_optimizer_matches_replicated_and_resumes(tmp_path, world):
+    assert _run("zero1", world, tmp_path, 29702 + world).count("CPU_OK zero1_resume") == world
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_checkpoint_holds_every_rank(tmp_path, world):
+    assert _run("ep_ckpt", world, tmp_path, 29712 + world).count("CPU_OK ep_checkpoint") == world

@@ -5,7 +5,7 @@ memory in an arena of its own, a server plugin with a fixed budget, a path that 
 synchronisation of cudaMalloc/cudaFree).  For them ``fmsb_rmsnorm_bwd_noalloc`` keeps the partial sums of the
 weight gradient in a scratch array built into the library.  The test calls it twice in a row with different
 inputs (the scratch keeps the first call's contents) and compares with the regular entry point, whose scratch is
-allocated by the caller.
+allocated by the caller, and with the fp32 PyTorch formula of the same operation.
 """
 import ctypes
 
@@ -42,6 +42,17 @@ def _reference(dy, x, w, inv, dres, gemma):
     return dx, dw
 
 
+def _oracle(dy, x, w, inv, dres, gemma):
+    """fp32 PyTorch statement of RMSNorm backward (inputs rounded to the storage dtype, arithmetic in fp32)."""
+    xf, dyf, wf = x.float(), dy.float(), w.float() + (1.0 if gemma else 0.0)
+    xhat = xf * inv[:, None]
+    g = dyf * wf
+    dx = inv[:, None] * (g - xhat * (g * xhat).mean(-1, keepdim=True))
+    if dres is not None:
+        dx = dx + dres.float()
+    return dx, (dyf * xhat).sum(0)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_noalloc_entry_matches_regular_entry_twice(dtype):
     fn, err = _entry()
@@ -72,6 +83,11 @@ def test_noalloc_entry_matches_regular_entry_twice(dtype):
         assert torch.allclose(dx.float(), rdx.float(), rtol=2e-2, atol=2e-2)
         rel = ((dw - rdw).norm() / rdw.norm()).item()
         assert rel < 1e-4, rel
+        odx, odw = _oracle(dy, x, w, inv, dres, gemma)
+        # dx is rounded once to the 16-bit storage type: half a unit in the last place of the largest element
+        ulp = 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11
+        assert ((dx.float() - odx).abs() <= ulp * odx.abs() + 1e-3).all()
+        assert ((dw - odw).norm() / odw.norm()).item() < 1e-4
 
 
 def test_noalloc_entry_rejects_oversized_rows():
@@ -85,3 +101,23 @@ def test_noalloc_entry_rejects_oversized_rows():
             torch.cuda.current_stream().cuda_stream)
     assert rc == -3
     assert b"exceeds the built-in scratch" in err()
+
+
+def test_noalloc_entry_rejects_misaligned_pointers():
+    fn, err = _entry()
+    dev = torch.device("cuda")
+    rows, H = 4, 256
+    buf = torch.zeros(rows * H + 8, device=dev, dtype=torch.bfloat16)
+    good = buf[:rows * H].view(rows, H)
+    off = buf[1:rows * H + 1]  # 2 bytes past a 16-byte boundary
+    inv = torch.ones(rows, device=dev)
+    dw = torch.zeros(H, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+    assert off.data_ptr() % 16 != 0 and good.data_ptr() % 16 == 0
+    for args in [(off, good, good, good), (good, off, good, good), (good, good, off, good), (good, good, good, off)]:
+        dy_, x_, w_, dx_ = args
+        rc = fn(dy_.data_ptr(), x_.data_ptr(), w_.data_ptr(), inv.data_ptr(), None, dx_.data_ptr(), dw.data_ptr(), rows, H,
+                0, 1, st)
+        assert rc == -2
+        assert b"16-byte aligned" in err()
+    torch.cuda.synchronize()  # nothing was launched; the context is intact
