@@ -28,8 +28,8 @@ _SIGNATURES = {
     "fmsb_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, I, I, P],
     "fmsb_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, I, I, I, P],
     "fmsb_rope": [P, P, P, P, I, I, I, L, F, I, P],
-    "fmsb_glu_fwd": [P, P, P, I, I, L, L, L, I, I, P],
-    "fmsb_glu_bwd": [P, P, P, P, P, P, I, I, L, L, L, L, L, L, I, I, P],
+    "fmsb_glu_fwd": [P, P, P, I, I, L, L, L, I, I, P, P],
+    "fmsb_glu_bwd": [P, P, P, P, P, P, I, I, L, L, L, L, L, L, I, I, P, P],
     "fmsb_add": [P, P, P, L, I, P],
     "fmsb_ce": [P, L, P, P, P, P, P, I, I, I, F, I, I, P],
     "fmsb_ce_bwd": [P, L, P, P, P, L, I, I, I, I, P],
@@ -149,24 +149,37 @@ _STATUS_NAMES = {
 _status_words: dict[int, torch.Tensor] = {}
 
 
+def _peer_wait_units() -> int:
+    """Budget of a device-side wait on another rank, in units of 2^20 SM cycles (``FMSB_PEER_WAIT_S`` seconds at a
+    nominal 1.9 GHz, default 20 s: ranks drift apart while one saves a checkpoint or waits for its data)."""
+    sec = float(os.environ.get("FMSB_PEER_WAIT_S", "20"))
+    return max(1, int(sec * 1.9e9) >> 20)
+
+
 def status_word(device=None) -> torch.Tensor:
-    """Per-device int32 status word shared by all kernels with bounded waits."""
+    """Per-device status block (4 x int32) shared by all kernels with bounded waits: [0] the status code (0 = fine),
+    [1] the budget of waits on other ranks in units of 2^20 cycles; the rest is reserved."""
     dev = torch.cuda.current_device() if device is None else torch.device(device).index
     if dev is None:
         dev = torch.cuda.current_device()
     w = _status_words.get(dev)
     if w is None:
-        w = torch.zeros(1, dtype=torch.int32, device=f"cuda:{dev}")
+        w = torch.tensor([0, _peer_wait_units(), 0, 0], dtype=torch.int32, device=f"cuda:{dev}")
         _status_words[dev] = w
     return w
+
+
+def set_peer_wait(seconds: float, device=None) -> None:
+    """Change the budget of device-side waits on other ranks (tests of the time-out path use a short one)."""
+    status_word(device)[1] = max(1, int(seconds * 1.9e9) >> 20)
 
 
 def check_status(device=None) -> None:
     """Synchronising check of the status word; raises if any kernel reported a time-out."""
     w = status_word(device)
-    v = int(w.item())
+    v = int(w[0].item())
     if v != 0:
-        w.zero_()
+        w[0] = 0
         raise NativeError(f"device status {v}: {_STATUS_NAMES.get(v, 'unknown')}")
 
 
@@ -183,7 +196,7 @@ class StatusMonitor:
         self.event = None
 
     def poll(self) -> None:
-        self.host.copy_(self.word, non_blocking=True)
+        self.host.copy_(self.word[:1], non_blocking=True)
         self.event = torch.cuda.Event()
         self.event.record(torch.cuda.current_stream(self.word.device))
 
@@ -197,7 +210,7 @@ class StatusMonitor:
         self.event = None
         v = int(self.host[0])
         if v != 0:
-            self.word.zero_()
+            self.word[0] = 0
             raise NativeError(f"device status {v}: {_STATUS_NAMES.get(v, 'unknown')} (reported by an earlier step)")
 
 declare("fmsb_attn_fwd", [P, L, P, L, P, L, P, L, P, P, P, I, I, I, I, F, I, P, P])

@@ -73,11 +73,24 @@ def bench_gemm(a):
     out = torch.empty(a.m, a.n, device="cuda", dtype=torch.bfloat16)
     b_mn = a.layout == "nn"
     wt = w.t().contiguous() if b_mn else w
+    from fms_acceleration_b200.ops.gemm import set_pair_mode
+
+    old = set_pair_mode(a.pair)
     t = timeit(lambda: gemm(x, wt, b_mn=b_mn, out=out), a.iters, a.warmup, a.flush)
     NV.check_status()
     fl = 2.0 * a.m * a.n * a.k
-    res = {"kernel": "gemm_tcgen05", "m": a.m, "n": a.n, "k": a.k, "layout": a.layout, "ms": t,
+    res = {"kernel": "gemm_tcgen05", "m": a.m, "n": a.n, "k": a.k, "layout": a.layout, "pair_mode": a.pair, "ms": t,
            "tflops": fl / t / 1e9, "frac_of_%s_bf16_peak" % pk["source"]: fl / t / 1e9 / pk["bf16_tflops"]}
+    import ctypes
+
+    NV.declare("fmsb_gemm_pair_occupancy", [])
+    res["pair_occupancy"] = int(NV.lib().fmsb_gemm_pair_occupancy())
+    if a.both:
+        set_pair_mode(0)
+        t1 = timeit(lambda: gemm(x, wt, b_mn=b_mn, out=out), a.iters, a.warmup, a.flush)
+        res["single_cta_ms"] = t1
+        res["single_cta_tflops"] = fl / t1 / 1e9
+    set_pair_mode(old)
     if a.cublas:
         t2 = timeit(lambda: torch.matmul(x, w.t(), out=out), a.iters, a.warmup, a.flush)
         res["cublas_ms"] = t2
@@ -275,6 +288,8 @@ def main(argv=None):
             p.add_argument("--k", type=int, default=4096)
             p.add_argument("--layout", default="nt", choices=["nt", "nn"], help="nt: B is [N,K]; nn: B is [K,N]")
             p.add_argument("--cublas", action="store_true", help="also time torch.matmul (cuBLAS) for comparison")
+            p.add_argument("--pair", type=int, default=1, help="CTA-pair kernel: 0 never, 1 by shape, 2 whenever possible")
+            p.add_argument("--both", action="store_true", help="also time the single-CTA kernel")
         elif name == "q4gemm":
             p.add_argument("--n", type=int, default=14336)
             p.add_argument("--k", type=int, default=4096)

@@ -42,7 +42,7 @@ __device__ __forceinline__ bool wait_signal_ge(const uint32_t* addr, uint32_t ep
     for (int i = 0; i < 64; ++i) {
       if ((int32_t)(ld_acquire_sys(addr) - epoch) >= 0) return true;
     }
-    if (clock64() - t0 > kWaitBudgetCycles) {
+    if (clock64() - t0 > peer_wait_budget(status)) {
       report_status(status, kTimeoutPeerFlag);
       return false;
     }
@@ -167,7 +167,7 @@ __global__ void allreduce_bucket_kernel(PeerPtrs buckets, PeerPtrs signals, long
     const long long t0 = clock64();
     unsigned v;
     while ((v = atomicAdd(grid_sync, 0u)) != epoch && v != 0xffffffffu) {
-      if (clock64() - t0 > 2 * kWaitBudgetCycles) { report_status(status, kTimeoutPeerFlag); break; }
+      if (clock64() - t0 > 2 * peer_wait_budget(status)) { report_status(status, kTimeoutPeerFlag); break; }
     }
     ok_sh = (v == epoch);
   }
@@ -252,7 +252,7 @@ __global__ void allreduce_bucket_kernel(PeerPtrs buckets, PeerPtrs signals, long
     }
     const long long t0 = clock64();
     while (atomicAdd(grid_sync + 2, 0u) != epoch) {
-      if (clock64() - t0 > 2 * kWaitBudgetCycles) { report_status(status, kTimeoutPeerFlag); break; }
+      if (clock64() - t0 > 2 * peer_wait_budget(status)) { report_status(status, kTimeoutPeerFlag); break; }
       if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) break;
     }
   }

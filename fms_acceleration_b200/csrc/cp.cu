@@ -50,7 +50,7 @@ __global__ void cp_wait_kernel(const uint32_t* __restrict__ my_signals, int rank
   if (!dep) return;
   const long long t0 = clock64();
   while ((int32_t)(cp_ld_acquire(my_signals + s) - epoch) < 0) {
-    if (clock64() - t0 > kWaitBudgetCycles) {
+    if (clock64() - t0 > peer_wait_budget(status)) {
       report_status(status, kTimeoutPeerFlag);
       return;
     }

@@ -324,7 +324,11 @@ __device__ __forceinline__ float act_grad(float e, int act) {
 // h[t, i] = act(e[t, i]) * g[t, i]    e, g, h: row strides in elements
 template <typename T>
 __global__ void glu_fwd_kernel(const T* __restrict__ e, const T* __restrict__ g, T* __restrict__ h, int rows,
-                               int I, long long se, long long sg, long long sh, int act) {
+                               int I, long long se, long long sg, long long sh, int act,
+                               const int* __restrict__ rows_dev) {
+  // rows_dev (optional): the number of rows actually in use, known only on the device (the filled part of a
+  // fixed-capacity mixture-of-experts buffer); never more than `rows`
+  if (rows_dev != nullptr) rows = min(rows, *rows_dev);
   const int vec_per_row = I / 8;
   const long long total = (long long)rows * vec_per_row;
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
@@ -350,7 +354,9 @@ __global__ void glu_fwd_kernel(const T* __restrict__ e, const T* __restrict__ g,
 template <typename T>
 __global__ void glu_bwd_kernel(const T* __restrict__ dh, const T* e, const T* g, T* de, T* dg,
                                T* __restrict__ h_out, int rows, int I, long long sdh, long long se, long long sg,
-                               long long sde, long long sdg, long long sh, int act) {
+                               long long sde, long long sdg, long long sh, int act,
+                               const int* __restrict__ rows_dev) {
+  if (rows_dev != nullptr) rows = min(rows, *rows_dev);
   const int vec_per_row = I / 8;
   const long long total = (long long)rows * vec_per_row;
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
@@ -482,33 +488,33 @@ extern "C" int fmsb_rope(void* qk, const int* pos, const float* cos_t, const flo
 }
 
 extern "C" int fmsb_glu_fwd(const void* e, const void* g, void* h, int rows, int I, long long se, long long sg,
-                            long long sh, int act, int dtype, cudaStream_t stream) {
+                            long long sh, int act, int dtype, const int* rows_dev, cudaStream_t stream) {
   if (I % 8 != 0 || se % 8 || sg % 8 || sh % 8) return -2;
   if (rows <= 0) return 0;
   const int grid = grid_for((long long)rows * (I / 8), 256, 148 * 16);
   if (dtype == 1)
     glu_fwd_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)e, (const __nv_bfloat16*)g,
-                                                            (__nv_bfloat16*)h, rows, I, se, sg, sh, act);
+                                                            (__nv_bfloat16*)h, rows, I, se, sg, sh, act, rows_dev);
   else
     glu_fwd_kernel<__half><<<grid, 256, 0, stream>>>((const __half*)e, (const __half*)g, (__half*)h, rows, I, se, sg,
-                                                     sh, act);
+                                                     sh, act, rows_dev);
   return (int)cudaGetLastError();
 }
 
 extern "C" int fmsb_glu_bwd(const void* dh, const void* e, const void* g, void* de, void* dg, void* h_out, int rows,
                             int I, long long sdh, long long se, long long sg, long long sde, long long sdg,
-                            long long sh, int act, int dtype, cudaStream_t stream) {
+                            long long sh, int act, int dtype, const int* rows_dev, cudaStream_t stream) {
   if (I % 8 != 0 || sdh % 8 || se % 8 || sg % 8 || sde % 8 || sdg % 8 || sh % 8) return -2;
   if (rows <= 0) return 0;
   const int grid = grid_for((long long)rows * (I / 8), 256, 148 * 16);
   if (dtype == 1)
     glu_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
         (const __nv_bfloat16*)dh, (const __nv_bfloat16*)e, (const __nv_bfloat16*)g, (__nv_bfloat16*)de,
-        (__nv_bfloat16*)dg, (__nv_bfloat16*)h_out, rows, I, sdh, se, sg, sde, sdg, sh, act);
+        (__nv_bfloat16*)dg, (__nv_bfloat16*)h_out, rows, I, sdh, se, sg, sde, sdg, sh, act, rows_dev);
   else
     glu_bwd_kernel<__half><<<grid, 256, 0, stream>>>((const __half*)dh, (const __half*)e, (const __half*)g,
                                                      (__half*)de, (__half*)dg, (__half*)h_out, rows, I, sdh, se, sg,
-                                                     sde, sdg, sh, act);
+                                                     sde, sdg, sh, act, rows_dev);
   return (int)cudaGetLastError();
 }
 

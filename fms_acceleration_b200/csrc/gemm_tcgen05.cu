@@ -26,6 +26,7 @@
 // torch.matmul in fms_acceleration_foak/fused_ops/unsloth_lora/utils.py:250-283 (matmul_lora)
 // and the "dequant then matmul" of fms_acceleration_peft/gptqmodel/nn_modules/triton_utils/dequant.py:132-161.
 #include "common.cuh"
+#include <cstdlib>
 #include <mutex>
 
 namespace fmsb {
@@ -180,6 +181,120 @@ __device__ __forceinline__ bool get_tile(int t, const GemmParams& p, TileInfo& t
   ti.b_row_off = 0;
   ti.d_off = (long long)g * p.d_group_stride;
   return true;
+}
+
+// Epilogue of one tile for one warp: read this warp's 32 accumulator lanes in 32-column chunks (every other chunk,
+// starting at `cpar`), apply alpha / beta * C, convert and store.  `gm` is the global row of this thread's lane.
+template <int BN>
+__device__ __forceinline__ void epilogue_store_tile(const GemmParams& p, const TileInfo& ti, uint32_t taddr, int cpar,
+                                                    int gm, int n0, bool empty_k) {
+  constexpr int CH = BN >= 32 ? 32 : 16;
+#pragma unroll 1
+  for (int c = cpar; c < BN / CH; c += 2) {
+    float v[CH];
+    if constexpr (CH == 32) {
+      uint32_t r[32];
+      tmem_ld_32x32(taddr + c * CH, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = empty_k ? 0.f : __uint_as_float(r[i]);
+    } else {
+      uint32_t r[16];
+      tmem_ld_32x16(taddr + c * CH, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = empty_k ? 0.f : __uint_as_float(r[i]);
+    }
+    const int gn = n0 + c * CH;
+    if (gm < ti.m_end && gn < p.N) {
+      const bool full = (gn + CH <= p.N);
+#pragma unroll
+      for (int i = 0; i < CH; ++i) v[i] *= p.alpha;
+      if (p.C != nullptr && p.beta != 0.f) {
+        if (p.c_fp32) {
+          const float* crow = reinterpret_cast<const float*>(p.C) + ti.d_off + (long long)gm * p.ldc + gn + ti.d_c;
+          if (full && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
+#pragma unroll
+            for (int i = 0; i < CH; i += 4) {
+              const float4 f = *reinterpret_cast<const float4*>(crow + i);
+              v[i] += p.beta * f.x;
+              v[i + 1] += p.beta * f.y;
+              v[i + 2] += p.beta * f.z;
+              v[i + 3] += p.beta * f.w;
+            }
+          } else {
+            for (int i = 0; i < CH; ++i)
+              if (gn + i < p.N) v[i] += p.beta * crow[i];
+          }
+        } else if (p.fmt == 1) {
+          const __nv_bfloat16* crow = reinterpret_cast<const __nv_bfloat16*>(p.C) + ti.d_off + (long long)gm * p.ldc + gn + ti.d_c;
+          if (full && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
+#pragma unroll
+            for (int i = 0; i < CH; i += 8) {
+              uint4 u = *reinterpret_cast<const uint4*>(crow + i);
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float2 f = __bfloat1622float2(h[j]);
+                v[i + 2 * j] += p.beta * f.x;
+                v[i + 2 * j + 1] += p.beta * f.y;
+              }
+            }
+          } else {
+            for (int i = 0; i < CH; ++i)
+              if (gn + i < p.N) v[i] += p.beta * __bfloat162float(crow[i]);
+          }
+        } else {
+          const __half* crow = reinterpret_cast<const __half*>(p.C) + ti.d_off + (long long)gm * p.ldc + gn + ti.d_c;
+          for (int i = 0; i < CH; ++i)
+            if (gn + i < p.N) v[i] += p.beta * __half2float(crow[i]);
+        }
+      }
+      if (p.d_fp32) {
+        float* drow = reinterpret_cast<float*>(p.D) + ti.d_off + (long long)gm * p.ldd + gn + ti.d_c;
+        if (full && ((reinterpret_cast<uintptr_t>(drow) & 15) == 0)) {
+#pragma unroll
+          for (int i = 0; i < CH; i += 4)
+            *reinterpret_cast<float4*>(drow + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+        } else {
+          for (int i = 0; i < CH; ++i)
+            if (gn + i < p.N) drow[i] = v[i];
+        }
+      } else {
+        uint16_t* drow = reinterpret_cast<uint16_t*>(p.D) + ti.d_off + (long long)gm * p.ldd + gn + ti.d_c;
+        if (full && ((reinterpret_cast<uintptr_t>(drow) & 15) == 0)) {
+#pragma unroll
+          for (int i = 0; i < CH; i += 8) {
+            uint4 u;
+            if (p.fmt == 1) {
+              u.x = pack_bf16x2(v[i], v[i + 1]);
+              u.y = pack_bf16x2(v[i + 2], v[i + 3]);
+              u.z = pack_bf16x2(v[i + 4], v[i + 5]);
+              u.w = pack_bf16x2(v[i + 6], v[i + 7]);
+            } else {
+              u.x = pack_f16x2(v[i], v[i + 1]);
+              u.y = pack_f16x2(v[i + 2], v[i + 3]);
+              u.z = pack_f16x2(v[i + 4], v[i + 5]);
+              u.w = pack_f16x2(v[i + 6], v[i + 7]);
+            }
+            *reinterpret_cast<uint4*>(drow + i) = u;
+          }
+        } else {
+          for (int i = 0; i < CH; ++i) {
+            if (gn + i < p.N) {
+              if (p.fmt == 1) {
+                __nv_bfloat16 b = __float2bfloat16_rn(v[i]);
+                drow[i] = *reinterpret_cast<uint16_t*>(&b);
+              } else {
+                __half b = __float2half_rn(v[i]);
+                drow[i] = *reinterpret_cast<uint16_t*>(&b);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
 }
 
 template <int BN, int A_MN, int B_MN>
@@ -339,112 +454,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_const
       if (!mbar_wait(tfull_bar(acc), acc_phase, p.status, kTimeoutEpilogue)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
-#pragma unroll 1
-      for (int c = cpar; c < BN / CH; c += 2) {
-        float v[CH];
-        if constexpr (CH == 32) {
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + c * CH, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = empty_k ? 0.f : __uint_as_float(r[i]);
-        } else {
-          uint32_t r[16];
-          tmem_ld_32x16(taddr + c * CH, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] = empty_k ? 0.f : __uint_as_float(r[i]);
-        }
-        const int gn = n0 + c * CH;
-        if (gm < ti.m_end && gn < p.N) {
-          const bool full = (gn + CH <= p.N);
-#pragma unroll
-          for (int i = 0; i < CH; ++i) v[i] *= p.alpha;
-          if (p.C != nullptr && p.beta != 0.f) {
-            if (p.c_fp32) {
-              const float* crow = reinterpret_cast<const float*>(p.C) + ti.d_off + (long long)gm * p.ldc + gn + ti.d_c;
-              if (full && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
-#pragma unroll
-                for (int i = 0; i < CH; i += 4) {
-                  const float4 f = *reinterpret_cast<const float4*>(crow + i);
-                  v[i] += p.beta * f.x;
-                  v[i + 1] += p.beta * f.y;
-                  v[i + 2] += p.beta * f.z;
-                  v[i + 3] += p.beta * f.w;
-                }
-              } else {
-                for (int i = 0; i < CH; ++i)
-                  if (gn + i < p.N) v[i] += p.beta * crow[i];
-              }
-            } else if (p.fmt == 1) {
-              const __nv_bfloat16* crow = reinterpret_cast<const __nv_bfloat16*>(p.C) + ti.d_off + (long long)gm * p.ldc + gn + ti.d_c;
-              if (full && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
-#pragma unroll
-                for (int i = 0; i < CH; i += 8) {
-                  uint4 u = *reinterpret_cast<const uint4*>(crow + i);
-                  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    float2 f = __bfloat1622float2(h[j]);
-                    v[i + 2 * j] += p.beta * f.x;
-                    v[i + 2 * j + 1] += p.beta * f.y;
-                  }
-                }
-              } else {
-                for (int i = 0; i < CH; ++i)
-                  if (gn + i < p.N) v[i] += p.beta * __bfloat162float(crow[i]);
-              }
-            } else {
-              const __half* crow = reinterpret_cast<const __half*>(p.C) + ti.d_off + (long long)gm * p.ldc + gn + ti.d_c;
-              for (int i = 0; i < CH; ++i)
-                if (gn + i < p.N) v[i] += p.beta * __half2float(crow[i]);
-            }
-          }
-          if (p.d_fp32) {
-            float* drow = reinterpret_cast<float*>(p.D) + ti.d_off + (long long)gm * p.ldd + gn + ti.d_c;
-            if (full && ((reinterpret_cast<uintptr_t>(drow) & 15) == 0)) {
-#pragma unroll
-              for (int i = 0; i < CH; i += 4)
-                *reinterpret_cast<float4*>(drow + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-            } else {
-              for (int i = 0; i < CH; ++i)
-                if (gn + i < p.N) drow[i] = v[i];
-            }
-          } else {
-            uint16_t* drow = reinterpret_cast<uint16_t*>(p.D) + ti.d_off + (long long)gm * p.ldd + gn + ti.d_c;
-            if (full && ((reinterpret_cast<uintptr_t>(drow) & 15) == 0)) {
-#pragma unroll
-              for (int i = 0; i < CH; i += 8) {
-                uint4 u;
-                if (p.fmt == 1) {
-                  u.x = pack_bf16x2(v[i], v[i + 1]);
-                  u.y = pack_bf16x2(v[i + 2], v[i + 3]);
-                  u.z = pack_bf16x2(v[i + 4], v[i + 5]);
-                  u.w = pack_bf16x2(v[i + 6], v[i + 7]);
-                } else {
-                  u.x = pack_f16x2(v[i], v[i + 1]);
-                  u.y = pack_f16x2(v[i + 2], v[i + 3]);
-                  u.z = pack_f16x2(v[i + 4], v[i + 5]);
-                  u.w = pack_f16x2(v[i + 6], v[i + 7]);
-                }
-                *reinterpret_cast<uint4*>(drow + i) = u;
-              }
-            } else {
-              for (int i = 0; i < CH; ++i) {
-                if (gn + i < p.N) {
-                  if (p.fmt == 1) {
-                    __nv_bfloat16 b = __float2bfloat16_rn(v[i]);
-                    drow[i] = *reinterpret_cast<uint16_t*>(&b);
-                  } else {
-                    __half b = __float2half_rn(v[i]);
-                    drow[i] = *reinterpret_cast<uint16_t*>(&b);
-                  }
-                }
-              }
-            }
-          }
-        }
-      }
+      epilogue_store_tile<BN>(p, ti, taddr, cpar, gm, n0, empty_k);
       tc_fence_before();
       mbar_arrive(tempty_bar(acc));
       acc ^= 1;
@@ -459,6 +469,215 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_const
   if (warp == 0) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+
+// ----------------------------------------------------------------------------------------
+// CTA-pair variant (plain mode, 256 x 256 output tiles): a cluster of two CTAs on the two SMs of one TPC computes
+// one tile with tcgen05.mma.cta_group::2 (M = 256, N = 256).  CTA r of the pair stages rows [m0 + 128 r, +128) of A
+// and rows/columns [n0 + 128 r, +128) of B (its half of the N extent) per K block with its own tensor loads (no
+// multicast), so per SM and K block 32 KB enter shared memory for a 256 x 256 x 64 product where the single-CTA kernel
+// moves 48 KB for 128 x 256 x 64: B traffic per output element halves, and so does the number of MMA instructions per
+// SM.  The pair's leader (cluster rank 0) issues all MMAs; they read both CTAs' shared memory and write 128 lanes of
+// tensor memory in each CTA; every CTA drains its own lanes with the same 8 epilogue warps as the single-CTA kernel.
+//
+// Barriers (same shared-memory offsets in both CTAs):
+//   full[s]    used in the leader only: 1 arrival (the leader's producer announces the bytes of BOTH CTAs' loads; the
+//              peer's loads complete on the same barrier, possibly before the announcement: the byte count of a
+//              phase may run negative, and a peer load of the next pass cannot start before this phase is over)
+//   empty[s]   per CTA: released by the leader's commit (arrives in both CTAs)
+//   tfull[a]   per CTA: accumulator a complete (leader's commit, both CTAs)
+//   tempty[a]  used in the leader only: 16 arrivals (8 epilogue warps of each CTA)
+// ----------------------------------------------------------------------------------------
+constexpr int BM2 = 256;   // rows of a pair's tile
+constexpr int BN2 = 256;   // columns of a pair's tile
+constexpr int BNH = 128;   // B rows staged by each CTA
+
+struct PairCfg {
+  static constexpr int kABytes = BM * BK * 2;    // 16 KB
+  static constexpr int kBBytes = BNH * BK * 2;   // 16 KB
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = 6;
+  static constexpr int kTmemCols = 2 * BN2;      // two accumulators of 256 columns: all of tensor memory
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+};
+
+template <int A_MN, int B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
+                         const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
+                         const GemmParams p) {
+  using Cfg = PairCfg;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + Cfg::kStages * Cfg::kStageBytes;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::kStages + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * Cfg::kStages + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * Cfg::kStages + 2 + a); };
+  const uint32_t holder = bar_base + 8u * (2 * Cfg::kStages + 4);
+  auto sA = [&](int s) { return smem_base + s * Cfg::kStageBytes; };
+  auto sB = [&](int s) { return smem_base + s * Cfg::kStageBytes + Cfg::kABytes; };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();        // 0: leader
+  const int pair = blockIdx.x >> 1;
+  const int n_pairs = gridDim.x >> 1;
+  const int tiles_m = (p.M + BM2 - 1) / BM2;
+  const int tiles_n = (p.N + BN2 - 1) / BN2;
+  const int n_tiles = tiles_m * tiles_n;
+  const int kblocks = p.kblocks1 + p.kblocks2;
+
+  if (warp == 1 && lane == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 16);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    if (lane == 0) {
+      prefetch_tmap(&tmA1);
+      prefetch_tmap(&tmB1);
+      if (p.kblocks2 > 0) {
+        prefetch_tmap(&tmA2);
+        prefetch_tmap(&tmB2);
+      }
+    }
+    __syncwarp();
+    tmem_alloc_pair(holder, Cfg::kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers are initialised before either one signals the other
+  tc_fence_after();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(holder));
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer (each CTA loads its own halves)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = pair; ok && t < n_tiles; t += n_pairs) {
+        int tm, tn;
+        tile_coords(t, tiles_m, tiles_n, tm, tn);
+        const int m0 = tm * BM2 + (int)cta * BM;
+        const int n0 = tn * BN2 + (int)cta * BNH;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, p.status, kTimeoutProducer)) {
+            ok = false;
+            break;
+          }
+          const uint32_t lead_full = mapa_shared(full_bar(stage), 0);
+          if (cta == 0) mbar_expect_tx(full_bar(stage), 2 * Cfg::kStageBytes);
+          const bool second = kb >= p.kblocks1;
+          const CUtensorMap* ta = second ? &tmA2 : &tmA1;
+          const CUtensorMap* tb = second ? &tmB2 : &tmB1;
+          const int k0 = second ? (kb - p.kblocks1) * BK : kb * BK;
+          if (A_MN == 0) {
+            tma_load_2d_pair(sA(stage), ta, lead_full, k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sA(stage) + j * 8192, ta, lead_full, m0 + 64 * j, k0);
+          }
+          if (B_MN == 0) {
+            tma_load_2d_pair(sB(stage), tb, lead_full, k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BNH / 64; ++j) tma_load_2d_pair(sB(stage) + j * 8192, tb, lead_full, n0 + 64 * j, k0);
+          }
+          if (++stage == Cfg::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && cta == 0) {
+      const uint32_t idesc = make_idesc_f16(BM2, BN2, p.fmt, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = pair; ok && t < n_tiles; t += n_pairs) {
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, p.status, kTimeoutMma)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN2);
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, p.status, kTimeoutMma)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t adesc = A_MN ? make_smem_desc(sA(stage) + k * 2048, 8192, 1024)
+                                        : make_smem_desc(sA(stage) + k * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? make_smem_desc(sB(stage) + k * 2048, 8192, 1024)
+                                        : make_smem_desc(sB(stage) + k * 32, 16, 1024);
+            tc_mma_f16_pair(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit_pair(empty_bar(stage), 3);  // the stage is free again in both CTAs
+          if (++stage == Cfg::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        tc_commit_pair(tfull_bar(acc), 3);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (8 warps, this CTA's 128 rows)
+    const int q = warp & 3;
+    const int cpar = (warp - 2) >> 2;
+    const int row = q * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    TileInfo ti;
+    ti.d_off = 0;
+    ti.d_c = 0;
+    ti.m_end = p.M;
+    for (int t = pair; t < n_tiles; t += n_pairs) {
+      int tm, tn;
+      tile_coords(t, tiles_m, tiles_n, tm, tn);
+      const int gm = tm * BM2 + (int)cta * BM + row;
+      const int n0 = tn * BN2;
+      ti.n0 = n0;
+      if (!mbar_wait(tfull_bar(acc), acc_phase, p.status, kTimeoutEpilogue)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN2);
+      epilogue_store_tile<BN2>(p, ti, taddr, cpar, gm, n0, kblocks == 0);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(tempty_bar(acc), 0));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves (or frees tensor memory) while the other may still signal or read it
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
   }
 }
 
@@ -529,7 +748,66 @@ int launch_gemm(const CUtensorMap& a1, const CUtensorMap& b1, const CUtensorMap&
   return static_cast<int>(cudaGetLastError());
 }
 
+static int g_pair_occupancy = -1, g_pair_occupancy_error = -1;
+
+// Clusters of two CTAs that can be resident at once (one pair per TPC when the kernel takes a whole SM).
+template <int A_MN, int B_MN>
+int launch_gemm_pair(const CUtensorMap& a1, const CUtensorMap& b1, const CUtensorMap& a2, const CUtensorMap& b2,
+                     const fmsb::GemmParams& p, int max_ctas, cudaStream_t stream) {
+  using Cfg = fmsb::PairCfg;
+  auto kern = fmsb::gemm_tcgen05_pair_kernel<A_MN, B_MN>;
+  static int max_pairs = -1;
+  if (max_pairs < 0) {
+    g_pair_occupancy_error = 0;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(sm_count(), 1, 1);
+    cfg.blockDim = dim3(fmsb::kGemmThreads, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+    g_pair_occupancy_error = (int)e;
+    g_pair_occupancy = n;
+    max_pairs = (e == cudaSuccess && n > 0) ? n : sm_count() / 2;
+    (void)cudaGetLastError();
+    if (const char* env = getenv("FMSB_GEMM_PAIRS")) {
+      const int v = atoi(env);
+      if (v > 0) max_pairs = v;
+    }
+  }
+  int pairs = max_pairs;
+  if (max_ctas > 0 && max_ctas / 2 < pairs) pairs = max_ctas / 2;
+  const int tiles = ((p.M + fmsb::BM2 - 1) / fmsb::BM2) * ((p.N + fmsb::BN2 - 1) / fmsb::BN2);
+  if (tiles < pairs) pairs = tiles;
+  if (pairs <= 0) return 0;
+  kern<<<2 * pairs, fmsb::kGemmThreads, Cfg::kSmemBytes, stream>>>(a1, b1, a2, b2, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// 0: never, 1: when there are enough 256 x 256 tiles to fill the machine about twice (default), 2: whenever M and N
+// reach 256; set through fmsb_gemm_set_pair_mode (tests compare both kernels on small shapes)
+static int g_pair_mode = 1;
+
 }  // namespace fmsb_host
+
+// what the occupancy query answered for the CTA-pair kernel (after its first launch): clusters, or -(error) - 1
+extern "C" int fmsb_gemm_pair_occupancy() {
+  return fmsb_host::g_pair_occupancy_error > 0 ? -fmsb_host::g_pair_occupancy_error - 1 : fmsb_host::g_pair_occupancy;
+}
+
+extern "C" int fmsb_gemm_set_pair_mode(int mode) {
+  const int old = fmsb_host::g_pair_mode;
+  fmsb_host::g_pair_mode = mode;
+  return old;
+}
 
 // D[M,N] = alpha * (A1.B1^T + A2.B2^T) + beta * C.   16-bit inputs (fmt 0 = fp16, 1 = bf16).
 // Constraints: leading dimensions multiples of 8 elements; base pointers 16-byte aligned.  bn selects the N tile (16/32/64/128/256); MN-major B needs bn >= 64.
@@ -566,6 +844,11 @@ static int gemm_impl(const void* A1, long long lda1, const void* B1, long long l
   if (b_mn && bn < 64) return -3;
   CUtensorMap ta1, tb1, ta2, tb2;
   int rc;
+  // CTA pairs: plain mode, 256-column tiles, enough 256 x 256 tiles to fill the machine about twice
+  const bool use_pair = mode == 0 && bn == 256 && g_pair_mode != 0 && M >= 256 && N >= 256 &&
+                        (g_pair_mode == 2 ||
+                         (long long)((M + 255) / 256) * ((N + 255) / 256) >= 2LL * (sm_count() / 2));
+  const int b_box_rows = use_pair ? fmsb::BNH : bn;
   // a_rows / b_rows: number of rows of the stored A / B matrices when it differs from the per-tile view
   // (grouped modes address several segments / expert matrices through one tensor map)
   const long long a_cols = bd && bd->a_cols > 0 ? bd->a_cols : 0, b_cols = bd && bd->b_cols > 0 ? bd->b_cols : 0;
@@ -577,7 +860,7 @@ static int gemm_impl(const void* A1, long long lda1, const void* B1, long long l
   const long long n_each = (gx != nullptr && gx->n_split > 0) ? gx->n_split : N;
   auto mk_b = [&](CUtensorMap* t, const void* B, long long ldb, int K) {
     if (b_mn) return make_tmap_2d_16b(t, B, b_rows > 0 ? b_rows : K, b_cols > 0 ? b_cols : n_each, ldb, 64, 64);
-    return make_tmap_2d_16b(t, B, b_rows > 0 ? b_rows : N, b_cols > 0 ? b_cols : K, ldb, bn, 64);
+    return make_tmap_2d_16b(t, B, b_rows > 0 ? b_rows : N, b_cols > 0 ? b_cols : K, ldb, b_box_rows, 64);
   };
   if ((rc = mk_a(&ta1, A1, lda1, K1))) return rc;
   if ((rc = mk_b(&tb1, B1, ldb1, K1))) return rc;
@@ -625,6 +908,12 @@ static int gemm_impl(const void* A1, long long lda1, const void* B1, long long l
     p.d_ro = bd->d_ro; p.d_ri = bd->d_ri; p.d_ci = bd->d_ci;
   }
 
+  if (use_pair) {
+    if (!a_mn && !b_mn) return launch_gemm_pair<0, 0>(ta1, tb1, ta2, tb2, p, max_ctas, stream);
+    if (a_mn && !b_mn) return launch_gemm_pair<1, 0>(ta1, tb1, ta2, tb2, p, max_ctas, stream);
+    if (!a_mn && b_mn) return launch_gemm_pair<0, 1>(ta1, tb1, ta2, tb2, p, max_ctas, stream);
+    return launch_gemm_pair<1, 1>(ta1, tb1, ta2, tb2, p, max_ctas, stream);
+  }
 #define FMSB_DISPATCH(BNV)                                                                          \
   if (bn == BNV) {                                                                                  \
     if (!a_mn && !b_mn) return launch_gemm<BNV, 0, 0>(ta1, tb1, ta2, tb2, p, max_ctas, stream);     \

@@ -41,7 +41,7 @@ __device__ __forceinline__ bool moe_wait_ge(const uint32_t* addr, uint32_t epoch
   while (true) {
     for (int i = 0; i < 64; ++i)
       if ((int32_t)(moe_ld_acquire(addr) - epoch) >= 0) return true;
-    if (clock64() - t0 > kWaitBudgetCycles) {
+    if (clock64() - t0 > peer_wait_budget(status)) {
       report_status(status, kTimeoutPeerFlag);
       return false;
     }

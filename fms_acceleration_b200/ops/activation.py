@@ -27,18 +27,19 @@ def glu_ref(e, g, act="silu"):
     return (f.to(e.dtype).float() * g.float()).to(e.dtype)
 
 
-def glu_fwd(e, g, act="silu", out=None):
-    """e, g: 2-D views (row stride arbitrary, unit column stride) -> h [rows, I]."""
+def glu_fwd(e, g, act="silu", out=None, rows_dev=None):
+    """e, g: 2-D views (row stride arbitrary, unit column stride) -> h [rows, I].  ``rows_dev``: optional int32
+    device scalar with the number of rows in use (the rest of a fixed-capacity buffer is left untouched)."""
     rows, I = e.shape
     if out is None:
         out = torch.empty(rows, I, dtype=e.dtype, device=e.device)
     rc = N.lib().fmsb_glu_fwd(e.data_ptr(), g.data_ptr(), out.data_ptr(), rows, I, e.stride(0), g.stride(0),
-                              out.stride(0), ACT_CODES[act], N.dtype_code(e.dtype), N.stream_ptr())
+                              out.stride(0), ACT_CODES[act], N.dtype_code(e.dtype), N.ptr(rows_dev), N.stream_ptr())
     N.check(rc, "fmsb_glu_fwd")
     return out
 
 
-def glu_bwd(dh, e, g, act="silu", de=None, dg=None, h_out=None):
+def glu_bwd(dh, e, g, act="silu", de=None, dg=None, h_out=None, rows_dev=None):
     rows, I = e.shape
     if de is None:
         de = torch.empty(rows, I, dtype=e.dtype, device=e.device)
@@ -47,7 +48,7 @@ def glu_bwd(dh, e, g, act="silu", de=None, dg=None, h_out=None):
     rc = N.lib().fmsb_glu_bwd(dh.data_ptr(), e.data_ptr(), g.data_ptr(), de.data_ptr(), dg.data_ptr(), N.ptr(h_out),
                               rows, I, dh.stride(0), e.stride(0), g.stride(0), de.stride(0), dg.stride(0),
                               h_out.stride(0) if h_out is not None else 0, ACT_CODES[act], N.dtype_code(e.dtype),
-                              N.stream_ptr())
+                              N.ptr(rows_dev), N.stream_ptr())
     N.check(rc, "fmsb_glu_bwd")
     return de, dg
 

@@ -112,6 +112,14 @@ def gemm(
     return out
 
 
+def set_pair_mode(mode: int) -> int:
+    """Choose between the single-CTA tile kernel and the CTA-pair kernel (256 x 256 tiles, ``cta_group::2``) for plain
+    products: 0 never, 1 when the product has enough tiles to fill the machine (default), 2 whenever M, N >= 256.
+    Returns the previous setting."""
+    N.declare("fmsb_gemm_set_pair_mode", [_ct.c_int])
+    return int(N.lib().fmsb_gemm_set_pair_mode(int(mode)))
+
+
 SM_COUNT = 148
 SPLIT_K_MIN = 512  # shortest contraction slice worth a tile of its own
 

@@ -368,7 +368,8 @@ def _experts_fwd_local(mctx, Xs, seg_off, w1, w3, w2, act, Ys=None):
     I_, El, H = mctx.I, mctx.E_local, mctx.H
     gu = grouped_gemm(Xs, w1.view(El * H, I_), seg_off, El, mode=1, n=2 * I_, b_alt=w3.view(El * H, I_),
                       max_ctas=mctx.gemm_ctas)
-    hs = ACT.glu_fwd(gu[:, :I_], gu[:, I_:], act)
+    used = seg_off[El:]  # rows in use (device scalar): the buffers are sized for the capacity, not for the load
+    hs = ACT.glu_fwd(gu[:, :I_], gu[:, I_:], act, rows_dev=used)
     Ys = grouped_gemm(hs, w2.view(El * I_, H), seg_off, El, mode=1, n=H, out=Ys, max_ctas=mctx.gemm_ctas)
     return gu, Ys
 
@@ -377,7 +378,8 @@ def _experts_bwd_local(mctx, Xs, gu, dYs, seg_off, w1, w3, w2, act, acc, need_dw
     """Gradients of the three expert weight tensors (accumulated into ``acc`` when it already holds a chunk) and the
     input gradient in the expert-sorted layout.  ``gu`` is overwritten with the pre-activation gradients."""
     I_, El, H = mctx.I, mctx.E_local, mctx.H
-    hs = ACT.glu_fwd(gu[:, :I_], gu[:, I_:], act)
+    used = seg_off[El:]
+    hs = ACT.glu_fwd(gu[:, :I_], gu[:, I_:], act, rows_dev=used)
     first = "dw2" not in acc
     if need_dw:
         if first:
@@ -386,7 +388,7 @@ def _experts_bwd_local(mctx, Xs, gu, dYs, seg_off, w1, w3, w2, act, acc, need_dw
             grouped_gemm(hs, dYs, seg_off, El, mode=2, m=I_, n=H, out=acc["dw2"], c=acc["dw2"], beta=1.0,
                          max_ctas=mctx.gemm_ctas)
     dhs = grouped_gemm(dYs, w2.view(El * I_, H), seg_off, El, mode=1, b_mn=False, n=I_, max_ctas=mctx.gemm_ctas)
-    ACT.glu_bwd(dhs, gu[:, :I_], gu[:, I_:], act, de=gu[:, :I_], dg=gu[:, I_:])
+    ACT.glu_bwd(dhs, gu[:, :I_], gu[:, I_:], act, de=gu[:, :I_], dg=gu[:, I_:], rows_dev=used)
     if need_dw:
         # [d gate | d up] side by side in gu: both weight gradients in one pass over Xs
         if first:
@@ -462,7 +464,8 @@ class _Experts(torch.autograd.Function):
 # ------------------------------------------------------------------------------------------------ expert parallel
 class _Chunk:
     """Plan and buffers of one token slice of an expert-parallel call."""
-    __slots__ = ("t0", "t1", "s", "seg_off", "seg_cnt", "dest_row", "hit", "stage_row", "stage_cnt", "Xs", "gu", "Ys")
+    __slots__ = ("t0", "t1", "s", "seg_off", "seg_cnt", "dest_row", "hit", "stage_row", "stage_cnt", "Xs", "gu", "Ys",
+                 "dYs", "rgate", "dXs")
 
 
 def _stage_plan(sh: _EPShared, idx_c, dest_row, n, dev):
@@ -574,16 +577,25 @@ class _ExpertsEP(torch.autograd.Function):
             ch.hit, ch.stage_row, ch.stage_cnt = _stage_plan(sh, idx[ch.t0:ch.t1], ch.dest_row, n, dev)
             chunks.append(ch)
         out = torch.empty(T, H, dtype=dt, device=dev)
-
-        def compute(ch):
+        for ch in chunks:
             ch.Xs = torch.empty(sh.cap, H, dtype=dt, device=dev)
+
+        # The data-movement kernels of a slice (store to the owners, replicate into the expert-sorted buffer; reduce per
+        # staged row, read back) run on the communication stream, so that they overlap the grouped GEMMs of the
+        # neighbouring slice, which are all the compute stream does.
+        def push(ch):
+            _push(sh, ch, x, idx, gates, BAR_A)
             _zero_pad(mctx, ch.Xs, ch.seg_off, ch.seg_cnt)
             _replicate(sh, ch, ch.Xs)
-            ch.gu, ch.Ys = _experts_fwd_local(mctx, ch.Xs, ch.seg_off, w1, w3, w2, act)
-            _prereduce(sh, ch, ch.Ys, weighted=True)
 
-        _pipeline(sh, chunks, lambda ch: _push(sh, ch, x, idx, gates, BAR_A), compute,
-                  lambda ch: _pull(sh, mctx, ch, out, BAR_B))
+        def compute(ch):
+            ch.gu, ch.Ys = _experts_fwd_local(mctx, ch.Xs, ch.seg_off, w1, w3, w2, act)
+
+        def pull(ch):
+            _prereduce(sh, ch, ch.Ys, weighted=True)
+            _pull(sh, mctx, ch, out, BAR_B)
+
+        _pipeline(sh, chunks, push, compute, pull)
         ctx.mctx, ctx.act, ctx.chunks = mctx, act, chunks
         ctx.save_for_backward(gates, idx, w1, w3, w2)
         return out
@@ -602,22 +614,26 @@ class _ExpertsEP(torch.autograd.Function):
         acc: dict = {}
         need_dw = any(ctx.needs_input_grad[3:6])
 
-        def compute(ch):
-            dYs = torch.empty(sh.cap, H, dtype=dt, device=dev)
-            rgate = torch.zeros(sh.cap, dtype=torch.float32, device=dev)
-            _zero_pad(mctx, dYs, ch.seg_off, ch.seg_cnt)
+        for ch in chunks:
+            ch.dYs = torch.empty(sh.cap, H, dtype=dt, device=dev)
+            ch.rgate = torch.zeros(sh.cap, dtype=torch.float32, device=dev)
+
+        def push(ch):
+            _push(sh, ch, dout, idx, gates, BAR_C)
+            _zero_pad(mctx, ch.dYs, ch.seg_off, ch.seg_cnt)
             # unscaled dout rows and the routing weight of every received row; the owner forms <expert output, dout>
             # per row (read back by the source, 4 bytes per pair) and applies the weight in place
-            _replicate(sh, ch, dYs, slot_out=rgate)
-            rc = N.lib().fmsb_moe_rowdot_scale(ch.Ys.data_ptr(), ch.Ys.stride(0), dYs.data_ptr(), dYs.stride(0),
-                                               rgate.data_ptr(), sh.local_ptr("rdots", ch.s), ch.seg_off.data_ptr(), El,
-                                               sh.cap, H, N.dtype_code(dt), N.stream_ptr())
+            _replicate(sh, ch, ch.dYs, slot_out=ch.rgate)
+            rc = N.lib().fmsb_moe_rowdot_scale(ch.Ys.data_ptr(), ch.Ys.stride(0), ch.dYs.data_ptr(), ch.dYs.stride(0),
+                                               ch.rgate.data_ptr(), sh.local_ptr("rdots", ch.s), ch.seg_off.data_ptr(),
+                                               El, sh.cap, H, N.dtype_code(dt), N.stream_ptr())
             N.check(rc, "fmsb_moe_rowdot_scale")
-            dXs = _experts_bwd_local(mctx, ch.Xs, ch.gu, dYs, ch.seg_off, w1, w3, w2, act, acc, need_dw)
-            _prereduce(sh, ch, dXs, weighted=False)
-            ch.Xs = ch.gu = ch.Ys = None
+
+        def compute(ch):
+            ch.dXs = _experts_bwd_local(mctx, ch.Xs, ch.gu, ch.dYs, ch.seg_off, w1, w3, w2, act, acc, need_dw)
 
         def pull(ch):
+            _prereduce(sh, ch, ch.dXs, weighted=False)
             _pull(sh, mctx, ch, dx, BAR_D)
             n = ch.t1 - ch.t0
             if n:
@@ -626,7 +642,9 @@ class _ExpertsEP(torch.autograd.Function):
                                                     dgate[ch.t0:ch.t1].data_ptr(), sh.world, N.stream_ptr())
                 N.check(rc, "fmsb_moe_gather_scalar")
 
-        _pipeline(sh, chunks, lambda ch: _push(sh, ch, dout, idx, gates, BAR_C), compute, pull)
+        _pipeline(sh, chunks, push, compute, pull)
+        for ch in chunks:  # only now: the communication stream has finished reading them
+            ch.Xs = ch.gu = ch.Ys = ch.dYs = ch.rgate = ch.dXs = None
         dw1, dw3, dw2 = _weight_grads(mctx, acc, w1, w3, w2, ctx.needs_input_grad[3:6])
         return dx, dgate, None, dw1, dw3, dw2, None, None
 

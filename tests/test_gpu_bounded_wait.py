@@ -14,15 +14,15 @@ def test_wait_runs_out_and_reports():
     dev = torch.device("cuda", 0)
     flag = torch.zeros(1, dtype=torch.int32, device=dev)
     st = NV.status_word(dev)
-    st.zero_()
+    st[0] = 0
     budget = 20_000_000  # cycles: about ten milliseconds
     rc = NV.lib().fmsb_comm_wait_flag(flag.data_ptr(), 1, st.data_ptr(), budget, NV.stream_ptr())
     assert rc == 0
     torch.cuda.synchronize()
-    assert int(st.item()) == 4  # kTimeoutPeerFlag
+    assert int(st[0].item()) == 4  # kTimeoutPeerFlag
     with pytest.raises(NV.NativeError, match="4"):
         NV.check_status(dev)
-    assert int(st.item()) == 0  # cleared by the check
+    assert int(st[0].item()) == 0  # cleared by the check
     # a flag that is already at the epoch returns at once and reports nothing
     flag.fill_(1)
     NV.lib().fmsb_comm_wait_flag(flag.data_ptr(), 1, st.data_ptr(), budget, NV.stream_ptr())

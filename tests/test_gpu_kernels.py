@@ -79,6 +79,40 @@ def test_gemm_large_persistent():
     assert torch.equal(out, out2)
 
 
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N_,K", [(512, 512, 256), (300, 520, 200), (1024, 768, 4096)])
+def test_gemm_cta_pair_kernel(a_mn, b_mn, M, N_, K):
+    """The CTA-pair kernel (256 x 256 tiles, tcgen05 cta_group::2) against the fp32 product and, bit for bit, against
+    the single-CTA kernel (same contraction order); ragged M, N and K, all operand layouts, LoRA pair and C."""
+    from fms_acceleration_b200.ops.gemm import set_pair_mode
+
+    if (a_mn and M % 8) or (b_mn and N_ % 8):
+        pytest.skip("MN-major operands need a leading dimension that is a multiple of 8")
+    torch.manual_seed(4)
+    a = torch.randn((K, M) if a_mn else (M, K), device=DEV, dtype=torch.bfloat16)
+    b = torch.randn((K, N_) if b_mn else (N_, K), device=DEV, dtype=torch.bfloat16)
+    ref = (a.float().t() if a_mn else a.float()) @ (b.float() if b_mn else b.float().t())
+    old = set_pair_mode(0)
+    try:
+        single = gemm(a, b, a_mn=a_mn, b_mn=b_mn, bn=256, out_dtype=torch.float32)
+        set_pair_mode(2)
+        pair = gemm(a, b, a_mn=a_mn, b_mn=b_mn, bn=256, out_dtype=torch.float32)
+        NV.check_status()
+        assert _rel(pair, ref) < 2e-3
+        assert torch.equal(pair, single)
+        if not a_mn and not b_mn:
+            r = 16
+            xa = torch.randn(M, r, device=DEV, dtype=torch.bfloat16)
+            lb = torch.randn(N_, r, device=DEV, dtype=torch.bfloat16)
+            c = torch.randn(M, N_, device=DEV, dtype=torch.bfloat16)
+            out = gemm(a, b, a2=xa, b2=lb, c=c, alpha=0.5, beta=2.0, bn=256)
+            NV.check_status()
+            want = 0.5 * (ref + xa.float() @ lb.float().t()) + 2.0 * c.float()
+            assert _rel(out, want) < 1e-2
+    finally:
+        set_pair_mode(old)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("rows,H", [(7, 256), (300, 4096), (33, 1536)])
 def test_rmsnorm(dtype, rows, H):

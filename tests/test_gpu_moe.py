@@ -93,11 +93,11 @@ def test_capacity_overflow_drops_rows_and_reports():
     ctx.cap = 384  # instead of T*k + padding = 1024 + ...
     idx = torch.randint(0, E, (T, k), dtype=torch.int32, device=DEV)
     st = NV.status_word(DEV)
-    st.zero_()
+    st[0] = 0
     MOE.overflow_count(DEV, reset=True)
     seg_off, seg_cnt, dest_row = MOE._plan(ctx, idx, T, DEV)
     torch.cuda.synchronize()
-    assert int(st.item()) == 0  # dropped rows do not make later bounded waits give up
+    assert int(st[0].item()) == 0  # dropped rows do not make later bounded waits give up
     assert MOE.overflow_count(DEV, reset=True) > 0
     so, sc, dr = seg_off.cpu(), seg_cnt.cpu(), dest_row.cpu()
     assert int(so[-1]) <= ctx.cap and int(sc.sum()) <= ctx.cap

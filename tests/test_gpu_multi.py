@@ -1,5 +1,6 @@
-"""Multi-GPU tests: run ``tests/dist_worker.py`` under torchrun on 2 GPUs (skipped with fewer).  NVLS is switched
-off for NCCL (it only bootstraps and provides the reference results here)."""
+"""Multi-GPU tests: run ``tests/dist_worker.py`` under torchrun on 2 GPUs and, where the machine has them, on 4 and
+8 (skipped with fewer).  NVLS is switched off for NCCL (it only bootstraps and provides the reference results
+here)."""
 import os
 import subprocess
 import sys
@@ -20,18 +21,19 @@ def _run(which: str, nproc: int = 2, timeout: int = 600):
     return res
 
 
+@pytest.mark.parametrize("nproc", [2, 4, 8])
 @pytest.mark.parametrize("which,expected", [
     ("comm", ["allgather", "allreduce", "reduce_scatter"]),
     ("engine", ["engine", "engine_train"]),
     ("zero1", ["zero1"]),
-    ("moe", ["moe_ep"]),
+    ("moe", ["moe_ep", "moe_library"]),
     ("cp", ["mamba_cp"]),
 ])
-def test_multi_gpu(which, expected):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
-    res = _run(which)
+def test_multi_gpu(which, expected, nproc):
+    if torch.cuda.device_count() < nproc:
+        pytest.skip(f"needs {nproc} GPUs")
+    res = _run(which, nproc=nproc)
     out = res.stdout + res.stderr
     assert res.returncode == 0, out[-3000:]
     for name in expected:
-        assert out.count(f"DIST_OK {name}") >= 2, f"{name} did not pass on both ranks\n{out[-3000:]}"
+        assert out.count(f"DIST_OK {name}") >= nproc, f"{name} did not pass on all {nproc} ranks\n{out[-3000:]}"
