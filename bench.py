@@ -27,21 +27,30 @@ BASELINE_TOK_S = 4128.0  # Mistral-7B NF4 QLoRA + fused ops, 1 x A100-80GB, bs4 
 
 
 def reference_arm(args) -> int:
-    """Run the unmodified reference from baseline/_ref; print why when that is impossible."""
+    """Run the unmodified reference from baseline/_ref through its own public API; print why when that is impossible.
+
+    The attempt is real: a child process with baseline/_ref first on its path imports the reference's framework
+    package and its benchmark's trainer entry point, exactly what ``scripts/benchmarks/benchmark.py`` of the reference
+    would launch.  On this image the import stops at the first missing dependency (peft / accelerate / trl /
+    bitsandbytes are not installed and cannot be: no network, not in the wheelhouse); that error is reported."""
     ref_dir = os.path.join(REPO, "baseline", "_ref")
-    reason = None
-    if not os.path.isdir(ref_dir):
-        reason = "baseline/_ref is not installed (offline pip install of the reference did not succeed)"
+    if not os.path.isdir(os.path.join(ref_dir, "fms_acceleration")):
+        reason = ("baseline/_ref holds no copy of the reference (python -m fms_acceleration_b200.baseline."
+                  "install_reference <checkout> was not run on this checkout)")
     else:
-        sys.path.insert(0, ref_dir)
-        try:
-            import fms_acceleration  # noqa: F401  (the reference's own package)
-            import tuning.sft_trainer  # noqa: F401  (its external trainer)
-        except Exception as exc:  # pragma: no cover - depends on the box
-            reason = f"reference does not import here: {type(exc).__name__}: {exc}".replace("\n", " ")[:300]
-    if reason is None:
-        reason = "reference stack imports but its benchmark needs network access for model and dataset"
-    print(json.dumps({"impl": "reference", "unavailable": reason}))
+        probe = ("import sys; sys.path.insert(0, sys.argv[1]); "
+                 "import fms_acceleration; from fms_acceleration import AccelerationFramework; "
+                 "import fms_acceleration_peft, fms_acceleration_foak; import tuning.sft_trainer")
+        res = subprocess.run([sys.executable, "-c", probe, ref_dir], capture_output=True, text=True, cwd=ref_dir,
+                             env={k: v for k, v in os.environ.items() if k != "PYTHONPATH"})
+        if res.returncode == 0:
+            reason = ("the reference imports, but its benchmark downloads the model and the dataset from the network, "
+                      "which this machine does not have")
+        else:
+            last = [ln for ln in res.stderr.strip().splitlines() if ln.strip()]
+            reason = ("the reference's public API does not import on this image: "
+                      + (last[-1] if last else f"exit code {res.returncode}"))[:300]
+    print(json.dumps({"impl": "reference", "unavailable": reason.replace("\n", " ")}), flush=True)
     return 0
 
 
@@ -103,7 +112,18 @@ CONFIGS = {
 FOAK = {"fused_lora": True, "fast_loss": "fused_ce_liger", "fast_rms_layernorm": True, "fast_rope_embeddings": True}
 
 
-def framework_config(name: str, world: int) -> dict:
+def framework_config(name: str, world: int, impl: str = "b200") -> dict:
+    cfg = _framework_config(name, world)
+    if impl == "baseline":
+        # the comparison arm runs the library kernels: the fused-ops plugin stays out
+        def strip(d):
+            return {k: strip(v) for k, v in d.items() if k != "fused_ops_and_kernels"} if isinstance(d, dict) else d
+
+        cfg = strip(cfg)
+    return cfg
+
+
+def _framework_config(name: str, world: int) -> dict:
     if name == "mistral-qlora":
         return {"peft": {"quantization": {"bitsandbytes": {"quant_type": "nf4", "no_peft_model": False},
                                           "fused_ops_and_kernels": dict(FOAK, base_layer="bitsandbytes")}},
@@ -149,8 +169,11 @@ def make_batches(name, cfg, batch, seq, rank, world, n_batches):
     return out, seq
 
 
-def run_config(name: str, args, ctx) -> dict:
-    """Build the model through the framework's public lifecycle and time `args.steps` optimizer steps."""
+def run_config(name: str, args, ctx, impl: str = "b200") -> dict:
+    """Build the model through the framework's public lifecycle and time `args.steps` optimizer steps.
+
+    ``impl="baseline"``: the same model, data, optimizer and trainer, executed through library kernels (cuBLAS,
+    flash-attn, NCCL) and the reference's Triton kernels loaded by file path (fms_acceleration_b200/baseline)."""
     import torch
     import torch.distributed as dist
     import yaml
@@ -173,13 +196,19 @@ def run_config(name: str, args, ctx) -> dict:
     with tempfile.TemporaryDirectory() as td:
         cfg_path = os.path.join(td, "accel.yaml")
         with open(cfg_path, "w", encoding="utf-8") as fh:
-            yaml.safe_dump({"plugins": framework_config(name, world)}, fh)
+            yaml.safe_dump({"plugins": framework_config(name, world, impl)}, fh)
         AccelerationFramework.reset()
         framework = AccelerationFramework(cfg_path)
     train_args = TrainArgs(per_device_train_batch_size=batch, learning_rate=1e-4 if "lora" in metric.lower() else 2e-5,
                            bf16=dtype == torch.bfloat16, fp16=dtype == torch.float16, max_seq_length=seq,
                            padding_free=name != "mamba-cp", world_size=world,
                            parallel_mode="DISTRIBUTED" if world > 1 else "NOT_DISTRIBUTED")
+    if impl == "baseline":
+        os.environ["FMSB_ENGINE_BACKEND"] = "library"
+        os.environ["FMSB_MOE_BACKEND"] = "library"
+    else:
+        os.environ.pop("FMSB_ENGINE_BACKEND", None)
+        os.environ.pop("FMSB_MOE_BACKEND", None)
     torch.manual_seed(1234)
     if framework.requires_custom_loading:
         model = framework.model_loader(cfg, torch_dtype=dtype, device=dev)
@@ -197,7 +226,14 @@ def run_config(name: str, args, ctx) -> dict:
         from fms_acceleration_b200.parallel.engine import install_engine
 
         engine = install_engine(model, accelerator, shard_frozen=False)
-    trainer = Trainer(model, train_args, engine=engine, callbacks=callbacks)
+    runner = model
+    if impl == "baseline":
+        from fms_acceleration_b200.baseline import BaselineRunner
+
+        runner = BaselineRunner(model, gradient_checkpointing=args.baseline_checkpointing)
+    elif args.gradient_checkpointing:
+        train_args.gradient_checkpointing = True
+    trainer = Trainer(runner, train_args, engine=engine, callbacks=callbacks)
 
     n_batches = 4
     host_batches, tokens_per_step = make_batches(name, cfg, batch, seq, rank, world, n_batches)
@@ -248,7 +284,7 @@ def run_config(name: str, args, ctx) -> dict:
     value = tokens_per_step * args.steps / (ms / 1e3)
     e2e_value = tokens_per_step * args.steps / (e2e_ms / 1e3)
     par = {"mistral-qlora": f"fsdp{world}", "llama70b-gptq": f"fsdp{world}",
-           "granite-moe": f"ep{framework_config(name, world)['training']['moe']['scattermoe']['ep_degree']}"
+           "granite-moe": f"ep{_framework_config(name, world)['training']['moe']['scattermoe']['ep_degree']}"
                           f"xdp{world}" if name == "granite-moe" else "", "mamba-cp": f"cp{world}"}[name]
     line = {
         "metric": metric, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
@@ -268,22 +304,110 @@ def run_config(name: str, args, ctx) -> dict:
         "final_loss": last,
         "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30,
     }
-    if name == "granite-moe":
-        from fms_acceleration_b200.ops.moe import MoEContext
+    if impl == "baseline":
+        from fms_acceleration_b200.baseline import reference_kernels_status
 
-        need = MoEContext.max_rows_needed(dev) / float(batch * seq * cfg.num_experts_per_tok)
+        line["impl"] = "baseline"
+        line["kernels"] = reference_kernels_status()
+        line["config"]["gradient_checkpointing"] = bool(args.baseline_checkpointing)
+    else:
+        line["config"]["gradient_checkpointing"] = bool(args.gradient_checkpointing)
+    if name == "granite-moe" and impl != "baseline":
+        from fms_acceleration_b200.ops import moe as MOE
+
+        chunks = max(1, len(MOE.MoEContext._shared) and next(iter(MOE.MoEContext._shared.values())).C or 1)
+        need = MOE.MoEContext.max_rows_needed(dev) / float(-(-batch * seq // chunks) * cfg.num_experts_per_tok)
         line["config"]["moe_rows_needed_over_balanced"] = round(need, 3)
+        line["config"]["moe_chunks"] = chunks
+        line["config"]["moe_rows_dropped_events"] = MOE.overflow_count(dev, reset=True)
+        MOE.MoEContext._shared.clear()
     if name == "mistral-qlora":
         line["config"].update({"lora": "r16 a16 qkvo", "packing": "padding-free docs U[128,4096]"})
         line["vs_baseline"] = value / world / published  # published number is per device
     # release everything before another configuration is built in the same process
-    del trainer, model, dev_batches, engine, accelerator, callbacks
+    del trainer, model, runner, dev_batches, engine, accelerator, callbacks
     import gc
 
     gc.collect()
     torch.cuda.empty_cache()
     torch.cuda.reset_peak_memory_stats()
     return line
+
+
+def baseline_summary(name: str, args, ctx) -> dict:
+    """Time the library-kernel arm of one configuration in the same process and boil it down to a few fields."""
+    try:
+        full = run_config(name, args, ctx, impl="baseline")
+        return {"what": "same model, data, optimizer and trainer through cuBLAS torch.matmul, the installed flash-attn, "
+                        "NCCL and the reference's Triton kernels loaded by file path; NOT the reference's public API",
+                "value": full["value"], "unit": full["unit"], "ms_per_step": full["ms_per_step"],
+                "e2e_value": full["e2e"]["value"], "final_loss": full["final_loss"], "kernels": full.get("kernels"),
+                "gradient_checkpointing": full["config"].get("gradient_checkpointing"),
+                "peak_mem_gb": full["peak_mem_gb"], "clocks": full["clocks"]}
+    except Exception as exc:  # the product number must survive a failure of the comparison arm
+        import traceback
+
+        tb = traceback.format_exc().strip().splitlines()
+        return {"error": f"{type(exc).__name__}: {exc}"[:300], "where": tb[-3:] if len(tb) >= 3 else tb}
+
+
+def selfcheck(ctx) -> dict:
+    """A few seconds of multi-GPU correctness before anything is timed: this package's peer-memory kernels against the
+    library collectives on the same data (all-reduce; one expert-parallel mixture-of-experts layer, forward and input
+    gradient, against the all_to_all form)."""
+    import torch
+    import torch.distributed as dist
+
+    from fms_acceleration_b200 import _native as NV
+    from fms_acceleration_b200.ops import moe as MOE
+    from fms_acceleration_b200.parallel.symm import Communicator, SymmBuffer
+    from fms_acceleration_b200.plugins.moe.utils.scattermoe import ScatterMoE
+
+    rank, world, dev = ctx["rank"], ctx["world"], ctx["dev"]
+    out = {}
+    comm = Communicator()
+    n = world * 8 * 4096
+    bucket = SymmBuffer(n * 2)
+    torch.manual_seed(10 + rank)
+    x = torch.randn(n, device=dev).bfloat16()
+    bucket.view(0, n, torch.bfloat16).copy_(x)
+    comm.barrier(0)
+    comm.allreduce_(bucket, n, torch.bfloat16)
+    ref = x.float()
+    dist.all_reduce(ref)
+    out["allreduce_max_abs_err"] = float((bucket.view(0, n, torch.bfloat16).float() - ref / world).abs().max())
+    E = 8 if 8 % world == 0 else 2 * world
+    H, I_, k, T = 512, 256, 2, 1024
+    res = []
+    for backend in ("fused", "library"):
+        MOE.MoEContext._shared.clear()
+        m = ScatterMoE(H, "silu", I_, E, top_k=k, dtype=torch.bfloat16, device=dev, ep_group=dist.group.WORLD,
+                       token_budget=T)
+        m.backend = backend
+        with torch.no_grad():
+            torch.manual_seed(5)
+            m.router.weight.normal_(0, 0.05)
+            torch.manual_seed(11 + rank)
+            for w in (m.w1, m.w2, m.w3):
+                w.weight.normal_(0, 0.05)
+        torch.manual_seed(50 + rank)
+        xi = (torch.randn(T, H, device=dev) * 0.5).bfloat16().requires_grad_()
+        o, _ = m(xi)
+        o.float().square().sum().backward()
+        res.append((o.detach().float(), xi.grad.float()))
+    MOE.MoEContext._shared.clear()
+    rel = lambda a, b: float((a - b).norm() / b.norm().clamp(min=1e-9))
+    out["moe_ep_fwd_rel_err_vs_all_to_all"] = rel(res[0][0], res[1][0])
+    out["moe_ep_dx_rel_err_vs_all_to_all"] = rel(res[0][1], res[1][1])
+    NV.check_status()
+    t = torch.tensor([out["allreduce_max_abs_err"], out["moe_ep_fwd_rel_err_vs_all_to_all"],
+                      out["moe_ep_dx_rel_err_vs_all_to_all"]], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    out = {k_: float(v) for k_, v in zip(out, t.tolist())}
+    out["ok"] = bool(out["allreduce_max_abs_err"] < 0.05 and out["moe_ep_fwd_rel_err_vs_all_to_all"] < 3e-2
+                     and out["moe_ep_dx_rel_err_vs_all_to_all"] < 3e-2)
+    out["ranks"] = world
+    return out
 
 
 def main() -> int:
@@ -301,6 +425,11 @@ def main() -> int:
     ap.add_argument("--seq", type=int, default=0)
     ap.add_argument("--fp16", action="store_true")
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (result marked invalid)")
+    ap.add_argument("--no-baseline", action="store_true", help="skip the library-kernel comparison arm")
+    ap.add_argument("--baseline-checkpointing", action="store_true",
+                    help="run the comparison arm with activation checkpointing (the reference's benchmark default)")
+    ap.add_argument("--gradient-checkpointing", action="store_true", help="activation checkpointing in the product arm")
+    ap.add_argument("--no-selfcheck", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -321,9 +450,25 @@ def main() -> int:
     import fms_acceleration_b200.plugins  # registers the plugins  # noqa: F401
 
     ctx = {"rank": rank, "local_rank": local_rank, "world": world, "dev": dev}
+    check = None
+    if world > 1 and not args.no_selfcheck:
+        try:
+            check = selfcheck(ctx)
+        except Exception as exc:
+            check = {"ok": False, "error": f"{type(exc).__name__}: {exc}"[:300]}
     line = run_config(args.config, args, ctx)
-    also = args.also if args.also is not None else (["granite-moe"] if args.config == "mistral-qlora" and not args.layers
-                                                    and not args.model else [])
+    if check is not None:
+        line["selfcheck"] = check
+    with_baseline = {"mistral-qlora", "granite-moe"} if not args.no_baseline else set()
+    if args.config in with_baseline:
+        line["baseline_backend"] = baseline_summary(args.config, args, ctx)
+    if args.also is not None:
+        also = args.also
+    elif args.config == "mistral-qlora" and not args.layers and not args.model:
+        # the other benchmark configurations, so that one run records all of them (context parallelism needs ranks)
+        also = ["granite-moe", "llama70b-gptq"] + (["mamba-cp"] if world > 1 else [])
+    else:
+        also = []
     secondary = []
     for name in also:
         if name == args.config:
@@ -331,7 +476,10 @@ def main() -> int:
         sub = argparse.Namespace(**vars(args))
         sub.batch, sub.seq, sub.model = 0, 0, None
         try:
-            secondary.append(run_config(name, sub, ctx))
+            sec = run_config(name, sub, ctx)
+            if name in with_baseline:
+                sec["baseline_backend"] = baseline_summary(name, sub, ctx)
+            secondary.append(sec)
         except Exception as exc:  # the headline number must survive a failure of an extra configuration
             secondary.append({"metric": CONFIGS[name][0], "error": f"{type(exc).__name__}: {exc}"[:300]})
     if secondary:

@@ -249,7 +249,7 @@ class MoEContext:
 
     ``token_budget``: the largest number of tokens this rank may hand to one call (expert parallelism only; default
     ``FMSB_MOE_TOKEN_BUDGET`` or, failing that, the maximum over the ranks of the first call's token count).
-    ``n_chunks``: slices a call is pipelined in (``FMSB_MOE_CHUNKS``, default 2).  ``capacity_factor`` (default
+    ``n_chunks``: slices a call is pipelined in (``FMSB_MOE_CHUNKS``; default 1 on two ranks, 2 beyond).  ``capacity_factor`` (default
     ``FMSB_MOE_CAPACITY_FACTOR`` or 2.0): receive capacity of an owner in units of the balanced load."""
 
     _shared: dict = {}
@@ -266,7 +266,9 @@ class MoEContext:
         self.E_local = num_experts // self.world
         self.capacity_factor = capacity_factor
         self.token_budget = token_budget or int(os.environ.get("FMSB_MOE_TOKEN_BUDGET", "0")) or None
-        self.n_chunks = n_chunks or int(os.environ.get("FMSB_MOE_CHUNKS", "2"))
+        # measured on two B200s (Granite-3B-sized layer): with one peer the exchange is small next to the fixed cost of a
+        # second slice, so pipelining starts at four ranks
+        self.n_chunks = n_chunks or int(os.environ.get("FMSB_MOE_CHUNKS", "0")) or (1 if self.world <= 2 else 2)
         self.gemm_ctas = int(os.environ.get("FMSB_MOE_GEMM_CTAS", "0"))  # 0: every SM
         self.tag = layer_tag
         self.cap = 0  # world == 1: rows of the expert-sorted buffer (tests may lower it to provoke an overflow)
