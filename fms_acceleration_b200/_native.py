@@ -215,7 +215,5 @@ class StatusMonitor:
 
 declare("fmsb_attn_fwd", [P, L, P, L, P, L, P, L, P, P, P, I, I, I, I, F, I, P, P])
 declare("fmsb_attn_delta", [P, P, L, L, P, I, I, I, I, P])
-declare("fmsb_attn_bwd_dq2", [P, L, P, L, P, L, P, L, P, L, P, P, P, P, I, I, I, I, F, I, P, P])
-declare("fmsb_attn_bwd_dkv2", [P, L, P, L, P, L, P, L, P, L, P, L, P, P, P, P, I, I, I, I, F, I, P, P])
 declare("fmsb_attn_bwd_dq3", [P, L, P, L, P, L, P, L, P, L, P, P, P, P, I, I, I, I, F, I, P, P])
 declare("fmsb_attn_bwd_dkv3", [P, L, P, L, P, L, P, L, P, L, P, L, P, P, P, P, I, I, I, I, F, I, P, P])

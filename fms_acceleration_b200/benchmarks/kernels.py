@@ -120,17 +120,6 @@ def bench_attn(a):
     t_b = timeit(lambda: AT._bwd(q, k, v, o, lse, do, ds, de, nh, nkv, d, scale), a.iters, a.warmup, a.flush)
     NV.check_status()
     extra = {}
-    if a.compare_v1:
-        g3 = AT._bwd(q, k, v, o, lse, do, ds, de, nh, nkv, d, scale)
-        for gen in (2,):
-            AT.BWD_GENERATION = gen
-            g = AT._bwd(q, k, v, o, lse, do, ds, de, nh, nkv, d, scale)
-            extra[f"bwd_gen{gen}_ms"] = timeit(lambda: AT._bwd(q, k, v, o, lse, do, ds, de, nh, nkv, d, scale), a.iters,
-                                               a.warmup, a.flush)
-            extra[f"max_abs_diff_vs_gen{gen}"] = [float((x.float() - y.float()).abs().max()) for x, y in zip(g3, g)]
-        AT.BWD_GENERATION = 3
-        NV.check_status()
-        extra["max_abs_grad"] = [float(y.float().abs().max()) for y in g3]
     print(json.dumps({**extra, "kernel": "varlen_attention", "tokens": T, "heads": nh, "kv_heads": nkv, "head_dim": d,
                       "causal_pairs_per_head": pairs, "fwd_ms": t_f, "fwd_tflops": fl_fwd / t_f / 1e9, "bwd_ms": t_b,
                       "bwd_tflops": 2.5 * fl_fwd / t_b / 1e9}))
@@ -300,7 +289,6 @@ def main(argv=None):
             p.add_argument("--heads", type=int, default=32)
             p.add_argument("--kv-heads", type=int, default=8)
             p.add_argument("--head-dim", type=int, default=128)
-            p.add_argument("--compare-v1", action="store_true", help="also run the earlier backward generations")
         elif name == "mamba":
             p.add_argument("--tokens", type=int, default=8192)
             p.add_argument("--heads", type=int, default=80)

@@ -1,8 +1,7 @@
-// Attention backward, full-width issue order (successor of the half-tile kernels in attention_bwd.cu; same
-// interface and layouts).  Replaces the backward half of flash_attn_varlen_func as used by the reference's
+// Attention backward, full-width issue order.  Replaces the backward half of flash_attn_varlen_func as used by the reference's
 // padding-free plugin (fms_acceleration_aadp/flash_attn.py:108-199).
 //
-// What the timeline trace of the half-tile kernels showed: the single MMA-issuing thread, not the exponentials,
+// What the timeline trace of an earlier half-tile design (128x64 products) showed: the single MMA-issuing thread, not the exponentials,
 // was the critical path, because a 128x64x16 product costs almost as much issue/operand time as a 128x128x16 one.
 // Here every product is 128 wide and the element-wise work is split into two stages that each overlap a pair of
 // products:

@@ -51,10 +51,6 @@ def attention_ref(q, k, v, doc_start, scale=None):
     return torch.matmul(p, vf).transpose(0, 1).contiguous()
 
 
-# Backward kernels: 3 = full-width issue order (csrc/attention_bwd3.cu, the default), 2 = half-tile pipeline
-# (csrc/attention_bwd.cu, kept as an independent cross-check of the same mathematics).
-BWD_GENERATION = int(os.environ.get("FMSB_ATTN_BWD", "3"))
-
 # The reference asks flash-attn for a deterministic backward when FLASH_ATTENTION_DETERMINISTIC is set
 # (fms_acceleration_aadp/flash_attn.py:152).  Here the variable is accepted and changes nothing: dQ and dK/dV are
 # produced by separate kernels that each own their output rows, so no gradient is accumulated with atomics and two
@@ -89,8 +85,7 @@ def _bwd(q2, k2, v2, o, lse, dout, doc_start, doc_end, nh, nkv, d, scale, dq=Non
     if dv is None:
         dv = torch.empty(T, nkv * d, dtype=q2.dtype, device=dev)
     st = N.status_word(dev)
-    dq_fn, dkv_fn = {3: (N.lib().fmsb_attn_bwd_dq3, N.lib().fmsb_attn_bwd_dkv3),
-                     2: (N.lib().fmsb_attn_bwd_dq2, N.lib().fmsb_attn_bwd_dkv2)}[BWD_GENERATION]
+    dq_fn, dkv_fn = N.lib().fmsb_attn_bwd_dq3, N.lib().fmsb_attn_bwd_dkv3
     rc = dq_fn(q2.data_ptr(), q2.stride(0), k2.data_ptr(), k2.stride(0), v2.data_ptr(),
                                   v2.stride(0), dout.data_ptr(), dout.stride(0), dq.data_ptr(), dq.stride(0),
                                   lse.data_ptr(), delta.data_ptr(), doc_start.data_ptr(), doc_end.data_ptr(), T, nh,

@@ -39,9 +39,17 @@ def code_book(quant_type: str, device=None) -> torch.Tensor:
     return torch.tensor(vals, dtype=torch.float32, device=device)
 
 
+_CODE_BOOKS: dict = {}
+
+
 def dynamic_code_book(device=None, exponent_bits: int = 7, total_bits: int = 8) -> torch.Tensor:
     """Sorted 256-entry signed "dynamic exponent" code book used for the 8-bit block scales: decade
-    10^-(6-i) carries 2^i linearly spaced fractions between 0.1 and 1, plus the end points 0 and 1."""
+    10^-(6-i) carries 2^i linearly spaced fractions between 0.1 and 1, plus the end points 0 and 1.
+    Built once per (device, format) and shared by every quantised layer (the table is read-only)."""
+    key = (str(torch.device(device)) if device is not None else "cpu", exponent_bits, total_bits)
+    cached = _CODE_BOOKS.get(key)
+    if cached is not None:
+        return cached
     vals: list[float] = []
     value_bits = total_bits - 1
     for i in range(exponent_bits):
@@ -61,7 +69,9 @@ def dynamic_code_book(device=None, exponent_bits: int = 7, total_bits: int = 8) 
     vals += [0.0, 1.0]
     vals += [0.0] * (2 ** total_bits - len(vals))
     vals.sort()
-    return torch.tensor(vals, dtype=torch.float32, device=device)
+    book = torch.tensor(vals, dtype=torch.float32, device=device)
+    _CODE_BOOKS[key] = book
+    return book
 
 
 @dataclass

@@ -66,6 +66,81 @@ def test_gptq_solver_beats_round_to_nearest():
     assert torch.allclose(ql.dequantize().t(), lin.weight.data, atol=1e-5)
 
 
+@pytest.mark.parametrize("actorder,static_groups,group_size", [(True, False, 32), (True, True, 32), (False, True, 32),
+                                                               (False, False, -1), (True, False, -1)])
+def test_gptq_solver_options_against_the_dense_objective(actorder, static_groups, group_size):
+    """Independent oracle: the quantity GPTQ minimises is tr((W - Q) H (W - Q)^T).  Under every option the solver
+    must do better on it than rounding every weight to the nearest level of the same kind of grid, and its output
+    must lie on the grid it reports (scale, zero, g_idx reproduce it exactly)."""
+    from fms_acceleration_b200.plugins.peft.gptqmodel.quantization.quantizer import quantize
+
+    torch.manual_seed(1)
+    cin, cout = 96, 40
+    lin = torch.nn.Linear(cin, cout, bias=False)
+    x = torch.randn(1024, cin) @ (torch.randn(cin, cin) * torch.logspace(0, -1.5, cin))
+    x[:, 7] = 0  # an input feature that never fires
+    W0 = lin.weight.data.clone()
+    H = 2.0 / x.shape[0] * x.t() @ x
+    g = GPTQ(lin)
+    g.quantizer.configure(4, perchannel=True, sym=True)
+    g.add_batch(x)
+    scale, zero, g_idx, _, avg_loss = g.fasterquant(blocksize=32, percdamp=0.01, group_size=group_size,
+                                                    actorder=actorder, static_groups=static_groups)
+    Qw = lin.weight.data
+    gs = group_size if group_size > 0 else cin
+    assert scale.shape == (cout, -(-cin // gs)) and g_idx.shape == (cin,)
+    # on the reported grid
+    s_col, z_col = scale[:, g_idx.long()], zero[:, g_idx.long()]
+    assert torch.allclose(quantize(Qw, s_col, z_col, 15), Qw, atol=1e-5)
+    # better than round-to-nearest on the layer objective
+    rtn = Quantizer()
+    rtn.configure(4, perchannel=True, sym=True)
+    Wr = torch.empty_like(W0)
+    for c in range(0, cin, gs):
+        rtn.find_params(W0[:, c:c + gs], weight=True)
+        Wr[:, c:c + gs] = rtn.quantize(W0[:, c:c + gs])
+
+    def objective(Wq):
+        d = (W0 - Wq)
+        d[:, 7] = 0  # the silent feature does not enter the objective
+        return torch.trace(d @ H @ d.t()).item()
+
+    assert objective(Qw) < 0.9 * objective(Wr), (objective(Qw), objective(Wr))
+    assert avg_loss >= 0
+
+
+def test_clipping_search_matches_a_plain_loop():
+    """The vectorised search over shrink factors picks, per row, the first factor with the smallest error."""
+    from fms_acceleration_b200.plugins.peft.gptqmodel.quantization.quantizer import quantize
+
+    torch.manual_seed(2)
+    w = torch.randn(12, 50) * torch.logspace(0, 1, 12)[:, None]
+    w[3, 10] = 40.0  # an outlier that a tighter range should clip
+    for sym in (True, False):
+        qz = Quantizer()
+        qz.configure(3, perchannel=True, sym=sym, mse=True, norm=2.4, grid=50, maxshrink=0.8)
+        qz.find_params(w, weight=True)
+        plain = Quantizer()
+        plain.configure(3, perchannel=True, sym=sym)
+        plain.find_params(w, weight=True)
+        lo = torch.minimum(w.amin(1), torch.zeros(12))
+        hi = torch.maximum(w.amax(1), torch.zeros(12))
+        if sym:
+            b = torch.maximum(lo.abs(), hi)
+            lo, hi = torch.where(lo < 0, -b, lo), b
+        for r in range(12):
+            best, arg = float("inf"), None
+            for i in range(int(0.8 * 50)):
+                f = 1 - i / 50
+                sc = f * (hi[r] - lo[r]) / 7
+                zp = plain.zero[r, 0] if sym else torch.round(-f * lo[r] / sc)
+                e = (quantize(w[r], sc, zp, 7) - w[r]).abs().pow(2.4).sum().item()
+                if e < best:
+                    best, arg = e, (sc, zp)
+            assert torch.allclose(qz.scale[r, 0], arg[0], rtol=1e-5) and torch.allclose(qz.zero[r, 0], arg[1])
+        assert (qz.quantize(w) - w).abs().pow(2.4).sum() <= (plain.quantize(w) - w).abs().pow(2.4).sum() + 1e-4
+
+
 def test_v1_v2_zero_point_conversion():
     ql = QuantLinear.random(64, 32, 4, 32, torch.float32)
     model = torch.nn.Sequential(ql)
