@@ -231,7 +231,8 @@ def run_config(name: str, args, ctx, impl: str = "b200") -> dict:
         from fms_acceleration_b200.baseline import BaselineRunner
 
         runner = BaselineRunner(model, gradient_checkpointing=args.baseline_checkpointing)
-    elif args.gradient_checkpointing:
+    elif args.gradient_checkpointing or (name == "mamba-cp" and seq // world > 8192):
+        # a 65536-token sequence on 2 or 4 ranks does not fit with every layer's activations resident
         train_args.gradient_checkpointing = True
     trainer = Trainer(runner, train_args, engine=engine, callbacks=callbacks)
 
@@ -311,7 +312,9 @@ def run_config(name: str, args, ctx, impl: str = "b200") -> dict:
         line["kernels"] = reference_kernels_status()
         line["config"]["gradient_checkpointing"] = bool(args.baseline_checkpointing)
     else:
-        line["config"]["gradient_checkpointing"] = bool(args.gradient_checkpointing)
+        line["config"]["gradient_checkpointing"] = bool(train_args.gradient_checkpointing)
+        line["config"]["optimizer_state"] = "sharded over the ranks (ZeRO-1)" if getattr(
+            trainer.optimizer, "sharded_state_dict", None) else "replicated"
     if name == "granite-moe" and impl != "baseline":
         from fms_acceleration_b200.ops import moe as MOE
 
@@ -465,8 +468,9 @@ def main() -> int:
     if args.also is not None:
         also = args.also
     elif args.config == "mistral-qlora" and not args.layers and not args.model:
-        # the other benchmark configurations, so that one run records all of them (context parallelism needs ranks)
-        also = ["granite-moe", "llama70b-gptq"] + (["mamba-cp"] if world > 1 else [])
+        # the other benchmark configurations, so that one run records all of them (on one GPU the context-parallel
+        # configuration is the same 65536-token sequence without a split: the strong-scaling reference)
+        also = ["granite-moe", "llama70b-gptq", "mamba-cp"]
     else:
         also = []
     secondary = []

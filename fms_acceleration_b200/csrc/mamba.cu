@@ -376,7 +376,7 @@ __global__ void ssd_state_bwd_kernel(const float* __restrict__ dhprev_direct, co
       dS[o] = (T)d_after;
       const float e = __expf(Ltot[c * nh + h]);
       part = d_after * e * (float)hprev[o];
-      d_after = e * d_after + dhprev_direct[o];
+      d_after = e * d_after + (dhprev_direct != nullptr ? dhprev_direct[o] : 0.f);
     }
     if (uniform) {
 #pragma unroll

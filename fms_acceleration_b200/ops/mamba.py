@@ -176,9 +176,14 @@ def _slabs(nc: int, nh: int, Q: int):
     return [(c0, min(nc, c0 + step)) for c0 in range(0, nc, step)]
 
 
-def _chunk_states(x2, dt, A, B2, C2, h0, T, nh, P, G, N, Q, dtp, dev):
+def _chunk_states(x2, dt, A, B2, C2, h0, T, nh, P, G, N, Q, dtp, dev, cp=None, want_zero_start=False):
     """Decay bookkeeping and the state entering every chunk: (L, Ltot, cb, wgt, hprev, hT).  Shared by the forward
-    and, with ``recompute``, by the backward (which then keeps none of these between the two passes)."""
+    and, with ``recompute``, by the backward (which then keeps none of these between the two passes).
+
+    ``cp`` (context parallelism): once the chunk states are known, ``cp.forward`` runs the zero-start recurrence whose
+    kernel hands this slice's final state to the later ranks, and returns the state ENTERING this slice; the
+    recurrence proper then starts from it.  Two more values are returned in that case: the entering state and the
+    zero-start entering states of the chunks (``want_zero_start`` asks for the latter without any exchange)."""
     nc, hpg = T // Q, nh // G
     # within-chunk cumulative sum of dt*A, taken along the unit-stride axis of the chunk-major layout
     dtt = _chunk_major(dt, nc, Q, nh)
@@ -195,18 +200,30 @@ def _chunk_states(x2, dt, A, B2, C2, h0, T, nh, P, G, N, Q, dtp, dev):
                      d_off=(nh * P, P, 0), a_mn=True, b_mn=True, out_rows=nc * nh * P, out_cols=N,
                      out_dtype=torch.float32)
     del xw
+    hprev0 = None
+    if cp is not None:
+        hprev0 = torch.empty(nc * nh * P, N, dtype=dtp, device=dev)
+        h0 = cp.forward(S, Ltot, hprev0, nc, nh, P * N, dtp)
+    elif want_zero_start:
+        hprev0 = torch.empty(nc * nh * P, N, dtype=dtp, device=dev)
+        scratch = torch.empty(nh, P, N, dtype=torch.float32, device=dev)
+        rc = NV.lib().fmsb_ssd_state_fwd(S.data_ptr(), Ltot.data_ptr(), None, hprev0.data_ptr(), scratch.data_ptr(), nc,
+                                         nh, P * N, NV.dtype_code(dtp), NV.stream_ptr())
+        NV.check(rc, "fmsb_ssd_state_fwd")
     hprev = torch.empty(nc * nh * P, N, dtype=dtp, device=dev)
     hT = torch.empty(nh, P, N, dtype=torch.float32, device=dev)
     h0c = None if h0 is None else h0.float().contiguous()
     rc = NV.lib().fmsb_ssd_state_fwd(S.data_ptr(), Ltot.data_ptr(), NV.ptr(h0c), hprev.data_ptr(), hT.data_ptr(), nc,
                                      nh, P * N, NV.dtype_code(dtp), NV.stream_ptr())
     NV.check(rc, "fmsb_ssd_state_fwd")
+    if cp is not None or want_zero_start:
+        return L, Ltot, Lt, dtt, cb, wgt, hprev, hT, h0c, hprev0
     return L, Ltot, Lt, dtt, cb, wgt, hprev, hT
 
 
 class _SSDScan(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, dt, A, B, C, D, h0, Q, recompute):
+    def forward(ctx, x, dt, A, B, C, D, h0, Q, recompute, cp=None):
         T, nh, P = x.shape
         G, N = B.shape[1], B.shape[2]
         assert T % Q == 0, "sequence length must be a multiple of the chunk size"
@@ -217,7 +234,13 @@ class _SSDScan(torch.autograd.Function):
         x2 = _rows16(x.reshape(T, nh * P))
         B2, C2 = B.reshape(T, G * N), C.reshape(T, G * N)
         dt = dt.float().contiguous()
-        L, Ltot, Lt, dtt, cb, wgt, hprev, hT = _chunk_states(x2, dt, A, B2, C2, h0, T, nh, P, G, N, Q, dtp, dev)
+        h_in = hprev0 = None
+        if cp is not None:
+            assert h0 is None, "the entering state of a context-parallel slice comes from the earlier ranks"
+            L, Ltot, Lt, dtt, cb, wgt, hprev, hT, h_in, hprev0 = _chunk_states(x2, dt, A, B2, C2, None, T, nh, P, G, N,
+                                                                              Q, dtp, dev, cp=cp)
+        else:
+            L, Ltot, Lt, dtt, cb, wgt, hprev, hT = _chunk_states(x2, dt, A, B2, C2, h0, T, nh, P, G, N, Q, dtp, dev)
         # intra-chunk term in slabs of chunks: the [chunks, heads, Q, Q] decay-weighted matrices are transient
         y_intra = torch.empty(T, nh * P, dtype=torch.float32, device=dev)
         for c0, c1 in _slabs(nc, nh, Q):
@@ -238,17 +261,22 @@ class _SSDScan(torch.autograd.Function):
                                            NV.stream_ptr())
         NV.check(rc, "fmsb_ssd_fwd_combine")
         if recompute:
-            # keep the inputs only; the backward rebuilds the bookkeeping and the entering states
-            ctx.save_for_backward(x, dt, A, B, C, D, h0)
+            # keep the inputs only; the backward rebuilds the bookkeeping and the entering states (under context
+            # parallelism from the entering state received in the forward: nothing is exchanged a second time)
+            ctx.save_for_backward(x, dt, A, B, C, D, h_in if cp is not None else h0)
+        elif cp is not None:
+            ctx.save_for_backward(x, dt, A, B, C, D, L, Ltot, cb, hprev, wgt, hprev0)
         else:
             ctx.save_for_backward(x, dt, A, B, C, D, L, Ltot, cb, hprev, wgt)
         ctx.meta = (Q, h0 is not None, recompute)
+        ctx.cp = cp
         return y, hT
 
     @staticmethod
     def backward(ctx, dy, dhT):
         Q, has_h0, recompute = ctx.meta
-        x, dt, A, B, C, D = ctx.saved_tensors[:6]
+        saved = ctx.saved_tensors  # read once: activation checkpointing allows a single unpack
+        x, dt, A, B, C, D = saved[:6]
         T, nh, P = x.shape
         G, N = B.shape[1], B.shape[2]
         nc, hpg = T // Q, nh // G
@@ -257,11 +285,19 @@ class _SSDScan(torch.autograd.Function):
         x2 = _rows16(x.reshape(T, nh * P))
         B2, C2 = B.reshape(T, G * N), C.reshape(T, G * N)
         dy2 = _rows16(dy.reshape(T, nh * P))
-        if recompute:
-            L, Ltot, Lt, dtt, cb, wgt, hprev, _ = _chunk_states(x2, dt, A, B2, C2, ctx.saved_tensors[6], T, nh, P, G, N,
+        cp = ctx.cp
+        hprev0 = None
+        if recompute and cp is not None:
+            L, Ltot, Lt, dtt, cb, wgt, hprev, _, _, hprev0 = _chunk_states(x2, dt, A, B2, C2, saved[6], T, nh,
+                                                                         P, G, N, Q, dtp, dev, want_zero_start=True)
+        elif recompute:
+            L, Ltot, Lt, dtt, cb, wgt, hprev, _ = _chunk_states(x2, dt, A, B2, C2, saved[6], T, nh, P, G, N,
                                                                 Q, dtp, dev)
         else:
-            L, Ltot, cb, hprev, wgt = ctx.saved_tensors[6:]
+            if cp is not None:
+                L, Ltot, cb, hprev, wgt, hprev0 = saved[6:]
+            else:
+                L, Ltot, cb, hprev, wgt = saved[6:]
             Lt, dtt = _chunk_major(L, nc, Q, nh), _chunk_major(dt, nc, Q, nh)
         # ---- inter-chunk term  y += exp(L) * (C . Hprev)
         dyi = _rowscale(dy2, torch.exp(L), nh, P)
@@ -279,7 +315,7 @@ class _SSDScan(torch.autograd.Function):
         del dyi
         # ---- recurrence backward
         dS16 = torch.empty(nc * nh * P, N, dtype=dtp, device=dev)
-        dh0 = torch.empty(nh, P, N, dtype=torch.float32, device=dev) if has_h0 else None
+        dh0 = torch.empty(nh, P, N, dtype=torch.float32, device=dev) if (has_h0 or cp is not None) else None
         dLtot = torch.zeros(nc, nh, dtype=torch.float32, device=dev)
         dhTc = None if dhT is None else dhT.float().contiguous()
         rc = NV.lib().fmsb_ssd_state_bwd(dhp.data_ptr(), NV.ptr(dhTc), Ltot.data_ptr(), hprev.data_ptr(),
@@ -287,6 +323,19 @@ class _SSDScan(torch.autograd.Function):
                                          NV.stream_ptr())
         NV.check(rc, "fmsb_ssd_state_bwd")
         del dhp
+        if cp is not None:
+            # dh0 is the gradient of the state that ENTERED this slice: it belongs to the final states and decays of
+            # the earlier ranks.  In return the later ranks send the gradient of THIS slice's zero-start final state
+            # and total log-decay; it runs back through the zero-start recurrence (same decays, zero-start states).
+            dF, dlogP = cp.backward(dh0, nh, P * N)
+            dS16b = torch.empty_like(dS16)
+            rc = NV.lib().fmsb_ssd_state_bwd(None, dF.data_ptr(), Ltot.data_ptr(), hprev0.data_ptr(), dS16b.data_ptr(),
+                                             None, dLtot.data_ptr(), nc, nh, P * N, code, NV.stream_ptr())
+            NV.check(rc, "fmsb_ssd_state_bwd")
+            dS16 += dS16b
+            del dS16b
+            dLtot += dlogP[None, :]
+            dh0 = None
         # ---- chunk state  S = (x w)^T B
         xw = _rowscale(x2, wgt, nh, P)
         # dXw[c,h] [Q, P] = B[c] [Q, N] . dS[c,h]^T
@@ -350,7 +399,7 @@ class _SSDScan(torch.autograd.Function):
         ddt = ddt + da * A.float()[None, :]
         dA = (da * dt).sum(0)
         return (dx, ddt.to(dt.dtype), dA.to(A.dtype), dB.view(T, G, N).to(B.dtype), dC.view(T, G, N).to(C.dtype),
-                dD.to(D.dtype), dh0, None, None)
+                dD.to(D.dtype), dh0, None, None, None)
 
 
 class _StateCorrection(torch.autograd.Function):
@@ -434,11 +483,11 @@ def state_correction(y0, h_in, dt, A, C, chunk_size=256):
     return _StateCorrection.apply(y0, h_in, dt, A, C, chunk_size)
 
 
-def ssd_scan(x, dt, A, B, C, D, h0=None, chunk_size=256, recompute=False):
+def ssd_scan(x, dt, A, B, C, D, h0=None, chunk_size=256, recompute=False, cp=None):
     """Chunked SSD scan.  Returns ``(y [T, nh, P], final_state [nh, P, N] fp32)``.  ``recompute``: keep only the
     inputs for the backward, which rebuilds the per-chunk entering states (the ``mamba_recompute`` switch of the
     context-parallel plugin, fms_acceleration_mcp/framework_plugin_mcp.py:37-44)."""
     if not x.is_cuda:
         y, h = ssd_ref(x, dt, A, B, C, D, h0)
         return y.to(x.dtype), h.float()
-    return _SSDScan.apply(x, dt, A, B, C, D, h0, chunk_size, bool(recompute))
+    return _SSDScan.apply(x, dt, A, B, C, D, h0, chunk_size, bool(recompute), cp)

@@ -1,13 +1,16 @@
 """Context parallelism for Mamba2: one sequence is split into contiguous slices over the ranks of a group.
 
-The SSD recurrence is linear in the state, so rank ``r`` can scan its slice with a zero initial state and only needs
-the state that ENTERS its slice, ``H_in(r) = sum_{j<r} (prod_{j<i<r} P_i) F_j``, where ``F_j`` is rank ``j``'s
-zero-initial-state final state and ``P_j = exp(sum of dt*A over slice j)`` its total decay.  Every rank writes its
-``(F, P)`` pair straight into a slot of every LATER rank's symmetric buffer (peer stores, ``csrc/cp.cu``) and
-release-flags it; the receivers combine the prefix locally and run the inter-chunk pass with ``h0 = H_in``.
-This is the "allgather" flavour the reference defaults to (fms_acceleration_mcp/framework_plugin_mcp.py:29-44); the
-backward pass mirrors it right-to-left with the gradient of the entering state.  The conv1d halo (last
-``d_conv - 1`` rows of the previous slice) travels the same way.
+The SSD recurrence is linear in the state, so the state that ENTERS rank ``r``'s slice is
+``H_in(r) = sum_{j<r} (prod_{j<i<r} P_i) F_j``, where ``F_j`` is rank ``j``'s zero-start final state and
+``P_j = exp(sum of dt*A over slice j)`` its total decay.  Inside the scan, once the chunk states of the slice are known,
+the kernel of the zero-start inter-chunk recurrence stores ``(F, log P)`` straight into a slot of every LATER rank's
+symmetric buffer (peer stores from the threads that computed them, release flag by the last CTA: ``csrc/cp.cu``); a
+second kernel waits (bounded) for the earlier ranks' flags and combines the prefix on the device; the recurrence
+proper then starts from ``H_in``, so the outputs need no correction pass.  This is the "allgather" flavour the
+reference defaults to (fms_acceleration_mcp/framework_plugin_mcp.py:29-44).  The backward mirrors it right to left:
+``dH_in`` becomes ``dF_j`` / ``dlog P_j`` for the earlier ranks (one kernel, pushed), and what the later ranks send runs
+back through the zero-start recurrence.  The conv1d halo (last ``d_conv - 1`` rows of the previous slice) and the
+label that the last position predicts go to the neighbour only.
 """
 from __future__ import annotations
 
@@ -21,8 +24,12 @@ from .. import _native as NV
 from ..ops import mamba as MB
 
 P_, I_, L_, U_ = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_uint
-NV.declare("fmsb_cp_push", [P_, L_, P_, P_, L_, I_, I_, I_, I_, U_, P_, P_])
+NV.declare("fmsb_cp_push", [P_, L_, P_, P_, L_, I_, I_, I_, I_, U_, I_, P_, P_])
 NV.declare("fmsb_cp_wait", [P_, I_, I_, I_, I_, I_, U_, P_, P_])
+NV.declare("fmsb_cp_state_push", [P_, P_, P_, I_, I_, I_, P_, L_, P_, I_, I_, U_, P_, I_, P_])
+NV.declare("fmsb_cp_prefix_fwd", [P_, L_, P_, I_, U_, I_, I_, P_, P_, P_])
+NV.declare("fmsb_cp_prefix_bwd", [P_, P_, L_, P_, P_, I_, I_, U_, I_, I_, P_, P_])
+NV.declare("fmsb_cp_sum_bwd", [P_, L_, P_, I_, I_, U_, I_, I_, P_, P_, P_, P_])
 
 CH_STATE_F, CH_STATE_B, CH_HALO_F, CH_HALO_B = 20, 21, 22, 23
 
@@ -55,11 +62,13 @@ class ContextParallel:
         self.impl, self.recompute = impl, recompute
         self.comm = Communicator(self.group, self.device)
         self._slots = {}
+        self._counter = torch.zeros(4, dtype=torch.int32, device=self.device)  # "last CTA" counters of the fused kernels
+        self._hooks = {}
 
     # ------------------------------------------------------------------ primitive: push to later / earlier ranks
-    def _exchange(self, payload: torch.Tensor, chan: int, direction: int, tag=None) -> torch.Tensor:
-        """Send ``payload`` (contiguous) to every rank after (direction=+1) or before (-1) this one; returns the
-        received slots as ``[world, numel]`` (only the slots of the sending side are meaningful)."""
+    def _exchange(self, payload: torch.Tensor, chan: int, direction: int, tag=None, span: int = 0) -> torch.Tensor:
+        """Send ``payload`` (contiguous) to the ``span`` ranks after (direction=+1) or before (-1) this one (0: all of
+        them); returns the received slots as ``[world, numel]`` (only the slots of the sending side are meaningful)."""
         nbytes = payload.numel() * payload.element_size()
         # one slot set per (channel, layer): an earlier rank may run several layers ahead of a later one, so a
         # slot is never reused before the step's backward (which needs the later ranks) has drained it
@@ -71,10 +80,10 @@ class ContextParallel:
         st = NV.status_word(self.device)
         sig = self.comm.signals.ptr_array(chan * self.world * 4)
         rc = NV.lib().fmsb_cp_push(payload.data_ptr(), nbytes, slots.buf.ptr_array(), sig, slots.slot_bytes, self.rank,
-                                   self.world, direction, 0, epoch, st.data_ptr(), NV.stream_ptr())
+                                   self.world, direction, 0, epoch, span, st.data_ptr(), NV.stream_ptr())
         NV.check(rc, "fmsb_cp_push")
         rc = NV.lib().fmsb_cp_wait(self.comm.signals.ptrs[self.rank] + chan * self.world * 4, self.rank, self.world,
-                                   direction, 0, 0, epoch, st.data_ptr(), NV.stream_ptr())
+                                   direction, span, 0, epoch, st.data_ptr(), NV.stream_ptr())
         NV.check(rc, "fmsb_cp_wait")
         numel = payload.numel()
         view = slots.buf.local.view(self.world, slots.slot_bytes)[:, :nbytes].view(payload.dtype).view(self.world, numel)
@@ -87,19 +96,17 @@ class ContextParallel:
     # ------------------------------------------------------------------ scan
     def scan(self, x, dt, A, B, C, D, Q, layer=None):
         """Context-parallel SSD scan of this rank's slice; returns y."""
-        nh = x.shape[1]
-        # pass 1: zero-initial-state scan gives the slice's final state F and total decay P
-        y0, F_local = MB.ssd_scan(x, dt, A, B, C, D, None, Q, recompute=self.recompute)
-        logP = (dt.float() * A.float()[None, :]).sum(0)                       # [nh]
-        h_in = _StateExchange.apply(F_local, logP, self, layer)
-        # the entering state only adds  exp(L_global(t)) * C_t . H_in  to every output row of the slice
-        return MB.state_correction(y0, h_in, dt, A, C, Q)
+        hook = self._hooks.get(layer)
+        if hook is None:
+            hook = self._hooks[layer] = StateHandoff(self, layer)
+        y, _ = MB.ssd_scan(x, dt, A, B, C, D, None, Q, recompute=self.recompute, cp=hook)
+        return y
 
     # ------------------------------------------------------------------ loss helpers
     def shift_labels(self, flat_labels: torch.Tensor) -> torch.Tensor:
         """Next-token targets for this slice: the last position takes the first label of the NEXT rank's slice."""
         first = flat_labels[:1].contiguous()
-        recv = self._exchange(first, CH_HALO_B, -1)                           # from later ranks, slot = sender
+        recv = self._exchange(first, CH_HALO_B, -1, span=1)                   # from the next rank, slot = sender
         nxt = recv[self.rank + 1] if self.rank + 1 < self.world else torch.full_like(first, -100)
         return torch.cat([flat_labels[1:], nxt.to(flat_labels.dtype)])
 
@@ -110,7 +117,7 @@ class ContextParallel:
 
 
 def prefix_state(Fs: torch.Tensor, lPs: torch.Tensor, r: int) -> torch.Tensor:
-    """State entering rank ``r``'s slice from the zero-initial-state final states ``Fs [>=r, nh, P, N]`` and the log
+    """PyTorch statement of the device-side prefix combine (``cp_prefix_fwd_kernel``): state entering rank ``r``'s slice from the zero-initial-state final states ``Fs [>=r, nh, P, N]`` and the log
     total decays ``lPs [>=r, nh]`` of the earlier ranks: left to right, ``H <- exp(lP_j) H + F_j``."""
     h = torch.zeros_like(Fs[0], dtype=torch.float32)
     for j in range(r):
@@ -119,7 +126,7 @@ def prefix_state(Fs: torch.Tensor, lPs: torch.Tensor, r: int) -> torch.Tensor:
 
 
 def prefix_state_grads(dh: torch.Tensor, Fs: torch.Tensor, lPs: torch.Tensor, r: int, world: int):
-    """Gradients of :func:`prefix_state` with respect to every earlier rank's ``F_j`` and ``lP_j``:
+    """PyTorch statement of ``cp_prefix_bwd_push_kernel``: gradients of :func:`prefix_state` with respect to every earlier rank's ``F_j`` and ``lP_j``:
     ``(dF [world, nh, P, N], dlP [world, nh])``, rows ``>= r`` zero."""
     nh = dh.shape[0]
     dF = torch.zeros(world, *dh.shape, dtype=torch.float32, device=dh.device)
@@ -136,43 +143,66 @@ def prefix_state_grads(dh: torch.Tensor, Fs: torch.Tensor, lPs: torch.Tensor, r:
     return dF, dlP
 
 
-class _StateExchange(torch.autograd.Function):
-    """(F [nh,P,N], logP [nh]) of every rank -> the state entering this rank's slice."""
+class StateHandoff:
+    """The hook the chunked scan calls (``ops/mamba.py``): ``forward`` hands this slice's zero-start final state to the
+    later ranks from inside the state kernel and returns the state entering the slice; ``backward`` turns the gradient
+    of the entering state into the earlier ranks' shares and returns what the later ranks sent for this slice.  One
+    set of slots per layer: an early rank may run several layers ahead of a late one."""
 
-    @staticmethod
-    def forward(ctx, F_local, logP, cp: ContextParallel, layer):
-        nh = logP.shape[0]
-        payload = torch.cat([F_local.reshape(-1).float(), logP.float()]).contiguous()
-        recv = cp._exchange(payload, CH_STATE_F, +1, layer)
-        ctx.layer = layer
-        n = F_local.numel()
-        Fs = recv[:, :n].view(cp.world, *F_local.shape)
-        lPs = recv[:, n:].view(cp.world, nh)
-        h = prefix_state(Fs, lPs, cp.rank) if cp.rank > 0 else torch.zeros_like(F_local, dtype=torch.float32)
-        ctx.cp = cp
-        ctx.save_for_backward(Fs[: cp.rank].clone(), lPs[: cp.rank].clone())
-        return h
+    def __init__(self, cp: ContextParallel, layer):
+        self.cp, self.layer = cp, layer
+        self.fwd = self.bwd = None
+        self.slot_elems = 0
 
-    @staticmethod
-    def backward(ctx, dh):
-        cp = ctx.cp
-        Fs, lPs = ctx.saved_tensors
-        r, nh = cp.rank, dh.shape[0]
-        # local chain: H_r = sum_{j<r} (prod_{j<i<r} P_i) F_j ; gradients w.r.t. the F_j / logP_j of EARLIER ranks
-        dF, dlP = prefix_state_grads(dh, Fs, lPs, r, cp.world)
-        # send each earlier rank its share; collect what later ranks computed for THIS rank
-        n = dh.numel()
-        mine_F = torch.zeros_like(dh, dtype=torch.float32)
-        mine_lP = torch.zeros(nh, dtype=torch.float32, device=dh.device)
-        payload = torch.cat([dF.reshape(cp.world, -1), dlP], 1).contiguous()  # [world, n + nh], row j is for rank j
-        recv = _exchange_rows(cp, payload, CH_STATE_B, -1, ctx.layer)         # [world(sender), n + nh]
-        for s in range(r + 1, cp.world):
-            mine_F += recv[s, :n].view_as(dh)
-            mine_lP += recv[s, n:]
-        return mine_F, mine_lP, None, None
+    def _ensure(self, nh: int, PN: int):
+        from .symm import SymmBuffer
+
+        if self.fwd is None:
+            cp = self.cp
+            self.slot_elems = (nh * PN + nh + 63) // 64 * 64
+            nbytes = cp.world * self.slot_elems * 4
+            self.fwd = SymmBuffer(nbytes, cp.group, cp.device)
+            self.bwd = SymmBuffer(nbytes, cp.group, cp.device)
+
+    def forward(self, S, Ltot, hprev0, nc, nh, PN, dtp):
+        cp = self.cp
+        self._ensure(nh, PN)
+        st = NV.status_word(cp.device)
+        epoch = cp.comm.next_epoch(CH_STATE_F)
+        sig_off = CH_STATE_F * cp.world * 4
+        rc = NV.lib().fmsb_cp_state_push(S.data_ptr(), Ltot.data_ptr(), hprev0.data_ptr(), nc, nh, PN,
+                                         self.fwd.ptr_array(), self.slot_elems, cp.comm.signals.ptr_array(sig_off),
+                                         cp.rank, cp.world, epoch, cp._counter.data_ptr(), NV.dtype_code(dtp),
+                                         NV.stream_ptr())
+        NV.check(rc, "fmsb_cp_state_push")
+        h_in = torch.empty(nh, PN, dtype=torch.float32, device=cp.device)
+        rc = NV.lib().fmsb_cp_prefix_fwd(self.fwd.local.data_ptr(), self.slot_elems,
+                                         cp.comm.signals.ptrs[cp.rank] + sig_off, cp.rank, epoch, nh, PN,
+                                         h_in.data_ptr(), st.data_ptr(), NV.stream_ptr())
+        NV.check(rc, "fmsb_cp_prefix_fwd")
+        return h_in
+
+    def backward(self, dh_in, nh: int, PN: int):
+        cp = self.cp
+        st = NV.status_word(cp.device)
+        epoch = cp.comm.next_epoch(CH_STATE_B)
+        sig_off = CH_STATE_B * cp.world * 4
+        dh = dh_in.float().contiguous()
+        rc = NV.lib().fmsb_cp_prefix_bwd(dh.data_ptr(), self.fwd.local.data_ptr(), self.slot_elems, self.bwd.ptr_array(),
+                                         cp.comm.signals.ptr_array(sig_off), cp.rank, cp.world, epoch, nh, PN,
+                                         cp._counter[1:].data_ptr(), NV.stream_ptr())
+        NV.check(rc, "fmsb_cp_prefix_bwd")
+        dF = torch.empty(nh, PN, dtype=torch.float32, device=cp.device)
+        dlogP = torch.empty(nh, dtype=torch.float32, device=cp.device)
+        rc = NV.lib().fmsb_cp_sum_bwd(self.bwd.local.data_ptr(), self.slot_elems,
+                                      cp.comm.signals.ptrs[cp.rank] + sig_off, cp.rank, cp.world, epoch, nh, PN,
+                                      dF.data_ptr(), dlogP.data_ptr(), st.data_ptr(), NV.stream_ptr())
+        NV.check(rc, "fmsb_cp_sum_bwd")
+        return dF, dlogP
 
 
-def _exchange_rows(cp: ContextParallel, payload: torch.Tensor, chan: int, direction: int, tag=None) -> torch.Tensor:
+def _exchange_rows(cp: ContextParallel, payload: torch.Tensor, chan: int, direction: int, tag=None,
+                   span: int = 0) -> torch.Tensor:
     """Row ``j`` of ``payload`` is delivered to rank ``j`` (only ranks on the ``direction`` side are served); returns
     ``[world (sender), row]``."""
     world, row = payload.shape
@@ -185,10 +215,10 @@ def _exchange_rows(cp: ContextParallel, payload: torch.Tensor, chan: int, direct
     st = NV.status_word(cp.device)
     sig = cp.comm.signals.ptr_array(chan * cp.world * 4)
     rc = NV.lib().fmsb_cp_push(payload.data_ptr(), nbytes, slots.buf.ptr_array(), sig, slots.slot_bytes, cp.rank, cp.world,
-                               direction, 1, epoch, st.data_ptr(), NV.stream_ptr())
+                               direction, 1, epoch, span, st.data_ptr(), NV.stream_ptr())
     NV.check(rc, "fmsb_cp_push")
-    rc = NV.lib().fmsb_cp_wait(cp.comm.signals.ptrs[cp.rank] + chan * cp.world * 4, cp.rank, cp.world, direction, 0, 0,
-                               epoch, st.data_ptr(), NV.stream_ptr())
+    rc = NV.lib().fmsb_cp_wait(cp.comm.signals.ptrs[cp.rank] + chan * cp.world * 4, cp.rank, cp.world, direction, span,
+                               0, epoch, st.data_ptr(), NV.stream_ptr())
     NV.check(rc, "fmsb_cp_wait")
     return slots.buf.local.view(cp.world, slots.slot_bytes)[:, :nbytes].view(payload.dtype).view(cp.world, row)
 
@@ -199,7 +229,7 @@ class _HaloExchange(torch.autograd.Function):
     @staticmethod
     def forward(ctx, xBC, cp: ContextParallel, k: int, layer):
         tail = xBC[-k:].contiguous()
-        recv = cp._exchange(tail.reshape(-1), CH_HALO_F, +1, layer)
+        recv = cp._exchange(tail.reshape(-1), CH_HALO_F, +1, layer, span=1)
         ctx.cp, ctx.k, ctx.shape, ctx.layer = cp, k, xBC.shape, layer
         if cp.rank == 0:
             return torch.zeros_like(tail)
@@ -212,7 +242,7 @@ class _HaloExchange(torch.autograd.Function):
         payload = torch.zeros(cp.world, dhalo.numel(), dtype=dhalo.dtype, device=dhalo.device)
         if cp.rank > 0:
             payload[cp.rank - 1] = dhalo.reshape(-1)
-        recv = _exchange_rows(cp, payload.contiguous(), CH_HALO_B + 4, -1, ctx.layer)
+        recv = _exchange_rows(cp, payload.contiguous(), CH_HALO_B + 4, -1, ctx.layer, span=1)
         dx = torch.zeros(ctx.shape, dtype=dhalo.dtype, device=dhalo.device)
         if cp.rank + 1 < cp.world:
             dx[-k:] = recv[cp.rank + 1].view(k, -1)

@@ -604,5 +604,11 @@ def install_engine(model: nn.Module, accelerator, **kwargs) -> Optional[ShardedE
         return None
     if os.environ.get("FMSB_SHARD_FROZEN", "1") == "0":
         kwargs["shard_frozen"] = False  # keep the frozen weights replicated (memory for less traffic)
+    if "shard_optimizer" not in kwargs:
+        # a full fine-tune: every rank would hold 12 bytes of AdamW state per replicated parameter; shard them over the
+        # ranks (reduce-scatter during backward, step on 1/world, all-gather), as FSDP does for the reference.  Adapter
+        # runs keep the replicated optimizer: their state is a few hundred MB and the all-gather would not pay.
+        full_ft = not any("lora_" in n for n, p in model.named_parameters() if p.requires_grad)
+        kwargs["shard_optimizer"] = full_ft and os.environ.get("FMSB_ZERO1", "1") != "0"
     accelerator.engine = ShardedEngine(model, **kwargs)
     return accelerator.engine

@@ -142,3 +142,75 @@ def test_state_correction_matches_einsum():
     assert _rel(y, yr) < 1e-2
     for n, t, r in zip(["y0", "h_in", "dt", "A", "C"], (y0, h_in, dt, A, C), ins):
         assert _rel(t.grad, r.grad) < 3e-2, (n, _rel(t.grad, r.grad))
+
+
+def test_context_parallel_handoff_kernels_against_the_prefix_formulas():
+    """The fused hand-off kernels on ONE GPU with three emulated ranks whose "peer" buffers are plain local tensors.
+    Launches run one after the other in rank order, so every flag a kernel waits for was written by a kernel that has
+    already finished (nothing here waits on a concurrently running kernel).  Forward: the zero-start recurrence with
+    the push, then the prefix combine, against ``prefix_state``; backward: ``prefix_state_grads`` and the sums."""
+    import ctypes
+
+    from fms_acceleration_b200.parallel import context_parallel as CP
+
+    world, nc, nh, PN = 3, 5, 4, 96
+    dev = DEV
+    torch.manual_seed(0)
+    slot_elems = (nh * PN + nh + 63) // 64 * 64
+    fwd = [torch.zeros(world * slot_elems, device=dev) for _ in range(world)]
+    bwd = [torch.zeros(world * slot_elems, device=dev) for _ in range(world)]
+    sig = [torch.zeros(2 * world, dtype=torch.int32, device=dev) for _ in range(world)]
+    counter = torch.zeros(4, dtype=torch.int32, device=dev)
+    st = NV.status_word(dev)
+
+    def ptrs(ts, off_bytes=0):
+        return (ctypes.c_void_p * world)(*[t.data_ptr() + off_bytes for t in ts])
+
+    S = [torch.randn(nc, nh, PN, device=dev) for _ in range(world)]
+    Ltot = [-torch.rand(nc, nh, device=dev) for _ in range(world)]
+    F, lP = [], []
+    for r in range(world):
+        hprev0 = torch.empty(nc, nh, PN, dtype=torch.bfloat16, device=dev)
+        rc = NV.lib().fmsb_cp_state_push(S[r].data_ptr(), Ltot[r].data_ptr(), hprev0.data_ptr(), nc, nh, PN, ptrs(fwd),
+                                         slot_elems, ptrs(sig), r, world, 1, counter.data_ptr(), 1, NV.stream_ptr())
+        assert rc == 0
+        f = torch.zeros(nh, PN, device=dev)
+        for c in range(nc):
+            assert torch.allclose(hprev0[c].float(), f, atol=2e-2, rtol=2e-2)
+            f = torch.exp(Ltot[r][c])[:, None] * f + S[r][c]
+        F.append(f)
+        lP.append(Ltot[r].sum(0))
+    torch.cuda.synchronize()
+    assert int(counter[0]) == 0  # the last CTA reset it
+    Fs, lPs = torch.stack(F), torch.stack(lP)
+    h_in = []
+    for r in range(world):
+        h = torch.empty(nh, PN, device=dev)
+        rc = NV.lib().fmsb_cp_prefix_fwd(fwd[r].data_ptr(), slot_elems, sig[r].data_ptr(), r, 1, nh, PN, h.data_ptr(),
+                                         st.data_ptr(), NV.stream_ptr())
+        assert rc == 0
+        want = CP.prefix_state(Fs.view(world, nh, PN, 1), lPs, r).view(nh, PN) if r else torch.zeros(nh, PN, device=dev)
+        assert torch.allclose(h, want, atol=1e-4, rtol=1e-4), r
+        h_in.append(h)
+    # backward: every rank turns dH_in into the shares of the earlier ranks (later ranks first, as in a real step)
+    dh = [torch.randn(nh, PN, device=dev) for _ in range(world)]
+    want_dF = torch.zeros(world, nh, PN, device=dev)
+    want_dlP = torch.zeros(world, nh, device=dev)
+    for r in reversed(range(world)):
+        rc = NV.lib().fmsb_cp_prefix_bwd(dh[r].data_ptr(), fwd[r].data_ptr(), slot_elems, ptrs(bwd),
+                                         ptrs(sig, world * 4), r, world, 1, nh, PN, counter[1:].data_ptr(),
+                                         NV.stream_ptr())
+        assert rc == 0
+        if r:
+            dF, dlP = CP.prefix_state_grads(dh[r].view(nh, PN, 1), Fs[:r].view(r, nh, PN, 1), lPs[:r], r, world)
+            want_dF += dF.view(world, nh, PN)
+            want_dlP += dlP
+    for r in range(world):
+        dF = torch.empty(nh, PN, device=dev)
+        dlP = torch.empty(nh, device=dev)
+        rc = NV.lib().fmsb_cp_sum_bwd(bwd[r].data_ptr(), slot_elems, sig[r].data_ptr() + world * 4, r, world, 1, nh, PN,
+                                      dF.data_ptr(), dlP.data_ptr(), st.data_ptr(), NV.stream_ptr())
+        assert rc == 0
+        assert torch.allclose(dF, want_dF[r], atol=1e-4, rtol=1e-4), r
+        assert torch.allclose(dlP, want_dlP[r], atol=1e-3, rtol=1e-3), r
+    NV.check_status()
