@@ -3,6 +3,8 @@
     python -m fms_acceleration_b200.benchmarks.kernels gemm --m 16384 --n 4096 --k 4096
     python -m fms_acceleration_b200.benchmarks.kernels attn --batch 4 --seq 4096
     python -m fms_acceleration_b200.benchmarks.kernels elementwise
+    python -m fms_acceleration_b200.benchmarks.kernels grouped      # the grouped GEMMs of one MoE layer
+    python -m fms_acceleration_b200.benchmarks.kernels reference    # beside the reference's Triton kernels / flash-attn
 
 Every number is taken after warm-up, with a synchronise on both sides, on inputs larger than the 126 MB L2 (or
 with an L2 flush between iterations: ``--flush``).  ``--iters 1 --warmup 0`` gives a run suitable for profiling
@@ -86,6 +88,13 @@ def bench_gemm(a):
     NV.declare("fmsb_gemm_pair_occupancy", [])
     res["pair_occupancy"] = int(NV.lib().fmsb_gemm_pair_occupancy())
     if a.both:
+        from fms_acceleration_b200.ops.gemm import set_pair_store
+
+        old_store = set_pair_store(0)
+        t0 = timeit(lambda: gemm(x, wt, b_mn=b_mn, out=out), a.iters, a.warmup, a.flush)
+        set_pair_store(old_store)
+        res["pair_direct_store_ms"] = t0
+        res["pair_direct_store_tflops"] = fl / t0 / 1e9
         set_pair_mode(0)
         t1 = timeit(lambda: gemm(x, wt, b_mn=b_mn, out=out), a.iters, a.warmup, a.flush)
         res["single_cta_ms"] = t1
@@ -177,6 +186,167 @@ def bench_elementwise(a):
     print(json.dumps({"kernel": "swiglu_fwd", "ms": t, "gbs": by / t / 1e6, "frac_of_%s_hbm" % pk["source"]: by / t / 1e6 / pk["hbm_gbs"]}))
 
 
+def bench_grouped(a):
+    """The grouped tcgen05 GEMMs of one Granite-3B-A800M expert layer (40 experts, top-8, hidden 1536, inter 512) on the
+    expert-sorted layout: gate|up in one pass, down projection, the two weight-gradient products, the input gradient."""
+    from fms_acceleration_b200 import _native as NV
+    from fms_acceleration_b200.ops import moe as MOE
+
+    T, H, I_, E, k = a.tokens, a.hidden, a.inter, a.experts, a.top_k
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev).manual_seed(0)
+    idx = torch.rand(T, E, device=dev, generator=g).topk(k, dim=-1).indices.int().contiguous()
+    ctx = MOE.MoEContext(H, I_, E, k)
+    cap = ctx.cap = (T * k + E * 128 + 127) // 128 * 128
+    seg_off, seg_cnt, dest_row = MOE._plan(ctx, idx, T, dev)
+    Xs = torch.randn(cap, H, device=dev, dtype=torch.bfloat16)
+    w1, w3 = (torch.randn(E, H, I_, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(2))
+    w2 = torch.randn(E, I_, H, device=dev, dtype=torch.bfloat16) * 0.02
+    gu = torch.empty(cap, 2 * I_, device=dev, dtype=torch.bfloat16)
+    hs = torch.randn(cap, I_, device=dev, dtype=torch.bfloat16)
+    dY = torch.randn(cap, H, device=dev, dtype=torch.bfloat16)
+    rows = T * k
+    runs = [
+        ("gate|up  [rows,H]x[H,2I] (one pass over A)", 2.0 * rows * H * 2 * I_,
+         lambda: MOE.grouped_gemm(Xs, w1.view(E * H, I_), seg_off, E, mode=1, n=2 * I_, b_alt=w3.view(E * H, I_), out=gu)),
+        ("down     [rows,I]x[I,H]", 2.0 * rows * I_ * H,
+         lambda: MOE.grouped_gemm(hs, w2.view(E * I_, H), seg_off, E, mode=1, n=H)),
+        ("dW gate|up  [H,rows]x[rows,2I] per expert", 2.0 * rows * H * 2 * I_,
+         lambda: MOE.grouped_gemm(Xs, gu, seg_off, E, mode=2, m=H, n=2 * I_)),
+        ("dW down  [I,rows]x[rows,H] per expert", 2.0 * rows * I_ * H,
+         lambda: MOE.grouped_gemm(hs, dY, seg_off, E, mode=2, m=I_, n=H)),
+        ("dX through gate and up (two operand pairs)", 2.0 * rows * 2 * I_ * H,
+         lambda: MOE.grouped_gemm(gu[:, :I_], w1.view(E * H, I_), seg_off, E, mode=1, b_mn=False, n=H, a2=gu[:, I_:],
+                                  b2=w3.view(E * H, I_))),
+    ]
+    for name, fl, fn in runs:
+        t = timeit(fn, a.iters, a.warmup, a.flush)
+        print(json.dumps({"kernel": "grouped_gemm " + name, "rows": rows, "ms": t, "tflops": fl / t / 1e9}))
+    NV.check_status()
+
+
+def bench_reference(a):
+    """This package's kernels beside the reference's own Triton kernels (loaded by file path from the copy under
+    baseline/_ref) and the installed flash-attn on the benchmark shapes: RMSNorm forward+backward, SwiGLU, fused
+    linear + cross-entropy, varlen attention, one ScatterMoE expert layer."""
+    from fms_acceleration_b200 import _native as NV
+    from fms_acceleration_b200.baseline import backend as BK
+    from fms_acceleration_b200.ops import activation as ACT
+    from fms_acceleration_b200.ops import attention as AT
+    from fms_acceleration_b200.ops import cross_entropy as CE
+    from fms_acceleration_b200.ops import moe as MOE
+    from fms_acceleration_b200.ops import rmsnorm as RN
+    from fms_acceleration_b200.trainer import synthetic_packed_batch
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    T, H, I_, V = a.tokens, 4096, 14336, 32000
+    out = []
+
+    def both(name, mine, ref):
+        tm = timeit(mine, a.iters, a.warmup, a.flush)
+        tr = timeit(ref, a.iters, a.warmup, a.flush) if ref is not None else None
+        rec = {"op": name, "this_ms": tm, "reference_ms": tr, "speedup": (tr / tm) if tr else None}
+        print(json.dumps(rec))
+        out.append(rec)
+
+    # RMSNorm forward + backward, hidden 4096
+    rms = BK._load_reference("fms_acceleration_foak", "kernels.unsloth.rms_layernorm")
+    norm = torch.nn.Module()
+    norm.weight = torch.nn.Parameter(torch.ones(H, device=dev, dtype=torch.bfloat16))
+    norm.variance_epsilon = 1e-6
+    x = torch.randn(T, H, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    gy = torch.randn(T, H, device=dev, dtype=torch.bfloat16)
+
+    def mine_rms():
+        y, _ = RN.rmsnorm(x, norm.weight, 1e-6)
+        torch.autograd.grad(y, (x, norm.weight), gy)
+
+    def ref_rms():
+        y = rms.fast_rms_layernorm(norm, x)
+        torch.autograd.grad(y, (x,), gy)  # the reference's kernel gives no weight gradient (frozen norms under LoRA)
+
+    both(f"rmsnorm fwd+bwd [{T}x{H}]", mine_rms, ref_rms)
+    # SwiGLU forward + backward, intermediate 14336
+    glu = BK._load_reference("fms_acceleration_foak", "fused_ops.unsloth_lora.swiglu")
+    e = torch.randn(T, I_, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    g = torch.randn(T, I_, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    gh = torch.randn(T, I_, device=dev, dtype=torch.bfloat16)
+
+    def mine_glu():
+        h = ACT.glu(e, g, "silu")
+        torch.autograd.grad(h, (e, g), gh)
+
+    def ref_glu():
+        h = BK._RefSwiGLU.apply(e, g, glu)
+        torch.autograd.grad(h, (e, g), gh)
+
+    both(f"swiglu fwd+bwd [{T}x{I_}]", mine_glu, ref_glu)
+    # fused linear + cross entropy, vocabulary 32000
+    lce = BK._load_reference("fms_acceleration_foak", "fused_ops.liger_ce.fused_linear_cross_entropy_loss")
+    hid = torch.randn(T, H, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    wv = (torch.randn(V, H, device=dev, dtype=torch.bfloat16) * 0.02).requires_grad_()
+    tgt = torch.randint(0, V, (T,), device=dev)
+
+    def mine_lce():
+        loss = CE.fused_linear_cross_entropy(hid, wv, tgt)
+        torch.autograd.grad(loss, (hid,))
+
+    def ref_lce():
+        loss = lce.LigerFusedLinearCrossEntropyFunction.apply(hid, wv, tgt, None, -100, 0.0, "mean")
+        torch.autograd.grad(loss, (hid,))
+
+    both(f"fused linear+CE fwd+bwd [{T}x{H}] -> {V}", mine_lce, ref_lce)
+    # varlen attention, 32 / 8 heads of 128
+    from flash_attn import flash_attn_varlen_func
+
+    nh, nkv, d = 32, 8, 128
+    b = synthetic_packed_batch(V, 4, T // 4, (128, T // 4), seed=1000, pin=False)
+    cu = b["cu_seqlens"].to(dev)
+    ds, de = AT.doc_bounds_from_cu_seqlens(cu, T)
+    q = torch.randn(T, nh, d, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    kk = torch.randn(T, nkv, d, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    vv = torch.randn(T, nkv, d, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    go = torch.randn(T, nh, d, device=dev, dtype=torch.bfloat16)
+    mx = int((cu[1:] - cu[:-1]).max())
+
+    def mine_attn():
+        o = AT.varlen_attention(q, kk, vv, ds, de)
+        torch.autograd.grad(o, (q, kk, vv), go)
+
+    def ref_attn():
+        o = flash_attn_varlen_func(q, kk, vv, cu, cu, mx, mx, causal=True)
+        torch.autograd.grad(o, (q, kk, vv), go)
+
+    both(f"varlen attention fwd+bwd [{T} tokens, {nh}/{nkv} heads x {d}]", mine_attn, ref_attn)
+    # one Granite expert layer: 40 experts, top-8, hidden 1536, intermediate 512
+    from fms_acceleration_b200.plugins.moe.utils.scattermoe import ScatterMoE
+
+    ops = BK._load_reference("fms_acceleration_moe", "utils.scattermoe_utils.khd.kernels.ops")
+    Hm, Im, E, k = 1536, 512, 40, 8
+    moe = ScatterMoE(Hm, "silu", Im, E, top_k=k, dtype=torch.bfloat16, device=dev)
+    with torch.no_grad():
+        moe.router.weight.normal_(0, 0.02)
+        for m in (moe.w1, moe.w2, moe.w3):
+            m.weight.normal_(0, 0.02)
+    xm = torch.randn(T, Hm, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    gm = torch.randn(T, Hm, device=dev, dtype=torch.bfloat16)
+    runner = BK.BaselineRunner.__new__(BK.BaselineRunner)
+    torch.nn.Module.__init__(runner)
+    runner.k_moe = ops
+
+    def mine_moe():
+        o, _ = moe(xm)
+        torch.autograd.grad(o, [xm] + list(moe.parameters()), gm)
+
+    def ref_moe():
+        o = runner._moe(moe, xm)
+        torch.autograd.grad(o, [xm] + list(moe.parameters()), gm)
+
+    both(f"ScatterMoE layer fwd+bwd [{T} tokens, {E} experts top-{k}, {Hm}/{Im}]", mine_moe, ref_moe)
+    NV.check_status()
+    return out
+
+
 def _line(kernel, ms, nbytes, pk, **extra):
     d = {"kernel": kernel, "ms": ms, "gbs": nbytes / ms / 1e6,
          "frac_of_%s_hbm" % pk["source"]: nbytes / ms / 1e6 / pk["hbm_gbs"]}
@@ -250,11 +420,12 @@ def bench_moe(a):
     idx = torch.rand(T, E, device=dev, generator=g).topk(k, dim=-1).indices.int().contiguous()
     wts = torch.full((T, k), 1.0 / k, device=dev)
     ctx = MOE.MoEContext(H, 512, E, k)
-    cap = ctx.ensure(T, x.dtype, dev)
+    cap = ctx.cap = (T * k + E * 128 + 127) // 128 * 128
     seg_off, seg_cnt, dest_row = MOE._plan(ctx, idx, T, dev)
     t = timeit(lambda: MOE._plan(ctx, idx, T, dev), a.iters, a.warmup, a.flush)
     print(json.dumps({"kernel": "moe_plan (count + plan + 3-phase slot assignment)", "ms": t, "pairs": T * k}))
-    buf, ptrs, _ = ctx._alloc("bench_recv", cap, H, x.dtype, dev)
+    buf = torch.zeros(cap, H, dtype=x.dtype, device=dev)
+    ptrs = MOE._one_ptr(buf)
     ld = buf.stride(0)
     t = timeit(lambda: MOE._dispatch(ctx, x, idx, dest_row, None, ptrs, ld), a.iters, a.warmup, a.flush)
     _line("moe_dispatch", t, (T * H + T * k * H) * 2.0, pk)
@@ -266,7 +437,7 @@ def bench_moe(a):
 def main(argv=None):
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="what", required=True)
-    for name in ("gemm", "attn", "elementwise", "q4gemm", "mamba", "moe"):
+    for name in ("gemm", "attn", "elementwise", "q4gemm", "mamba", "moe", "grouped", "reference"):
         p = sub.add_parser(name)
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--warmup", type=int, default=5)
@@ -295,18 +466,21 @@ def main(argv=None):
             p.add_argument("--head-dim", type=int, default=64)
             p.add_argument("--state", type=int, default=128)
             p.add_argument("--chunk", type=int, default=256)
-        elif name == "moe":
+        elif name in ("moe", "grouped"):
             p.add_argument("--tokens", type=int, default=16384)
             p.add_argument("--hidden", type=int, default=1536)
+            p.add_argument("--inter", type=int, default=512)
             p.add_argument("--experts", type=int, default=40)
             p.add_argument("--top-k", type=int, default=8)
+        elif name == "reference":
+            p.add_argument("--tokens", type=int, default=16384)
         else:
             p.add_argument("--tokens", type=int, default=16384)
             p.add_argument("--hidden", type=int, default=4096)
             p.add_argument("--inter", type=int, default=14336)
     a = ap.parse_args(argv)
     {"gemm": bench_gemm, "attn": bench_attn, "elementwise": bench_elementwise, "q4gemm": bench_q4gemm,
-     "mamba": bench_mamba, "moe": bench_moe}[a.what](a)
+     "mamba": bench_mamba, "moe": bench_moe, "grouped": bench_grouped, "reference": bench_reference}[a.what](a)
     return 0
 
 

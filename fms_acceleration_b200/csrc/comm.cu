@@ -259,6 +259,118 @@ __global__ void allreduce_bucket_kernel(PeerPtrs buckets, PeerPtrs signals, long
   __syncthreads();
 }
 
+// ----------------------------------------------------------------------------------------
+// All-reduce through the NVSwitch multicast object (NVLS): every rank's bucket is bound to one multicast address range.
+// A rank reduces ITS slice with multimem.ld_reduce (one instruction returns the sum over all ranks, added inside the
+// switch), scales it, and multimem.st writes the result into every rank's bucket at once: per element one load and one
+// store cross this GPU's links instead of world - 1 peer loads and world - 1 peer stores.  Barriers before and after
+// as in allreduce_bucket_kernel.  `mc` is the multicast address of the bucket (same layout as the local one).
+// ----------------------------------------------------------------------------------------
+__device__ __forceinline__ void multimem_ld_reduce_bf16x8(const void* addr, float (&f)[8]) {
+  uint32_t r0, r1, r2, r3;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "l"(addr)
+               : "memory");
+  const uint32_t r[4] = {r0, r1, r2, r3};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&r[i]);
+    const float2 p = __bfloat1622float2(v);
+    f[2 * i] = p.x;
+    f[2 * i + 1] = p.y;
+  }
+}
+__device__ __forceinline__ void multimem_st_bf16x8(void* addr, const float (&f)[8]) {
+  const uint32_t r0 = pack_bf16x2(f[0], f[1]), r1 = pack_bf16x2(f[2], f[3]), r2 = pack_bf16x2(f[4], f[5]),
+                 r3 = pack_bf16x2(f[6], f[7]);
+  asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(addr), "r"(r0), "r"(r1), "r"(r2),
+               "r"(r3)
+               : "memory");
+}
+__device__ __forceinline__ void multimem_ld_reduce_f32x4(const void* addr, float (&f)[4]) {
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(f[0]), "=f"(f[1]), "=f"(f[2]), "=f"(f[3])
+               : "l"(addr)
+               : "memory");
+}
+__device__ __forceinline__ void multimem_st_f32x4(void* addr, const float (&f)[4]) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(f[0]), "f"(f[1]), "f"(f[2]),
+               "f"(f[3])
+               : "memory");
+}
+
+template <typename T>
+__global__ void allreduce_multimem_kernel(T* mc, PeerPtrs signals, long long n, int rank, int world, float scale, int chan,
+                                          uint32_t epoch, unsigned* grid_sync, int* status) {
+  constexpr int V = 16 / sizeof(T);
+  __shared__ int ok_sh;
+  if (blockIdx.x == 0) {
+    if (threadIdx.x == 0) ok_sh = 1;
+    __syncthreads();
+    if (threadIdx.x < world) {
+      __threadfence_system();
+      st_release_sys(reinterpret_cast<uint32_t*>(signals.p[threadIdx.x]) + chan * world + rank, epoch);
+      if (!wait_signal_ge(reinterpret_cast<const uint32_t*>(signals.p[rank]) + chan * world + threadIdx.x, epoch, status))
+        ok_sh = 0;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      atomicExch(grid_sync, ok_sh ? epoch : 0xffffffffu);
+    }
+  }
+  if (threadIdx.x == 0) {
+    const long long t0 = clock64();
+    unsigned v;
+    while ((v = atomicAdd(grid_sync, 0u)) != epoch && v != 0xffffffffu) {
+      if (clock64() - t0 > 2 * peer_wait_budget(status)) { report_status(status, kTimeoutPeerFlag); break; }
+    }
+    ok_sh = (v == epoch);
+  }
+  __syncthreads();
+  if (!ok_sh) return;
+  const long long n_own = n / world;
+  const long long nvec = n_own / V;
+  T* base = mc + (long long)rank * n_own;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    if constexpr (sizeof(T) == 4) {
+      float f[4];
+      multimem_ld_reduce_f32x4(base + i * V, f);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) f[k] *= scale;
+      multimem_st_f32x4(base + i * V, f);
+    } else {
+      float f[8];
+      multimem_ld_reduce_bf16x8(base + i * V, f);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) f[k] *= scale;
+      multimem_st_bf16x8(base + i * V, f);
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned arrived = atomicAdd(grid_sync + 1, 1u) + 1;
+    if (arrived == gridDim.x) {
+      atomicExch(grid_sync + 1, 0u);
+      __threadfence_system();
+      for (int t = 0; t < world; ++t)
+        st_release_sys(reinterpret_cast<uint32_t*>(signals.p[t]) + (chan + 1) * world + rank, epoch);
+      for (int t = 0; t < world; ++t)
+        wait_signal_ge(reinterpret_cast<const uint32_t*>(signals.p[rank]) + (chan + 1) * world + t, epoch, status);
+      __threadfence();
+      atomicExch(grid_sync + 2, epoch);
+    }
+    const long long t0 = clock64();
+    while (atomicAdd(grid_sync + 2, 0u) != epoch) {
+      if (clock64() - t0 > 2 * peer_wait_budget(status)) { report_status(status, kTimeoutPeerFlag); break; }
+      if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) break;
+    }
+  }
+  __syncthreads();
+}
+
 // Bounded local wait used by tests of the time-out path: waits for a word that nobody sets.
 __global__ void wait_flag_kernel(const uint32_t* flag, uint32_t epoch, int* status, long long budget_cycles) {
   const long long t0 = clock64();
@@ -344,5 +456,25 @@ extern "C" int fmsb_comm_allreduce(void* const* bucket_ptrs, void* const* signal
 extern "C" int fmsb_comm_wait_flag(const unsigned* flag, unsigned epoch, int* status, long long budget_cycles,
                                    cudaStream_t stream) {
   wait_flag_kernel<<<1, 1, 0, stream>>>(flag, epoch, status, budget_cycles);
+  return (int)cudaGetLastError();
+}
+
+// The same all-reduce through the switch's multicast object: `mc_bucket` is the MULTICAST address of the symmetric
+// bucket (0 elements allowed).  bf16 and fp32 buckets (the switch adds those; fp16 is not offered here).
+extern "C" int fmsb_comm_allreduce_multimem(void* mc_bucket, void* const* signal_ptrs, long long n, int rank, int world,
+                                            float scale, int dtype, int chan, unsigned epoch, unsigned* grid_sync, int ctas,
+                                            int* status, cudaStream_t stream) {
+  if (world > kMaxRanks || mc_bucket == nullptr) return -2;
+  if (n == 0) return 0;
+  const int V = dtype == 2 ? 4 : 8;
+  if (n % ((long long)world * V) != 0 || (dtype != 1 && dtype != 2)) return -2;
+  int maxc = fmsb_host::sm_count();
+  if (ctas <= 0) ctas = 32;
+  if (ctas > maxc) ctas = maxc;
+  PeerPtrs s = make_ptrs(signal_ptrs, world);
+  if (dtype == 2)
+    allreduce_multimem_kernel<float><<<ctas, 512, 0, stream>>>((float*)mc_bucket, s, n, rank, world, scale, chan, epoch, grid_sync, status);
+  else
+    allreduce_multimem_kernel<__nv_bfloat16><<<ctas, 512, 0, stream>>>((__nv_bfloat16*)mc_bucket, s, n, rank, world, scale, chan, epoch, grid_sync, status);
   return (int)cudaGetLastError();
 }

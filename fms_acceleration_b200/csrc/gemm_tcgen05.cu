@@ -57,6 +57,7 @@ struct GemmParams {
   int n_split;               // > 0: output columns >= n_split take their B tiles from the second B map at column - n_split
                              //      (two weight matrices side by side in one pass over A; needs kblocks2 == 0)
   int c_fp32;                // C holds fp32 (accumulating into an fp32 D over several launches)
+  int tma_store;             // CTA-pair kernel: D (16-bit) leaves through shared memory and bulk tensor stores
   long long d_group_stride;  // elements between the D matrices of consecutive groups (mode 2)
   // mode 3: uniform batch indexed by (outer o, inner i), i < n_inner.  Operand offsets in elements of the
   // stored 2-D matrices: rows += o * x_ro + i * x_ri, columns += (i / x_div) * x_ci.
@@ -473,6 +474,63 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_const
 }
 
 
+// Epilogue of one tile for one warp through shared memory: every 32-column chunk of this warp's 32 accumulator lanes is
+// converted to 16 bits, written into a 2 KB staging slot (64-byte rows, 64-byte swizzle so that the quarter-warp phases
+// of the 16-byte stores hit distinct banks) and leaves with ONE bulk tensor store of a 32 x 32 box, which also clips the
+// ragged edges of M and N.  Two slots per warp alternate; a slot is rewritten only after the store that read it.
+template <int BN>
+__device__ __forceinline__ void epilogue_store_tile_tma(const GemmParams& p, const CUtensorMap* tmD, uint32_t taddr,
+                                                        int cpar, int row0, int gm, int n0, bool empty_k, uint32_t slots,
+                                                        int lane, int& slot) {
+  constexpr int CH = 32;
+#pragma unroll 1
+  for (int c = cpar; c < BN / CH; c += 2) {
+    uint32_t r[32];
+    tmem_ld_32x32(taddr + c * CH, r);
+    tmem_ld_wait();
+    float v[CH];
+#pragma unroll
+    for (int i = 0; i < CH; ++i) v[i] = (empty_k ? 0.f : __uint_as_float(r[i])) * p.alpha;
+    const int gn = n0 + c * CH;
+    if (p.C != nullptr && p.beta != 0.f && gm < p.M && gn < p.N) {
+      if (p.fmt == 1) {
+        const __nv_bfloat16* crow = reinterpret_cast<const __nv_bfloat16*>(p.C) + (long long)gm * p.ldc + gn;
+        for (int i = 0; i < CH; ++i)
+          if (gn + i < p.N) v[i] += p.beta * __bfloat162float(crow[i]);
+      } else {
+        const __half* crow = reinterpret_cast<const __half*>(p.C) + (long long)gm * p.ldc + gn;
+        for (int i = 0; i < CH; ++i)
+          if (gn + i < p.N) v[i] += p.beta * __half2float(crow[i]);
+      }
+    }
+    const uint32_t buf = slots + static_cast<uint32_t>(slot) * 2048u;
+    if (lane == 0) tma_store_wait_read<1>();  // the store that last read this slot (two stores ago) is done with it
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t w0, w1, w2, w3;
+      if (p.fmt == 1) {
+        w0 = pack_bf16x2(v[8 * j], v[8 * j + 1]); w1 = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
+        w2 = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]); w3 = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
+      } else {
+        w0 = pack_f16x2(v[8 * j], v[8 * j + 1]); w1 = pack_f16x2(v[8 * j + 2], v[8 * j + 3]);
+        w2 = pack_f16x2(v[8 * j + 4], v[8 * j + 5]); w3 = pack_f16x2(v[8 * j + 6], v[8 * j + 7]);
+      }
+      const uint32_t chunk = static_cast<uint32_t>(j) ^ ((static_cast<uint32_t>(lane) >> 1) & 3u);  // 64-byte swizzle
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(buf + lane * 64u + chunk * 16u), "r"(w0), "r"(w1),
+                   "r"(w2), "r"(w3)
+                   : "memory");
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0 && gn < p.N && row0 < p.M) {
+      tma_store_2d(tmD, buf, gn, row0);
+      tma_store_commit();
+    }
+    slot ^= 1;
+  }
+}
+
 // ----------------------------------------------------------------------------------------
 // CTA-pair variant (plain mode, 256 x 256 output tiles): a cluster of two CTAs on the two SMs of one TPC computes
 // one tile with tcgen05.mma.cta_group::2 (M = 256, N = 256).  CTA r of the pair stages rows [m0 + 128 r, +128) of A
@@ -500,18 +558,20 @@ struct PairCfg {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = 6;
   static constexpr int kTmemCols = 2 * BN2;      // two accumulators of 256 columns: all of tensor memory
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+  static constexpr int kEpiBytes = 8 * 2 * 2048;  // staging of the store epilogue: 8 warps x 2 slots x (32 rows x 64 B)
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 + 256;
 };
 
 template <int A_MN, int B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
                          const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
-                         const GemmParams p) {
+                         const __grid_constant__ CUtensorMap tmD, const GemmParams p) {
   using Cfg = PairCfg;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bar_base = smem_base + Cfg::kStages * Cfg::kStageBytes;
+  const uint32_t epi_base = smem_base + Cfg::kStages * Cfg::kStageBytes;
+  const uint32_t bar_base = epi_base + Cfg::kEpiBytes;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::kStages + s); };
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * Cfg::kStages + a); };
@@ -648,6 +708,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_
     const int row = q * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
+    int slot = 0;
+    const uint32_t my_slots = epi_base + static_cast<uint32_t>(warp - 2) * 4096u;
+    if (p.tma_store && lane == 0) prefetch_tmap(&tmD);
     TileInfo ti;
     ti.d_off = 0;
     ti.d_c = 0;
@@ -655,19 +718,24 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_
     for (int t = pair; t < n_tiles; t += n_pairs) {
       int tm, tn;
       tile_coords(t, tiles_m, tiles_n, tm, tn);
-      const int gm = tm * BM2 + (int)cta * BM + row;
+      const int row0 = tm * BM2 + (int)cta * BM + q * 32;
+      const int gm = row0 + lane;
       const int n0 = tn * BN2;
       ti.n0 = n0;
       if (!mbar_wait(tfull_bar(acc), acc_phase, p.status, kTimeoutEpilogue)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN2);
-      epilogue_store_tile<BN2>(p, ti, taddr, cpar, gm, n0, kblocks == 0);
+      if (p.tma_store)
+        epilogue_store_tile_tma<BN2>(p, &tmD, taddr, cpar, row0, gm, n0, kblocks == 0, my_slots, lane, slot);
+      else
+        epilogue_store_tile<BN2>(p, ti, taddr, cpar, gm, n0, kblocks == 0);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(tempty_bar(acc), 0));
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
+    if (p.tma_store && lane == 0) tma_store_wait<0>();  // the staging slots stay valid until the last store has read them
   }
 
   // ------------------------------------------------------------------ teardown
@@ -716,6 +784,21 @@ int make_tmap_2d_16b(CUtensorMap* out, const void* base, uint64_t rows, uint64_t
   return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r) - 100;
 }
 
+// 2-D row-major tensor of 16-bit elements with a 64-byte swizzle (staging of the store epilogue: 32 x 32 boxes).
+int make_tmap_2d_16b_sw64(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride_elems,
+                          uint32_t box_rows, uint32_t box_cols) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (enc == nullptr) return -1;
+  cuuint64_t gdim[2] = {cols, rows};
+  cuuint64_t gstr[1] = {row_stride_elems * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstr, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r) - 100;
+}
+
 int sm_count() {
   static int n = 0;
   if (n == 0) {
@@ -753,7 +836,7 @@ static int g_pair_occupancy = -1, g_pair_occupancy_error = -1;
 // Clusters of two CTAs that can be resident at once (one pair per TPC when the kernel takes a whole SM).
 template <int A_MN, int B_MN>
 int launch_gemm_pair(const CUtensorMap& a1, const CUtensorMap& b1, const CUtensorMap& a2, const CUtensorMap& b2,
-                     const fmsb::GemmParams& p, int max_ctas, cudaStream_t stream) {
+                     const CUtensorMap& d, const fmsb::GemmParams& p, int max_ctas, cudaStream_t stream) {
   using Cfg = fmsb::PairCfg;
   auto kern = fmsb::gemm_tcgen05_pair_kernel<A_MN, B_MN>;
   static int max_pairs = -1;
@@ -788,9 +871,12 @@ int launch_gemm_pair(const CUtensorMap& a1, const CUtensorMap& b1, const CUtenso
   const int tiles = ((p.M + fmsb::BM2 - 1) / fmsb::BM2) * ((p.N + fmsb::BN2 - 1) / fmsb::BN2);
   if (tiles < pairs) pairs = tiles;
   if (pairs <= 0) return 0;
-  kern<<<2 * pairs, fmsb::kGemmThreads, Cfg::kSmemBytes, stream>>>(a1, b1, a2, b2, p);
+  kern<<<2 * pairs, fmsb::kGemmThreads, Cfg::kSmemBytes, stream>>>(a1, b1, a2, b2, d, p);
   return static_cast<int>(cudaGetLastError());
 }
+
+// store epilogue through shared memory and bulk tensor stores (1, default) or per-thread 16-byte stores (0)
+static int g_pair_tma_store = 1;
 
 // 0: never, 1: when there are enough 256 x 256 tiles to fill the machine about twice (default), 2: whenever M and N
 // reach 256; set through fmsb_gemm_set_pair_mode (tests compare both kernels on small shapes)
@@ -801,6 +887,12 @@ static int g_pair_mode = 1;
 // what the occupancy query answered for the CTA-pair kernel (after its first launch): clusters, or -(error) - 1
 extern "C" int fmsb_gemm_pair_occupancy() {
   return fmsb_host::g_pair_occupancy_error > 0 ? -fmsb_host::g_pair_occupancy_error - 1 : fmsb_host::g_pair_occupancy;
+}
+
+extern "C" int fmsb_gemm_set_pair_store(int tma_store) {
+  const int old = fmsb_host::g_pair_tma_store;
+  fmsb_host::g_pair_tma_store = tma_store;
+  return old;
 }
 
 extern "C" int fmsb_gemm_set_pair_mode(int mode) {
@@ -899,6 +991,7 @@ static int gemm_impl(const void* A1, long long lda1, const void* B1, long long l
   p.b2_group_rows = gx != nullptr ? gx->b2_group_rows : 0;
   p.n_split = gx != nullptr ? gx->n_split : 0;
   p.c_fp32 = gx != nullptr ? gx->c_fp32 : 0;
+  p.tma_store = 0;
   p.n_batch = 0; p.n_inner = 1; p.a_div = p.b_div = 1;
   p.a_ro = p.a_ri = p.a_ci = p.b_ro = p.b_ri = p.b_ci = p.d_ro = p.d_ri = p.d_ci = 0;
   if (bd != nullptr) {
@@ -909,10 +1002,15 @@ static int gemm_impl(const void* A1, long long lda1, const void* B1, long long l
   }
 
   if (use_pair) {
-    if (!a_mn && !b_mn) return launch_gemm_pair<0, 0>(ta1, tb1, ta2, tb2, p, max_ctas, stream);
-    if (a_mn && !b_mn) return launch_gemm_pair<1, 0>(ta1, tb1, ta2, tb2, p, max_ctas, stream);
-    if (!a_mn && b_mn) return launch_gemm_pair<0, 1>(ta1, tb1, ta2, tb2, p, max_ctas, stream);
-    return launch_gemm_pair<1, 1>(ta1, tb1, ta2, tb2, p, max_ctas, stream);
+    CUtensorMap td = ta1;
+    p.tma_store = 0;
+    if (g_pair_tma_store && !d_fp32 && ldd % 8 == 0 && (reinterpret_cast<uintptr_t>(D) & 15) == 0 &&
+        make_tmap_2d_16b_sw64(&td, D, (uint64_t)M, (uint64_t)N, (uint64_t)ldd, 32, 32) == 0)
+      p.tma_store = 1;
+    if (!a_mn && !b_mn) return launch_gemm_pair<0, 0>(ta1, tb1, ta2, tb2, td, p, max_ctas, stream);
+    if (a_mn && !b_mn) return launch_gemm_pair<1, 0>(ta1, tb1, ta2, tb2, td, p, max_ctas, stream);
+    if (!a_mn && b_mn) return launch_gemm_pair<0, 1>(ta1, tb1, ta2, tb2, td, p, max_ctas, stream);
+    return launch_gemm_pair<1, 1>(ta1, tb1, ta2, tb2, td, p, max_ctas, stream);
   }
 #define FMSB_DISPATCH(BNV)                                                                          \
   if (bn == BNV) {                                                                                  \

@@ -120,6 +120,13 @@ def set_pair_mode(mode: int) -> int:
     return int(N.lib().fmsb_gemm_set_pair_mode(int(mode)))
 
 
+def set_pair_store(tma_store: int) -> int:
+    """Epilogue of the CTA-pair kernel for 16-bit outputs: 1 (default) stages the tile through shared memory and
+    stores it with bulk tensor stores, 0 uses per-thread 16-byte stores.  Returns the previous setting."""
+    N.declare("fmsb_gemm_set_pair_store", [_ct.c_int])
+    return int(N.lib().fmsb_gemm_set_pair_store(int(tma_store)))
+
+
 SM_COUNT = 148
 SPLIT_K_MIN = 512  # shortest contraction slice worth a tile of its own
 

@@ -312,7 +312,8 @@ class ShardedEngine:
                 self.comm.reduce_scatter_ptrs(ptrs, seg.numel_padded // self.world, self.grad_dtype,
                                               self.sharded_optimizer.grad_slice(seg), scale=self.grad_scale)
             else:
-                self.comm.allreduce_ptrs(ptrs, seg.numel_padded, self.grad_dtype, scale=self.grad_scale)
+                mc = self.bucket.mc_ptr + seg.offset * esize if self.bucket.mc_ptr else 0
+                self.comm.allreduce_ptrs(ptrs, seg.numel_padded, self.grad_dtype, scale=self.grad_scale, mc_ptr=mc)
             seg.done = torch.cuda.Event()
             seg.done.record(self.reduce_stream)
 

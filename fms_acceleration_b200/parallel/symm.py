@@ -8,6 +8,7 @@ process group's store); everything that moves data afterwards is this package's 
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import List, Optional
 
 import torch
@@ -22,6 +23,7 @@ N.declare("fmsb_comm_allgather", [P, P, L, I, I, I, P])
 N.declare("fmsb_comm_reduce_scatter", [P, P, L, I, I, F, I, I, I, P])
 N.declare("fmsb_comm_allreduce", [P, P, L, I, I, F, I, I, U, P, I, P, P])
 N.declare("fmsb_comm_wait_flag", [P, U, P, L, P])
+N.declare("fmsb_comm_allreduce_multimem", [P, P, L, I, I, F, I, I, U, P, I, P, P])
 
 N_CHANNELS = 64
 
@@ -49,6 +51,9 @@ class SymmBuffer:
         self.handle = symm_mem.rendezvous(self.local, self.group)
         self.ptrs: List[int] = [int(p) for p in self.handle.buffer_ptrs]
         self._arr = _ptr_array(self.ptrs)
+        # address of the NVSwitch multicast object the allocation is bound to (0 where the fabric offers none):
+        # multimem loads / stores on it reach every rank's copy through the switch
+        self.mc_ptr: int = int(getattr(self.handle, "multicast_ptr", 0) or 0)
 
     def ptr_array(self, offset: int = 0):
         """ctypes array of the peers' base addresses (+ ``offset`` bytes)."""
@@ -100,11 +105,12 @@ class Communicator:
         N.check(rc, "fmsb_comm_allgather")
 
     def allreduce_(self, bucket: SymmBuffer, numel: int, dtype: torch.dtype, scale: Optional[float] = None,
-                   chan: int = 2, ctas: Optional[int] = None) -> None:
-        self.allreduce_ptrs(bucket.ptr_array(), numel, dtype, scale, chan, ctas)
+                   chan: int = 2, ctas: Optional[int] = None, multimem: Optional[bool] = None) -> None:
+        self.allreduce_ptrs(bucket.ptr_array(), numel, dtype, scale, chan, ctas, mc_ptr=bucket.mc_ptr, multimem=multimem)
 
     def allreduce_ptrs(self, ptrs, numel: int, dtype: torch.dtype, scale: Optional[float] = None,
-                       chan: int = 2, ctas: Optional[int] = None) -> None:
+                       chan: int = 2, ctas: Optional[int] = None, mc_ptr: int = 0,
+                       multimem: Optional[bool] = None) -> None:
         """In-place sum (times ``scale``, default 1/world) of the first ``numel`` elements of a symmetric bucket.
         ``ctas`` defaults to 32 for adapter-sized buckets and to 128 for buckets of 32 MiB and more (a full
         fine-tune's gradients), which runs at the end of the backward when nothing else needs the SMs."""
@@ -114,6 +120,16 @@ class Communicator:
         st = N.status_word(self.device)
         scale = 1.0 / self.world if scale is None else scale
         self.epochs[chan + 1] = self.epochs[chan] + 1
+        if multimem is None:
+            multimem = os.environ.get("FMSB_ALLREDUCE", "p2p") == "multimem"
+        if multimem and mc_ptr and dtype in (torch.bfloat16, torch.float32):
+            # in-switch reduction (NVLS): one multimem load returns the sum over the ranks, one multimem store
+            # writes the result everywhere
+            rc = N.lib().fmsb_comm_allreduce_multimem(mc_ptr, self.signals.ptr_array(), numel, self.rank, self.world,
+                                                      float(scale), N.dtype_code(dtype), chan, self.next_epoch(chan),
+                                                      self.grid_sync.data_ptr(), ctas, st.data_ptr(), N.stream_ptr())
+            N.check(rc, "fmsb_comm_allreduce_multimem")
+            return
         rc = N.lib().fmsb_comm_allreduce(ptrs, self.signals.ptr_array(), numel, self.rank, self.world,
                                          float(scale), N.dtype_code(dtype), chan, self.next_epoch(chan),
                                          self.grid_sync.data_ptr(), ctas, st.data_ptr(), N.stream_ptr())

@@ -37,8 +37,6 @@ class ScatterMoEAccelerationPlugin(AccelerationPlugin):
             world = torch.distributed.get_world_size()
             rank = torch.distributed.get_rank()
         (peft_config,) = modifiable_args if len(modifiable_args) == 1 else (None,)
-        if self._ep_degree > 1 and peft_config is not None:
-            raise NotImplementedError("LoRA on the experts is only supported with ep_degree 1")
         budget = None
         bs, sl = getattr(train_args, "per_device_train_batch_size", None), getattr(train_args, "max_seq_length", None)
         if bs and sl:

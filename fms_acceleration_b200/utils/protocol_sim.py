@@ -122,6 +122,113 @@ class SimWorld:
         return self.buffers[slot][rank][: rank * n].reshape(rank, n).copy()
 
 
+class StagedExchange:
+    """The chunk-pipelined expert-parallel exchange of ``ops/moe.py`` with its two streams per rank.
+
+    Every rank runs two threads: the *communication stream* (push rows into the owners' staging set, barrier, copy
+    them out; later reduce the results into the staging set, barrier, read them back) and the *compute stream* (the
+    experts).  Events order the two inside a rank exactly as the CUDA events do; the barriers are the cross-rank
+    epoch barriers.  Two staging sets are reused every other chunk.  What must hold: a set is never overwritten
+    while an owner still copies it out or a source still reads results from it.  The payload makes a violation
+    visible: row values encode (source, chunk, index) and the "expert" maps ``x -> 2 x + owner``.
+
+    ``sets``: number of staging sets, 2 (what the code does) or 1 (chunk c+1 is pushed into the set an owner may not
+    have copied chunk c out of yet: the reuse bug that the second set prevents; the model must catch it)."""
+
+    CH_A, CH_B = 0, 1
+
+    def __init__(self, sim: SimWorld, n_chunks: int, rows: int, sets: int = 2):
+        self.sim, self.C, self.rows, self.sets = sim, n_chunks, rows, sets
+        w = sim.world
+        sim.alloc("stage_x", 2 * w * rows, np.float64)   # [set][source][row]
+        sim.alloc("stage_y", 2 * w * rows, np.float64)
+        self.epoch = [[0, 0] for _ in range(w)]
+        self.ready = [[threading.Event() for _ in range(n_chunks)] for _ in range(w)]
+        self.done = [[threading.Event() for _ in range(n_chunks)] for _ in range(w)]
+        self.xs = [[None] * n_chunks for _ in range(w)]
+        self.ys = [[None] * n_chunks for _ in range(w)]
+        self.out = [[None] * n_chunks for _ in range(w)]
+        self.failed = [False] * w
+
+    @staticmethod
+    def value(src: int, chunk: int, i: int) -> float:
+        return 1000.0 * src + 10.0 * chunk + 0.001 * i
+
+    def _barrier(self, rank: int, chan: int) -> bool:
+        self.epoch[rank][chan] += 1
+        return self.sim.barrier(rank, chan, self.epoch[rank][chan])
+
+    def _push(self, rank: int, c: int) -> bool:
+        sim, w, n, s = self.sim, self.sim.world, self.rows, c % self.sets
+        payload = np.array([self.value(rank, c, i) for i in range(n)])
+        for owner in range(w):  # every owner gets this source's rows (one per (token, rank))
+            sim._pause(rank)
+            base = (s * w + rank) * n
+            sim.buffers["stage_x"][owner][base: base + n] = payload
+        if not self._barrier(rank, self.CH_A):
+            return False
+        sim._pause(rank)
+        self.xs[rank][c] = sim.buffers["stage_x"][rank][s * w * n: (s + 1) * w * n].copy()  # replicate (local)
+        self.ready[rank][c].set()
+        return True
+
+    def _pull(self, rank: int, c: int) -> bool:
+        sim, w, n, s = self.sim, self.sim.world, self.rows, c % self.sets
+        if not self.done[rank][c].wait(timeout=10 * sim.wait_budget + 5):
+            return False
+        sim._pause(rank)
+        sim.buffers["stage_y"][rank][s * w * n: (s + 1) * w * n] = self.ys[rank][c]        # owner-side reduction
+        if not self._barrier(rank, self.CH_B):
+            return False
+        got = np.zeros(n)
+        for owner in range(w):  # one row per (token, owner) comes back
+            sim._pause(rank)
+            base = (s * w + rank) * n
+            got += sim.buffers["stage_y"][owner][base: base + n]
+        self.out[rank][c] = got
+        return True
+
+    def comm_stream(self, rank: int) -> None:
+        C = self.C
+        ok = self._push(rank, 0) and (C < 2 or self._push(rank, 1))
+        for c in range(C):
+            if not ok:
+                break
+            ok = self._pull(rank, c) and (c + 2 >= C or self._push(rank, c + 2))
+        if not ok:
+            self.failed[rank] = True
+            for ev in self.ready[rank] + self.done[rank]:
+                ev.set()  # let the other stream of this rank unwind
+
+    def compute_stream(self, rank: int) -> None:
+        for c in range(self.C):
+            self.ready[rank][c].wait()
+            if self.failed[rank]:
+                return
+            self.sim._pause(rank)
+            self.ys[rank][c] = 2.0 * self.xs[rank][c] + rank
+            self.done[rank][c].set()
+
+    def expected(self, rank: int, c: int) -> np.ndarray:
+        w = self.sim.world
+        x = np.array([self.value(rank, c, i) for i in range(self.rows)])
+        return sum(2.0 * x + owner for owner in range(w))
+
+    def run(self) -> bool:
+        """Returns True when every rank got every chunk right; False on a time-out (status set) or wrong data."""
+        w = self.sim.world
+        threads = [threading.Thread(target=self.comm_stream, args=(r,)) for r in range(w)]
+        threads += [threading.Thread(target=self.compute_stream, args=(r,)) for r in range(w)]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join()
+        if any(self.failed):
+            return False
+        return all(self.out[r][c] is not None and np.allclose(self.out[r][c], self.expected(r, c))
+                   for r in range(w) for c in range(self.C))
+
+
 def run_ranks(world: SimWorld, fn: Callable[[int], None]) -> List[Optional[BaseException]]:
     """Run ``fn(rank)`` on one thread per rank; returns the exception (or None) of each."""
     errs: List[Optional[BaseException]] = [None] * world.world

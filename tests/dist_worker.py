@@ -43,6 +43,27 @@ def check_comm(dev, rank, world):
         got = bucket.view(0, n, dtype).float()
         tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
         assert torch.allclose(got, ref, rtol=tol, atol=tol), f"allreduce {dtype} mismatch {(got - ref).abs().max()}"
+    # the same through the switch's multicast object (in-switch reduction), where the fabric offers one
+    n = world * 16 * 1024 * 3
+    for dtype in (torch.bfloat16, torch.float32):
+        esz = torch.empty((), dtype=dtype).element_size()
+        bucket = SymmBuffer(n * esz)
+        if not bucket.mc_ptr:
+            print("multimem: no multicast object on this fabric, skipped", flush=True)
+            break
+        x = torch.randn(n, device=dev).to(dtype)
+        for it in range(2):
+            bucket.view(0, n, dtype).copy_(x)
+            comm.barrier(0)
+            comm.allreduce_(bucket, n, dtype, multimem=True)
+        NV.check_status()
+        ref = x.float().clone()
+        dist.all_reduce(ref)
+        got = bucket.view(0, n, dtype).float()
+        tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+        assert torch.allclose(got, ref / world, rtol=tol, atol=tol), f"multimem allreduce {dtype} mismatch"
+    else:
+        print("multimem allreduce checked against NCCL", flush=True)
     print("DIST_OK allreduce", flush=True)
     # reduce-scatter with fused scale and fp32 output
     n_own = 8 * 4096

@@ -186,6 +186,45 @@ def check_ep_checkpoint(rank, world, tmp):
     print("CPU_OK ep_checkpoint", flush=True)
 
 
+def check_ep_lora(rank, world, tmp):
+    """Per-expert LoRA under expert parallelism (adapters are created per local expert, base experts frozen): the
+    plugin accepts it, only adapters and nothing else of the experts trains, the loss goes down, and the adapter
+    checkpoint holds every rank's adapters."""
+    from fms_acceleration_b200.models.builder import build_model
+    from fms_acceleration_b200.nn.lora import LoraConfig
+    from fms_acceleration_b200.parallel.engine import ShardedEngine
+    from fms_acceleration_b200.plugins.moe.framework_plugin_scattermoe import ScatterMoEAccelerationPlugin
+    from fms_acceleration_b200.plugins.moe.utils import checkpoint_utils as CU
+    from fms_acceleration_b200.trainer import TrainArgs, Trainer
+
+    model = build_model("tiny-granitemoe", dtype=torch.float32, seed=0)
+    plugin = ScatterMoEAccelerationPlugin({"training": {"moe": {"scattermoe": {"ep_degree": world}}}})
+    targs = TrainArgs(learning_rate=5e-2, output_dir=os.path.join(tmp, "lora"))
+    cfg = LoraConfig(r=4, lora_alpha=8, target_modules=["all-linear"])
+    model, _ = plugin.augmentation(model, targs, modifiable_args=(cfg,))
+    for n, p in model.named_parameters():  # a LoRA run trains adapters only
+        p.requires_grad_("lora_" in n)
+    moe = model.model.layers[0].block_sparse_moe
+    assert moe.w1.lora_A.shape[0] == moe.num_experts // world and not moe.w1.weight.requires_grad
+    eng = ShardedEngine(model, shard_frozen=False, backend="library")
+    assert eng.ep_params and all("lora" in n for n, p in model.named_parameters() if p.requires_grad)
+    tr = Trainer(model, targs, engine=eng)
+    eng.zero_grad()
+    b = _batches(1024, rank, 1, seq=32)[0]
+    w0 = moe.w1.weight.detach().clone()
+    losses = [float(tr.train_step(b)) for _ in range(6)]
+    assert losses[-1] < losses[0], losses
+    assert torch.equal(moe.w1.weight, w0)
+    ckpt = tr.save_checkpoint()
+    dist.barrier()
+    if rank == 0:
+        sd = CU.get_state_dict_from_dcp_checkpoint(os.path.join(ckpt, "pytorch_model_fsdp_0"))
+        key = [k for k in sd if k.endswith("layers.0.block_sparse_moe.w1.lora_A")][0]
+        assert sd[key].shape[0] == moe.num_experts  # all ranks' adapters, not one rank's
+    dist.barrier()
+    print("CPU_OK ep_lora", flush=True)
+
+
 def main():
     dist.init_process_group("gloo")
     rank, world = dist.get_rank(), dist.get_world_size()
@@ -196,6 +235,8 @@ def main():
         check_zero1_and_resume(rank, world, tmp)
     elif which == "ep_ckpt":
         check_ep_checkpoint(rank, world, tmp)
+    elif which == "ep_lora":
+        check_ep_lora(rank, world, tmp)
     dist.barrier()
     dist.destroy_process_group()
 

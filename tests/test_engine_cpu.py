@@ -31,3 +31,7 @@ def test_sharded_optimizer_matches_replicated_and_resumes(tmp_path, world):
 @pytest.mark.parametrize("world", [2, 4])
 def test_expert_parallel_checkpoint_holds_every_rank(tmp_path, world):
     assert _run("ep_ckpt", world, tmp_path, 29712 + world).count("CPU_OK ep_checkpoint") == world
+
+
+def test_expert_lora_under_expert_parallelism(tmp_path):
+    assert _run("ep_lora", 2, tmp_path, 29731).count("CPU_OK ep_lora") == 2

@@ -97,6 +97,47 @@ def test_lost_link_times_out_with_status_instead_of_hanging():
     assert all(o[:3] == [True, True, True] and o[3] is False for o in ok[1:])
 
 
+@pytest.mark.parametrize("world,chunks", [(2, 2), (3, 5), (4, 3)])
+def test_staged_expert_exchange_reuses_its_two_staging_sets_safely(world, chunks):
+    """The chunk-pipelined expert-parallel exchange (two streams per rank, two staging sets) under scheduling
+    jitter: every row comes back right, call after call (the sets and the epochs are reused across calls)."""
+    from fms_acceleration_b200.utils.protocol_sim import StagedExchange
+
+    sim = SimWorld(world, jitter=3e-4, wait_budget=5.0, seed=3)
+    for _ in range(3):
+        ex = StagedExchange(sim, chunks, rows=4)
+        # epochs continue across calls, as they do across layers
+        ex.epoch = getattr(sim, "_ep_epochs", ex.epoch)
+        assert ex.run()
+        sim._ep_epochs = ex.epoch
+    assert sim.status == [0] * world
+
+
+def test_staged_expert_exchange_model_catches_a_single_staging_set():
+    """With ONE staging set, chunk c+1 is pushed while a slower owner may not have copied chunk c out yet: the bug
+    the second set prevents.  The model must see corrupted rows then (or the test above proves nothing)."""
+    from fms_acceleration_b200.utils.protocol_sim import StagedExchange
+
+    bad = 0
+    for seed in range(8):
+        sim = SimWorld(3, jitter=2e-3, wait_budget=5.0, seed=seed)
+        if not StagedExchange(sim, 6, rows=4, sets=1).run():
+            bad += 1
+    assert bad > 0
+
+
+def test_staged_expert_exchange_dropped_barrier_signal_times_out():
+    """One barrier signal of one chunk never arrives: the waiting ranks give up with the peer-flag status and every
+    thread returns (nothing hangs, nothing reads half-written rows as results)."""
+    from fms_acceleration_b200.utils.protocol_sim import StagedExchange
+
+    sim = SimWorld(3, jitter=1e-4, wait_budget=0.3, seed=1)
+    sim.drop = lambda writer, owner, chan, epoch: (writer, owner, chan, epoch) == (1, 2, StagedExchange.CH_A, 2)
+    ex = StagedExchange(sim, 4, rows=4)
+    assert ex.run() is False
+    assert sim.status[2] == TIMEOUT_PEER_FLAG
+
+
 def test_context_parallel_handoff_order():
     world, n = 4, 6
     sim = SimWorld(world, seed=5)

@@ -100,6 +100,17 @@ def test_gemm_cta_pair_kernel(a_mn, b_mn, M, N_, K):
         NV.check_status()
         assert _rel(pair, ref) < 2e-3
         assert torch.equal(pair, single)
+        # 16-bit output: through shared memory and bulk tensor stores (ragged M / N are clipped by the store) and
+        # through per-thread stores, bit for bit
+        from fms_acceleration_b200.ops.gemm import set_pair_store
+
+        staged = gemm(a, b, a_mn=a_mn, b_mn=b_mn, bn=256)
+        old_store = set_pair_store(0)
+        direct = gemm(a, b, a_mn=a_mn, b_mn=b_mn, bn=256)
+        set_pair_store(old_store)
+        NV.check_status()
+        assert torch.equal(staged, direct)
+        assert _rel(staged, ref) < 1e-2
         if not a_mn and not b_mn:
             r = 16
             xa = torch.randn(M, r, device=DEV, dtype=torch.bfloat16)
