@@ -278,6 +278,21 @@ def run_config(name: str, args, ctx, impl: str = "b200") -> dict:
     barrier()
     e2e_ms_local = e_start.elapsed_time(e_end)
 
+    kernel_table = None
+    if getattr(args, "kernel_table", False) and rank == 0 or (getattr(args, "kernel_table", False) and world > 1):
+        # device time per kernel over two more steps (torch.profiler / CUPTI; not part of any timed region)
+        from torch.profiler import ProfilerActivity, profile
+
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for i in range(2):
+                trainer.train_step(dev_batches[i % n_batches])
+            torch.cuda.synchronize()
+        evs = sorted((e for e in prof.key_averages() if e.device_time_total > 0), key=lambda e: -e.device_time_total)
+        total = sum(e.device_time_total for e in evs)
+        kernel_table = {"device_ms_per_step": total / 2e3,
+                        "top": [{"kernel": e.key[:100], "ms_per_step": round(e.device_time_total / 2e3, 3),
+                                 "launches_per_step": e.count // 2} for e in evs[:25]]}
+
     t = torch.tensor([ms, e2e_ms_local], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -305,6 +320,8 @@ def run_config(name: str, args, ctx, impl: str = "b200") -> dict:
         "final_loss": last,
         "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30,
     }
+    if kernel_table is not None:
+        line["kernel_table"] = kernel_table
     if impl == "baseline":
         from fms_acceleration_b200.baseline import reference_kernels_status
 
@@ -433,6 +450,8 @@ def main() -> int:
                     help="run the comparison arm with activation checkpointing (the reference's benchmark default)")
     ap.add_argument("--gradient-checkpointing", action="store_true", help="activation checkpointing in the product arm")
     ap.add_argument("--no-selfcheck", action="store_true")
+    ap.add_argument("--kernel-table", action="store_true",
+                    help="after the timed regions, profile two more steps and report device time per kernel")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)

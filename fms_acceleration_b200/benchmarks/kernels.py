@@ -184,6 +184,11 @@ def bench_elementwise(a):
     t = timeit(lambda: ACT.glu_fwd(gu[:, :I], gu[:, I:], "silu"), a.iters, a.warmup, a.flush)
     by = 3.0 * T * I * 2
     print(json.dumps({"kernel": "swiglu_fwd", "ms": t, "gbs": by / t / 1e6, "frac_of_%s_hbm" % pk["source"]: by / t / 1e6 / pk["hbm_gbs"]}))
+    dh = torch.randn(T, I, device="cuda", dtype=torch.bfloat16)
+    de, dg = torch.empty_like(dh), torch.empty_like(dh)
+    t = timeit(lambda: ACT.glu_bwd(dh, gu[:, :I], gu[:, I:], "silu", de=de, dg=dg), a.iters, a.warmup, a.flush)
+    by = 5.0 * T * I * 2
+    print(json.dumps({"kernel": "swiglu_bwd", "ms": t, "gbs": by / t / 1e6, "frac_of_%s_hbm" % pk["source"]: by / t / 1e6 / pk["hbm_gbs"]}))
 
 
 def bench_grouped(a):
@@ -240,6 +245,7 @@ def bench_reference(a):
 
     dev = torch.device("cuda", torch.cuda.current_device())
     T, H, I_, V = a.tokens, 4096, 14336, 32000
+    Te = 4 * T  # rows of the element-wise comparisons: large enough that device time, not the host, is what is timed
     out = []
 
     def both(name, mine, ref):
@@ -254,23 +260,24 @@ def bench_reference(a):
     norm = torch.nn.Module()
     norm.weight = torch.nn.Parameter(torch.ones(H, device=dev, dtype=torch.bfloat16))
     norm.variance_epsilon = 1e-6
-    x = torch.randn(T, H, device=dev, dtype=torch.bfloat16, requires_grad=True)
-    gy = torch.randn(T, H, device=dev, dtype=torch.bfloat16)
+    x = torch.randn(Te, H, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    gy = torch.randn(Te, H, device=dev, dtype=torch.bfloat16)
 
     def mine_rms():
-        y, _ = RN.rmsnorm(x, norm.weight, 1e-6)
-        torch.autograd.grad(y, (x, norm.weight), gy)
+        y = RN.rmsnorm(x, norm.weight, 1e-6)
+        torch.autograd.grad(y, (x,), gy)  # like the reference: no weight gradient (frozen norms under LoRA)
 
     def ref_rms():
         y = rms.fast_rms_layernorm(norm, x)
-        torch.autograd.grad(y, (x,), gy)  # the reference's kernel gives no weight gradient (frozen norms under LoRA)
+        torch.autograd.grad(y, (x,), gy)
 
-    both(f"rmsnorm fwd+bwd [{T}x{H}]", mine_rms, ref_rms)
+    both(f"rmsnorm fwd+bwd [{Te}x{H}]", mine_rms, ref_rms)
+    del x, gy
     # SwiGLU forward + backward, intermediate 14336
     glu = BK._load_reference("fms_acceleration_foak", "fused_ops.unsloth_lora.swiglu")
-    e = torch.randn(T, I_, device=dev, dtype=torch.bfloat16, requires_grad=True)
-    g = torch.randn(T, I_, device=dev, dtype=torch.bfloat16, requires_grad=True)
-    gh = torch.randn(T, I_, device=dev, dtype=torch.bfloat16)
+    e = torch.randn(Te, I_, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    g = torch.randn(Te, I_, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    gh = torch.randn(Te, I_, device=dev, dtype=torch.bfloat16)
 
     def mine_glu():
         h = ACT.glu(e, g, "silu")
@@ -280,7 +287,8 @@ def bench_reference(a):
         h = BK._RefSwiGLU.apply(e, g, glu)
         torch.autograd.grad(h, (e, g), gh)
 
-    both(f"swiglu fwd+bwd [{T}x{I_}]", mine_glu, ref_glu)
+    both(f"swiglu fwd+bwd [{Te}x{I_}]", mine_glu, ref_glu)
+    del e, g, gh
     # fused linear + cross entropy, vocabulary 32000
     lce = BK._load_reference("fms_acceleration_foak", "fused_ops.liger_ce.fused_linear_cross_entropy_loss")
     hid = torch.randn(T, H, device=dev, dtype=torch.bfloat16, requires_grad=True)

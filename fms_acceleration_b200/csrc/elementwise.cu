@@ -177,20 +177,33 @@ rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* _
       }
     }
   }
+  // Rows are software-pipelined: the 16-byte loads of the NEXT row (x, dy and the incoming residual gradient) are
+  // issued before this row's block-wide reduction, so a CTA always has two rows' worth of loads in flight.
+  Vec8<T> xn[MAXV], dyn[MAXV], rn[MAXV];
+  auto fetch = [&](int row) {
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j) {
+      const int v = threadIdx.x + j * NORM_THREADS;
+      if (v < nvec) {
+        xn[j].load(x + (long long)row * H + v * 8);
+        dyn[j].load(dy + (long long)row * H + v * 8);
+        if (dres_in != nullptr) rn[j].load(dres_in + (long long)row * H + v * 8);
+      }
+    }
+  };
+  if ((int)blockIdx.x < rows) fetch(blockIdx.x);
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const float inv = inv_rms[row];
-    float xh[MAXV][8], g[MAXV][8];
+    float xh[MAXV][8], g[MAXV][8], rf[MAXV][8];
     float dot = 0.f;
 #pragma unroll
     for (int j = 0; j < MAXV; ++j) {
       const int v = threadIdx.x + j * NORM_THREADS;
       if (v < nvec) {
-        Vec8<T> a, b;
         float dyf[8];
-        a.load(x + (long long)row * H + v * 8);
-        a.to_float(xh[j]);
-        b.load(dy + (long long)row * H + v * 8);
-        b.to_float(dyf);
+        xn[j].to_float(xh[j]);
+        dyn[j].to_float(dyf);
+        if (dres_in != nullptr) rn[j].to_float(rf[j]);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           xh[j][i] *= inv;
@@ -200,6 +213,7 @@ rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* _
         }
       }
     }
+    if (row + (int)gridDim.x < rows) fetch(row + gridDim.x);
     const float tot = block_sum(dot, red);
     const float c = tot / (float)H;
 #pragma unroll
@@ -210,12 +224,8 @@ rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* _
 #pragma unroll
         for (int i = 0; i < 8; ++i) out[i] = inv * (g[j][i] - xh[j][i] * c);
         if (dres_in != nullptr) {
-          Vec8<T> r;
-          float rf[8];
-          r.load(dres_in + (long long)row * H + v * 8);
-          r.to_float(rf);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) out[i] += rf[i];
+          for (int i = 0; i < 8; ++i) out[i] += rf[j][i];
         }
         Vec8<T> o;
         o.from_float(out);
@@ -331,14 +341,19 @@ __global__ void glu_fwd_kernel(const T* __restrict__ e, const T* __restrict__ g,
   if (rows_dev != nullptr) rows = min(rows, *rows_dev);
   const int vec_per_row = I / 8;
   const long long total = (long long)rows * vec_per_row;
-  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
-       idx += (long long)gridDim.x * blockDim.x) {
-    const long long r = idx / vec_per_row;
-    const int c = (int)(idx % vec_per_row) * 8;
-    Vec8<T> a, b;
-    float ef[8], gf[8], out[8];
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  // two independent vectors per thread and trip: four 16-byte loads in flight before the first use
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += 2 * stride) {
+    const long long idx2 = idx + stride;
+    const bool two = idx2 < total;
+    const long long r = idx / vec_per_row, r2 = two ? idx2 / vec_per_row : r;
+    const int c = (int)(idx % vec_per_row) * 8, c2 = two ? (int)(idx2 % vec_per_row) * 8 : c;
+    Vec8<T> a, b, a2, b2;
     a.load(e + r * se + c);
     b.load(g + r * sg + c);
+    a2.load(e + r2 * se + c2);
+    b2.load(g + r2 * sg + c2);
+    float ef[8], gf[8], out[8];
     a.to_float(ef);
     b.to_float(gf);
 #pragma unroll
@@ -346,6 +361,14 @@ __global__ void glu_fwd_kernel(const T* __restrict__ e, const T* __restrict__ g,
     Vec8<T> o;
     o.from_float(out);
     o.store(h + r * sh + c);
+    if (two) {
+      a2.to_float(ef);
+      b2.to_float(gf);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) out[i] = round_to<T>(act_fwd(ef[i], act)) * gf[i];
+      o.from_float(out);
+      o.store(h + r2 * sh + c2);
+    }
   }
 }
 

@@ -16,7 +16,14 @@
 // each weight tile would be expanded again by every row tile; there the framework dequantises once into
 // an L2-resident 16-bit buffer and runs gemm_tcgen05.cu.
 //
-// Reference counterparts: bitsandbytes' cgemm_4bit_inference_naive / dequantize + matmul as called from
+// The same kernel serves GPTQ int4 weights (template parameter GPTQ): qweight [K/8, N] int32 holds eight consecutive
+// k of one output column per word, which is exactly one 16-byte chunk of the K-major operand row; scales [K/g, N]
+// and packed zero points [K/g, N/8] are per group of g input features (g a multiple of 64, groups in order).
+// A dequant warp reads 32 neighbouring columns per load (coalesced) and writes 32 swizzled rows.  Reference
+// counterpart: the fused dequantise-and-matmul Triton kernels of
+// fms_acceleration_peft/gptqmodel/nn_modules/triton_utils/kernels.py:105-201.
+//
+// Reference counterparts (NF4 / FP4): bitsandbytes' cgemm_4bit_inference_naive / dequantize + matmul as called from
 // fms_acceleration_foak/fused_ops/unsloth_lora/utils.py:119-136,190-203,262-279 and the NCCL all-gather
 // of the FSDP-sharded packed parameter that precedes them.
 //
@@ -44,6 +51,12 @@ struct Q4Params {
   const float* absmax2;      // [N*K/64/256]
   float offset;
   float code16[16];
+  // GPTQ int4 (template parameter GPTQ = 1): W[k, n] = scales[g, n] * (q[k, n] - (zero[g, n] + zero_offset)), g = k / group
+  const uint32_t* gq_weight;  // [K/8, N]
+  const uint16_t* gq_scales;  // [K/group, N] in the compute format
+  const uint32_t* gq_zeros;   // [K/group, N/8]
+  int gq_group;               // input features per group: a multiple of 64
+  int gq_zero_offset;
   void* D;
   long long ldd;
   float alpha;
@@ -82,7 +95,7 @@ __device__ __forceinline__ uint32_t q4_pack2(float a, float b, int fmt) {
   return fmt == 1 ? pack_bf16x2(a, b) : pack_f16x2(a, b);
 }
 
-template <int BN>
+template <int BN, int GPTQ>
 __global__ void __launch_bounds__(64 + Q4_DQ_THREADS, 1)
 gemm_q4_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmXa,
                      const __grid_constant__ CUtensorMap tmBl, const Q4Params p) {
@@ -166,8 +179,10 @@ gemm_q4_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
     constexpr int TPR = Q4_DQ_THREADS / BN;  // threads per weight row
     constexpr int EPT = Q4_BK / TPR;     // elements per thread and K block: 32, 16 or 8
     const int tid = threadIdx.x - 64;    // 0..Q4_DQ_THREADS-1
-    const int r = tid / TPR;             // row inside the tile
-    const int part = tid % TPR;          // which slice of the row's 64 elements
+    // NF4 / FP4: a row's bytes are contiguous, neighbouring threads share a row.  GPTQ: a word's neighbours in memory
+    // are the same k of the next columns, so neighbouring threads take neighbouring rows of the tile.
+    const int r = GPTQ ? tid % BN : tid / TPR;     // row inside the tile
+    const int part = GPTQ ? tid / BN : tid % TPR;  // which slice of the row's 64 elements
     const int n = n0 + r;
     const bool row_ok = n < p.N;
     bool ok = true;
@@ -184,6 +199,17 @@ gemm_q4_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       sq[slot] = 0u;
       s2[slot] = 0.f;
       if (!row_ok || kb >= p.kblocks1) return;
+      if constexpr (GPTQ) {
+        const int g = (kb * Q4_BK) / p.gq_group;
+        const uint16_t sc = p.gq_scales[(long long)g * p.N + n];
+        sq[slot] = __float_as_uint(p.fmt == 1 ? __uint_as_float((uint32_t)sc << 16) : __half2float(__ushort_as_half(sc)));
+        const uint32_t zw = p.gq_zeros[(long long)g * (p.N >> 3) + (n >> 3)];
+        s2[slot] = (float)(int)(((zw >> ((n & 7) * 4)) & 15u) + p.gq_zero_offset);
+#pragma unroll
+        for (int i = 0; i < WPT; ++i)
+          w[slot][i] = q4_ld4(reinterpret_cast<const uint8_t*>(p.gq_weight + (long long)(kb * 8 + part * WPT + i) * p.N + n));
+        return;
+      }
       const long long e0 = (long long)n * p.K + (long long)kb * Q4_BK;  // first element of the 64-block
       const long long blk = e0 >> 6;
       if (p.absmax_q != nullptr) {
@@ -212,7 +238,9 @@ gemm_q4_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
         const int kb = kb0 + j;
         if (kb >= p.kblocks1 || !ok) break;
         const int s = kb % Q4_STAGES;
-        const float scale = p.absmax_q != nullptr ? s_code256[sq[j]] * s2[j] + p.offset : __uint_as_float(sq[j]);
+        const float scale = GPTQ ? __uint_as_float(sq[j])
+                                 : (p.absmax_q != nullptr ? s_code256[sq[j]] * s2[j] + p.offset : __uint_as_float(sq[j]));
+        const float zs = GPTQ ? -s2[j] * scale : 0.f;  // (q - z) * s = q * s - z * s
         if (!mbar_wait(bar_empty(s), ((kb / Q4_STAGES) & 1) ^ 1u, p.status, kTimeoutDequant)) { ok = false; break; }
         // one 32-bit word = 8 values = one 16-byte chunk of the swizzled row
 #pragma unroll
@@ -221,7 +249,10 @@ gemm_q4_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
 #pragma unroll
           for (int b = 0; b < 4; ++b) {
             const uint32_t byte = (w[j][i] >> (8 * b)) & 0xffu;
-            o[b] = q4_pack2(s_code[byte >> 4] * scale, s_code[byte & 15] * scale, p.fmt);
+            if constexpr (GPTQ)  // low nibble first: the smaller k
+              o[b] = q4_pack2(fmaf((float)(byte & 15u), scale, zs), fmaf((float)(byte >> 4), scale, zs), p.fmt);
+            else
+              o[b] = q4_pack2(s_code[byte >> 4] * scale, s_code[byte & 15] * scale, p.fmt);
           }
           const int chunk = part * WPT + i;  // 0..7 within the row
           const uint32_t addr = sB(s) + static_cast<uint32_t>(r * 128 + ((chunk ^ (r & 7)) << 4));
@@ -277,19 +308,34 @@ gemm_q4_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
 
 using namespace fmsb;
 
-template <int BN>
+template <int BN, int GPTQ>
 static int q4_launch(const CUtensorMap& tx, const CUtensorMap& txa, const CUtensorMap& tbl, const Q4Params& p,
                      cudaStream_t stream) {
   static bool cfg = false;
   if (!cfg) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_q4_fused_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_q4_fused_kernel<BN, GPTQ>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Q4Cfg<BN>::kSmemBytes);
     if (e != cudaSuccess) return (int)e;
     cfg = true;
   }
   dim3 grid((p.N + BN - 1) / BN, (p.M + Q4_BM - 1) / Q4_BM);
-  gemm_q4_fused_kernel<BN><<<grid, 64 + Q4_DQ_THREADS, Q4Cfg<BN>::kSmemBytes, stream>>>(tx, txa, tbl, p);
+  gemm_q4_fused_kernel<BN, GPTQ><<<grid, 64 + Q4_DQ_THREADS, Q4Cfg<BN>::kSmemBytes, stream>>>(tx, txa, tbl, p);
   return (int)cudaGetLastError();
+}
+
+static int q4_maps(CUtensorMap* tx, CUtensorMap* txa, CUtensorMap* tbl, const void* x, long long ldx, const void* xa,
+                   long long ldxa, const void* bl, long long ldbl, int r2, int M, int N, int K, int bn) {
+  using namespace fmsb_host;
+  int rc;
+  if ((rc = make_tmap_2d_16b(tx, x, M, K, ldx, 128, 64))) return rc;
+  if (xa != nullptr) {
+    if ((rc = make_tmap_2d_16b(txa, xa, M, r2, ldxa, 128, 64))) return rc;
+    if ((rc = make_tmap_2d_16b(tbl, bl, N, r2, ldbl, bn, 64))) return rc;
+  } else {
+    *txa = *tx;
+    *tbl = *tx;
+  }
+  return 0;
 }
 
 // x [M, K] (ldx), packed shards (world pointers, shard_bytes each; world = 1: one local pointer), scales either
@@ -318,17 +364,37 @@ extern "C" int fmsb_gemm_q4_fused(const void* x, long long ldx, void* const* pac
   for (int i = 0; i < 16; ++i) p.code16[i] = code16_host[i];
   p.D = y; p.ldd = ldy; p.alpha = alpha; p.fmt = fmt; p.status = status;
   CUtensorMap tx, txa, tbl;
-  int rc;
-  if ((rc = make_tmap_2d_16b(&tx, x, M, K, ldx, 128, 64))) return rc;
-  if (xa != nullptr) {
-    if ((rc = make_tmap_2d_16b(&txa, xa, M, r2, ldxa, 128, 64))) return rc;
-    if ((rc = make_tmap_2d_16b(&tbl, bl, N, r2, ldbl, bn, 64))) return rc;
-  } else {
-    txa = tx;
-    tbl = tx;
-  }
-  if (bn == 128) return q4_launch<128>(tx, txa, tbl, p, stream);
-  if (bn == 64) return q4_launch<64>(tx, txa, tbl, p, stream);
-  if (bn == 32) return q4_launch<32>(tx, txa, tbl, p, stream);
+  if (int rc = q4_maps(&tx, &txa, &tbl, x, ldx, xa, ldxa, bl, ldbl, r2, M, N, K, bn)) return rc;
+  if (bn == 128) return q4_launch<128, 0>(tx, txa, tbl, p, stream);
+  if (bn == 64) return q4_launch<64, 0>(tx, txa, tbl, p, stream);
+  if (bn == 32) return q4_launch<32, 0>(tx, txa, tbl, p, stream);
+  return -2;
+}
+
+// GPTQ int4 form: y [M, N] = alpha * (x [M, K] . W [K, N] + xa [M, R] . bl [N, R]^T) with W given as qweight [K/8, N]
+// (int32, eight k per word), scales [K/group, N] (16-bit, the format of x), qzeros [K/group, N/8] (int32) and
+// zero_offset (1 for checkpoints that store the zero point minus one).  Groups follow the input features in order
+// (no activation reordering) and group % 64 == 0; K % 64 == 0, N % 8 == 0; bn in {32, 64, 128}.
+extern "C" int fmsb_gemm_gptq_fused(const void* x, long long ldx, const void* qweight, const void* scales,
+                                    const void* qzeros, int group, int zero_offset, const void* xa, long long ldxa,
+                                    const void* bl, long long ldbl, int r2, void* y, long long ldy, float alpha, int M,
+                                    int N, int K, int fmt, int bn, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K % 64 != 0 || N % 8 != 0 || (ldx % 8) || (ldy % 8) || group <= 0 || group % 64 != 0 || K % group != 0) return -2;
+  if (qweight == nullptr || scales == nullptr || qzeros == nullptr) return -2;
+  if (xa != nullptr && ((ldxa % 8) || (ldbl % 8) || r2 <= 0 || bl == nullptr)) return -2;
+  Q4Params p{};
+  p.M = M; p.N = N; p.K = K;
+  p.kblocks1 = K / 64;
+  p.kblocks2 = xa != nullptr ? (r2 + 63) / 64 : 0;
+  p.world = 1;
+  p.gq_weight = (const uint32_t*)qweight; p.gq_scales = (const uint16_t*)scales; p.gq_zeros = (const uint32_t*)qzeros;
+  p.gq_group = group; p.gq_zero_offset = zero_offset;
+  p.D = y; p.ldd = ldy; p.alpha = alpha; p.fmt = fmt; p.status = status;
+  CUtensorMap tx, txa, tbl;
+  if (int rc = q4_maps(&tx, &txa, &tbl, x, ldx, xa, ldxa, bl, ldbl, r2, M, N, K, bn)) return rc;
+  if (bn == 128) return q4_launch<128, 1>(tx, txa, tbl, p, stream);
+  if (bn == 64) return q4_launch<64, 1>(tx, txa, tbl, p, stream);
+  if (bn == 32) return q4_launch<32, 1>(tx, txa, tbl, p, stream);
   return -2;
 }

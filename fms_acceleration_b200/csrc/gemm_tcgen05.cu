@@ -54,8 +54,8 @@ struct GemmParams {
   const int* seg_off;        // [n_groups + 1] segment starts in rows, multiples of 128 (device memory)
   int b_group_rows;          // rows of B that belong to one group
   int b2_group_rows;         // rows of B2 that belong to one group (mode 1 with a second operand pair)
-  int n_split;               // > 0: output columns >= n_split take their B tiles from the second B map at column - n_split
-                             //      (two weight matrices side by side in one pass over A; needs kblocks2 == 0)
+  int n_split;               // > 0: output columns >= n_split take their B tiles from the side-by-side map at
+                             //      column - n_split (two weight matrices in one pass over A)
   int c_fp32;                // C holds fp32 (accumulating into an fp32 D over several launches)
   int tma_store;             // CTA-pair kernel: D (16-bit) leaves through shared memory and bulk tensor stores
   long long d_group_stride;  // elements between the D matrices of consecutive groups (mode 2)
@@ -302,7 +302,7 @@ template <int BN, int A_MN, int B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
                     const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
-                    const GemmParams p) {
+                    const __grid_constant__ CUtensorMap tmBalt, const GemmParams p) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzled tiles need 1024-byte alignment
@@ -338,6 +338,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_const
         prefetch_tmap(&tmA2);
         prefetch_tmap(&tmB2);
       }
+      if (p.n_split > 0) prefetch_tmap(&tmBalt);
     }
     __syncwarp();
     tmem_alloc(holder, Cfg::kTmemCols);
@@ -366,10 +367,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_const
           }
           mbar_expect_tx(full_bar(stage), Cfg::kStageBytes);
           const bool second = kb >= ti.kblocks1;
-          const bool alt = p.n_split > 0 && ti.n0 >= p.n_split;  // right-hand weight matrix of a side-by-side pair
+          // right-hand weight matrix of a side-by-side pair; the second operand pair spans all N columns itself
+          const bool alt = !second && p.n_split > 0 && ti.n0 >= p.n_split;
           const int n0 = alt ? ti.n0 - p.n_split : ti.n0;
           const CUtensorMap* ta = second ? &tmA2 : &tmA1;
-          const CUtensorMap* tb = (second || alt) ? &tmB2 : &tmB1;
+          const CUtensorMap* tb = second ? &tmB2 : (alt ? &tmBalt : &tmB1);
           const int k0 = second ? (kb - ti.kblocks1) * BK : ti.k_begin + kb * BK;
           // the group offset applies to B's row coordinate: the k rows of an MN-major B, the n rows of a K-major B
           const int brow = second ? ti.b2_row_off : ti.b_row_off;
@@ -811,7 +813,7 @@ int sm_count() {
 
 template <int BN, int A_MN, int B_MN>
 int launch_gemm(const CUtensorMap& a1, const CUtensorMap& b1, const CUtensorMap& a2, const CUtensorMap& b2,
-                const fmsb::GemmParams& p, int max_ctas, cudaStream_t stream) {
+                const CUtensorMap& balt, const fmsb::GemmParams& p, int max_ctas, cudaStream_t stream) {
   using Cfg = fmsb::GemmCfg<BN>;
   auto kern = fmsb::gemm_tcgen05_kernel<BN, A_MN, B_MN>;
   static bool configured = false;
@@ -827,7 +829,7 @@ int launch_gemm(const CUtensorMap& a1, const CUtensorMap& b1, const CUtensorMap&
     if (tiles < ctas) ctas = tiles;
   }
   if (ctas <= 0) return 0;
-  kern<<<ctas, fmsb::kGemmThreads, Cfg::kSmemBytes, stream>>>(a1, b1, a2, b2, p);
+  kern<<<ctas, fmsb::kGemmThreads, Cfg::kSmemBytes, stream>>>(a1, b1, a2, b2, balt, p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -934,7 +936,7 @@ static int gemm_impl(const void* A1, long long lda1, const void* B1, long long l
   if (K1 <= 0 || K2 < 0) return -2;
   if ((lda1 % 8) || (ldb1 % 8) || (K2 > 0 && ((lda2 % 8) || (ldb2 % 8)))) return -2;
   if (b_mn && bn < 64) return -3;
-  CUtensorMap ta1, tb1, ta2, tb2;
+  CUtensorMap ta1, tb1, ta2, tb2, tbalt;
   int rc;
   // CTA pairs: plain mode, 256-column tiles, enough 256 x 256 tiles to fill the machine about twice
   const bool use_pair = mode == 0 && bn == 256 && g_pair_mode != 0 && M >= 256 && N >= 256 &&
@@ -950,24 +952,29 @@ static int gemm_impl(const void* A1, long long lda1, const void* B1, long long l
   };
   // with n_split every one of the two side-by-side weight matrices is n_split columns wide
   const long long n_each = (gx != nullptr && gx->n_split > 0) ? gx->n_split : N;
-  auto mk_b = [&](CUtensorMap* t, const void* B, long long ldb, int K) {
-    if (b_mn) return make_tmap_2d_16b(t, B, b_rows > 0 ? b_rows : K, b_cols > 0 ? b_cols : n_each, ldb, 64, 64);
-    return make_tmap_2d_16b(t, B, b_rows > 0 ? b_rows : N, b_cols > 0 ? b_cols : K, ldb, b_box_rows, 64);
+  auto mk_b = [&](CUtensorMap* t, const void* B, long long ldb, int K, long long n_cols, long long rows) {
+    if (b_mn) return make_tmap_2d_16b(t, B, rows > 0 ? rows : K, b_cols > 0 ? b_cols : n_cols, ldb, 64, 64);
+    return make_tmap_2d_16b(t, B, rows > 0 ? rows : N, b_cols > 0 ? b_cols : K, ldb, b_box_rows, 64);
   };
+  // stored rows of the second pair's B: its own group height times the number of groups (a low-rank factor is far
+  // shorter than the weight it sits beside), so that reads past its end are zero-filled, not taken from memory
+  const long long b2_rows = (gx != nullptr && gx->b2_group_rows > 0 && n_groups > 0)
+                                ? (long long)gx->b2_group_rows * n_groups : b_rows;
   if ((rc = mk_a(&ta1, A1, lda1, K1))) return rc;
-  if ((rc = mk_b(&tb1, B1, ldb1, K1))) return rc;
+  if ((rc = mk_b(&tb1, B1, ldb1, K1, n_each, b_rows))) return rc;
   if (K2 > 0) {
-    if (gx != nullptr && gx->n_split > 0) return -2;  // the second B map is taken
+    // the second pair covers all N output columns, also beside a side-by-side pair of first operands
     if ((rc = mk_a(&ta2, A2, lda2, K2))) return rc;
-    if ((rc = mk_b(&tb2, B2, ldb2, K2))) return rc;
+    if ((rc = mk_b(&tb2, B2, ldb2, K2, N, b2_rows))) return rc;
   } else {
     ta2 = ta1;
     tb2 = tb1;
-    if (gx != nullptr && gx->n_split > 0) {
-      if (gx->B_alt == nullptr || gx->n_split % bn != 0 || gx->n_split >= N) return -2;
-      // same shape as B1: the column extent of one matrix is n_split (MN-major) / its row extent per group (K-major)
-      if ((rc = mk_b(&tb2, gx->B_alt, ldb1, K1))) return rc;
-    }
+  }
+  tbalt = tb1;
+  if (gx != nullptr && gx->n_split > 0) {
+    if (gx->B_alt == nullptr || gx->n_split % bn != 0 || gx->n_split >= N) return -2;
+    // same shape as B1: the column extent of one matrix is n_split (MN-major) / its row extent per group (K-major)
+    if ((rc = mk_b(&tbalt, gx->B_alt, ldb1, K1, n_each, b_rows))) return rc;
   }
   fmsb::GemmParams p;
   p.M = M;
@@ -1014,11 +1021,11 @@ static int gemm_impl(const void* A1, long long lda1, const void* B1, long long l
   }
 #define FMSB_DISPATCH(BNV)                                                                          \
   if (bn == BNV) {                                                                                  \
-    if (!a_mn && !b_mn) return launch_gemm<BNV, 0, 0>(ta1, tb1, ta2, tb2, p, max_ctas, stream);     \
-    if (a_mn && !b_mn) return launch_gemm<BNV, 1, 0>(ta1, tb1, ta2, tb2, p, max_ctas, stream);      \
+    if (!a_mn && !b_mn) return launch_gemm<BNV, 0, 0>(ta1, tb1, ta2, tb2, tbalt, p, max_ctas, stream);     \
+    if (a_mn && !b_mn) return launch_gemm<BNV, 1, 0>(ta1, tb1, ta2, tb2, tbalt, p, max_ctas, stream);      \
     if constexpr (BNV >= 64) {                                                                      \
-      if (!a_mn && b_mn) return launch_gemm<BNV, 0, 1>(ta1, tb1, ta2, tb2, p, max_ctas, stream);    \
-      if (a_mn && b_mn) return launch_gemm<BNV, 1, 1>(ta1, tb1, ta2, tb2, p, max_ctas, stream);     \
+      if (!a_mn && b_mn) return launch_gemm<BNV, 0, 1>(ta1, tb1, ta2, tb2, tbalt, p, max_ctas, stream);    \
+      if (a_mn && b_mn) return launch_gemm<BNV, 1, 1>(ta1, tb1, ta2, tb2, tbalt, p, max_ctas, stream);     \
     }                                                                                               \
   }
   FMSB_DISPATCH(256)

@@ -5,7 +5,9 @@ Tensor layout is the GPTQ checkpoint layout the reference loads
 ``[in*bits/32, out]`` (consecutive input rows packed along the bit positions), ``qzeros`` int32
 ``[groups, out*bits/32]`` (packed along the output columns), ``scales`` ``[groups, out]``, ``g_idx`` int32
 ``[in]``, optional ``bias``.  ``forward`` is dequantise (``csrc/quant.cu``) followed by the tcgen05 GEMM with
-the dequantised ``[in, out]`` matrix as the MN-major operand, so no transpose is ever materialised.
+the dequantised ``[in, out]`` matrix as the MN-major operand, so no transpose is ever materialised; with few rows
+(generation, evaluation of short prompts) int4 weights are expanded inside the GEMM instead
+(``csrc/gemm_q4_fused.cu``, the counterpart of gptqmodel/nn_modules/triton_utils/kernels.py:105-201).
 """
 from __future__ import annotations
 
@@ -15,7 +17,7 @@ import torch
 from torch import nn
 
 from ..ops import quant as Q
-from ..ops.gemm import gemm
+from ..ops.gemm import FUSED_Q4_MAX_ROWS, gemm, gemm_gptq_fused
 
 
 class QuantLinear(nn.Module):
@@ -109,18 +111,31 @@ class QuantLinear(nn.Module):
     # ------------------------------------------------------------------ compute
     def dequantize(self, out=None, dtype=None) -> torch.Tensor:
         """Dense ``[in, out]`` weight."""
-        scales = self.scales
-        if dtype is not None and dtype != scales.dtype:
-            cached = getattr(self, "_scales_cast", None)
-            if cached is None or cached[0] != dtype or cached[1] is not self.scales:
-                cached = (dtype, self.scales, self.scales.to(dtype))  # the weights are frozen: convert once
-                self._scales_cast = cached
-            scales = cached[2]
+        scales = self._scales_as(dtype)
         g_idx = None if self._sequential_groups else self.g_idx
         return Q.gptq_dequant(self.qweight, scales, self.qzeros, g_idx if self.qweight.is_cuda else self.g_idx,
                               self.bits, self.group_size, self.zero_offset, out=out)
 
+    def _scales_as(self, dtype) -> torch.Tensor:
+        if dtype is None or dtype == self.scales.dtype:
+            return self.scales
+        cached = getattr(self, "_scales_cast", None)
+        if cached is None or cached[0] != dtype or cached[1] is not self.scales:
+            cached = (dtype, self.scales, self.scales.to(dtype))  # the weights are frozen: convert once
+            self._scales_cast = cached
+        return cached[2]
+
+    def fused_ok(self, x: torch.Tensor) -> bool:
+        """Few rows, int4, groups in order and a multiple of 64 wide: dequantise inside the GEMM."""
+        rows = x.numel() // x.shape[-1]
+        return (x.is_cuda and x.dtype in (torch.float16, torch.bfloat16) and self.bits == 4 and rows <= FUSED_Q4_MAX_ROWS
+                and self._sequential_groups and self.group_size % 64 == 0 and self.infeatures % self.group_size == 0
+                and self.infeatures % 64 == 0)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.fused_ok(x):
+            y = _GPTQFusedMatmul.apply(x, self)
+            return y if self.bias is None else y + self.bias.to(y.dtype)
         w = self.dequantize(dtype=x.dtype if x.dtype in (torch.float16, torch.bfloat16) else None)
         if x.is_cuda and x.dtype in (torch.float16, torch.bfloat16):
             y = _GPTQMatmul.apply(x, w)
@@ -132,6 +147,28 @@ class QuantLinear(nn.Module):
 
     def extra_repr(self):
         return f"in={self.infeatures}, out={self.outfeatures}, bits={self.bits}, group_size={self.group_size}"
+
+
+class _GPTQFusedMatmul(torch.autograd.Function):
+    """Forward through the fused int4 dequantise+GEMM kernel (few rows); the backward (dx only) expands the weight."""
+
+    @staticmethod
+    def forward(ctx, x, layer):
+        ctx.layer, ctx.shape = layer, x.shape
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.stride(1) != 1 or x2.stride(0) % 8:
+            x2 = x2.contiguous()
+        y = gemm_gptq_fused(x2, layer.qweight, layer._scales_as(x.dtype), layer.qzeros, layer.group_size,
+                            layer.zero_offset)
+        return y.view(*x.shape[:-1], layer.outfeatures)
+
+    @staticmethod
+    def backward(ctx, dy):
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if dy2.stride(1) != 1 or dy2.stride(0) % 8:
+            dy2 = dy2.contiguous()
+        w = ctx.layer.dequantize(dtype=dy.dtype)
+        return gemm(dy2, w).view(ctx.shape), None
 
 
 class _GPTQMatmul(torch.autograd.Function):

@@ -253,3 +253,46 @@ def gemm_q4_fused(x: torch.Tensor, qs, xa: torch.Tensor | None = None, bl: torch
         N.dtype_code(x.dtype), bn, st.data_ptr(), N.stream_ptr())
     N.check(rc, "fmsb_gemm_q4_fused")
     return out
+
+
+N.declare("fmsb_gemm_gptq_fused", [_ct.c_void_p, _ct.c_longlong, _ct.c_void_p, _ct.c_void_p, _ct.c_void_p, _ct.c_int,
+                                    _ct.c_int, _ct.c_void_p, _ct.c_longlong, _ct.c_void_p, _ct.c_longlong, _ct.c_int,
+                                    _ct.c_void_p, _ct.c_longlong, _ct.c_float, _ct.c_int, _ct.c_int, _ct.c_int,
+                                    _ct.c_int, _ct.c_int, _ct.c_void_p, _ct.c_void_p])
+
+
+def gemm_gptq_fused(x: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, qzeros: torch.Tensor,
+                    group_size: int, zero_offset: int = 0, xa: torch.Tensor | None = None,
+                    bl: torch.Tensor | None = None, alpha: float = 1.0, out: torch.Tensor | None = None,
+                    bn: int | None = None) -> torch.Tensor:
+    """``x [M, K] @ W [K, N] (+ xa [M, R] @ bl [N, R]^T)`` for a GPTQ int4 weight, dequantised inside the GEMM.
+
+    ``qweight [K/8, N]`` int32, ``scales [K/group, N]`` in the dtype of ``x``, ``qzeros [K/group, N/8]`` int32; groups
+    in input-feature order (no activation reordering), ``group_size % 64 == 0``.  The few-row counterpart of the
+    reference's fused Triton kernels (gptqmodel/nn_modules/triton_utils/kernels.py:105-201); with many rows the
+    weight is dequantised once (``ops.quant.gptq_dequant``) and the plain GEMM runs.
+    """
+    K, Nn = qweight.shape[0] * 8, qweight.shape[1]
+    M = x.shape[0]
+    if x.dtype not in (torch.bfloat16, torch.float16) or x.stride(1) != 1 or x.stride(0) % 8 or K % 64 or Nn % 8:
+        raise ValueError("x must be a 16-bit row-major matrix; K % 64 == 0 and N % 8 == 0")
+    if group_size % 64 or K % group_size or scales.dtype != x.dtype or not (
+            qweight.is_contiguous() and scales.is_contiguous() and qzeros.is_contiguous()):
+        raise ValueError("group_size % 64 == 0, scales in the dtype of x, contiguous packed tensors")
+    if out is None:
+        out = torch.empty(M, Nn, dtype=x.dtype, device=x.device)
+    if bn is None:
+        bn = 128 if (Nn // 128) * ((M + 127) // 128) >= 148 else (64 if (Nn // 64) * ((M + 127) // 128) >= 148 else 32)
+    r2 = 0
+    if xa is not None:
+        if bl is None or xa.shape[0] != M or bl.shape[0] != Nn or xa.shape[1] != bl.shape[1]:
+            raise ValueError("LoRA pair: xa [M, R] and bl [N, R]")
+        r2 = xa.shape[1]
+    st = N.status_word(x.device)
+    rc = N.lib().fmsb_gemm_gptq_fused(
+        x.data_ptr(), x.stride(0), qweight.data_ptr(), scales.data_ptr(), qzeros.data_ptr(), int(group_size),
+        int(zero_offset), N.ptr(xa), xa.stride(0) if xa is not None else 0, N.ptr(bl),
+        bl.stride(0) if bl is not None else 0, r2, out.data_ptr(), out.stride(0), float(alpha), M, Nn, K,
+        N.dtype_code(x.dtype), bn, st.data_ptr(), N.stream_ptr())
+    N.check(rc, "fmsb_gemm_gptq_fused")
+    return out

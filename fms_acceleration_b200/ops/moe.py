@@ -365,42 +365,82 @@ def _one_ptr(t):
 
 
 # ------------------------------------------------------------------------------------------------ expert math
-def _experts_fwd_local(mctx, Xs, seg_off, w1, w3, w2, act, Ys=None):
-    """gate|up (one grouped GEMM over the two weight tensors), activation, down projection."""
+def _acc_gemm(acc, key, a, b, seg_off, n_groups, m, n, max_ctas):
+    """Per-group ``a^T b`` into ``acc[key]`` (fp32): the first token slice writes it, later slices add to it."""
+    if key not in acc:
+        acc[key] = grouped_gemm(a, b, seg_off, n_groups, mode=2, m=m, n=n, max_ctas=max_ctas)
+    else:
+        grouped_gemm(a, b, seg_off, n_groups, mode=2, m=m, n=n, out=acc[key], c=acc[key], beta=1.0, max_ctas=max_ctas)
+
+
+def _experts_fwd_local(mctx, Xs, seg_off, w1, w3, w2, act, Ys=None, lora=None):
+    """gate|up (one grouped GEMM over the two weight tensors), activation, down projection.
+
+    ``lora`` = (A13 [El, H, R13], B13 [El, R13, 2I], A2 [El, I, R2], B2 [El, R2, H]): per-expert low-rank factors,
+    gate and up side by side in A13 and block-diagonal in B13.  Each projection is then
+    ``rows . W_e + (rows . A_e) . B_e`` with the low-rank product accumulated into the same output tile as the
+    frozen weight's (the second operand pair of the grouped kernel), never a dense ``W + A B`` per expert.  What
+    the reference does in one Triton kernel (scattermoe_utils/khd/kernels/kernels.py:110-300)."""
     I_, El, H = mctx.I, mctx.E_local, mctx.H
-    gu = grouped_gemm(Xs, w1.view(El * H, I_), seg_off, El, mode=1, n=2 * I_, b_alt=w3.view(El * H, I_),
-                      max_ctas=mctx.gemm_ctas)
     used = seg_off[El:]  # rows in use (device scalar): the buffers are sized for the capacity, not for the load
+    if lora is None:
+        gu = grouped_gemm(Xs, w1.view(El * H, I_), seg_off, El, mode=1, n=2 * I_, b_alt=w3.view(El * H, I_),
+                          max_ctas=mctx.gemm_ctas)
+        hs = ACT.glu_fwd(gu[:, :I_], gu[:, I_:], act, rows_dev=used)
+        Ys = grouped_gemm(hs, w2.view(El * I_, H), seg_off, El, mode=1, n=H, out=Ys, max_ctas=mctx.gemm_ctas)
+        return gu, Ys, None
+    a13, b13, a2, b2 = lora
+    R13, R2 = a13.shape[2], a2.shape[2]
+    XA = grouped_gemm(Xs, a13.view(El * H, R13), seg_off, El, mode=1, n=R13, max_ctas=mctx.gemm_ctas)
+    gu = grouped_gemm(Xs, w1.view(El * H, I_), seg_off, El, mode=1, n=2 * I_, b_alt=w3.view(El * H, I_), a2=XA,
+                      b2=b13.view(El * R13, 2 * I_), max_ctas=mctx.gemm_ctas)
     hs = ACT.glu_fwd(gu[:, :I_], gu[:, I_:], act, rows_dev=used)
-    Ys = grouped_gemm(hs, w2.view(El * I_, H), seg_off, El, mode=1, n=H, out=Ys, max_ctas=mctx.gemm_ctas)
-    return gu, Ys
+    HA = grouped_gemm(hs, a2.view(El * I_, R2), seg_off, El, mode=1, n=R2, max_ctas=mctx.gemm_ctas)
+    Ys = grouped_gemm(hs, w2.view(El * I_, H), seg_off, El, mode=1, n=H, out=Ys, a2=HA, b2=b2.view(El * R2, H),
+                      max_ctas=mctx.gemm_ctas)
+    return gu, Ys, XA
 
 
-def _experts_bwd_local(mctx, Xs, gu, dYs, seg_off, w1, w3, w2, act, acc, need_dw=True):
-    """Gradients of the three expert weight tensors (accumulated into ``acc`` when it already holds a chunk) and the
-    input gradient in the expert-sorted layout.  ``gu`` is overwritten with the pre-activation gradients."""
+def _experts_bwd_local(mctx, Xs, gu, dYs, seg_off, w1, w3, w2, act, acc, need_dw=True, lora=None, XA=None):
+    """Gradients of the three expert weight tensors (accumulated into ``acc`` when it already holds a chunk), of the
+    low-rank factors when there are some, and the input gradient in the expert-sorted layout.  ``gu`` is overwritten
+    with the pre-activation gradients."""
     I_, El, H = mctx.I, mctx.E_local, mctx.H
+    nc = mctx.gemm_ctas
     used = seg_off[El:]
     hs = ACT.glu_fwd(gu[:, :I_], gu[:, I_:], act, rows_dev=used)
-    first = "dw2" not in acc
     if need_dw:
-        if first:
-            acc["dw2"] = grouped_gemm(hs, dYs, seg_off, El, mode=2, m=I_, n=H, max_ctas=mctx.gemm_ctas)
-        else:
-            grouped_gemm(hs, dYs, seg_off, El, mode=2, m=I_, n=H, out=acc["dw2"], c=acc["dw2"], beta=1.0,
-                         max_ctas=mctx.gemm_ctas)
-    dhs = grouped_gemm(dYs, w2.view(El * I_, H), seg_off, El, mode=1, b_mn=False, n=I_, max_ctas=mctx.gemm_ctas)
+        _acc_gemm(acc, "dw2", hs, dYs, seg_off, El, I_, H, nc)
+    dHA = None
+    if lora is not None:
+        a13, b13, a2, b2 = lora
+        R13, R2 = a13.shape[2], a2.shape[2]
+        HA = grouped_gemm(hs, a2.view(El * I_, R2), seg_off, El, mode=1, n=R2, max_ctas=nc)
+        _acc_gemm(acc, "db2", HA, dYs, seg_off, El, R2, H, nc)
+        dHA = grouped_gemm(dYs, b2.view(El * R2, H), seg_off, El, mode=1, b_mn=False, n=R2, max_ctas=nc)
+        _acc_gemm(acc, "da2", hs, dHA, seg_off, El, I_, R2, nc)
+    dhs = grouped_gemm(dYs, w2.view(El * I_, H), seg_off, El, mode=1, b_mn=False, n=I_, max_ctas=nc, a2=dHA,
+                       b2=(a2.view(El * I_, R2) if lora is not None else None))
     ACT.glu_bwd(dhs, gu[:, :I_], gu[:, I_:], act, de=gu[:, :I_], dg=gu[:, I_:], rows_dev=used)
     if need_dw:
         # [d gate | d up] side by side in gu: both weight gradients in one pass over Xs
-        if first:
-            acc["dw13"] = grouped_gemm(Xs, gu, seg_off, El, mode=2, m=H, n=2 * I_, max_ctas=mctx.gemm_ctas)
-        else:
-            grouped_gemm(Xs, gu, seg_off, El, mode=2, m=H, n=2 * I_, out=acc["dw13"], c=acc["dw13"], beta=1.0,
-                         max_ctas=mctx.gemm_ctas)
+        _acc_gemm(acc, "dw13", Xs, gu, seg_off, El, H, 2 * I_, nc)
     dXs = grouped_gemm(gu[:, :I_], w1.view(El * H, I_), seg_off, El, mode=1, b_mn=False, n=H, a2=gu[:, I_:],
-                       b2=w3.view(El * H, I_), max_ctas=mctx.gemm_ctas)
+                       b2=w3.view(El * H, I_), max_ctas=nc)
+    if lora is not None:
+        _acc_gemm(acc, "db13", XA, gu, seg_off, El, R13, 2 * I_, nc)
+        dXA = grouped_gemm(gu, b13.view(El * R13, 2 * I_), seg_off, El, mode=1, b_mn=False, n=R13, max_ctas=nc)
+        _acc_gemm(acc, "da13", Xs, dXA, seg_off, El, H, R13, nc)
+        grouped_gemm(dXA, a13.view(El * H, R13), seg_off, El, mode=1, b_mn=False, n=H, out=dXs, c=dXs, beta=1.0,
+                     max_ctas=nc)
     return dXs
+
+
+def _lora_grads(acc, lora, needs):
+    if lora is None:
+        return None, None, None, None
+    keys = ("da13", "db13", "da2", "db2")
+    return tuple(acc[k].to(t.dtype) if need and k in acc else None for k, t, need in zip(keys, lora, needs))
 
 
 def _weight_grads(mctx, acc, w1, w3, w2, needs):
@@ -415,7 +455,8 @@ class _Experts(torch.autograd.Function):
     """One rank owns every expert.  x [T,H], gates fp32 [T,k], idx int32 [T,k], w1/w3 [E,H,I], w2 [E,I,H] -> [T,H]."""
 
     @staticmethod
-    def forward(ctx, x, gates, idx, w1, w3, w2, mctx: MoEContext, act: str):
+    def forward(ctx, x, gates, idx, w1, w3, w2, mctx: MoEContext, act: str, *lora):
+        lora = lora if lora and lora[0] is not None else None
         T, H = x.shape
         dev, dt = x.device, x.dtype
         cap = mctx.cap = _round_up(T * mctx.k + mctx.E_local * 128, 128)  # exact upper bound: never overflows
@@ -423,16 +464,17 @@ class _Experts(torch.autograd.Function):
         Xs = torch.empty(cap, H, dtype=dt, device=dev)
         _zero_pad(mctx, Xs, seg_off, seg_cnt)
         _dispatch(mctx, x, idx, dest_row, None, _one_ptr(Xs), Xs.stride(0))
-        gu, Ys = _experts_fwd_local(mctx, Xs, seg_off, w1, w3, w2, act)
+        gu, Ys, XA = _experts_fwd_local(mctx, Xs, seg_off, w1, w3, w2, act, lora=lora)
         out = _combine(mctx, _one_ptr(Ys), Ys.stride(0), idx, dest_row, gates, T, H, dt, dev)
-        ctx.mctx, ctx.act = mctx, act
-        ctx.save_for_backward(gates, idx, w1, w3, w2, seg_off, seg_cnt, dest_row, gu, Xs, Ys)
+        ctx.mctx, ctx.act, ctx.has_lora = mctx, act, lora is not None
+        ctx.save_for_backward(gates, idx, w1, w3, w2, seg_off, seg_cnt, dest_row, gu, Xs, Ys, *((XA,) + lora if lora else ()))
         return out
 
     @staticmethod
     def backward(ctx, dout):
         mctx, act = ctx.mctx, ctx.act
-        gates, idx, w1, w3, w2, seg_off, seg_cnt, dest_row, gu, Xs, Ys = ctx.saved_tensors
+        gates, idx, w1, w3, w2, seg_off, seg_cnt, dest_row, gu, Xs, Ys, *rest = ctx.saved_tensors
+        XA, lora = (rest[0], tuple(rest[1:])) if ctx.has_lora else (None, None)
         dout = dout.contiguous()
         T, H = dout.shape
         El, cap = mctx.E_local, gu.shape[0]
@@ -453,14 +495,14 @@ class _Experts(torch.autograd.Function):
         N.check(rc, "fmsb_moe_rowdot_scale")
         acc: dict = {}
         need_dw = any(ctx.needs_input_grad[3:6])
-        dXs = _experts_bwd_local(mctx, Xs, gu, dYs, seg_off, w1, w3, w2, act, acc, need_dw)
+        dXs = _experts_bwd_local(mctx, Xs, gu, dYs, seg_off, w1, w3, w2, act, acc, need_dw, lora=lora, XA=XA)
         dx = _combine(mctx, _one_ptr(dXs), dXs.stride(0), idx, dest_row, None, T, H, dt, dev)
         dgate = torch.empty(T, mctx.k, dtype=torch.float32, device=dev)
         rc = N.lib().fmsb_moe_gather_scalar(_one_ptr(rdots), idx.data_ptr(), dest_row.data_ptr(), T * mctx.k, El,
                                             dgate.data_ptr(), 1, N.stream_ptr())
         N.check(rc, "fmsb_moe_gather_scalar")
         dw1, dw3, dw2 = _weight_grads(mctx, acc, w1, w3, w2, ctx.needs_input_grad[3:6])
-        return dx, dgate, None, dw1, dw3, dw2, None, None
+        return (dx, dgate, None, dw1, dw3, dw2, None, None) + (_lora_grads(acc, lora, ctx.needs_input_grad[8:12]) if lora else ())
 
 
 # ------------------------------------------------------------------------------------------------ expert parallel
@@ -564,7 +606,8 @@ class _ExpertsEP(torch.autograd.Function):
     """Expert-parallel form: this rank owns ``E / world`` experts (w1/w3 [E_local,H,I], w2 [E_local,I,H])."""
 
     @staticmethod
-    def forward(ctx, x, gates, idx, w1, w3, w2, mctx: MoEContext, act: str):
+    def forward(ctx, x, gates, idx, w1, w3, w2, mctx: MoEContext, act: str, *lora):
+        lora = lora if lora and lora[0] is not None else None
         T, H = x.shape
         dev, dt = x.device, x.dtype
         sh = mctx.ensure_shared(T, dt, dev)
@@ -591,21 +634,22 @@ class _ExpertsEP(torch.autograd.Function):
             _replicate(sh, ch, ch.Xs)
 
         def compute(ch):
-            ch.gu, ch.Ys = _experts_fwd_local(mctx, ch.Xs, ch.seg_off, w1, w3, w2, act)
+            ch.gu, ch.Ys, ch.XA = _experts_fwd_local(mctx, ch.Xs, ch.seg_off, w1, w3, w2, act, lora=lora)
 
         def pull(ch):
             _prereduce(sh, ch, ch.Ys, weighted=True)
             _pull(sh, mctx, ch, out, BAR_B)
 
         _pipeline(sh, chunks, push, compute, pull)
-        ctx.mctx, ctx.act, ctx.chunks = mctx, act, chunks
-        ctx.save_for_backward(gates, idx, w1, w3, w2)
+        ctx.mctx, ctx.act, ctx.chunks, ctx.has_lora = mctx, act, chunks, lora is not None
+        ctx.save_for_backward(gates, idx, w1, w3, w2, *(lora or ()))
         return out
 
     @staticmethod
     def backward(ctx, dout):
         mctx, act, chunks = ctx.mctx, ctx.act, ctx.chunks
-        gates, idx, w1, w3, w2 = ctx.saved_tensors
+        gates, idx, w1, w3, w2, *rest = ctx.saved_tensors
+        lora = tuple(rest) if ctx.has_lora else None
         sh = mctx.shared
         dout = dout.contiguous()
         T, H = dout.shape
@@ -632,7 +676,8 @@ class _ExpertsEP(torch.autograd.Function):
             N.check(rc, "fmsb_moe_rowdot_scale")
 
         def compute(ch):
-            ch.dXs = _experts_bwd_local(mctx, ch.Xs, ch.gu, ch.dYs, ch.seg_off, w1, w3, w2, act, acc, need_dw)
+            ch.dXs = _experts_bwd_local(mctx, ch.Xs, ch.gu, ch.dYs, ch.seg_off, w1, w3, w2, act, acc, need_dw, lora=lora,
+                                        XA=ch.XA)
 
         def pull(ch):
             _prereduce(sh, ch, ch.dXs, weighted=False)
@@ -646,12 +691,32 @@ class _ExpertsEP(torch.autograd.Function):
 
         _pipeline(sh, chunks, push, compute, pull)
         for ch in chunks:  # only now: the communication stream has finished reading them
-            ch.Xs = ch.gu = ch.Ys = ch.dYs = ch.rgate = ch.dXs = None
+            ch.Xs = ch.gu = ch.Ys = ch.dYs = ch.rgate = ch.dXs = ch.XA = None
         dw1, dw3, dw2 = _weight_grads(mctx, acc, w1, w3, w2, ctx.needs_input_grad[3:6])
-        return dx, dgate, None, dw1, dw3, dw2, None, None
+        return (dx, dgate, None, dw1, dw3, dw2, None, None) + (_lora_grads(acc, lora, ctx.needs_input_grad[8:12]) if lora else ())
 
 
-def experts_forward(x, gates, idx, w1, w3, w2, mctx: MoEContext, act="silu"):
-    if mctx.world > 1:
-        return _ExpertsEP.apply(x, gates, idx, w1, w3, w2, mctx, act)
-    return _Experts.apply(x, gates, idx, w1, w3, w2, mctx, act)
+def pack_expert_lora(a1, b1, a3, b3, a2, b2):
+    """Low-rank factors of the three expert projections in the layout the grouped kernel reads.
+
+    Inputs per projection: ``A [El, in, r]`` and ``B [El, r, out]``.  Returns ``(A13 [El, H, R13], B13 [El, R13, 2I],
+    A2 [El, I, R2], B2 [El, R2, H])`` with gate and up side by side (``A13 = [A1 | A3 | 0]``, ``B13`` block-diagonal)
+    and the ranks padded with zeros to the kernel's 64-element contraction block, so that one group's block never
+    reaches into the next group's rows.  Plain tensor ops: autograd carries the gradients back to the six factors."""
+    r = a1.shape[2]
+    I_ = b1.shape[2]
+    R13, R2 = _round_up(2 * r, 64), _round_up(r, 64)
+    z = a1.new_zeros
+    El, H = a1.shape[0], a1.shape[1]
+    A13 = torch.cat([a1, a3, z(El, H, R13 - 2 * r)], dim=2)
+    B13 = torch.cat([torch.cat([b1, z(El, r, I_)], dim=2), torch.cat([z(El, r, I_), b3], dim=2),
+                     z(El, R13 - 2 * r, 2 * I_)], dim=1)
+    A2 = torch.cat([a2, z(El, I_, R2 - r)], dim=2)
+    B2 = torch.cat([b2, z(El, R2 - r, b2.shape[2])], dim=1)
+    return A13.contiguous(), B13.contiguous(), A2.contiguous(), B2.contiguous()
+
+
+def experts_forward(x, gates, idx, w1, w3, w2, mctx: MoEContext, act="silu", lora=None):
+    """``lora``: the four tensors of :func:`pack_expert_lora`, or None."""
+    fn = _ExpertsEP if mctx.world > 1 else _Experts
+    return fn.apply(x, gates, idx, w1, w3, w2, mctx, act, *(lora or ()))

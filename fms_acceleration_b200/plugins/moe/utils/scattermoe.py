@@ -36,7 +36,8 @@ class ScatteredExperts(nn.Module):
             nn.init.normal_(self.lora_B)
 
     def effective_weight(self) -> torch.Tensor:
-        """Dense expert weights including the LoRA update (scale 1, as in the reference's kernels)."""
+        """Dense expert weights including the LoRA update (scale 1, as in the reference's kernels).  Used by the
+        library / CPU paths and as the oracle of the fused path, which never forms it."""
         if self.lora_A is None:
             return self.weight
         return self.weight + torch.bmm(self.lora_A, self.lora_B)
@@ -97,8 +98,14 @@ class ScatterMoE(nn.Module):
             x2 = x2.contiguous()
         logits, w, idx = self._compute_routing_weights(x2)
         if x2.is_cuda and x2.dtype in (torch.bfloat16, torch.float16) and self.backend == "fused":
-            out = MOE.experts_forward(x2, w, idx, self.w1.effective_weight(), self.w3.effective_weight(),
-                                      self.w2.effective_weight(), self._context(), self.activation)
+            lora = None
+            if self.w1.lora_A is not None:
+                # frozen expert weights plus per-expert low-rank factors: the low-rank products ride in the grouped
+                # GEMMs as a second operand pair, the dense W + A B is never formed
+                lora = MOE.pack_expert_lora(self.w1.lora_A, self.w1.lora_B, self.w3.lora_A, self.w3.lora_B,
+                                            self.w2.lora_A, self.w2.lora_B)
+            out = MOE.experts_forward(x2, w, idx, self.w1.weight, self.w3.weight, self.w2.weight, self._context(),
+                                      self.activation, lora=lora)
         elif self.expert_parallel:
             out = self._forward_library_ep(x2, w, idx)
         else:

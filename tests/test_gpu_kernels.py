@@ -306,6 +306,59 @@ def test_fused_q4_gemm_matches_dequant_then_gemm(M, Nn, K, bn, double_quant, lor
         assert torch.equal(y2, y)
 
 
+@pytest.mark.parametrize("M,Nn,K,gs,bn,dtype,zoff,lora", [(64, 512, 256, 128, 128, torch.float16, 0, False),
+                                                         (128, 384, 512, 64, 64, torch.bfloat16, 1, True),
+                                                         (200, 264, 1024, 1024, 32, torch.bfloat16, 0, True),
+                                                         (5, 4096, 4096, 128, None, torch.float16, 1, False)])
+def test_fused_gptq_gemm_matches_fp32_oracle(M, Nn, K, gs, bn, dtype, zoff, lora):
+    """GPTQ int4 weights expanded inside the GEMM (+ LoRA pair) against the fp32 formula scale * (q - zero)."""
+    from fms_acceleration_b200.ops.gemm import gemm_gptq_fused
+
+    torch.manual_seed(M + Nn)
+    wi = torch.randint(0, 16, (K, Nn), device=DEV)
+    zi = torch.randint(0, 15, (K // gs, Nn), device=DEV)
+    sc = (torch.rand(K // gs, Nn, device=DEV) * 0.02 + 0.001).to(dtype)
+    qw, qz = Q.gptq_pack(wi, 4), Q.gptq_pack_zeros(zi, 4)
+    g = (torch.arange(K, device=DEV) // gs).long()
+    W = sc[g].float() * (wi - (zi[g] + zoff)).float()  # [K, N]
+    x = (torch.randn(M, K, device=DEV) * 0.5).to(dtype)
+    ref = x.float() @ W
+    xa = bl = None
+    if lora:
+        xa = (torch.randn(M, 16, device=DEV) * 0.3).to(dtype)
+        bl = (torch.randn(Nn, 16, device=DEV) * 0.3).to(dtype)
+        ref = ref + xa.float() @ bl.float().t()
+    y = gemm_gptq_fused(x, qw, sc, qz, gs, zoff, xa, bl, bn=bn)
+    NV.check_status()
+    assert y.shape == (M, Nn)
+    assert (y.float() - ref).abs().max() <= 2e-2 * ref.abs().max() + 1e-3
+
+
+def test_gptq_quantlinear_few_rows_uses_the_fused_kernel():
+    """QuantLinear with a handful of rows: same numbers as dequantise-then-GEMM, forward and input gradient."""
+    from fms_acceleration_b200.nn import gptq as G
+
+    torch.manual_seed(4)
+    q = G.QuantLinear.random(512, 384, bits=4, group_size=128, dtype=torch.float16, device=DEV, scale_std=0.01)
+    x = (torch.randn(2, 5, 512, device=DEV) * 0.5).half().requires_grad_()
+    assert q.fused_ok(x)
+    y = q(x)
+    y.float().square().sum().backward()
+    NV.check_status()
+    gx = x.grad.clone()
+    x.grad = None
+    saved = G.FUSED_Q4_MAX_ROWS
+    G.FUSED_Q4_MAX_ROWS = 0
+    try:
+        assert not q.fused_ok(x)
+        y2 = q(x)
+        y2.float().square().sum().backward()
+    finally:
+        G.FUSED_Q4_MAX_ROWS = saved
+    assert (y.float() - y2.float()).abs().max() <= 1e-2 * y2.float().abs().max() + 1e-3
+    assert (gx.float() - x.grad.float()).abs().max() <= 2e-2 * x.grad.float().abs().max() + 1e-3
+
+
 def test_linear4bit_few_rows_uses_the_fused_kernel():
     """Same numbers as the dequantise-then-GEMM path, forward and backward, for a handful of rows."""
     from fms_acceleration_b200.nn import Linear4bit

@@ -66,6 +66,44 @@ def test_scattermoe_matches_dense_oracle(T, H, I, E, k):
     assert _rel(moe.router.weight.grad, ws[0].grad) < 6e-2
 
 
+@pytest.mark.parametrize("T,H,I,E,k,r", [(300, 256, 128, 8, 2, 8), (1024, 1536, 512, 40, 8, 16), (77, 512, 256, 16, 4, 40)])
+def test_expert_lora_rides_in_the_grouped_gemm(T, H, I, E, k, r):
+    """Frozen expert weights with per-expert low-rank factors: the fused path (low-rank products as the second
+    operand pair of the grouped GEMMs) against the fp32 dense ``W + A B`` oracle, outputs and all adapter gradients."""
+    from types import SimpleNamespace
+
+    torch.manual_seed(2)
+    moe = ScatterMoE(H, "silu", I, E, top_k=k, dtype=torch.bfloat16, device=DEV,
+                     lora_config=SimpleNamespace(r=r, lora_alpha=r))
+    with torch.no_grad():
+        moe.router.weight.normal_(0, 0.05)
+        for m in (moe.w1, moe.w2, moe.w3):
+            m.weight.normal_(0, 0.05)
+            m.lora_A.normal_(0, 0.1)
+            m.lora_B.normal_(0, 0.1)
+    x = (torch.randn(T, H, device=DEV) * 0.5).bfloat16().requires_grad_()
+    out, logits = moe(x)
+    NV.check_status()
+    _, kidx = MOE.router_topk(logits.detach(), k)
+    g = torch.randn_like(out)
+    out.backward(g)
+    NV.check_status()
+    assert moe.w1.weight.grad is None and moe.w2.weight.grad is None
+    xf = x.detach().float().requires_grad_()
+    rw = moe.router.weight.detach().float().requires_grad_()
+    fac = {n: (getattr(moe, n).lora_A.detach().float().requires_grad_(), getattr(moe, n).lora_B.detach().float().requires_grad_())
+           for n in ("w1", "w2", "w3")}
+    dense = {n: getattr(moe, n).weight.detach().float() + torch.bmm(*fac[n]) for n in fac}
+    ref, _ = MOE.moe_ref(xf, rw, dense["w1"], dense["w2"], dense["w3"], k, idx=kidx)
+    ref.backward(g.float())
+    assert _rel(out, ref) < 2e-2
+    assert _rel(x.grad, xf.grad) < 3e-2
+    for n in fac:
+        assert _rel(getattr(moe, n).lora_A.grad, fac[n][0].grad) < 4e-2, n + ".lora_A"
+        assert _rel(getattr(moe, n).lora_B.grad, fac[n][1].grad) < 4e-2, n + ".lora_B"
+    assert _rel(moe.router.weight.grad, rw.grad) < 6e-2
+
+
 def test_granitemoe_fused_model_trains():
     torch.manual_seed(0)
     model = build_model("tiny-granitemoe", device=DEV, dtype=torch.bfloat16, seed=0)

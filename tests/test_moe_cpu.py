@@ -170,3 +170,132 @@ def test_expert_lora_starts_at_the_base_and_trains_only_the_adapters():
     assert lora.w2.lora_A.grad is not None and lora.w2.lora_B.grad.abs().sum() > 0
     assert lora.w1.lora_A.grad.abs().sum() > 0 and lora.w1.weight.grad is None
     assert lora.router.weight.grad is not None
+
+
+def test_packed_expert_lora_reproduces_the_three_low_rank_updates():
+    """pack_expert_lora: gate and up side by side, ranks padded to the kernel's 64-element contraction block; the
+    packed products equal the per-projection A B and gradients flow back to the six factors."""
+    from fms_acceleration_b200.ops.moe import pack_expert_lora
+
+    torch.manual_seed(0)
+    El, H, I, r = 3, 16, 24, 5
+    f = [torch.randn(*s, dtype=torch.float64, requires_grad=True) for s in
+         ((El, H, r), (El, r, I), (El, H, r), (El, r, I), (El, I, r), (El, r, H))]
+    A13, B13, A2, B2 = pack_expert_lora(*f)
+    assert A13.shape == (El, H, 64) and B13.shape == (El, 64, 2 * I) and A2.shape == (El, I, 64) and B2.shape == (El, 64, H)
+    up13 = torch.bmm(A13, B13)
+    assert torch.allclose(up13[:, :, :I], torch.bmm(f[0], f[1])) and torch.allclose(up13[:, :, I:], torch.bmm(f[2], f[3]))
+    assert torch.allclose(torch.bmm(A2, B2), torch.bmm(f[4], f[5]))
+    (up13.sum() + torch.bmm(A2, B2).sum()).backward()
+    assert all(t.grad is not None and t.grad.abs().sum() > 0 for t in f)
+
+
+def _emulated_grouped_gemm(a, b, seg_off, n_groups, *, mode, b_mn=True, out=None, out_dtype=None, c=None, beta=0.0,
+                           n=None, m=None, b_alt=None, a2=None, b2=None, max_ctas=0):
+    """Plain-torch statement of what ``ops.moe.grouped_gemm`` asks of the kernel (fp64 accumulation)."""
+    off = seg_off.tolist()
+    if mode == 1:
+        rows, K = a.shape
+        res = torch.zeros(rows, n, dtype=torch.float64)
+        for g in range(n_groups):
+            r0, r1 = off[g], off[g + 1]
+
+            def weight(t, kk, cols):
+                if b_mn:
+                    return t[g * kk:(g + 1) * kk, :cols].double()            # stored [K, N]
+                return t[g * cols:(g + 1) * cols, :kk].double().t()          # stored [N, K]
+
+            if b_alt is not None:
+                half = b.shape[1]
+                res[r0:r1, :half] = a[r0:r1].double() @ weight(b, K, half)
+                res[r0:r1, half:] = a[r0:r1].double() @ weight(b_alt, K, half)
+            else:
+                res[r0:r1] = a[r0:r1].double() @ weight(b, K, n)
+            if a2 is not None:
+                res[r0:r1] += a2[r0:r1].double() @ weight(b2, a2.shape[1], n)
+        if c is not None:
+            res += beta * c.double()
+        res = res.to(out_dtype or (out.dtype if out is not None else a.dtype))
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
+    res = torch.zeros(n_groups, m, n, dtype=torch.float64)
+    for g in range(n_groups):
+        r0, r1 = off[g], off[g + 1]
+        res[g] = a[r0:r1].double().t() @ b[r0:r1].double()
+    if c is not None:
+        res += beta * c.double()
+    res = res.to(out_dtype or torch.float32)
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
+
+
+def test_expert_lora_gradient_algebra_against_autograd(monkeypatch):
+    """The chain of grouped products that carries per-expert LoRA through the expert MLP (forward and backward of
+    ops.moe._experts_fwd_local / _experts_bwd_local), with the kernel calls replaced by plain torch: outputs, the
+    input gradient and the gradients of the four packed factors equal autograd's on the dense W + A B formulation."""
+    from types import SimpleNamespace
+
+    from fms_acceleration_b200.ops import moe as MOE
+
+    torch.manual_seed(0)
+    El, H, I, r = 3, 16, 24, 4
+    counts = [5, 0, 9]
+    off = [0]
+    for cnt in counts:
+        off.append(off[-1] + cnt)
+    rows = off[-1]
+    seg_off = torch.tensor(off + [rows], dtype=torch.int32)
+    dd = torch.float64
+
+    def glu_fwd(e, g, act, rows_dev=None):
+        return torch.nn.functional.silu(e) * g
+
+    def glu_bwd(dh, e, g, act, de=None, dg=None, rows_dev=None):
+        sig = torch.sigmoid(e)
+        d_e = dh * g * (sig * (1 + e * (1 - sig)))
+        d_g = dh * torch.nn.functional.silu(e)
+        de.copy_(d_e)
+        dg.copy_(d_g)
+
+    monkeypatch.setattr(MOE, "grouped_gemm", _emulated_grouped_gemm)
+    monkeypatch.setattr(MOE.ACT, "glu_fwd", glu_fwd)
+    monkeypatch.setattr(MOE.ACT, "glu_bwd", glu_bwd)
+    mctx = SimpleNamespace(I=I, E_local=El, H=H, gemm_ctas=0)
+    w1, w3 = torch.randn(El, H, I, dtype=dd) * 0.3, torch.randn(El, H, I, dtype=dd) * 0.3
+    w2 = torch.randn(El, I, H, dtype=dd) * 0.3
+    fac = [(torch.randn(*s, dtype=dd) * 0.3).requires_grad_() for s in
+           ((El, H, r), (El, r, I), (El, H, r), (El, r, I), (El, I, r), (El, r, H))]
+    lora = MOE.pack_expert_lora(*fac)
+    Xs = torch.randn(rows, H, dtype=dd)
+    dYs = torch.randn(rows, H, dtype=dd)
+    packed = tuple(t.detach() for t in lora)
+    gu, Ys, XA = MOE._experts_fwd_local(mctx, Xs, seg_off, w1, w3, w2, "silu", lora=packed)
+    acc: dict = {}
+    dXs = MOE._experts_bwd_local(mctx, Xs, gu, dYs, seg_off, w1, w3, w2, "silu", acc, need_dw=False, lora=packed, XA=XA)
+
+    xs = Xs.clone().requires_grad_()
+    ref = torch.zeros(rows, H, dtype=dd)
+    for g in range(El):
+        r0, r1 = off[g], off[g + 1]
+        d1, d3, d2 = w1[g] + fac[0][g] @ fac[1][g], w3[g] + fac[2][g] @ fac[3][g], w2[g] + fac[4][g] @ fac[5][g]
+        ref[r0:r1] = (torch.nn.functional.silu(xs[r0:r1] @ d1) * (xs[r0:r1] @ d3)) @ d2
+    assert torch.allclose(Ys, ref.detach(), atol=1e-9)
+    ref.backward(dYs)
+    assert torch.allclose(dXs, xs.grad, atol=1e-9)
+    got = dict(zip(("da13", "db13", "da2", "db2"), (acc[k].double() for k in ("da13", "db13", "da2", "db2"))))
+    # autograd through the packing gives the reference gradients of the packed tensors
+    pk = [t.detach().clone().requires_grad_() for t in lora]
+    xs2 = Xs.clone()
+    ref2 = torch.zeros(rows, H, dtype=dd)
+    for g in range(El):
+        r0, r1 = off[g], off[g + 1]
+        up = torch.cat([w1[g], w3[g]], dim=1) + pk[0][g] @ pk[1][g]
+        hid = torch.nn.functional.silu(xs2[r0:r1] @ up[:, :I]) * (xs2[r0:r1] @ up[:, I:])
+        ref2[r0:r1] = hid @ (w2[g] + pk[2][g] @ pk[3][g])
+    ref2.backward(dYs)
+    for key, t in zip(("da13", "db13", "da2", "db2"), pk):
+        assert torch.allclose(got[key], t.grad, atol=1e-5), key
