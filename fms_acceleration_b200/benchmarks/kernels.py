@@ -258,14 +258,15 @@ def bench_reference(a):
     # RMSNorm forward + backward, hidden 4096
     rms = BK._load_reference("fms_acceleration_foak", "kernels.unsloth.rms_layernorm")
     norm = torch.nn.Module()
-    norm.weight = torch.nn.Parameter(torch.ones(H, device=dev, dtype=torch.bfloat16))
+    # frozen, as the norms are under LoRA: the reference's kernel never forms a weight gradient
+    norm.weight = torch.nn.Parameter(torch.ones(H, device=dev, dtype=torch.bfloat16), requires_grad=False)
     norm.variance_epsilon = 1e-6
     x = torch.randn(Te, H, device=dev, dtype=torch.bfloat16, requires_grad=True)
     gy = torch.randn(Te, H, device=dev, dtype=torch.bfloat16)
 
     def mine_rms():
         y = RN.rmsnorm(x, norm.weight, 1e-6)
-        torch.autograd.grad(y, (x,), gy)  # like the reference: no weight gradient (frozen norms under LoRA)
+        torch.autograd.grad(y, (x,), gy)
 
     def ref_rms():
         y = rms.fast_rms_layernorm(norm, x)

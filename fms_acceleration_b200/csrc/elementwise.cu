@@ -85,6 +85,173 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return t;
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Row-in-registers RMSNorm for the common row widths (H = 1024 ... 4096): one warp (or a pair of warps, WPR = 2) keeps
+// its row packed in registers (VPL 16-byte vectors per lane), reduces with shuffles (plus one 64-thread named barrier
+// for a pair) and never meets a block-wide barrier, so the warps of a CTA stream independent rows and an SM has 16 or
+// more rows in flight.  The block-per-row kernels below had one or two rows in flight per CTA around two
+// __syncthreads each and stopped at 0.57 (forward) / 0.67 (backward) of the copy bandwidth.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int NORM_WARPS = 8;
+
+// sum over the WPR warps that share a row; `red` is double-buffered by `parity` (a warp cannot run two barriers ahead
+// of its partner, so the buffer written two sums ago is free)
+template <int WPR>
+__device__ __forceinline__ float row_sum(float v, float (*red)[NORM_WARPS], int& parity) {
+  v = warp_sum(v);
+  if (WPR == 1) return v;
+  const int warp = threadIdx.x >> 5;
+  if ((threadIdx.x & 31) == 0) red[parity][warp] = v;
+  asm volatile("bar.sync %0, %1;" ::"r"(1 + warp / WPR), "n"(WPR * 32) : "memory");
+  float t = 0.f;
+#pragma unroll
+  for (int i = 0; i < WPR; ++i) t += red[parity][warp / WPR * WPR + i];
+  parity ^= 1;
+  return t;
+}
+
+template <typename T, int VPL, int WPR>
+__global__ void __launch_bounds__(NORM_WARPS * 32, 2)
+rmsnorm_fwd_rows_kernel(const T* __restrict__ x, const T* __restrict__ residual, const T* __restrict__ w,
+                        T* __restrict__ y, T* __restrict__ h_out, float* __restrict__ inv_rms, int rows, float eps,
+                        int gemma) {
+  constexpr int H = VPL * 256 * WPR;
+  constexpr int RPC = NORM_WARPS / WPR;  // rows per CTA and trip
+  __shared__ float red[2][NORM_WARPS];
+  int parity = 0;
+  const int warp = threadIdx.x >> 5;
+  const int col0 = ((warp % WPR) * 32 + (threadIdx.x & 31)) * 8;  // this lane's first element; vectors 256 * WPR apart
+  for (int row = blockIdx.x * RPC + warp / WPR; row < rows; row += gridDim.x * RPC) {
+    const long long base = (long long)row * H + col0;
+    Vec8<T> c[VPL];
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) c[j].load(x + base + j * (256 * WPR));
+    if (residual != nullptr) {
+#pragma unroll
+      for (int j = 0; j < VPL; ++j) {
+        Vec8<T> r;
+        float a[8], b[8];
+        r.load(residual + base + j * (256 * WPR));
+        c[j].to_float(a);
+        r.to_float(b);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) a[i] += b[i];
+        c[j].from_float(a);  // the new residual stream, rounded to the storage type as the next layer will read it
+        if (h_out != nullptr) c[j].store(h_out + base + j * (256 * WPR));
+      }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      float a[8];
+      c[j].to_float(a);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += a[i] * a[i];
+    }
+    ss = row_sum<WPR>(ss, red, parity);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    if (col0 == 0 && inv_rms != nullptr) inv_rms[row] = inv;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      Vec8<T> wv, o;
+      float a[8], wf[8], out[8];
+      wv.load(w + col0 + j * (256 * WPR));
+      wv.to_float(wf);
+      c[j].to_float(a);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) out[i] = gemma ? a[i] * inv * (wf[i] + 1.f) : round_to<T>(a[i] * inv) * wf[i];
+      o.from_float(out);
+      o.store(y + base + j * (256 * WPR));
+    }
+  }
+}
+
+// dx = inv/H * (H * dy*w - xhat * sum(dy*w*xhat)) [+ dres_in].  WITH_DW: every lane also sums dy * xhat over its rows;
+// the warps of a CTA fold their sums in shared memory and the CTA writes ONE partial row dw_partial[blockIdx.x, :].
+template <typename T, int VPL, int WPR, bool WITH_DW>
+__global__ void __launch_bounds__(NORM_WARPS * 32, 2)
+rmsnorm_bwd_rows_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
+                        const float* __restrict__ inv_rms, const T* __restrict__ dres_in, T* __restrict__ dx,
+                        float* __restrict__ dw_partial, int rows, int gemma) {
+  constexpr int H = VPL * 256 * WPR;
+  constexpr int RPC = NORM_WARPS / WPR;
+  __shared__ float red[2][NORM_WARPS];
+  __shared__ float dwred[WITH_DW ? RPC * H : 1];
+  int parity = 0;
+  const int warp = threadIdx.x >> 5;
+  const int col0 = ((warp % WPR) * 32 + (threadIdx.x & 31)) * 8;
+  const float wadd = gemma ? 1.f : 0.f;
+  float dwacc[WITH_DW ? VPL : 1][8];
+#pragma unroll
+  for (int j = 0; j < (WITH_DW ? VPL : 1); ++j)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dwacc[j][i] = 0.f;
+  for (int row = blockIdx.x * RPC + warp / WPR; row < rows; row += gridDim.x * RPC) {
+    const long long base = (long long)row * H + col0;
+    Vec8<T> xc[VPL], dc[VPL];
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      xc[j].load(x + base + j * (256 * WPR));
+      dc[j].load(dy + base + j * (256 * WPR));
+    }
+    const float inv = inv_rms[row];
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      Vec8<T> wv;
+      float xf[8], df[8], wf[8];
+      wv.load(w + col0 + j * (256 * WPR));
+      wv.to_float(wf);
+      xc[j].to_float(xf);
+      dc[j].to_float(df);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float xh = xf[i] * inv;
+        dot += df[i] * (wf[i] + wadd) * xh;
+        if (WITH_DW) dwacc[WITH_DW ? j : 0][i] += df[i] * xh;
+      }
+    }
+    dot = row_sum<WPR>(dot, red, parity);
+    const float c = dot / (float)H;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      Vec8<T> wv, o;
+      float xf[8], df[8], wf[8], out[8];
+      wv.load(w + col0 + j * (256 * WPR));
+      wv.to_float(wf);
+      xc[j].to_float(xf);
+      dc[j].to_float(df);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) out[i] = inv * (df[i] * (wf[i] + wadd) - xf[i] * inv * c);
+      if (dres_in != nullptr) {
+        Vec8<T> rv;
+        float rf[8];
+        rv.load(dres_in + base + j * (256 * WPR));
+        rv.to_float(rf);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) out[i] += rf[i];
+      }
+      o.from_float(out);
+      o.store(dx + base + j * (256 * WPR));
+    }
+  }
+  if (WITH_DW) {
+#pragma unroll
+    for (int j = 0; j < (WITH_DW ? VPL : 1); ++j) {
+      float* dst = dwred + (warp / WPR) * H + col0 + j * (256 * WPR);
+      *reinterpret_cast<float4*>(dst) = make_float4(dwacc[j][0], dwacc[j][1], dwacc[j][2], dwacc[j][3]);
+      *reinterpret_cast<float4*>(dst + 4) = make_float4(dwacc[j][4], dwacc[j][5], dwacc[j][6], dwacc[j][7]);
+    }
+    __syncthreads();
+    for (int col = threadIdx.x; col < H; col += NORM_WARPS * 32) {
+      float t = 0.f;
+#pragma unroll
+      for (int r = 0; r < RPC; ++r) t += dwred[r * H + col];
+      dw_partial[(long long)blockIdx.x * H + col] = t;
+    }
+  }
+}
+
 // y = rms_norm(x [+ residual]) * (w [+1]);  optional h_out = x + residual (the new residual stream)
 template <typename T>
 __global__ void __launch_bounds__(NORM_THREADS)
@@ -310,106 +477,120 @@ __global__ void rope_kernel(T* __restrict__ qk, const int* __restrict__ pos, con
   }
 }
 
-// activation codes: 0 = SwiGLU (silu), 1 = GEGLU exact (erf), 2 = GEGLU tanh approximation
-__device__ __forceinline__ float act_fwd(float e, int act) {
-  if (act == 0) return e / (1.f + __expf(-e));
-  if (act == 1) return 0.5f * e * (1.f + erff(e * 0.70710678118654752f));
+// activation codes: 0 = SwiGLU (silu), 1 = GEGLU exact (erf), 2 = GEGLU tanh approximation.  The code is a template
+// parameter and the sigmoid uses the approximate reciprocal: with a run-time switch, a full-precision division per
+// element and a 64-bit division per vector these kernels were bound by instruction issue (0.70 of the copy bandwidth),
+// not by memory.
+template <int ACT>
+__device__ __forceinline__ float act_fwd(float e) {
+  if (ACT == 0) return e * __fdividef(1.f, 1.f + __expf(-e));
+  if (ACT == 1) return 0.5f * e * (1.f + erff(e * 0.70710678118654752f));
   const float k = 0.7978845608028654f;
   return 0.5f * e * (1.f + tanhf(k * e * (1.f + 0.044715f * e * e)));
 }
-__device__ __forceinline__ float act_grad(float e, int act) {
-  if (act == 0) {
-    const float s = 1.f / (1.f + __expf(-e));
-    return s * (1.f + e * (1.f - s));
+// activation and its derivative together (the backward needs both)
+template <int ACT>
+__device__ __forceinline__ void act_both(float e, float& f, float& df) {
+  if (ACT == 0) {
+    const float s = __fdividef(1.f, 1.f + __expf(-e));
+    f = e * s;
+    df = s * (1.f + e * (1.f - s));
+    return;
   }
-  if (act == 1) {
-    return 0.5f * (1.f + erff(e * 0.70710678118654752f)) + e * 0.3989422804014327f * __expf(-0.5f * e * e);
+  if (ACT == 1) {
+    const float cdf = 0.5f * (1.f + erff(e * 0.70710678118654752f));
+    f = e * cdf;
+    df = cdf + e * 0.3989422804014327f * __expf(-0.5f * e * e);
+    return;
   }
   const float k = 0.7978845608028654f;
   const float u = k * e * (1.f + 0.044715f * e * e);
   const float th = tanhf(u);
-  return 0.5f * (1.f + th) + 0.5f * e * (1.f - th * th) * k * (1.f + 3.f * 0.044715f * e * e);
+  f = 0.5f * e * (1.f + th);
+  df = 0.5f * (1.f + th) + 0.5f * e * (1.f - th * th) * k * (1.f + 3.f * 0.044715f * e * e);
 }
 
+// Walks the [rows, I / 8] grid of 16-byte vectors with a grid-sized stride using 32-bit adds only: the stride's
+// (rows, vectors) decomposition is formed once per thread.
+struct VecWalk {
+  int r, c, dr, dc, vpr;
+  __device__ __forceinline__ VecWalk(int vec_per_row) : vpr(vec_per_row) {
+    const long long first = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    r = (int)(first / vpr);
+    c = (int)(first % vpr);
+    dr = (int)(stride / vpr);
+    dc = (int)(stride % vpr);
+  }
+  __device__ __forceinline__ void next() {
+    r += dr;
+    c += dc;
+    if (c >= vpr) {
+      c -= vpr;
+      r += 1;
+    }
+  }
+};
+
 // h[t, i] = act(e[t, i]) * g[t, i]    e, g, h: row strides in elements
-template <typename T>
-__global__ void glu_fwd_kernel(const T* __restrict__ e, const T* __restrict__ g, T* __restrict__ h, int rows,
-                               int I, long long se, long long sg, long long sh, int act,
-                               const int* __restrict__ rows_dev) {
+template <typename T, int ACT>
+__global__ void __launch_bounds__(256)
+glu_fwd_kernel(const T* __restrict__ e, const T* __restrict__ g, T* __restrict__ h, int rows, int I, long long se,
+               long long sg, long long sh, const int* __restrict__ rows_dev) {
   // rows_dev (optional): the number of rows actually in use, known only on the device (the filled part of a
   // fixed-capacity mixture-of-experts buffer); never more than `rows`
   if (rows_dev != nullptr) rows = min(rows, *rows_dev);
-  const int vec_per_row = I / 8;
-  const long long total = (long long)rows * vec_per_row;
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  // two independent vectors per thread and trip: four 16-byte loads in flight before the first use
-  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += 2 * stride) {
-    const long long idx2 = idx + stride;
-    const bool two = idx2 < total;
-    const long long r = idx / vec_per_row, r2 = two ? idx2 / vec_per_row : r;
-    const int c = (int)(idx % vec_per_row) * 8, c2 = two ? (int)(idx2 % vec_per_row) * 8 : c;
-    Vec8<T> a, b, a2, b2;
-    a.load(e + r * se + c);
-    b.load(g + r * sg + c);
-    a2.load(e + r2 * se + c2);
-    b2.load(g + r2 * sg + c2);
+  for (VecWalk it(I / 8); it.r < rows; it.next()) {
+    const int c = it.c * 8;
+    Vec8<T> a, b;
     float ef[8], gf[8], out[8];
+    a.load(e + it.r * se + c);
+    b.load(g + it.r * sg + c);
     a.to_float(ef);
     b.to_float(gf);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) out[i] = round_to<T>(act_fwd(ef[i], act)) * gf[i];
+    for (int i = 0; i < 8; ++i) out[i] = round_to<T>(act_fwd<ACT>(ef[i])) * gf[i];
     Vec8<T> o;
     o.from_float(out);
-    o.store(h + r * sh + c);
-    if (two) {
-      a2.to_float(ef);
-      b2.to_float(gf);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) out[i] = round_to<T>(act_fwd(ef[i], act)) * gf[i];
-      o.from_float(out);
-      o.store(h + r2 * sh + c2);
-    }
+    o.store(h + it.r * sh + c);
   }
 }
 
 // Given dh, e, g:  de = dh * g * act'(e),  dg = dh * act(e); optionally also h = act(e) * g.
 // de/dg may alias e/g (the in-place scheme of the reference).
-template <typename T>
-__global__ void glu_bwd_kernel(const T* __restrict__ dh, const T* e, const T* g, T* de, T* dg,
-                               T* __restrict__ h_out, int rows, int I, long long sdh, long long se, long long sg,
-                               long long sde, long long sdg, long long sh, int act,
-                               const int* __restrict__ rows_dev) {
+template <typename T, int ACT>
+__global__ void __launch_bounds__(256)
+glu_bwd_kernel(const T* __restrict__ dh, const T* e, const T* g, T* de, T* dg, T* __restrict__ h_out, int rows, int I,
+               long long sdh, long long se, long long sg, long long sde, long long sdg, long long sh,
+               const int* __restrict__ rows_dev) {
   if (rows_dev != nullptr) rows = min(rows, *rows_dev);
-  const int vec_per_row = I / 8;
-  const long long total = (long long)rows * vec_per_row;
-  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
-       idx += (long long)gridDim.x * blockDim.x) {
-    const long long r = idx / vec_per_row;
-    const int c = (int)(idx % vec_per_row) * 8;
+  for (VecWalk it(I / 8); it.r < rows; it.next()) {
+    const int c = it.c * 8;
     Vec8<T> a, b, d;
     float ef[8], gf[8], df[8], o1[8], o2[8], o3[8];
-    a.load(e + r * se + c);
-    b.load(g + r * sg + c);
-    d.load(dh + r * sdh + c);
+    a.load(e + it.r * se + c);
+    b.load(g + it.r * sg + c);
+    d.load(dh + it.r * sdh + c);
     a.to_float(ef);
     b.to_float(gf);
     d.to_float(df);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const float f = act_fwd(ef[i], act);
-      o1[i] = df[i] * gf[i] * act_grad(ef[i], act);
+      float f, fp;
+      act_both<ACT>(ef[i], f, fp);
+      o1[i] = df[i] * gf[i] * fp;
       o2[i] = df[i] * f;
       o3[i] = f * gf[i];
     }
     Vec8<T> w1, w2;
     w1.from_float(o1);
     w2.from_float(o2);
-    w1.store(de + r * sde + c);
-    w2.store(dg + r * sdg + c);
+    w1.store(de + it.r * sde + c);
+    w2.store(dg + it.r * sdg + c);
     if (h_out != nullptr) {
       Vec8<T> w3;
       w3.from_float(o3);
-      w3.store(h_out + r * sh + c);
+      w3.store(h_out + it.r * sh + c);
     }
   }
 }
@@ -432,6 +613,21 @@ __global__ void add_kernel(const T* __restrict__ a, const T* __restrict__ b, T* 
   }
 }
 
+// One resident wave of a grid-stride kernel: SMs x CTAs that fit per SM (asked of the runtime once per kernel).  A grid
+// of a fixed 16 CTAs per SM ran as 2.67 waves of equal CTAs on kernels that fit 6 per SM, i.e. a third wave at a third
+// of the machine.
+template <typename K>
+static int wave_grid(K kernel, int threads, long long work_items, int* cache) {
+  if (*cache <= 0) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0) != cudaSuccess || per_sm < 1) per_sm = 4;
+    *cache = per_sm * 148;
+  }
+  long long b = (work_items + threads - 1) / threads;
+  if (b > *cache) b = *cache;
+  return b < 1 ? 1 : (int)b;
+}
+
 static inline int grid_for(long long work_items, int threads, int cap_blocks) {
   long long b = (work_items + threads - 1) / threads;
   if (b > cap_blocks) b = cap_blocks;
@@ -443,11 +639,36 @@ static inline int grid_for(long long work_items, int threads, int cap_blocks) {
 
 using namespace fmsb;
 
+// row widths served by the row-in-registers kernels (the block-per-row kernels take every other width)
+static bool norm_rows_ok(int H) { return H == 1024 || H == 1536 || H == 2048 || H == 2560 || H == 4096; }
+static int norm_rows_grid(int rows, int wpr) {
+  const int rpc = NORM_WARPS / wpr;
+  const int need = (rows + rpc - 1) / rpc;
+  return need < 148 * 8 ? need : 148 * 8;
+}
+
 extern "C" int fmsb_rmsnorm_fwd(const void* x, const void* residual, const void* w, void* y, void* h_out,
                                 float* inv_rms, int rows, int H, float eps, int gemma, int dtype,
                                 cudaStream_t stream) {
   if (H % 8 != 0 || H > 8 * NORM_THREADS * NORM_MAXV) return -2;
   if (rows <= 0) return 0;
+  if (norm_rows_ok(H)) {
+#define FMSB_NORM_FWD_R(T, VPL, WPR)                                                                            \
+  rmsnorm_fwd_rows_kernel<T, VPL, WPR><<<norm_rows_grid(rows, WPR), NORM_WARPS * 32, 0, stream>>>(              \
+      (const T*)x, (const T*)residual, (const T*)w, (T*)y, (T*)h_out, inv_rms, rows, eps, gemma)
+#define FMSB_NORM_FWD_RT(T)                                     \
+  switch (H) {                                                  \
+    case 1024: FMSB_NORM_FWD_R(T, 4, 1); break;                 \
+    case 1536: FMSB_NORM_FWD_R(T, 6, 1); break;                 \
+    case 2048: FMSB_NORM_FWD_R(T, 4, 2); break;                 \
+    case 2560: FMSB_NORM_FWD_R(T, 5, 2); break;                 \
+    default: FMSB_NORM_FWD_R(T, 8, 2); break;                   \
+  }
+    if (dtype == 1) { FMSB_NORM_FWD_RT(__nv_bfloat16) } else { FMSB_NORM_FWD_RT(__half) }
+#undef FMSB_NORM_FWD_RT
+#undef FMSB_NORM_FWD_R
+    return (int)cudaGetLastError();
+  }
   const int grid = rows < 148 * 8 ? rows : 148 * 8;
   if (dtype == 1)
     rmsnorm_fwd_kernel<__nv_bfloat16><<<grid, NORM_THREADS, 0, stream>>>(
@@ -467,6 +688,34 @@ extern "C" int fmsb_rmsnorm_bwd(const void* dy, const void* x, const void* w, co
                                 int rows, int H, int gemma, int dtype, cudaStream_t stream) {
   if (H % 8 != 0 || H > 8 * NORM_THREADS * NORM_MAXV) return -2;
   if (rows <= 0) return 0;
+  if (norm_rows_ok(H)) {
+    const bool with_dw = dw_partial != nullptr;
+    if (with_dw && n_partial_blocks <= 0) return -2;
+    int rgrid = 0;
+#define FMSB_NORM_BWD_R(T, VPL, WPR)                                                                              \
+  rgrid = norm_rows_grid(rows, WPR);                                                                              \
+  if (with_dw) {                                                                                                  \
+    if (rgrid > n_partial_blocks) rgrid = n_partial_blocks; /* one partial row per CTA */                         \
+    rmsnorm_bwd_rows_kernel<T, VPL, WPR, true><<<rgrid, NORM_WARPS * 32, 0, stream>>>(                            \
+        (const T*)dy, (const T*)x, (const T*)w, inv_rms, (const T*)dres_in, (T*)dx, dw_partial, rows, gemma);     \
+  } else {                                                                                                        \
+    rmsnorm_bwd_rows_kernel<T, VPL, WPR, false><<<rgrid, NORM_WARPS * 32, 0, stream>>>(                           \
+        (const T*)dy, (const T*)x, (const T*)w, inv_rms, (const T*)dres_in, (T*)dx, nullptr, rows, gemma);        \
+  }
+#define FMSB_NORM_BWD_RT(T)                                     \
+  switch (H) {                                                  \
+    case 1024: FMSB_NORM_BWD_R(T, 4, 1); break;                 \
+    case 1536: FMSB_NORM_BWD_R(T, 3, 2); break;                 \
+    case 2048: FMSB_NORM_BWD_R(T, 4, 2); break;                 \
+    case 2560: FMSB_NORM_BWD_R(T, 5, 2); break;                 \
+    default: FMSB_NORM_BWD_R(T, 4, 4); break;                   \
+  }
+    if (dtype == 1) { FMSB_NORM_BWD_RT(__nv_bfloat16) } else { FMSB_NORM_BWD_RT(__half) }
+#undef FMSB_NORM_BWD_RT
+#undef FMSB_NORM_BWD_R
+    if (with_dw && dw != nullptr) colsum_kernel<<<(H + 31) / 32, dim3(32, 8), 0, stream>>>(dw_partial, dw, rgrid, H);
+    return (int)cudaGetLastError();
+  }
   // without a weight gradient the kernel is light on registers: several CTAs per SM, 8 waves of rows each
   int grid = rows < 148 * 8 ? rows : 148 * 8;
   if (dw_partial != nullptr) {
@@ -514,13 +763,16 @@ extern "C" int fmsb_glu_fwd(const void* e, const void* g, void* h, int rows, int
                             long long sh, int act, int dtype, const int* rows_dev, cudaStream_t stream) {
   if (I % 8 != 0 || se % 8 || sg % 8 || sh % 8) return -2;
   if (rows <= 0) return 0;
-  const int grid = grid_for((long long)rows * (I / 8), 256, 148 * 16);
-  if (dtype == 1)
-    glu_fwd_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)e, (const __nv_bfloat16*)g,
-                                                            (__nv_bfloat16*)h, rows, I, se, sg, sh, act, rows_dev);
-  else
-    glu_fwd_kernel<__half><<<grid, 256, 0, stream>>>((const __half*)e, (const __half*)g, (__half*)h, rows, I, se, sg,
-                                                     sh, act, rows_dev);
+  if (act < 0 || act > 2) return -2;
+  static int waves[2][3];
+#define FMSB_GLU_FWD(T, ACT)                                                                                      \
+  glu_fwd_kernel<T, ACT><<<wave_grid(glu_fwd_kernel<T, ACT>, 256, (long long)rows * (I / 8), &waves[dtype == 1][ACT]), \
+                           256, 0, stream>>>((const T*)e, (const T*)g, (T*)h, rows, I, se, sg, sh, rows_dev)
+#define FMSB_GLU_FWD_T(T) \
+  if (act == 0) FMSB_GLU_FWD(T, 0); else if (act == 1) FMSB_GLU_FWD(T, 1); else FMSB_GLU_FWD(T, 2);
+  if (dtype == 1) { FMSB_GLU_FWD_T(__nv_bfloat16) } else { FMSB_GLU_FWD_T(__half) }
+#undef FMSB_GLU_FWD_T
+#undef FMSB_GLU_FWD
   return (int)cudaGetLastError();
 }
 
@@ -529,15 +781,17 @@ extern "C" int fmsb_glu_bwd(const void* dh, const void* e, const void* g, void* 
                             long long sh, int act, int dtype, const int* rows_dev, cudaStream_t stream) {
   if (I % 8 != 0 || sdh % 8 || se % 8 || sg % 8 || sde % 8 || sdg % 8 || sh % 8) return -2;
   if (rows <= 0) return 0;
-  const int grid = grid_for((long long)rows * (I / 8), 256, 148 * 16);
-  if (dtype == 1)
-    glu_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
-        (const __nv_bfloat16*)dh, (const __nv_bfloat16*)e, (const __nv_bfloat16*)g, (__nv_bfloat16*)de,
-        (__nv_bfloat16*)dg, (__nv_bfloat16*)h_out, rows, I, sdh, se, sg, sde, sdg, sh, act, rows_dev);
-  else
-    glu_bwd_kernel<__half><<<grid, 256, 0, stream>>>((const __half*)dh, (const __half*)e, (const __half*)g,
-                                                     (__half*)de, (__half*)dg, (__half*)h_out, rows, I, sdh, se, sg,
-                                                     sde, sdg, sh, act, rows_dev);
+  if (act < 0 || act > 2) return -2;
+  static int waves[2][3];
+#define FMSB_GLU_BWD(T, ACT)                                                                                      \
+  glu_bwd_kernel<T, ACT><<<wave_grid(glu_bwd_kernel<T, ACT>, 256, (long long)rows * (I / 8), &waves[dtype == 1][ACT]), \
+                           256, 0, stream>>>((const T*)dh, (const T*)e, (const T*)g, (T*)de, (T*)dg, (T*)h_out, rows,  \
+                                             I, sdh, se, sg, sde, sdg, sh, rows_dev)
+#define FMSB_GLU_BWD_T(T) \
+  if (act == 0) FMSB_GLU_BWD(T, 0); else if (act == 1) FMSB_GLU_BWD(T, 1); else FMSB_GLU_BWD(T, 2);
+  if (dtype == 1) { FMSB_GLU_BWD_T(__nv_bfloat16) } else { FMSB_GLU_BWD_T(__half) }
+#undef FMSB_GLU_BWD_T
+#undef FMSB_GLU_BWD
   return (int)cudaGetLastError();
 }
 

@@ -125,7 +125,7 @@ def test_gemm_cta_pair_kernel(a_mn, b_mn, M, N_, K):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("rows,H", [(7, 256), (300, 4096), (33, 1536)])
+@pytest.mark.parametrize("rows,H", [(7, 256), (300, 4096), (33, 1536), (20011, 1024), (130, 2048), (5000, 2560), (10007, 4096)])
 def test_rmsnorm(dtype, rows, H):
     torch.manual_seed(0)
     x = torch.randn(rows, H, device=DEV, dtype=dtype, requires_grad=True)
@@ -154,6 +154,39 @@ def test_rmsnorm(dtype, rows, H):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,H", [(37, 1024), (20011, 1024), (301, 1536), (130, 2048), (77, 2560), (300, 4096),
+                                    (10007, 4096), (19, 8192), (45, 512)])
+@pytest.mark.parametrize("gemma", [False, True])
+def test_rmsnorm_frozen_weight_paths(dtype, rows, H, gemma):
+    """Frozen norm weight (adapter training): forward with and without the fused residual add and the backward that
+    produces only the input / residual gradient, on every row width with a row-in-registers kernel, on widths that
+    take the block-per-row kernels, and with more rows than one pass of the grid covers."""
+    torch.manual_seed(rows + H)
+    x = torch.randn(rows, H, device=DEV, dtype=dtype, requires_grad=True)
+    r = torch.randn(rows, H, device=DEV, dtype=dtype, requires_grad=True)
+    w = (torch.randn(H, device=DEV, dtype=dtype) * 0.1 + (0.0 if gemma else 1.0))
+    y, h = RN.rmsnorm(x, w, 1e-6, gemma, r)
+    gy, gh = torch.randn_like(y), torch.randn_like(h)
+    torch.autograd.backward((y, h), (gy, gh))
+    xf, rf = (t.detach().float().requires_grad_() for t in (x, r))
+    hf = xf + rf
+    hq = hf.detach().to(dtype).float() + (hf - hf.detach())  # the kernel normalises the stored (rounded) residual stream
+    yf = hq * torch.rsqrt(hq.pow(2).mean(-1, keepdim=True) + 1e-6) * (w.float() + (1.0 if gemma else 0.0))
+    torch.autograd.backward((yf, hf), (gy.float(), gh.float()))
+    tol = 2e-2
+    assert _rel(y, yf) < tol and _rel(h, hf) < tol
+    assert _rel(x.grad, xf.grad) < tol and _rel(r.grad, rf.grad) < tol
+    # no residual
+    x2 = torch.randn(rows, H, device=DEV, dtype=dtype, requires_grad=True)
+    y2 = RN.rmsnorm(x2, w, 1e-5, gemma)
+    y2.backward(gy)
+    x2f = x2.detach().float().requires_grad_()
+    y2f = x2f * torch.rsqrt(x2f.pow(2).mean(-1, keepdim=True) + 1e-5) * (w.float() + (1.0 if gemma else 0.0))
+    y2f.backward(gy.float())
+    assert _rel(y2, y2f) < tol and _rel(x2.grad, x2f.grad) < tol
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_rope(dtype):
     torch.manual_seed(0)
     T, nh, d = 257, 6, 128
@@ -170,9 +203,9 @@ def test_rope(dtype):
 
 
 @pytest.mark.parametrize("act", ["silu", "gelu", "gelu_pytorch_tanh"])
-def test_glu(act):
+@pytest.mark.parametrize("rows,I", [(130, 1024), (3001, 24), (5, 14336), (70000, 520)])
+def test_glu(act, rows, I):
     torch.manual_seed(0)
-    rows, I = 130, 1024
     eg = torch.randn(rows, 2 * I, device=DEV, dtype=torch.bfloat16, requires_grad=True)
     e, g = eg[:, :I], eg[:, I:]
     h = A.glu(e, g, act)
@@ -185,6 +218,26 @@ def test_glu(act):
     h.backward(gh)
     hf.backward(gh.float())
     assert _rel(eg.grad, ef.grad) < 1.5e-2
+
+
+def test_glu_device_side_row_bound():
+    """rows_dev: only the first n rows (a device scalar) are touched, forward and backward."""
+    torch.manual_seed(1)
+    rows, I, n = 300, 512, 123
+    eg = torch.randn(rows, 2 * I, device=DEV, dtype=torch.bfloat16)
+    used = torch.tensor([n], device=DEV, dtype=torch.int32)
+    h = torch.full((rows, I), 7.0, device=DEV, dtype=torch.bfloat16)
+    A.glu_fwd(eg[:, :I], eg[:, I:], "silu", out=h, rows_dev=used)
+    ref = torch.nn.functional.silu(eg[:n, :I].float()) * eg[:n, I:].float()
+    assert _rel(h[:n], ref) < 1e-2 and torch.all(h[n:] == 7.0)
+    dh = torch.randn(rows, I, device=DEV, dtype=torch.bfloat16)
+    de = torch.full((rows, I), 7.0, device=DEV, dtype=torch.bfloat16)
+    dg = torch.full((rows, I), 7.0, device=DEV, dtype=torch.bfloat16)
+    A.glu_bwd(dh, eg[:, :I], eg[:, I:], "silu", de=de, dg=dg, rows_dev=used)
+    ef = eg[:n].float().requires_grad_()
+    (torch.nn.functional.silu(ef[:, :I]) * ef[:, I:]).backward(dh[:n].float())
+    assert _rel(de[:n], ef.grad[:, :I]) < 1.5e-2 and _rel(dg[:n], ef.grad[:, I:]) < 1.5e-2
+    assert torch.all(de[n:] == 7.0) and torch.all(dg[n:] == 7.0)  # rows beyond the bound are not written
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
