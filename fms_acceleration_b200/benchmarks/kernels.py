@@ -189,6 +189,17 @@ def bench_elementwise(a):
     t = timeit(lambda: ACT.glu_bwd(dh, gu[:, :I], gu[:, I:], "silu", de=de, dg=dg), a.iters, a.warmup, a.flush)
     by = 5.0 * T * I * 2
     print(json.dumps({"kernel": "swiglu_bwd", "ms": t, "gbs": by / t / 1e6, "frac_of_%s_hbm" % pk["source"]: by / t / 1e6 / pk["hbm_gbs"]}))
+    del gu, dh, de, dg
+    # NF4 weight of the gate|up projection [2 * I, H] with double-quantised scales -> bf16 (0.5 + 2 bytes per value)
+    from fms_acceleration_b200.ops import quant as Q
+
+    wq = torch.randn(2 * I, H, device="cuda", dtype=torch.bfloat16) * 0.02
+    qs = Q.quantize_4bit(wq, "nf4", 64, True)
+    wd = torch.empty_like(wq)
+    t = timeit(lambda: Q.dequantize_4bit(qs, torch.bfloat16, out=wd), a.iters, a.warmup, a.flush)
+    by = 2.5 * wq.numel()
+    print(json.dumps({"kernel": "dequant_nf4 [%d x %d]" % (2 * I, H), "ms": t, "gbs": by / t / 1e6,
+                      "frac_of_%s_hbm" % pk["source"]: by / t / 1e6 / pk["hbm_gbs"]}))
 
 
 def bench_grouped(a):

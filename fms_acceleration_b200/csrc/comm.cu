@@ -80,6 +80,7 @@ __global__ void allgather_pull_kernel(PeerPtrs src, uint8_t* __restrict__ dst, l
     const int owner = (rank + 1 + s) % world;
     const uint4* __restrict__ from = reinterpret_cast<const uint4*>(src.p[owner]);
     uint4* __restrict__ to = reinterpret_cast<uint4*>(dst) + (long long)owner * shard16;
+    if (from == to) continue;  // gathering in place: this rank's own shard is already where it belongs
     for (long long base = tid; base < shard16; base += stride * UNROLL) {
       uint4 v[UNROLL];
 #pragma unroll
@@ -102,35 +103,69 @@ __global__ void allgather_pull_kernel(PeerPtrs src, uint8_t* __restrict__ dst, l
 //   out (own slice, dtype of the bucket or fp32).  Peers must have finished writing their buckets
 //   (barrier before) and must not overwrite them until everybody has read (barrier after).
 // ----------------------------------------------------------------------------------------
-template <typename T, typename OutT>
-__global__ void reduce_scatter_pull_kernel(PeerPtrs buckets, OutT* __restrict__ out, long long n_own, int rank,
-                                           int world, float scale) {
+template <typename T>
+__device__ __forceinline__ void rs_accumulate(const uint4& v, float* acc) {
   constexpr int V = 16 / sizeof(T);
+  const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+  for (int k = 0; k < V; ++k) {
+    if (sizeof(T) == 4) acc[k] += *reinterpret_cast<const float*>(e + k);
+    else if (std::is_same<T, __nv_bfloat16>::value) acc[k] += __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(e + k));
+    else acc[k] += __half2float(*reinterpret_cast<const __half*>(e + k));
+  }
+}
+
+// Each thread works on U vectors at a time, so U independent 16-byte peer loads are in flight per thread.  The pull
+// rate over NVLink is (bytes in flight) / latency and the loaded latency is several microseconds: one load in flight
+// per thread gave 60 GB/s per direction, four gave 190 GB/s, and the all-gather above reaches 650 GB/s with 6 MB in
+// flight per GPU.  Results leave as 16-byte stores.
+template <typename T, typename OutT>
+__global__ void __launch_bounds__(512)
+reduce_scatter_pull_kernel(PeerPtrs buckets, OutT* __restrict__ out, long long n_own, int rank, int world,
+                           float scale) {
+  constexpr int V = 16 / sizeof(T);
+  constexpr int U = 8;
   const long long nvec = n_own / V;
   const long long base = (long long)rank * n_own;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
-       i += (long long)gridDim.x * blockDim.x) {
-    float acc[V];
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * U) {
+    float acc[U][V];
 #pragma unroll
-    for (int k = 0; k < V; ++k) acc[k] = 0.f;
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int k = 0; k < V; ++k) acc[u][k] = 0.f;
+#pragma unroll 1
     for (int rr = 0; rr < world; ++rr) {
       const int r = (rank + rr) % world;
-      const uint4 v = *(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(buckets.p[r]) + base) + i);
-      const T* e = reinterpret_cast<const T*>(&v);
+      const uint4* __restrict__ src = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(buckets.p[r]) + base);
+      uint4 v[U];
 #pragma unroll
-      for (int k = 0; k < V; ++k) {
-        if (sizeof(T) == 4) acc[k] += *reinterpret_cast<const float*>(e + k);
-        else if (std::is_same<T, __nv_bfloat16>::value) acc[k] += __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(e + k));
-        else acc[k] += __half2float(*reinterpret_cast<const __half*>(e + k));
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        v[u] = i < nvec ? src[i] : make_uint4(0u, 0u, 0u, 0u);
       }
-    }
-    OutT* o = out + i * V;
 #pragma unroll
-    for (int k = 0; k < V; ++k) {
-      const float v = acc[k] * scale;
-      if (sizeof(OutT) == 4) *reinterpret_cast<float*>(o + k) = v;
-      else if (std::is_same<OutT, __nv_bfloat16>::value) *reinterpret_cast<__nv_bfloat16*>(o + k) = __float2bfloat16_rn(v);
-      else *reinterpret_cast<__half*>(o + k) = __float2half_rn(v);
+      for (int u = 0; u < U; ++u) rs_accumulate<T>(v[u], acc[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= nvec) continue;
+      OutT* o = out + i * V;
+      if (sizeof(OutT) == 4) {
+#pragma unroll
+        for (int k = 0; k < V; k += 4)
+          *reinterpret_cast<float4*>(reinterpret_cast<float*>(o) + k) =
+              make_float4(acc[u][k] * scale, acc[u][k + 1] * scale, acc[u][k + 2] * scale, acc[u][k + 3] * scale);
+      } else {
+        uint4 w;
+        uint32_t* ww = reinterpret_cast<uint32_t*>(&w);
+#pragma unroll
+        for (int k = 0; k < V; k += 2)
+          ww[k / 2] = std::is_same<OutT, __nv_bfloat16>::value ? pack_bf16x2(acc[u][k] * scale, acc[u][k + 1] * scale)
+                                                               : pack_f16x2(acc[u][k] * scale, acc[u][k + 1] * scale);
+        *reinterpret_cast<uint4*>(o) = w;
+      }
     }
   }
 }
@@ -421,7 +456,7 @@ extern "C" int fmsb_comm_reduce_scatter(void* const* bucket_ptrs, void* out, lon
   if (world > kMaxRanks) return -2;
   if (n_own == 0) return 0;
   const int V = dtype == 2 ? 4 : 8;
-  if (n_own % V != 0) return -2;
+  if (n_own % V != 0 || (reinterpret_cast<uintptr_t>(out) & 15u)) return -2;
   if (ctas <= 0) ctas = 64;
   PeerPtrs b = make_ptrs(bucket_ptrs, world);
 #define RS(T, O) reduce_scatter_pull_kernel<T, O><<<ctas, 512, 0, stream>>>(b, (O*)out, n_own, rank, world, scale)

@@ -14,7 +14,7 @@
 
 namespace fmsb {
 
-__device__ __forceinline__ float silu_f(float v) { return v / (1.f + __expf(-v)); }
+__device__ __forceinline__ float silu_f(float v) { return v * __fdividef(1.f, 1.f + __expf(-v)); }
 
 // ---------------------------------------------------------------------------------------------------------
 // Depthwise causal conv (4 taps) + SiLU on packed rows x [T, C].  A thread owns 8 neighbouring channels (one
@@ -273,7 +273,7 @@ __global__ void __launch_bounds__(256, 2) conv1d_bwd_kernel(const T* __restrict_
 #pragma unroll
           for (int j = 0; j < 3; ++j)
             if (valid[j]) p += wf[j][ch] * win[j][ch];
-          const float sg = 1.f / (1.f + __expf(-p));
+          const float sg = __fdividef(1.f, 1.f + __expf(-p));
           const float d = g[ch] * sg * (1.f + p * (1.f - sg));
 #pragma unroll
           for (int j = 0; j < 4; ++j)

@@ -103,47 +103,56 @@ __global__ void quant8_kernel(const float* __restrict__ v, long long n, float of
 }
 
 // ---------------------------------------------------------------------------- dequantise 4-bit
-// Each thread expands 16 packed bytes (32 values, never straddling a block since blocksize % 32 == 0).
+// Per trip a warp expands 512 packed bytes into 2 KB.  Lane l takes the four 4-byte words at l*4 + {0, 128, 256, 384}
+// of the warp's bytes and writes the four 16-byte results at l*16 + {0, 512, 1024, 1536}, so every load instruction
+// covers 128 contiguous bytes and every store instruction 512.  (A lane that expands 16 contiguous bytes writes its 64
+// output bytes with four stores that are 64 bytes apart from the neighbouring lane's: 16 cache lines per store
+// instruction, four times the requests the same bytes need.)  The 256-entry code book of the double-quantised scales
+// sits in shared memory.
 template <typename T>
-__global__ void dequant4_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ absmax,
-                                const uint8_t* __restrict__ absmax_q, const float* __restrict__ code256,
-                                const float* __restrict__ absmax2, float offset, const float* __restrict__ code16,
-                                int blocksize, long long n, T* __restrict__ out) {
+__global__ void __launch_bounds__(256)
+dequant4_warp_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ absmax,
+                     const uint8_t* __restrict__ absmax_q, const float* __restrict__ code256,
+                     const float* __restrict__ absmax2, float offset, const float* __restrict__ code16, int blocksize,
+                     int block_shift, long long n, T* __restrict__ out) {
   __shared__ float code[16];
+  __shared__ float code2[256];
   if (threadIdx.x < 16) code[threadIdx.x] = code16[threadIdx.x];
+  if (absmax_q != nullptr) code2[threadIdx.x] = code256[threadIdx.x];
   __syncthreads();
-  const long long nchunks = n / 32;
-  for (long long c = blockIdx.x * (long long)blockDim.x + threadIdx.x; c < nchunks;
-       c += (long long)gridDim.x * blockDim.x) {
-    const long long e0 = c * 32;
-    const long long b = e0 / blocksize;
-    float s;
-    if (absmax_q != nullptr) {
-      s = code256[absmax_q[b]] * absmax2[b >> 8] + offset;
-    } else {
-      s = absmax[b];
-    }
-    const uint4 u = *reinterpret_cast<const uint4*>(packed + (e0 >> 1));
-    const uint32_t words[4] = {u.x, u.y, u.z, u.w};
-    uint4 o[4];
-    uint32_t* ow = reinterpret_cast<uint32_t*>(o);
+  const int lane = threadIdx.x & 31;
+  const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+  const long long trips = (n + 1023) / 1024;
+  for (long long t = blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5); t < trips; t += nwarps) {
+    const long long e_warp = t * 1024;
+    uint32_t word[4];
+    float scale[4];
 #pragma unroll
-    for (int wi = 0; wi < 4; ++wi) {
-#pragma unroll
-      for (int bi = 0; bi < 4; ++bi) {
-        const uint32_t byte = (words[wi] >> (8 * bi)) & 0xff;
-        const float hi = code[byte >> 4] * s;
-        const float lo = code[byte & 15] * s;
-        if (sizeof(T) == 2) {
-          ow[wi * 4 + bi] = std::is_same<T, __nv_bfloat16>::value ? pack_bf16x2(hi, lo) : pack_f16x2(hi, lo);
-        }
+    for (int k = 0; k < 4; ++k) {
+      const long long e0 = e_warp + (k * 32 + lane) * 8;
+      word[k] = 0u;
+      scale[k] = 0.f;
+      if (e0 < n) {
+        word[k] = *reinterpret_cast<const uint32_t*>(packed + (e0 >> 1));
+        const long long b = block_shift >= 0 ? (e0 >> block_shift) : e0 / blocksize;
+        scale[k] = absmax_q != nullptr ? code2[absmax_q[b]] * absmax2[b >> 8] + offset : absmax[b];
       }
     }
-    uint4* dst = reinterpret_cast<uint4*>(out + e0);
-    dst[0] = o[0];
-    dst[1] = o[1];
-    dst[2] = o[2];
-    dst[3] = o[3];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const long long e0 = e_warp + (k * 32 + lane) * 8;
+      if (e0 >= n) continue;
+      uint4 o;
+      uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+      for (int bi = 0; bi < 4; ++bi) {
+        const uint32_t byte = (word[k] >> (8 * bi)) & 0xff;
+        const float hi = code[byte >> 4] * scale[k];
+        const float lo = code[byte & 15] * scale[k];
+        ow[bi] = std::is_same<T, __nv_bfloat16>::value ? pack_bf16x2(hi, lo) : pack_f16x2(hi, lo);
+      }
+      *reinterpret_cast<uint4*>(out + e0) = o;
+    }
   }
 }
 
@@ -293,18 +302,32 @@ extern "C" int fmsb_dequant4(const void* packed, const float* absmax, const void
                              void* out, int dtype, cudaStream_t stream) {
   if (blocksize % 32 != 0 || n % 32 != 0) return -2;
   if (n <= 0) return 0;
-  long long ctas = (n / 32 + 255) / 256;
-  if (ctas > 148 * 16) ctas = 148 * 16;
+  if (dtype != 0 && dtype != 1) return -2;
+  // shift for the usual power-of-two block sizes, a division otherwise
+  int block_shift = -1;
+  if ((blocksize & (blocksize - 1)) == 0) {
+    block_shift = 0;
+    while ((1 << block_shift) < blocksize) ++block_shift;
+  }
+  static int wave[2];
+  int& per_wave = wave[dtype];
+  if (per_wave <= 0) {
+    int per_sm = 0;
+    cudaError_t e = dtype == 1 ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, dequant4_warp_kernel<__nv_bfloat16>, 256, 0)
+                               : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, dequant4_warp_kernel<__half>, 256, 0);
+    per_wave = (e == cudaSuccess && per_sm > 0 ? per_sm : 4) * 148;
+  }
+  long long ctas = ((n + 1023) / 1024 + 7) / 8;  // eight warps per CTA, 1024 values per warp and trip
+  if (ctas > per_wave) ctas = per_wave;
   if (dtype == 1)
-    dequant4_kernel<__nv_bfloat16><<<(int)ctas, 256, 0, stream>>>((const uint8_t*)packed, absmax,
-                                                                  (const uint8_t*)absmax_q, code256, absmax2, offset,
-                                                                  code16, blocksize, n, (__nv_bfloat16*)out);
-  else if (dtype == 0)
-    dequant4_kernel<__half><<<(int)ctas, 256, 0, stream>>>((const uint8_t*)packed, absmax, (const uint8_t*)absmax_q,
-                                                           code256, absmax2, offset, code16, blocksize, n,
-                                                           (__half*)out);
+    dequant4_warp_kernel<__nv_bfloat16><<<(int)ctas, 256, 0, stream>>>((const uint8_t*)packed, absmax,
+                                                                       (const uint8_t*)absmax_q, code256, absmax2,
+                                                                       offset, code16, blocksize, block_shift, n,
+                                                                       (__nv_bfloat16*)out);
   else
-    return -2;
+    dequant4_warp_kernel<__half><<<(int)ctas, 256, 0, stream>>>((const uint8_t*)packed, absmax,
+                                                                (const uint8_t*)absmax_q, code256, absmax2, offset,
+                                                                code16, blocksize, block_shift, n, (__half*)out);
   return (int)cudaGetLastError();
 }
 

@@ -509,7 +509,7 @@ class _Experts(torch.autograd.Function):
 class _Chunk:
     """Plan and buffers of one token slice of an expert-parallel call."""
     __slots__ = ("t0", "t1", "s", "seg_off", "seg_cnt", "dest_row", "hit", "stage_row", "stage_cnt", "Xs", "gu", "Ys",
-                 "dYs", "rgate", "dXs")
+                 "dYs", "rgate", "dXs", "XA")
 
 
 def _stage_plan(sh: _EPShared, idx_c, dest_row, n, dev):

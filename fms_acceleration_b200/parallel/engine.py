@@ -504,8 +504,9 @@ class ShardedOptimizer:
         for seg in e.segments:
             n = seg.numel_padded // e.world
             ptrs = e.param_bucket.ptr_array_strided(seg.offset * esize, n * esize)
+            # after the optimizer step nothing else runs: give the pull most of the SMs
             rc = NV.lib().fmsb_comm_allgather(ptrs, e.flat_params.data_ptr() + seg.offset * esize, n * esize, e.rank,
-                                              e.world, 32, NV.stream_ptr())
+                                              e.world, 96, NV.stream_ptr())
             NV.check(rc, "fmsb_comm_allgather")
         e.comm.barrier(7)  # nobody rewrites a slice that a peer is still pulling
 

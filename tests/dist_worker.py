@@ -199,10 +199,11 @@ def main():
     if which in ("all", "zero1"):
         check_zero1(dev, rank, world)
     if which in ("all", "moe") and os.path.exists(os.path.join(os.path.dirname(__file__), "dist_worker_moe.py")):
-        from dist_worker_moe import check_moe, check_moe_library
+        from dist_worker_moe import check_moe, check_moe_library, check_moe_lora
 
         check_moe(dev, rank, world)
         check_moe_library(dev, rank, world)
+        check_moe_lora(dev, rank, world)
     if which in ("all", "cp"):
         from dist_worker_cp import check_cp
 

@@ -26,7 +26,7 @@ def _run(which: str, nproc: int = 2, timeout: int = 600):
     ("comm", ["allgather", "allreduce", "reduce_scatter"]),
     ("engine", ["engine", "engine_train"]),
     ("zero1", ["zero1"]),
-    ("moe", ["moe_ep", "moe_library"]),
+    ("moe", ["moe_ep", "moe_library", "moe_lora"]),
     ("cp", ["mamba_cp"]),
 ])
 def test_multi_gpu(which, expected, nproc):
