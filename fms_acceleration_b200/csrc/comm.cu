@@ -368,19 +368,27 @@ __global__ void allreduce_multimem_kernel(T* mc, PeerPtrs signals, long long n, 
   const long long n_own = n / world;
   const long long nvec = n_own / V;
   T* base = mc + (long long)rank * n_own;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
-    if constexpr (sizeof(T) == 4) {
-      float f[4];
-      multimem_ld_reduce_f32x4(base + i * V, f);
+  // four reductions in flight per thread: a round trip through the switch takes microseconds
+  constexpr int U = 4;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * U) {
+    float f[U][V];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) f[k] *= scale;
-      multimem_st_f32x4(base + i * V, f);
-    } else {
-      float f[8];
-      multimem_ld_reduce_bf16x8(base + i * V, f);
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < nvec) {
+        if constexpr (sizeof(T) == 4) multimem_ld_reduce_f32x4(base + i * V, f[u]);
+        else multimem_ld_reduce_bf16x8(base + i * V, f[u]);
+      }
+    }
 #pragma unroll
-      for (int k = 0; k < 8; ++k) f[k] *= scale;
-      multimem_st_bf16x8(base + i * V, f);
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= nvec) continue;
+#pragma unroll
+      for (int k = 0; k < V; ++k) f[u][k] *= scale;
+      if constexpr (sizeof(T) == 4) multimem_st_f32x4(base + i * V, f[u]);
+      else multimem_st_bf16x8(base + i * V, f[u]);
     }
   }
   __threadfence_system();

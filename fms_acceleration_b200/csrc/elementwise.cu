@@ -433,6 +433,28 @@ __global__ void colsum_kernel(const float* __restrict__ partial, float* __restri
   }
 }
 
+// Walks the [rows, I / 8] grid of 16-byte vectors with a grid-sized stride using 32-bit adds only: the stride's
+// (rows, vectors) decomposition is formed once per thread.
+struct VecWalk {
+  int r, c, dr, dc, vpr;
+  __device__ __forceinline__ VecWalk(int vec_per_row) : vpr(vec_per_row) {
+    const long long first = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    r = (int)(first / vpr);
+    c = (int)(first % vpr);
+    dr = (int)(stride / vpr);
+    dc = (int)(stride % vpr);
+  }
+  __device__ __forceinline__ void next() {
+    r += dr;
+    c += dc;
+    if (c >= vpr) {
+      c -= vpr;
+      r += 1;
+    }
+  }
+};
+
 // Rotary embedding on a packed [T, row_stride] buffer holding n_heads heads of size d starting
 // at column 0 (e.g. the q|k part of a fused qkv projection).  cos/sin: [max_pos, d/2] fp32.
 // sign = +1 forward, -1 backward.  In place.
@@ -442,13 +464,11 @@ __global__ void rope_kernel(T* __restrict__ qk, const int* __restrict__ pos, con
                             long long row_stride, float sign) {
   const int half = d / 2;
   const int vec_per_head = half / 8;
-  const long long total = (long long)T_tokens * n_heads * vec_per_head;
-  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
-       idx += (long long)gridDim.x * blockDim.x) {
-    const int v = (int)(idx % vec_per_head);
-    const long long th = idx / vec_per_head;
-    const int h = (int)(th % n_heads);
-    const long long t = th / n_heads;
+  // (token, vector within the token's heads) by 32-bit adds; the head comes from one small 32-bit division
+  for (VecWalk it(n_heads * vec_per_head); it.r < T_tokens; it.next()) {
+    const int h = it.c / vec_per_head;
+    const int v = it.c - h * vec_per_head;
+    const long long t = it.r;
     const int p = pos[t];
     T* base = qk + t * row_stride + (long long)h * d + v * 8;
     Vec8<T> a, b;
@@ -510,27 +530,6 @@ __device__ __forceinline__ void act_both(float e, float& f, float& df) {
   df = 0.5f * (1.f + th) + 0.5f * e * (1.f - th * th) * k * (1.f + 3.f * 0.044715f * e * e);
 }
 
-// Walks the [rows, I / 8] grid of 16-byte vectors with a grid-sized stride using 32-bit adds only: the stride's
-// (rows, vectors) decomposition is formed once per thread.
-struct VecWalk {
-  int r, c, dr, dc, vpr;
-  __device__ __forceinline__ VecWalk(int vec_per_row) : vpr(vec_per_row) {
-    const long long first = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-    const long long stride = (long long)gridDim.x * blockDim.x;
-    r = (int)(first / vpr);
-    c = (int)(first % vpr);
-    dr = (int)(stride / vpr);
-    dc = (int)(stride % vpr);
-  }
-  __device__ __forceinline__ void next() {
-    r += dr;
-    c += dc;
-    if (c >= vpr) {
-      c -= vpr;
-      r += 1;
-    }
-  }
-};
 
 // h[t, i] = act(e[t, i]) * g[t, i]    e, g, h: row strides in elements
 template <typename T, int ACT>
