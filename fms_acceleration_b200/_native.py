@@ -32,7 +32,7 @@ _SIGNATURES = {
     "fmsb_glu_bwd": [P, P, P, P, P, P, I, I, L, L, L, L, L, L, I, I, P, P],
     "fmsb_add": [P, P, P, L, I, P],
     "fmsb_ce": [P, L, P, P, P, P, P, I, I, I, F, I, I, P],
-    "fmsb_ce_bwd": [P, L, P, P, P, L, I, I, I, I, P],
+    "fmsb_ce_bwd": [P, L, P, L, P, P, P, L, I, I, I, I, P],
     "fmsb_count_valid": [P, L, I, P, P],
     "fmsb_quant4": [P, L, P, I, P, P, I, P],
     "fmsb_quant8_blockwise": [P, L, F, P, P, P, P],

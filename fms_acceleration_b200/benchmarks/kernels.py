@@ -364,6 +364,90 @@ def bench_reference(a):
 
     both(f"ScatterMoE layer fwd+bwd [{T} tokens, {E} experts top-{k}, {Hm}/{Im}]", mine_moe, ref_moe)
     NV.check_status()
+    del moe, xm, gm
+
+    def guarded(name, build):
+        """A comparison whose reference side has its own calling convention: a failure there is reported on the
+        line instead of ending the run."""
+        try:
+            mine, ref = build()
+            both(name, mine, ref)
+        except Exception as exc:  # noqa: BLE001 - the reference's kernels are foreign code
+            rec = {"op": name, "error": f"{type(exc).__name__}: {exc}"[:200]}
+            print(json.dumps(rec))
+            out.append(rec)
+
+    # rotary embedding on q and k (32 + 8 heads x 128), forward + backward, one 4096-token sequence per batch row
+    def build_rope():
+        from fms_acceleration_b200.ops import rope as RP
+
+        rope = BK._load_reference("fms_acceleration_foak", "kernels.unsloth.rope_embedding")
+        B, S, nq, nk, hd = T // 4096, 4096, 32, 8, 128
+        cos_t, sin_t = RP.rope_tables(hd, S, 10000.0, dev)
+        pos = torch.arange(S, device=dev, dtype=torch.int32).repeat(B)
+        q = torch.randn(B * S, nq, hd, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        kk = torch.randn(B * S, nk, hd, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        gq, gk = torch.randn_like(q), torch.randn_like(kk)
+        # the reference takes [batch, heads, seq, dim] views and full-width cos / sin tables in the compute dtype
+        cos_r = torch.cat([cos_t, cos_t], dim=-1).to(torch.bfloat16)
+        sin_r = torch.cat([sin_t, sin_t], dim=-1).to(torch.bfloat16)
+        q4 = q.detach().view(B, S, nq, hd).transpose(1, 2).requires_grad_()
+        k4 = kk.detach().view(B, S, nk, hd).transpose(1, 2).requires_grad_()
+        gq4, gk4 = gq.view(B, S, nq, hd).transpose(1, 2), gk.view(B, S, nk, hd).transpose(1, 2)
+
+        def mine():
+            a, b = RP.apply_rope(q, pos, cos_t, sin_t), RP.apply_rope(kk, pos, cos_t, sin_t)
+            torch.autograd.grad((a, b), (q, kk), (gq, gk))
+
+        def ref():
+            a, b = rope.fast_rope_embedding(q4, k4, cos_r, sin_r)
+            torch.autograd.grad((a, b), (q4, k4), (gq4, gk4))
+
+        return mine, ref
+
+    guarded(f"rope q,k fwd+bwd [{T} tokens, 32+8 heads x 128]", build_rope)
+
+    # plain cross-entropy on materialised logits, vocabulary 32000
+    def build_ce():
+        ce = BK._load_reference("fms_acceleration_foak", "kernels.unsloth.cross_entropy_loss")
+        logits = torch.randn(T, V, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        labels = torch.randint(0, V, (T,), device=dev)
+
+        def mine():
+            loss = CE.fast_cross_entropy_loss(logits, labels).sum() / T  # gradient over the logits, as the reference
+            torch.autograd.grad(loss, logits)
+
+        def ref():
+            loss = ce.fast_cross_entropy_loss(logits.view(1, T, V), labels.view(1, T))
+            torch.autograd.grad(loss, logits)
+
+        return mine, ref
+
+    guarded(f"cross-entropy fwd+bwd [{T} x {V}]", build_ce)
+
+    # GPTQ int4 dequantisation of a 4096 x 14336 weight (group 128)
+    def build_gptq():
+        from fms_acceleration_b200.ops import quant as Q
+
+        gk = BK._load_reference("fms_acceleration_foak", "fused_ops.unsloth_lora.gptq.triton.kernels")
+        i_f, o_f, gs = 4096, 14336, 128
+        wi = torch.randint(0, 16, (i_f, o_f), device=dev)
+        zi = torch.randint(0, 15, (i_f // gs, o_f), device=dev)
+        sc = (torch.rand(i_f // gs, o_f, device=dev) * 0.01).half()
+        qw, qz = Q.gptq_pack(wi, 4), Q.gptq_pack_zeros(zi, 4)
+        g_idx = (torch.arange(i_f, device=dev) // gs).int()
+        outw = torch.empty(i_f, o_f, device=dev, dtype=torch.float16)
+
+        def mine():
+            Q.gptq_dequant(qw, sc, qz, None, 4, gs, 0, out=outw)
+
+        def ref():
+            gk.dequant248(qw, sc, qz, g_idx, 4)
+
+        return mine, ref
+
+    guarded("GPTQ int4 dequantise [4096 x 14336]", build_gptq)
+    NV.check_status()
     return out
 
 

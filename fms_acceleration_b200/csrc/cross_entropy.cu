@@ -100,18 +100,37 @@ ce_kernel(T* logits, long long row_stride, const long long* __restrict__ labels,
   }
 
   MaxSum acc{-INFINITY, 0.f, 0.f};
-  for (int v = threadIdx.x; v < nvec; v += CE_THREADS) {
-    float f[n];
-    load_vec<T>(x + v * n, f);
-    float mx = f[0];
+  // four 16-byte loads in flight per thread, then one running-maximum update for the four vectors together
+  constexpr int U = 4;
+  for (int v0 = threadIdx.x; v0 < nvec; v0 += CE_THREADS * U) {
+    uint4 raw[U];
 #pragma unroll
-    for (int i = 1; i < n; ++i) mx = fmaxf(mx, f[i]);
+    for (int u = 0; u < U; ++u) {
+      const int v = v0 + u * CE_THREADS;
+      if (v < nvec) raw[u] = *reinterpret_cast<const uint4*>(x + v * n);
+    }
+    float f[U][n];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const bool ok = v0 + u * CE_THREADS < nvec;
+      const T* e = reinterpret_cast<const T*>(&raw[u]);
+#pragma unroll
+      for (int i = 0; i < n; ++i) {
+        f[u][i] = ok ? ld_as_float<T>(e + i) : -INFINITY;
+        mx = fmaxf(mx, f[u][i]);
+      }
+    }
     const float nm = fmaxf(acc.m, mx);
     float s = acc.m == -INFINITY ? 0.f : acc.s * __expf(acc.m - nm);
 #pragma unroll
-    for (int i = 0; i < n; ++i) {
-      s += __expf(f[i] - nm);
-      acc.t += f[i];
+    for (int u = 0; u < U; ++u) {
+      const bool ok = v0 + u * CE_THREADS < nvec;
+#pragma unroll
+      for (int i = 0; i < n; ++i) {
+        s += __expf(f[u][i] - nm);  // exp(-inf) = 0 for the slots beyond the row
+        if (ok) acc.t += f[u][i];
+      }
     }
     acc.m = nm;
     acc.s = s;
@@ -183,25 +202,61 @@ ce_kernel(T* logits, long long row_stride, const long long* __restrict__ labels,
   }
 }
 
-// Separate backward: dlogits = dloss[row] * (exp(x - lse[row]) - onehot), in place.
+// Separate backward: dst[row] = dloss[row] * (exp(src[row] - lse[row]) - onehot); dst may be src (in place, as the
+// reference does) or another matrix (no clone of the logits is needed for an out-of-place gradient).  16-byte loads
+// and stores when both rows are aligned; grid (rows, chunks of the vocabulary).
 template <typename T>
 __global__ void __launch_bounds__(256)
-ce_bwd_kernel(T* logits, long long row_stride, const long long* __restrict__ labels, const float* __restrict__ lse,
-              const float* __restrict__ dloss, long long dloss_stride, int V, int ignore_index) {
+ce_bwd_kernel(const T* src, long long src_stride, T* dst, long long dst_stride, const long long* __restrict__ labels,
+              const float* __restrict__ lse, const float* __restrict__ dloss, long long dloss_stride, int V,
+              int ignore_index) {
+  constexpr int n = VecN<T>::n;
   const int row = blockIdx.x;
-  T* x = logits + (long long)row * row_stride;
+  const T* x = src + (long long)row * src_stride;
+  T* y = dst + (long long)row * dst_stride;
   const long long label = labels[row];
   const float l = lse[row];
-  const float d = label == ignore_index ? 0.f : dloss[row * dloss_stride];
   const bool dead = label == ignore_index;
-  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < V; i += gridDim.y * blockDim.x) {
+  const float d = dead ? 0.f : dloss[row * dloss_stride];
+  const bool vec_ok = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
+  const int nvec = vec_ok ? V / n : 0;
+  // four vectors per thread and trip: the loads go out together
+  constexpr int U = 4;
+  const int stride = gridDim.y * blockDim.x;
+  for (int v0 = blockIdx.y * blockDim.x + threadIdx.x; v0 < nvec; v0 += stride * U) {
+    uint4 raw[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int v = v0 + u * stride;
+      raw[u] = (!dead && v < nvec) ? *reinterpret_cast<const uint4*>(x + v * n) : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int v = v0 + u * stride;
+      if (v >= nvec) continue;
+      float f[n];
+      const T* e = reinterpret_cast<const T*>(&raw[u]);
+#pragma unroll
+      for (int i = 0; i < n; ++i) {
+        float g = 0.f;
+        if (!dead) {
+          g = __expf(ld_as_float<T>(e + i) - l);
+          if ((long long)(v * n + i) == label) g -= 1.f;
+          g *= d;
+        }
+        f[i] = g;
+      }
+      store_vec<T>(y + v * n, f);
+    }
+  }
+  for (int i = nvec * n + blockIdx.y * blockDim.x + threadIdx.x; i < V; i += gridDim.y * blockDim.x) {
     float g = 0.f;
     if (!dead) {
       g = __expf(ld_as_float<T>(x + i) - l);
       if ((long long)i == label) g -= 1.f;
       g *= d;
     }
-    st_from_float<T>(x + i, g);
+    st_from_float<T>(y + i, g);
   }
 }
 
@@ -252,22 +307,27 @@ extern "C" int fmsb_ce(void* logits, long long row_stride, const long long* labe
   return (int)cudaGetLastError();
 }
 
-extern "C" int fmsb_ce_bwd(void* logits, long long row_stride, const long long* labels, const float* lse,
-                           const float* dloss, long long dloss_stride, int rows, int V, int ignore_index, int dtype,
-                           cudaStream_t stream) {
+extern "C" int fmsb_ce_bwd(const void* logits, long long row_stride, void* dlogits, long long d_stride,
+                           const long long* labels, const float* lse, const float* dloss, long long dloss_stride,
+                           int rows, int V, int ignore_index, int dtype, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  int chunks = (V + 4095) / 4096;
+  // 256 threads x 4 vectors of 16 bytes per trip, about four trips per thread: CTAs long enough to amortise the
+  // row's label / lse / dloss look-ups
+  const int per_vec = dtype == 2 ? 4 : 8;
+  int chunks = (V / per_vec + 4095) / 4096;
+  if (chunks < 1) chunks = 1;
   if (chunks > 65535) chunks = 65535;
   dim3 grid(rows, chunks);
   if (dtype == 0)
-    ce_bwd_kernel<__half><<<grid, 256, 0, stream>>>((__half*)logits, row_stride, labels, lse, dloss, dloss_stride, V,
-                                                    ignore_index);
+    ce_bwd_kernel<__half><<<grid, 256, 0, stream>>>((const __half*)logits, row_stride, (__half*)dlogits, d_stride,
+                                                    labels, lse, dloss, dloss_stride, V, ignore_index);
   else if (dtype == 1)
-    ce_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((__nv_bfloat16*)logits, row_stride, labels, lse, dloss,
+    ce_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)logits, row_stride,
+                                                           (__nv_bfloat16*)dlogits, d_stride, labels, lse, dloss,
                                                            dloss_stride, V, ignore_index);
   else if (dtype == 2)
-    ce_bwd_kernel<float><<<grid, 256, 0, stream>>>((float*)logits, row_stride, labels, lse, dloss, dloss_stride, V,
-                                                   ignore_index);
+    ce_bwd_kernel<float><<<grid, 256, 0, stream>>>((const float*)logits, row_stride, (float*)dlogits, d_stride, labels,
+                                                   lse, dloss, dloss_stride, V, ignore_index);
   else
     return -2;
   return (int)cudaGetLastError();

@@ -88,7 +88,9 @@ struct GemmCfg {
   static constexpr int kStagesRaw = (200 * 1024) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kTmemCols = (2 * BN) < 32 ? 32 : (2 * BN);
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+  // staging of the store epilogue (BN = 256 only): 8 warps x 2 slots x (32 rows x 64 B)
+  static constexpr int kEpiBytes = BN == 256 ? 8 * 2 * 2048 : 0;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
@@ -298,16 +300,75 @@ __device__ __forceinline__ void epilogue_store_tile(const GemmParams& p, const T
   }
 }
 
+// Epilogue of one tile for one warp through shared memory: every 32-column chunk of this warp's 32 accumulator lanes is
+// converted to 16 bits, written into a 2 KB staging slot (64-byte rows, 64-byte swizzle so that the quarter-warp phases
+// of the 16-byte stores hit distinct banks) and leaves with ONE bulk tensor store of a 32 x 32 box, which also clips the
+// ragged edges of M and N.  Two slots per warp alternate; a slot is rewritten only after the store that read it.
+template <int BN>
+__device__ __forceinline__ void epilogue_store_tile_tma(const GemmParams& p, const CUtensorMap* tmD, uint32_t taddr,
+                                                        int cpar, int row0, int gm, int n0, bool empty_k, uint32_t slots,
+                                                        int lane, int& slot) {
+  constexpr int CH = 32;
+#pragma unroll 1
+  for (int c = cpar; c < BN / CH; c += 2) {
+    uint32_t r[32];
+    tmem_ld_32x32(taddr + c * CH, r);
+    tmem_ld_wait();
+    float v[CH];
+#pragma unroll
+    for (int i = 0; i < CH; ++i) v[i] = (empty_k ? 0.f : __uint_as_float(r[i])) * p.alpha;
+    const int gn = n0 + c * CH;
+    if (p.C != nullptr && p.beta != 0.f && gm < p.M && gn < p.N) {
+      if (p.fmt == 1) {
+        const __nv_bfloat16* crow = reinterpret_cast<const __nv_bfloat16*>(p.C) + (long long)gm * p.ldc + gn;
+        for (int i = 0; i < CH; ++i)
+          if (gn + i < p.N) v[i] += p.beta * __bfloat162float(crow[i]);
+      } else {
+        const __half* crow = reinterpret_cast<const __half*>(p.C) + (long long)gm * p.ldc + gn;
+        for (int i = 0; i < CH; ++i)
+          if (gn + i < p.N) v[i] += p.beta * __half2float(crow[i]);
+      }
+    }
+    const uint32_t buf = slots + static_cast<uint32_t>(slot) * 2048u;
+    if (lane == 0) tma_store_wait_read<1>();  // the store that last read this slot (two stores ago) is done with it
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t w0, w1, w2, w3;
+      if (p.fmt == 1) {
+        w0 = pack_bf16x2(v[8 * j], v[8 * j + 1]); w1 = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
+        w2 = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]); w3 = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
+      } else {
+        w0 = pack_f16x2(v[8 * j], v[8 * j + 1]); w1 = pack_f16x2(v[8 * j + 2], v[8 * j + 3]);
+        w2 = pack_f16x2(v[8 * j + 4], v[8 * j + 5]); w3 = pack_f16x2(v[8 * j + 6], v[8 * j + 7]);
+      }
+      const uint32_t chunk = static_cast<uint32_t>(j) ^ ((static_cast<uint32_t>(lane) >> 1) & 3u);  // 64-byte swizzle
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(buf + lane * 64u + chunk * 16u), "r"(w0), "r"(w1),
+                   "r"(w2), "r"(w3)
+                   : "memory");
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0 && gn < p.N && row0 < p.M) {
+      tma_store_2d(tmD, buf, gn, row0);
+      tma_store_commit();
+    }
+    slot ^= 1;
+  }
+}
+
 template <int BN, int A_MN, int B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
                     const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
-                    const __grid_constant__ CUtensorMap tmBalt, const GemmParams p) {
+                    const __grid_constant__ CUtensorMap tmBalt, const __grid_constant__ CUtensorMap tmD,
+                    const GemmParams p) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzled tiles need 1024-byte alignment
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bar_base = smem_base + Cfg::kStages * Cfg::kStageBytes;
+  const uint32_t epi_base = smem_base + Cfg::kStages * Cfg::kStageBytes;
+  const uint32_t bar_base = epi_base + Cfg::kEpiBytes;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::kStages + s); };
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * Cfg::kStages + a); };
@@ -448,8 +509,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_const
     const int row = q * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
-    constexpr int CH = BN >= 32 ? 32 : 16;
     TileInfo ti;
+    // store epilogue through shared memory (BN = 256, 16-bit D, plain and grouped-M modes): two 2 KB slots per warp
+    const uint32_t my_slots = epi_base + static_cast<uint32_t>(warp - 2) * 4096u;
+    int slot = 0;
     for (int t = blockIdx.x; get_tile<BN>(t, p, ti); t += gridDim.x) {
       const int gm = ti.m_store + row;
       const int n0 = ti.n0;
@@ -457,11 +520,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_const
       if (!mbar_wait(tfull_bar(acc), acc_phase, p.status, kTimeoutEpilogue)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
-      epilogue_store_tile<BN>(p, ti, taddr, cpar, gm, n0, empty_k);
+      bool stored = false;
+      if constexpr (BN == 256) {
+        // a box store writes 32 whole rows: only for tiles whose rows all belong to the segment
+        if (p.tma_store && ti.m_store + BM <= ti.m_end) {
+          epilogue_store_tile_tma<BN>(p, &tmD, taddr, cpar, ti.m_store + q * 32, gm, n0, empty_k, my_slots, lane, slot);
+          stored = true;
+        }
+      }
+      if (!stored) epilogue_store_tile<BN>(p, ti, taddr, cpar, gm, n0, empty_k);
       tc_fence_before();
       mbar_arrive(tempty_bar(acc));
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
+    }
+    if constexpr (BN == 256) {
+      if (p.tma_store && lane == 0) tma_store_wait<0>();  // the staging slots stay valid until the last store has read them
     }
   }
 
@@ -475,63 +549,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA1, const __grid_const
   }
 }
 
-
-// Epilogue of one tile for one warp through shared memory: every 32-column chunk of this warp's 32 accumulator lanes is
-// converted to 16 bits, written into a 2 KB staging slot (64-byte rows, 64-byte swizzle so that the quarter-warp phases
-// of the 16-byte stores hit distinct banks) and leaves with ONE bulk tensor store of a 32 x 32 box, which also clips the
-// ragged edges of M and N.  Two slots per warp alternate; a slot is rewritten only after the store that read it.
-template <int BN>
-__device__ __forceinline__ void epilogue_store_tile_tma(const GemmParams& p, const CUtensorMap* tmD, uint32_t taddr,
-                                                        int cpar, int row0, int gm, int n0, bool empty_k, uint32_t slots,
-                                                        int lane, int& slot) {
-  constexpr int CH = 32;
-#pragma unroll 1
-  for (int c = cpar; c < BN / CH; c += 2) {
-    uint32_t r[32];
-    tmem_ld_32x32(taddr + c * CH, r);
-    tmem_ld_wait();
-    float v[CH];
-#pragma unroll
-    for (int i = 0; i < CH; ++i) v[i] = (empty_k ? 0.f : __uint_as_float(r[i])) * p.alpha;
-    const int gn = n0 + c * CH;
-    if (p.C != nullptr && p.beta != 0.f && gm < p.M && gn < p.N) {
-      if (p.fmt == 1) {
-        const __nv_bfloat16* crow = reinterpret_cast<const __nv_bfloat16*>(p.C) + (long long)gm * p.ldc + gn;
-        for (int i = 0; i < CH; ++i)
-          if (gn + i < p.N) v[i] += p.beta * __bfloat162float(crow[i]);
-      } else {
-        const __half* crow = reinterpret_cast<const __half*>(p.C) + (long long)gm * p.ldc + gn;
-        for (int i = 0; i < CH; ++i)
-          if (gn + i < p.N) v[i] += p.beta * __half2float(crow[i]);
-      }
-    }
-    const uint32_t buf = slots + static_cast<uint32_t>(slot) * 2048u;
-    if (lane == 0) tma_store_wait_read<1>();  // the store that last read this slot (two stores ago) is done with it
-    __syncwarp();
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      uint32_t w0, w1, w2, w3;
-      if (p.fmt == 1) {
-        w0 = pack_bf16x2(v[8 * j], v[8 * j + 1]); w1 = pack_bf16x2(v[8 * j + 2], v[8 * j + 3]);
-        w2 = pack_bf16x2(v[8 * j + 4], v[8 * j + 5]); w3 = pack_bf16x2(v[8 * j + 6], v[8 * j + 7]);
-      } else {
-        w0 = pack_f16x2(v[8 * j], v[8 * j + 1]); w1 = pack_f16x2(v[8 * j + 2], v[8 * j + 3]);
-        w2 = pack_f16x2(v[8 * j + 4], v[8 * j + 5]); w3 = pack_f16x2(v[8 * j + 6], v[8 * j + 7]);
-      }
-      const uint32_t chunk = static_cast<uint32_t>(j) ^ ((static_cast<uint32_t>(lane) >> 1) & 3u);  // 64-byte swizzle
-      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(buf + lane * 64u + chunk * 16u), "r"(w0), "r"(w1),
-                   "r"(w2), "r"(w3)
-                   : "memory");
-    }
-    fence_proxy_async_smem();
-    __syncwarp();
-    if (lane == 0 && gn < p.N && row0 < p.M) {
-      tma_store_2d(tmD, buf, gn, row0);
-      tma_store_commit();
-    }
-    slot ^= 1;
-  }
-}
 
 // ----------------------------------------------------------------------------------------
 // CTA-pair variant (plain mode, 256 x 256 output tiles): a cluster of two CTAs on the two SMs of one TPC computes
@@ -813,7 +830,8 @@ int sm_count() {
 
 template <int BN, int A_MN, int B_MN>
 int launch_gemm(const CUtensorMap& a1, const CUtensorMap& b1, const CUtensorMap& a2, const CUtensorMap& b2,
-                const CUtensorMap& balt, const fmsb::GemmParams& p, int max_ctas, cudaStream_t stream) {
+                const CUtensorMap& balt, const CUtensorMap& d, const fmsb::GemmParams& p, int max_ctas,
+                cudaStream_t stream) {
   using Cfg = fmsb::GemmCfg<BN>;
   auto kern = fmsb::gemm_tcgen05_kernel<BN, A_MN, B_MN>;
   static bool configured = false;
@@ -829,7 +847,7 @@ int launch_gemm(const CUtensorMap& a1, const CUtensorMap& b1, const CUtensorMap&
     if (tiles < ctas) ctas = tiles;
   }
   if (ctas <= 0) return 0;
-  kern<<<ctas, fmsb::kGemmThreads, Cfg::kSmemBytes, stream>>>(a1, b1, a2, b2, balt, p);
+  kern<<<ctas, fmsb::kGemmThreads, Cfg::kSmemBytes, stream>>>(a1, b1, a2, b2, balt, d, p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -879,6 +897,7 @@ int launch_gemm_pair(const CUtensorMap& a1, const CUtensorMap& b1, const CUtenso
 
 // store epilogue through shared memory and bulk tensor stores (1, default) or per-thread 16-byte stores (0)
 static int g_pair_tma_store = 1;
+static int g_single_tma_store = 1;
 
 // 0: never, 1: when there are enough 256 x 256 tiles to fill the machine about twice (default), 2: whenever M and N
 // reach 256; set through fmsb_gemm_set_pair_mode (tests compare both kernels on small shapes)
@@ -891,9 +910,12 @@ extern "C" int fmsb_gemm_pair_occupancy() {
   return fmsb_host::g_pair_occupancy_error > 0 ? -fmsb_host::g_pair_occupancy_error - 1 : fmsb_host::g_pair_occupancy;
 }
 
+// 1 (default): 16-bit D leaves through shared memory and bulk tensor stores (CTA-pair kernel, and the single-CTA kernel
+// with BN = 256 in the plain and grouped-M modes); 0: per-thread 16-byte stores everywhere (the cross-check of the tests)
 extern "C" int fmsb_gemm_set_pair_store(int tma_store) {
   const int old = fmsb_host::g_pair_tma_store;
   fmsb_host::g_pair_tma_store = tma_store;
+  fmsb_host::g_single_tma_store = tma_store;
   return old;
 }
 
@@ -1019,13 +1041,19 @@ static int gemm_impl(const void* A1, long long lda1, const void* B1, long long l
     if (!a_mn && b_mn) return launch_gemm_pair<0, 1>(ta1, tb1, ta2, tb2, td, p, max_ctas, stream);
     return launch_gemm_pair<1, 1>(ta1, tb1, ta2, tb2, td, p, max_ctas, stream);
   }
+  // single-CTA kernel: the store epilogue through shared memory serves BN = 256 in the plain and grouped-M modes
+  CUtensorMap td1 = ta1;
+  if (bn == 256 && (mode == 0 || mode == 1) && bd == nullptr && g_single_tma_store && !d_fp32 && ldd % 8 == 0 &&
+      (reinterpret_cast<uintptr_t>(D) & 15) == 0 &&
+      make_tmap_2d_16b_sw64(&td1, D, (uint64_t)M, (uint64_t)N, (uint64_t)ldd, 32, 32) == 0)
+    p.tma_store = 1;
 #define FMSB_DISPATCH(BNV)                                                                          \
   if (bn == BNV) {                                                                                  \
-    if (!a_mn && !b_mn) return launch_gemm<BNV, 0, 0>(ta1, tb1, ta2, tb2, tbalt, p, max_ctas, stream);     \
-    if (a_mn && !b_mn) return launch_gemm<BNV, 1, 0>(ta1, tb1, ta2, tb2, tbalt, p, max_ctas, stream);      \
+    if (!a_mn && !b_mn) return launch_gemm<BNV, 0, 0>(ta1, tb1, ta2, tb2, tbalt, td1, p, max_ctas, stream);     \
+    if (a_mn && !b_mn) return launch_gemm<BNV, 1, 0>(ta1, tb1, ta2, tb2, tbalt, td1, p, max_ctas, stream);      \
     if constexpr (BNV >= 64) {                                                                      \
-      if (!a_mn && b_mn) return launch_gemm<BNV, 0, 1>(ta1, tb1, ta2, tb2, tbalt, p, max_ctas, stream);    \
-      if (a_mn && b_mn) return launch_gemm<BNV, 1, 1>(ta1, tb1, ta2, tb2, tbalt, p, max_ctas, stream);     \
+      if (!a_mn && b_mn) return launch_gemm<BNV, 0, 1>(ta1, tb1, ta2, tb2, tbalt, td1, p, max_ctas, stream);    \
+      if (a_mn && b_mn) return launch_gemm<BNV, 1, 1>(ta1, tb1, ta2, tb2, tbalt, td1, p, max_ctas, stream);     \
     }                                                                                               \
   }
   FMSB_DISPATCH(256)

@@ -71,10 +71,11 @@ class _CrossEntropy(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dloss):
         l2, lab, lse = ctx.saved_tensors
-        g = l2 if ctx.inplace else l2.clone()
+        g = l2 if ctx.inplace else torch.empty_like(l2)
         d = dloss.reshape(-1).float().contiguous()
-        rc = N.lib().fmsb_ce_bwd(g.data_ptr(), g.stride(0), lab.data_ptr(), lse.data_ptr(), d.data_ptr(), 1,
-                                 g.shape[0], g.shape[1], ctx.ignore_index, N.dtype_code(g.dtype), N.stream_ptr())
+        rc = N.lib().fmsb_ce_bwd(l2.data_ptr(), l2.stride(0), g.data_ptr(), g.stride(0), lab.data_ptr(),
+                                 lse.data_ptr(), d.data_ptr(), 1, g.shape[0], g.shape[1], ctx.ignore_index,
+                                 N.dtype_code(g.dtype), N.stream_ptr())
         N.check(rc, "fmsb_ce_bwd")
         return g.view(ctx.shape), None, None, None
 

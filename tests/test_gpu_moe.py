@@ -104,6 +104,40 @@ def test_expert_lora_rides_in_the_grouped_gemm(T, H, I, E, k, r):
     assert _rel(moe.router.weight.grad, rw.grad) < 6e-2
 
 
+@pytest.mark.parametrize("N,K,b_mn", [(1536, 512, True), (512, 1536, False), (1024, 1536, True), (264, 512, True)])
+def test_grouped_gemm_store_epilogue_matches_plain_stores(N, K, b_mn):
+    """Grouped-M GEMM: the epilogue through shared memory and bulk tensor stores gives the same bits as per-thread
+    stores, with empty and single-tile segments, and both equal the fp32 product per segment."""
+    from fms_acceleration_b200.ops.gemm import set_pair_store
+
+    torch.manual_seed(N + K)
+    E = 6
+    tiles = [3, 0, 1, 5, 2, 0]
+    off = [0]
+    for t in tiles:
+        off.append(off[-1] + 128 * t)
+    rows = off[-1]
+    seg_off = torch.tensor(off + [rows], dtype=torch.int32, device=DEV)
+    a = (torch.randn(rows, K, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(E, K, N, device=DEV) * 0.05).bfloat16() if b_mn else (torch.randn(E, N, K, device=DEV) * 0.05).bfloat16()
+    outs = []
+    for store in (1, 0):
+        old = set_pair_store(store)
+        try:
+            out = torch.full((rows, N), 3.0, device=DEV, dtype=torch.bfloat16)
+            MOE.grouped_gemm(a, w.view(-1, w.shape[2]), seg_off, E, mode=1, b_mn=b_mn, n=N, out=out)
+            NV.check_status()
+            outs.append(out)
+        finally:
+            set_pair_store(old)
+    assert torch.equal(outs[0], outs[1])
+    for e in range(E):
+        r0, r1 = off[e], off[e + 1]
+        if r1 > r0:
+            ref = a[r0:r1].float() @ (w[e].float() if b_mn else w[e].float().t())
+            assert _rel(outs[0][r0:r1], ref) < 1e-2
+
+
 def test_granitemoe_fused_model_trains():
     torch.manual_seed(0)
     model = build_model("tiny-granitemoe", device=DEV, dtype=torch.bfloat16, seed=0)
