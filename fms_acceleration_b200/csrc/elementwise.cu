@@ -86,7 +86,7 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// Row-in-registers RMSNorm for the common row widths (H = 1024 ... 4096): one warp (or a pair of warps, WPR = 2) keeps
+// Row-in-registers RMSNorm for the common row widths (H = 1024 ... 8192): one warp (or 2, 4 or 8 warps, WPR) keeps
 // its row packed in registers (VPL 16-byte vectors per lane), reduces with shuffles (plus one 64-thread named barrier
 // for a pair) and never meets a block-wide barrier, so the warps of a CTA stream independent rows and an SM has 16 or
 // more rows in flight.  The block-per-row kernels below had one or two rows in flight per CTA around two
@@ -639,7 +639,9 @@ static inline int grid_for(long long work_items, int threads, int cap_blocks) {
 using namespace fmsb;
 
 // row widths served by the row-in-registers kernels (the block-per-row kernels take every other width)
-static bool norm_rows_ok(int H) { return H == 1024 || H == 1536 || H == 2048 || H == 2560 || H == 4096; }
+static bool norm_rows_ok(int H) {
+  return H == 1024 || H == 1536 || H == 2048 || H == 2560 || H == 4096 || H == 5120 || H == 8192;
+}
 static int norm_rows_grid(int rows, int wpr) {
   const int rpc = NORM_WARPS / wpr;
   const int need = (rows + rpc - 1) / rpc;
@@ -661,6 +663,8 @@ extern "C" int fmsb_rmsnorm_fwd(const void* x, const void* residual, const void*
     case 1536: FMSB_NORM_FWD_R(T, 6, 1); break;                 \
     case 2048: FMSB_NORM_FWD_R(T, 4, 2); break;                 \
     case 2560: FMSB_NORM_FWD_R(T, 5, 2); break;                 \
+    case 5120: FMSB_NORM_FWD_R(T, 5, 4); break;                 \
+    case 8192: FMSB_NORM_FWD_R(T, 4, 8); break;                 \
     default: FMSB_NORM_FWD_R(T, 8, 2); break;                   \
   }
     if (dtype == 1) { FMSB_NORM_FWD_RT(__nv_bfloat16) } else { FMSB_NORM_FWD_RT(__half) }
@@ -707,6 +711,8 @@ extern "C" int fmsb_rmsnorm_bwd(const void* dy, const void* x, const void* w, co
     case 1536: FMSB_NORM_BWD_R(T, 3, 2); break;                 \
     case 2048: FMSB_NORM_BWD_R(T, 4, 2); break;                 \
     case 2560: FMSB_NORM_BWD_R(T, 5, 2); break;                 \
+    case 5120: FMSB_NORM_BWD_R(T, 5, 4); break;                 \
+    case 8192: FMSB_NORM_BWD_R(T, 4, 8); break;                 \
     default: FMSB_NORM_BWD_R(T, 4, 4); break;                   \
   }
     if (dtype == 1) { FMSB_NORM_BWD_RT(__nv_bfloat16) } else { FMSB_NORM_BWD_RT(__half) }

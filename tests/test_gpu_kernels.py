@@ -125,7 +125,8 @@ def test_gemm_cta_pair_kernel(a_mn, b_mn, M, N_, K):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("rows,H", [(7, 256), (300, 4096), (33, 1536), (20011, 1024), (130, 2048), (5000, 2560), (10007, 4096)])
+@pytest.mark.parametrize("rows,H", [(7, 256), (300, 4096), (33, 1536), (20011, 1024), (130, 2048), (5000, 2560), (10007, 4096),
+                                    (3001, 5120), (1501, 8192), (9, 6144)])
 def test_rmsnorm(dtype, rows, H):
     torch.manual_seed(0)
     x = torch.randn(rows, H, device=DEV, dtype=dtype, requires_grad=True)
@@ -155,7 +156,7 @@ def test_rmsnorm(dtype, rows, H):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("rows,H", [(37, 1024), (20011, 1024), (301, 1536), (130, 2048), (77, 2560), (300, 4096),
-                                    (10007, 4096), (19, 8192), (45, 512)])
+                                    (10007, 4096), (33, 5120), (2999, 8192), (45, 512), (11, 6144)])
 @pytest.mark.parametrize("gemma", [False, True])
 def test_rmsnorm_frozen_weight_paths(dtype, rows, H, gemma):
     """Frozen norm weight (adapter training): forward with and without the fused residual add and the backward that
