@@ -73,10 +73,18 @@ __global__ void __launch_bounds__(256) ssd_make_g2_kernel(const T* __restrict__ 
   const int vpr = Q >> 3, rpp = 256 / vpr;  // vectors per row, rows per pass of the block
   const int s0 = (threadIdx.x % vpr) << 3, r0 = threadIdx.x / vpr;
   const int t_end = min(Q, t0 + G2_ROWS);
-  float ls[8], ds[8];
+  float ls[8], ds[8], wj[8];
+  bool split = false;
   if (s0 < t_end) {
     ld8f(Lt + lbase + s0, ls);
     ld8f(dtt + lbase + s0, ds);
+    // exp(L_t - L_s) = exp(L_t - L_s0) * exp(L_s0 - L_s): one exponential per row and thread instead of eight, the
+    // column factors (times dt_s) are formed once.  Only while the decay across the thread's eight columns is
+    // moderate (exponent below 60: no overflow of the column factor, no underflow of the row factor that matters);
+    // otherwise every element takes its own exponential.
+    split = fabsf(ls[0] - ls[7]) < 60.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) wj[j] = split ? __expf(ls[0] - ls[j]) * ds[j] : 0.f;
   }
   const int gi = h / (nh / G);
   const T* cbt = cb + ((long long)c * G + gi) * Q * Q;
@@ -89,8 +97,14 @@ __global__ void __launch_bounds__(256) ssd_make_g2_kernel(const T* __restrict__ 
       const float lt = __ldg(Lt + lbase + t);
       float f[8];
       unpack8<T>(u, f);
+      if (split) {
+        const float e = __expf(lt - ls[0]);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) f[j] = (s0 + j <= t) ? f[j] * __expf(lt - ls[j]) * ds[j] : 0.f;
+        for (int j = 0; j < 8; ++j) f[j] = (s0 + j <= t) ? f[j] * e * wj[j] : 0.f;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = (s0 + j <= t) ? f[j] * __expf(lt - ls[j]) * ds[j] : 0.f;
+      }
       out = pack8<T>(f);
     }
     *reinterpret_cast<uint4*>(gt + (long long)t * Q + s0) = out;

@@ -95,6 +95,29 @@ def test_ssd_scan_matches_recurrence(T, nh, P, G, N, Q, with_h0, monkeypatch):
         assert _rel(h0.grad.cpu(), h0r.grad) < 5e-2
 
 
+@pytest.mark.parametrize("Q", [64, 256])
+def test_decay_matrix_kernel_with_moderate_and_extreme_decay(Q):
+    """G[c, h, t, s] = CB[c, g, t, s] exp(L_t - L_s) dt_s for s <= t, 0 above the diagonal.  Heads with a moderate
+    decay take the factored exponentials (one per row and thread), a head that forgets within a step takes one
+    exponential per element; both must match the fp64 formula."""
+    torch.manual_seed(0)
+    nc, nh, G = 3, 4, 2
+    cb = (torch.randn(nc * G * Q, Q, device=DEV) * 0.5).bfloat16()
+    dt = torch.rand(nc, nh, Q, device=DEV) * 0.09 + 0.01
+    A = torch.tensor([-0.5, -3.0, -16.0, -2000.0], device=DEV)  # the last head: exp(-20..-200) per step
+    Lt = (dt * A[None, :, None]).cumsum(-1).contiguous()
+    g = MB._make_g(cb, Lt, dt.contiguous(), nc, nh, G, Q).view(nc, nh, Q, Q)
+    NV.check_status()
+    cb4 = cb.view(nc, G, Q, Q).double().repeat_interleave(nh // G, dim=1)
+    Ld = Lt.double()
+    ref = cb4 * torch.exp(Ld[..., :, None] - Ld[..., None, :]) * dt.double()[..., None, :]
+    ref = torch.tril(ref)
+    assert torch.isfinite(g.float()).all()
+    for h in range(nh):
+        assert _rel(g[:, h], ref[:, h]) < 1e-2, h
+    assert torch.all(torch.triu(g.float(), diagonal=1) == 0)
+
+
 def test_mamba2_model_matches_cpu_reference():
     from fms_acceleration_b200.models.builder import build_model
 
