@@ -70,9 +70,10 @@ class GraniteMoeDecoderLayer(LlamaDecoderLayer):
 
     def forward(self, x, pos, cos_t, sin_t, cu_seqlens):
         rm = self.cfg.residual_multiplier
-        x = x + rm * self.self_attn(self.input_layernorm(x), pos, cos_t, sin_t, cu_seqlens)
+        # x + rm * y as ONE element-wise kernel (add with alpha), not a multiply followed by an add
+        x = torch.add(x, self.self_attn(self.input_layernorm(x), pos, cos_t, sin_t, cu_seqlens), alpha=rm)
         moe_out, _ = self.block_sparse_moe(self.post_attention_layernorm(x))
-        return x + rm * moe_out
+        return torch.add(x, moe_out, alpha=rm)
 
 
 class GraniteMoeModel(LlamaModel):
@@ -117,8 +118,8 @@ class GraniteMoeSharedDecoderLayer(GraniteMoeDecoderLayer):
 
     def forward(self, x, pos, cos_t, sin_t, cu_seqlens):
         rm = self.cfg.residual_multiplier
-        x = x + rm * self.self_attn(self.input_layernorm(x), pos, cos_t, sin_t, cu_seqlens)
-        return x + rm * self._ffn(self.post_attention_layernorm(x))
+        x = torch.add(x, self.self_attn(self.input_layernorm(x), pos, cos_t, sin_t, cu_seqlens), alpha=rm)
+        return torch.add(x, self._ffn(self.post_attention_layernorm(x)), alpha=rm)
 
 
 class GraniteMoeSharedModel(LlamaModel):

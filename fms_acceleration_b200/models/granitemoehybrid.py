@@ -42,7 +42,7 @@ class GraniteMoeHybridDecoderLayer(nn.Module):
             mix = torch.cat([self.mamba(h[s:e]) for s, e in zip(cu[:-1], cu[1:])], dim=0) if len(cu) > 2 else self.mamba(h)
         else:
             mix = self.self_attn(h, pos, cos_t, sin_t, cu)
-        x = x + rm * mix
+        x = torch.add(x, mix, alpha=rm)
         y = self.post_attention_layernorm(x)
         out = 0
         if self.block_sparse_moe is not None:
@@ -50,7 +50,7 @@ class GraniteMoeHybridDecoderLayer(nn.Module):
             out = moe[0] if isinstance(moe, tuple) else moe
         if self.shared_mlp is not None:
             out = out + self.shared_mlp(y)
-        return x + rm * out
+        return torch.add(x, out, alpha=rm)
 
 
 class GraniteMoeHybridModel(nn.Module):

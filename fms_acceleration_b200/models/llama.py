@@ -121,8 +121,8 @@ class LlamaDecoderLayer(nn.Module):
     # eager
     def forward(self, x, pos, cos_t, sin_t, cu_seqlens):
         rm = self.cfg.residual_multiplier
-        x = x + rm * self.self_attn(self.input_layernorm(x), pos, cos_t, sin_t, cu_seqlens)
-        x = x + rm * self.mlp(self.post_attention_layernorm(x))
+        x = torch.add(x, self.self_attn(self.input_layernorm(x), pos, cos_t, sin_t, cu_seqlens), alpha=rm)
+        x = torch.add(x, self.mlp(self.post_attention_layernorm(x)), alpha=rm)
         return x
 
     # fused
