@@ -118,7 +118,9 @@ class Mamba2Mixer(nn.Module):
             y = self.cp.scan(x.contiguous(), dt, A, B.contiguous(), C.contiguous(), self.D.float(), Q, self.layer_idx)
         else:
             y, _ = MB.ssd_scan(x.contiguous(), dt, A, B.contiguous(), C.contiguous(), self.D.float(), None, Q)
-        y = y[:T].reshape(T, di)
+        if pad:  # an unconditional y[:T] records a slice whose backward zero-fills and copies a [T, d_inner] tensor
+            y = y[:T]
+        y = y.reshape(T, di)
         y = self.norm(_aligned(y), _aligned(z))
         return _linear(y, self.out_proj)
 
