@@ -15,10 +15,10 @@ Expert parallelism (every rank owns ``E / ep`` experts), no host synchronisation
   buffer, and on the way back sums the (weighted) expert outputs of a staged row into one row that the source
   pulls.  For 40 experts on 8 ranks with top-8 that is 5.6 instead of 8 rows per token and direction, on 2 ranks
   2 instead of 8.
-* **Token chunks pipelined over two streams.**  The tokens of a call are cut into ``n_chunks`` slices; dispatch and
-  combine of one slice run on a communication stream while the grouped GEMMs of the neighbouring slice run on the
-  compute stream (two staging sets, reused every other chunk; the cross-rank barriers that order the reuse are on
-  the communication stream).
+* **Token chunks pipelined over two streams (optional).**  The tokens of a call can be cut into ``n_chunks`` slices;
+  dispatch and combine of one slice then run on a communication stream while the grouped GEMMs of the neighbouring
+  slice run on the compute stream (two staging sets, reused every other chunk; the cross-rank barriers that order
+  the reuse are on the communication stream).  One slice is the default: see :class:`MoEContext`.
 * **Fixed layout from an agreed token budget.**  Staging blocks and the expert-sorted capacity are sized once from
   the largest number of tokens a rank may bring to one call (agreed over the group at set-up), so ranks whose
   padding-free batches differ in length still address the same layout and nothing is re-allocated per step.  Rows
@@ -249,7 +249,9 @@ class MoEContext:
 
     ``token_budget``: the largest number of tokens this rank may hand to one call (expert parallelism only; default
     ``FMSB_MOE_TOKEN_BUDGET`` or, failing that, the maximum over the ranks of the first call's token count).
-    ``n_chunks``: slices a call is pipelined in (``FMSB_MOE_CHUNKS``; default 1 on two ranks, 2 beyond).  ``capacity_factor`` (default
+    ``n_chunks``: slices a call is pipelined in (``FMSB_MOE_CHUNKS``; default 1: on 4 and 8 GPUs the Granite step
+    measured the same or slightly faster unsliced, 231.9 against 234.6 ms and 268.7 against 270.6 ms, because half-size
+    grouped GEMMs and the doubled barriers cost what the overlap gains).  ``capacity_factor`` (default
     ``FMSB_MOE_CAPACITY_FACTOR`` or 2.0): receive capacity of an owner in units of the balanced load."""
 
     _shared: dict = {}
@@ -268,7 +270,7 @@ class MoEContext:
         self.token_budget = token_budget or int(os.environ.get("FMSB_MOE_TOKEN_BUDGET", "0")) or None
         # measured on two B200s (Granite-3B-sized layer): with one peer the exchange is small next to the fixed cost of a
         # second slice, so pipelining starts at four ranks
-        self.n_chunks = n_chunks or int(os.environ.get("FMSB_MOE_CHUNKS", "0")) or (1 if self.world <= 2 else 2)
+        self.n_chunks = n_chunks or int(os.environ.get("FMSB_MOE_CHUNKS", "0")) or 1
         self.gemm_ctas = int(os.environ.get("FMSB_MOE_GEMM_CTAS", "0"))  # 0: every SM
         self.tag = layer_tag
         self.cap = 0  # world == 1: rows of the expert-sorted buffer (tests may lower it to provoke an overflow)
@@ -431,8 +433,10 @@ def _experts_bwd_local(mctx, Xs, gu, dYs, seg_off, w1, w3, w2, act, acc, need_dw
         acc["dw1_final"] = grouped_gemm(Xs, gu[:, :I_], seg_off, El, mode=2, m=H, n=I_, out_dtype=w1.dtype, max_ctas=nc)
         acc["dw3_final"] = grouped_gemm(Xs, gu[:, I_:], seg_off, El, mode=2, m=H, n=I_, out_dtype=w3.dtype, max_ctas=nc)
     elif need_dw:
-        # [d gate | d up] side by side in gu: both weight gradients in one pass over Xs
-        _acc_gemm(acc, "dw13", Xs, gu, seg_off, El, H, 2 * I_, nc)
+        # one fp32 accumulator per weight: the cast at the end is then a contiguous one (the halves of a merged
+        # [H, 2I] accumulator would need a strided cast each)
+        _acc_gemm(acc, "dw1", Xs, gu[:, :I_], seg_off, El, H, I_, nc)
+        _acc_gemm(acc, "dw3", Xs, gu[:, I_:], seg_off, El, H, I_, nc)
     dXs = grouped_gemm(gu[:, :I_], w1.view(El * H, I_), seg_off, El, mode=1, b_mn=False, n=H, a2=gu[:, I_:],
                        b2=w3.view(El * H, I_), max_ctas=nc)
     if lora is not None:
@@ -456,8 +460,8 @@ def _weight_grads(mctx, acc, w1, w3, w2, needs):
     if "dw2_final" in acc:
         return (acc["dw1_final"] if needs[0] else None, acc["dw3_final"] if needs[1] else None,
                 acc["dw2_final"] if needs[2] else None)
-    dw1 = acc["dw13"][:, :, :I_].to(w1.dtype) if needs[0] and "dw13" in acc else None
-    dw3 = acc["dw13"][:, :, I_:].to(w3.dtype) if needs[1] and "dw13" in acc else None
+    dw1 = acc["dw1"].to(w1.dtype) if needs[0] and "dw1" in acc else None
+    dw3 = acc["dw3"].to(w3.dtype) if needs[1] and "dw3" in acc else None
     dw2 = acc["dw2"].to(w2.dtype) if needs[2] and "dw2" in acc else None
     return dw1, dw3, dw2
 
