@@ -50,7 +50,8 @@ def reference_arm(args) -> int:
             last = [ln for ln in res.stderr.strip().splitlines() if ln.strip()]
             reason = ("the reference's public API does not import on this image: "
                       + (last[-1] if last else f"exit code {res.returncode}"))[:300]
-    print(json.dumps({"impl": "reference", "unavailable": reason.replace("\n", " ")}), flush=True)
+    if int(os.environ.get("RANK", "0")) == 0:  # one line per job, also when launched with one process per GPU
+        print(json.dumps({"impl": "reference", "unavailable": reason.replace("\n", " ")}), flush=True)
     return 0
 
 
