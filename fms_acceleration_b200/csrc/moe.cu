@@ -438,6 +438,27 @@ __global__ void moe_zero_pad_kernel(T* __restrict__ buf, long long ld, int H, co
 // out[t][:] = sum_k w[t, k] * owner_buf(t, k)[dest_row(t, k)][:]   (w == nullptr: plain sum).  One warp per token;
 // the expert outputs are read from the owners' buffers (peer loads when remote).  Lanes 0..k-1 fetch the pair
 // metadata once; the rows of two pairs (8 vectors of 16 bytes per lane) are in flight together.
+// Predicated 16-byte load (zeros when `on` is false) that the compiler keeps where it is written: the combine kernel
+// issues all loads of a pass as straight-line code before the first use (left to itself the compiler sinks each load
+// next to its use and the gather runs one row at a time).
+__device__ __forceinline__ uint4 ld_row16_if(const void* p, bool on) {
+  uint4 v;
+  asm volatile(
+      "{\n\t.reg .pred q;\n\tsetp.ne.u32 q, %5, 0;\n\t"
+      "mov.u32 %0, 0;\n\tmov.u32 %1, 0;\n\tmov.u32 %2, 0;\n\tmov.u32 %3, 0;\n\t"
+      "@q ld.global.v4.u32 {%0, %1, %2, %3}, [%4];\n\t}"
+      : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+      : "l"(p), "r"((unsigned)on));
+  return v;
+}
+
+// Empty statement that reads and redefines four loaded vectors.  Placed after the last load of a pass (volatile
+// statements keep their order), it keeps every use of the loaded values behind ALL the loads of the pass.
+__device__ __forceinline__ void pin_after_loads(uint4& a, uint4& b, uint4& c, uint4& d) {
+  asm volatile("" : "+r"(a.x), "+r"(a.y), "+r"(a.z), "+r"(a.w), "+r"(b.x), "+r"(b.y), "+r"(b.z), "+r"(b.w), "+r"(c.x),
+               "+r"(c.y), "+r"(c.z), "+r"(c.w), "+r"(d.x), "+r"(d.y), "+r"(d.z), "+r"(d.w));
+}
+
 template <typename T>
 __device__ __forceinline__ void combine_add(float (&acc)[8], const uint4& v, float ws) {
   const T* e = reinterpret_cast<const T*>(&v);
@@ -469,7 +490,10 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(MoePeers ybuf, long lo
     my_owner = (topk_idx != nullptr && my_row >= 0) ? topk_idx[pair] / E_local : 0;
     if (w != nullptr) my_w = w[pair];
   }
-  constexpr int CV = 4;  // vectors of 16 bytes per lane and pass (1024 columns per pass)
+  // A pass covers 512 columns (two 16-byte vectors per lane) of up to eight source rows at once: sixteen independent
+  // loads per lane are in flight before the first sum.  (Two rows at a time over 1024 columns left eight dependent
+  // load rounds per token of a 1536-wide top-8 layer, and the gather ran at 0.45 of the copy bandwidth.)
+  constexpr int CV = 2, RG = 8;
   const int nvec = H >> 3;
   for (int v0 = 0; v0 < nvec; v0 += 32 * CV) {
     float acc[CV][8];
@@ -477,30 +501,30 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(MoePeers ybuf, long lo
     for (int j = 0; j < CV; ++j)
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[j][i] = 0.f;
-    for (int s = 0; s < k; s += 2) {
-      const int o0 = __shfl_sync(0xffffffffu, my_owner, s), r0 = __shfl_sync(0xffffffffu, my_row, s);
-      const float w0 = __shfl_sync(0xffffffffu, my_w, s);
-      const int s1 = s + 1 < k ? s + 1 : s;
-      const int o1 = __shfl_sync(0xffffffffu, my_owner, s1);
-      const int r1 = s + 1 < k ? __shfl_sync(0xffffffffu, my_row, s1) : -1;
-      const float w1 = __shfl_sync(0xffffffffu, my_w, s1);
-      const T* p0 = reinterpret_cast<const T*>(ybuf.p[o0]) + (long long)(r0 < 0 ? 0 : r0) * ldy;
-      const T* p1 = reinterpret_cast<const T*>(ybuf.p[o1]) + (long long)(r1 < 0 ? 0 : r1) * ldy;
-      uint4 a[CV], b[CV];
+    for (int s0 = 0; s0 < k; s0 += RG) {
+      uint4 a[RG][CV];
+      float ws[RG];
 #pragma unroll
-      for (int j = 0; j < CV; ++j) {
-        const int vi = v0 + lane + 32 * j;
-        a[j] = b[j] = make_uint4(0u, 0u, 0u, 0u);
-        if (vi < nvec) {
-          if (r0 >= 0) a[j] = *reinterpret_cast<const uint4*>(p0 + vi * 8);  // a dropped pair contributes nothing
-          if (r1 >= 0) b[j] = *reinterpret_cast<const uint4*>(p1 + vi * 8);
+      for (int u = 0; u < RG; ++u) {
+        const int s = s0 + u;
+        const int src = s < k ? s : 0;  // every lane takes part in the shuffles; rows beyond k contribute zeros
+        const int o = __shfl_sync(0xffffffffu, my_owner, src);
+        const int r = __shfl_sync(0xffffffffu, my_row, src);
+        ws[u] = __shfl_sync(0xffffffffu, my_w, src);
+        const bool on = s < k && r >= 0;  // a dropped pair contributes nothing
+        const T* p = reinterpret_cast<const T*>(ybuf.p[o]) + (long long)(on ? r : 0) * ldy;
+#pragma unroll
+        for (int j = 0; j < CV; ++j) {
+          const int vi = v0 + lane + 32 * j;
+          a[u][j] = ld_row16_if(p + (vi < nvec ? vi : 0) * 8, on && vi < nvec);
         }
       }
 #pragma unroll
-      for (int j = 0; j < CV; ++j) {
-        combine_add<T>(acc[j], a[j], w0);
-        combine_add<T>(acc[j], b[j], w1);
-      }
+      for (int u = 0; u < RG; u += 2) pin_after_loads(a[u][0], a[u][1], a[u + 1][0], a[u + 1][1]);
+#pragma unroll
+      for (int u = 0; u < RG; ++u)
+#pragma unroll
+        for (int j = 0; j < CV; ++j) combine_add<T>(acc[j], a[u][j], ws[u]);
     }
 #pragma unroll
     for (int j = 0; j < CV; ++j) {
