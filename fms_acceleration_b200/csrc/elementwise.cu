@@ -612,6 +612,61 @@ __global__ void add_kernel(const T* __restrict__ a, const T* __restrict__ b, T* 
   }
 }
 
+// AdamW with decoupled weight decay on one parameter tensor, the arithmetic of torch's fused implementation: fp32
+// math per element, one rounding per stored value.  p, g, m, v have the same element type; 16-byte accesses.
+//   p <- p (1 - lr wd);  m <- m + (1 - b1)(g s - m);  v <- b2 v + (1 - b2)(g s)^2;
+//   p <- p - (lr / c1) m / (sqrt(v) / sqrt(c2) + eps)        c1 = 1 - b1^t, c2 = 1 - b2^t, s = grad_scale
+template <typename T>
+__global__ void __launch_bounds__(256)
+adamw_kernel(T* __restrict__ p, const T* __restrict__ g, T* __restrict__ m, T* __restrict__ v, long long n, float lr,
+             float b1, float b2, float eps, float wd, float c1, float c2, float grad_scale) {
+  constexpr int V = 16 / sizeof(T);
+  const long long nvec = n / V;
+  const float decay = 1.f - lr * wd, step = lr / c1, rs2 = rsqrtf(c2);
+  auto upd = [&](float& pf, float gf, float& mf, float& vf) {
+    gf *= grad_scale;
+    pf *= decay;
+    mf += (1.f - b1) * (gf - mf);
+    vf = b2 * vf + (1.f - b2) * gf * gf;
+    pf -= step * mf / (sqrtf(vf) * rs2 + eps);
+  };
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    if constexpr (sizeof(T) == 4) {
+      float4 pv = reinterpret_cast<float4*>(p)[i], mv = reinterpret_cast<float4*>(m)[i], vv = reinterpret_cast<float4*>(v)[i];
+      const float4 gv = reinterpret_cast<const float4*>(g)[i];
+      upd(pv.x, gv.x, mv.x, vv.x); upd(pv.y, gv.y, mv.y, vv.y); upd(pv.z, gv.z, mv.z, vv.z); upd(pv.w, gv.w, mv.w, vv.w);
+      reinterpret_cast<float4*>(p)[i] = pv; reinterpret_cast<float4*>(m)[i] = mv; reinterpret_cast<float4*>(v)[i] = vv;
+    } else {
+      Vec8<T> pv, gv, mv, vv;
+      float pf[8], gf[8], mf[8], vf[8];
+      pv.load(p + i * 8); gv.load(g + i * 8); mv.load(m + i * 8); vv.load(v + i * 8);
+      pv.to_float(pf); gv.to_float(gf); mv.to_float(mf); vv.to_float(vf);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) upd(pf[k], gf[k], mf[k], vf[k]);
+      pv.from_float(pf); mv.from_float(mf); vv.from_float(vf);
+      pv.store(p + i * 8); mv.store(m + i * 8); vv.store(v + i * 8);
+    }
+  }
+  // tail (fewer than one vector) by the first threads of the grid
+  const long long t = nvec * V + blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (t < n) {
+    float pf, gf, mf, vf;
+    if constexpr (sizeof(T) == 4) {
+      pf = p[t]; gf = g[t]; mf = m[t]; vf = v[t];
+      upd(pf, gf, mf, vf);
+      p[t] = pf; m[t] = mf; v[t] = vf;
+    } else if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+      pf = __bfloat162float(p[t]); gf = __bfloat162float(g[t]); mf = __bfloat162float(m[t]); vf = __bfloat162float(v[t]);
+      upd(pf, gf, mf, vf);
+      p[t] = __float2bfloat16_rn(pf); m[t] = __float2bfloat16_rn(mf); v[t] = __float2bfloat16_rn(vf);
+    } else {
+      pf = __half2float(p[t]); gf = __half2float(g[t]); mf = __half2float(m[t]); vf = __half2float(v[t]);
+      upd(pf, gf, mf, vf);
+      p[t] = __float2half_rn(pf); m[t] = __float2half_rn(mf); v[t] = __float2half_rn(vf);
+    }
+  }
+}
+
 // One resident wave of a grid-stride kernel: SMs x CTAs that fit per SM (asked of the runtime once per kernel).  A grid
 // of a fixed 16 CTAs per SM ran as 2.67 waves of equal CTAs on kernels that fit 6 per SM, i.e. a third wave at a third
 // of the machine.
@@ -809,5 +864,29 @@ extern "C" int fmsb_add(const void* a, const void* b, void* y, long long n, int 
                                                         (__nv_bfloat16*)y, n / 8);
   else
     add_kernel<__half><<<grid, 256, 0, stream>>>((const __half*)a, (const __half*)b, (__half*)y, n / 8);
+  return (int)cudaGetLastError();
+}
+
+// One AdamW step on a tensor of n elements (dtype 0 fp16, 1 bf16, 2 fp32 for p, g, m and v alike; all four 16-byte
+// aligned).  c1 = 1 - beta1^t and c2 = 1 - beta2^t are formed by the caller; grad_scale multiplies the gradient first
+// (clipping coefficient, 1 / accumulation steps).
+extern "C" int fmsb_adamw(void* p, const void* g, void* m, void* v, long long n, float lr, float b1, float b2, float eps,
+                          float wd, float c1, float c2, float grad_scale, int dtype, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(m) |
+       reinterpret_cast<uintptr_t>(v)) & 15u)
+    return -2;
+  if (c1 <= 0.f || c2 <= 0.f) return -2;
+  static int waves[3];
+  const int per = dtype == 2 ? 4 : 8;
+  const long long items = n / per + 1;
+#define FMSB_ADAMW(T, SLOT)                                                                                      \
+  adamw_kernel<T><<<wave_grid(adamw_kernel<T>, 256, items, &waves[SLOT]), 256, 0, stream>>>(                     \
+      (T*)p, (const T*)g, (T*)m, (T*)v, n, lr, b1, b2, eps, wd, c1, c2, grad_scale)
+  if (dtype == 1) FMSB_ADAMW(__nv_bfloat16, 1);
+  else if (dtype == 0) FMSB_ADAMW(__half, 0);
+  else if (dtype == 2) FMSB_ADAMW(float, 2);
+  else return -2;
+#undef FMSB_ADAMW
   return (int)cudaGetLastError();
 }

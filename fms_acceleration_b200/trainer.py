@@ -71,6 +71,16 @@ def to_device(batch: Dict[str, torch.Tensor], device) -> Dict[str, torch.Tensor]
     return {k: v.to(device, non_blocking=True) for k, v in batch.items()}
 
 
+def _adamw(params, lr: float, weight_decay: float) -> torch.optim.Optimizer:
+    """AdamW for ``params``: the in-tree kernel on a GPU (``FMSB_ADAMW=torch`` keeps torch's fused one), torch's on a CPU."""
+    on_gpu = bool(params) and params[0].is_cuda
+    if on_gpu and os.environ.get("FMSB_ADAMW", "native") != "torch":
+        from .ops.optim import AdamW
+
+        return AdamW(params, lr=lr, weight_decay=weight_decay)
+    return torch.optim.AdamW(params, lr=lr, weight_decay=weight_decay, fused=on_gpu)
+
+
 class Trainer:
     """Minimal single-process-per-GPU trainer.
 
@@ -91,12 +101,9 @@ class Trainer:
             # and gradient buffers); expert-parallel parameters, already disjoint over the ranks, get a plain AdamW
             optimizer = engine.build_optimizer(args.learning_rate, args.weight_decay)
             if engine.ep_params:
-                optimizer.ep_optimizer = torch.optim.AdamW(engine.ep_params, lr=args.learning_rate,
-                                                           weight_decay=args.weight_decay,
-                                                           fused=engine.ep_params[0].is_cuda)
+                optimizer.ep_optimizer = _adamw(engine.ep_params, args.learning_rate, args.weight_decay)
         if optimizer is None:
-            fused = bool(params) and params[0].is_cuda
-            optimizer = torch.optim.AdamW(params, lr=args.learning_rate, weight_decay=args.weight_decay, fused=fused)
+            optimizer = _adamw(params, args.learning_rate, args.weight_decay)
         self.optimizer = optimizer
         self.params = params
         self.global_step = 0

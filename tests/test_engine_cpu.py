@@ -35,3 +35,33 @@ def test_expert_parallel_checkpoint_holds_every_rank(tmp_path, world):
 
 def test_expert_lora_under_expert_parallelism(tmp_path):
     assert _run("ep_lora", 2, tmp_path, 29731).count("CPU_OK ep_lora") == 2
+
+
+def test_in_tree_adamw_matches_torch_on_cpu_and_shares_its_state_layout():
+    """ops.optim.AdamW: same numbers as torch.optim.AdamW (fp32 parameters, CPU fall-back path) over several steps,
+    and a state_dict that torch's optimizer loads (and vice versa)."""
+    import torch
+
+    from fms_acceleration_b200.ops.optim import AdamW
+
+    torch.manual_seed(0)
+    ws = [torch.randn(33, 7), torch.randn(5)]
+    a = [w.clone().requires_grad_() for w in ws]
+    b = [w.clone().requires_grad_() for w in ws]
+    oa = AdamW(a, lr=1e-2, weight_decay=0.1)
+    ob = torch.optim.AdamW(b, lr=1e-2, weight_decay=0.1)
+    for it in range(4):
+        gs = [torch.randn_like(w) for w in ws]
+        for p, q, g in zip(a, b, gs):
+            p.grad, q.grad = g.clone(), g.clone()
+        oa.step()
+        ob.step()
+    for p, q in zip(a, b):
+        assert torch.allclose(p, q, atol=1e-6, rtol=1e-5)
+    sd = oa.state_dict()
+    assert set(sd["state"][0]) == {"step", "exp_avg", "exp_avg_sq"} and float(sd["state"][0]["step"]) == 4.0
+    ob2 = torch.optim.AdamW([w.clone().requires_grad_() for w in ws], lr=1e-2, weight_decay=0.1)
+    ob2.load_state_dict(sd)
+    oa2 = AdamW([w.clone().requires_grad_() for w in ws], lr=1e-2, weight_decay=0.1)
+    oa2.load_state_dict(ob.state_dict())
+    assert float(oa2.state_dict()["state"][1]["step"]) == 4.0

@@ -470,3 +470,39 @@ def test_weight_gradient_gemm_splits_the_contraction(M, Nn, K, dtype):
     assert out.dtype == dtype and out.shape == (M, Nn)
     tol = 2e-3 if dtype == torch.float32 else 1e-2
     assert (out.float() - ref).abs().max() <= tol * ref.abs().max()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
+@pytest.mark.parametrize("n", [8 * 1000 + 3, 1 << 20, 5])
+def test_adamw_kernel_matches_torch_fused(dtype, n):
+    """The in-tree AdamW step against torch's fused AdamW on the same parameters and gradients, three steps, with
+    weight decay; sizes with a ragged tail and one smaller than a vector."""
+    from fms_acceleration_b200.ops.optim import AdamW
+
+    torch.manual_seed(n)
+    w = torch.randn(n, device=DEV).to(dtype)
+    a, b = w.clone().requires_grad_(), w.clone().requires_grad_()
+    oa = AdamW([a], lr=3e-3, weight_decay=0.05)
+    ob = torch.optim.AdamW([b], lr=3e-3, weight_decay=0.05, fused=True)
+    for it in range(3):
+        g = (torch.randn(n, device=DEV) * 0.1).to(dtype)
+        a.grad, b.grad = g.clone(), g.clone()
+        oa.step()
+        ob.step()
+    NV.check_status()
+    tol = 1e-6 if dtype == torch.float32 else (8e-3 if dtype == torch.bfloat16 else 1e-3)
+    assert (a.float() - b.float()).abs().max() <= tol * (1 + b.float().abs().max())
+    sa, sb = oa.state[a], ob.state[b]
+    assert _rel(sa["exp_avg"], sb["exp_avg"]) < 1e-2 and _rel(sa["exp_avg_sq"], sb["exp_avg_sq"]) < 1e-2
+    # the clipping coefficient rides in the kernel
+    oa.grad_scale = 0.5
+    a2 = w.clone().requires_grad_()
+    o2 = AdamW([a2], lr=3e-3, weight_decay=0.0)
+    o2.grad_scale = 0.5
+    b2 = w.clone().requires_grad_()
+    o3 = torch.optim.AdamW([b2], lr=3e-3, weight_decay=0.0, fused=True)
+    g = (torch.randn(n, device=DEV) * 0.1).to(dtype)
+    a2.grad, b2.grad = g.clone(), (g.float() * 0.5).to(dtype)
+    o2.step()
+    o3.step()
+    assert (a2.float() - b2.float()).abs().max() <= tol * (1 + b2.float().abs().max())
