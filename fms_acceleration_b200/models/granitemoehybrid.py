@@ -40,6 +40,16 @@ class GraniteMoeHybridDecoderLayer(nn.Module):
         if self.layer_type == "mamba":
             # one scan per packed document so that no state leaks across a document boundary
             mix = torch.cat([self.mamba(h[s:e]) for s, e in zip(cu[:-1], cu[1:])], dim=0) if len(cu) > 2 else self.mamba(h)
+        elif getattr(self, "cp", None) is not None:
+            # context parallelism: this rank holds one slice of one sequence; keys and values of the earlier slices
+            # come over the group (this family's attention layers use no positional embedding)
+            from ..parallel.context_parallel import cp_attention
+
+            a, T = self.self_attn, h.shape[0]
+            q = a.q_proj(h).view(T, a.num_heads, a.head_dim)
+            k = a.k_proj(h).view(T, a.num_kv_heads, a.head_dim)
+            v = a.v_proj(h).view(T, a.num_kv_heads, a.head_dim)
+            mix = a.o_proj(cp_attention(q, k, v, self.cp.group, a.scaling).reshape(T, -1))
         else:
             mix = self.self_attn(h, pos, cos_t, sin_t, cu)
         x = torch.add(x, mix, alpha=rm)

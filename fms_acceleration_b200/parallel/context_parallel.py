@@ -247,3 +247,58 @@ class _HaloExchange(torch.autograd.Function):
         if cp.rank + 1 < cp.world:
             dx[-k:] = recv[cp.rank + 1].view(k, -1)
         return dx, None, None, None
+
+
+# ------------------------------------------------------------------------------------------------
+# Attention layers of hybrid models under context parallelism (library collectives)
+# ------------------------------------------------------------------------------------------------
+class _GatherTokens(torch.autograd.Function):
+    """All-gather along the token axis over the context-parallel group; the backward sums every rank's gradient of
+    the gathered tensor and keeps this rank's slice (a reduce-scatter, stated with all_reduce so that gloo runs it)."""
+
+    @staticmethod
+    def forward(ctx, t, group):
+        ctx.group, ctx.n = group, t.shape[0]
+        world = dist.get_world_size(group)
+        parts = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(parts, t.contiguous(), group=group)
+        return torch.cat(parts, dim=0)
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous()
+        dist.all_reduce(g, group=ctx.group)
+        r = dist.get_rank(ctx.group)
+        return g[r * ctx.n:(r + 1) * ctx.n], None
+
+
+def cp_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, group, scaling: float,
+                 q_block: int = 1024) -> torch.Tensor:
+    """Causal attention of ONE sequence whose tokens are split evenly and in order over the ranks of ``group``.
+
+    ``q [Tl, nh, d]``, ``k`` / ``v [Tl, nkv, d]`` are this rank's slice (rank r holds tokens ``[r Tl, (r + 1) Tl)``).
+    Keys and values of all ranks are gathered, query ``i`` of this rank attends the keys ``0 .. r Tl + i``.  Queries
+    are processed in blocks of ``q_block`` rows so that the explicit mask stays small.  Differentiable (the gradient
+    of the gathered keys / values is summed over the ranks).  Library form: the hybrid models' few attention layers
+    under the Mamba context-parallel plugin, where the reference relies on torch's experimental context-parallel
+    attention (fms_acceleration_mcp/utils/utils.py:64-80)."""
+    import torch.nn.functional as F
+
+    r = dist.get_rank(group)
+    Tl, nh, d = q.shape
+    nkv = k.shape[1]
+    K = _GatherTokens.apply(k, group)[: (r + 1) * Tl]
+    V = _GatherTokens.apply(v, group)[: (r + 1) * Tl]
+    rep = nh // nkv
+    Kh = K.repeat_interleave(rep, dim=1).transpose(0, 1).unsqueeze(0)  # [1, nh, Tk, d]
+    Vh = V.repeat_interleave(rep, dim=1).transpose(0, 1).unsqueeze(0)
+    outs = []
+    kpos = torch.arange((r + 1) * Tl, device=q.device)
+    for s in range(0, Tl, q_block):
+        e = min(Tl, s + q_block)
+        last = r * Tl + e  # keys beyond the block's last query are masked for every row of the block: cut them off
+        qh = q[s:e].transpose(0, 1).unsqueeze(0)
+        mask = kpos[None, :last] <= (r * Tl + torch.arange(s, e, device=q.device))[:, None]
+        o = F.scaled_dot_product_attention(qh, Kh[:, :, :last], Vh[:, :, :last], attn_mask=mask, scale=scaling)
+        outs.append(o.squeeze(0).transpose(0, 1))
+    return torch.cat(outs, dim=0)

@@ -134,9 +134,18 @@ def patch_mamba_layers_with_cp_head(model, checkpoint_name_or_path: Optional[str
     swap_hf_mamba_modules(base, names=("mamba",))  # Hugging Face layers become the in-tree mixer, same weights
     inner = getattr(base, "model", base)
     patched = 0
+    from ....models.granitemoehybrid import GraniteMoeHybridDecoderLayer
+
     for layer in inner.layers:
         mixer = getattr(layer, "mamba", None)
         if mixer is None:
+            if getattr(layer, "self_attn", None) is not None:
+                # an attention layer of a hybrid model: it has to see the keys of the earlier slices
+                if not isinstance(layer, GraniteMoeHybridDecoderLayer):
+                    raise NotImplementedError(
+                        "context parallelism over the attention layers of a Hugging Face hybrid model: build the model "
+                        "with fms_acceleration_b200.models (its attention layers gather keys and values over the group)")
+                layer.cp = cp
             continue
         mixer.cp = cp
         patched += 1

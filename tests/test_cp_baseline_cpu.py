@@ -16,3 +16,15 @@ def test_context_parallel_scan_equals_the_whole_sequence(world):
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, MASTER_ADDR="127.0.0.1"))
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
     assert "CP_BASELINE_OK" in out.stdout
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_context_parallel_attention_equals_the_whole_sequence(world):
+    """Attention layers of hybrid models under context parallelism: keys and values gathered over the group, causal
+    mask by global position; outputs, gradients (the key / value gradients summed over the ranks) and a whole hybrid
+    decoder layer against the single-sequence computation."""
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29680 + world), os.path.join(HERE, "dist_worker_cp_attention.py")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, MASTER_ADDR="127.0.0.1"))
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    assert "CP_ATTENTION_OK" in out.stdout
