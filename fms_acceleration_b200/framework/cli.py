@@ -45,6 +45,33 @@ def install(plugin: str = None, build: bool = False, **kwargs) -> int:
     return 0
 
 
+def install_plugin(*args: str) -> int:
+    """Name and calling convention of the reference's verb (fms_acceleration/cli.py:36-96): one plugin name plus
+    optional pip-style flags.  Every plugin ships inside this package, so the flags are accepted and ignored and
+    nothing is downloaded; an unknown name is an error."""
+    names = [a for a in args if not a.startswith("-")]
+    if len(names) != 1:
+        raise ValueError("Please specify exactly one plugin to install")
+    name = os.path.basename(names[0].format(toxinidir=os.getcwd()).rstrip("/"))
+    return install(name.replace("fms_acceleration_", "").replace("fms-acceleration-", ""))
+
+
+def get_benchmark_artifacts(dest_dir: str) -> str:
+    """Place the benchmark harness and the sample configurations under ``dest_dir`` (the reference sparse-checks them
+    out of its repository, fms_acceleration/cli.py:99-120; here they are copied from this installation)."""
+    import shutil
+
+    os.makedirs(dest_dir, exist_ok=True)
+    bench_src = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "benchmarks")
+    pairs = [(bench_src, os.path.join(dest_dir, "scripts", "benchmarks")),
+             (os.path.dirname(CONTENTS), os.path.join(dest_dir, "sample-configurations"))]
+    for src, dst in pairs:
+        if not os.path.isdir(src):
+            raise RuntimeError(f"could not get benchmark artifacts: {src} is not part of this installation")
+        shutil.copytree(src, dst, dirs_exist_ok=True, ignore=shutil.ignore_patterns("__pycache__", "*.pyc"))
+    return dest_dir
+
+
 def list_plugins() -> int:
     print("\nplugins (x = importable):\n")
     for short in PLUGINS:

@@ -17,6 +17,23 @@ def prepare_fa2_from_position_ids(query, key, value, position_ids):
     return q, k, v, cu
 
 
+#: position ids of the batch a model is processing, by model id: older transformers versions do not hand the position
+#: ids to the attention function, the backbone's forward leaves them here (as in the reference, flash_attn.py:33-82)
+POSITION_IDS_CACHE: dict = {}
+
+
+def build_backbone_forward(model: torch.nn.Module, model_id: str):
+    """A ``forward`` for the decoder backbone that records the batch's ``position_ids`` under ``model_id`` before
+    calling the original one.  Meant to be bound as a method (first argument ``self``)."""
+    original = model.forward
+
+    def forward(self, *args, **kwargs):
+        POSITION_IDS_CACHE[model_id] = kwargs.get("position_ids")
+        return original(*args, **kwargs)
+
+    return forward
+
+
 def build_fa_forward():
     def _flash_attention_forward(query_states, key_states, value_states, attention_mask=None, query_length=None,
                                  is_causal=True, dropout=0.0, position_ids=None, softmax_scale=None, **kwargs):

@@ -201,3 +201,79 @@ def find_packing_max_batch_len_and_grad_accum(num_gpus: int, avg_sample_len: flo
         else:
             cap = int(avg_sample_len * per_step / num_gpus)
     return cap, grad_accum
+
+
+# ------------------------------------------------------------------------------------------- reference-named helpers
+# The reference exposes its packing primitives and its padded-capacity search as module-level functions
+# (fms_acceleration_aadp/multipack_sampler.py:38-164, 230-340); the same names here, on top of this module's allocator.
+def ffd_check(a: np.ndarray, c: int, n: int) -> bool:
+    """Do the lengths ``a`` fit into ``n`` bins of ``c`` tokens (first-fit decreasing)?"""
+    return _fits(np.asarray(a), int(c), int(n), False)
+
+
+def ffd_check_padding(a: np.ndarray, c: int, n: int) -> bool:
+    """The same when every bin is padded to its longest sample (a bin costs ``longest x samples``)."""
+    return _fits(np.asarray(a), int(c), int(n), True)
+
+
+def ffd_with_result(a: np.ndarray, c: int, start_index: int) -> List[List[int]]:
+    """First-fit-decreasing bins of capacity ``c`` as lists of ``start_index + position``."""
+    return _assign(np.asarray(a), int(c), int(start_index), False)
+
+
+def ffd_with_result_padding(a: np.ndarray, c: int, start_index: int) -> List[List[int]]:
+    return _assign(np.asarray(a), int(c), int(start_index), True)
+
+
+def _padded_capacity(base_avg: float, addition: float, goal: int, num_gpus: int, grad_accum: int) -> int:
+    return int((base_avg + addition) * ((goal / num_gpus) / grad_accum))
+
+
+def guess_starting_avg_padding(base_avg, goal, num_gpus, grad_accum, sorted_lengths) -> int:
+    """Average padding per sample of the first bucket that the longest samples would form (``sorted_lengths`` is in
+    descending order): the starting point of the search for the capacity addition; it tends to overshoot."""
+    cap = _padded_capacity(base_avg, 0, goal, num_gpus, grad_accum)
+    longest = int(sorted_lengths[0])
+    n = max(1, min(len(sorted_lengths), cap // max(longest, 1)))
+    return round(sum(longest - int(x) for x in sorted_lengths[:n]) / n)
+
+
+def simulate_buckets(base_avg, goal, num_gpus, grad_accum, pad_id, max_batch_len, lengths, seed, dataset, addition) -> float:
+    """Average number of samples per step that padded multipack batches give when the per-GPU capacity is raised by
+    ``addition`` tokens per sample.  ``pad_id``, ``max_batch_len`` and ``dataset`` are accepted for the reference's
+    calling convention; only the lengths matter."""
+    import os as _os
+
+    cap = _padded_capacity(base_avg, addition, goal, num_gpus, grad_accum)
+    world = int(_os.environ.get("WORLD_SIZE", num_gpus))
+    rank = int(_os.environ.get("RANK", 0))
+    sampler = MultipackDistributedBatchSampler(cap, np.asarray(lengths), world, rank, seed, padding=True)
+    n_batches = len(sampler.generate_batches())
+    return len(lengths) / n_batches if n_batches else 0.0
+
+
+def find_padding_max_batch_len_addition(base_avg, goal, dataset, num_gpus, grad_accum, pad_id, max_batch_len, seed) -> int:
+    """Tokens per sample to add to the unpadded capacity so that padded batches still average ``goal`` samples per
+    step (within 2 %, at least 10 samples): bracket from the first-bucket guess, doubling the upper end until the
+    simulation overshoots, then bisect."""
+    if hasattr(dataset, "get_lengths"):
+        lengths = np.asarray(dataset.get_lengths())
+    else:  # plain lengths, or samples that carry their tokens
+        lengths = np.asarray([len(s["input_ids"]) if isinstance(s, dict) else int(s) for s in dataset])
+    guess = guess_starting_avg_padding(base_avg, goal, num_gpus, grad_accum, sorted(lengths.tolist(), reverse=True))
+    lo, hi, cur, overshot = 0, max(2 * guess, 2), max(guess, 1), False
+    tol = max(10, round(goal * 0.02))
+    for _ in range(64):
+        if hi - lo <= 1:
+            break
+        got = simulate_buckets(base_avg, goal, num_gpus, grad_accum, pad_id, max_batch_len, lengths, seed, dataset, cur)
+        if abs(got - goal) <= tol:
+            break
+        if got > goal:
+            overshot, hi = True, cur
+        elif not overshot:
+            hi *= 2
+        else:
+            lo = cur
+        cur = lo + (hi - lo) // 2
+    return cur

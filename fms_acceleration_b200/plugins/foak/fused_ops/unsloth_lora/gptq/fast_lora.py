@@ -50,6 +50,22 @@ def matmul_lora(X, W, A, B, s, out=None, dropout=None):
     return y
 
 
+def matmul_lora_canonicalized(X, W, A, B, s, dropout=None):
+    """``X W + s (d(X) A^T) B^T`` for a rank-2 ``X [rows, in]`` and ``W [in, out]``; ``dropout`` is a mask tensor that
+    multiplies ``X`` or a dropout module (the dropped-out input is left on it as ``dropout.X`` for the backward, as
+    in the reference, fused_ops/unsloth_lora/gptq/fast_lora.py:119-140)."""
+    out = X @ W.to(X.dtype)
+    if dropout is not None:
+        if isinstance(dropout, torch.Tensor):
+            X = X * dropout
+        elif isinstance(dropout, torch.nn.Module):
+            X = dropout(X)
+            dropout.X = X
+        else:
+            raise NotImplementedError("dropout must be a tensor or module.")
+    return out + (X @ A.to(X.dtype).t()) @ (s * B.to(X.dtype).t())
+
+
 def dequantize(qstate: GPTQuantState) -> torch.Tensor:
     return dequant248(qstate.qweight, qstate.scales, qstate.qzeros, qstate.g_idx, qstate.bits,
                       zero_offset=qstate.zero_offset)

@@ -98,3 +98,26 @@ def build_lora_fused_ops(attn: torch.nn.Module, base_type: str = "auto_gptq", su
 
     return [(ModelPatcherTrigger(check=(lambda m, _t=mod: m is _t), module_name=n), make_forward(i, n))
             for i, (n, mod) in enumerate(zip(names, mods))]
+
+
+KEY_HIDDEN_ACTIVATIONS = ["hidden_act", "activation_function"]
+
+
+def get_hidden_activation_fn_key(config) -> str:
+    """The MLP activation named by a model configuration, read from ``hidden_act`` (most families) or
+    ``activation_function`` (GPTBigCode); fms_acceleration_foak/models/utils.py:208-217."""
+    for key in KEY_HIDDEN_ACTIVATIONS:
+        value = getattr(config, key, None)
+        if value:
+            return value
+    raise ValueError(f"Unable to determine activation function key for architecture {getattr(config, 'architectures', None)}.")
+
+
+def get_transformers_version():
+    """Installed ``transformers`` version string, or None."""
+    try:
+        from importlib.metadata import version
+
+        return version("transformers")
+    except Exception:  # noqa: BLE001 - not installed
+        return None

@@ -30,6 +30,18 @@ def hf_config_ssm_config(hf_config) -> Dict:
     }
 
 
+# the name this helper carries in the reference (fms_acceleration_mcp/utils/utils.py:51-60)
+get_ssmconfig_from_hfconfig = hf_config_ssm_config
+
+
+def __getattr__(name: str):
+    # ``Mamba2CPHF`` is the reference's name for the module that sits behind a Hugging Face Mamba layer's call
+    # convention (fms_acceleration_mcp/utils/utils.py:64-80); here that is the adapter class, made on first use
+    if name == "Mamba2CPHF":
+        return _adapter_class()
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+
+
 def _adapter_class():
     """``HFMamba2Adapter`` is a subclass of the in-tree mixer (so parameter names, and with them checkpoints, are
     those of the Hugging Face module); the class is made on first use to keep this module importable without the

@@ -233,6 +233,53 @@ def patch_huggingface_fsdp2_load_full_state_dict() -> bool:
     return patch_prepare_sd_options()
 
 
+def fsdp2_load_full_state_dict(accelerator, model: torch.nn.Module, full_sd: Optional[dict]) -> torch.nn.Module:
+    """Load a FULL state dict that only rank 0 needs to hold into the model of every rank (the job of the reference's
+    function of this name, :775-880, for FSDP2-sharded models).  Here ordinary parameters are replicated and expert
+    tensors hold ``E / ep`` experts of the group: rank 0 broadcasts every tensor, a rank copies what it owns (its
+    slice of dimension 0 for expert-parallel parameters).  Without a process group the dict is simply loaded."""
+    dist = torch.distributed
+    multi = dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
+    ep_groups = _ep_param_names(model)
+    own = dict(model.named_parameters())
+    own.update(dict(model.named_buffers()))
+    names = sorted(own)
+    if multi:
+        holder = [sorted(k for k in (full_sd or {}) if k in own)] if dist.get_rank() == 0 else [None]
+        dist.broadcast_object_list(holder, src=0)
+        names = holder[0]
+    elif full_sd is not None:
+        names = [k for k in names if k in full_sd]
+    with torch.no_grad():
+        for name in names:
+            dst = own[name]
+            g = ep_groups.get(name)
+            rows = dst.shape[0] * (dist.get_world_size(g) if g is not None else 1) if dst.dim() else 0
+            full_shape = (rows,) + tuple(dst.shape[1:]) if dst.dim() else ()
+            if multi:
+                buf = (full_sd[name].to(device=dst.device, dtype=dst.dtype).contiguous() if dist.get_rank() == 0
+                       else torch.empty(full_shape, device=dst.device, dtype=dst.dtype))
+                dist.broadcast(buf, src=0)
+            else:
+                buf = full_sd[name].to(device=dst.device, dtype=dst.dtype)
+            if g is not None and buf.shape[0] != dst.shape[0]:
+                r = dist.get_rank(g)
+                buf = buf[r * dst.shape[0]:(r + 1) * dst.shape[0]]
+            dst.copy_(buf)
+    return model
+
+
+def fsdp2_prepare_model(accelerator, model: torch.nn.Module) -> torch.nn.Module:
+    """Make the model ready for sharded multi-GPU training and hand it back (the reference wraps it with FSDP2 here,
+    :883-1037).  This package shards through its own engine (frozen packed weights, gradient bucket, optimizer
+    state); with one process the model is returned as it is."""
+    from ....parallel.engine import install_engine
+
+    if accelerator is not None and next(model.parameters()).is_cuda:
+        install_engine(model, accelerator)
+    return model
+
+
 def clip_grad_norm_(parameters, max_norm: float, norm_type: float = 2.0, foreach=None) -> torch.Tensor:
     """Total gradient norm over replicated AND expert-parallel parameters: the squared norms of expert shards are
     summed over their expert-parallel group before the global norm is formed (the reference's FSDP2 version,

@@ -42,8 +42,17 @@ class ScatteredExperts(nn.Module):
             return self.weight
         return self.weight + torch.bmm(self.lora_A, self.lora_B)
 
-    def forward(self, x, *args, **kwargs):  # pragma: no cover - experts are driven by ScatterMoE.forward
-        raise RuntimeError("ScatteredExperts is executed through its parent ScatterMoE module")
+    def forward(self, x, bin_ids, indices, padded_block_idxs, expert_offsets, gates=None):
+        """One projection on its own, rows gathered into expert order on the way in and scattered back on the way out
+        (the reference's ``ScatteredExperts.forward``, fms_acceleration_moe/utils/scattermoe.py:129-181).
+        ``bin_ids``: sorted expert of every (token, choice) pair; ``indices``: the permutation that sorts the pairs;
+        ``expert_offsets``: where each expert's rows end; ``gates [T, k]``: weights of the sum over a token's rows.
+        ``ScatterMoE.forward`` does not call this: it runs both projections and the combine as one fused operator."""
+        from .scattermoe_utils.khd.kernels.ops import scattered_experts
+
+        return scattered_experts(x, self.weight, self.fan_out, bin_ids, indices, padded_block_idxs, expert_offsets,
+                                 gates=gates, grouped_in=self.grouped_in, grouped_out=self.grouped_out,
+                                 expert_lora_A=self.lora_A, expert_lora_B=self.lora_B, lora_alp=float(self.lora_r))
 
 
 class ScatterMoE(nn.Module):
@@ -64,9 +73,12 @@ class ScatterMoE(nn.Module):
         self.num_experts_per_device = num_experts // self.ep_size
         self.router = nn.Linear(hidden_size, num_experts, bias=False, dtype=dtype, device=device)
         El = self.num_experts_per_device
-        self.w1 = ScatteredExperts(hidden_size, intermediate_size, El, top_k, dtype=dtype, device=device, lora_config=lora_config)
-        self.w2 = ScatteredExperts(intermediate_size, hidden_size, El, 1, dtype=dtype, device=device, lora_config=lora_config)
-        self.w3 = ScatteredExperts(hidden_size, intermediate_size, El, top_k, dtype=dtype, device=device, lora_config=lora_config)
+        self.w1 = ScatteredExperts(hidden_size, intermediate_size, El, top_k, grouped_out=True, dtype=dtype, device=device,
+                                   lora_config=lora_config)
+        self.w2 = ScatteredExperts(intermediate_size, hidden_size, El, 1, grouped_in=True, dtype=dtype, device=device,
+                                   lora_config=lora_config)
+        self.w3 = ScatteredExperts(hidden_size, intermediate_size, El, top_k, grouped_out=True, dtype=dtype, device=device,
+                                   lora_config=lora_config)
         # largest number of tokens this rank hands to one forward (sizes the expert-parallel staging once)
         self.token_budget = token_budget
         self._ctx: Optional[MOE.MoEContext] = None

@@ -134,3 +134,26 @@ def prepare_scattermoe(model: nn.Module, checkpoint_name_or_path: Optional[str] 
     if not swapped:
         warnings.warn(f"no '{moe_cls}' module found: nothing was converted to ScatterMoE")
     return swapped
+
+
+def load_experts_onto_device(module: nn.Module, state_dict, device_mesh=None, num_experts_per_device: Optional[int] = None):
+    """Copy router and expert weights into a ``ScatterMoE`` module (the reference's helper of this name,
+    scattermoe_prepare.py:49-108, which also wraps them as DTensors).  ``state_dict`` maps ``router.weight`` /
+    ``w1.weight`` ... (also the LoRA factors) to tensors that hold either all ``E`` experts or already this rank's
+    ``E / ep``; a rank keeps the slice of dimension 0 that it owns.  ``device_mesh``: a process group, a DeviceMesh
+    whose last dimension is the expert-parallel one, or None (the module's own group)."""
+    group = device_mesh
+    if device_mesh is not None and hasattr(device_mesh, "get_group"):
+        group = device_mesh.get_group(device_mesh.ndim - 1)
+    if group is None:
+        group = getattr(module, "ep_group", None)
+    rank = torch.distributed.get_rank(group) if group is not None else 0
+    with torch.no_grad():
+        for name, value in state_dict.items():
+            path, _, leaf = name.rpartition(".")
+            dst = getattr(module.get_submodule(path) if path else module, leaf)
+            per = num_experts_per_device if num_experts_per_device is not None else dst.shape[0]
+            if "router" not in name and value.shape[0] > per:
+                value = value[rank * per:(rank + 1) * per]
+            dst.copy_(value.to(device=dst.device, dtype=dst.dtype))
+    return module

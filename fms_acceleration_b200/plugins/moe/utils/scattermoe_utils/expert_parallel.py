@@ -63,3 +63,11 @@ def scatter_with_routing_weights(y: torch.Tensor, routing_weights: torch.Tensor,
     pairs = torch.empty_like(back)
     pairs[state["order"]] = back                                        # pair p = token p // k, choice p % k
     return (pairs.view(T, k, -1) * routing_weights.reshape(T, k, 1).to(pairs.dtype)).sum(1)
+
+
+def no_indices_just_bins(top_expert: torch.Tensor, num_experts: int):
+    """``(bins, tokens_per_expert)``: how many (token, k) pairs go to each expert and the inclusive running total,
+    i.e. where each expert's rows end once the pairs are sorted by expert (the reference's helper of this name,
+    scattermoe_utils/expert_parallel.py:79-92)."""
+    tokens_per_expert = torch.bincount(top_expert.reshape(-1).long(), minlength=num_experts).to(torch.int32)
+    return tokens_per_expert.cumsum(0).to(torch.int32), tokens_per_expert

@@ -60,6 +60,37 @@ def restore_dataloader_state(dataloader, resume_dir: str) -> bool:
     return True
 
 
+def skip_first_batches(dataloader, num_batches=0):
+    """Replacement for ``transformers.trainer.skip_first_batches``: the restored loader already points at the next
+    sample, so nothing is skipped (fms_acceleration_odm/patch.py:232-233)."""
+    return dataloader
+
+
+def get_train_dataloader(self):
+    """Replacement for ``Trainer.get_train_dataloader`` (fms_acceleration_odm/patch.py:187-229): build the loader the
+    stock way, then, when ``model.resume_from_checkpoint`` names a checkpoint (``True`` = the last one under
+    ``args.output_dir``), restore the loader / dataset state saved there."""
+    if self.train_dataset is None:
+        raise ValueError("Trainer: training requires a train_dataset.")
+    original = getattr(type(self), "_fmsb_original_get_train_dataloader", None)
+    if original is not None:
+        dl = original(self)
+    else:
+        dl = self._get_dataloader(dataset=self.train_dataset, description="Training", batch_size=self._train_batch_size,
+                                  sampler_fn=self._get_train_sampler, is_training=True)
+    resume = getattr(self.model, "resume_from_checkpoint", None)
+    if resume is True:
+        from transformers.trainer_utils import get_last_checkpoint
+
+        resume = get_last_checkpoint(self.args.output_dir)
+        if resume is None:
+            raise ValueError(f"No valid checkpoint found in output directory ({self.args.output_dir})")
+        self.model.resume_from_checkpoint = resume
+    if isinstance(resume, str) and os.path.isdir(resume):
+        restore_dataloader_state(dl, resume)
+    return dl
+
+
 def patch_hf_trainer_evaluate() -> bool:
     """Install the hooks on ``transformers.Trainer``.  Returns False when transformers is not available."""
     try:
@@ -69,20 +100,13 @@ def patch_hf_trainer_evaluate() -> bool:
     from ...framework.model_patcher import patch_target_module
 
     patch_target_module("transformers.trainer.Trainer._evaluate", _evaluate)
-    original_get = Trainer.get_train_dataloader
-
-    def get_train_dataloader(self):
-        dl = original_get(self)
-        resume = getattr(self.model, "resume_from_checkpoint", None)
-        if isinstance(resume, str) and os.path.isdir(resume):
-            restore_dataloader_state(dl, resume)
-        return dl
-
+    if not hasattr(Trainer, "_fmsb_original_get_train_dataloader"):
+        Trainer._fmsb_original_get_train_dataloader = Trainer.get_train_dataloader
     Trainer.get_train_dataloader = get_train_dataloader
     try:
         import transformers.trainer as tr
 
-        tr.skip_first_batches = lambda dataloader, num_batches=0: dataloader
+        tr.skip_first_batches = skip_first_batches
     except Exception:
         pass
     return True

@@ -15,6 +15,7 @@ from typing import Dict, Tuple
 import torch
 
 from ...framework.framework_plugin import AccelerationPlugin
+from .autogptq_utils import requires_installation_on_all_linears
 from .framework_plugin_bnb import _prepare_model_for_kbit_training
 
 
@@ -68,7 +69,8 @@ class AutoGPTQAccelerationPlugin(AccelerationPlugin):
             gradient_checkpointing_kwargs=train_args.gradient_checkpointing_kwargs)
         qm = getattr(model, "quantization_method", "gptq")
         model = get_gptq_peft_model(model, peft_config=peft_config,
-                                    auto_find_all_linears=requires_installation_on_all_linears(peft_config),
+                                    auto_find_all_linears=requires_installation_on_all_linears(
+                                        peft_config, getattr(getattr(model, "config", None), "model_type", None)),
                                     train_mode=True)
         model.quantization_method = qm
         return model, (None,)
@@ -80,12 +82,6 @@ class AutoGPTQAccelerationPlugin(AccelerationPlugin):
 
             install_engine(model, accelerator)
         return []
-
-
-def requires_installation_on_all_linears(peft_config) -> bool:
-    """True when ``target_modules`` asks for every linear layer (``all-linear``)."""
-    tm = getattr(peft_config, "target_modules", None)
-    return isinstance(tm, str) and tm in ("all-linear", "all_linear")
 
 
 AccelerationPlugin.register_plugin(AutoGPTQAccelerationPlugin, configuration_and_paths=["peft.quantization.auto_gptq"])

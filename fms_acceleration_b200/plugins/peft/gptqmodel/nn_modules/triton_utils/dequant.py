@@ -26,3 +26,22 @@ def quant_matmul_248(input, qweight, scales, qzeros, g_idx, bits: int, maxq=None
     else:
         y = x2 @ (W.t() if transpose else W).to(x2.dtype)
     return y.reshape(*input.shape[:-1], y.shape[-1])
+
+
+class QuantLinearFunction(torch.autograd.Function):
+    """``input @ W`` for a packed GPTQ weight with the reference's argument list (dequant.py:141-161): the weight is
+    expanded for the product and again, transposed, for the input gradient; the packed tensors take no gradient."""
+
+    @staticmethod
+    def forward(ctx, input, qweight, scales, qzeros, g_idx, bits, maxq):
+        ctx.save_for_backward(qweight, scales, qzeros, g_idx)
+        ctx.bits, ctx.maxq = bits, maxq
+        return quant_matmul_248(input, qweight, scales, qzeros, g_idx, bits, maxq)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        qweight, scales, qzeros, g_idx = ctx.saved_tensors
+        grad_input = None
+        if ctx.needs_input_grad[0]:
+            grad_input = quant_matmul_248(grad_output, qweight, scales, qzeros, g_idx, ctx.bits, ctx.maxq, transpose=True)
+        return grad_input, None, None, None, None, None, None

@@ -145,3 +145,13 @@ class QuantizeConfig:
                     continue
             return cls.from_quant_config(raw, format)
         raise ValueError(f"No {QUANT_CONFIG_FILENAME_COMPAT} found in {save_dir!r}")
+
+
+class BaseQuantizeConfig(QuantizeConfig):
+    """Earlier name of :class:`QuantizeConfig`, kept as the reference keeps it (quantization/config.py:324-331)."""
+
+    def __init__(self, *args, **kwargs):
+        import warnings
+
+        warnings.warn("BaseQuantizeConfig is the earlier name of QuantizeConfig", DeprecationWarning, stacklevel=2)
+        super().__init__(*args, **kwargs)

@@ -245,3 +245,89 @@ def verify_file_hash(path: str, expected: str) -> bool:
         for piece in iter(lambda: fh.read(1 << 20), b""):
             h.update(piece)
     return h.hexdigest() == digest.lower()
+
+
+# ------------------------------------------------------------------------------------------------
+# Small helpers with the reference's names (fms_acceleration_peft/gptqmodel/utils/model.py:82-100, 272-290, 367-404,
+# 455-520), so that code written against its GPTQ library keeps importing.
+# ------------------------------------------------------------------------------------------------
+def get_device(obj) -> torch.device:
+    """Device of a tensor, or of a module's first parameter (buffers when it has no parameter)."""
+    if isinstance(obj, torch.Tensor):
+        return obj.device
+    for t in obj.parameters():
+        return t.device
+    for t in obj.buffers():
+        return t.device
+    raise ValueError("the module holds no tensor")
+
+
+def move_to(obj, device):
+    """``obj`` on ``device``; tensors and modules already there are returned as they are."""
+    device = torch.device(device)
+    return obj if get_device(obj) == device else obj.to(device)
+
+
+def nested_move_to(value, device):
+    """:func:`move_to` through lists, tuples and dicts; anything that is not a tensor is passed through."""
+    if isinstance(value, torch.Tensor):
+        return move_to(value, device)
+    if isinstance(value, (list, tuple)):
+        return type(value)(nested_move_to(v, device) for v in value)
+    if isinstance(value, dict):
+        return {k: nested_move_to(v, device) for k, v in value.items()}
+    return value
+
+
+def select_quant_linear_with_pack(bits: int, group_size: int, desc_act: bool, sym: bool, backend=None,
+                                  format: str = None, pack: bool = True):
+    """The ``QuantLinear`` class for these settings that can also pack a float layer."""
+    from ..quantization.config import FORMAT
+    from .backend import Backend
+    from .importer import select_quant_linear
+
+    return select_quant_linear(bits=bits, group_size=group_size, desc_act=desc_act, sym=sym,
+                               backend=backend if backend is not None else Backend.AUTO,
+                               format=format if format is not None else FORMAT.GPTQ_V2, pack=pack)
+
+
+def verify_model_hash(file_path: str, verify_hash: str) -> bool:
+    """``verify_hash`` is ``"<algorithm>:<hex digest>"``."""
+    if not isinstance(verify_hash, str):
+        raise ValueError("model verify_hash must be a string")
+    if ":" not in verify_hash:
+        raise ValueError("verify_hash must be in the format 'hash_type:hash_value'")
+    return verify_file_hash(file_path, verify_hash)
+
+
+def verify_sharded_model_hashes(index_json: str, verify_hash: List[str]) -> bool:
+    """One hash per shard file named in a ``*.index.json`` weight map (shards in sorted order, resolved beside the
+    index file)."""
+    if not isinstance(verify_hash, list):
+        raise ValueError("sharded model verify_hash must be a list")
+    with open(index_json, encoding="utf-8") as fh:
+        shards = sorted(set(json.load(fh)["weight_map"].values()))
+    if len(shards) != len(verify_hash):
+        raise ValueError("Number of shards and number of hash values do not match.")
+    folder = os.path.dirname(os.path.abspath(index_json))
+    return all(verify_model_hash(os.path.join(folder, shard), h) for shard, h in zip(shards, verify_hash))
+
+
+def check_and_get_model_type(model_dir: str, trust_remote_code: bool = False) -> str:
+    """``model_type`` of the configuration in ``model_dir`` if the GPTQ library has a class for it."""
+    from ..models.auto import MODEL_MAP
+
+    with open(os.path.join(model_dir, "config.json"), encoding="utf-8") as fh:
+        model_type = json.load(fh).get("model_type")
+    if model_type not in MODEL_MAP:
+        raise TypeError(f"{model_type} isn't supported yet.")
+    return model_type
+
+
+def gptqmodel_post_init(model: nn.Module, use_act_order: bool = False, max_input_length: Optional[int] = None) -> nn.Module:
+    """Run ``post_init`` of every quantised linear (here: decide whether its groups are in input order, which selects
+    the kernels).  The reference's scratch buffers for the exllama kernels have no counterpart."""
+    for m in model.modules():
+        if isinstance(m, QuantLinear):
+            m.post_init()
+    return model

@@ -2,12 +2,23 @@
 from __future__ import annotations
 
 import contextlib
+from dataclasses import dataclass
 from typing import List
 
 import torch
 
 from fms_acceleration_b200.nn.gptq import QuantLinear
 from fms_acceleration_b200.nn.lora import LoraConfig, LoraLinear, PeftModelShim
+
+
+@dataclass
+class GPTQLoraConfig(LoraConfig):
+    """``LoraConfig`` with the two switches of the reference's GPTQ LoRA configuration
+    (fms_acceleration_peft/gptqmodel/utils/peft.py:41-43); both describe fused modules injected by other GPTQ
+    back-ends and are only carried along here."""
+
+    injected_fused_attention: bool = False
+    injected_fused_mlp: bool = False
 
 
 class GPTQLoraLinear(LoraLinear):
