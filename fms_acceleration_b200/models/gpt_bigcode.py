@@ -15,6 +15,7 @@ from torch import nn
 
 from ..ops import cross_entropy as CE
 from .config import DecoderConfig
+from .generation import GenerationMixin
 from .llama import CausalLMOutput, _init_weights, _run_layer
 
 
@@ -116,7 +117,7 @@ class GPTBigCodeModel(nn.Module):
         return self.ln_f(x)
 
 
-class GPTBigCodeForCausalLM(nn.Module):
+class GPTBigCodeForCausalLM(GenerationMixin, nn.Module):
     def __init__(self, cfg: DecoderConfig, layer_hook=None):
         super().__init__()
         self.config = cfg

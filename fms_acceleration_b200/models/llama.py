@@ -22,6 +22,7 @@ from ..ops import cross_entropy as CE
 from ..ops import rmsnorm as RN
 from ..ops.rope import rope_ref, rope_tables
 from .config import DecoderConfig
+from .generation import GenerationMixin
 
 
 @dataclass
@@ -236,7 +237,7 @@ class LlamaModel(nn.Module):
         return self.norm(x)
 
 
-class LlamaForCausalLM(nn.Module):
+class LlamaForCausalLM(GenerationMixin, nn.Module):
     model_cls = LlamaModel
 
     def __init__(self, cfg: DecoderConfig, layer_hook=None):

@@ -19,6 +19,7 @@ from ..ops import cross_entropy as CE
 from ..ops import mamba as MB
 from ..ops import rmsnorm as RN
 from .config import DecoderConfig
+from .generation import GenerationMixin
 from .llama import CausalLMOutput, LlamaRMSNorm, _DenseLinear, _init_weights, _run_layer
 
 
@@ -161,7 +162,7 @@ class Mamba2Model(nn.Module):
         return RN.rmsnorm(x, self.norm_f.weight, self.norm_f.variance_epsilon) if x.is_cuda else self.norm_f(x)
 
 
-class Mamba2ForCausalLM(nn.Module):
+class Mamba2ForCausalLM(GenerationMixin, nn.Module):
     def __init__(self, cfg: DecoderConfig, layer_hook=None):
         super().__init__()
         self.config = cfg

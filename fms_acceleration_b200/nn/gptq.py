@@ -145,6 +145,13 @@ class QuantLinear(nn.Module):
             y = y + self.bias.to(y.dtype)
         return y
 
+    @classmethod
+    def warmup(cls, model, transpose: bool = False, seqlen: int = 2048) -> int:
+        """The reference pre-tunes its Triton kernel for every distinct ``(in, out)`` shape here
+        (gptqmodel/nn_modules/qlinear/qlinear_tritonv2.py:184-230); these kernels choose their tiles from the problem
+        size, so there is nothing to tune.  Returns the number of distinct shapes found."""
+        return len({(m.infeatures, m.outfeatures) for m in model.modules() if isinstance(m, cls)})
+
     def extra_repr(self):
         return f"in={self.infeatures}, out={self.outfeatures}, bits={self.bits}, group_size={self.group_size}"
 

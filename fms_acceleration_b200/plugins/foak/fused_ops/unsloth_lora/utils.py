@@ -13,16 +13,19 @@ def QUANT_STATE(W, base_layer=None):
 
 
 def get_lora_parameters(proj):
-    """``(W, quant_state, A, B, scaling, dropout)`` of a (possibly LoRA-wrapped, possibly 4-bit) projection."""
+    """``(W, quant_state, bias, A, B, scaling, dropout)`` of a (possibly LoRA-wrapped, possibly 4-bit) projection;
+    the four adapter entries are None for a bare layer or when the adapter is disabled or merged (the reference's
+    tuple, fused_ops/unsloth_lora/utils.py:66-82)."""
     base, lora = _unwrap(proj)
     qs = base.quant_state() if hasattr(base, "quant_state") else None
     W = base.weight
-    if lora is None:
-        return W, qs, None, None, None, None
+    bias = getattr(base, "bias", None)
+    if lora is None or getattr(lora, "disable_adapters", False) or getattr(lora, "merged", False):
+        return W, qs, bias, None, None, None, None
     A, B, s = _lora_parts(lora)
     name = lora.active_adapters[0] if hasattr(lora, "active_adapters") else "default"
     drop = lora.lora_dropout[name] if hasattr(lora, "lora_dropout") else None
-    return W, qs, A, B, s, drop
+    return W, qs, bias, A, B, s, drop
 
 
 def matmul_lora(X, W, W_quant, A, B, s, out=None, dropout=None):
@@ -40,7 +43,7 @@ def matmul_lora(X, W, W_quant, A, B, s, out=None, dropout=None):
 def fast_linear_forward(proj, X, temp_lora=None, out=None):
     """Inference forward of a (LoRA-wrapped, possibly 4-bit) projection: ``X W^T (+ bias) + s (X A^T) B^T``
     (reference :209-247).  A few rows on a 4-bit base go through the fused dequantise+GEMM kernel."""
-    W, qs, A, B, s, _ = get_lora_parameters(proj)
+    W, qs, bias, A, B, s, _ = get_lora_parameters(proj)
     base, _lora = _unwrap(proj)
     rows = X.numel() // X.shape[-1]
     if qs is not None and X.is_cuda and rows <= 128:
@@ -49,5 +52,4 @@ def fast_linear_forward(proj, X, temp_lora=None, out=None):
             y = y + s * ((X @ A.to(X.dtype).t()) @ B.to(X.dtype).t())
     else:
         y = matmul_lora(X, W, qs, A, B, s)
-    bias = getattr(base, "bias", None)
     return y if bias is None else y + bias.to(y.dtype)

@@ -22,7 +22,9 @@ class AutoCategorizeConfig:
     tokenizer: Any = None                       # when given, ``input_ids`` are detokenised into text first
     seed: int = 42
     model_kwargs: Dict[str, Any] = field(default_factory=dict)
-    kmeans_kwargs: Dict[str, Any] = field(default_factory=dict)
+    cluster_algo: str = "kmeans"                # the only clustering offered, as in the reference
+    cluster_kwargs: Dict[str, Any] = field(default_factory=dict)   # extra arguments of the clusterer
+    kmeans_kwargs: Dict[str, Any] = field(default_factory=dict)    # older name of ``cluster_kwargs``; both apply
 
 
 class DatasetAutoCategorizer:
@@ -53,15 +55,18 @@ class DatasetAutoCategorizer:
         return max(c.min_categories, min(c.max_categories, k, n))
 
     def _cluster(self, emb: np.ndarray, k: int) -> np.ndarray:
+        c = self.config
+        if c.cluster_algo.lower() != "kmeans":
+            raise ValueError(f"Unsupported clustering algorithm '{c.cluster_algo}'. Only 'kmeans' is currently supported.")
+        extra = {"random_state": c.seed, **c.kmeans_kwargs, **c.cluster_kwargs}
         try:
             from cuml.cluster import KMeans as GpuKMeans  # optional
 
-            return np.asarray(GpuKMeans(n_clusters=k, random_state=self.config.seed, **self.config.kmeans_kwargs)
-                              .fit_predict(emb))
+            return np.asarray(GpuKMeans(n_clusters=k, **extra).fit_predict(emb))
         except ImportError:
             from sklearn.cluster import KMeans
 
-            return KMeans(n_clusters=k, random_state=self.config.seed, n_init=10, **self.config.kmeans_kwargs).fit_predict(emb)
+            return KMeans(n_clusters=k, **{"n_init": 10, **extra}).fit_predict(emb)
 
     # -- entry point ----------------------------------------------------------------------------------
     def __call__(self, dataset) -> Dict[str, Any]:

@@ -38,6 +38,8 @@ class BaseGPTQModel(nn.Module):
     layer_modules: List[List[str]] = None
     dynamic_expert_index: Optional[str] = None
     info: Dict[str, str] = {}
+    # families whose Hugging Face implementation is remote code ask for ``trust_remote_code=True`` when loading
+    require_trust_remote_code = None
 
     def __init__(self, model: nn.Module, quantized: bool, quantize_config: QuantizeConfig):
         super().__init__()
@@ -56,6 +58,45 @@ class BaseGPTQModel(nn.Module):
     def to(self, device):
         self.model.to(device)
         return self
+
+    @property
+    def hf_device_map(self):
+        return getattr(self.model, "hf_device_map", None)
+
+    @property
+    def device(self) -> torch.device:
+        placement = self.hf_device_map
+        if placement:
+            return torch.device(next(d for d in placement.values() if d != "disk"))
+        inner = getattr(self.model, "device", None)
+        return inner if isinstance(inner, torch.device) else next(self.model.parameters()).device
+
+    def generate(self, **kwargs):
+        """Shortcut for ``model.generate`` under inference mode and autocast."""
+        with torch.inference_mode(), torch.amp.autocast(device_type=self.device.type):
+            return self.model.generate(**kwargs)
+
+    def prepare_inputs_for_generation(self, *args, **kwargs):
+        return self.model.prepare_inputs_for_generation(*args, **kwargs)
+
+    def shard_checkpoint(self, state_dict: Dict[str, torch.Tensor], max_shard_size: Union[int, str] = "10GB",
+                         weights_name: str = SAFE_WEIGHTS_NAME):
+        """``(shards: file name -> tensors, index or None)``: tensors in key order, a new file whenever the next
+        tensor would take the current one over ``max_shard_size`` (a larger single tensor gets a file of its own)."""
+        return shard_checkpoint(state_dict, parse_size(max_shard_size), weights_name)
+
+    def warmup_triton(self, enabled: bool = True):
+        """Kept for call compatibility: the CUDA kernels here have no autotuning cache to fill."""
+        if enabled:
+            QuantLinear.warmup(self.model, seqlen=getattr(self.model, "seqlen", 2048))
+
+    def __getattr__(self, item):
+        try:
+            return super().__getattr__(item)
+        except AttributeError:
+            if item == "model":
+                raise
+            return getattr(self.model, item)
 
     # ------------------------------------------------------------------ helpers
     @classmethod
@@ -205,8 +246,14 @@ class BaseGPTQModel(nn.Module):
     @classmethod
     def from_pretrained(cls, pretrained_model_name_or_path, quantize_config: QuantizeConfig,
                         torch_dtype=torch.float32, device="cpu", **kwargs):
+        cls._check_remote_code(pretrained_model_name_or_path, kwargs.get("trust_remote_code", False))
         model = build_model(pretrained_model_name_or_path, device=device, dtype=torch_dtype)
         return cls(model, False, quantize_config)
+
+    @classmethod
+    def _check_remote_code(cls, name, trust_remote_code: bool) -> None:
+        if cls.require_trust_remote_code and not trust_remote_code:
+            raise ValueError(f"{name} requires trust_remote_code=True. Please set trust_remote_code=True to load this model.")
 
     @classmethod
     def from_quantized(cls, model_name_or_path, quantize_config: Optional[QuantizeConfig] = None,
@@ -214,6 +261,7 @@ class BaseGPTQModel(nn.Module):
                        low_cpu_mem_usage: bool = False, **kwargs):
         from safetensors.torch import load_file
 
+        cls._check_remote_code(model_name_or_path, kwargs.get("trust_remote_code", False))
         device = device if device is not None else "cpu"
         cfg = resolve_config(model_name_or_path)
         is_dir = isinstance(model_name_or_path, str) and os.path.isdir(model_name_or_path)

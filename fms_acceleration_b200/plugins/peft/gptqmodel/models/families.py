@@ -65,6 +65,7 @@ class DbrxGPTQ(BaseGPTQModel):
 
 
 class DbrxConvertedGPTQ(BaseGPTQModel):
+    require_trust_remote_code = True  # the converted layout exists only as remote code on the Hugging Face side
     base_modules = ["transformer.wte", "transformer.norm_f"]
     layers_node = "transformer.blocks"
     layer_type = "DbrxBlock"

@@ -454,3 +454,65 @@ def test_cli_helper_names(tmp_path):
     assert install_plugin("no-such-plugin") != 0
     dest = get_benchmark_artifacts(str(tmp_path))
     assert os.path.isdir(dest) and os.listdir(dest)
+
+
+# --------------------------------------------------------------------------------- class members of the GPTQ library
+def test_gptq_model_wrapper_members():
+    from fms_acceleration_peft.gptqmodel import GPTQModel, QuantizeConfig
+    from fms_acceleration_peft.gptqmodel.models.dbrx_converted import DbrxConvertedGPTQ
+    from fms_acceleration_peft.gptqmodel.nn_modules.qlinear.qlinear_tritonv2 import QuantLinear
+
+    qc = QuantizeConfig(bits=4, group_size=32, desc_act=False, sym=True)
+    m = GPTQModel.from_quantized("tiny-llama", quantize_config=qc, torch_dtype=torch.float32, device="cpu")
+    assert m.device == torch.device("cpu") and m.hf_device_map is None and m.require_trust_remote_code is None
+    ids = torch.randint(0, 100, (1, 4))
+    out = m.generate(input_ids=ids, max_new_tokens=3)
+    assert out.shape == (1, 7) and torch.equal(out[:, :4], ids)
+    assert m.prepare_inputs_for_generation(ids)["input_ids"] is ids
+    shards, index = m.shard_checkpoint(dict(m.model.state_dict()), max_shard_size="200KB")
+    assert len(shards) > 1 and set(index["weight_map"]) == set(m.model.state_dict())
+    m.warmup_triton()
+    assert QuantLinear.warmup(m.model) >= 1
+    assert m.fast_loss is m.model.fast_loss  # unknown attributes are looked up on the wrapped model
+    with pytest.raises(AttributeError):
+        m.no_such_attribute  # noqa: B018
+    with pytest.raises(ValueError, match="trust_remote_code"):
+        DbrxConvertedGPTQ.from_quantized("anything", quantize_config=qc)
+
+
+def test_lora_parameter_tuples_have_the_reference_arity():
+    from fms_acceleration_foak.fused_ops.unsloth_lora.gptq.fast_lora import GPTQuantState, extract_gptq_state
+    from fms_acceleration_foak.fused_ops.unsloth_lora.gptq.fast_lora import get_lora_parameters as gptq_params
+    from fms_acceleration_foak.fused_ops.unsloth_lora.utils import get_lora_parameters as dense_params
+    from fms_acceleration_b200.nn.gptq import QuantLinear
+    from fms_acceleration_b200.nn.lora import LoraLinear
+
+    q = QuantLinear.random(64, 32, group_size=32, dtype=torch.float32)
+    st = extract_gptq_state(q)
+    assert isinstance(st, GPTQuantState) and (st.infeatures, st.outfeatures, st.group_size, st.maxq) == (64, 32, 32, 15)
+    assert st.bias is None and st.trainable and not st.autogptq_cuda_available
+    bare = gptq_params(q)
+    assert len(bare) == 6 and bare[0].qweight is q.qweight and all(v is None for v in bare[2:])
+    wrapped = LoraLinear(q, r=4, lora_alpha=8)
+    qs, bias, A, B, s, drop = gptq_params(wrapped)
+    assert A.shape == (4, 64) and B.shape == (32, 4) and s == 2.0 and bias is None
+    wrapped.disable_adapters = True
+    assert all(v is None for v in gptq_params(wrapped)[2:])
+
+    lin = torch.nn.Linear(8, 6)
+    W, qstate, bias, A, B, s, drop = dense_params(LoraLinear(lin, r=2, lora_alpha=2))
+    assert W is lin.weight and qstate is None and bias is lin.bias and A.shape == (2, 8) and s == 1.0
+    assert len(dense_params(lin)) == 7 and dense_params(lin)[3] is None
+
+
+def test_auto_categorizer_cluster_options():
+    from fms_acceleration_odm.odm.auto_categorizer import AutoCategorizeConfig, DatasetAutoCategorizer
+
+    cfg = AutoCategorizeConfig(cluster_kwargs={"n_init": 3}, num_categories=2)
+    assert cfg.cluster_algo == "kmeans"
+    rng = np.random.default_rng(0)
+    emb = np.concatenate([rng.normal(0, 0.1, (10, 4)), rng.normal(5, 0.1, (10, 4))])
+    labels = DatasetAutoCategorizer(cfg)._cluster(emb, 2)
+    assert len(set(labels[:10])) == 1 and len(set(labels[10:])) == 1 and labels[0] != labels[10]
+    with pytest.raises(ValueError, match="kmeans"):
+        DatasetAutoCategorizer(AutoCategorizeConfig(cluster_algo="dbscan"))._cluster(emb, 2)
