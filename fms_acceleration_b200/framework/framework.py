@@ -138,7 +138,9 @@ class AccelerationFramework:
         return plugin.model_loader(model_name, **kwargs)
 
     def augmentation(self, model, train_args, modifiable_args: Tuple):
-        archs = getattr(getattr(model, "config", None), "architectures", None)
+        # a model without a ``config`` is an error (AttributeError), as in the reference; a config that lists no
+        # architectures matches no restricted plugin
+        archs = getattr(model.config, "architectures", None)
         model_archs = set(archs if archs is not None else [])
         for plugin_name, plugin in self.active_plugins:
             if plugin.restricted_model_archs and not any(a in model_archs for a in plugin.restricted_model_archs):

@@ -3,11 +3,21 @@ cluster (role of fms_acceleration_odm/odm/auto_categorizer.py:38-201).  The embe
 and cuML are optional; scikit-learn's KMeans is the default clusterer."""
 from __future__ import annotations
 
+import copy
 import math
 from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional
 
 import numpy as np
+import torch
+
+try:  # optional dependency; the module-level name is what callers (and tests) may replace
+    from sentence_transformers import SentenceTransformer
+except ImportError:  # pragma: no cover - depends on the environment
+    SentenceTransformer = None
+
+#: column that receives the rebuilt text of a pre-tokenised dataset
+AUTO_CATEGORIZATION_COLUMN_NAME = "auto_categorization_text"
 
 
 @dataclass
@@ -29,30 +39,57 @@ class AutoCategorizeConfig:
 
 class DatasetAutoCategorizer:
     def __init__(self, config: Optional[AutoCategorizeConfig] = None):
-        self.config = config or AutoCategorizeConfig()
+        # a private copy: a pre-tokenised dataset redirects ``input_column`` to the rebuilt text
+        self.config = copy.copy(config) if config is not None else AutoCategorizeConfig()
 
     # -- pieces ---------------------------------------------------------------------------------------
+    def _column(self, dataset, name: str):
+        cols = getattr(dataset, "column_names", None)
+        if cols is not None:
+            return dataset[name]
+        return [dataset[i][name] for i in range(len(dataset))]
+
     def _texts(self, dataset) -> List[str]:
+        """The strings to embed: the input column itself, or, when it holds token ids, their decoding (which needs
+        ``config.tokenizer``; an AssertionError without one, as in the reference :107-135)."""
         c = self.config
         cols = getattr(dataset, "column_names", None)
-        if cols is not None and c.input_column in cols:
-            return [str(t) for t in dataset[c.input_column]]
-        if c.tokenizer is not None:
-            return [c.tokenizer.decode(dataset[i]["input_ids"], skip_special_tokens=True) for i in range(len(dataset))]
-        raise ValueError(f"dataset has no column {c.input_column!r} and no tokenizer was given to rebuild the text")
+        if cols is None:
+            cols = list(dataset[0].keys())
+        if c.input_column not in cols:
+            raise ValueError(f"Dataset is missing column '{c.input_column}'. Provide a input field in "
+                             "auto_categorize_config['input_column'].")
+        values = self._column(dataset, c.input_column)
+        if isinstance(values[0], str):
+            return [str(t) for t in values]
+        assert c.tokenizer is not None, (
+            f"Attempting detokenizing the data on column '{c.input_column}' but the tokenizer is not provided")
+        assert AUTO_CATEGORIZATION_COLUMN_NAME not in cols, (
+            f"Default detokenizing column '{AUTO_CATEGORIZATION_COLUMN_NAME}' is already present in the dataset")
+        rows = [v.tolist() if hasattr(v, "tolist") else list(v) for v in values]
+        if hasattr(c.tokenizer, "batch_decode"):
+            return list(c.tokenizer.batch_decode(rows))
+        return [c.tokenizer.decode(r) for r in rows]
 
     def _embed(self, texts: List[str]) -> np.ndarray:
-        from sentence_transformers import SentenceTransformer  # optional dependency
-
-        model = SentenceTransformer(self.config.model_name, **self.config.model_kwargs)
+        if SentenceTransformer is None:
+            raise ImportError("auto-categorisation needs the sentence-transformers package for its embeddings")
+        model = SentenceTransformer(self.config.model_name, model_kwargs=self.config.model_kwargs,
+                                    prompts={"clustering": "Identify the topic or theme based on the text: "},
+                                    default_prompt_name="clustering")
         emb = model.encode(texts, batch_size=self.config.batch_size, convert_to_numpy=True, normalize_embeddings=True,
                            show_progress_bar=False)
         return np.asarray(emb, dtype=np.float32)
 
     def _num_clusters(self, n: int) -> int:
+        """``num_categories`` when given, else ``floor(sqrt(n))`` kept inside ``[min_categories, max_categories]``;
+        never more clusters than rows (reference :137-149)."""
         c = self.config
-        k = c.num_categories if c.num_categories else int(round(math.sqrt(n)))
-        return max(c.min_categories, min(c.max_categories, k, n))
+        if c.num_categories is not None:
+            k = c.num_categories
+        else:
+            k = min(max(int(math.sqrt(max(n, 1))), c.min_categories), c.max_categories)
+        return max(1, min(n, k))
 
     def _cluster(self, emb: np.ndarray, k: int) -> np.ndarray:
         c = self.config
@@ -70,6 +107,11 @@ class DatasetAutoCategorizer:
 
     # -- entry point ----------------------------------------------------------------------------------
     def __call__(self, dataset) -> Dict[str, Any]:
+        if isinstance(dataset, torch.utils.data.IterableDataset):
+            raise NotImplementedError("Iterable (or streaming) datasets are not yet supported for auto categorization. "
+                                      "Please use a non-iterable dataset.")
+        if len(dataset) == 0:
+            raise ValueError("Cannot auto-categorize an empty dataset")
         texts = self._texts(dataset)
         emb = self._embed(texts)
         k = self._num_clusters(len(texts))

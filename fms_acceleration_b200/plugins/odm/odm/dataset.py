@@ -29,20 +29,34 @@ logger = getLogger(__name__)
 
 class _ResumableLoader:
     """Batch-size-1 sequential loader whose position can be saved and restored (the job ``StatefulDataLoader`` of
-    torchdata does for the reference)."""
+    torchdata does for the reference).  Map-style datasets are indexed; iterable (streaming) ones are consumed
+    through their iterator and a restored position is reached by skipping that many samples."""
 
     def __init__(self, dataset, collate_fn=None):
         self.dataset, self.collate_fn = dataset, collate_fn
+        self.streaming = isinstance(dataset, IterableDataset) or not hasattr(dataset, "__getitem__")
         self.pos = 0
+        self._it = None
 
     def __iter__(self):
         self.pos = 0
+        self._it = iter(self.dataset) if self.streaming else None
         return self
 
+    def _next_item(self):
+        if not self.streaming:
+            if self.pos >= len(self.dataset):
+                raise StopIteration
+            return self.dataset[self.pos]
+        if self._it is None:
+            # first use, or a restored position: start the stream and skip what was already consumed
+            self._it = iter(self.dataset)
+            for _ in range(self.pos):
+                next(self._it)
+        return next(self._it)
+
     def __next__(self):
-        if self.pos >= len(self.dataset):
-            raise StopIteration
-        item = self.dataset[self.pos]
+        item = self._next_item()
         self.pos += 1
         if self.collate_fn is not None:
             return self.collate_fn([item])
@@ -53,6 +67,7 @@ class _ResumableLoader:
 
     def load_state_dict(self, sd):
         self.pos = int(sd["pos"])
+        self._it = None
 
 
 class OnlineMixingDataset(IterableDataset):

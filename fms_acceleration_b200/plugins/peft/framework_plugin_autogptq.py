@@ -19,6 +19,18 @@ from .autogptq_utils import requires_installation_on_all_linears
 from .framework_plugin_bnb import _prepare_model_for_kbit_training
 
 
+def _package_available(name: str) -> bool:
+    try:
+        from transformers.utils import import_utils
+
+        found = import_utils._is_package_available(name)
+        return bool(found[0] if isinstance(found, tuple) else found)
+    except Exception:  # transformers absent or its helper renamed
+        import importlib.util
+
+        return importlib.util.find_spec(name) is not None
+
+
 class AutoGPTQAccelerationPlugin(AccelerationPlugin):
     require_packages = None
 
@@ -28,6 +40,16 @@ class AutoGPTQAccelerationPlugin(AccelerationPlugin):
         self._check_config_equal(key="peft.quantization.auto_gptq.from_quantized", value=True)
         self.use_external_lib = self._check_config_and_maybe_check_values(
             key="peft.quantization.auto_gptq.use_external_lib", values=[True, False], default=False)
+        if self.use_external_lib:
+            # the reference would now load through the external ``auto_gptq`` package; asking for it without having
+            # it is the same error here.  When it is installed the in-tree loader and kernels are used all the same
+            # (there is one GPTQ path in this package) and a warning says so.
+            assert _package_available("auto_gptq"), (
+                "Unable to use external library, auto_gptq module not found. "
+                "Refer to README for installation instructions  as a specific version might be required.")
+            import warnings
+
+            warnings.warn("use_external_lib is set, but this package always runs its own GPTQ loader and kernels")
 
     @property
     def requires_custom_loading(self):

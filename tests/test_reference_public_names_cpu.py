@@ -1,6 +1,7 @@
 """Every public function and class that a module of the reference's seven packages defines at module level resolves
 under the alias package of the same name.  ``data/reference_public_names.json`` is the frozen list (module path ->
-names, taken from the reference's sources with ``ast``; names only).  The only exceptions are Triton-specific: the
+names, taken from the reference's sources with ``ast``: module-level functions and classes, and for a package what its
+``__init__`` re-exports; names only).  The only exceptions are Triton-specific: the
 ``@triton.jit`` kernels themselves and the two autotuner modules, which have no counterpart in hand-written CUDA that
 picks its tile shapes from the problem size."""
 import importlib
@@ -28,6 +29,10 @@ TRITON_ONLY_NAMES = {
     ("fms_acceleration_foak.fused_ops.liger_ce.cross_entropy", "element_mul_kernel"),
     ("fms_acceleration_foak.fused_ops.unsloth_lora.gptq.triton.kernels", "make_dequant_configs"),
     ("fms_acceleration_foak.fused_ops.unsloth_lora.gptq.triton.kernels", "dequant_kernel_248"),
+    ("fms_acceleration_moe.utils.scattermoe_utils.khd.kernels", "groupXtY_triton_kernel"),
+    ("fms_acceleration_moe.utils.scattermoe_utils.khd.kernels", "group_triton_kernel"),
+    ("fms_acceleration_moe.utils.scattermoe_utils.khd.kernels", "scatter2scatter_lora_triton_kernel"),
+    ("fms_acceleration_moe.utils.scattermoe_utils.khd.kernels", "scatter2scatter_triton_kernel"),
 }
 
 
