@@ -293,7 +293,9 @@ def fast_dequantize(W, quant_state: "Quant4State | None" = None, out: torch.Tens
         if hasattr(W, "quant_state"):
             return dequantize_4bit(W.quant_state(), out=out)
         return W
-    return dequantize_4bit(quant_state, out=out)
+    dense = dequantize_4bit(quant_state, out=out)
+    # packed data laid out as one row ``[1, n]`` asks for the transposed weight (reference :138-140)
+    return dense.t() if isinstance(W, torch.Tensor) and W.dim() == 2 and W.shape[0] == 1 else dense
 
 
 def fast_gemv(x: torch.Tensor, W, quant_state: "Quant4State | None" = None, out: torch.Tensor | None = None):
