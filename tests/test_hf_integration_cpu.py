@@ -15,7 +15,10 @@ from fms_acceleration_b200.trainer import TrainArgs  # noqa: E402
 
 
 def _tiny_llama():
-    from transformers import LlamaConfig, LlamaForCausalLM
+    # the class of the module as it is NOW: the clean-up of this test reloads the modelling module, and the
+    # top-level ``transformers.LlamaForCausalLM`` may still be the class of the module before the reload
+    from transformers import LlamaConfig
+    from transformers.models.llama.modeling_llama import LlamaForCausalLM
 
     cfg = LlamaConfig(vocab_size=512, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
                       num_key_value_heads=2, max_position_embeddings=128, rms_norm_eps=1e-6, tie_word_embeddings=False,
