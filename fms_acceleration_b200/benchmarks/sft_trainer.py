@@ -65,6 +65,15 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--skip_memory_metrics", type=tf, nargs="?", const=True, default=True)
     ap.add_argument("--include_tokens_per_second", type=tf, nargs="?", const=True, default=True)
     ap.add_argument("--save_strategy", default="no")
+    ap.add_argument("--gradient_checkpointing", type=tf, nargs="?", const=True, default=False,
+                    help="recompute every decoder layer in backward (the reference's benchmark default)")
+    # arguments of the reference's benchmark defaults that have nothing to switch here: attention is always the
+    # in-tree variable-length kernel, there is no evaluation loop, and the training file is already tokenised and
+    # masked by data_processing.py (which is where the response template and the text field are used)
+    ap.add_argument("--use_flash_attn", type=tf, nargs="?", const=True, default=True)
+    ap.add_argument("--evaluation_strategy", "--eval_strategy", dest="evaluation_strategy", default="no")
+    ap.add_argument("--response_template", default=None)
+    ap.add_argument("--dataset_text_field", default=None)
     ap.add_argument("--num_layers_override", type=int, default=0, help="debugging: shrink the model")
     return ap
 
@@ -163,6 +172,7 @@ def main(argv: Optional[List[str]] = None) -> int:
                       weight_decay=args.weight_decay, max_grad_norm=args.max_grad_norm, bf16=dtype == torch.bfloat16,
                       seed=args.seed, max_seq_length=args.max_seq_length, output_dir=args.output_dir,
                       logging_steps=args.logging_steps, padding_free=True, world_size=world,
+                      gradient_checkpointing=bool(args.gradient_checkpointing),
                       parallel_mode="DISTRIBUTED" if world > 1 else "NOT_DISTRIBUTED")
     torch.manual_seed(args.seed)
     if cuda:

@@ -160,6 +160,54 @@ def tiny_granitemoehybrid() -> DecoderConfig:
                          layer_types=["mamba", "attention", "mamba", "mamba"])
 
 
+# The presets below take their shapes from the model cards as remembered (there is no network here to fetch the
+# configuration files); weights are random-init, so only the shapes matter for the benchmark scenarios that name them.
+def llama3_8b() -> DecoderConfig:
+    return DecoderConfig(vocab_size=128256, hidden_size=4096, intermediate_size=14336, num_hidden_layers=32,
+                         num_attention_heads=32, num_key_value_heads=8, rms_norm_eps=1e-5, rope_theta=500000.0,
+                         max_position_embeddings=8192, model_type="llama", architectures=["LlamaForCausalLM"])
+
+
+def powerlm_3b() -> DecoderConfig:
+    """ibm/PowerLM-3b: dense Granite-architecture decoder."""
+    return DecoderConfig(vocab_size=49152, hidden_size=2304, intermediate_size=9216, num_hidden_layers=40,
+                         num_attention_heads=36, num_key_value_heads=36, rms_norm_eps=1e-5, rope_theta=10000.0,
+                         max_position_embeddings=4096, tie_word_embeddings=True, model_type="granite",
+                         architectures=["GraniteForCausalLM"], embedding_multiplier=12.0, attention_multiplier=0.015625,
+                         residual_multiplier=0.22, logits_scaling=8.0)
+
+
+def powermoe_3b() -> DecoderConfig:
+    """ibm/PowerMoE-3b: 40 experts, 8 active (the shapes of granite-3.0-3b-a800m)."""
+    return DecoderConfig(vocab_size=49152, hidden_size=1536, intermediate_size=512, num_hidden_layers=32,
+                         num_attention_heads=24, num_key_value_heads=8, rms_norm_eps=1e-6, rope_theta=10000.0,
+                         max_position_embeddings=4096, tie_word_embeddings=True, model_type="granitemoe",
+                         architectures=["GraniteMoeForCausalLM"], num_local_experts=40, num_experts_per_tok=8,
+                         moe_intermediate_size=512, embedding_multiplier=12.0, attention_multiplier=0.015625,
+                         residual_multiplier=0.22, logits_scaling=6.0)
+
+
+def granite_moe_7b_1b_shared() -> DecoderConfig:
+    """ibm-research/moe-7b-1b-active-shared-experts: 62 routed experts, 6 active, plus a shared dense branch."""
+    return DecoderConfig(vocab_size=49160, hidden_size=1536, intermediate_size=512, num_hidden_layers=40,
+                         num_attention_heads=12, num_key_value_heads=4, rms_norm_eps=1e-5, rope_theta=10000.0,
+                         max_position_embeddings=8192, tie_word_embeddings=True, model_type="granitemoeshared",
+                         architectures=["GraniteMoeSharedForCausalLM"], num_local_experts=62, num_experts_per_tok=6,
+                         moe_intermediate_size=512, shared_intermediate_size=1024, embedding_multiplier=12.0,
+                         attention_multiplier=0.0078125, residual_multiplier=0.22, logits_scaling=6.0)
+
+
+def granite_4_tiny_preview() -> DecoderConfig:
+    """ibm-granite/granite-4.0-tiny-preview: the same feed-forward, Mamba2 mixers with an attention layer every tenth
+    layer (5, 15, 25, 35), no positional embedding."""
+    cfg = granite_moe_7b_1b_shared()
+    cfg.model_type, cfg.architectures = "granitemoehybrid", ["GraniteMoeHybridForCausalLM"]
+    cfg.mamba_d_state, cfg.mamba_d_head, cfg.mamba_expand, cfg.mamba_d_conv = 128, 64, 2, 4
+    cfg.mamba_n_groups, cfg.mamba_chunk_size = 1, 256
+    cfg.layer_types = ["attention" if i % 10 == 5 else "mamba" for i in range(cfg.num_hidden_layers)]
+    return cfg
+
+
 PRESETS = {
     "tiny-llama": tiny_llama,
     "mistral-7b": mistral_7b,
@@ -175,6 +223,11 @@ PRESETS = {
     "santacoder": santacoder,
     "tiny-gpt-bigcode": tiny_gpt_bigcode,
     "tiny-granitemoehybrid": tiny_granitemoehybrid,
+    "llama3-8b": llama3_8b,
+    "powerlm-3b": powerlm_3b,
+    "powermoe-3b": powermoe_3b,
+    "granite-moe-7b-1b-shared": granite_moe_7b_1b_shared,
+    "granite-4.0-tiny-preview": granite_4_tiny_preview,
 }
 
 # Hugging Face hub ids used by the reference's benchmark scenarios -> the preset of the same architecture
@@ -190,6 +243,12 @@ HUB_ALIASES = {
     "ibm-granite/granite-3.0-8b-instruct": "granite-8b",
     "bigcode/gpt_bigcode-santacoder": "santacoder",
     "state-spaces/mamba2-2.7b": "mamba2-2.7b",
+    "meta-llama/Meta-Llama-3-8B": "llama3-8b",
+    "TechxGenus/Meta-Llama-3-8B-GPTQ": "llama3-8b",
+    "ibm/PowerLM-3b": "powerlm-3b",
+    "ibm/PowerMoE-3b": "powermoe-3b",
+    "ibm-research/moe-7b-1b-active-shared-experts": "granite-moe-7b-1b-shared",
+    "ibm-granite/granite-4.0-tiny-preview": "granite-4.0-tiny-preview",
 }
 
 

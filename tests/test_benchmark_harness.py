@@ -49,9 +49,9 @@ def test_matrix_and_command_lines(tmp_path):
     assert json.load(open(e.path(B.FILE_ARGS)))["framework_config"] == "accelerated-peft-bnb-foak"
     # 5 cannot be split over 2 GPUs
     assert all(x.num_gpus == 1 for x in B.build_experiments([sc], {}, [1, 2], [5], str(tmp_path), B.framework_config_files()))
-    with pytest.raises(KeyError):
-        B.build_experiments([B.Scenario("x", ["nope"], {"model_name_or_path": "tiny-llama"})], {}, [1], [4], str(tmp_path),
-                            B.framework_config_files())
+    # a short name without a sample configuration drops out of the matrix
+    assert B.build_experiments([B.Scenario("x", ["nope"], {"model_name_or_path": "tiny-llama"})], {}, [1], [4],
+                               str(tmp_path), B.framework_config_files()) == []
 
 
 def test_output_scraping(tmp_path):
@@ -138,3 +138,69 @@ def test_shell_driver_dry_run(tmp_path):
     assert r.returncode == 0, r.stderr
     cmds = [open(out / d / "command.sh").read() for d in os.listdir(out) if d.startswith("exp_")]
     assert len(cmds) == 24 and any("moe-scattermoe-granite-ep8-foak" in c for c in cmds)
+
+
+# hub ids that the reference's scenario files name (scripts/benchmarks/scenarios*.yaml)
+REFERENCE_SCENARIO_MODELS = [
+    "NousResearch/Llama-2-70b-hf", "TheBloke/Llama-2-70B-GPTQ", "TheBloke/Mistral-7B-v0.1-GPTQ",
+    "TheBloke/Mixtral-8x7B-Instruct-v0.1-GPTQ", "bigcode/gpt_bigcode-santacoder",
+    "ibm-granite/granite-3.0-3b-a800m-instruct", "ibm-granite/granite-4.0-tiny-preview",
+    "ibm-research/moe-7b-1b-active-shared-experts", "ibm/PowerLM-3b", "ibm/PowerMoE-3b", "meta-llama/Meta-Llama-3-8B",
+    "TechxGenus/Meta-Llama-3-8B-GPTQ", "mistralai/Mistral-7B-v0.1", "mistralai/Mixtral-8x7B-Instruct-v0.1",
+]
+
+
+@pytest.mark.parametrize("hub_id", REFERENCE_SCENARIO_MODELS)
+def test_models_of_the_reference_scenarios_resolve_to_presets(hub_id):
+    import torch
+
+    from fms_acceleration_b200.models.builder import build_model, resolve_config
+
+    cfg = resolve_config(hub_id)
+    with torch.device("meta"):
+        model = build_model(cfg, device="meta", dtype=torch.bfloat16)
+    billions = sum(p.numel() for p in model.parameters()) / 1e9
+    expected = {"Llama-2-70": 69.0, "Mistral-7B": 7.2, "Mixtral-8x7B": 46.7, "santacoder": 1.1, "3b-a800m": 3.3,
+                "tiny-preview": 6.7, "7b-1b": 6.4, "PowerLM-3b": 3.5, "PowerMoE-3b": 3.3, "Llama-3-8B": 8.0}
+    want = next(v for k, v in expected.items() if k in hub_id)
+    assert abs(billions - want) / want < 0.06, (hub_id, billions)
+
+
+def test_a_scenario_file_in_the_reference_format_runs_through_the_matrix(tmp_path):
+    """Hub ids as model names, learning rates written as strings, a framework short name without a sample
+    configuration (dropped with a message, as the reference does), the reference's default arguments."""
+    scen = {"scenarios": [{"name": "accelerated-peft-bnb",
+                           "framework_config": ["accelerated-peft-bnb", "no-such-shortname"],
+                           "arguments": {"learning_rate": "2e-4", "torch_dtype": "bfloat16", "peft_method": "lora", "r": 16,
+                                         "lora_alpha": 16, "lora_dropout": 0.1,
+                                         "target_modules": ["q_proj", "k_proj", "v_proj", "o_proj"],
+                                         "model_name_or_path": ["ibm/PowerLM-3b"]}}]}
+    defaults = {"use_flash_attn": True, "response_template": "\n### Response:", "dataset_text_field": "output",
+                "gradient_checkpointing": True, "evaluation_strategy": "no", "adam_epsilon": "1e-4", "max_steps": 100}
+    sp, dp = tmp_path / "scenarios.yaml", tmp_path / "defaults.yaml"
+    sp.write_text(yaml.safe_dump(scen))
+    dp.write_text(yaml.safe_dump(defaults))
+    out = tmp_path / "results"
+    rc = B.main(["--num_gpus", "1", "--effective_batch_size_matrix", "4", "--scenarios_config_path", str(sp),
+                 "--defaults_config_path", str(dp), "--results_output_path", str(out), "--dry_run"])
+    assert rc == 0
+    exps = sorted(os.listdir(out))
+    assert [e for e in exps if e.startswith("exp_")] == ["exp_0"]  # the unknown short name dropped out
+    cmd = (out / "exp_0" / "command.sh").read_text()
+    assert "--gradient_checkpointing True" in cmd and "--model_name_or_path ibm/PowerLM-3b" in cmd
+
+
+def test_trainer_cli_takes_the_reference_default_arguments(capsys):
+    from fms_acceleration_b200.benchmarks import sft_trainer as T
+
+    args, unknown = T.build_parser().parse_known_args([
+        "--model_name_or_path", "tiny-llama", "--use_flash_attn", "True", "--response_template", "\n### Response:",
+        "--dataset_text_field", "output", "--gradient_checkpointing", "True", "--evaluation_strategy", "no",
+        "--adam_epsilon", "1e-4", "--include_tokens_per_second", "True", "--save_strategy", "no"])
+    assert unknown == [] and args.gradient_checkpointing is True and args.adam_epsilon == 1e-4
+    rc = T.main(["--model_name_or_path", "tiny-llama", "--torch_dtype", "float32", "--max_steps", "2", "--logging_steps", "1",
+                 "--per_device_train_batch_size", "2", "--max_seq_length", "32", "--gradient_checkpointing", "True",
+                 "--gradient_accumulation_steps", "2"])
+    assert rc == 0
+    text = capsys.readouterr().out
+    assert "train_tokens_per_second" in text and "ignored arguments" not in text
