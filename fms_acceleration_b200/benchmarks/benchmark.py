@@ -61,6 +61,7 @@ class Scenario:
     name: str
     framework_configs: List[Optional[str]]
     arguments: Dict[str, Any]
+    slow: bool = False  # a slow scenario runs only when it is asked for by name
 
     def argument_sets(self) -> Iterable[Dict[str, Any]]:
         """Cartesian product over the list-valued arguments."""
@@ -79,8 +80,12 @@ def load_scenarios(path: str, only: Optional[List[str]] = None) -> List[Scenario
     for s in doc["scenarios"]:
         if only and s["name"] not in only:
             continue
+        if not only and s.get("slow"):
+            # unfiltered runs leave out the scenarios marked slow (scripts/benchmarks/benchmark.py:722-728)
+            print(f"skipping slow scenario {s['name']!r}: name it to run it", file=sys.stderr)
+            continue
         fcs = s.get("framework_config") or [None]
-        out.append(Scenario(s["name"], list(fcs), dict(s.get("arguments") or {})))
+        out.append(Scenario(s["name"], list(fcs), dict(s.get("arguments") or {}), bool(s.get("slow", False))))
     return out
 
 
@@ -303,11 +308,17 @@ def memory_metrics(path: str) -> Dict[str, Any]:
 # --------------------------------------------------------------------------------------- matrix
 def build_experiments(scenarios: List[Scenario], defaults: Dict[str, Any], num_gpus: List[int],
                       effective_batch_sizes: List[int], root: str, config_files: Dict[str, str],
-                      extra: Optional[Dict[str, Any]] = None, base_port: int = 29511) -> List[Experiment]:
+                      extra: Optional[Dict[str, Any]] = None, base_port: int = 29511,
+                      matrices: Optional[Dict[str, List[Any]]] = None) -> List[Experiment]:
+    """``matrices``: further run-wide dimensions (argument name -> values, e.g. ``max_seq_length``, ``packing``) that
+    multiply every scenario like the numbers of GPUs and the effective batch sizes do."""
     exps: List[Experiment] = []
     n = 0
+    dims = {k: v for k, v in (matrices or {}).items() if v}
+    combos = [dict(zip(dims, c)) for c in itertools.product(*dims.values())] or [{}]
     for sc in scenarios:
-        for args in sc.argument_sets():
+        for base_args, combo in itertools.product(list(sc.argument_sets()), combos):
+            args = {**combo, **base_args}  # what a scenario fixes is not varied
             for fc in sc.framework_configs:
                 if fc is not None and fc not in config_files:
                     # a short name without a sample configuration drops out of the matrix, as in the reference
@@ -345,7 +356,7 @@ def write_summary(exps: List[Experiment], path: str) -> None:
 
 def main(argv: Optional[List[str]] = None) -> int:
     ap = argparse.ArgumentParser(description="run the benchmark matrix")
-    ap.add_argument("--num_gpus", type=int, nargs="+", default=[1])
+    ap.add_argument("--num_gpus", "--num_gpus_matrix", dest="num_gpus", type=int, nargs="+", default=[1])
     ap.add_argument("--effective_batch_size_matrix", type=int, nargs="+", default=[4])
     ap.add_argument("--scenarios_config_path", default=os.path.join(HERE, "scenarios.yaml"))
     ap.add_argument("--defaults_config_path", default=os.path.join(HERE, "defaults.yaml"))
@@ -358,15 +369,51 @@ def main(argv: Optional[List[str]] = None) -> int:
     ap.add_argument("--no_overwrite", action="store_true", help="skip experiments that already have results")
     ap.add_argument("--log_nvidia_smi", action="store_true")
     ap.add_argument("--timeout", type=float, default=None, help="seconds per experiment")
+    # further options of the reference's runner (scripts/benchmarks/benchmark.py:1010-1110)
+    tf = lambda v: str(v).lower() in ("1", "true", "yes")  # noqa: E731
+    ap.add_argument("--max_seq_len_matrix", type=int, nargs="+", default=None, help="sequence lengths to multiply by")
+    ap.add_argument("--packing_matrix", type=tf, nargs="+", default=None, help="packing settings to multiply by")
+    ap.add_argument("--acceleration_framework_config_keypairs", nargs="+", default=None,
+                    help="short name / file pairs that replace the sample-configuration table")
+    ap.add_argument("--process_port", type=int, default=29511, help="first rendezvous port of multi-GPU experiments")
+    ap.add_argument("--dataset_save_path", default=None,
+                    help="directory with a tokenised cache made by data_processing.py (cache_bench.json)")
+    ap.add_argument("--no_data_processing", action="store_true", help="accepted: an existing cache is always kept")
+    ap.add_argument("--preload_models", action="store_true", help="resolve every model name before anything runs")
+    ap.add_argument("--log_memory_hf", action="store_true", help="record the allocator's peak memory")
+    ap.add_argument("--accelerate_config", default=None,
+                    help="accepted for call compatibility: ranks are launched with torch.distributed.run")
     a = ap.parse_args(argv)
 
     extra = {k: v for k, v in (("training_data_path", a.training_data_path), ("max_seq_length", a.max_seq_length),
                                ("max_steps", a.max_steps)) if v is not None}
-    if a.log_nvidia_smi:
+    if a.log_nvidia_smi or a.log_memory_hf:
         extra["skip_memory_metrics"] = False
+    if a.dataset_save_path and "training_data_path" not in extra:
+        cache = os.path.join(a.dataset_save_path, "cache_bench.json")
+        if os.path.isfile(cache):
+            extra["training_data_path"] = cache
+        else:
+            print(f"no tokenised cache at {cache}: experiments use synthetic packed documents", file=sys.stderr)
+    config_files = framework_config_files()
+    if a.acceleration_framework_config_keypairs:
+        pairs = a.acceleration_framework_config_keypairs
+        if len(pairs) % 2:
+            ap.error("--acceleration_framework_config_keypairs takes short name / file pairs")
+        config_files = dict(zip(pairs[0::2], pairs[1::2]))
     scenarios = load_scenarios(a.scenarios_config_path, a.run_only_scenarios)
+    if a.preload_models:
+        from ..models.builder import resolve_config
+
+        for sc in scenarios:
+            names = sc.arguments.get("model_name_or_path", [])
+            for name in names if isinstance(names, list) else [names]:
+                resolve_config(name)
+                print(f"scenario {sc.name!r}: model {name!r} resolves")
+    matrices = {"max_seq_length": a.max_seq_len_matrix, "packing": a.packing_matrix}
     exps = build_experiments(scenarios, load_defaults(a.defaults_config_path), a.num_gpus,
-                             a.effective_batch_size_matrix, a.results_output_path, framework_config_files(), extra)
+                             a.effective_batch_size_matrix, a.results_output_path, config_files, extra,
+                             base_port=a.process_port, matrices=matrices)
     os.makedirs(a.results_output_path, exist_ok=True)
     print(f"{len(exps)} experiments from {len(scenarios)} scenarios")
     for e in exps:

@@ -204,3 +204,35 @@ def test_trainer_cli_takes_the_reference_default_arguments(capsys):
     assert rc == 0
     text = capsys.readouterr().out
     assert "train_tokens_per_second" in text and "ignored arguments" not in text
+
+
+def test_runner_options_of_the_reference(tmp_path):
+    """Run-wide matrices (sequence lengths, packing), slow scenarios, short name / file pairs, flag aliases."""
+    scen = {"scenarios": [
+        {"name": "quick", "framework_config": [None, "mine"],
+         "arguments": {"model_name_or_path": ["tiny-llama"], "torch_dtype": "float32"}},
+        {"name": "heavy", "slow": True, "arguments": {"model_name_or_path": ["tiny-llama"], "packing": False}},
+    ]}
+    sp = tmp_path / "scenarios.yaml"
+    sp.write_text(yaml.safe_dump(scen))
+    cfg = tmp_path / "mine.yaml"
+    cfg.write_text("plugins: {}\n")
+    common = ["--effective_batch_size_matrix", "4", "--scenarios_config_path", str(sp), "--defaults_config_path", "",
+              "--dry_run", "--acceleration_framework_config_keypairs", "mine", str(cfg), "--accelerate_config", "unused.yaml",
+              "--no_data_processing", "--process_port", "29700", "--preload_models"]
+    out = tmp_path / "all"
+    assert B.main(["--num_gpus_matrix", "1", "--max_seq_len_matrix", "128", "256", "--packing_matrix", "True",
+                   "--results_output_path", str(out)] + common) == 0
+    runs = [json.load(open(out / d / B.FILE_ARGS)) for d in sorted(os.listdir(out)) if d.startswith("exp_")]
+    # the slow scenario is left out of an unfiltered run; 2 framework settings x 2 sequence lengths remain
+    assert len(runs) == 4 and {r["scenario"] for r in runs} == {"quick"}
+    assert sorted(r["arguments"]["max_seq_length"] for r in runs) == [128, 128, 256, 256]
+    assert all(r["arguments"]["packing"] is True for r in runs)
+    assert {r["framework_config"] for r in runs} == {None, "mine"}
+    assert any(str(cfg) in open(out / d / B.FILE_COMMAND).read() for d in os.listdir(out) if d.startswith("exp_"))
+    # named explicitly, the slow scenario runs; what it fixes itself is not varied
+    out2 = tmp_path / "named"
+    assert B.main(["--num_gpus", "1", "--packing_matrix", "True", "--run_only_scenarios", "heavy",
+                   "--results_output_path", str(out2)] + common) == 0
+    runs = [json.load(open(out2 / d / B.FILE_ARGS)) for d in sorted(os.listdir(out2)) if d.startswith("exp_")]
+    assert len(runs) == 1 and runs[0]["scenario"] == "heavy" and runs[0]["arguments"]["packing"] is False
