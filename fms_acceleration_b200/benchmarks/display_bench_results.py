@@ -64,25 +64,30 @@ def select_columns(rows: List[Dict[str, Any]], argument_columns: List[str], keep
 
 def main(argv: Optional[List[str]] = None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("result_dir")
+    ap.add_argument("result_dir", nargs="+", help="one or more result directories (their experiments are pooled)")
     ap.add_argument("--result_file", default=None)
     ap.add_argument("--keep_columns", nargs="*", default=[])
     ap.add_argument("--remove_columns", nargs="*", default=[])
     a = ap.parse_args(argv)
-    rows, failed = gather(a.result_dir)
+    rows, failed = [], []
+    for d in a.result_dir:
+        r, f = gather(d)
+        rows += r
+        failed += [(os.path.join(d, name), why) for name, why in f]
     for name, why in failed:
         print(f"{name}: {why}", file=sys.stderr)
     if not rows:
         print("no successful experiments", file=sys.stderr)
         return 1
     arg_cols = set()
-    for name in os.listdir(a.result_dir):
-        p = os.path.join(a.result_dir, name, "script.json")
-        if os.path.exists(p):
-            with open(p, encoding="utf-8") as fh:
-                arg_cols |= set(json.load(fh)["arguments"])
+    for d in a.result_dir:
+        for name in os.listdir(d):
+            p = os.path.join(d, name, "script.json")
+            if os.path.exists(p):
+                with open(p, encoding="utf-8") as fh:
+                    arg_cols |= set(json.load(fh)["arguments"])
     cols = select_columns(rows, sorted(arg_cols), a.keep_columns, a.remove_columns)
-    out = a.result_file or os.path.join(a.result_dir, "benchmarks.csv")
+    out = a.result_file or os.path.join(a.result_dir[0], "benchmarks.csv")
     with open(out, "w", newline="", encoding="utf-8") as fh:
         w = csv.DictWriter(fh, fieldnames=cols, extrasaction="ignore")
         w.writeheader()
