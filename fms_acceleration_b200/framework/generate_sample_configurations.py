@@ -151,7 +151,11 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", default=os.path.join(REPO_ROOT, "sample-configurations"))
     ap.add_argument("--check", action="store_true")
+    ap.add_argument("output_dir", nargs="?", default=None,
+                    help="where the files go: the positional form of --out, as the reference's script takes it")
     args = ap.parse_args(argv)
+    if args.output_dir:
+        args.out = args.output_dir
     files = generate()
     if args.check:
         bad = []
