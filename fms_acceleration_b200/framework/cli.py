@@ -2,8 +2,9 @@
 
 Verbs as in fms_acceleration/cli.py:36-213 of the reference.  All plugins ship in-tree here, so ``install`` only
 reports that (and can build the native library); ``plugins`` lists the plugins and whether they import;
-``configs`` lists the sample configurations from ``sample-configurations/CONTENTS.yaml``; ``arguments <shortname>``
-prints the framework arguments to use for a sample configuration.
+``configs`` lists the sample configurations from ``sample-configurations/CONTENTS.yaml``; ``arguments <shortname>...``
+prints the framework arguments that select a sample configuration and the benchmark scenarios (with their trainer
+arguments) that use it.
 """
 from __future__ import annotations
 
@@ -92,16 +93,36 @@ def list_sample_configs() -> int:
     return 0
 
 
-def list_arguments(config_shortname: str) -> int:
-    for c in _read_contents():
-        if c["shortname"] == config_shortname:
+def list_arguments(*config_shortnames: str, scenario_file: str = None, ignored_fields=None) -> int:
+    """For every sample configuration named: the framework arguments that select it, then (as the reference's verb
+    prints, fms_acceleration/cli.py:139-186) the benchmark scenarios that use it with their trainer arguments."""
+    ignored_fields = ["model_name_or_path"] if ignored_fields is None else ignored_fields
+    contents = {c["shortname"]: c for c in _read_contents()}
+    unknown = [n for n in config_shortnames if n not in contents]
+    for name in unknown:
+        print(f"no sample configuration with shortname '{name}'; see the `configs` verb")
+    for name in config_shortnames:
+        if name in contents:
+            c = contents[name]
             path = os.path.join(os.path.dirname(CONTENTS), c["filename"])
             print(f"--acceleration_framework_config_file {path}")
             print(f"(or: export ACCELERATION_FRAMEWORK_CONFIG_FILE={path})")
             print("required plugins: " + ", ".join(c["plugins"]))
-            return 0
-    print(f"no sample configuration with shortname '{config_shortname}'; see the `configs` verb")
-    return 1
+    scenario_file = scenario_file or os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+                                                  "benchmarks", "scenarios.yaml")
+    found = 0
+    if os.path.isfile(scenario_file):
+        with open(scenario_file, encoding="utf-8") as fh:
+            scenarios = yaml.safe_load(fh)["scenarios"]
+        for scn in scenarios:
+            hits = [n for n in config_shortnames if n in (scn.get("framework_config") or [])]
+            if not hits:
+                continue
+            found += 1
+            print(f"{found}. scenario: {scn['name']}\n   configs: {', '.join(hits)}\n   arguments:")
+            lines = [f"      --{k} {v}" for k, v in (scn.get("arguments") or {}).items() if k not in ignored_fields]
+            print(" \\\n".join(lines) + "\n")
+    return 1 if unknown else 0
 
 
 def cli(argv=None) -> int:
@@ -112,16 +133,30 @@ def cli(argv=None) -> int:
     p.add_argument("--build", action="store_true", help="(re)build the native CUDA/C++ library")
     sub.add_parser("plugins", help="list plugins")
     sub.add_parser("configs", help="list sample configurations")
-    p = sub.add_parser("arguments", help="print the arguments for a sample configuration")
-    p.add_argument("config_shortname")
-    a = ap.parse_args(argv)
+    p = sub.add_parser("arguments", help="print the arguments for one or more sample configurations")
+    p.add_argument("config_shortname", nargs="+")
+    a, extra = ap.parse_known_args(argv)
     if a.verb == "install":
-        return install(a.plugin, a.build)
+        # pip-style flags of the reference's verb (-e, --no-deps, ...) have nothing to act on here
+        flags = [x for x in extra if x.startswith("-")]
+        names = [x for x in extra if not x.startswith("-")]
+        if a.plugin is None and len(names) == 1:
+            a.plugin = os.path.basename(names.pop().rstrip("/"))
+        if names:
+            ap.error("Please specify exactly one plugin to install")
+        if flags:
+            print(f"ignored installer flags: {' '.join(flags)}")
+        plugin = a.plugin
+        if plugin is not None:
+            plugin = os.path.basename(plugin.rstrip("/")).replace("fms_acceleration_", "").replace("fms-acceleration-", "")
+        return install(plugin, a.build)
+    if extra:
+        ap.error(f"unrecognized arguments: {' '.join(extra)}")
     if a.verb == "plugins":
         return list_plugins()
     if a.verb == "configs":
         return list_sample_configs()
-    return list_arguments(a.config_shortname)
+    return list_arguments(*a.config_shortname)
 
 
 if __name__ == "__main__":

@@ -516,3 +516,19 @@ def test_auto_categorizer_cluster_options():
     assert len(set(labels[:10])) == 1 and len(set(labels[10:])) == 1 and labels[0] != labels[10]
     with pytest.raises(ValueError, match="kmeans"):
         DatasetAutoCategorizer(AutoCategorizeConfig(cluster_algo="dbscan"))._cluster(emb, 2)
+
+
+def test_cli_verbs(capsys):
+    from fms_acceleration.cli import cli
+
+    assert cli(["install", "-e", "plugins/accelerated-peft", "--no-deps"]) == 0
+    assert "ignored installer flags: -e --no-deps" in capsys.readouterr().out
+    assert cli(["install", "no-such-plugin"]) != 0
+    assert cli(["plugins"]) == 0 and "accelerated-moe" in capsys.readouterr().out
+    assert cli(["configs"]) == 0 and "accelerated-peft-bnb" in capsys.readouterr().out
+    assert cli(["arguments", "accelerated-peft-bnb"]) == 0
+    text = capsys.readouterr().out
+    # the arguments that select the configuration, then the scenarios that use it with their trainer arguments
+    assert "--acceleration_framework_config_file" in text and "scenario: accelerated-peft-bnb" in text
+    assert "--peft_method lora" in text and "model_name_or_path" not in text.split("arguments:")[1]
+    assert cli(["arguments", "no-such-config"]) == 1
