@@ -69,3 +69,18 @@ def test_truncated_shard_is_detected(tmp_path):
     fresh = _make(False, str(tmp_path / "x"))
     with pytest.raises(RuntimeError, match="incomplete or damaged"):
         fresh.load_checkpoint(os.path.join(out, "checkpoint-3"))
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_full_state_dict_of_rank_zero_reaches_every_rank(world):
+    """``fsdp2_load_full_state_dict`` / ``load_experts_onto_device`` on gloo ranks: replicated parameters arrive whole,
+    expert-parallel ones as each rank's slice."""
+    import subprocess
+    import sys
+
+    here = os.path.dirname(os.path.abspath(__file__))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29670 + world), os.path.join(here, "dist_worker_state_loading.py")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, MASTER_ADDR="127.0.0.1"))
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    assert "STATE_LOADING_OK" in out.stdout
