@@ -49,6 +49,20 @@ def main():
     (y * g).sum().backward()
     (ref * g).sum().backward()
     assert torch.allclose(x.grad, ref_x.grad, atol=1e-4), (x.grad - ref_x.grad).abs().max()
+    # the differentiable variable-split all-to-all under its MegaBlocks name: rank r sends (r + d + 1) rows to rank d;
+    # the backward brings every row's gradient back to where the row came from
+    from fms_acceleration_b200.plugins.moe.utils.scattermoe_utils.megablocks import all_to_all
+
+    send = [rank + d + 1 for d in range(world)]
+    recv = [s + rank + 1 for s in range(world)]
+    rows = torch.cat([torch.full((n, 3), float(100 * rank + d)) for d, n in enumerate(send)]).requires_grad_()
+    got, handle = all_to_all(rows, recv, send, dist.group.WORLD)
+    assert handle is None and got.shape == (sum(recv), 3)
+    want_rows = torch.cat([torch.full((n, 3), float(100 * s + rank)) for s, n in enumerate(recv)])
+    assert torch.equal(got, want_rows)
+    (got * float(rank + 1)).sum().backward()  # the receiver scales by its rank + 1
+    want_grad = torch.cat([torch.full((n, 3), float(d + 1)) for d, n in enumerate(send)])
+    assert torch.equal(rows.grad, want_grad)
     dist.barrier()
     if rank == 0:
         print("EP_BASELINE_OK")
