@@ -140,3 +140,12 @@ def test_plugin_rewrites_eval_schedule(tmp_path):
         fw.augmentation(model, args, modifiable_args=(None,))
         assert model.ta_eval_steps == 50 and args.eval_steps == 1 and args.eval_strategy == "steps"
         assert model.ta_update_interval == 1
+
+
+def test_custom_training_loop_example_runs(capsys):
+    """The hand-written loop of the artifacts folder (mixing dataset + plain DataLoader + periodic bandit update)."""
+    from fms_acceleration_b200.plugins.odm.artifacts import custom_loop_usage
+
+    assert custom_loop_usage.main(["--steps", "12", "--batch", "2"]) == 0
+    out = capsys.readouterr().out
+    assert "step 10:" in out and "sampling ratio" in out
