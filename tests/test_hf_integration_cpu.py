@@ -66,6 +66,75 @@ def test_foak_patches_hf_llama_and_keeps_the_numbers(fast_loss):
         importlib.reload(ml)
 
 
+def _tiny_hf(family):
+    """A two-layer model of ``family``, its class taken from the modelling module as it is now."""
+    common = dict(vocab_size=512, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2)
+    if family == "mistral":
+        from transformers import MistralConfig as C
+        from transformers.models.mistral.modeling_mistral import MistralForCausalLM as M
+
+        cfg = C(intermediate_size=128, architectures=["MistralForCausalLM"], **common)
+    elif family == "granite":
+        from transformers import GraniteConfig as C
+        from transformers.models.granite.modeling_granite import GraniteForCausalLM as M
+
+        cfg = C(intermediate_size=128, architectures=["GraniteForCausalLM"], logits_scaling=4.0, embedding_multiplier=3.0,
+                residual_multiplier=0.5, attention_multiplier=0.1, **common)
+    elif family == "mixtral":
+        from transformers import MixtralConfig as C
+        from transformers.models.mixtral.modeling_mixtral import MixtralForCausalLM as M
+
+        cfg = C(intermediate_size=96, num_local_experts=4, num_experts_per_tok=2, architectures=["MixtralForCausalLM"],
+                **common)
+    else:
+        from transformers import GraniteMoeConfig as C
+        from transformers.models.granitemoe.modeling_granitemoe import GraniteMoeForCausalLM as M
+
+        cfg = C(intermediate_size=96, num_local_experts=4, num_experts_per_tok=2, architectures=["GraniteMoeForCausalLM"],
+                **common)
+    torch.manual_seed(0)
+    return M(cfg)
+
+
+@pytest.mark.parametrize("family", ["mistral", "granite", "mixtral", "granitemoe"])
+@pytest.mark.parametrize("fast_loss", [True, "fused_ce_liger"])
+def test_foak_rules_of_the_other_families_keep_the_numbers(family, fast_loss):
+    """RMSNorm, rotary embedding and loss rules on the Hugging Face classes of every family that has them: the
+    rules apply, and loss and gradients equal the unpatched model's (Granite's logit scaling included)."""
+    model = _tiny_hf(family)
+    ref = copy.deepcopy(model)
+    ids = torch.randint(0, 512, (2, 24))
+    cfg = {"training": {"fused_ops_and_kernels": {"fused_lora": False, "fast_loss": fast_loss, "fast_rms_layernorm": True,
+                                                 "fast_rope_embeddings": True}}}
+    saved_rules, saved_hist = dict(ModelPatcher.rules), list(ModelPatcher.history)
+    try:
+        with instantiate_framework(cfg, require_packages_check=False) as fw:
+            model, _ = fw.augmentation(model, TrainArgs(bf16=False), modifiable_args=(None,))
+            fw.get_callbacks_and_ready_for_train(model, None)
+            ModelPatcher.patch(model)
+            applied = {h.rule_id for h in ModelPatcher.history}
+            loss_rule = f"{family}-fused-lce" if fast_loss == "fused_ce_liger" else f"{family}-custom-loss"
+            assert {f"{family}-rms", f"{family}-rope", loss_rule} <= applied, applied
+            model.train()
+            ref.train()
+            out, want = model(input_ids=ids, labels=ids), ref(input_ids=ids, labels=ids)
+            assert torch.allclose(out.loss, want.loss, atol=1e-5, rtol=1e-5)
+            out.loss.backward()
+            want.loss.backward()
+            got = {n: p.grad for n, p in model.named_parameters() if p.grad is not None}
+            exp = {n: p.grad for n, p in ref.named_parameters() if p.grad is not None}
+            assert set(got) == set(exp)
+            for n in exp:
+                assert torch.allclose(got[n], exp[n], atol=1e-5, rtol=1e-3), n
+    finally:
+        ModelPatcher.rules.clear()
+        ModelPatcher.rules.update(saved_rules)
+        ModelPatcher.history[:] = saved_hist
+        import importlib
+
+        importlib.reload(importlib.import_module(type(ref).__module__))
+
+
 @pytest.mark.parametrize("family", ["granitemoe", "mixtral"])
 def test_scattermoe_swaps_hf_moe_blocks_exactly_and_converts_back(family):
     """The module swap works on the installed transformers' MoE classes (fused 3-D expert parameters and hidden-only
