@@ -50,6 +50,28 @@ def _check_operand(t: torch.Tensor, name: str) -> None:
         raise ValueError(f"{name}: leading dimension must be a multiple of 8 elements and 16-byte aligned")
 
 
+def _gemm_host(a, b, a_mn, b_mn, a2, b2, c, alpha, beta, out, out_dtype):
+    """The contract of :func:`gemm` stated with torch operators for tensors that live on the host (any floating
+    dtype, fp32 accumulation): ``out = alpha * (op(a) op(b) + op(a2) op(b2)) + beta * c`` with ``op(a) = a^T`` when
+    ``a_mn`` and ``op(b) = b`` when ``b_mn`` (else ``b^T``).  What the CPU tests of the layers above run on; a tensor
+    on a GPU never comes here."""
+    def prod(x, y):
+        x = (x.t() if a_mn else x).float()
+        y = (y if b_mn else y.t()).float()
+        return x @ y
+
+    acc = prod(a, b)
+    if a2 is not None:
+        acc = acc + prod(a2, b2)
+    acc = acc * alpha
+    if c is not None and beta != 0.0:
+        acc = acc + beta * c.float()
+    if out is None:
+        return acc.to(out_dtype or a.dtype)
+    out.copy_(acc)
+    return out
+
+
 def gemm(
     a: torch.Tensor,
     b: torch.Tensor,
@@ -66,6 +88,8 @@ def gemm(
     bn: int | None = None,
     max_ctas: int = 0,
 ) -> torch.Tensor:
+    if not a.is_cuda:
+        return _gemm_host(a, b, a_mn, b_mn, a2, b2, c, alpha, beta, out, out_dtype)
     if a.dtype not in (torch.bfloat16, torch.float16) or b.dtype != a.dtype:
         raise TypeError("gemm operands must both be bf16 or both fp16")
     _check_operand(a, "a")

@@ -202,7 +202,11 @@ def quantize_4bit(w: torch.Tensor, quant_type: str = "nf4", blocksize: int = 64,
 def dequantize_4bit(qs: Quant4State, dtype: torch.dtype | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
     dtype = dtype or qs.dtype
     if not qs.packed.is_cuda:
-        return dequantize_4bit_ref(qs, dtype)
+        dense = dequantize_4bit_ref(qs, dtype)
+        if out is None:
+            return dense
+        out.copy_(dense.view(out.shape))
+        return out
     n = qs.numel
     if out is None:
         out = torch.empty(qs.shape, dtype=dtype, device=qs.packed.device)
@@ -235,7 +239,11 @@ def gptq_dequant(qweight, scales, qzeros, g_idx, bits: int, group_size: int, zer
     if not qweight.is_cuda:
         if g_idx is None:
             g_idx = torch.arange(in_features, device=qweight.device) // group_size
-        return gptq_dequant_ref(qweight, scales, qzeros, g_idx, bits, zero_offset)
+        dense = gptq_dequant_ref(qweight, scales, qzeros, g_idx, bits, zero_offset)
+        if out is None:
+            return dense
+        out.copy_(dense)
+        return out
     if out is None:
         out = torch.empty(in_features, out_features, dtype=scales.dtype, device=qweight.device)
     elif out.shape != (in_features, out_features) or out.stride(1) != 1 or out.dtype != scales.dtype:

@@ -255,3 +255,67 @@ def test_hf_mamba_layers_swap_to_the_in_tree_mixer(family):
     after = model.state_dict()
     assert sorted(after) == sorted(before) and all(torch.equal(after[k], before[k]) for k in before)
     assert not model.load_state_dict(before).missing_keys
+
+
+@pytest.mark.parametrize("base", ["bitsandbytes", "auto_gptq"])
+def test_fused_lora_rules_on_a_quantised_hf_llama_keep_the_numbers(base):
+    """LoRA adapters over 4-bit (NF4 / GPTQ) base layers inside a Hugging Face Llama: the fused attention and MLP
+    rules fire (one projection group per fused op, the first projection called computes the group and the others read
+    their slice), and loss and every adapter gradient equal the unfused model's."""
+    from transformers import LlamaConfig
+    from transformers.models.llama.modeling_llama import LlamaForCausalLM
+
+    from fms_acceleration_b200.models.builder import quantize_linears_
+    from fms_acceleration_b200.nn import Linear4bit, LoraConfig, get_peft_model
+    from fms_acceleration_b200.nn.gptq import QuantLinear
+
+    cfg = LlamaConfig(vocab_size=512, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, architectures=["LlamaForCausalLM"])
+    torch.manual_seed(0)
+    model = LlamaForCausalLM(cfg)
+
+    def four_bit(lin):
+        if base == "bitsandbytes":
+            return Linear4bit.from_linear(lin, "nf4", 64, torch.float32)
+        return QuantLinear.random(lin.in_features, lin.out_features, group_size=32, dtype=torch.float32)
+
+    for layer in model.model.layers:
+        quantize_linears_(layer, four_bit)
+    model = get_peft_model(model, LoraConfig(r=4, lora_alpha=8, lora_dropout=0.0, target_modules=[
+        "q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"]))
+    for name, p in model.named_parameters():
+        if "lora_B" in name:
+            torch.nn.init.normal_(p, std=0.05)
+    model.quantization_method = "bitsandbytes" if base == "bitsandbytes" else "gptq"
+    ref = copy.deepcopy(model)
+    ids = torch.randint(0, 512, (2, 24))
+    conf = {"peft": {"quantization": {"fused_ops_and_kernels": {"base_layer": base, "fused_lora": True, "fast_loss": True,
+                                                               "fast_rms_layernorm": True, "fast_rope_embeddings": True}}}}
+    saved_rules, saved_hist = dict(ModelPatcher.rules), list(ModelPatcher.history)
+    try:
+        with instantiate_framework(conf, require_packages_check=False) as fw:
+            model, _ = fw.augmentation(model, TrainArgs(bf16=True), modifiable_args=(None,))
+            fw.get_callbacks_and_ready_for_train(model, None)
+            ModelPatcher.patch(model)
+            applied = {h.rule_id for h in ModelPatcher.history}
+            assert "llama-mlp" in applied and any(r.startswith("llama-qkvo") for r in applied), applied
+            model.train()
+            ref.train()
+            out, want = model(input_ids=ids, labels=ids), ref(input_ids=ids, labels=ids)
+            assert torch.allclose(out.loss, want.loss, atol=1e-6)
+            out.loss.backward()
+            want.loss.backward()
+            got = {n: p.grad for n, p in model.named_parameters() if p.grad is not None}
+            exp = {n: p.grad for n, p in ref.named_parameters() if p.grad is not None}
+            assert set(got) == set(exp) and len(exp) == 28  # 7 projections x 2 layers x (A, B)
+            for n in exp:
+                assert torch.allclose(got[n], exp[n], atol=1e-6, rtol=1e-4), n
+    finally:
+        ModelPatcher.rules.clear()
+        ModelPatcher.rules.update(saved_rules)
+        ModelPatcher.history[:] = saved_hist
+        import importlib
+
+        import transformers.models.llama.modeling_llama as ml
+
+        importlib.reload(ml)

@@ -85,3 +85,23 @@ def test_context_parallel_prefix_state_and_its_gradients():
         assert torch.allclose(dF.double(), gF, rtol=1e-4, atol=1e-5)
         assert torch.allclose(dlP.double(), glP, rtol=1e-4, atol=1e-5)
         assert torch.count_nonzero(dF[r:]) == 0 and torch.count_nonzero(dlP[r:]) == 0
+
+
+def test_gemm_host_statement_of_the_kernel_contract():
+    """On host tensors ``gemm`` is stated with torch operators: both operand orientations, the second operand pair,
+    ``alpha`` / ``beta * c`` and an ``out`` buffer."""
+    import torch
+
+    from fms_acceleration_b200.ops.gemm import gemm
+
+    torch.manual_seed(0)
+    a, b = torch.randn(5, 7), torch.randn(3, 7)           # b is [N, K] unless b_mn
+    assert torch.allclose(gemm(a, b), a @ b.t(), atol=1e-6)
+    assert torch.allclose(gemm(a, b.t().contiguous(), b_mn=True), a @ b.t(), atol=1e-6)
+    assert torch.allclose(gemm(a.t().contiguous(), b, a_mn=True), a @ b.t(), atol=1e-6)
+    a2, b2, c = torch.randn(5, 2), torch.randn(3, 2), torch.randn(5, 3)
+    want = 0.5 * (a @ b.t() + a2 @ b2.t()) + 2.0 * c
+    out = torch.empty(5, 3)
+    assert gemm(a, b, a2=a2, b2=b2, c=c, alpha=0.5, beta=2.0, out=out) is out
+    assert torch.allclose(out, want, atol=1e-6)
+    assert gemm(a.bfloat16(), b.bfloat16(), out_dtype=torch.float32).dtype == torch.float32
