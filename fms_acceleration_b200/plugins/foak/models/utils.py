@@ -45,11 +45,26 @@ class _GroupFn(torch.autograd.Function):
         return (dx, None, *grads)
 
 
+def _group_bias(group: ProjGroup, dtype, device):
+    """The biases of the group's base layers side by side (zeros for a layer without one), or None when no layer has
+    a bias.  Added after the fused product, as the reference's fused functions do
+    (fused_ops/unsloth_lora/bnb/fast_lora.py:72-76); a bias that is trained takes its gradient through this sum."""
+    biases = [getattr(b, "bias", None) for b in group.bases]
+    if all(b is None for b in biases):
+        return None
+    parts = [b.to(dtype) if b is not None else torch.zeros(n, dtype=dtype, device=device)
+             for b, n in zip(biases, group.out_sizes)]
+    return parts[0] if len(parts) == 1 else torch.cat(parts)
+
+
 def _run_group(group: ProjGroup, x: torch.Tensor) -> torch.Tensor:
     x2 = x.reshape(-1, x.shape[-1])
     if x2.stride(1) != 1 or x2.stride(0) % 8:
         x2 = x2.contiguous()
     y = _GroupFn.apply(x2, group, *group.trainable())
+    bias = _group_bias(group, y.dtype, y.device)
+    if bias is not None:
+        y = y + bias
     return y.view(*x.shape[:-1], y.shape[-1])
 
 

@@ -257,8 +257,9 @@ def test_hf_mamba_layers_swap_to_the_in_tree_mixer(family):
     assert not model.load_state_dict(before).missing_keys
 
 
+@pytest.mark.parametrize("with_bias", [False, True])
 @pytest.mark.parametrize("base", ["bitsandbytes", "auto_gptq"])
-def test_fused_lora_rules_on_a_quantised_hf_llama_keep_the_numbers(base):
+def test_fused_lora_rules_on_a_quantised_hf_llama_keep_the_numbers(base, with_bias):
     """LoRA adapters over 4-bit (NF4 / GPTQ) base layers inside a Hugging Face Llama: the fused attention and MLP
     rules fire (one projection group per fused op, the first projection called computes the group and the others read
     their slice), and loss and every adapter gradient equal the unfused model's."""
@@ -270,14 +271,22 @@ def test_fused_lora_rules_on_a_quantised_hf_llama_keep_the_numbers(base):
     from fms_acceleration_b200.nn.gptq import QuantLinear
 
     cfg = LlamaConfig(vocab_size=512, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
-                      num_key_value_heads=2, architectures=["LlamaForCausalLM"])
+                      num_key_value_heads=2, architectures=["LlamaForCausalLM"], attention_bias=with_bias,
+                      mlp_bias=with_bias)
     torch.manual_seed(0)
     model = LlamaForCausalLM(cfg)
+    if with_bias:
+        for name, p in model.named_parameters():
+            if name.endswith("proj.bias"):
+                torch.nn.init.normal_(p, std=0.5)  # large enough that a dropped bias cannot go unnoticed
 
     def four_bit(lin):
         if base == "bitsandbytes":
             return Linear4bit.from_linear(lin, "nf4", 64, torch.float32)
-        return QuantLinear.random(lin.in_features, lin.out_features, group_size=32, dtype=torch.float32)
+        q = QuantLinear.random(lin.in_features, lin.out_features, group_size=32, dtype=torch.float32)
+        if lin.bias is not None:
+            q.bias = lin.bias.data.clone()
+        return q
 
     for layer in model.model.layers:
         quantize_linears_(layer, four_bit)
