@@ -33,15 +33,16 @@ class _GroupFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x2, group: ProjGroup, *params):
-        y, xa = group.forward(x2)
-        ctx.group = group
+        aux = {}  # receives the keep mask when the adapters have input dropout
+        y, xa = group.forward(x2, aux=aux)
+        ctx.group, ctx.aux = group, aux
         ctx.save_for_backward(x2, xa)
         return y
 
     @staticmethod
     def backward(ctx, dy):
         x2, xa = ctx.saved_tensors
-        dx, grads = ctx.group.backward(dy.contiguous(), x2, xa, need_dx=ctx.needs_input_grad[0])
+        dx, grads = ctx.group.backward(dy.contiguous(), x2, xa, need_dx=ctx.needs_input_grad[0], aux=ctx.aux)
         return (dx, None, *grads)
 
 

@@ -328,3 +328,60 @@ def test_fused_lora_rules_on_a_quantised_hf_llama_keep_the_numbers(base, with_bi
         import transformers.models.llama.modeling_llama as ml
 
         importlib.reload(ml)
+
+
+@pytest.mark.parametrize("kind", ["nf4", "gptq", "dense"])
+def test_projection_group_with_lora_dropout_matches_the_written_out_formula(kind):
+    """``y = x W^T + b + s (dropout(x) A^T) B^T`` per projection: the group's autograd function keeps the dropout mask
+    of its forward for its backward, the base branch sees ``x`` and the adapter branch the dropped-out ``x``."""
+    from fms_acceleration_b200.nn import Linear4bit
+    from fms_acceleration_b200.nn.gptq import QuantLinear
+    from fms_acceleration_b200.nn.lora import LoraLinear
+    from fms_acceleration_b200.ops.proj import ProjGroup
+    from fms_acceleration_b200.plugins.foak.models.utils import _run_group
+
+    torch.manual_seed(0)
+    p, layers, weights = 0.25, [], []
+    for out_features in (32, 16):
+        lin = torch.nn.Linear(64, out_features, bias=True)
+        if kind == "nf4":
+            base = Linear4bit.from_linear(lin, "nf4", 64, torch.float32)
+            weights.append(base.dequantize(dtype=torch.float32))
+        elif kind == "gptq":
+            base = QuantLinear.random(64, out_features, group_size=32, dtype=torch.float32, scale_std=0.05)
+            base.bias = lin.bias.data.clone()
+            weights.append(base.dequantize(dtype=torch.float32).t())
+        else:
+            base = lin
+            base.weight.requires_grad_(False)
+            weights.append(lin.weight.data)
+        lora = LoraLinear(base, r=4, lora_alpha=8, lora_dropout=p)
+        torch.nn.init.normal_(lora.lora_B["default"].weight, std=0.1)
+        layers.append(lora.train())
+    group = ProjGroup(layers, "dropout-test")
+    x = torch.randn(6, 64, requires_grad=True)
+
+    torch.manual_seed(11)
+    y = _run_group(group, x)
+    torch.manual_seed(11)
+    keep = (torch.rand(x.shape) >= p).float() / (1.0 - p)  # the first random draw of the forward
+    x_ref = x.detach().clone().requires_grad_()
+    outs = []
+    for lora, W in zip(layers, weights):
+        A, B = lora.lora_A["default"].weight, lora.lora_B["default"].weight
+        bias = lora.base_layer.bias
+        outs.append(x_ref @ W.t() + bias + lora.scaling["default"] * ((x_ref * keep) @ A.t()) @ B.t())
+    want = torch.cat(outs, dim=-1)
+    assert torch.allclose(y, want, atol=1e-5)
+
+    g = torch.randn_like(y)
+    params = [t for lora in layers for t in (lora.lora_A["default"].weight, lora.lora_B["default"].weight)]
+    got = torch.autograd.grad(y, [x] + params, g)
+    exp = torch.autograd.grad(want, [x_ref] + params, g)
+    for a, b in zip(got, exp):
+        assert torch.allclose(a, b, atol=1e-5, rtol=1e-4)
+    # in eval mode nothing is dropped
+    for lora in layers:
+        lora.eval()
+    plain = torch.cat([lora(x) for lora in layers], dim=-1)
+    assert torch.allclose(_run_group(group, x), plain, atol=1e-5)
