@@ -133,7 +133,17 @@ def prepare_scattermoe(model: nn.Module, checkpoint_name_or_path: Optional[str] 
         del module
     if not swapped:
         warnings.warn(f"no '{moe_cls}' module found: nothing was converted to ScatterMoE")
-    return swapped
+    return SwappedModules(swapped)
+
+
+class SwappedModules(set):
+    """What :func:`prepare_scattermoe` returns: the attribute names of the replaced blocks inside their decoder layer
+    (e.g. ``{"block_sparse_moe"}``, the set the reference returns, scattermoe_prepare.py:223,347,355, so that
+    ``getattr(layer, name)`` finds them), with the full dotted path of every replaced module in ``paths``."""
+
+    def __init__(self, paths):
+        super().__init__(p.rpartition(".")[2] for p in paths)
+        self.paths = list(paths)
 
 
 def load_experts_onto_device(module: nn.Module, state_dict, device_mesh=None, num_experts_per_device: Optional[int] = None):

@@ -157,7 +157,8 @@ def test_scattermoe_swaps_hf_moe_blocks_exactly_and_converts_back(family):
     ids = torch.randint(0, 512, (2, 16))
     ref = model(input_ids=ids, labels=ids).loss
     swapped = prepare_scattermoe(model, None, 0, 1, 1)
-    assert len(swapped) == 2
+    # the attribute name of the block inside its layer depends on the transformers version
+    assert len(swapped.paths) == 2 and len(swapped) == 1 and swapped <= {"block_sparse_moe", "mlp"}
     assert abs(model(input_ids=ids, labels=ids).loss.item() - ref.item()) < 1e-5
     sd = CU.recover_original_state_dict_from_checkpoint(dict(model.state_dict()),
                                                         weight_map={k: "model.safetensors" for k in original},

@@ -67,7 +67,7 @@ def test_swap_is_exact_and_converts_back(tmp_path):
     ids = torch.randint(0, 1024, (2, 48))
     ref = model(ids, labels=ids).loss
     swapped = prepare_scattermoe(model, None, 0, 1, 1)
-    assert len(swapped) == 2
+    assert len(swapped.paths) == 2 and swapped == {"block_sparse_moe"}
     assert abs(model(ids, labels=ids).loss.item() - ref.item()) < 1e-5
     # ScatterMoE state -> original Hugging Face layout
     wm = {k: "model.safetensors" for k in original}
@@ -131,7 +131,7 @@ def test_swap_other_families(name, arch):
     cu = torch.tensor([0, 16, 40], dtype=torch.int32)
     ref = model(ids, labels=ids, cu_seqlens=cu).loss
     swapped = prepare_scattermoe(model, None, 0, 1, 1)
-    assert len(swapped) == model.config.num_hidden_layers
+    assert len(swapped.paths) == model.config.num_hidden_layers
     assert abs(model(ids, labels=ids, cu_seqlens=cu).loss.item() - ref.item()) < 1e-5
     sd = CU.recover_original_state_dict_from_checkpoint(dict(model.state_dict()),
                                                         weight_map={k: "model.safetensors" for k in original},
