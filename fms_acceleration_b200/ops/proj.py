@@ -151,6 +151,20 @@ class ProjGroup:
                 return p
         return 0.0
 
+    def dropout_module(self):
+        """A dropout module other than ``nn.Dropout`` / ``nn.Identity`` on the group's adapters while training (e.g. one
+        that applies a fixed mask), else None.  Such a module is asked once for its element-wise factor,
+        ``module(ones_like(x))``, which then serves the whole group (the reference calls the module on the input and
+        reads the mask back from the zeros, fused_ops/unsloth_lora/bnb/fast_lora.py:262-288, 339-352)."""
+        for l in self.loras:
+            if l is None or not l.training or not hasattr(l, "lora_dropout"):
+                continue
+            name = l.active_adapters[0] if hasattr(l, "active_adapters") else "default"
+            d = l.lora_dropout[name]
+            if not isinstance(d, (nn.Dropout, nn.Identity)):
+                return d
+        return None
+
     def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                 aux: Optional[dict] = None):
         """x [T, in] -> (y [T, total_out], xa [T, R] or None).  ``residual`` is added in the GEMM epilogue.
@@ -162,7 +176,13 @@ class ProjGroup:
         if self.has_lora:
             A_cat, B_blk, _ = self.lora_cat(dtype, dev)
             p = self.dropout_p()
-            if p > 0.0:
+            custom = self.dropout_module()
+            if custom is not None:
+                if aux is None:
+                    raise ValueError("LoRA dropout is active: pass an `aux` dict to keep the mask for the backward")
+                aux["mask"], aux["keep_scale"] = custom(torch.ones_like(x)), 1.0
+                xa = gemm(x * aux["mask"], A_cat)
+            elif p > 0.0:
                 if aux is None:
                     raise ValueError("LoRA dropout is active: pass an `aux` dict to keep the mask for the backward")
                 mask = torch.rand(x.shape, device=dev) >= p

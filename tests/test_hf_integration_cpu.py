@@ -386,3 +386,40 @@ def test_projection_group_with_lora_dropout_matches_the_written_out_formula(kind
         lora.eval()
     plain = torch.cat([lora(x) for lora in layers], dim=-1)
     assert torch.allclose(_run_group(group, x), plain, atol=1e-5)
+
+
+def test_projection_group_honours_a_user_supplied_dropout_module():
+    """A dropout module that is not ``nn.Dropout`` (here: a fixed mask, as the reference's own fused-ops test installs on
+    every adapter) gives the same output and gradients fused and unfused."""
+    from fms_acceleration_b200.nn import Linear4bit
+    from fms_acceleration_b200.nn.lora import LoraLinear
+    from fms_acceleration_b200.ops.proj import ProjGroup
+    from fms_acceleration_b200.plugins.foak.models.utils import _run_group
+
+    class FixedMask(torch.nn.Module):
+        mask = None
+
+        def forward(self, x):
+            return x * FixedMask.mask
+
+    torch.manual_seed(3)
+    FixedMask.mask = (torch.rand(6, 64) >= 0.3).float()
+    layers = []
+    for out_features in (32, 16, 16):
+        base = Linear4bit.from_linear(torch.nn.Linear(64, out_features, bias=False), "nf4", 64, torch.float32)
+        lora = LoraLinear(base, r=4, lora_alpha=8)
+        lora.lora_dropout = torch.nn.ModuleDict({"default": FixedMask()})
+        torch.nn.init.normal_(lora.lora_B["default"].weight, std=0.1)
+        layers.append(lora.train())
+    group = ProjGroup(layers, "fixed-mask")
+    x = torch.randn(6, 64, requires_grad=True)
+    x_ref = x.detach().clone().requires_grad_()
+    y = _run_group(group, x)
+    want = torch.cat([lora(x_ref) for lora in layers], dim=-1)
+    assert torch.allclose(y, want, atol=1e-5)
+    params = [t for lora in layers for t in (lora.lora_A["default"].weight, lora.lora_B["default"].weight)]
+    g = torch.randn_like(y)
+    got = torch.autograd.grad(y, [x] + params, g)
+    exp = torch.autograd.grad(want, [x_ref] + params, g)
+    for a, b in zip(got, exp):
+        assert torch.allclose(a, b, atol=1e-5, rtol=1e-4)
