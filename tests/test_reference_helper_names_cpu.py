@@ -532,3 +532,36 @@ def test_cli_verbs(capsys):
     assert "--acceleration_framework_config_file" in text and "scenario: accelerated-peft-bnb" in text
     assert "--peft_method lora" in text and "model_name_or_path" not in text.split("arguments:")[1]
     assert cli(["arguments", "no-such-config"]) == 1
+
+
+def test_apply_lora_entry_points_equal_the_unfused_projections():
+    """``apply_lora_qkv / _o / _mlp_*`` of the bnb flavour on modules whose projections are LoRA over NF4 layers with
+    biases: each fused call equals the projections applied one by one."""
+    from fms_acceleration_foak.fused_ops.unsloth_lora.bnb.fast_lora import (apply_lora_mlp_geglu_approx,
+                                                                           apply_lora_mlp_geglu_exact,
+                                                                           apply_lora_mlp_swiglu, apply_lora_o,
+                                                                           apply_lora_qkv)
+    from fms_acceleration_b200.nn import Linear4bit
+    from fms_acceleration_b200.nn.lora import LoraLinear
+
+    torch.manual_seed(0)
+
+    def proj(i, o):
+        layer = LoraLinear(Linear4bit.from_linear(torch.nn.Linear(i, o, bias=True), "nf4", 64, torch.float32), r=4,
+                           lora_alpha=8)
+        torch.nn.init.normal_(layer.lora_B["default"].weight, std=0.1)
+        return layer
+
+    attn, mlp = torch.nn.Module(), torch.nn.Module()
+    attn.q_proj, attn.k_proj, attn.v_proj, attn.o_proj = proj(64, 64), proj(64, 32), proj(64, 32), proj(64, 64)
+    mlp.gate_proj, mlp.up_proj, mlp.down_proj = proj(64, 128), proj(64, 128), proj(128, 64)
+    x = torch.randn(2, 5, 64)
+    q, k, v = apply_lora_qkv(attn, x)
+    for got, layer in ((q, attn.q_proj), (k, attn.k_proj), (v, attn.v_proj), (apply_lora_o(attn, x), attn.o_proj)):
+        assert torch.allclose(got, layer(x), atol=1e-5)
+    F = torch.nn.functional
+    acts = [(apply_lora_mlp_swiglu, F.silu), (apply_lora_mlp_geglu_exact, F.gelu),
+            (apply_lora_mlp_geglu_approx, lambda t: F.gelu(t, approximate="tanh"))]
+    for fused, act in acts:
+        want = mlp.down_proj(act(mlp.gate_proj(x)) * mlp.up_proj(x))
+        assert torch.allclose(fused(mlp, x), want, atol=1e-5)
