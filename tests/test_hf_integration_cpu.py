@@ -86,6 +86,19 @@ def _tiny_hf(family):
 
         cfg = C(intermediate_size=96, num_local_experts=4, num_experts_per_tok=2, architectures=["MixtralForCausalLM"],
                 **common)
+    elif family == "granitemoeshared":
+        from transformers import GraniteMoeSharedConfig as C
+        from transformers.models.granitemoeshared.modeling_granitemoeshared import GraniteMoeSharedForCausalLM as M
+
+        cfg = C(intermediate_size=96, num_local_experts=4, num_experts_per_tok=2, shared_intermediate_size=64,
+                architectures=["GraniteMoeSharedForCausalLM"], **common)
+    elif family == "granitemoehybrid":
+        from transformers import GraniteMoeHybridConfig as C
+        from transformers.models.granitemoehybrid.modeling_granitemoehybrid import GraniteMoeHybridForCausalLM as M
+
+        cfg = C(intermediate_size=96, num_local_experts=4, num_experts_per_tok=2, shared_intermediate_size=64,
+                layer_types=["mamba", "attention"], mamba_n_heads=4, mamba_d_head=32, mamba_expand=2, mamba_d_state=16,
+                mamba_chunk_size=8, architectures=["GraniteMoeHybridForCausalLM"], **common)
     else:
         from transformers import GraniteMoeConfig as C
         from transformers.models.granitemoe.modeling_granitemoe import GraniteMoeForCausalLM as M
@@ -96,7 +109,7 @@ def _tiny_hf(family):
     return M(cfg)
 
 
-@pytest.mark.parametrize("family", ["mistral", "granite", "mixtral", "granitemoe"])
+@pytest.mark.parametrize("family", ["mistral", "granite", "mixtral", "granitemoe", "granitemoeshared", "granitemoehybrid"])
 @pytest.mark.parametrize("fast_loss", [True, "fused_ce_liger"])
 def test_foak_rules_of_the_other_families_keep_the_numbers(family, fast_loss):
     """RMSNorm, rotary embedding and loss rules on the Hugging Face classes of every family that has them: the
