@@ -148,24 +148,17 @@ def test_foak_rules_of_the_other_families_keep_the_numbers(family, fast_loss):
         importlib.reload(importlib.import_module(type(ref).__module__))
 
 
-@pytest.mark.parametrize("family", ["granitemoe", "mixtral"])
+@pytest.mark.parametrize("family", ["granitemoe", "mixtral", "granitemoeshared", "granitemoehybrid"])
 def test_scattermoe_swaps_hf_moe_blocks_exactly_and_converts_back(family):
     """The module swap works on the installed transformers' MoE classes (fused 3-D expert parameters and hidden-only
-    return value in transformers >= 5; one linear per expert and a tuple before), and the ScatterMoE state converts
-    back to the original parameter names and values."""
+    return value in transformers >= 5; one linear per expert and a tuple before; with a shared dense branch and with
+    Mamba layers beside the attention layers), and the ScatterMoE state converts back to the original parameter names
+    and values."""
     from fms_acceleration_b200.plugins.moe.utils import checkpoint_utils as CU
     from fms_acceleration_b200.plugins.moe.utils import prepare_scattermoe
 
-    if family == "granitemoe":
-        from transformers import GraniteMoeConfig as C
-        from transformers import GraniteMoeForCausalLM as M
-    else:
-        from transformers import MixtralConfig as C
-        from transformers import MixtralForCausalLM as M
-    torch.manual_seed(0)
-    cfg = C(vocab_size=512, hidden_size=64, intermediate_size=32, num_hidden_layers=2, num_attention_heads=4,
-            num_key_value_heads=2, num_local_experts=4, num_experts_per_tok=2, architectures=[M.__name__])
-    model = M(cfg).eval()
+    model = _tiny_hf(family).eval()
+    M = type(model)
     original = {k: v.clone() for k, v in model.state_dict().items()}
     ids = torch.randint(0, 512, (2, 16))
     ref = model(input_ids=ids, labels=ids).loss
