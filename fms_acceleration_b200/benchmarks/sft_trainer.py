@@ -169,7 +169,10 @@ def main(argv: Optional[List[str]] = None) -> int:
     framework = AccelerationFramework(cfg_file) if cfg_file else None
     targs = TrainArgs(per_device_train_batch_size=args.per_device_train_batch_size,
                       gradient_accumulation_steps=args.gradient_accumulation_steps, learning_rate=args.learning_rate,
-                      weight_decay=args.weight_decay, max_grad_norm=args.max_grad_norm, bf16=dtype == torch.bfloat16,
+                      weight_decay=args.weight_decay, max_grad_norm=args.max_grad_norm,
+                      # mixed precision as asked for on the command line, or implied by the model dtype
+                      bf16=bool(args.bf16) or dtype == torch.bfloat16,
+                      fp16=(bool(args.fp16) or dtype == torch.float16) and not bool(args.bf16),
                       seed=args.seed, max_seq_length=args.max_seq_length, output_dir=args.output_dir,
                       logging_steps=args.logging_steps, padding_free=True, world_size=world,
                       gradient_checkpointing=bool(args.gradient_checkpointing),

@@ -236,3 +236,61 @@ def test_runner_options_of_the_reference(tmp_path):
                    "--results_output_path", str(out2)] + common) == 0
     runs = [json.load(open(out2 / d / B.FILE_ARGS)) for d in sorted(os.listdir(out2)) if d.startswith("exp_")]
     assert len(runs) == 1 and runs[0]["scenario"] == "heavy" and runs[0]["arguments"]["packing"] is False
+
+
+def _single_process_sample_configurations():
+    import glob
+
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    names = []
+    for f in sorted(glob.glob(os.path.join(here, "sample-configurations", "*-sample-configuration.yaml"))):
+        n = os.path.basename(f)[:-len("-sample-configuration.yaml")]
+        if not any(t in n for t in ("ep2", "ep4", "ep8", "multipack")):  # those need more than one rank
+            names.append((n, f))
+    return names
+
+
+@pytest.mark.parametrize("name,path", _single_process_sample_configurations())
+def test_trainer_cli_runs_every_single_process_sample_configuration(name, path, tmp_path, capsys):
+    """Two optimizer steps of a tiny model under each sample configuration, with the mixed-precision flag the
+    scenario files give (``--bf16 True``, ``--fp16 True`` for GPTQ): loading, augmentation and training go through."""
+    from fms_acceleration_b200.benchmarks import sft_trainer as T
+    from fms_acceleration_b200.framework import AccelerationFramework
+    from fms_acceleration_b200.framework.model_patcher import ModelPatcher
+
+    model = "tiny-granitemoe" if name.startswith("moe-") else "tiny-llama"
+    lora = [] if name.startswith(("moe-", "foak-fast", "aadp-")) else ["--peft_method", "lora", "--r", "4", "--lora_alpha", "8"]
+    precision = ["--fp16", "True"] if "autogptq" in name else ["--bf16", "True"]
+    saved = (dict(ModelPatcher.rules), list(ModelPatcher.history))
+    try:
+        AccelerationFramework.reset()
+        rc = T.main(["--model_name_or_path", model, "--acceleration_framework_config_file", path, "--torch_dtype", "float32",
+                     *precision, *lora, "--max_steps", "2", "--logging_steps", "1", "--per_device_train_batch_size", "2",
+                     "--max_seq_length", "32", "--output_dir", str(tmp_path)])
+    finally:
+        AccelerationFramework.reset()
+        ModelPatcher.rules.clear()
+        ModelPatcher.rules.update(saved[0])
+        ModelPatcher.history[:] = saved[1]
+    assert rc == 0
+    assert "train_tokens_per_second" in capsys.readouterr().out
+
+
+@pytest.mark.parametrize("name", ["moe-scattermoe-granite-ep2-padding-free-foak", "aadp-padding-free-multipack"])
+def test_trainer_cli_runs_two_rank_sample_configurations(name, tmp_path):
+    """Expert parallelism of degree 2 and the multipack data loader (which insists on distributed training) on two
+    gloo ranks."""
+    import sys
+
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    model = "tiny-granitemoe" if name.startswith("moe-") else "tiny-llama"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29689", "-m", "fms_acceleration_b200.benchmarks.sft_trainer",
+           "--model_name_or_path", model, "--acceleration_framework_config_file",
+           os.path.join(here, "sample-configurations", f"{name}-sample-configuration.yaml"), "--torch_dtype", "float32",
+           "--bf16", "True", "--max_steps", "2", "--logging_steps", "1", "--per_device_train_batch_size", "2",
+           "--max_seq_length", "32", "--output_dir", str(tmp_path)]
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", PYTHONPATH=here + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env, cwd=here)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    assert "train_tokens_per_second" in out.stdout
