@@ -287,6 +287,13 @@ class LlamaForCausalLM(GenerationMixin, nn.Module):
                 S = input_ids.shape[1]
                 shift_labels = shift_labels.clone()
                 shift_labels[S - 1:: S] = CE.IGNORE_INDEX
+            cp = getattr(self, "cp", None)
+            if cp is not None:
+                # context parallelism (hybrid models): this rank holds one slice of one sequence.  Its last position
+                # predicts the first token of the next rank's slice, and the mean runs over the tokens of all ranks.
+                shift_labels = cp.shift_labels(flat_labels)
+                if num_items_in_batch is None:
+                    num_items_in_batch = cp.global_count(shift_labels != CE.IGNORE_INDEX).reshape(())
         if labels is not None and self.fast_loss == "fused_ce_liger" and hidden.is_cuda:
             h = hidden if scale == 1.0 else hidden * scale
             loss = CE.fused_linear_cross_entropy(h, self.lm_head.weight, shift_labels, num_items=num_items_in_batch)

@@ -207,7 +207,12 @@ class Mamba2ForCausalLM(GenerationMixin, nn.Module):
                 logits = self.lm_head(hidden)
                 per = CE.cross_entropy_ref(logits, shift) if not (self.fast_loss and logits.is_cuda) else \
                     CE.fast_cross_entropy_loss(logits, shift)
-                n = num_items_in_batch if num_items_in_batch is not None else (shift != CE.IGNORE_INDEX).sum().clamp(min=1)
+                if num_items_in_batch is not None:
+                    n = num_items_in_batch
+                elif self.cp is not None:
+                    n = self.cp.global_count(shift != CE.IGNORE_INDEX).reshape(())  # tokens of ALL ranks, as above
+                else:
+                    n = (shift != CE.IGNORE_INDEX).sum().clamp(min=1)
                 loss = per.sum() / n
         else:
             logits = self.lm_head(hidden)

@@ -11,10 +11,18 @@ reference defaults to (fms_acceleration_mcp/framework_plugin_mcp.py:29-44).  The
 ``dH_in`` becomes ``dF_j`` / ``dlog P_j`` for the earlier ranks (one kernel, pushed), and what the later ranks send runs
 back through the zero-start recurrence.  The conv1d halo (last ``d_conv - 1`` rows of the previous slice) and the
 label that the last position predicts go to the neighbour only.
+
+``backend="library"`` (or ``FMSB_CP_BACKEND=library``; the default on a CPU) states the same exchange with the process
+group's collectives, NCCL on GPUs and gloo on CPUs: every rank scans its slice from a zero state, the
+``(F, log P)`` pairs are all-gathered, the prefix is combined locally and the entering state's contribution is added
+to the outputs; the halo is an all-gather of every rank's last rows.  It is the like-for-like library form of the
+fused path (what the reference's external ``Mamba2CP`` module does with ``torch.distributed``) and the form that CPU
+tests run.
 """
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -48,7 +56,7 @@ class ContextParallel:
     """Communication state shared by all Mamba2 layers of a model (buffers are reused layer after layer)."""
 
     def __init__(self, group: Optional[dist.ProcessGroup] = None, device=None, impl: str = "allgather",
-                 recompute: bool = False):
+                 recompute: bool = False, backend: Optional[str] = None):
         from .symm import Communicator
 
         self.group = group if group is not None else dist.group.WORLD
@@ -60,10 +68,16 @@ class ContextParallel:
         # rank-to-rank chain would only add world-1 latencies to the last rank.  recompute: the scan keeps only its
         # inputs and rebuilds the per-chunk entering states in the backward.
         self.impl, self.recompute = impl, recompute
-        self.comm = Communicator(self.group, self.device)
+        self.backend = backend or os.environ.get("FMSB_CP_BACKEND") or ("fused" if self.device.type == "cuda" else "library")
+        if self.backend not in ("fused", "library"):
+            raise ValueError(f"unknown context-parallel backend {self.backend!r}")
         self._slots = {}
-        self._counter = torch.zeros(4, dtype=torch.int32, device=self.device)  # "last CTA" counters of the fused kernels
         self._hooks = {}
+        if self.backend == "library":
+            self.comm = None  # no peer memory: the process group's collectives carry everything
+            return
+        self.comm = Communicator(self.group, self.device)
+        self._counter = torch.zeros(4, dtype=torch.int32, device=self.device)  # "last CTA" counters of the fused kernels
 
     # ------------------------------------------------------------------ primitive: push to later / earlier ranks
     def _exchange(self, payload: torch.Tensor, chan: int, direction: int, tag=None, span: int = 0) -> torch.Tensor:
@@ -91,21 +105,49 @@ class ContextParallel:
 
     # ------------------------------------------------------------------ conv halo
     def exchange_halo(self, xBC: torch.Tensor, k: int, layer=None) -> torch.Tensor:
+        if self.backend == "library":
+            # every rank's last k rows, gathered; mine are the previous rank's (zeros on rank 0).  The zero-weight
+            # term keeps the gather in every rank's graph, so that its backward (a collective) runs everywhere.
+            tails = _GatherTokens.apply(xBC[-k:].contiguous(), self.group)
+            halo = tails[(self.rank - 1) * k:self.rank * k] if self.rank > 0 else torch.zeros_like(xBC[-k:])
+            return halo + 0.0 * tails.sum()
         return _HaloExchange.apply(xBC, self, k, layer)
 
     # ------------------------------------------------------------------ scan
     def scan(self, x, dt, A, B, C, D, Q, layer=None):
         """Context-parallel SSD scan of this rank's slice; returns y."""
+        if self.backend == "library":
+            return self._scan_library(x, dt, A, B, C, D, Q)
         hook = self._hooks.get(layer)
         if hook is None:
             hook = self._hooks[layer] = StateHandoff(self, layer)
         y, _ = MB.ssd_scan(x, dt, A, B, C, D, None, Q, recompute=self.recompute, cp=hook)
         return y
 
+    def _scan_library(self, x, dt, A, B, C, D, Q):
+        """Zero-start scan of the slice, all-gather of every rank's ``(final state, log total decay)``, prefix combine
+        on this rank, then the entering state's contribution ``exp(cumsum dt A) (C . H_in)`` added to the outputs.
+        Every piece is differentiable (the gather's backward is the matching reduce-scatter), so the state gradients
+        travel right to left through the same collectives."""
+        nh, P = x.shape[1], x.shape[2]
+        N = B.shape[2]
+        y0, F = MB.ssd_scan(x, dt, A, B, C, D, None, Q, recompute=self.recompute)
+        logP = (dt.float() * A.float()[None, :]).sum(0)
+        mine = torch.cat([F.float().reshape(nh, P * N), logP[:, None]], dim=1)[None]     # [1, nh, P*N + 1]
+        every = _GatherTokens.apply(mine, self.group)                                    # [world, nh, P*N + 1]
+        Fs, lPs = every[..., :-1].reshape(self.world, nh, P, N), every[..., -1]
+        h_in = prefix_state(Fs, lPs, self.rank) + 0.0 * every.sum()  # rank 0 too keeps the gather in its graph
+        return MB.state_correction(y0, h_in, dt, A, C, Q)
+
     # ------------------------------------------------------------------ loss helpers
     def shift_labels(self, flat_labels: torch.Tensor) -> torch.Tensor:
         """Next-token targets for this slice: the last position takes the first label of the NEXT rank's slice."""
         first = flat_labels[:1].contiguous()
+        if self.backend == "library":
+            firsts = [torch.empty_like(first) for _ in range(self.world)]
+            dist.all_gather(firsts, first, group=self.group)
+            nxt = firsts[self.rank + 1] if self.rank + 1 < self.world else torch.full_like(first, -100)
+            return torch.cat([flat_labels[1:], nxt])
         recv = self._exchange(first, CH_HALO_B, -1, span=1)                   # from the next rank, slot = sender
         nxt = recv[self.rank + 1] if self.rank + 1 < self.world else torch.full_like(first, -100)
         return torch.cat([flat_labels[1:], nxt.to(flat_labels.dtype)])
