@@ -126,7 +126,8 @@ class Experiment:
         for k, v in self.arguments.items():
             if v is None:
                 continue
-            cmd.append(f"--{k}")
+            # the launcher's parser takes a bare ``--r`` for an abbreviation of its own options: spell it out
+            cmd.append("--lora_r" if k == "r" else f"--{k}")
             if isinstance(v, (list, tuple)):
                 cmd.extend(str(x) for x in v)
             else:

@@ -40,7 +40,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--bf16", type=tf, nargs="?", const=True, default=False)
     ap.add_argument("--fp16", type=tf, nargs="?", const=True, default=False)
     ap.add_argument("--peft_method", default="none", choices=["none", "lora"])
-    ap.add_argument("--r", type=int, default=16)
+    # ``--lora_r`` is the spelling the benchmark runner uses under torch.distributed.run, whose own parser rejects a
+    # bare ``--r`` in the trainer's arguments as an ambiguous abbreviation of its ``--rdzv-*`` / ``--role`` options
+    ap.add_argument("--r", "--lora_r", dest="r", type=int, default=16)
     ap.add_argument("--lora_alpha", type=int, default=16)
     ap.add_argument("--lora_dropout", type=float, default=0.0)
     ap.add_argument("--target_modules", nargs="*", default=["q_proj", "k_proj", "v_proj", "o_proj"])

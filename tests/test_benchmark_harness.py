@@ -294,3 +294,22 @@ def test_trainer_cli_runs_two_rank_sample_configurations(name, tmp_path):
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env, cwd=here)
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
     assert "train_tokens_per_second" in out.stdout
+
+
+def test_two_rank_lora_experiment_runs_through_the_launcher(tmp_path):
+    """A LoRA scenario (``r: 4``) on two ranks, run for real through ``torch.distributed.run`` (gloo on the CPU): the
+    rank argument reaches the trainer although the launcher's own parser would take ``--r`` for one of its options."""
+    scen = {"scenarios": [{"name": "standard-peft", "arguments": {
+        "model_name_or_path": ["tiny-llama"], "torch_dtype": "float32", "bf16": True, "peft_method": "lora", "r": 4,
+        "lora_alpha": 8, "lora_dropout": 0.1, "target_modules": ["q_proj", "k_proj", "v_proj", "o_proj"],
+        "max_seq_length": 32, "max_steps": 2, "logging_steps": 1}}]}
+    sp = tmp_path / "scenarios.yaml"
+    sp.write_text(yaml.safe_dump(scen))
+    out = tmp_path / "results"
+    rc = B.main(["--num_gpus", "2", "--effective_batch_size_matrix", "4", "--scenarios_config_path", str(sp),
+                 "--defaults_config_path", "", "--results_output_path", str(out), "--timeout", "600"])
+    assert rc == 0
+    res = json.load(open(out / "exp_0" / B.FILE_RESULTS))
+    assert not res.get("error_messages"), res
+    assert res["train_tokens_per_second"] > 0
+    assert "--lora_r 4" in open(out / "exp_0" / B.FILE_COMMAND).read()
