@@ -115,7 +115,11 @@ class PackedRows:
     def __init__(self, rows, batch: int, seq_len: int, seed: int, rank: int, world: int):
         from ..plugins.aadp.aadp_utils import DataCollatorWithFlattening
 
-        self.rows = [r for r in rows if len(r["input_ids"]) <= seq_len]
+        # longer samples are cut at the maximum sequence length (what the reference's trainer does with them)
+        self.rows = [r if len(r["input_ids"]) <= seq_len else
+                     {"input_ids": r["input_ids"][:seq_len], "labels": r["labels"][:seq_len]} for r in rows]
+        if not self.rows:
+            raise ValueError("the training file holds no samples")
         self.cap = batch * seq_len
         self.collate = DataCollatorWithFlattening(return_cu_seqlens=True)
         g = torch.Generator().manual_seed(seed)

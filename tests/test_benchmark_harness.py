@@ -313,3 +313,18 @@ def test_two_rank_lora_experiment_runs_through_the_launcher(tmp_path):
     assert not res.get("error_messages"), res
     assert res["train_tokens_per_second"] > 0
     assert "--lora_r 4" in open(out / "exp_0" / B.FILE_COMMAND).read()
+
+
+def test_trainer_cli_on_a_tokenised_file_with_over_long_samples(tmp_path, capsys):
+    """Samples longer than ``max_seq_length`` are cut, not dropped (a file of only long samples still trains)."""
+    from fms_acceleration_b200.benchmarks import sft_trainer as T
+
+    records = [{"instruction": f"Add {i}", "input": f"{i} + {i + 1}", "output": f"The answer is {2 * i + 1}."}
+               for i in range(16)]
+    path = DP.prepare_dataset(records, str(tmp_path / "cache"), "bench")
+    rows = json.load(open(path))
+    assert min(len(r["input_ids"]) for r in rows) > 64
+    rc = T.main(["--model_name_or_path", "tiny-llama", "--torch_dtype", "float32", "--training_data_path", path,
+                 "--max_steps", "2", "--logging_steps", "1", "--per_device_train_batch_size", "2", "--max_seq_length", "64",
+                 "--output_dir", str(tmp_path / "out")])
+    assert rc == 0 and "train_tokens_per_second" in capsys.readouterr().out
