@@ -97,12 +97,19 @@ class LoraLinear(nn.Module):
         return y
 
 
+def _all_linear(targets) -> bool:
+    """``"all-linear"`` as a string or as the only entry of a list (what a command line produces)."""
+    if isinstance(targets, str):
+        return targets in ("all-linear", "all_linear")
+    return targets is not None and len(targets) == 1 and next(iter(targets)) in ("all-linear", "all_linear")
+
+
 def _matches(name: str, targets) -> bool:
     if targets is None:
         return False
+    if _all_linear(targets):
+        return True
     if isinstance(targets, str):
-        if targets == "all-linear":
-            return True
         return re.fullmatch(targets, name) is not None
     leaf = name.split(".")[-1]
     return any(leaf == t or name.endswith("." + t) or name == t for t in targets)
@@ -123,7 +130,7 @@ def inject_lora(model: nn.Module, config: LoraConfig, adapter_name: str = "defau
     for name, mod in list(model.named_modules()):
         if not _is_linear_like(mod) or not _matches(name, config.target_modules):
             continue
-        if config.target_modules == "all-linear" and name.split(".")[-1] in skip:
+        if _all_linear(config.target_modules) and name.split(".")[-1] in skip:
             continue
         parent_name, _, leaf = name.rpartition(".")
         parent = model.get_submodule(parent_name) if parent_name else model

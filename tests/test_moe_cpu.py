@@ -299,3 +299,20 @@ def test_expert_lora_gradient_algebra_against_autograd(monkeypatch):
     ref2.backward(dYs)
     for key, t in zip(("da13", "db13", "da2", "db2"), pk):
         assert torch.allclose(got[key], t.grad, atol=1e-5), key
+
+
+def test_all_linear_given_as_a_one_element_list_targets_every_linear():
+    """``--target_modules all-linear`` arrives from a command line as ``["all-linear"]``."""
+    import torch
+
+    from fms_acceleration_b200.models.builder import build_model
+    from fms_acceleration_b200.nn import LoraConfig, get_peft_model
+    from fms_acceleration_b200.nn.lora import LoraLinear
+
+    as_list = get_peft_model(build_model("tiny-llama", seed=0), LoraConfig(r=2, lora_alpha=4, target_modules=["all-linear"]))
+    as_text = get_peft_model(build_model("tiny-llama", seed=0), LoraConfig(r=2, lora_alpha=4, target_modules="all-linear"))
+    names = lambda m: sorted(n for n, mod in m.named_modules() if isinstance(mod, LoraLinear))  # noqa: E731
+    assert names(as_list) == names(as_text) and len(names(as_list)) == 7 * 2  # 7 projections x 2 layers, no lm_head
+    assert not any("lm_head" in n for n in names(as_list))
+    ids = torch.randint(0, 100, (1, 8))
+    assert torch.isfinite(as_list(ids, labels=ids).loss)
