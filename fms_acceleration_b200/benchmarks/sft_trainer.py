@@ -66,7 +66,11 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--output_dir", default="./out")
     ap.add_argument("--skip_memory_metrics", type=tf, nargs="?", const=True, default=True)
     ap.add_argument("--include_tokens_per_second", type=tf, nargs="?", const=True, default=True)
-    ap.add_argument("--save_strategy", default="no")
+    ap.add_argument("--save_strategy", default="no", choices=["no", "steps", "epoch"],
+                    help="steps: a checkpoint every --save_steps steps; epoch: one at the end of the run")
+    ap.add_argument("--save_steps", type=int, default=500)
+    ap.add_argument("--resume_from_checkpoint", default=None,
+                    help="a checkpoint directory, or True for the newest one under --output_dir")
     ap.add_argument("--gradient_checkpointing", type=tf, nargs="?", const=True, default=False,
                     help="recompute every decoder layer in backward (the reference's benchmark default)")
     # arguments of the reference's benchmark defaults that have nothing to switch here: attention is always the
@@ -233,16 +237,33 @@ def main(argv: Optional[List[str]] = None) -> int:
         if cuda:
             torch.cuda.synchronize()
 
+    first_step = 1
+    accum = max(1, int(args.gradient_accumulation_steps or 1))
+    if args.resume_from_checkpoint:
+        ckpt = args.resume_from_checkpoint
+        if str(ckpt).lower() == "true":
+            ckpt = Trainer.latest_checkpoint(args.output_dir)
+            if ckpt is None:
+                raise ValueError(f"No valid checkpoint found in output directory ({args.output_dir})")
+        trainer.load_checkpoint(ckpt, scheduler=sched)
+        first_step = trainer.global_step * accum + 1  # the loop counts micro-batches, the trainer optimizer steps
+        for _ in range(first_step - 1):  # the data stream continues where the saved run stopped
+            next_batch()
+
     sync()
     t0 = time.perf_counter()
     tokens = 0
     run_loss, n_log = 0.0, 0
     total_loss = 0.0
-    for step in range(1, args.max_steps + 1):
+    for step in range(first_step, args.max_steps + 1):
         batch = next_batch()
         tokens += int(batch["input_ids"].numel())
         loss = trainer.train_step(batch)
         sched.step()
+        boundary = step % accum == 0  # checkpoints are taken between optimizer steps only
+        if boundary and ((args.save_strategy == "steps" and (step // accum) % args.save_steps == 0) or
+                         (args.save_strategy == "epoch" and step + accum > args.max_steps)):
+            trainer.save_checkpoint(args.output_dir, scheduler=sched)
         run_loss += float(loss)
         n_log += 1
         if args.logging_strategy == "steps" and step % args.logging_steps == 0 and rank == 0:

@@ -328,3 +328,28 @@ def test_trainer_cli_on_a_tokenised_file_with_over_long_samples(tmp_path, capsys
                  "--max_steps", "2", "--logging_steps", "1", "--per_device_train_batch_size", "2", "--max_seq_length", "64",
                  "--output_dir", str(tmp_path / "out")])
     assert rc == 0 and "train_tokens_per_second" in capsys.readouterr().out
+
+
+def test_trainer_cli_saves_and_resumes(tmp_path, capsys):
+    """``--save_strategy steps`` writes checkpoints at optimizer-step boundaries and ``--resume_from_checkpoint True``
+    continues from the newest one: the resumed run prints the losses of the uninterrupted run."""
+    import ast
+
+    from fms_acceleration_b200.benchmarks import sft_trainer as T
+
+    common = ["--model_name_or_path", "tiny-llama", "--torch_dtype", "float32", "--peft_method", "lora", "--r", "4",
+              "--lora_alpha", "8", "--logging_steps", "2", "--per_device_train_batch_size", "2", "--max_seq_length", "32",
+              "--gradient_accumulation_steps", "2"]
+
+    def losses(argv):
+        assert T.main(common + argv) == 0
+        lines = [ast.literal_eval(l) for l in capsys.readouterr().out.splitlines() if l.startswith("{'loss'")]
+        return [d["loss"] for d in lines]
+
+    whole = losses(["--max_steps", "8", "--output_dir", str(tmp_path / "a")])
+    first = losses(["--max_steps", "4", "--save_strategy", "steps", "--save_steps", "2", "--output_dir", str(tmp_path / "b")])
+    assert sorted(os.listdir(tmp_path / "b")) == ["checkpoint-2"]  # 4 micro-batches = 2 optimizer steps
+    rest = losses(["--max_steps", "8", "--resume_from_checkpoint", "True", "--output_dir", str(tmp_path / "b")])
+    assert first == whole[:2] and rest == whole[2:]
+    with pytest.raises(ValueError, match="No valid checkpoint"):
+        T.main(common + ["--max_steps", "2", "--resume_from_checkpoint", "True", "--output_dir", str(tmp_path / "none")])
