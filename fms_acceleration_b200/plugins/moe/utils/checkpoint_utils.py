@@ -437,7 +437,18 @@ def recover_safetensors_from_dcp(checkpoint_dir: str, pretrained_model_name_or_p
         cleaned[nk] = v
     sd = cleaned
     if pretrained_model_name_or_path is not None and not lora:
-        sd = recover_original_state_dict_from_checkpoint(sd, pretrained_model_name_or_path)
+        if os.path.isdir(pretrained_model_name_or_path):
+            sd = recover_original_state_dict_from_checkpoint(sd, pretrained_model_name_or_path)
+        else:
+            # a run that started from an architecture preset (random-init weights): the original parameter names
+            # and the architecture come from the preset's model skeleton instead of from checkpoint files
+            from ....models.builder import build_model, resolve_config
+
+            cfg = resolve_config(pretrained_model_name_or_path)
+            with torch.device("meta"):
+                skeleton = build_model(cfg, device="meta", dtype=torch.bfloat16)
+            sd = recover_original_state_dict_from_checkpoint(
+                sd, weight_map={k: SAFE_WEIGHTS_NAME for k in skeleton.state_dict()}, architectures=list(cfg.architectures))
     save_sharded_safetensors({k: v.contiguous() for k, v in sd.items()}, output_dir, metadata={"format": "pt"}, lora=lora)
 
 

@@ -316,3 +316,41 @@ def test_all_linear_given_as_a_one_element_list_targets_every_linear():
     assert not any("lm_head" in n for n in names(as_list))
     ids = torch.randint(0, 100, (1, 8))
     assert torch.isfinite(as_list(ids, labels=ids).loss)
+
+
+def test_cli_checkpoint_of_a_preset_run_converts_back_to_the_original_layout(tmp_path):
+    """Train a ScatterMoE model that started from an architecture preset, save through the trainer CLI, convert with
+    the checkpoint tool (the preset name stands in for the original checkpoint) and load the result into the plain
+    model: every parameter is there under its original name."""
+    import os
+
+    import torch
+    from safetensors.torch import load_file
+
+    from fms_acceleration_b200.benchmarks import sft_trainer as T
+    from fms_acceleration_b200.framework import AccelerationFramework
+    from fms_acceleration_b200.framework.model_patcher import ModelPatcher
+    from fms_acceleration_b200.models.builder import build_model
+    from fms_acceleration_b200.plugins.moe.utils import checkpoint_utils as CU
+
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = os.path.join(here, "sample-configurations", "moe-scattermoe-granite-ep1-sample-configuration.yaml")
+    saved = (dict(ModelPatcher.rules), list(ModelPatcher.history))
+    try:
+        AccelerationFramework.reset()
+        assert T.main(["--model_name_or_path", "tiny-granitemoe", "--acceleration_framework_config_file", cfg,
+                       "--torch_dtype", "float32", "--bf16", "True", "--max_steps", "2", "--logging_steps", "1",
+                       "--per_device_train_batch_size", "2", "--max_seq_length", "32", "--save_strategy", "epoch",
+                       "--output_dir", str(tmp_path / "run")]) == 0
+    finally:
+        AccelerationFramework.reset()
+        ModelPatcher.rules.clear()
+        ModelPatcher.rules.update(saved[0])
+        ModelPatcher.history[:] = saved[1]
+    assert CU.main([str(tmp_path / "run" / "checkpoint-2"), str(tmp_path / "hf"), "tiny-granitemoe"]) == 0
+    sd = load_file(str(tmp_path / "hf" / "model.safetensors"))
+    plain = build_model("tiny-granitemoe", seed=0)
+    before = {k: v.clone() for k, v in plain.state_dict().items()}
+    missing, unexpected = plain.load_state_dict(sd, strict=False)
+    assert not missing and not unexpected
+    assert any(not torch.equal(before[k], v) for k, v in plain.state_dict().items())  # trained values, not the init
