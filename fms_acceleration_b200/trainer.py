@@ -234,7 +234,10 @@ class Trainer:
             if lora:
                 from safetensors.torch import save_file
 
-                sd = {k: v.detach().cpu().contiguous() for k, v in self.model.state_dict().items() if "lora_" in k}
+                # PEFT's file layout: adapter tensors without the adapter name in their keys
+                src = (self.model.adapter_state_dict() if hasattr(self.model, "adapter_state_dict") else
+                       {k.replace(".default", ""): v for k, v in self.model.state_dict().items() if "lora_" in k})
+                sd = {k: v.detach().cpu().contiguous() for k, v in src.items()}
                 save_file(sd, os.path.join(ckpt, "adapter_model.safetensors"), metadata={"format": "pt"})
                 cfg = getattr(self.model, "peft_config", None)
                 cfg = cfg.get("default") if isinstance(cfg, dict) else cfg

@@ -51,6 +51,8 @@ def test_lora_checkpoint_holds_only_adapters(tmp_path):
     t.train(_batches(t.model.config.vocab_size, 0, 3))
     sd = load_file(os.path.join(out, "checkpoint-3", "adapter_model.safetensors"))
     assert sd and all("lora_" in k for k in sd)
+    # PEFT's key layout: no adapter name between ``lora_A`` / ``lora_B`` and ``weight``
+    assert all(k.endswith(("lora_A.weight", "lora_B.weight")) and k.startswith("base_model.model.") for k in sd)
     cfg = json.load(open(os.path.join(out, "checkpoint-3", "adapter_config.json")))
     assert cfg["r"] == 4 and sorted(cfg["target_modules"]) == ["q_proj", "v_proj"]
 
