@@ -191,10 +191,12 @@ def main(argv: Optional[List[str]] = None) -> int:
     if cuda:
         torch.cuda.reset_peak_memory_stats()
     t_load = time.perf_counter()
+    # a checkpoint directory is handed over as such (the loaders read its weights); a preset as its configuration
+    source = args.model_name_or_path if os.path.isdir(str(args.model_name_or_path)) and not args.num_layers_override else cfg
     if framework is not None and framework.requires_custom_loading:
-        model = framework.model_loader(cfg, torch_dtype=dtype, device=dev)
+        model = framework.model_loader(source, torch_dtype=dtype, device=dev)
     else:
-        model = build_model(cfg, device=dev, dtype=dtype, seed=args.seed)
+        model = build_model(source, device=dev, dtype=dtype, seed=args.seed)
     peft_config = None
     if args.peft_method == "lora":
         peft_config = LoraConfig(r=args.r, lora_alpha=args.lora_alpha, lora_dropout=args.lora_dropout,

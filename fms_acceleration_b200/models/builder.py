@@ -4,6 +4,7 @@ from __future__ import annotations
 import contextlib
 import json
 import os
+import re
 from typing import Callable, Optional
 
 import torch
@@ -81,21 +82,92 @@ def _default_dtype(dtype):
         torch.set_default_dtype(old)
 
 
+class _CheckpointReader:
+    """Tensors of a local safetensors checkpoint (one file, or shards with ``model.safetensors.index.json``), read one
+    at a time."""
+
+    _LAYER = re.compile(r"^(?:.*\.)?(?:layers|h)\.(\d+)\.(.+)$")
+
+    def __init__(self, directory: str):
+        self.directory = directory
+        index = os.path.join(directory, "model.safetensors.index.json")
+        single = os.path.join(directory, "model.safetensors")
+        if os.path.exists(index):
+            with open(index, encoding="utf-8") as fh:
+                self.weight_map = dict(json.load(fh)["weight_map"])
+        elif os.path.exists(single):
+            from safetensors import safe_open
+
+            with safe_open(single, framework="pt") as f:
+                self.weight_map = {k: "model.safetensors" for k in f.keys()}
+        else:
+            self.weight_map = {}
+        self.by_layer = {}
+        for key in self.weight_map:
+            m = self._LAYER.match(key)
+            if m:
+                self.by_layer.setdefault(int(m.group(1)), {})[m.group(2)] = key
+        self._open = {}
+
+    def __bool__(self):
+        return bool(self.weight_map)
+
+    def tensor(self, key: str) -> torch.Tensor:
+        from safetensors import safe_open
+
+        name = self.weight_map[key]
+        if name not in self._open:
+            self._open[name] = safe_open(os.path.join(self.directory, name), framework="pt")
+        return self._open[name].get_tensor(key)
+
+    def load_layer(self, layer: nn.Module, index: int) -> None:
+        """Copy the tensors stored for decoder layer ``index`` into ``layer`` (names relative to the layer)."""
+        own = dict(layer.named_parameters())
+        own.update(dict(layer.named_buffers()))
+        with torch.no_grad():
+            for rest, key in self.by_layer.get(index, {}).items():
+                if rest in own:
+                    own[rest].copy_(self.tensor(key).to(own[rest].dtype))
+
+    def load_rest(self, model: nn.Module) -> None:
+        """Everything that does not belong to a decoder layer (embeddings, final norm, output head)."""
+        layer_keys = {k for d in self.by_layer.values() for k in d.values()}
+        own = dict(model.named_parameters())
+        own.update(dict(model.named_buffers()))
+        with torch.no_grad():
+            for key in self.weight_map:
+                if key not in layer_keys and key in own:
+                    own[key].copy_(self.tensor(key).to(own[key].dtype))
+
+
 def build_model(model_name_or_cfg, device="cpu", dtype=torch.float32, layer_hook: Optional[Callable] = None,
                 seed: Optional[int] = None) -> nn.Module:
-    """Random-init model (normal(0, initializer_range)), built directly on ``device``; ``layer_hook`` runs on
-    every decoder layer right after its construction."""
+    """A model built directly on ``device``: random-init (normal(0, initializer_range)) for a preset, with the weights of
+    the checkpoint for a local directory that holds safetensors files.  ``layer_hook`` runs on every decoder layer
+    right after its construction, and after that layer's checkpoint tensors are in place (so a hook that quantises
+    the layer packs the real weights, one layer at a time)."""
     cfg = resolve_config(model_name_or_cfg)
     cls = _registry()[cfg.architectures[0]]
     if seed is not None:
         torch.manual_seed(seed)
-    with torch.device(device), _default_dtype(dtype):
-        model = cls(cfg, layer_hook=layer_hook)
-    state_file = os.path.join(cfg.name_or_path, "model.safetensors") if cfg.name_or_path else ""
-    if state_file and os.path.exists(state_file) and layer_hook is None:
-        from safetensors.torch import load_file
+    reader = _CheckpointReader(cfg.name_or_path) if cfg.name_or_path and os.path.isdir(cfg.name_or_path) else None
+    hook = layer_hook
+    if reader and layer_hook is not None:
+        seen = [0]
 
-        model.load_state_dict(load_file(state_file), strict=False)
+        def hook(layer):  # noqa: F811 - decoder layers are constructed in order
+            reader.load_layer(layer, seen[0])
+            seen[0] += 1
+            return layer_hook(layer)
+
+    with torch.device(device), _default_dtype(dtype):
+        model = cls(cfg, layer_hook=hook)
+    if reader:
+        if layer_hook is None:
+            state = {k: reader.tensor(k) for k in reader.weight_map}
+            model.load_state_dict(state, strict=False)
+        else:
+            reader.load_rest(model)
     return model
 
 

@@ -56,3 +56,45 @@ def test_hub_aliases_resolve_to_presets():
         cfg = resolve_config(hub)
         assert cfg.architectures == PRESETS[name]().architectures
     assert resolve_config("mistralai/Mixtral-8x7B-Instruct-v0.1").num_local_experts == 8
+
+
+def test_checkpoint_directories_load_plain_quantised_at_load_and_sharded(tmp_path):
+    """``build_model`` on a directory with safetensors files: the plain model gets the stored weights, a per-layer hook
+    (the 4-bit loader) sees each layer with its stored weights before it packs them, and shards with an index file
+    work the same."""
+    import json
+    import os
+
+    import torch
+    from safetensors.torch import save_file
+
+    import fms_acceleration_b200.plugins  # noqa: F401
+    from fms_acceleration_b200.models.builder import build_model
+    from fms_acceleration_b200.nn import Linear4bit
+    from fms_acceleration_b200.plugins.peft.framework_plugin_bnb import BNBAccelerationPlugin
+    from fms_acceleration_b200.plugins.peft.gptqmodel.utils.model import shard_checkpoint
+
+    src = build_model("tiny-llama", seed=3)
+    state = {k: v.contiguous() for k, v in src.state_dict().items()}
+    config = {**src.config.to_dict(), "name_or_path": ""}
+    one, many = tmp_path / "one", tmp_path / "many"
+    os.makedirs(one)
+    os.makedirs(many)
+    save_file(state, str(one / "model.safetensors"), metadata={"format": "pt"})
+    shards, index = shard_checkpoint(state, 200_000)
+    assert len(shards) > 1
+    for name, part in shards.items():
+        save_file(part, str(many / name), metadata={"format": "pt"})
+    json.dump(index, open(many / "model.safetensors.index.json", "w"))
+    for d in (one, many):
+        json.dump(config, open(d / "config.json", "w"))
+        loaded = build_model(str(d))
+        assert all(torch.equal(a, b) for a, b in zip(loaded.state_dict().values(), src.state_dict().values()))
+
+    plugin = BNBAccelerationPlugin({"peft": {"quantization": {"bitsandbytes": {"quant_type": "nf4", "no_peft_model": False}}}})
+    packed = plugin.model_loader(str(many), torch_dtype=torch.float32, device="cpu")
+    got = packed.model.layers[1].mlp.down_proj.dequantize(dtype=torch.float32)
+    want = Linear4bit.from_linear(src.model.layers[1].mlp.down_proj, "nf4", 64, torch.float32).dequantize(dtype=torch.float32)
+    assert torch.equal(got, want)
+    assert torch.equal(packed.model.embed_tokens.weight, src.model.embed_tokens.weight)
+    assert torch.equal(packed.model.norm.weight, src.model.norm.weight)
