@@ -201,6 +201,54 @@ class PeftModelShim(nn.Module):
             json.dump(self.peft_config[self.active_adapter].to_dict(), fh, indent=2)
 
 
+    def load_adapter(self, path: str, adapter_name: Optional[str] = None) -> None:
+        """Read ``adapter_model.safetensors`` (PEFT's key layout, no adapter name in the keys) from directory ``path``
+        into this model's adapter tensors; every adapter tensor has to be there."""
+        from safetensors.torch import load_file
+
+        name = adapter_name or self.active_adapter
+        stored = load_file(os.path.join(path, "adapter_model.safetensors"))
+        own = {k.replace(f".{name}", ""): v for k, v in self.state_dict().items() if "lora_" in k}
+        missing = sorted(set(own) - set(stored))
+        if missing:
+            raise KeyError(f"adapter file lacks {missing[:4]}{'...' if len(missing) > 4 else ''}")
+        with torch.no_grad():
+            for k, dst in own.items():
+                dst.copy_(stored[k].to(device=dst.device, dtype=dst.dtype))
+
+    @classmethod
+    def from_pretrained(cls, model: nn.Module, path: str, adapter_name: str = "default", is_trainable: bool = False):
+        """Wrap ``model`` with the adapter saved under ``path`` (``adapter_config.json`` + ``adapter_model.safetensors``,
+        what :meth:`save_pretrained` and the trainer's checkpoints write)."""
+        with open(os.path.join(path, "adapter_config.json"), encoding="utf-8") as fh:
+            raw = json.load(fh)
+        fields = LoraConfig.__dataclass_fields__
+        peft = cls(model, LoraConfig(**{k: v for k, v in raw.items() if k in fields}), adapter_name)
+        peft.load_adapter(path, adapter_name)
+        if not is_trainable:
+            for p in peft.parameters():
+                p.requires_grad_(False)
+        return peft
+
+    def merge_and_unload(self) -> nn.Module:
+        """Fold every adapter into its dense base weight (``W += scaling * B A``) and hand back the plain model.
+        A packed 4-bit or GPTQ base cannot take the update and is refused."""
+        model = self.base_model.model
+        for name, mod in list(model.named_modules()):
+            if not isinstance(mod, LoraLinear):
+                continue
+            base = mod.base_layer
+            if not isinstance(base, nn.Linear):
+                raise NotImplementedError(f"{name}: a LoRA adapter cannot be merged into a {type(base).__name__} base")
+            ad = mod.active_adapter
+            A, B = mod.lora_A[ad].weight, mod.lora_B[ad].weight
+            with torch.no_grad():
+                base.weight.add_((B.float() @ A.float() * mod.scaling[ad]).to(base.weight.dtype))
+            parent_name, _, leaf = name.rpartition(".")
+            setattr(model.get_submodule(parent_name) if parent_name else model, leaf, base)
+        return model
+
+
 def get_peft_model(model: nn.Module, peft_config, adapter_name: str = "default"):
     """Use ``peft.get_peft_model`` when PEFT is installed and the config is a PEFT config; otherwise the shim."""
     if not isinstance(peft_config, LoraConfig):

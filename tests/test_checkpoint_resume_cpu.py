@@ -86,3 +86,41 @@ def test_full_state_dict_of_rank_zero_reaches_every_rank(world):
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, MASTER_ADDR="127.0.0.1"))
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
     assert "STATE_LOADING_OK" in out.stdout
+
+
+def test_adapter_round_trip_and_merge(tmp_path):
+    """``save_pretrained`` -> ``PeftModelShim.from_pretrained`` on a fresh base gives the same function; the adapter
+    file of a trainer checkpoint loads the same way; ``merge_and_unload`` folds the adapters into dense weights and a
+    packed base refuses the merge."""
+    from fms_acceleration_b200.models.builder import quantize_linears_
+    from fms_acceleration_b200.nn import Linear4bit
+    from fms_acceleration_b200.nn.lora import PeftModelShim
+
+    torch.manual_seed(0)
+    model = get_peft_model(build_model("tiny-llama", seed=0), LoraConfig(r=4, lora_alpha=8, target_modules=["q_proj", "v_proj"]))
+    for name, p in model.named_parameters():
+        if "lora_B" in name:
+            torch.nn.init.normal_(p, std=0.05)
+    ids = torch.randint(0, 1000, (1, 12))
+    want = model(ids, return_logits=True).logits
+    model.save_pretrained(str(tmp_path / "adapter"))
+    again = PeftModelShim.from_pretrained(build_model("tiny-llama", seed=0), str(tmp_path / "adapter"))
+    assert torch.allclose(again(ids, return_logits=True).logits, want, atol=1e-6)
+    assert not any(p.requires_grad for p in again.parameters())
+    trainable = PeftModelShim.from_pretrained(build_model("tiny-llama", seed=0), str(tmp_path / "adapter"), is_trainable=True)
+    assert sum(p.requires_grad for p in trainable.parameters()) == 2 * 2 * 2  # (A, B) x 2 projections x 2 layers
+    plain = again.merge_and_unload()
+    assert not any("lora" in n for n, _ in plain.named_parameters())
+    assert torch.allclose(plain(ids, return_logits=True).logits, want, atol=1e-4)
+
+    # the adapter file a trainer checkpoint writes
+    t = _make(True, str(tmp_path / "run"))
+    t.train(_batches(t.model.config.vocab_size, 0, 3))
+    from_ckpt = PeftModelShim.from_pretrained(build_model("tiny-llama", seed=0), str(tmp_path / "run" / "checkpoint-3"))
+    for (n1, a), (n2, b) in zip(sorted(t.model.adapter_state_dict().items()), sorted(from_ckpt.adapter_state_dict().items())):
+        assert n1 == n2 and torch.equal(a, b)
+
+    packed = build_model("tiny-llama", seed=0, layer_hook=lambda layer: quantize_linears_(
+        layer, lambda lin: Linear4bit.from_linear(lin, "nf4", 64, torch.float32)))
+    with pytest.raises(NotImplementedError):
+        get_peft_model(packed, LoraConfig(r=4, lora_alpha=8, target_modules=["q_proj"])).merge_and_unload()
